@@ -1,0 +1,166 @@
+/* C-ABI of the B200 (sm_100a) paged KV-cache attention library.
+ *
+ * Plain C, plain pointers and sizes: this is the boundary a host binds
+ * (C++, ctypes, cgo, JNI ...).  Fixed instantiation, as in the reference
+ * (src/kernels/rope/rope.hpp:11-17): 64-wide heads, bf16, 4 query heads per
+ * KV head, 16-token cache blocks.  bf16 tensors are passed as `void*`.
+ *
+ * Every entry returns a status (PA_OK == 0) and never exits or throws;
+ * pa_last_error() gives the message of the calling thread's last failure.
+ * Kernel entries are asynchronous on the stream they are given and do no
+ * device synchronisation and no allocation.  A pool's host-side calls are not
+ * thread-safe per pool; calls on one pool that overlap on the GPU share its
+ * split-KV workspace and therefore must be ordered on one stream.
+ *
+ * Which reference interface each group replaces:
+ *   pool / sequence / block-table calls
+ *       src/pagedattention/paged_attention.hpp (declared, 0 bytes) and the
+ *       contiguous cache owned by runtime::Attention, src/runtime/attention.hpp:47-54,
+ *       src/runtime/attention.cu:74-98.
+ *   pa_append
+ *       launch_rope_qkv, src/kernels/rope/rope.hpp:52-63, plus the append loop
+ *       of Attention::forward, src/runtime/attention.cu:239-262.
+ *   pa_decode
+ *       transformer::launch_flash_attention with q_seq_len == 1,
+ *       src/kernels/flashattention/flashattention.h:54-76 as called at
+ *       src/runtime/attention.cu:278-334, plus launch_flash_output_layout,
+ *       src/runtime/layout.hpp:5-9.
+ *   pa_prefill
+ *       the same pair for q_seq_len > 1 (causal, kv_len = position + tokens,
+ *       src/runtime/attention.cu:303-313).
+ *   pa_gather_kv
+ *       Attention::get_key_cache / get_value_cache, src/runtime/attention.hpp:30-31
+ *       (hands back the [8, L, 64] view the reference keeps as its cache).
+ *   pa_build_rope_tables
+ *       LlamaRuntime::build_rope_tables, src/runtime/llama_runtime.cu:320-451.
+ */
+#ifndef PAGED_ATTENTION_H
+#define PAGED_ATTENTION_H
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PA_OK 0
+#define PA_ERR_INVALID_ARG 1
+#define PA_ERR_OUT_OF_BLOCKS 2
+#define PA_ERR_UNSUPPORTED 3
+#define PA_ERR_CUDA 4
+#define PA_ERR_TIMEOUT 5 /* a bounded device-side wait gave up */
+#define PA_ERR_STATE 6
+
+#define PA_HEAD_DIM 64
+#define PA_GROUP 4         /* query heads per KV head */
+#define PA_BLOCK_TOKENS 16 /* tokens per cache block */
+#define PA_TILE_BYTES 2048 /* one (block, head) K or V tile */
+
+typedef struct pa_pool pa_pool;
+
+const char* pa_last_error(void);
+
+/* ---- pool ----------------------------------------------------------------
+ * Device storage for `num_layers` caches of `num_blocks` blocks holding
+ * `kv_heads` KV heads each (8 for the whole model, 8/n when heads are sharded
+ * over n GPUs), the host free list, up to `max_seqs` block tables of
+ * `max_blocks_per_seq` entries (host + device mirror) and the split-KV
+ * workspace.  All device memory is allocated here, none per call. */
+int pa_pool_create(pa_pool** out, int device, int num_layers, int num_blocks,
+                   int kv_heads, int max_seqs, int max_blocks_per_seq);
+int pa_pool_destroy(pa_pool* pool);
+int pa_pool_free_blocks(const pa_pool* pool, int* n_free);
+/* Order in which free blocks are handed out (order[0] first).  Only valid
+ * while no block is in use; lets a seeded permutation reproduce a shuffled or
+ * fragmented table exactly. */
+int pa_pool_set_free_order(pa_pool* pool, const int32_t* order, int n);
+/* Raw device storage of one layer's cache (for inspection by tests) and its
+ * size in bytes.  Physical layout: tile(block, head, kv) at byte offset
+ * ((block * kv_heads + head) * 2 + kv) * 2048, kv = 0 for K, 1 for V; inside a
+ * tile token slot r (0..15) is a 128-byte row and its 16-byte chunk c (0..7)
+ * sits at chunk position c ^ (r & 7) — the 128-byte shared-memory swizzle, so
+ * a tile copied verbatim is bank-conflict free for ldmatrix and is the
+ * canonical K-major operand layout of tcgen05.mma. */
+int pa_pool_layer_storage(const pa_pool* pool, int layer, void** dev_ptr,
+                          uint64_t* bytes);
+
+/* ---- sequences and block tables (host) ------------------------------------ */
+int pa_seq_create(pa_pool* pool, int* seq_id);
+int pa_seq_free(pa_pool* pool, int seq_id);
+/* Grow the sequence to `new_len` tokens, taking blocks from the free list as
+ * needed.  All or nothing: PA_ERR_OUT_OF_BLOCKS leaves the sequence unchanged.
+ * Never shrinks; an unchanged length is a no-op. */
+int pa_seq_reserve(pa_pool* pool, int seq_id, int new_len);
+int pa_seq_length(const pa_pool* pool, int seq_id, int* len);
+/* Host view of the table: entry i holds the block of positions [16i, 16i+16).
+ * The pointer stays valid until the sequence is freed. */
+int pa_seq_block_table(const pa_pool* pool, int seq_id, const int32_t** table,
+                       int* n_blocks);
+
+/* ---- batch -----------------------------------------------------------------
+ * Names the sequences the following pa_append / pa_decode / pa_prefill calls
+ * work on, uploads pending block-table changes and the batch descriptor on
+ * `stream`.  Row i of the per-sequence tensors belongs to seq_ids[i].
+ * new_tokens[i] (NULL means 1 each) is how many tokens sequence i appends in
+ * this step: they occupy its last new_tokens[i] positions, i.e. the caller has
+ * already reserved the new length.  Token rows of q_in/k_in/v_in are the
+ * sequences' new tokens concatenated in batch order. */
+int pa_batch_set(pa_pool* pool, const int32_t* seq_ids, const int32_t* new_tokens,
+                 int n_seqs, void* stream);
+
+/* ---- kernels ---------------------------------------------------------------
+ * pa_append: RoPE (half-split pairs, fp32, round to nearest even) on the new
+ * tokens' Q and K, K and V scattered into the cache through the block table.
+ *   q_in  [rows][q_heads][64]   k_in, v_in [rows][kv_heads][64]   (bf16)
+ *   cos, sin fp32 [>= max position + 1][32]
+ *   q_out [rows][q_heads][64] (may alias q_in; may be NULL to skip Q)
+ * q_heads = 4 * kv_heads of the pool. */
+int pa_append(pa_pool* pool, int layer, const void* q_in, const void* k_in,
+              const void* v_in, const float* cos_table, const float* sin_table,
+              void* q_out, void* stream);
+
+/* pa_decode: one query token per batch sequence against its whole cache
+ * (split-KV over CTAs, log-sum-exp combine).
+ *   q        [n_seqs][q_heads][64] bf16 (RoPE applied)
+ *   out      bf16, row i at out + i*out_stride, q_heads*64 valid columns
+ *            (head-major: column h*64+d) — the [tokens, 2048] layout; may be NULL
+ *   out_f32  fp32 [n_seqs][q_heads][64], normalised; may be NULL
+ *   lse      fp32 [n_seqs][q_heads], natural-log-sum-exp of the scaled scores
+ *            (-inf for an empty sequence); may be NULL */
+int pa_decode(pa_pool* pool, int layer, const void* q, void* out,
+              int64_t out_stride, float* out_f32, float* lse, float scale,
+              void* stream);
+
+/* pa_prefill: causal attention of the batch's new tokens (batch of ONE
+ * sequence) against positions [0, kv_len) of its cache.
+ *   q   [rows][q_heads][64] bf16 (RoPE applied)   out [rows][q_heads*64] bf16
+ *   lse fp32 [q_heads][rows], may be NULL */
+int pa_prefill(pa_pool* pool, int layer, const void* q, void* out, float* lse,
+               float scale, void* stream);
+
+/* Merge split-KV partials from n_parts disjoint key ranges (e.g. one per GPU):
+ *   o_parts [n_parts][rows][64] fp32 normalised, lse_parts [n_parts][rows];
+ *   out bf16 [rows][64] (may be NULL), out_f32 / lse_out optional. */
+int pa_merge_partials(const float* o_parts, const float* lse_parts, int n_parts,
+                      int rows, void* out, float* out_f32, float* lse_out,
+                      void* stream);
+
+/* Un-page one sequence of the batch-independent cache: K and V as
+ * [kv_heads][out_stride_tokens][64] bf16, first `length` rows written. */
+int pa_gather_kv(pa_pool* pool, int layer, int seq_id, void* k_out, void* v_out,
+                 int out_stride_tokens, void* stream);
+
+/* Host: fp32 cos/sin tables [seq_len][32], Llama-3 frequency scaling. */
+int pa_build_rope_tables(float* cos_table, float* sin_table, int seq_len);
+
+/* Device status word of the pool: 0, or PA_ERR_TIMEOUT / PA_ERR_INVALID_ARG
+ * recorded by a kernel (bounded wait ran out, block id out of range).
+ * Synchronises `stream`, reads and clears the word. */
+int pa_pool_check(pa_pool* pool, void* stream);
+
+/* Tuning knobs (0 keeps the built-in heuristic): blocks per split-KV chunk. */
+int pa_pool_set_decode_chunk_blocks(pa_pool* pool, int chunk_blocks);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

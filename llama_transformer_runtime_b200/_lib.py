@@ -1,0 +1,75 @@
+"""ctypes loader of ``libpaged_attention.so`` (the C-ABI in include/paged_attention.h).
+
+There is no fallback: if the library is missing it is built with nvcc, and if
+that fails the import error is raised to the caller.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import build as _build
+
+_LIB = None
+
+# every symbol include/paged_attention.h declares (checked by the CPU tests)
+SYMBOLS = [
+    "pa_last_error", "pa_pool_create", "pa_pool_destroy", "pa_pool_free_blocks",
+    "pa_pool_set_free_order", "pa_pool_layer_storage", "pa_seq_create", "pa_seq_free",
+    "pa_seq_reserve", "pa_seq_length", "pa_seq_block_table", "pa_batch_set", "pa_append",
+    "pa_decode", "pa_prefill", "pa_merge_partials", "pa_gather_kv", "pa_build_rope_tables",
+    "pa_pool_check", "pa_pool_set_decode_chunk_blocks",
+]
+
+
+class PagedAttentionError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"[{code}] {msg}")
+        self.code = code
+
+
+def lib():
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = _build.LIB
+    if not os.path.exists(path):
+        _build.build()
+    L = C.CDLL(path)
+    vp, i, i64, f = C.c_void_p, C.c_int, C.c_int64, C.c_float
+    ip = C.POINTER(C.c_int)
+    L.pa_last_error.restype = C.c_char_p
+    L.pa_last_error.argtypes = []
+    sigs = {
+        "pa_pool_create": [C.POINTER(vp), i, i, i, i, i, i],
+        "pa_pool_destroy": [vp],
+        "pa_pool_free_blocks": [vp, ip],
+        "pa_pool_set_free_order": [vp, vp, i],
+        "pa_pool_layer_storage": [vp, i, C.POINTER(vp), C.POINTER(C.c_uint64)],
+        "pa_seq_create": [vp, ip],
+        "pa_seq_free": [vp, i],
+        "pa_seq_reserve": [vp, i, i],
+        "pa_seq_length": [vp, i, ip],
+        "pa_seq_block_table": [vp, i, C.POINTER(C.POINTER(C.c_int32)), ip],
+        "pa_batch_set": [vp, vp, vp, i, vp],
+        "pa_append": [vp, i, vp, vp, vp, vp, vp, vp, vp],
+        "pa_decode": [vp, i, vp, vp, i64, vp, vp, f, vp],
+        "pa_prefill": [vp, i, vp, vp, vp, f, vp],
+        "pa_merge_partials": [vp, vp, i, i, vp, vp, vp, vp],
+        "pa_gather_kv": [vp, i, i, vp, vp, i, vp],
+        "pa_build_rope_tables": [vp, vp, i],
+        "pa_pool_check": [vp, vp],
+        "pa_pool_set_decode_chunk_blocks": [vp, i],
+        "pa_debug_set_rope_variant": [vp, i],
+    }
+    for name, args in sigs.items():
+        fn = getattr(L, name)
+        fn.argtypes = args
+        fn.restype = i
+    _LIB = L
+    return L
+
+
+def check(code: int) -> None:
+    if code != 0:
+        raise PagedAttentionError(code, lib().pa_last_error().decode())

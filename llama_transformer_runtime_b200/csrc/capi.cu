@@ -1,0 +1,416 @@
+// C-ABI layer (include/paged_attention.h): argument checks, pool ownership and
+// launches.  No torch types, no exceptions across the boundary, no allocation
+// outside pa_pool_create.
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "../../include/paged_attention.h"
+#include "block_pool.hpp"
+#include "kernels.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define PA_CUDA(call)                                                                   \
+  do {                                                                                  \
+    cudaError_t _e = (call);                                                            \
+    if (_e != cudaSuccess)                                                              \
+      return fail(PA_ERR_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(_e),  \
+                  __FILE__, __LINE__);                                                  \
+  } while (0)
+
+constexpr int kWsItems = 148 * 32;  // split-KV partials the workspace can hold
+
+// Restores the caller's current device on scope exit.
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) != cudaSuccess) ok = false;
+    if (ok && prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+}  // namespace
+
+struct pa_pool {
+  pa::BlockPool host;
+  int device, num_layers, kv_heads;
+  size_t layer_bytes = 0;
+  char* storage = nullptr;
+  int32_t* d_tables = nullptr;
+  pa::BatchEntry* d_batch = nullptr;
+  float* ws_acc = nullptr;
+  float* ws_ml = nullptr;
+  unsigned int* ws_count = nullptr;
+  int* d_status = nullptr;
+  std::vector<pa::BatchEntry> batch;  // host copy of the active batch
+  int max_new = 0, total_rows = 0, max_kv_blocks = 0;
+  int chunk_blocks_override = 0;
+  int rope_variant = 1;
+  pa_pool(int nb, int ms, int mb) : host(nb, ms, mb) {}
+};
+
+extern "C" {
+
+const char* pa_last_error(void) { return g_err; }
+
+int pa_pool_create(pa_pool** out, int device, int num_layers, int num_blocks, int kv_heads,
+                   int max_seqs, int max_blocks_per_seq) {
+  if (!out) return fail(PA_ERR_INVALID_ARG, "pa_pool_create: out is NULL");
+  *out = nullptr;
+  if (num_layers <= 0 || num_blocks <= 0 || max_seqs <= 0 || max_blocks_per_seq <= 0)
+    return fail(PA_ERR_INVALID_ARG, "pa_pool_create: sizes must be positive");
+  if (kv_heads != 1 && kv_heads != 2 && kv_heads != 4 && kv_heads != 8)
+    return fail(PA_ERR_UNSUPPORTED, "pa_pool_create: kv_heads must be 1, 2, 4 or 8 (got %d)", kv_heads);
+  pa_pool* p = new (std::nothrow) pa_pool(num_blocks, max_seqs, max_blocks_per_seq);
+  if (!p) return fail(PA_ERR_INVALID_ARG, "pa_pool_create: out of host memory");
+  p->device = device;
+  p->num_layers = num_layers;
+  p->kv_heads = kv_heads;
+  p->layer_bytes = (size_t)num_blocks * kv_heads * pa::kPairBytes;
+  if (device >= 0) {
+    // device < 0 makes a host-only pool (allocator and tables, no kernels)
+    DeviceGuard g(device);
+    cudaError_t e = g.ok ? cudaSuccess : cudaErrorInvalidDevice;
+    auto alloc = [&](void** ptr, size_t bytes) {
+      if (e == cudaSuccess) e = cudaMalloc(ptr, bytes);
+      if (e == cudaSuccess) e = cudaMemset(*ptr, 0, bytes);
+    };
+    alloc((void**)&p->storage, p->layer_bytes * num_layers);
+    alloc((void**)&p->d_tables, (size_t)max_seqs * max_blocks_per_seq * sizeof(int32_t));
+    alloc((void**)&p->d_batch, (size_t)max_seqs * sizeof(pa::BatchEntry));
+    alloc((void**)&p->ws_acc, (size_t)kWsItems * pa::decode_ws_acc_floats_per_item() * sizeof(float));
+    alloc((void**)&p->ws_ml, (size_t)kWsItems * 2 * pa::kGroup * sizeof(float));
+    alloc((void**)&p->ws_count, (size_t)max_seqs * kv_heads * sizeof(unsigned int));
+    alloc((void**)&p->d_status, sizeof(int));
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+      int code = fail(PA_ERR_CUDA, "pa_pool_create: device allocation failed: %s", cudaGetErrorString(e));
+      cudaGetLastError();
+      pa_pool_destroy(p);
+      return code;
+    }
+  }
+  *out = p;
+  return PA_OK;
+}
+
+int pa_pool_destroy(pa_pool* p) {
+  if (!p) return PA_OK;
+  if (p->device >= 0) {
+    DeviceGuard g(p->device);
+    cudaFree(p->storage);
+    cudaFree(p->d_tables);
+    cudaFree(p->d_batch);
+    cudaFree(p->ws_acc);
+    cudaFree(p->ws_ml);
+    cudaFree(p->ws_count);
+    cudaFree(p->d_status);
+  }
+  delete p;
+  return PA_OK;
+}
+
+int pa_pool_free_blocks(const pa_pool* p, int* n_free) {
+  if (!p || !n_free) return fail(PA_ERR_INVALID_ARG, "pa_pool_free_blocks: NULL argument");
+  *n_free = p->host.free_blocks();
+  return PA_OK;
+}
+
+int pa_pool_set_free_order(pa_pool* p, const int32_t* order, int n) {
+  if (!p || !order) return fail(PA_ERR_INVALID_ARG, "pa_pool_set_free_order: NULL argument");
+  if (!p->host.set_free_order(order, n))
+    return fail(PA_ERR_INVALID_ARG,
+                "pa_pool_set_free_order: needs a permutation of all %d blocks while none is in use",
+                p->host.num_blocks());
+  return PA_OK;
+}
+
+int pa_pool_layer_storage(const pa_pool* p, int layer, void** dev_ptr, uint64_t* bytes) {
+  if (!p || layer < 0 || layer >= p->num_layers)
+    return fail(PA_ERR_INVALID_ARG, "pa_pool_layer_storage: bad pool or layer");
+  if (dev_ptr) *dev_ptr = p->storage ? p->storage + (size_t)layer * p->layer_bytes : nullptr;
+  if (bytes) *bytes = p->layer_bytes;
+  return PA_OK;
+}
+
+int pa_seq_create(pa_pool* p, int* seq_id) {
+  if (!p || !seq_id) return fail(PA_ERR_INVALID_ARG, "pa_seq_create: NULL argument");
+  int s = p->host.create();
+  if (s < 0) return fail(PA_ERR_OUT_OF_BLOCKS, "pa_seq_create: all %d sequence ids in use", p->host.max_seqs());
+  *seq_id = s;
+  return PA_OK;
+}
+
+int pa_seq_free(pa_pool* p, int seq_id) {
+  if (!p || !p->host.release(seq_id)) return fail(PA_ERR_INVALID_ARG, "pa_seq_free: unknown sequence %d", seq_id);
+  return PA_OK;
+}
+
+int pa_seq_reserve(pa_pool* p, int seq_id, int new_len) {
+  if (!p) return fail(PA_ERR_INVALID_ARG, "pa_seq_reserve: NULL pool");
+  int r = p->host.reserve(seq_id, new_len);
+  if (r == 1)
+    return fail(PA_ERR_INVALID_ARG, "pa_seq_reserve: bad sequence %d or length %d (table holds %d blocks)",
+                seq_id, new_len, p->host.max_blocks_per_seq());
+  if (r == 2)
+    return fail(PA_ERR_OUT_OF_BLOCKS, "pa_seq_reserve: %d free blocks cannot grow sequence %d to %d tokens",
+                p->host.free_blocks(), seq_id, new_len);
+  return PA_OK;
+}
+
+int pa_seq_length(const pa_pool* p, int seq_id, int* len) {
+  if (!p || !len || !p->host.valid(seq_id)) return fail(PA_ERR_INVALID_ARG, "pa_seq_length: bad argument");
+  *len = p->host.length(seq_id);
+  return PA_OK;
+}
+
+int pa_seq_block_table(const pa_pool* p, int seq_id, const int32_t** table, int* n_blocks) {
+  if (!p || !p->host.valid(seq_id)) return fail(PA_ERR_INVALID_ARG, "pa_seq_block_table: bad argument");
+  if (table) *table = p->host.table(seq_id);
+  if (n_blocks) *n_blocks = p->host.table_size(seq_id);
+  return PA_OK;
+}
+
+static int upload_tables(pa_pool* p, cudaStream_t st) {
+  const int mb = p->host.max_blocks_per_seq();
+  for (const auto& d : p->host.dirty()) {
+    if (d.hi <= d.lo) continue;
+    PA_CUDA(cudaMemcpyAsync(p->d_tables + (size_t)d.seq * mb + d.lo,
+                            p->host.all_tables() + (size_t)d.seq * mb + d.lo,
+                            (size_t)(d.hi - d.lo) * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+  }
+  p->host.clear_dirty();
+  return PA_OK;
+}
+
+int pa_batch_set(pa_pool* p, const int32_t* seq_ids, const int32_t* new_tokens, int n_seqs,
+                 void* stream) {
+  if (!p || !seq_ids) return fail(PA_ERR_INVALID_ARG, "pa_batch_set: NULL argument");
+  if (p->device < 0) return fail(PA_ERR_STATE, "pa_batch_set: host-only pool");
+  if (n_seqs <= 0 || n_seqs > p->host.max_seqs())
+    return fail(PA_ERR_INVALID_ARG, "pa_batch_set: n_seqs %d outside 1..%d", n_seqs, p->host.max_seqs());
+  std::vector<pa::BatchEntry> b(n_seqs);
+  int row = 0, max_new = 0, max_blocks = 0;
+  for (int i = 0; i < n_seqs; i++) {
+    if (!p->host.valid(seq_ids[i])) return fail(PA_ERR_INVALID_ARG, "pa_batch_set: unknown sequence %d", seq_ids[i]);
+    int nn = new_tokens ? new_tokens[i] : 1;
+    int len = p->host.length(seq_ids[i]);
+    if (nn < 0 || nn > len)
+      return fail(PA_ERR_INVALID_ARG, "pa_batch_set: sequence %d has %d tokens, cannot append %d", seq_ids[i], len, nn);
+    b[i] = {seq_ids[i], len, nn, row};
+    row += nn;
+    if (nn > max_new) max_new = nn;
+    if (p->host.table_size(seq_ids[i]) > max_blocks) max_blocks = p->host.table_size(seq_ids[i]);
+  }
+  DeviceGuard g(p->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  int r = upload_tables(p, st);
+  if (r != PA_OK) return r;
+  // pageable source: the runtime stages it before returning, so `b` may die
+  PA_CUDA(cudaMemcpyAsync(p->d_batch, b.data(), (size_t)n_seqs * sizeof(pa::BatchEntry),
+                          cudaMemcpyHostToDevice, st));
+  p->batch.swap(b);
+  p->max_new = max_new;
+  p->total_rows = row;
+  p->max_kv_blocks = max_blocks;
+  return PA_OK;
+}
+
+int pa_append(pa_pool* p, int layer, const void* q_in, const void* k_in, const void* v_in,
+              const float* cos_table, const float* sin_table, void* q_out, void* stream) {
+  if (!p || !k_in || !v_in || !cos_table || !sin_table)
+    return fail(PA_ERR_INVALID_ARG, "pa_append: NULL argument");
+  if (q_out && !q_in) return fail(PA_ERR_INVALID_ARG, "pa_append: q_out given without q_in");
+  if (p->device < 0) return fail(PA_ERR_STATE, "pa_append: host-only pool");
+  if (layer < 0 || layer >= p->num_layers) return fail(PA_ERR_INVALID_ARG, "pa_append: layer %d out of range", layer);
+  if (p->batch.empty()) return fail(PA_ERR_STATE, "pa_append: no active batch (call pa_batch_set)");
+  DeviceGuard g(p->device);
+  pa::AppendParams a;
+  a.q_in = (const __nv_bfloat16*)q_in;
+  a.k_in = (const __nv_bfloat16*)k_in;
+  a.v_in = (const __nv_bfloat16*)v_in;
+  a.q_out = (__nv_bfloat16*)q_out;
+  a.cos_table = cos_table;
+  a.sin_table = sin_table;
+  a.storage = p->storage + (size_t)layer * p->layer_bytes;
+  a.tables = p->d_tables;
+  a.batch = p->d_batch;
+  a.status = p->d_status;
+  a.kv_heads = p->kv_heads;
+  a.num_blocks = p->host.num_blocks();
+  a.max_blocks_per_seq = p->host.max_blocks_per_seq();
+  PA_CUDA(pa::launch_append(a, (int)p->batch.size(), p->max_new, p->rope_variant, (cudaStream_t)stream));
+  return PA_OK;
+}
+
+// Blocks per split-KV chunk: aim at about two CTAs per resident slot
+// (3 CTAs of 4 warps per SM on 148 SMs), at least one block per warp and
+// stage, and never more chunks than the workspace can hold.
+static int pick_chunk_blocks(const pa_pool* p) {
+  if (p->chunk_blocks_override > 0) return p->chunk_blocks_override;
+  long long total = 0;
+  for (const auto& e : p->batch) total += (e.kv_len + pa::kBlockTokens - 1) / pa::kBlockTokens;
+  total *= p->kv_heads;
+  const long long target_ctas = 148 * 3 * 2;
+  long long cb = (total + target_ctas - 1) / target_ctas;
+  if (cb < 16) cb = 16;
+  return (int)cb;
+}
+
+int pa_decode(pa_pool* p, int layer, const void* q, void* out, int64_t out_stride, float* out_f32,
+              float* lse, float scale, void* stream) {
+  if (!p || !q) return fail(PA_ERR_INVALID_ARG, "pa_decode: NULL argument");
+  if (!out && !out_f32) return fail(PA_ERR_INVALID_ARG, "pa_decode: no output buffer");
+  if (p->device < 0) return fail(PA_ERR_STATE, "pa_decode: host-only pool");
+  if (layer < 0 || layer >= p->num_layers) return fail(PA_ERR_INVALID_ARG, "pa_decode: layer %d out of range", layer);
+  if (p->batch.empty()) return fail(PA_ERR_STATE, "pa_decode: no active batch (call pa_batch_set)");
+  if (out && out_stride < (int64_t)p->kv_heads * pa::kGroup * pa::kHeadDim)
+    return fail(PA_ERR_INVALID_ARG, "pa_decode: out_stride %lld shorter than a row", (long long)out_stride);
+  const int n_seqs = (int)p->batch.size();
+  int cb = pick_chunk_blocks(p);
+  int max_chunks = (p->max_kv_blocks + cb - 1) / cb;
+  if (max_chunks < 1) max_chunks = 1;
+  while ((long long)max_chunks * p->kv_heads * n_seqs > kWsItems) {
+    cb *= 2;
+    max_chunks = (p->max_kv_blocks + cb - 1) / cb;
+    if (max_chunks < 1) max_chunks = 1;
+    if (max_chunks == 1) break;
+  }
+  if ((long long)max_chunks * p->kv_heads * n_seqs > kWsItems && max_chunks > 1)
+    return fail(PA_ERR_UNSUPPORTED, "pa_decode: batch too large for the split-KV workspace");
+  DeviceGuard g(p->device);
+  pa::DecodeParams d;
+  d.q = (const __nv_bfloat16*)q;
+  d.out = (__nv_bfloat16*)out;
+  d.out_f32 = out_f32;
+  d.lse = lse;
+  d.storage = p->storage + (size_t)layer * p->layer_bytes;
+  d.tables = p->d_tables;
+  d.batch = p->d_batch;
+  d.ws_acc = p->ws_acc;
+  d.ws_ml = p->ws_ml;
+  d.ws_count = p->ws_count;
+  d.status = p->d_status;
+  d.out_stride = out_stride;
+  d.scale_log2 = scale * pa::kLog2e;
+  d.kv_heads = p->kv_heads;
+  d.num_blocks = p->host.num_blocks();
+  d.max_blocks_per_seq = p->host.max_blocks_per_seq();
+  d.chunk_blocks = cb;
+  d.max_chunks = max_chunks;
+  PA_CUDA(pa::launch_decode(d, n_seqs, (cudaStream_t)stream));
+  return PA_OK;
+}
+
+int pa_prefill(pa_pool* p, int layer, const void* q, void* out, float* lse, float scale, void* stream) {
+  (void)p; (void)layer; (void)q; (void)out; (void)lse; (void)scale; (void)stream;
+  return fail(PA_ERR_UNSUPPORTED, "pa_prefill: not built yet");
+}
+
+int pa_merge_partials(const float* o_parts, const float* lse_parts, int n_parts, int rows, void* out,
+                      float* out_f32, float* lse_out, void* stream) {
+  if (!o_parts || !lse_parts || n_parts <= 0 || rows <= 0)
+    return fail(PA_ERR_INVALID_ARG, "pa_merge_partials: bad argument");
+  if (!out && !out_f32) return fail(PA_ERR_INVALID_ARG, "pa_merge_partials: no output buffer");
+  pa::MergeParams m{o_parts, lse_parts, (__nv_bfloat16*)out, out_f32, lse_out, n_parts, rows};
+  PA_CUDA(pa::launch_merge(m, (cudaStream_t)stream));
+  return PA_OK;
+}
+
+int pa_gather_kv(pa_pool* p, int layer, int seq_id, void* k_out, void* v_out, int out_stride_tokens,
+                 void* stream) {
+  if (!p || !k_out || !v_out) return fail(PA_ERR_INVALID_ARG, "pa_gather_kv: NULL argument");
+  if (p->device < 0) return fail(PA_ERR_STATE, "pa_gather_kv: host-only pool");
+  if (layer < 0 || layer >= p->num_layers || !p->host.valid(seq_id))
+    return fail(PA_ERR_INVALID_ARG, "pa_gather_kv: bad layer or sequence");
+  const int len = p->host.length(seq_id);
+  if (out_stride_tokens < len) return fail(PA_ERR_INVALID_ARG, "pa_gather_kv: out_stride_tokens %d < length %d", out_stride_tokens, len);
+  DeviceGuard g(p->device);
+  int r = upload_tables(p, (cudaStream_t)stream);
+  if (r != PA_OK) return r;
+  pa::GatherParams gp;
+  gp.storage = p->storage + (size_t)layer * p->layer_bytes;
+  gp.table = p->d_tables + (size_t)seq_id * p->host.max_blocks_per_seq();
+  gp.k_out = (__nv_bfloat16*)k_out;
+  gp.v_out = (__nv_bfloat16*)v_out;
+  gp.status = p->d_status;
+  gp.kv_heads = p->kv_heads;
+  gp.num_blocks = p->host.num_blocks();
+  gp.length = len;
+  gp.out_stride = out_stride_tokens;
+  PA_CUDA(pa::launch_gather(gp, (cudaStream_t)stream));
+  return PA_OK;
+}
+
+// Host fp32 tables exactly as the reference builds them
+// (src/runtime/llama_runtime.cu:320-451): float arithmetic throughout,
+// theta 500000, Llama-3 scaling (factor 32, low 1, high 4, original context 8192).
+int pa_build_rope_tables(float* cos_table, float* sin_table, int seq_len) {
+  if (!cos_table || !sin_table || seq_len <= 0) return fail(PA_ERR_INVALID_ARG, "pa_build_rope_tables: bad argument");
+  const float theta = 500000.0f, factor = 32.0f, low_ff = 1.0f, high_ff = 4.0f, orig = 8192.0f;
+  for (int pair = 0; pair < 32; pair++) {
+    const float inv_freq = 1.0f / std::pow(theta, (float)(2 * pair) / 64.0f);
+    const float wavelen = 2.0f * (float)M_PI / inv_freq;
+    float inv;
+    if (wavelen < orig / high_ff) {
+      inv = inv_freq;
+    } else if (wavelen <= orig / low_ff) {
+      const float smooth = (orig / wavelen - low_ff) / (high_ff - low_ff);
+      inv = (1.0f - smooth) * (inv_freq / factor) + smooth * inv_freq;
+    } else {
+      inv = inv_freq / factor;
+    }
+    for (int pos = 0; pos < seq_len; pos++) {
+      const float angle = (float)pos * inv;
+      cos_table[(size_t)pos * 32 + pair] = std::cos(angle);
+      sin_table[(size_t)pos * 32 + pair] = std::sin(angle);
+    }
+  }
+  return PA_OK;
+}
+
+int pa_pool_check(pa_pool* p, void* stream) {
+  if (!p || p->device < 0) return fail(PA_ERR_INVALID_ARG, "pa_pool_check: bad pool");
+  DeviceGuard g(p->device);
+  int st = 0;
+  PA_CUDA(cudaMemcpyAsync(&st, p->d_status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  PA_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  if (st == 0) return PA_OK;
+  PA_CUDA(cudaMemsetAsync(p->d_status, 0, sizeof(int), (cudaStream_t)stream));
+  if (st == pa::kStatusTimeout) return fail(PA_ERR_TIMEOUT, "a kernel gave up waiting for a bulk copy");
+  return fail(PA_ERR_INVALID_ARG, "a kernel met a block id outside the pool");
+}
+
+int pa_pool_set_decode_chunk_blocks(pa_pool* p, int chunk_blocks) {
+  if (!p || chunk_blocks < 0) return fail(PA_ERR_INVALID_ARG, "pa_pool_set_decode_chunk_blocks: bad argument");
+  p->chunk_blocks_override = chunk_blocks;
+  return PA_OK;
+}
+
+// Test hook: selects how y0 = x0*c - x1*s is rounded in pa_append (0, 1, 2 as
+// in rope_pair); the default is the form that matches the reference kernel.
+int pa_debug_set_rope_variant(pa_pool* p, int variant) {
+  if (!p || variant < 0 || variant > 2) return fail(PA_ERR_INVALID_ARG, "pa_debug_set_rope_variant: bad argument");
+  p->rope_variant = variant;
+  return PA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,332 @@
+// K2: paged split-KV GQA decode attention with an in-kernel log-sum-exp combine.
+//
+// Replaces the reference's use of its prefill kernel at q_seq_len == 1
+// (src/kernels/flashattention/flashattention.cu:98-376 as launched from
+// src/runtime/attention.cu:303-334: one CTA per query head walking the whole
+// sequence, K/V read once per query head) and the separate output transpose
+// (src/runtime/layout.cu:11-42).
+//
+// Decode is an HBM stream: 4 KiB (K tile + V tile of one block and KV head)
+// per 16 tokens, read exactly once for the 4 query heads that share it.
+//   * grid (chunk, kv head, sequence); a CTA owns a contiguous run of blocks of
+//     the sequence's table, its warps take them round-robin;
+//   * every warp runs its own ring of STAGES 4 KiB buffers filled by bulk
+//     (TMA) copies that complete on per-stage mbarriers, so WARPS*STAGES*4 KiB
+//     are in flight per CTA and no CTA-wide barrier sits in the loop;
+//   * tiles land in shared memory exactly as stored (rows of 128 bytes, chunks
+//     XOR-swizzled), which ldmatrix reads without bank conflicts;
+//   * the 4 query heads are rows 0..3 of an m16n8k16 A fragment (rows 4..15
+//     zero); scores and P*V use mma.sync, softmax is done on the accumulator
+//     fragments with quad shuffles, base 2, fp32 (numerics of the reference
+//     kernel: scale after the dot product, sum of un-rounded probabilities,
+//     probabilities rounded to bf16 for P*V, flashattention.cu:249-336);
+//   * warps merge through shared memory; chunks merge through a workspace, the
+//     last CTA to arrive for a (sequence, KV head) does the combine and writes
+//     the [tokens, 2048]-layout row directly.
+#include "kernels.cuh"
+
+namespace pa {
+
+namespace {
+
+template <int WARPS, int STAGES>
+struct DecodeSmem {
+  static constexpr int kTiles = WARPS * STAGES * kPairBytes;
+  static constexpr int kBars = WARPS * STAGES * 8;
+  static constexpr int kMergeFloats = WARPS * (kGroup * kHeadDim + 2 * kGroup);
+  static constexpr int kBytes = 128 + kTiles + kBars + kMergeFloats * 4 + 16;
+};
+
+__device__ __forceinline__ void write_row_outputs(const DecodeParams& p, int z, int h, int r, int d,
+                                                  float o, float m, float l) {
+  const int q_heads = p.kv_heads * kGroup;
+  const int head = h * kGroup + r;
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  const float v = o * inv;
+  if (p.out) p.out[(size_t)z * p.out_stride + head * kHeadDim + d] = __float2bfloat16_rn(v);
+  if (p.out_f32) p.out_f32[((size_t)z * q_heads + head) * kHeadDim + d] = v;
+  if (p.lse && d == 0)
+    p.lse[(size_t)z * q_heads + head] = l > 0.f ? kLn2 * (m + log2f(l)) : -INFINITY;
+}
+
+template <int WARPS, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32)
+decode_kernel(DecodeParams p) {
+  using S = DecodeSmem<WARPS, STAGES>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem =
+      reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+  unsigned char* tiles = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kTiles);
+  float* mrg = reinterpret_cast<float*>(smem + S::kTiles + S::kBars);
+  float* mrg_o = mrg;                                // [WARPS][4][64]
+  float* mrg_m = mrg + WARPS * kGroup * kHeadDim;     // [WARPS][4]
+  float* mrg_l = mrg_m + WARPS * kGroup;              // [WARPS][4]
+  __shared__ unsigned int s_ticket;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int x = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
+  const BatchEntry e = p.batch[z];
+  const int n_blocks = (e.kv_len + kBlockTok - 1) / kBlockTok;
+  const int n_chunks = max(1, (n_blocks + p.chunk_blocks - 1) / p.chunk_blocks);
+  if (x >= n_chunks) return;
+  const int blk_lo = x * p.chunk_blocks;
+  const int cnt = max(0, min(n_blocks, blk_lo + p.chunk_blocks) - blk_lo);
+  const int my_n = cnt > warp ? (cnt - warp + WARPS - 1) / WARPS : 0;
+  const int32_t* table = p.tables + (size_t)e.seq * p.max_blocks_per_seq + blk_lo + warp;
+  const int q_heads = p.kv_heads * kGroup;
+
+  const uint32_t tile0 = smem_u32(tiles) + warp * STAGES * kPairBytes;
+  const uint32_t bar0 = smem_u32(bars) + warp * STAGES * 8;
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; s++) mbar_init(bar0 + s * 8, 1);
+    mbar_fence_init();
+    fence_proxy_async_smem();
+  }
+  __syncwarp();
+
+  // Block-table entries of this warp's blocks, 32 at a time, one per lane.
+  int tbase = 0;
+  int tbl_reg = lane < my_n ? table[(size_t)lane * WARPS] : 0;
+  const char* head_base = p.storage + (size_t)h * kPairBytes;
+  const size_t block_stride = (size_t)p.kv_heads * kPairBytes;
+
+  auto issue = [&](int i) {
+    if (i >= tbase + 32) {
+      tbase += 32;
+      const int ii = tbase + lane;
+      tbl_reg = ii < my_n ? table[(size_t)ii * WARPS] : 0;
+    }
+    int blk = __shfl_sync(0xffffffffu, tbl_reg, i - tbase);
+    if (lane == 0) {
+      if (blk < 0 || blk >= p.num_blocks) {
+        atomicExch(p.status, kStatusBadBlock);
+        blk = 0;
+      }
+      const int st = i % STAGES;
+      mbar_expect_tx(bar0 + st * 8, kPairBytes);
+      bulk_g2s(tile0 + st * kPairBytes, head_base + (size_t)blk * block_stride, kPairBytes,
+               bar0 + st * 8);
+    }
+  };
+
+  for (int i = 0; i < STAGES && i < my_n; i++) issue(i);
+
+  // Query fragments: rows 0..3 are the group's heads, the rest zero.
+  const int qrow = lane >> 2, qcol = (lane & 3) * 2;
+  uint32_t qa[4][4];
+#pragma unroll
+  for (int ks = 0; ks < 4; ks++) {
+    qa[ks][0] = qa[ks][1] = qa[ks][2] = qa[ks][3] = 0u;
+    if (qrow < kGroup) {
+      const __nv_bfloat16* qp =
+          p.q + ((size_t)z * q_heads + h * kGroup + qrow) * kHeadDim + ks * 16 + qcol;
+      qa[ks][0] = *reinterpret_cast<const uint32_t*>(qp);
+      qa[ks][2] = *reinterpret_cast<const uint32_t*>(qp + 8);
+    }
+  }
+
+  float o[8][4];
+#pragma unroll
+  for (int nt = 0; nt < 8; nt++) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;
+
+  const int mj = lane >> 3, rr = lane & 7;
+  const uint32_t k_row_off = (uint32_t)(((mj >> 1) * 8 + rr) * 128);
+  const uint32_t v_row_off = (uint32_t)(kTileBytes + ((mj & 1) * 8 + rr) * 128);
+  bool failed = false;
+
+  for (int i = 0; i < my_n; i++) {
+    const int st = i % STAGES;
+    const bool ok = mbar_wait(bar0 + st * 8, (uint32_t)((i / STAGES) & 1));
+    if (!__all_sync(0xffffffffu, ok)) {
+      failed = true;
+      break;
+    }
+    const uint32_t tile = tile0 + st * kPairBytes;
+
+    float s[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < 4; ks++) {
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4(b0, b1, b2, b3, tile + k_row_off + ((((ks * 2 + (mj & 1)) ^ rr)) << 4));
+      mma_bf16(s[0], qa[ks], b0, b1);
+      mma_bf16(s[1], qa[ks], b2, b3);
+    }
+
+    // scaled scores (base 2), tail mask, online softmax on rows lane/4
+    const int key0 = (blk_lo + warp + i * WARPS) * kBlockTok + qcol;
+    float t[4];
+    t[0] = s[0][0] * p.scale_log2;
+    t[1] = s[0][1] * p.scale_log2;
+    t[2] = s[1][0] * p.scale_log2;
+    t[3] = s[1][1] * p.scale_log2;
+    if (key0 + 9 >= e.kv_len) {
+      if (key0 >= e.kv_len) t[0] = -INFINITY;
+      if (key0 + 1 >= e.kv_len) t[1] = -INFINITY;
+      if (key0 + 8 >= e.kv_len) t[2] = -INFINITY;
+      if (key0 + 9 >= e.kv_len) t[3] = -INFINITY;
+    }
+    float mx = fmaxf(fmaxf(t[0], t[1]), fmaxf(t[2], t[3]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);
+    const float corr = ex2(m_run - m_new);
+    m_run = m_new;
+    const float p0 = ex2(t[0] - m_new), p1 = ex2(t[1] - m_new);
+    const float p2 = ex2(t[2] - m_new), p3 = ex2(t[3] - m_new);
+    l_run = l_run * corr + ((p0 + p1) + (p2 + p3));
+    uint32_t pa[4];
+    pa[0] = pack_bf16(p0, p1);
+    pa[1] = 0u;
+    pa[2] = pack_bf16(p2, p3);
+    pa[3] = 0u;
+#pragma unroll
+    for (int nt = 0; nt < 8; nt++) {
+      o[nt][0] *= corr;
+      o[nt][1] *= corr;
+    }
+#pragma unroll
+    for (int np = 0; np < 4; np++) {
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4_t(b0, b1, b2, b3, tile + v_row_off + ((((np * 2 + (mj >> 1)) ^ rr)) << 4));
+      mma_bf16(o[2 * np], pa, b0, b1);
+      mma_bf16(o[2 * np + 1], pa, b2, b3);
+    }
+
+    __syncwarp();
+    if (i + STAGES < my_n) {
+      if (lane == 0) fence_proxy_async_smem();
+      issue(i + STAGES);
+    }
+  }
+  if (failed && lane == 0) atomicExch(p.status, kStatusTimeout);
+
+  // ---- merge the warps of this CTA -------------------------------------------
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  if (qrow < kGroup) {
+    float* orow = mrg_o + (warp * kGroup + qrow) * kHeadDim;
+#pragma unroll
+    for (int nt = 0; nt < 8; nt++)
+      *reinterpret_cast<float2*>(orow + nt * 8 + qcol) = make_float2(o[nt][0], o[nt][1]);
+    if ((lane & 3) == 0) {
+      mrg_m[warp * kGroup + qrow] = m_run;
+      mrg_l[warp * kGroup + qrow] = l_run;
+    }
+  }
+  __syncthreads();
+
+  const int item = (z * p.kv_heads + h) * p.max_chunks + x;
+  for (int idx = threadIdx.x; idx < kGroup * kHeadDim; idx += WARPS * 32) {
+    const int r = idx >> 6, d = idx & 63;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; w++) M = fmaxf(M, mrg_m[w * kGroup + r]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; w++) {
+      const float mw = mrg_m[w * kGroup + r];
+      const float wgt = mw == -INFINITY ? 0.f : ex2(mw - M);
+      L += wgt * mrg_l[w * kGroup + r];
+      O += wgt * mrg_o[(w * kGroup + r) * kHeadDim + d];
+    }
+    if (n_chunks == 1) {
+      write_row_outputs(p, z, h, r, d, O, M, L);
+    } else {
+      p.ws_acc[(size_t)item * (kGroup * kHeadDim) + idx] = O;
+      if (d == 0) {
+        p.ws_ml[(size_t)item * (2 * kGroup) + r] = M;
+        p.ws_ml[(size_t)item * (2 * kGroup) + kGroup + r] = L;
+      }
+    }
+  }
+  if (n_chunks == 1) return;
+
+  // ---- combine across chunks: the last CTA to arrive does it ---------------
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_ticket = atomicAdd(&p.ws_count[z * p.kv_heads + h], 1u);
+  __syncthreads();
+  if (s_ticket != (unsigned)(n_chunks - 1)) return;
+  __threadfence();
+
+  const size_t item0 = (size_t)(z * p.kv_heads + h) * p.max_chunks;
+  for (int idx = threadIdx.x; idx < kGroup * kHeadDim; idx += WARPS * 32) {
+    const int r = idx >> 6, d = idx & 63;
+    float M = -INFINITY;
+    for (int c = 0; c < n_chunks; c++)
+      M = fmaxf(M, __ldcg(p.ws_ml + (item0 + c) * (2 * kGroup) + r));
+    float L = 0.f, O = 0.f;
+    for (int c = 0; c < n_chunks; c++) {
+      const float mc = __ldcg(p.ws_ml + (item0 + c) * (2 * kGroup) + r);
+      const float wgt = mc == -INFINITY ? 0.f : ex2(mc - M);
+      L += wgt * __ldcg(p.ws_ml + (item0 + c) * (2 * kGroup) + kGroup + r);
+      O += wgt * __ldcg(p.ws_acc + (item0 + c) * (kGroup * kHeadDim) + idx);
+    }
+    write_row_outputs(p, z, h, r, d, O, M, L);
+  }
+  if (threadIdx.x == 0) p.ws_count[z * p.kv_heads + h] = 0u;
+}
+
+template <int WARPS, int STAGES>
+cudaError_t launch_decode_cfg(const DecodeParams& p, int n_seqs, cudaStream_t stream) {
+  using S = DecodeSmem<WARPS, STAGES>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(decode_kernel<WARPS, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  dim3 grid(p.max_chunks, p.kv_heads, n_seqs);
+  decode_kernel<WARPS, STAGES><<<grid, WARPS * 32, S::kBytes, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+size_t decode_ws_acc_floats_per_item() { return kGroup * kHeadDim; }
+
+cudaError_t launch_decode(const DecodeParams& p, int n_seqs, cudaStream_t stream) {
+  if (n_seqs <= 0) return cudaSuccess;
+  return launch_decode_cfg<4, 4>(p, n_seqs, stream);
+}
+
+// ---- merge of split-KV partials from disjoint key ranges ---------------------
+// One thread per output element; n_parts is small (one part per GPU).
+__global__ void __launch_bounds__(256)
+merge_kernel(MergeParams p) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= p.rows * kHeadDim) return;
+  const int r = idx >> 6;
+  float M = -INFINITY;
+  for (int k = 0; k < p.n_parts; k++) M = fmaxf(M, p.lse_parts[(size_t)k * p.rows + r]);
+  float L = 0.f, O = 0.f;
+  if (M > -INFINITY) {
+    for (int k = 0; k < p.n_parts; k++) {
+      const float lk = p.lse_parts[(size_t)k * p.rows + r];
+      const float w = lk == -INFINITY ? 0.f : __expf(lk - M);
+      L += w;
+      O += w * p.o_parts[(size_t)k * p.rows * kHeadDim + idx];
+    }
+  }
+  const float v = L > 0.f ? O / L : 0.f;
+  if (p.out) p.out[idx] = __float2bfloat16_rn(v);
+  if (p.out_f32) p.out_f32[idx] = v;
+  if (p.lse_out && (idx & 63) == 0) p.lse_out[r] = L > 0.f ? M + __logf(L) : -INFINITY;
+}
+
+cudaError_t launch_merge(const MergeParams& p, cudaStream_t stream) {
+  if (p.rows <= 0 || p.n_parts <= 0) return cudaSuccess;
+  const int total = p.rows * kHeadDim;
+  merge_kernel<<<(total + 255) / 256, 256, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace pa

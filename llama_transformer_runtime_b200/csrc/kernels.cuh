@@ -1,0 +1,65 @@
+// Launch descriptors and launcher prototypes of the sm_100a kernels.
+#pragma once
+#include "pa_common.cuh"
+
+namespace pa {
+
+struct AppendParams {
+  const __nv_bfloat16* q_in;
+  const __nv_bfloat16* k_in;
+  const __nv_bfloat16* v_in;
+  __nv_bfloat16* q_out;  // nullptr: leave Q alone
+  const float* cos_table;
+  const float* sin_table;
+  char* storage;              // this layer's cache
+  const int32_t* tables;      // device mirror [max_seqs][max_blocks_per_seq]
+  const BatchEntry* batch;    // device, n_seqs entries
+  int* status;
+  int kv_heads, num_blocks, max_blocks_per_seq;
+};
+cudaError_t launch_append(const AppendParams& p, int n_seqs, int max_new, int rope_variant,
+                          cudaStream_t stream);
+
+struct GatherParams {
+  const char* storage;
+  const int32_t* table;  // device row of one sequence
+  __nv_bfloat16* k_out;
+  __nv_bfloat16* v_out;
+  int* status;
+  int kv_heads, num_blocks, length, out_stride;
+};
+cudaError_t launch_gather(const GatherParams& p, cudaStream_t stream);
+
+// Split-KV decode.  Grid (max_chunks, kv_heads, n_seqs); CTA (x, h, z) streams
+// blocks [x*chunk_blocks, (x+1)*chunk_blocks) of sequence z's table for KV head
+// h and serves the 4 query heads of that group.
+struct DecodeParams {
+  const __nv_bfloat16* q;     // [n_seqs][q_heads][64]
+  __nv_bfloat16* out;         // bf16 rows, stride out_stride elements (nullable)
+  float* out_f32;             // [n_seqs][q_heads][64] (nullable)
+  float* lse;                 // [n_seqs][q_heads] (nullable)
+  const char* storage;
+  const int32_t* tables;
+  const BatchEntry* batch;
+  float* ws_acc;              // workspace: [item][4][64] un-normalised partial sums
+  float* ws_ml;               // workspace: [item][2][4] running max (base-2 scaled) and sum
+  unsigned int* ws_count;     // arrival tickets, one per (batch row, kv head), zero between launches
+  int* status;
+  long long out_stride;
+  float scale_log2;           // scale * log2(e)
+  int kv_heads, num_blocks, max_blocks_per_seq, chunk_blocks, max_chunks;
+};
+cudaError_t launch_decode(const DecodeParams& p, int n_seqs, cudaStream_t stream);
+size_t decode_ws_acc_floats_per_item();
+
+struct MergeParams {
+  const float* o_parts;    // [n_parts][rows][64]
+  const float* lse_parts;  // [n_parts][rows]
+  __nv_bfloat16* out;      // [rows][64] (nullable)
+  float* out_f32;          // nullable
+  float* lse_out;          // nullable
+  int n_parts, rows;
+};
+cudaError_t launch_merge(const MergeParams& p, cudaStream_t stream);
+
+}  // namespace pa

@@ -1,0 +1,150 @@
+"""Thin Python view of the C-ABI, used by the tests and the bench.
+
+Every method forwards to one ``pa_*`` entry of ``libpaged_attention.so``; no
+arithmetic happens here.  Device buffers are passed as torch CUDA tensors (or
+raw integer addresses); torch is only the owner of that memory.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from ._lib import check, lib
+
+HEAD_DIM = 64
+GROUP = 4
+BLOCK_TOKENS = 16
+TILE_BYTES = 2048
+
+
+def _ptr(x):
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    if isinstance(x, np.ndarray):
+        return x.ctypes.data
+    return x.data_ptr()
+
+
+def build_rope_tables(seq_len: int):
+    """fp32 cos/sin tables [seq_len, 32] (host), as the reference's runtime builds them."""
+    cos = np.empty((seq_len, 32), np.float32)
+    sin = np.empty((seq_len, 32), np.float32)
+    check(lib().pa_build_rope_tables(cos.ctypes.data, sin.ctypes.data, seq_len))
+    return cos, sin
+
+
+def physical_chunk_offset(block: int, kv_heads: int, head: int, kv: int, slot: int, chunk: int) -> int:
+    """Byte offset, inside one layer's storage, of 16-byte chunk ``chunk`` of token
+    slot ``slot`` of tile (block, head, K if kv == 0 else V)."""
+    return (((block * kv_heads + head) * 2 + kv) * TILE_BYTES + slot * 128
+            + ((chunk ^ (slot & 7)) << 4))
+
+
+class KVPool:
+    """Paged KV cache of one GPU: storage, block allocator, block tables."""
+
+    def __init__(self, num_layers: int, num_blocks: int, kv_heads: int = 8, max_seqs: int = 1,
+                 max_blocks_per_seq: int | None = None, device: int = 0):
+        self._h = C.c_void_p()
+        self.num_layers, self.num_blocks, self.kv_heads = num_layers, num_blocks, kv_heads
+        self.q_heads = kv_heads * GROUP
+        self.max_seqs = max_seqs
+        self.max_blocks_per_seq = max_blocks_per_seq or num_blocks
+        self.device = device
+        check(lib().pa_pool_create(C.byref(self._h), device, num_layers, num_blocks, kv_heads,
+                                   max_seqs, self.max_blocks_per_seq))
+
+    def close(self) -> None:
+        if self._h:
+            lib().pa_pool_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- allocator / tables (host) ----
+    def free_blocks(self) -> int:
+        n = C.c_int()
+        check(lib().pa_pool_free_blocks(self._h, C.byref(n)))
+        return n.value
+
+    def set_free_order(self, order) -> None:
+        o = np.ascontiguousarray(order, np.int32)
+        check(lib().pa_pool_set_free_order(self._h, o.ctypes.data, int(o.size)))
+
+    def create_seq(self) -> int:
+        s = C.c_int()
+        check(lib().pa_seq_create(self._h, C.byref(s)))
+        return s.value
+
+    def free_seq(self, seq: int) -> None:
+        check(lib().pa_seq_free(self._h, seq))
+
+    def reserve(self, seq: int, new_len: int) -> None:
+        check(lib().pa_seq_reserve(self._h, seq, new_len))
+
+    def length(self, seq: int) -> int:
+        n = C.c_int()
+        check(lib().pa_seq_length(self._h, seq, C.byref(n)))
+        return n.value
+
+    def block_table(self, seq: int) -> np.ndarray:
+        t = C.POINTER(C.c_int32)()
+        n = C.c_int()
+        check(lib().pa_seq_block_table(self._h, seq, C.byref(t), C.byref(n)))
+        if n.value == 0:
+            return np.zeros((0,), np.int32)
+        return np.ctypeslib.as_array(t, shape=(n.value,)).copy()
+
+    def layer_storage(self, layer: int):
+        p = C.c_void_p()
+        b = C.c_uint64()
+        check(lib().pa_pool_layer_storage(self._h, layer, C.byref(p), C.byref(b)))
+        return p.value, b.value
+
+    # ---- device work ----
+    def batch_set(self, seq_ids, new_tokens=None, stream: int = 0) -> None:
+        s = np.ascontiguousarray(seq_ids, np.int32)
+        nt = None if new_tokens is None else np.ascontiguousarray(new_tokens, np.int32)
+        check(lib().pa_batch_set(self._h, s.ctypes.data, None if nt is None else nt.ctypes.data,
+                                 int(s.size), stream))
+
+    def append(self, layer: int, q_in, k_in, v_in, cos, sin, q_out, stream: int = 0) -> None:
+        check(lib().pa_append(self._h, layer, _ptr(q_in), _ptr(k_in), _ptr(v_in), _ptr(cos),
+                              _ptr(sin), _ptr(q_out), stream))
+
+    def decode(self, layer: int, q, out=None, out_stride: int | None = None, out_f32=None,
+               lse=None, scale: float = 0.125, stream: int = 0) -> None:
+        if out_stride is None:
+            out_stride = self.q_heads * HEAD_DIM
+        check(lib().pa_decode(self._h, layer, _ptr(q), _ptr(out), out_stride, _ptr(out_f32),
+                              _ptr(lse), scale, stream))
+
+    def prefill(self, layer: int, q, out, lse=None, scale: float = 0.125, stream: int = 0) -> None:
+        check(lib().pa_prefill(self._h, layer, _ptr(q), _ptr(out), _ptr(lse), scale, stream))
+
+    def gather_kv(self, layer: int, seq: int, k_out, v_out, out_stride_tokens: int,
+                  stream: int = 0) -> None:
+        check(lib().pa_gather_kv(self._h, layer, seq, _ptr(k_out), _ptr(v_out), out_stride_tokens,
+                                 stream))
+
+    def check(self, stream: int = 0) -> None:
+        check(lib().pa_pool_check(self._h, stream))
+
+    def set_decode_chunk_blocks(self, n: int) -> None:
+        check(lib().pa_pool_set_decode_chunk_blocks(self._h, n))
+
+    def _set_rope_variant(self, v: int) -> None:
+        check(lib().pa_debug_set_rope_variant(self._h, v))
+
+
+def merge_partials(o_parts, lse_parts, n_parts: int, rows: int, out=None, out_f32=None,
+                   lse_out=None, stream: int = 0) -> None:
+    check(lib().pa_merge_partials(_ptr(o_parts), _ptr(lse_parts), n_parts, rows, _ptr(out),
+                                  _ptr(out_f32), _ptr(lse_out), stream))

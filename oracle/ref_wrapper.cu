@@ -1,0 +1,119 @@
+// TEST INFRASTRUCTURE — not part of the product.
+//
+// extern "C" handles onto the reference's own, unmodified CUDA entry points
+// for the KV-cache attention path, so tests and the bench's reference arm can
+// drive them through ctypes.  The reference sources are compiled where they
+// lie (see oracle/Makefile); nothing from them is copied into this file.
+//
+// What each handle calls in the reference:
+//   ref_rope_qkv            -> launch_rope_qkv            (src/kernels/rope/rope.hpp:52-63)
+//   ref_flash_attention     -> transformer::launch_flash_attention
+//                              (src/kernels/flashattention/flashattention.h:54-76)
+//   ref_flash_output_layout -> launch_flash_output_layout (src/runtime/layout.hpp:5-9)
+//   ref_append_*            -> the append the reference performs inline in
+//                              Attention::forward (src/runtime/attention.cu:239-262):
+//                              2*8*tokens device-to-device copies of 128 bytes.
+//                              That loop is not a callable function in the
+//                              reference, so it is restated here twice: literally
+//                              (one cudaMemcpy per 128 bytes) and as one strided
+//                              cudaMemcpy2DAsync per head, which moves the same bytes.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "flashattention.h"
+#include "layout.hpp"
+#include "rope.hpp"
+
+extern "C" {
+
+void ref_rope_qkv(const void* q_in, void* q_out, const void* k_in, void* k_out,
+                  const void* v_in, void* v_out, float* cos_table,
+                  float* sin_table, int tokens, int position_offset) {
+  launch_rope_qkv((const __nv_bfloat16*)q_in, (__nv_bfloat16*)q_out,
+                  (const __nv_bfloat16*)k_in, (__nv_bfloat16*)k_out,
+                  (const __nv_bfloat16*)v_in, (__nv_bfloat16*)v_out, cos_table,
+                  sin_table, tokens, position_offset);
+}
+
+// Field-by-field fill of the reference's launch descriptor, exactly as
+// Attention::forward does it (src/runtime/attention.cu:278-328).
+void ref_flash_attention(const void* Q, const void* K, const void* V, void* O,
+                         float* L, int batch, int heads, int kv_heads,
+                         int q_seq_len, int kv_seq_len, int kv_stride,
+                         float scale, int causal, void* stream) {
+  transformer::FlashAttentionParams p{};
+  p.Q = Q;
+  p.K = K;
+  p.V = V;
+  p.O = O;
+  p.L = L;
+  p.batch_size = batch;
+  p.num_heads = heads;
+  p.num_kv_heads = kv_heads;
+  p.q_seq_len = q_seq_len;
+  p.kv_seq_len = kv_seq_len;
+  p.kv_stride = kv_stride;
+  p.d_head = 64;
+  p.scale = scale;
+  p.causal = causal != 0;
+  p.dtype = transformer::DType::BF16;
+  p.stream = (cudaStream_t)stream;
+  transformer::launch_flash_attention(p);
+}
+
+void ref_flash_output_layout(const void* in, void* out, int tokens) {
+  launch_flash_output_layout((const __nv_bfloat16*)in, (__nv_bfloat16*)out,
+                             tokens);
+}
+
+// Literal restatement of the append loop: k_flash/v_flash are [8, tokens, 64],
+// the caches are [8, max_seq_len, 64].
+int ref_append_memcpy_loop(void* key_cache, void* value_cache,
+                           const void* k_flash, const void* v_flash,
+                           int max_seq_len, int position, int tokens) {
+  __nv_bfloat16* kc = (__nv_bfloat16*)key_cache;
+  __nv_bfloat16* vc = (__nv_bfloat16*)value_cache;
+  const __nv_bfloat16* kf = (const __nv_bfloat16*)k_flash;
+  const __nv_bfloat16* vf = (const __nv_bfloat16*)v_flash;
+  for (int h = 0; h < 8; h++) {
+    for (int t = 0; t < tokens; t++) {
+      cudaError_t e1 = cudaMemcpy(
+          kc + (size_t)h * max_seq_len * 64 + (size_t)(position + t) * 64,
+          kf + (size_t)h * tokens * 64 + (size_t)t * 64,
+          64 * sizeof(__nv_bfloat16), cudaMemcpyDeviceToDevice);
+      cudaError_t e2 = cudaMemcpy(
+          vc + (size_t)h * max_seq_len * 64 + (size_t)(position + t) * 64,
+          vf + (size_t)h * tokens * 64 + (size_t)t * 64,
+          64 * sizeof(__nv_bfloat16), cudaMemcpyDeviceToDevice);
+      if (e1 != cudaSuccess || e2 != cudaSuccess) return 1;
+    }
+  }
+  return 0;
+}
+
+// Same bytes, one strided copy per head and tensor (16 API calls instead of
+// 16*tokens), so that a kernel-to-kernel comparison is not drowned by the
+// reference's host loop.
+int ref_append_strided(void* key_cache, void* value_cache, const void* k_flash,
+                       const void* v_flash, int max_seq_len, int position,
+                       int tokens, void* stream) {
+  __nv_bfloat16* kc = (__nv_bfloat16*)key_cache;
+  __nv_bfloat16* vc = (__nv_bfloat16*)value_cache;
+  const __nv_bfloat16* kf = (const __nv_bfloat16*)k_flash;
+  const __nv_bfloat16* vf = (const __nv_bfloat16*)v_flash;
+  size_t bytes = (size_t)tokens * 64 * sizeof(__nv_bfloat16);
+  for (int h = 0; h < 8; h++) {
+    cudaError_t e1 = cudaMemcpyAsync(
+        kc + (size_t)h * max_seq_len * 64 + (size_t)position * 64,
+        kf + (size_t)h * tokens * 64, bytes, cudaMemcpyDeviceToDevice,
+        (cudaStream_t)stream);
+    cudaError_t e2 = cudaMemcpyAsync(
+        vc + (size_t)h * max_seq_len * 64 + (size_t)position * 64,
+        vf + (size_t)h * tokens * 64, bytes, cudaMemcpyDeviceToDevice,
+        (cudaStream_t)stream);
+    if (e1 != cudaSuccess || e2 != cudaSuccess) return 1;
+  }
+  return 0;
+}
+
+}  // extern "C"

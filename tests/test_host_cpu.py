@@ -1,0 +1,137 @@
+"""CPU checks of the product's host side: the C-ABI library loads and exports
+what the header declares, the C++ block allocator matches the model, argument
+errors come back as status codes.  No kernel is launched."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+from llama_transformer_runtime_b200 import _lib, paged
+from oracle import oracle as orc
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared(header):
+    src = open(os.path.join(ROOT, "include", header)).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b((?:pa|lt)_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_library_exports_every_declared_symbol():
+    L = _lib.lib()
+    names = _declared("paged_attention.h")
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(L, n), n
+    assert sorted(set(_lib.SYMBOLS)) == [n for n in names if n in _lib.SYMBOLS]
+    assert set(names) <= set(_lib.SYMBOLS) | {"pa_debug_set_rope_variant"}, set(names) - set(_lib.SYMBOLS)
+
+
+def test_rope_tables_equal_oracle_bits():
+    cos, sin = paged.build_rope_tables(4200)
+    oc, os_ = orc.build_rope_tables(4200)
+    assert np.array_equal(cos, oc) and np.array_equal(sin, os_)
+
+
+def host_pool(nb, max_seqs=8, mb=None):
+    return paged.KVPool(1, nb, 8, max_seqs, mb, device=-1)
+
+
+def test_allocator_matches_model_under_random_traffic():
+    rng = np.random.default_rng(7)
+    nb = 257
+    order = rng.permutation(nb)
+    pool = host_pool(nb, 16, 64)
+    pool.set_free_order(order)
+    model = orc.BlockPoolModel(nb, order)
+    live = []
+    for step in range(3000):
+        op = rng.integers(0, 10)
+        if op < 2 and len(live) < 16:
+            s = pool.create_seq()
+            assert s == model.create()
+            live.append(s)
+        elif op < 3 and live:
+            s = live.pop(rng.integers(0, len(live)))
+            pool.free_seq(s)
+            model.release(s)
+        elif live:
+            s = live[rng.integers(0, len(live))]
+            new_len = model.lens[s] + int(rng.integers(0, 40))
+            if (new_len + 15) // 16 > 64:
+                continue
+            ok = model.reserve(s, new_len)
+            if ok:
+                pool.reserve(s, new_len)
+            else:
+                with pytest.raises(_lib.PagedAttentionError) as ei:
+                    pool.reserve(s, new_len)
+                assert ei.value.code == 2
+            assert pool.length(s) == model.lens[s]
+            assert pool.block_table(s).tolist() == model.tables[s]
+        assert pool.free_blocks() == len(model.free)
+    used = [b for s in live for b in pool.block_table(s).tolist()]
+    assert len(used) == len(set(used)) and len(used) + pool.free_blocks() == nb
+
+
+def test_reserve_semantics():
+    pool = host_pool(4, 2, 4)
+    s = pool.create_seq()
+    pool.reserve(s, 0)
+    assert pool.block_table(s).size == 0
+    pool.reserve(s, 1)
+    assert pool.block_table(s).tolist() == [0]
+    pool.reserve(s, 16)
+    pool.reserve(s, 5)  # never shrinks, no-op
+    assert pool.length(s) == 16 and pool.block_table(s).tolist() == [0]
+    pool.reserve(s, 17)
+    assert pool.block_table(s).tolist() == [0, 1]  # entry i covers positions [16i, 16i+16)
+    with pytest.raises(_lib.PagedAttentionError) as ei:
+        pool.reserve(s, 16 * 4 + 1)  # table too small
+    assert ei.value.code == 1
+    t = pool.create_seq()
+    with pytest.raises(_lib.PagedAttentionError) as ei:
+        pool.reserve(t, 16 * 3)  # only 2 blocks left
+    assert ei.value.code == 2 and pool.length(t) == 0 and pool.free_blocks() == 2
+    with pytest.raises(_lib.PagedAttentionError):
+        pool.create_seq()  # both ids in use
+    with pytest.raises(_lib.PagedAttentionError):
+        pool.set_free_order(np.arange(4))  # blocks in use
+    pool.free_seq(s)
+    pool.free_seq(t)
+    with pytest.raises(_lib.PagedAttentionError):
+        pool.free_seq(t)
+    with pytest.raises(_lib.PagedAttentionError):
+        pool.set_free_order([0, 1, 1, 2])
+    pool.set_free_order([3, 2, 1, 0])
+    s = pool.create_seq()
+    pool.reserve(s, 40)
+    assert pool.block_table(s).tolist() == [3, 2, 1]
+
+
+def test_argument_errors_are_status_codes():
+    L = _lib.lib()
+    h = C.c_void_p()
+    assert L.pa_pool_create(C.byref(h), -1, 1, 0, 8, 1, 1) == 1
+    assert L.pa_pool_create(C.byref(h), -1, 1, 4, 3, 1, 1) == 3
+    assert b"kv_heads" in L.pa_last_error()
+    pool = host_pool(4)
+    s = pool.create_seq()
+    pool.reserve(s, 3)
+    with pytest.raises(_lib.PagedAttentionError) as ei:
+        pool.batch_set([s])  # host-only pool has no device side
+    assert ei.value.code == 6
+    with pytest.raises(_lib.PagedAttentionError):
+        pool.decode(0, 1, out=1)
+    assert L.pa_merge_partials(None, None, 1, 1, None, None, None, None) == 1
+
+
+def test_physical_layout_formula():
+    # 16-byte chunks of one tile are a permutation of its 2048 bytes
+    offs = sorted(paged.physical_chunk_offset(0, 8, 0, 0, r, c) for r in range(16) for c in range(8))
+    assert offs == list(range(0, 2048, 16))
+    assert paged.physical_chunk_offset(5, 8, 3, 1, 0, 0) == ((5 * 8 + 3) * 2 + 1) * 2048
+    assert paged.physical_chunk_offset(0, 8, 0, 0, 9, 2) == 9 * 128 + ((2 ^ 1) << 4)
