@@ -1,0 +1,471 @@
+"""Benchmark of the paged KV-cache decode path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload decode128k|decode4k]
+
+Default workload (decode128k): long-context decode, batch 1, context 131072 x 16
+layers (about 4.3 GB of bf16 paged KV, 16-token blocks, seeded random fragmented
+block table), KV values N(0,1)*0.5.  One step = one new token: per layer a fused
+RoPE + paged append, then paged GQA decode attention over the whole cache.
+With N GPUs the sequence is split by token range over the ranks (strong
+scaling); every layer ends with an exchange of the ranks' (O, LSE) partials and
+a log-sum-exp merge.
+
+metric  paged_decode_attn_hbm_gbs = algorithmic cache bytes streamed per second,
+        sum over ranks: steps x layers x (2048 L + 8192 + 4 ceil(L/16)) / time.
+        The line also carries us_per_token (time per step).
+value   inputs resident in HBM.      e2e   host buffers: per step the new
+        token's q/k/v for all layers go host->device from pinned memory and the
+        attention outputs come back, inside the timed region.
+The cache is 4.3 GB per step (268 MB per layer) — larger than L2, no flush needed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+LAYERS = 16
+Q_HEADS, KV_HEADS, D = 32, 8, 64
+BLOCK = 16
+WORKLOADS = {
+    "decode128k": dict(ctx=131072, name="decode_ctx131072_x16layers_batch1"),
+    "decode4k": dict(ctx=4096, name="decode_ctx4096_x16layers_batch1"),
+}
+
+
+def decode_bytes(L: int) -> int:
+    """Algorithmic bytes of one layer's decode over a context of L tokens:
+    K+V read once, Q read, O written, block table read."""
+    return 2 * KV_HEADS * L * D * 2 + 2 * Q_HEADS * D * 2 + 4 * ((L + BLOCK - 1) // BLOCK)
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# ncu capture of decode_kernel (profiles/): dram read+write bytes per launch for
+# the workload, or None when not captured.
+NCU_TRAFFIC_BYTES = {"decode128k": None, "decode4k": None}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "200"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def mark(self):
+        return len(self.rows)
+
+    def stop(self, lo: int = 0, hi: int | None = None):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        rows = [r for r in self.rows[lo:hi] if len(r) >= 6] or [r for r in self.rows if len(r) >= 6]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
+        sm = [float(r[0]) for r in rows if r[0].replace(".", "").isdigit()]
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": float(rows[0][1]) if rows[0][1].replace(".", "").isdigit() else None,
+                "reasons": reasons, "samples": len(rows)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+def token_ranges(L: int, n: int):
+    """Split [0, L) into n contiguous ranges on 16-token block borders."""
+    blocks = (L + BLOCK - 1) // BLOCK
+    cuts = [min(L, (blocks * r // n) * BLOCK) for r in range(n)] + [L]
+    return [(cuts[r], cuts[r + 1]) for r in range(n)]
+
+
+# =============================================================================
+# our arm
+# =============================================================================
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from llama_transformer_runtime_b200 import paged
+
+    rank, local_rank, world = dist_env()
+    torch.cuda.set_device(local_rank)
+    dev = f"cuda:{local_rank}"
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+    wl = WORKLOADS[args.workload]
+    ctx = wl["ctx"]
+    total_steps = args.warmup + 2 * args.steps + 8
+    lo, hi = token_ranges(ctx, world)[rank]
+    local_len = hi - lo
+    owner = world - 1  # the last range takes the appended tokens
+    cap_tokens = local_len + (total_steps if rank == owner else 0)
+    need_blocks = (cap_tokens + BLOCK - 1) // BLOCK
+    num_blocks = need_blocks + need_blocks // 4 + 8  # fragmented: table scattered over a larger pool
+
+    pool = paged.KVPool(LAYERS, num_blocks, KV_HEADS, 1, need_blocks + 1, device=local_rank)
+    rng = np.random.default_rng(1234 + rank)
+    pool.set_free_order(rng.permutation(num_blocks))
+    seq = pool.create_seq()
+
+    # ---- fill the cache: N(0,1)*0.5, generated on the device, appended with the identity rotation
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4321 + rank)
+    chunk = 8192
+    ones = torch.ones(chunk, 32, dtype=torch.float32, device=dev)
+    zeros = torch.zeros(chunk, 32, dtype=torch.float32, device=dev)
+    for c0 in range(0, local_len, chunk):
+        n = min(chunk, local_len - c0)
+        pool.reserve(seq, c0 + n)
+        pool.batch_set([seq], [n])
+        for layer in range(LAYERS):
+            k = (torch.randn(n, KV_HEADS, D, generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+            v = (torch.randn(n, KV_HEADS, D, generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+            pool.append(layer, None, k, v, ones, zeros, None)
+    torch.cuda.synchronize()
+    del ones, zeros
+
+    cos_h, sin_h = paged.build_rope_tables(ctx + total_steps + 1)
+    cos = torch.from_numpy(cos_h).to(dev)
+    sin = torch.from_numpy(sin_h).to(dev)
+
+    # ---- per-step inputs (all layers), host pinned + device
+    q_host = (torch.randn(LAYERS, 1, Q_HEADS, D, generator=torch.Generator().manual_seed(7))).to(torch.bfloat16).pin_memory()
+    k_host = (torch.randn(LAYERS, 1, KV_HEADS, D, generator=torch.Generator().manual_seed(8))).to(torch.bfloat16).pin_memory()
+    v_host = (torch.randn(LAYERS, 1, KV_HEADS, D, generator=torch.Generator().manual_seed(9))).to(torch.bfloat16).pin_memory()
+    out_host = torch.zeros(LAYERS, 1, Q_HEADS * D, dtype=torch.bfloat16).pin_memory()
+    q_dev, k_dev, v_dev = q_host.to(dev), k_host.to(dev), v_host.to(dev)
+    q_rot = torch.empty_like(q_dev)
+    out_dev = torch.zeros(LAYERS, 1, Q_HEADS * D, dtype=torch.bfloat16, device=dev)
+    if world > 1:
+        part = torch.zeros(LAYERS, Q_HEADS * D + Q_HEADS, dtype=torch.float32, device=dev)  # [O | lse] per layer
+        gathered = torch.zeros(LAYERS, world, Q_HEADS * D + Q_HEADS, dtype=torch.float32, device=dev)
+        o_parts = torch.zeros(world, Q_HEADS, D, dtype=torch.float32, device=dev)
+        l_parts = torch.zeros(world, Q_HEADS, dtype=torch.float32, device=dev)
+
+    state = {"global_len": ctx, "launches": 0}
+
+    def step(qs, ks, vs, outs):
+        """One token: every layer appends and attends over the whole context."""
+        state["global_len"] += 1
+        g = state["global_len"]
+        if rank == owner:
+            pool.reserve(seq, pool.length(seq) + 1)
+        if world == 1:
+            pool.batch_set([seq])
+            pool.decode_step(0, LAYERS, qs, ks, vs, Q_HEADS * D, KV_HEADS * D, cos, sin, q_rot, outs,
+                             Q_HEADS * D, Q_HEADS * D)
+            state["launches"] += 2 * LAYERS
+            return
+        pool.batch_set_sharded([seq], [1 if rank == owner else 0], [1], [g - 1], [lo])
+        for layer in range(LAYERS):
+            pool.append(layer, qs[layer], ks[layer], vs[layer], cos, sin, q_rot[layer])
+            pool.decode(layer, q_rot[layer], None, 0, part[layer, :Q_HEADS * D], part[layer, Q_HEADS * D:])
+            dist.all_gather_into_tensor(gathered[layer].view(-1), part[layer])
+            o_parts.copy_(gathered[layer, :, :Q_HEADS * D].reshape(world, Q_HEADS, D))
+            l_parts.copy_(gathered[layer, :, Q_HEADS * D:])
+            paged.merge_partials(o_parts, l_parts, world, Q_HEADS, outs[layer])
+            state["launches"] += 3
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def resident_step():
+        step(q_dev, k_dev, v_dev, out_dev)
+
+    def e2e_step():
+        q_dev.copy_(q_host, non_blocking=True)
+        k_dev.copy_(k_host, non_blocking=True)
+        v_dev.copy_(v_host, non_blocking=True)
+        step(q_dev, k_dev, v_dev, out_dev)
+        out_host.copy_(out_dev, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller reads the result every step
+
+    for _ in range(args.warmup):
+        resident_step()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    m0 = sampler.mark()
+    len_before = state["global_len"]
+    state["launches"] = 0
+    ms = timed(resident_step, args.steps)
+    launches = state["launches"]
+    len_after = state["global_len"]
+    m1 = sampler.mark()
+    bytes_timed = sum(LAYERS * decode_bytes(L) for L in range(len_before + 1, len_after + 1))
+    value = bytes_timed / (ms * 1e-3) / 1e9
+
+    len_before = state["global_len"]
+    ms_e2e = timed(e2e_step, args.steps)
+    bytes_e2e = sum(LAYERS * decode_bytes(L) for L in range(len_before + 1, state["global_len"] + 1))
+    e2e_value = bytes_e2e / (ms_e2e * 1e-3) / 1e9
+    h2d = (q_host.numel() + k_host.numel() + v_host.numel()) * 2
+    d2h = out_host.numel() * 2
+
+    # ---- dominant kernel alone: 16 back-to-back decode launches (one per layer) per event pair
+    pool.batch_set_sharded([seq], [0], [1], [state["global_len"] - 1], [lo])
+    L_local = pool.length(seq)
+    f32o = torch.zeros(1, Q_HEADS, D, dtype=torch.float32, device=dev)
+
+    def decode_only():
+        for layer in range(LAYERS):
+            pool.decode(layer, q_rot[layer], out_dev[layer], Q_HEADS * D, None, None)
+
+    decode_only()
+    reps = max(3, args.steps)
+    ms_k = timed(decode_only, reps) / (reps * LAYERS)
+    kern_bytes = decode_bytes(L_local)
+    achieved = kern_bytes / (ms_k * 1e-3) / 1e9
+    peak, peak_kind = measured_peak()
+    pool.check()
+
+    line = None
+    if rank == 0:
+        clocks = sampler.stop(m0, m1)
+        line = {
+            "metric": "paged_decode_attn_hbm_gbs", "value": round(value, 1), "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms / args.steps, 4),
+            "us_per_token": round(ms / args.steps * 1e3, 2),
+            "us_per_token_per_layer": round(ms / args.steps * 1e3 / LAYERS, 2),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": wl["name"], "context": ctx, "layers": LAYERS, "batch": 1,
+                       "q_heads": Q_HEADS, "kv_heads": KV_HEADS, "head_dim": D, "block_tokens": BLOCK,
+                       "block_table": "seeded random permutation over a pool 25% larger than the sequence",
+                       "parallelism": "1 GPU" if world == 1 else f"sequence range split over {world} GPUs, NCCL all-gather of (O, LSE) per layer + merge",
+                       "l2": f"inputs larger than L2 ({decode_bytes(ctx) * LAYERS / 1e9:.2f} GB streamed per step)"},
+            "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": round(ms_e2e / args.steps, 4)},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "kernel": "decode_kernel", "achieved": round(achieved, 1),
+                         "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                         "peak_source": f"of {peak_kind}", "frac_of_nominal_8000": round(achieved / 8000.0, 4),
+                         "us_per_launch": round(ms_k * 1e3, 2), "bytes_per_launch": kern_bytes,
+                         "traffic": NCU_TRAFFIC_BYTES.get(args.workload)},
+        }
+        if world == 1:
+            line["cpu_baseline"] = cpu_baseline(pool, seq, q_rot, out_dev, L_local)
+        print(json.dumps(line), flush=True)
+    barrier()
+    pool.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(pool, seq, q_rot, out_dev, L):
+    """The CPU oracle (fp32 naive attention, OpenMP) on a bounded sample: layer
+    0 of this workload, repeated for about ten seconds; its answer is also the
+    check of the GPU output of that layer."""
+    import torch
+
+    from oracle import oracle as orc
+
+    dev = q_rot.device
+    k = torch.zeros(KV_HEADS, L, D, dtype=torch.bfloat16, device=dev)
+    v = torch.zeros_like(k)
+    pool.gather_kv(0, seq, k, v, L)
+    torch.cuda.synchronize()
+    k_h = k.view(torch.int16).cpu().numpy().view(np.uint16)
+    v_h = v.view(torch.int16).cpu().numpy().view(np.uint16)
+    q_h = q_rot[0].view(torch.int16).cpu().numpy().view(np.uint16).reshape(Q_HEADS, 1, D)
+    del k, v
+    t0 = time.perf_counter()
+    O, _ = orc.attention(q_h, k_h, v_h, L)
+    t1 = time.perf_counter() - t0
+    reps = 1
+    budget = 10.0
+    while t1 * reps < budget and reps < 64:
+        orc.attention(q_h, k_h, v_h, L)
+        reps += 1
+    total = time.perf_counter() - t0
+    got = orc.bf16_to_f32(out_dev[0].view(torch.int16).cpu().numpy().view(np.uint16)).reshape(-1)
+    err = float(np.max(np.abs(got - O[:, 0].reshape(-1))))
+    return {"value": round(decode_bytes(L) * reps / total / 1e9, 3), "unit": "GB/s",
+            "cores": orc.num_threads(), "kind": "port",
+            "sample": f"layer 0 of the workload (context {L}), {reps} passes of the fp32 CPU oracle",
+            "gpu_vs_cpu_max_abs_err": err}
+
+
+# =============================================================================
+# reference arm: the reference's own CUDA kernels (oracle/_ref/libref.so) on this GPU
+# =============================================================================
+def run_reference(args):
+    rank, local_rank, world = dist_env()
+    if rank != 0:
+        return
+    from oracle import oracle as orc
+
+    if not orc.ref_available():
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libref.so was not built (no reference checkout at build time)"}))
+        return
+    import torch
+
+    torch.cuda.set_device(local_rank)
+    dev = f"cuda:{local_rank}"
+    ref = orc.ref()
+    wl = WORKLOADS[args.workload]
+    ctx = wl["ctx"]
+    total_steps = args.warmup + 2 * args.steps + 4
+    max_seq = ctx + total_steps + 1
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4321)
+    # the reference's cache: per layer K and V [8, max_seq, 64], zero-initialised
+    kc = torch.zeros(LAYERS, KV_HEADS, max_seq, D, dtype=torch.bfloat16, device=dev)
+    vc = torch.zeros_like(kc)
+    for layer in range(LAYERS):
+        kc[layer, :, :ctx] = (torch.randn(KV_HEADS, ctx, D, generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+        vc[layer, :, :ctx] = (torch.randn(KV_HEADS, ctx, D, generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+    cos_h, sin_h = orc.build_rope_tables(max_seq)
+    cos, sin = torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev)
+    q_host = torch.randn(LAYERS, 1, Q_HEADS, D, generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).pin_memory()
+    k_host = torch.randn(LAYERS, 1, KV_HEADS, D, generator=torch.Generator().manual_seed(8)).to(torch.bfloat16).pin_memory()
+    v_host = torch.randn(LAYERS, 1, KV_HEADS, D, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16).pin_memory()
+    out_host = torch.zeros(LAYERS, 1, Q_HEADS * D, dtype=torch.bfloat16).pin_memory()
+    q_dev, k_dev, v_dev = q_host.to(dev), k_host.to(dev), v_host.to(dev)
+    qf = torch.empty(Q_HEADS, 1, D, dtype=torch.bfloat16, device=dev)
+    kf = torch.empty(KV_HEADS, 1, D, dtype=torch.bfloat16, device=dev)
+    vf = torch.empty(KV_HEADS, 1, D, dtype=torch.bfloat16, device=dev)
+    of = torch.empty(Q_HEADS, 1, D, dtype=torch.bfloat16, device=dev)
+    out_dev = torch.zeros(LAYERS, 1, Q_HEADS * D, dtype=torch.bfloat16, device=dev)
+    state = {"len": ctx}
+
+    def step():
+        """What Attention::forward does per layer for one token (steps 5-7):
+        launch_rope_qkv, the 128-byte append copies, launch_flash_attention with
+        q_seq_len 1, launch_flash_output_layout."""
+        pos = state["len"]
+        state["len"] += 1
+        for layer in range(LAYERS):
+            ref.ref_rope_qkv(q_dev[layer].data_ptr(), qf.data_ptr(), k_dev[layer].data_ptr(), kf.data_ptr(),
+                             v_dev[layer].data_ptr(), vf.data_ptr(), cos.data_ptr(), sin.data_ptr(), 1, pos)
+            ref.ref_append_memcpy_loop(kc[layer].data_ptr(), vc[layer].data_ptr(), kf.data_ptr(), vf.data_ptr(),
+                                       max_seq, pos, 1)
+            ref.ref_flash_attention(qf.data_ptr(), kc[layer].data_ptr(), vc[layer].data_ptr(), of.data_ptr(),
+                                    None, 1, Q_HEADS, KV_HEADS, 1, pos + 1, max_seq, 0.125, 1, None)
+            ref.ref_flash_output_layout(of.data_ptr(), out_dev[layer].data_ptr(), 1)
+
+    def e2e_step():
+        q_dev.copy_(q_host, non_blocking=True)
+        k_dev.copy_(k_host, non_blocking=True)
+        v_dev.copy_(v_host, non_blocking=True)
+        step()
+        out_host.copy_(out_dev, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def timed(fn, n):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = state["len"]
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        b = sum(LAYERS * decode_bytes(L) for L in range(l0 + 1, state["len"] + 1))
+        return e0.elapsed_time(e1), b
+
+    for _ in range(args.warmup):
+        step()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.3)
+    ms, b = timed(step, args.steps)
+    clocks = sampler.stop()
+    ms2, b2 = timed(e2e_step, args.steps)
+    value = b / (ms * 1e-3) / 1e9
+    e2e = b2 / (ms2 * 1e-3) / 1e9
+    print(json.dumps({
+        "impl": "reference", "metric": "paged_decode_attn_hbm_gbs", "value": round(value, 2), "unit": "GB/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4),
+        "us_per_token": round(ms / args.steps * 1e3, 2), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": wl["name"], "context": ctx, "layers": LAYERS, "batch": 1,
+                   "note": "the reference's own CUDA kernels (flashattention.cu, rope.cu, layout.cu compiled "
+                           "unmodified for sm_100a) on this GPU, contiguous cache, single GPU only"},
+        "e2e": {"value": round(e2e, 2), "unit": "GB/s",
+                "h2d_bytes_per_step": (q_host.numel() + k_host.numel() + v_host.numel()) * 2,
+                "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": round(ms2 / args.steps, 4)},
+        "gpu_launches": args.steps * LAYERS * 5, "clocks": clocks,
+        "cpu_baseline": {"value": round(value, 2), "unit": "GB/s", "cores": 0, "kind": "reference",
+                         "sample": "whole workload; the reference has no CPU implementation of this path, "
+                                   "so its CUDA kernels run on the GPU (host cores only drive the launches)"},
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode128k", choices=sorted(WORKLOADS))
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

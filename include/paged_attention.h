@@ -107,6 +107,17 @@ int pa_seq_block_table(const pa_pool* pool, int seq_id, const int32_t** table,
 int pa_batch_set(pa_pool* pool, const int32_t* seq_ids, const int32_t* new_tokens,
                  int n_seqs, void* stream);
 
+/* The same for sequences whose cache is sharded by token range over several
+ * pools (one per GPU): the local cache of sequence i starts at RoPE position
+ * kv_pos_offset[i]; it appends new_tokens[i] (possibly 0) tokens locally while
+ * q_rows[i] query rows, the first at RoPE position q_pos[i], are rotated for
+ * it.  NULL arrays take the defaults of pa_batch_set (offset 0, one query row
+ * per new token, positions following the cache). */
+int pa_batch_set_sharded(pa_pool* pool, const int32_t* seq_ids,
+                         const int32_t* new_tokens, const int32_t* q_rows,
+                         const int32_t* q_pos, const int32_t* kv_pos_offset,
+                         int n_seqs, void* stream);
+
 /* ---- kernels ---------------------------------------------------------------
  * pa_append: RoPE (half-split pairs, fp32, round to nearest even) on the new
  * tokens' Q and K, K and V scattered into the cache through the block table.
@@ -129,6 +140,21 @@ int pa_append(pa_pool* pool, int layer, const void* q_in, const void* k_in,
 int pa_decode(pa_pool* pool, int layer, const void* q, void* out,
               int64_t out_stride, float* out_f32, float* lse, float scale,
               void* stream);
+
+/* pa_decode_step: one decode step over layers [layer_begin, layer_end): per
+ * layer a pa_append of the batch's new tokens followed by a pa_decode, all on
+ * `stream` — the attention part of the reference's layer loop
+ * (Transformer::forward, src/runtime/transformer.cu:47-89, calling steps 5-7 of
+ * Attention::forward, src/runtime/attention.cu:192-359) without a host round
+ * trip per layer.  Layer l reads q_in + l*q_layer_stride, k_in/v_in +
+ * l*kv_layer_stride, writes the rotated Q to q_rot + l*q_layer_stride (may
+ * alias q_in) and its output rows to out + l*out_layer_stride (strides in
+ * elements).  lse, if given, is [layers][n_seqs][q_heads]. */
+int pa_decode_step(pa_pool* pool, int layer_begin, int layer_end, const void* q_in,
+                   const void* k_in, const void* v_in, int64_t q_layer_stride,
+                   int64_t kv_layer_stride, const float* cos_table,
+                   const float* sin_table, void* q_rot, void* out, int64_t out_stride,
+                   int64_t out_layer_stride, float* lse, float scale, void* stream);
 
 /* pa_prefill: causal attention of the batch's new tokens (batch of ONE
  * sequence) against positions [0, kv_len) of its cache.

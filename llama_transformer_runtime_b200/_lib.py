@@ -16,8 +16,8 @@ _LIB = None
 SYMBOLS = [
     "pa_last_error", "pa_pool_create", "pa_pool_destroy", "pa_pool_free_blocks",
     "pa_pool_set_free_order", "pa_pool_layer_storage", "pa_seq_create", "pa_seq_free",
-    "pa_seq_reserve", "pa_seq_length", "pa_seq_block_table", "pa_batch_set", "pa_append",
-    "pa_decode", "pa_prefill", "pa_merge_partials", "pa_gather_kv", "pa_build_rope_tables",
+    "pa_seq_reserve", "pa_seq_length", "pa_seq_block_table", "pa_batch_set", "pa_batch_set_sharded", "pa_append",
+    "pa_decode", "pa_decode_step", "pa_prefill", "pa_merge_partials", "pa_gather_kv", "pa_build_rope_tables",
     "pa_pool_check", "pa_pool_set_decode_chunk_blocks",
 ]
 
@@ -52,8 +52,10 @@ def lib():
         "pa_seq_length": [vp, i, ip],
         "pa_seq_block_table": [vp, i, C.POINTER(C.POINTER(C.c_int32)), ip],
         "pa_batch_set": [vp, vp, vp, i, vp],
+        "pa_batch_set_sharded": [vp, vp, vp, vp, vp, vp, i, vp],
         "pa_append": [vp, i, vp, vp, vp, vp, vp, vp, vp],
         "pa_decode": [vp, i, vp, vp, i64, vp, vp, f, vp],
+        "pa_decode_step": [vp, i, i, vp, vp, vp, i64, i64, vp, vp, vp, vp, i64, i64, vp, f, vp],
         "pa_prefill": [vp, i, vp, vp, vp, f, vp],
         "pa_merge_partials": [vp, vp, i, i, vp, vp, vp, vp],
         "pa_gather_kv": [vp, i, i, vp, vp, i, vp],

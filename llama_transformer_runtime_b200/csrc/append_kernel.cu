@@ -51,8 +51,10 @@ __global__ void __launch_bounds__(kAppendThreads)
 append_kernel(AppendParams p) {
   const BatchEntry e = p.batch[blockIdx.y];
   const int tok0 = blockIdx.x * kAppendTokPerCta;
-  if (tok0 >= e.n_new) return;
-  const int ntok = min(kAppendTokPerCta, e.n_new - tok0);
+  const int n_q = p.q_out ? e.n_q : 0;
+  const int span = max(n_q, e.n_new);
+  if (tok0 >= span) return;
+  const int ntok = min(kAppendTokPerCta, span - tok0);
   const int q_heads = p.kv_heads * kGroup;
   const int q_units = p.q_out ? q_heads * 4 : 0;
   const int k_units = p.kv_heads * 4;
@@ -63,12 +65,13 @@ append_kernel(AppendParams p) {
     const int t = u / units_per_tok;
     int w = u - t * units_per_tok;
     const int tok = tok0 + t;
-    const size_t row = (size_t)e.row_off + tok;
-    const int pos = e.kv_len - e.n_new + tok;
     const int c = w & 3;  // chunk pair (c, c+4)
 
     if (w < q_units) {
+      if (tok >= n_q) continue;
       const int h = w >> 2;
+      const size_t row = (size_t)e.q_row_off + tok;
+      const int pos = e.q_pos0 + tok;
       const uint4* src = reinterpret_cast<const uint4*>(p.q_in + (row * q_heads + h) * kHeadDim);
       uint4* dst = reinterpret_cast<uint4*>(p.q_out + (row * q_heads + h) * kHeadDim);
       const float4* cs = reinterpret_cast<const float4*>(p.cos_table + (size_t)pos * 32 + c * 8);
@@ -81,9 +84,13 @@ append_kernel(AppendParams p) {
       dst[c + 4] = yhi;
       continue;
     }
+    if (tok >= e.n_new) continue;
     w -= q_units;
-    const int blk = table[pos / kBlockTok];
-    const int slot = pos % kBlockTok;
+    const size_t row = (size_t)e.kv_row_off + tok;
+    const int lpos = e.kv_len - e.n_new + tok;  // position inside the local cache
+    const int pos = e.kv_pos_off + lpos;        // RoPE position
+    const int blk = table[lpos / kBlockTok];
+    const int slot = lpos % kBlockTok;
     if (blk < 0 || blk >= p.num_blocks) {
       atomicExch(p.status, kStatusBadBlock);
       continue;

@@ -32,7 +32,7 @@ int fail(int code, const char* fmt, ...) {
                   __FILE__, __LINE__);                                                  \
   } while (0)
 
-constexpr int kWsItems = 148 * 32;  // split-KV partials the workspace can hold
+constexpr int kWsItems = 148 * 64;  // split-KV partials the workspace can hold
 
 // Restores the caller's current device on scope exit.
 struct DeviceGuard {
@@ -201,23 +201,30 @@ static int upload_tables(pa_pool* p, cudaStream_t st) {
   return PA_OK;
 }
 
-int pa_batch_set(pa_pool* p, const int32_t* seq_ids, const int32_t* new_tokens, int n_seqs,
-                 void* stream) {
+int pa_batch_set_sharded(pa_pool* p, const int32_t* seq_ids, const int32_t* new_tokens,
+                         const int32_t* q_rows, const int32_t* q_pos, const int32_t* kv_pos_offset,
+                         int n_seqs, void* stream) {
   if (!p || !seq_ids) return fail(PA_ERR_INVALID_ARG, "pa_batch_set: NULL argument");
   if (p->device < 0) return fail(PA_ERR_STATE, "pa_batch_set: host-only pool");
   if (n_seqs <= 0 || n_seqs > p->host.max_seqs())
     return fail(PA_ERR_INVALID_ARG, "pa_batch_set: n_seqs %d outside 1..%d", n_seqs, p->host.max_seqs());
   std::vector<pa::BatchEntry> b(n_seqs);
-  int row = 0, max_new = 0, max_blocks = 0;
+  int kv_row = 0, q_row = 0, max_new = 0, max_blocks = 0;
   for (int i = 0; i < n_seqs; i++) {
     if (!p->host.valid(seq_ids[i])) return fail(PA_ERR_INVALID_ARG, "pa_batch_set: unknown sequence %d", seq_ids[i]);
-    int nn = new_tokens ? new_tokens[i] : 1;
-    int len = p->host.length(seq_ids[i]);
+    const int nn = new_tokens ? new_tokens[i] : 1;
+    const int len = p->host.length(seq_ids[i]);
     if (nn < 0 || nn > len)
       return fail(PA_ERR_INVALID_ARG, "pa_batch_set: sequence %d has %d tokens, cannot append %d", seq_ids[i], len, nn);
-    b[i] = {seq_ids[i], len, nn, row};
-    row += nn;
+    const int nq = q_rows ? q_rows[i] : nn;
+    const int off = kv_pos_offset ? kv_pos_offset[i] : 0;
+    const int qp = q_pos ? q_pos[i] : off + len - nn;
+    if (nq < 0 || qp < 0 || off < 0) return fail(PA_ERR_INVALID_ARG, "pa_batch_set: negative row count or position");
+    b[i] = {seq_ids[i], len, nn, kv_row, nq, q_row, qp, off};
+    kv_row += nn;
+    q_row += nq;
     if (nn > max_new) max_new = nn;
+    if (nq > max_new) max_new = nq;
     if (p->host.table_size(seq_ids[i]) > max_blocks) max_blocks = p->host.table_size(seq_ids[i]);
   }
   DeviceGuard g(p->device);
@@ -229,16 +236,23 @@ int pa_batch_set(pa_pool* p, const int32_t* seq_ids, const int32_t* new_tokens, 
                           cudaMemcpyHostToDevice, st));
   p->batch.swap(b);
   p->max_new = max_new;
-  p->total_rows = row;
+  p->total_rows = q_row;
   p->max_kv_blocks = max_blocks;
   return PA_OK;
 }
 
+int pa_batch_set(pa_pool* p, const int32_t* seq_ids, const int32_t* new_tokens, int n_seqs,
+                 void* stream) {
+  return pa_batch_set_sharded(p, seq_ids, new_tokens, nullptr, nullptr, nullptr, n_seqs, stream);
+}
+
 int pa_append(pa_pool* p, int layer, const void* q_in, const void* k_in, const void* v_in,
               const float* cos_table, const float* sin_table, void* q_out, void* stream) {
-  if (!p || !k_in || !v_in || !cos_table || !sin_table)
-    return fail(PA_ERR_INVALID_ARG, "pa_append: NULL argument");
+  if (!p || !cos_table || !sin_table) return fail(PA_ERR_INVALID_ARG, "pa_append: NULL argument");
   if (q_out && !q_in) return fail(PA_ERR_INVALID_ARG, "pa_append: q_out given without q_in");
+  if (!k_in || !v_in)
+    for (const auto& e : p->batch)
+      if (e.n_new > 0) return fail(PA_ERR_INVALID_ARG, "pa_append: the batch appends tokens but k_in/v_in is NULL");
   if (p->device < 0) return fail(PA_ERR_STATE, "pa_append: host-only pool");
   if (layer < 0 || layer >= p->num_layers) return fail(PA_ERR_INVALID_ARG, "pa_append: layer %d out of range", layer);
   if (p->batch.empty()) return fail(PA_ERR_STATE, "pa_append: no active batch (call pa_batch_set)");
@@ -317,6 +331,32 @@ int pa_decode(pa_pool* p, int layer, const void* q, void* out, int64_t out_strid
   d.chunk_blocks = cb;
   d.max_chunks = max_chunks;
   PA_CUDA(pa::launch_decode(d, n_seqs, (cudaStream_t)stream));
+  return PA_OK;
+}
+
+int pa_decode_step(pa_pool* p, int layer_begin, int layer_end, const void* q_in, const void* k_in,
+                   const void* v_in, int64_t q_layer_stride, int64_t kv_layer_stride,
+                   const float* cos_table, const float* sin_table, void* q_rot, void* out,
+                   int64_t out_stride, int64_t out_layer_stride, float* lse, float scale,
+                   void* stream) {
+  if (!p || !q_in || !q_rot || !out) return fail(PA_ERR_INVALID_ARG, "pa_decode_step: NULL argument");
+  if (layer_begin < 0 || layer_end > p->num_layers || layer_begin > layer_end)
+    return fail(PA_ERR_INVALID_ARG, "pa_decode_step: layers [%d, %d) out of range", layer_begin, layer_end);
+  const int n_seqs = (int)p->batch.size();
+  const int q_heads = p->kv_heads * pa::kGroup;
+  for (int l = layer_begin; l < layer_end; l++) {
+    const int i = l - layer_begin;
+    const __nv_bfloat16* qi = (const __nv_bfloat16*)q_in + (size_t)i * q_layer_stride;
+    const __nv_bfloat16* ki = k_in ? (const __nv_bfloat16*)k_in + (size_t)i * kv_layer_stride : nullptr;
+    const __nv_bfloat16* vi = v_in ? (const __nv_bfloat16*)v_in + (size_t)i * kv_layer_stride : nullptr;
+    __nv_bfloat16* qr = (__nv_bfloat16*)q_rot + (size_t)i * q_layer_stride;
+    __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)i * out_layer_stride;
+    int r = pa_append(p, l, qi, ki, vi, cos_table, sin_table, qr, stream);
+    if (r != PA_OK) return r;
+    r = pa_decode(p, l, qr, o, out_stride, nullptr, lse ? lse + (size_t)i * n_seqs * q_heads : nullptr,
+                  scale, stream);
+    if (r != PA_OK) return r;
+  }
   return PA_OK;
 }
 

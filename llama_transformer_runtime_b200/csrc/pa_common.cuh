@@ -22,10 +22,14 @@ constexpr int kStatusBadBlock = 1;
 
 // Descriptor of one batch entry, uploaded by pa_batch_set.
 struct BatchEntry {
-  int32_t seq;      // sequence id (row of the device table mirror)
-  int32_t kv_len;   // tokens in the cache including this step's new ones
-  int32_t n_new;    // tokens appended this step
-  int32_t row_off;  // first row of this sequence in q_in/k_in/v_in
+  int32_t seq;         // sequence id (row of the device table mirror)
+  int32_t kv_len;      // tokens in the local cache including this step's new ones
+  int32_t n_new;       // tokens appended to the local cache this step
+  int32_t kv_row_off;  // first row of this sequence in k_in/v_in
+  int32_t n_q;         // query rows of this sequence this step
+  int32_t q_row_off;   // first row of this sequence in q_in/q_out
+  int32_t q_pos0;      // RoPE position of its first query row
+  int32_t kv_pos_off;  // RoPE position of local token 0 (0 unless the sequence is range-sharded)
 };
 
 // Byte offset of chunk `c` (16 bytes, 0..7) of token slot `r` (0..15) inside a

@@ -115,6 +115,13 @@ class KVPool:
         check(lib().pa_batch_set(self._h, s.ctypes.data, None if nt is None else nt.ctypes.data,
                                  int(s.size), stream))
 
+    def batch_set_sharded(self, seq_ids, new_tokens=None, q_rows=None, q_pos=None,
+                          kv_pos_offset=None, stream: int = 0) -> None:
+        arrs = [None if a is None else np.ascontiguousarray(a, np.int32)
+                for a in (seq_ids, new_tokens, q_rows, q_pos, kv_pos_offset)]
+        check(lib().pa_batch_set_sharded(self._h, *[None if a is None else a.ctypes.data for a in arrs],
+                                         int(arrs[0].size), stream))
+
     def append(self, layer: int, q_in, k_in, v_in, cos, sin, q_out, stream: int = 0) -> None:
         check(lib().pa_append(self._h, layer, _ptr(q_in), _ptr(k_in), _ptr(v_in), _ptr(cos),
                               _ptr(sin), _ptr(q_out), stream))
@@ -125,6 +132,14 @@ class KVPool:
             out_stride = self.q_heads * HEAD_DIM
         check(lib().pa_decode(self._h, layer, _ptr(q), _ptr(out), out_stride, _ptr(out_f32),
                               _ptr(lse), scale, stream))
+
+    def decode_step(self, layer_begin: int, layer_end: int, q_in, k_in, v_in, q_layer_stride: int,
+                    kv_layer_stride: int, cos, sin, q_rot, out, out_stride: int,
+                    out_layer_stride: int, lse=None, scale: float = 0.125, stream: int = 0) -> None:
+        check(lib().pa_decode_step(self._h, layer_begin, layer_end, _ptr(q_in), _ptr(k_in),
+                                   _ptr(v_in), q_layer_stride, kv_layer_stride, _ptr(cos), _ptr(sin),
+                                   _ptr(q_rot), _ptr(out), out_stride, out_layer_stride, _ptr(lse),
+                                   scale, stream))
 
     def prefill(self, layer: int, q, out, lse=None, scale: float = 0.125, stream: int = 0) -> None:
         check(lib().pa_prefill(self._h, layer, _ptr(q), _ptr(out), _ptr(lse), scale, stream))
