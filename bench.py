@@ -67,7 +67,7 @@ NCU_TRAFFIC_BYTES = {"decode128k": None, "decode4k": None}
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 200 ms."""
+    """nvidia-smi clocks and throttle reasons sampled every 100 ms."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
@@ -79,7 +79,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-i", str(self.index), "-lms", "200"], stdout=subprocess.PIPE, text=True)
+                 "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
             self.proc = None
@@ -131,6 +131,9 @@ def run_ours(args):
     dev = f"cuda:{local_rank}"
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device(dev))
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     wl = WORKLOADS[args.workload]
     ctx = wl["ctx"]
     total_steps = args.warmup + 2 * args.steps + 8
@@ -150,8 +153,9 @@ def run_ours(args):
     gen = torch.Generator(device=dev)
     gen.manual_seed(4321 + rank)
     chunk = 8192
-    ones = torch.ones(chunk, 32, dtype=torch.float32, device=dev)
-    zeros = torch.zeros(chunk, 32, dtype=torch.float32, device=dev)
+    # tables are indexed by absolute position, so they cover the whole local range
+    ones = torch.ones(local_len + 1, 32, dtype=torch.float32, device=dev)
+    zeros = torch.zeros(local_len + 1, 32, dtype=torch.float32, device=dev)
     for c0 in range(0, local_len, chunk):
         n = min(chunk, local_len - c0)
         pool.reserve(seq, c0 + n)
@@ -237,19 +241,14 @@ def run_ours(args):
         out_host.copy_(out_dev, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller reads the result every step
 
+    m0 = sampler.mark()  # clock samples from here on are taken under load
     for _ in range(args.warmup):
         resident_step()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.3)
-    m0 = sampler.mark()
     len_before = state["global_len"]
     state["launches"] = 0
     ms = timed(resident_step, args.steps)
     launches = state["launches"]
     len_after = state["global_len"]
-    m1 = sampler.mark()
     bytes_timed = sum(LAYERS * decode_bytes(L) for L in range(len_before + 1, len_after + 1))
     value = bytes_timed / (ms * 1e-3) / 1e9
 
@@ -276,6 +275,7 @@ def run_ours(args):
     achieved = kern_bytes / (ms_k * 1e-3) / 1e9
     peak, peak_kind = measured_peak()
     pool.check()
+    m1 = sampler.mark()
 
     line = None
     if rank == 0:
@@ -455,12 +455,15 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode128k", choices=sorted(WORKLOADS))
+    ap.add_argument("--layers", type=int, default=16, help="fewer layers make a small case for profiling")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    global LAYERS
+    LAYERS = args.layers
     if args.impl == "reference":
         run_reference(args)
     else:

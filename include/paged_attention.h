@@ -185,6 +185,8 @@ int pa_pool_check(pa_pool* pool, void* stream);
 
 /* Tuning knobs (0 keeps the built-in heuristic): blocks per split-KV chunk. */
 int pa_pool_set_decode_chunk_blocks(pa_pool* pool, int chunk_blocks);
+/* Warps per decode CTA and 4 KiB ring stages per warp (built shapes only). */
+int pa_pool_set_decode_shape(pa_pool* pool, int warps, int stages);
 
 #ifdef __cplusplus
 }

@@ -18,7 +18,7 @@ SYMBOLS = [
     "pa_pool_set_free_order", "pa_pool_layer_storage", "pa_seq_create", "pa_seq_free",
     "pa_seq_reserve", "pa_seq_length", "pa_seq_block_table", "pa_batch_set", "pa_batch_set_sharded", "pa_append",
     "pa_decode", "pa_decode_step", "pa_prefill", "pa_merge_partials", "pa_gather_kv", "pa_build_rope_tables",
-    "pa_pool_check", "pa_pool_set_decode_chunk_blocks",
+    "pa_pool_check", "pa_pool_set_decode_chunk_blocks", "pa_pool_set_decode_shape",
 ]
 
 
@@ -62,6 +62,7 @@ def lib():
         "pa_build_rope_tables": [vp, vp, i],
         "pa_pool_check": [vp, vp],
         "pa_pool_set_decode_chunk_blocks": [vp, i],
+        "pa_pool_set_decode_shape": [vp, i, i],
         "pa_debug_set_rope_variant": [vp, i],
     }
     for name, args in sigs.items():

@@ -63,6 +63,8 @@ struct pa_pool {
   std::vector<pa::BatchEntry> batch;  // host copy of the active batch
   int max_new = 0, total_rows = 0, max_kv_blocks = 0;
   int chunk_blocks_override = 0;
+  int decode_warps = 0, decode_stages = 0;  // 0: chosen per batch
+  int sm_count = 0;
   int rope_variant = 1;
   pa_pool(int nb, int ms, int mb) : host(nb, ms, mb) {}
 };
@@ -100,6 +102,7 @@ int pa_pool_create(pa_pool** out, int device, int num_layers, int num_blocks, in
     alloc((void**)&p->ws_ml, (size_t)kWsItems * 2 * pa::kGroup * sizeof(float));
     alloc((void**)&p->ws_count, (size_t)max_seqs * kv_heads * sizeof(unsigned int));
     alloc((void**)&p->d_status, sizeof(int));
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&p->sm_count, cudaDevAttrMultiProcessorCount, device);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) {
       int code = fail(PA_ERR_CUDA, "pa_pool_create: device allocation failed: %s", cudaGetErrorString(e));
@@ -278,15 +281,50 @@ int pa_append(pa_pool* p, int layer, const void* q_in, const void* k_in, const v
 // Blocks per split-KV chunk: aim at about two CTAs per resident slot
 // (3 CTAs of 4 warps per SM on 148 SMs), at least one block per warp and
 // stage, and never more chunks than the workspace can hold.
-static int pick_chunk_blocks(const pa_pool* p) {
-  if (p->chunk_blocks_override > 0) return p->chunk_blocks_override;
-  long long total = 0;
-  for (const auto& e : p->batch) total += (e.kv_len + pa::kBlockTokens - 1) / pa::kBlockTokens;
-  total *= p->kv_heads;
-  const long long target_ctas = 148 * 3 * 2;
-  long long cb = (total + target_ctas - 1) / target_ctas;
-  if (cb < 16) cb = 16;
-  return (int)cb;
+// Split-KV plan of the active batch.  Measured on B200: CTAs that all start and
+// end together cost a ramp-up and a drain per wave, so the best plan is ONE
+// wave — 8-warp CTAs, one per SM, each streaming a long run of blocks.  When
+// the batch has more (sequence, KV head) pairs than SMs that is impossible and
+// smaller CTAs (4 warps, 3 per SM) in several ragged waves are used instead.
+struct DecodePlan {
+  int warps, stages, chunk_blocks;
+};
+
+static long long plan_ctas(const pa_pool* p, int cb) {
+  long long n = 0;
+  for (const auto& e : p->batch) {
+    const int nb = (e.kv_len + pa::kBlockTokens - 1) / pa::kBlockTokens;
+    n += nb > 0 ? (nb + cb - 1) / cb : 1;
+  }
+  return n * p->kv_heads;
+}
+
+static DecodePlan pick_plan(const pa_pool* p) {
+  DecodePlan plan{p->decode_warps, p->decode_stages, p->chunk_blocks_override};
+  const int sms = p->sm_count > 0 ? p->sm_count : 148;
+  const long long pairs = (long long)p->batch.size() * p->kv_heads;
+  if (plan.warps == 0) {
+    plan.warps = pairs <= sms ? 8 : 4;
+    plan.stages = 4;
+  }
+  if (plan.chunk_blocks == 0) {
+    if (pairs <= sms) {
+      // smallest chunk for which every CTA is resident at once
+      int lo = 1, hi = p->max_kv_blocks > 1 ? p->max_kv_blocks : 1;
+      while (lo < hi) {
+        const int mid = (lo + hi) / 2;
+        if (plan_ctas(p, mid) <= sms) hi = mid; else lo = mid + 1;
+      }
+      plan.chunk_blocks = lo;
+    } else {
+      long long total = 0;
+      for (const auto& e : p->batch) total += (e.kv_len + pa::kBlockTokens - 1) / pa::kBlockTokens;
+      total *= p->kv_heads;
+      long long cb = total / ((long long)sms * 3 * 4);
+      plan.chunk_blocks = (int)(cb < 32 ? 32 : cb);
+    }
+  }
+  return plan;
 }
 
 int pa_decode(pa_pool* p, int layer, const void* q, void* out, int64_t out_stride, float* out_f32,
@@ -299,17 +337,16 @@ int pa_decode(pa_pool* p, int layer, const void* q, void* out, int64_t out_strid
   if (out && out_stride < (int64_t)p->kv_heads * pa::kGroup * pa::kHeadDim)
     return fail(PA_ERR_INVALID_ARG, "pa_decode: out_stride %lld shorter than a row", (long long)out_stride);
   const int n_seqs = (int)p->batch.size();
-  int cb = pick_chunk_blocks(p);
-  int max_chunks = (p->max_kv_blocks + cb - 1) / cb;
-  if (max_chunks < 1) max_chunks = 1;
-  while ((long long)max_chunks * p->kv_heads * n_seqs > kWsItems) {
+  DecodePlan plan = pick_plan(p);
+  int cb = plan.chunk_blocks;
+  // the combine keeps 48 bytes per chunk in the (then idle) tile ring
+  const int scratch_chunks = plan.warps * plan.stages * pa::kPairBytes / 48;
+  auto chunks_for = [&](int c) { int m = (p->max_kv_blocks + c - 1) / c; return m < 1 ? 1 : m; };
+  int max_chunks = chunks_for(cb);
+  while (max_chunks > 1 && ((long long)max_chunks * p->kv_heads * n_seqs > kWsItems || max_chunks > scratch_chunks)) {
     cb *= 2;
-    max_chunks = (p->max_kv_blocks + cb - 1) / cb;
-    if (max_chunks < 1) max_chunks = 1;
-    if (max_chunks == 1) break;
+    max_chunks = chunks_for(cb);
   }
-  if ((long long)max_chunks * p->kv_heads * n_seqs > kWsItems && max_chunks > 1)
-    return fail(PA_ERR_UNSUPPORTED, "pa_decode: batch too large for the split-KV workspace");
   DeviceGuard g(p->device);
   pa::DecodeParams d;
   d.q = (const __nv_bfloat16*)q;
@@ -330,7 +367,7 @@ int pa_decode(pa_pool* p, int layer, const void* q, void* out, int64_t out_strid
   d.max_blocks_per_seq = p->host.max_blocks_per_seq();
   d.chunk_blocks = cb;
   d.max_chunks = max_chunks;
-  PA_CUDA(pa::launch_decode(d, n_seqs, (cudaStream_t)stream));
+  PA_CUDA(pa::launch_decode(d, n_seqs, plan.warps, plan.stages, (cudaStream_t)stream));
   return PA_OK;
 }
 
@@ -442,6 +479,15 @@ int pa_pool_check(pa_pool* p, void* stream) {
 int pa_pool_set_decode_chunk_blocks(pa_pool* p, int chunk_blocks) {
   if (!p || chunk_blocks < 0) return fail(PA_ERR_INVALID_ARG, "pa_pool_set_decode_chunk_blocks: bad argument");
   p->chunk_blocks_override = chunk_blocks;
+  return PA_OK;
+}
+
+int pa_pool_set_decode_shape(pa_pool* p, int warps, int stages) {
+  if (!p) return fail(PA_ERR_INVALID_ARG, "pa_pool_set_decode_shape: NULL pool");
+  if (!(warps == 0 && stages == 0) && !pa::decode_shape_supported(warps, stages))
+    return fail(PA_ERR_UNSUPPORTED, "pa_pool_set_decode_shape: %d warps x %d stages is not built", warps, stages);
+  p->decode_warps = warps;
+  p->decode_stages = stages;
   return PA_OK;
 }
 

@@ -254,20 +254,77 @@ decode_kernel(DecodeParams p) {
   if (s_ticket != (unsigned)(n_chunks - 1)) return;
   __threadfence();
 
-  const size_t item0 = (size_t)(z * p.kv_heads + h) * p.max_chunks;
-  for (int idx = threadIdx.x; idx < kGroup * kHeadDim; idx += WARPS * 32) {
-    const int r = idx >> 6, d = idx & 63;
-    float M = -INFINITY;
-    for (int c = 0; c < n_chunks; c++)
-      M = fmaxf(M, __ldcg(p.ws_ml + (item0 + c) * (2 * kGroup) + r));
-    float L = 0.f, O = 0.f;
-    for (int c = 0; c < n_chunks; c++) {
-      const float mc = __ldcg(p.ws_ml + (item0 + c) * (2 * kGroup) + r);
-      const float wgt = mc == -INFINITY ? 0.f : ex2(mc - M);
-      L += wgt * __ldcg(p.ws_ml + (item0 + c) * (2 * kGroup) + kGroup + r);
-      O += wgt * __ldcg(p.ws_acc + (item0 + c) * (kGroup * kHeadDim) + idx);
+  // The tile ring is idle now and serves as scratch: (m, l) of every chunk,
+  // then one weight per chunk and row.  All loads of a phase are independent,
+  // so their latencies overlap instead of adding up.
+  constexpr int T = WARPS * 32;
+  if (n_chunks * 48 > S::kTiles) {  // the host sizes chunks so that this cannot happen
+    if (threadIdx.x == 0) {
+      atomicExch(p.status, kStatusBadBlock);
+      p.ws_count[z * p.kv_heads + h] = 0u;
     }
-    write_row_outputs(p, z, h, r, d, O, M, L);
+    return;
+  }
+  const size_t item0 = (size_t)(z * p.kv_heads + h) * p.max_chunks;
+  float* cm = reinterpret_cast<float*>(tiles);  // [n_chunks][8]
+  float* cw = cm + (size_t)n_chunks * 8;        // [n_chunks][4]
+  for (int i = threadIdx.x; i < n_chunks * 8; i += T) cm[i] = __ldcg(p.ws_ml + item0 * 8 + i);
+  __syncthreads();
+  for (int r = warp; r < kGroup; r += WARPS) {
+    float M = -INFINITY;
+    for (int c = lane; c < n_chunks; c += 32) M = fmaxf(M, cm[c * 8 + r]);
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, s));
+    float L = 0.f;
+    for (int c = lane; c < n_chunks; c += 32) {
+      const float mc = cm[c * 8 + r];
+      const float wgt = mc == -INFINITY ? 0.f : ex2(mc - M);
+      cw[c * 4 + r] = wgt;
+      L += wgt * cm[c * 8 + kGroup + r];
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) L += __shfl_xor_sync(0xffffffffu, L, s);
+    if (lane == 0) {
+      mrg_m[r] = M;
+      mrg_l[r] = L;
+    }
+  }
+  __syncthreads();
+  // thread = (chunk group g, float4 column q): 64 float4 columns cover the 4x64 outputs
+  constexpr int G = T / 64;
+  const int q4 = threadIdx.x & 63, g = threadIdx.x >> 6;
+  const int r4 = q4 >> 4;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4* src = reinterpret_cast<const float4*>(p.ws_acc + item0 * (kGroup * kHeadDim)) + q4;
+  int c = g;
+  for (; c + 3 * G < n_chunks; c += 4 * G) {
+    float4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) v[u] = __ldcg(src + (size_t)(c + u * G) * 64);
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      const float wgt = cw[(c + u * G) * 4 + r4];
+      acc.x += wgt * v[u].x;
+      acc.y += wgt * v[u].y;
+      acc.z += wgt * v[u].z;
+      acc.w += wgt * v[u].w;
+    }
+  }
+  for (; c < n_chunks; c += G) {
+    const float4 v = __ldcg(src + (size_t)c * 64);
+    const float wgt = cw[c * 4 + r4];
+    acc.x += wgt * v.x;
+    acc.y += wgt * v.y;
+    acc.z += wgt * v.z;
+    acc.w += wgt * v.w;
+  }
+  reinterpret_cast<float4*>(mrg_o)[g * 64 + q4] = acc;
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < kGroup * kHeadDim; idx += T) {
+    float O = 0.f;
+#pragma unroll
+    for (int gg = 0; gg < G; gg++) O += mrg_o[gg * (kGroup * kHeadDim) + idx];
+    write_row_outputs(p, z, h, idx >> 6, idx & 63, O, mrg_m[idx >> 6], mrg_l[idx >> 6]);
   }
   if (threadIdx.x == 0) p.ws_count[z * p.kv_heads + h] = 0u;
 }
@@ -293,9 +350,26 @@ cudaError_t launch_decode_cfg(const DecodeParams& p, int n_seqs, cudaStream_t st
 
 size_t decode_ws_acc_floats_per_item() { return kGroup * kHeadDim; }
 
-cudaError_t launch_decode(const DecodeParams& p, int n_seqs, cudaStream_t stream) {
+bool decode_shape_supported(int warps, int stages) {
+  return (warps == 4 && (stages == 3 || stages == 4 || stages == 6)) ||
+         (warps == 8 && (stages == 2 || stages == 3 || stages == 4 || stages == 6)) ||
+         (warps == 2 && (stages == 4 || stages == 8));
+}
+
+cudaError_t launch_decode(const DecodeParams& p, int n_seqs, int warps, int stages,
+                          cudaStream_t stream) {
   if (n_seqs <= 0) return cudaSuccess;
-  return launch_decode_cfg<4, 4>(p, n_seqs, stream);
+  switch (warps * 16 + stages) {
+    case 4 * 16 + 3: return launch_decode_cfg<4, 3>(p, n_seqs, stream);
+    case 4 * 16 + 6: return launch_decode_cfg<4, 6>(p, n_seqs, stream);
+    case 8 * 16 + 2: return launch_decode_cfg<8, 2>(p, n_seqs, stream);
+    case 8 * 16 + 3: return launch_decode_cfg<8, 3>(p, n_seqs, stream);
+    case 8 * 16 + 4: return launch_decode_cfg<8, 4>(p, n_seqs, stream);
+    case 8 * 16 + 6: return launch_decode_cfg<8, 6>(p, n_seqs, stream);
+    case 2 * 16 + 4: return launch_decode_cfg<2, 4>(p, n_seqs, stream);
+    case 2 * 16 + 8: return launch_decode_cfg<2, 8>(p, n_seqs, stream);
+    default: return launch_decode_cfg<4, 4>(p, n_seqs, stream);
+  }
 }
 
 // ---- merge of split-KV partials from disjoint key ranges ---------------------

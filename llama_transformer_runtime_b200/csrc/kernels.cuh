@@ -49,7 +49,9 @@ struct DecodeParams {
   float scale_log2;           // scale * log2(e)
   int kv_heads, num_blocks, max_blocks_per_seq, chunk_blocks, max_chunks;
 };
-cudaError_t launch_decode(const DecodeParams& p, int n_seqs, cudaStream_t stream);
+cudaError_t launch_decode(const DecodeParams& p, int n_seqs, int warps, int stages,
+                          cudaStream_t stream);
+bool decode_shape_supported(int warps, int stages);
 size_t decode_ws_acc_floats_per_item();
 
 struct MergeParams {

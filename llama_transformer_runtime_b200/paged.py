@@ -155,6 +155,9 @@ class KVPool:
     def set_decode_chunk_blocks(self, n: int) -> None:
         check(lib().pa_pool_set_decode_chunk_blocks(self._h, n))
 
+    def set_decode_shape(self, warps: int, stages: int) -> None:
+        check(lib().pa_pool_set_decode_shape(self._h, warps, stages))
+
     def _set_rope_variant(self, v: int) -> None:
         check(lib().pa_debug_set_rope_variant(self._h, v))
 
