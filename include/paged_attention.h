@@ -175,6 +175,31 @@ int pa_merge_partials(const float* o_parts, const float* lse_parts, int n_parts,
 int pa_gather_kv(pa_pool* pool, int layer, int seq_id, void* k_out, void* v_out,
                  int out_stride_tokens, void* stream);
 
+/* pa_decode_noalloc: pa_decode for hosts that are not allowed to allocate
+ * device memory — a plug-in inside a serving process that owns the whole GPU
+ * through its own arena, a latency-critical loop that cannot afford the
+ * device-wide synchronisation an allocation implies, a process with a fixed,
+ * audited memory budget.  It has no counterpart in the reference; it exists
+ * because pa_pool_create (which allocates) is closed to such callers.
+ * Everything is caller-owned: the cache layer in this library's physical
+ * layout (see pa_pool_layer_storage), device block tables
+ * [n_seqs][table_stride], host kv_lens[n_seqs], q [n_seqs][4*kv_heads][64],
+ * out rows of out_stride elements, optional lse [n_seqs][4*kv_heads].
+ * The split-KV scratch is a fixed array inside the library image (about
+ * 266 KiB, held by every GPU that loads the library until exit), hence the
+ * limit: at most PA_NOALLOC_MAX_SEQS sequences per call, larger batches are
+ * rejected with PA_ERR_UNSUPPORTED.  No cudaMalloc/cudaFree or allocating
+ * library routine is called.  All calls on a device share that array and it
+ * keeps the previous call's contents (the entry re-zeroes what must start at
+ * zero): calls that overlap on the GPU — different streams, no ordering —
+ * race.  The first call on each device also resolves the array's device
+ * address; make it before any stream capture begins. */
+#define PA_NOALLOC_MAX_SEQS 8
+int pa_decode_noalloc(const void* cache_layer, int num_blocks, int kv_heads,
+                      const int32_t* block_tables, int table_stride,
+                      const int32_t* kv_lens, int n_seqs, const void* q, void* out,
+                      int64_t out_stride, float* lse, float scale, void* stream);
+
 /* Host: fp32 cos/sin tables [seq_len][32], Llama-3 frequency scaling. */
 int pa_build_rope_tables(float* cos_table, float* sin_table, int seq_len);
 

@@ -19,6 +19,7 @@ SYMBOLS = [
     "pa_seq_reserve", "pa_seq_length", "pa_seq_block_table", "pa_batch_set", "pa_batch_set_sharded", "pa_append",
     "pa_decode", "pa_decode_step", "pa_prefill", "pa_merge_partials", "pa_gather_kv", "pa_build_rope_tables",
     "pa_pool_check", "pa_pool_set_decode_chunk_blocks", "pa_pool_set_decode_shape",
+    "pa_decode_noalloc",
 ]
 
 
@@ -63,6 +64,7 @@ def lib():
         "pa_pool_check": [vp, vp],
         "pa_pool_set_decode_chunk_blocks": [vp, i],
         "pa_pool_set_decode_shape": [vp, i, i],
+        "pa_decode_noalloc": [vp, i, i, vp, i, vp, i, vp, vp, i64, vp, f, vp],
         "pa_debug_set_rope_variant": [vp, i],
     }
     for name, args in sigs.items():

@@ -16,8 +16,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libpaged_attention.so")
 
-SOURCES = ["capi.cu", "append_kernel.cu", "decode_kernel.cu", "prefill_kernel.cu", "compat.cu",
-           "block_pool.cpp"]
+SOURCES = ["capi.cu", "append_kernel.cu", "decode_kernel.cu", "decode_noalloc.cu",
+           "prefill_kernel.cu", "compat.cu", "block_pool.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -49,6 +49,11 @@ struct DeviceGuard {
 
 }  // namespace
 
+namespace pa {
+// For entry points that live in other translation units.
+void set_last_error(const char* msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
+}  // namespace pa
+
 struct pa_pool {
   pa::BlockPool host;
   int device, num_layers, kv_heads;

@@ -162,6 +162,17 @@ class KVPool:
         check(lib().pa_debug_set_rope_variant(self._h, v))
 
 
+def decode_noalloc(cache_layer, num_blocks: int, kv_heads: int, block_tables, table_stride: int,
+                   kv_lens, q, out, out_stride: int, lse=None, scale: float = 0.125,
+                   stream: int = 0) -> None:
+    """pa_decode_noalloc: decode over caller-owned buffers, for hosts that may not
+    allocate device memory; at most PA_NOALLOC_MAX_SEQS (8) sequences per call."""
+    lens = np.ascontiguousarray(kv_lens, np.int32)
+    check(lib().pa_decode_noalloc(_ptr(cache_layer), num_blocks, kv_heads, _ptr(block_tables),
+                                  table_stride, lens.ctypes.data, int(lens.size), _ptr(q), _ptr(out),
+                                  out_stride, _ptr(lse), scale, stream))
+
+
 def merge_partials(o_parts, lse_parts, n_parts: int, rows: int, out=None, out_f32=None,
                    lse_out=None, stream: int = 0) -> None:
     check(lib().pa_merge_partials(_ptr(o_parts), _ptr(lse_parts), n_parts, rows, _ptr(out),
