@@ -403,8 +403,29 @@ int pa_decode_step(pa_pool* p, int layer_begin, int layer_end, const void* q_in,
 }
 
 int pa_prefill(pa_pool* p, int layer, const void* q, void* out, float* lse, float scale, void* stream) {
-  (void)p; (void)layer; (void)q; (void)out; (void)lse; (void)scale; (void)stream;
-  return fail(PA_ERR_UNSUPPORTED, "pa_prefill: not built yet");
+  if (!p || !q || !out) return fail(PA_ERR_INVALID_ARG, "pa_prefill: NULL argument");
+  if (p->device < 0) return fail(PA_ERR_STATE, "pa_prefill: host-only pool");
+  if (layer < 0 || layer >= p->num_layers) return fail(PA_ERR_INVALID_ARG, "pa_prefill: layer %d out of range", layer);
+  if (p->batch.size() != 1) return fail(PA_ERR_UNSUPPORTED, "pa_prefill: the batch must hold exactly one sequence (has %zu)", p->batch.size());
+  const pa::BatchEntry& e = p->batch[0];
+  if (e.n_q < 1 || e.kv_len < 1 || e.q_pos0 < 0)
+    return fail(PA_ERR_INVALID_ARG, "pa_prefill: needs at least one query row and one cached token");
+  DeviceGuard g(p->device);
+  pa::PrefillParams a;
+  a.q = (const __nv_bfloat16*)q;
+  a.out = (__nv_bfloat16*)out;
+  a.lse = lse;
+  a.storage = p->storage + (size_t)layer * p->layer_bytes;
+  a.tables = p->d_tables;
+  a.batch = p->d_batch;
+  a.status = p->d_status;
+  a.out_stride = (long long)p->kv_heads * pa::kGroup * pa::kHeadDim;
+  a.scale_log2 = scale * pa::kLog2e;
+  a.kv_heads = p->kv_heads;
+  a.num_blocks = p->host.num_blocks();
+  a.max_blocks_per_seq = p->host.max_blocks_per_seq();
+  PA_CUDA(pa::launch_prefill(a, e.n_q, (cudaStream_t)stream));
+  return PA_OK;
 }
 
 int pa_merge_partials(const float* o_parts, const float* lse_parts, int n_parts, int rows, void* out,

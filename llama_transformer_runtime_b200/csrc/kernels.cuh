@@ -54,6 +54,22 @@ cudaError_t launch_decode(const DecodeParams& p, int n_seqs, int warps, int stag
 bool decode_shape_supported(int warps, int stages);
 size_t decode_ws_acc_floats_per_item();
 
+// Causal prefill of the batch's single sequence: its n_q query rows (positions
+// q_pos0 ...) against keys [0, kv_len) of the paged cache.
+struct PrefillParams {
+  const __nv_bfloat16* q;   // [rows][q_heads][64], RoPE applied
+  __nv_bfloat16* out;       // [rows][out_stride], columns h*64+d
+  float* lse;               // [q_heads][n_q] (nullable)
+  const char* storage;
+  const int32_t* tables;
+  const BatchEntry* batch;  // entry 0 is used
+  int* status;
+  long long out_stride;
+  float scale_log2;
+  int kv_heads, num_blocks, max_blocks_per_seq;
+};
+cudaError_t launch_prefill(const PrefillParams& p, int n_q, cudaStream_t stream);
+
 struct MergeParams {
   const float* o_parts;    // [n_parts][rows][64]
   const float* lse_parts;  // [n_parts][rows]
