@@ -148,6 +148,11 @@ def run_ours(args):
     rng = np.random.default_rng(1234 + rank)
     pool.set_free_order(rng.permutation(num_blocks))
     seq = pool.create_seq()
+    if args.chunk_blocks:
+        pool.set_decode_chunk_blocks(args.chunk_blocks)
+    if args.decode_shape:
+        w, s = args.decode_shape.lower().split("x")
+        pool.set_decode_shape(int(w), int(s))
 
     # ---- fill the cache: N(0,1)*0.5, generated on the device, appended with the identity rotation
     gen = torch.Generator(device=dev)
@@ -452,19 +457,219 @@ def run_reference(args):
     }), flush=True)
 
 
+# =============================================================================
+# prefill workload (config 3): 2048 tokens x 16 layers, causal, batch 1
+# =============================================================================
+PREFILL_TOKENS = 2048
+
+
+def prefill_flops(S: int) -> float:
+    """Causal-useful flops of one layer: 4 * Hq * D * S (S + 1) / 2."""
+    return 4.0 * Q_HEADS * D * S * (S + 1) / 2.0
+
+
+def measured_tflops():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            j = json.load(open(path))
+            return float(j["bf16_tflops"]), float(j.get("bf16_tflops_sustained", j["bf16_tflops"])), "measured"
+        except Exception:
+            pass
+    return 1590.0, 1400.0, "fallback"
+
+
+def run_prefill(args):
+    """One step = one 2048-token prompt through 16 layers: per layer fused RoPE +
+    paged append of the prompt's K/V, then causal GQA attention over the cache,
+    output [2048, 2048] bf16.  Both arms: ours (pa_append + pa_prefill) and the
+    reference's kernels (rope kernels + append copies + flash kernel + layout)."""
+    import torch
+
+    rank, local_rank, world = dist_env()
+    if rank != 0:
+        return  # independent replicas only: prefill is not sharded here
+    torch.cuda.set_device(local_rank)
+    dev = f"cuda:{local_rank}"
+    S = PREFILL_TOKENS
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(99)
+    # per-layer inputs differ so that no layer finds its operands in L2 from the previous one
+    q_in = torch.randn(LAYERS, S, Q_HEADS, D, generator=gen, device=dev).to(torch.bfloat16)
+    k_in = torch.randn(LAYERS, S, KV_HEADS, D, generator=gen, device=dev).to(torch.bfloat16)
+    v_in = torch.randn(LAYERS, S, KV_HEADS, D, generator=gen, device=dev).to(torch.bfloat16)
+    out = torch.zeros(LAYERS, S, Q_HEADS * D, dtype=torch.bfloat16, device=dev)
+    q_host, k_host, v_host = q_in.cpu().pin_memory(), k_in.cpu().pin_memory(), v_in.cpu().pin_memory()
+    out_host = torch.zeros(S, Q_HEADS * D, dtype=torch.bfloat16).pin_memory()
+    burst, sustained, kind = measured_tflops()
+
+    if args.impl == "reference":
+        from oracle import oracle as orc
+        if not orc.ref_available():
+            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libref.so was not built"}))
+            return
+        ref = orc.ref()
+        cos_h, sin_h = orc.build_rope_tables(S)
+        cos, sin = torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev)
+        kc = torch.zeros(LAYERS, KV_HEADS, S, D, dtype=torch.bfloat16, device=dev)
+        vc = torch.zeros_like(kc)
+        qf = torch.empty(Q_HEADS, S, D, dtype=torch.bfloat16, device=dev)
+        kf = torch.empty(KV_HEADS, S, D, dtype=torch.bfloat16, device=dev)
+        vf = torch.empty_like(kf)
+        of = torch.empty(Q_HEADS, S, D, dtype=torch.bfloat16, device=dev)
+
+        def step():
+            for layer in range(LAYERS):
+                ref.ref_rope_qkv(q_in[layer].data_ptr(), qf.data_ptr(), k_in[layer].data_ptr(), kf.data_ptr(),
+                                 v_in[layer].data_ptr(), vf.data_ptr(), cos.data_ptr(), sin.data_ptr(), S, 0)
+                # the reference's own append is 2*8*2048 copies of 128 bytes per layer; the
+                # strided form moves the same bytes in 16 calls (kernel-to-kernel comparison)
+                if args.ref_literal_append:
+                    ref.ref_append_memcpy_loop(kc[layer].data_ptr(), vc[layer].data_ptr(), kf.data_ptr(),
+                                               vf.data_ptr(), S, 0, S)
+                else:
+                    ref.ref_append_strided(kc[layer].data_ptr(), vc[layer].data_ptr(), kf.data_ptr(),
+                                           vf.data_ptr(), S, 0, S, None)
+                ref.ref_flash_attention(qf.data_ptr(), kc[layer].data_ptr(), vc[layer].data_ptr(), of.data_ptr(),
+                                        None, 1, Q_HEADS, KV_HEADS, S, S, S, 0.125, 1, None)
+                ref.ref_flash_output_layout(of.data_ptr(), out[layer].data_ptr(), S)
+        launches_per_step = LAYERS * 5
+        kernel_name = "flash_attention_fat_kernel (reference)"
+    else:
+        from llama_transformer_runtime_b200 import paged
+        nb = (S + BLOCK - 1) // BLOCK
+        num_blocks = nb + nb // 4 + 8
+        pool = paged.KVPool(LAYERS, num_blocks, KV_HEADS, 1, nb + 1, device=local_rank)
+        pool.set_free_order(np.random.default_rng(5).permutation(num_blocks))
+        seq = pool.create_seq()
+        pool.reserve(seq, S)
+        pool.batch_set([seq], [S])
+        cos_h, sin_h = paged.build_rope_tables(S)
+        cos, sin = torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev)
+        q_rot = torch.empty_like(q_in)
+
+        def step():
+            # the same prompt positions are rewritten every step (the table is fixed)
+            for layer in range(LAYERS):
+                pool.append(layer, q_in[layer], k_in[layer], v_in[layer], cos, sin, q_rot[layer])
+                pool.prefill(layer, q_rot[layer], out[layer], None, 0.125)
+        launches_per_step = LAYERS * 2
+        kernel_name = "prefill_kernel"
+
+    def e2e_step():
+        q_in.copy_(q_host, non_blocking=True)
+        k_in.copy_(k_host, non_blocking=True)
+        v_in.copy_(v_host, non_blocking=True)
+        step()
+        out_host.copy_(out[LAYERS - 1], non_blocking=True)  # the last layer's attention output
+        torch.cuda.current_stream().synchronize()
+
+    def timed(fn, n):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    m0 = sampler.mark()
+    for _ in range(args.warmup):
+        step()
+    ms = timed(step, args.steps) / args.steps
+    ms_e2e = timed(e2e_step, args.steps) / args.steps
+    flops = prefill_flops(S) * LAYERS
+    value = flops / (ms * 1e-3) / 1e12
+    line = {
+        "metric": "prefill_attn_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
+        "us_per_layer": round(ms * 1e3 / LAYERS, 2), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"prefill_{S}tokens_x{LAYERS}layers_batch1_causal", "tokens": S, "layers": LAYERS,
+                   "q_heads": Q_HEADS, "kv_heads": KV_HEADS, "head_dim": D,
+                   "flops": "causal-useful 4*Hq*D*S(S+1)/2 per layer",
+                   "dense_count_tflops": round(4.0 * Q_HEADS * D * S * S * LAYERS / (ms * 1e-3) / 1e12, 2),
+                   "l2": "per-layer inputs are distinct tensors (24 MiB per layer, 384 MiB per step)"},
+        "e2e": {"value": round(flops / (ms_e2e * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": (q_host.numel() + k_host.numel() + v_host.numel()) * 2,
+                "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": round(ms_e2e, 4)},
+        "gpu_launches": launches_per_step * args.steps,
+    }
+    if args.impl == "reference":
+        line["impl"] = "reference"
+        line["cpu_baseline"] = {"value": line["value"], "unit": "TFLOP/s", "cores": 0, "kind": "reference",
+                                "sample": "whole workload on the GPU: the reference has no CPU implementation of this path"}
+    else:
+        # dominant kernel alone
+        def attn_only():
+            for layer in range(LAYERS):
+                pool.prefill(layer, q_rot[layer], out[layer], None, 0.125)
+        attn_only()
+        reps = max(3, args.steps)
+        ms_k = timed(attn_only, reps) / (reps * LAYERS)
+        achieved = prefill_flops(S) / (ms_k * 1e-3) / 1e12
+        line["roofline"] = {"bound": "tensor", "kernel": kernel_name, "achieved": round(achieved, 2),
+                            "peak": burst, "unit": "TFLOP/s", "frac": round(achieved / burst, 4),
+                            "peak_source": f"of {kind} (cuBLAS bf16 burst)", "us_per_launch": round(ms_k * 1e3, 2),
+                            "flops_per_launch": prefill_flops(S), "traffic": None}
+        pool.check()
+        line["cpu_baseline"] = prefill_cpu_baseline(q_rot, out, pool, seq, S)
+        pool.close()
+    line["clocks"] = sampler.stop(m0, None)
+    print(json.dumps(line), flush=True)
+
+
+def prefill_cpu_baseline(q_rot, out, pool, seq, S):
+    """fp32 CPU oracle on a bounded sample: the first 512 query rows of layer 0
+    (all 32 heads) against their causal keys; also checks the GPU output."""
+    import torch
+
+    from oracle import oracle as orc
+
+    n = 512
+    k = torch.zeros(KV_HEADS, S, D, dtype=torch.bfloat16, device=q_rot.device)
+    v = torch.zeros_like(k)
+    pool.gather_kv(0, seq, k, v, S)
+    torch.cuda.synchronize()
+    to_u16 = lambda t: t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+    qh = to_u16(q_rot[0][:n].permute(1, 0, 2))  # [32, n, 64]
+    kh, vh = to_u16(k[:, :n]), to_u16(v[:, :n])
+    t0 = time.perf_counter()
+    O, _ = orc.attention(qh, kh, vh, n, causal=True)
+    reps = 1
+    while time.perf_counter() - t0 < 10.0 and reps < 200:
+        orc.attention(qh, kh, vh, n, causal=True)
+        reps += 1
+    total = time.perf_counter() - t0
+    got = orc.bf16_to_f32(to_u16(out[0][:n]))
+    err = float(np.max(np.abs(got - orc.output_layout(O))))
+    return {"value": round(prefill_flops(n) * reps / total / 1e12, 4), "unit": "TFLOP/s", "cores": orc.num_threads(),
+            "kind": "port", "sample": f"first {n} query rows of layer 0, {reps} passes of the fp32 CPU oracle",
+            "gpu_vs_cpu_max_abs_err": err}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode128k", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="decode128k", choices=sorted(WORKLOADS) + ["prefill2k"])
     ap.add_argument("--layers", type=int, default=16, help="fewer layers make a small case for profiling")
+    ap.add_argument("--chunk-blocks", type=int, default=0, help="decode: blocks per split-KV chunk (0 = planner)")
+    ap.add_argument("--decode-shape", default="", help="decode: WARPSxSTAGES, e.g. 8x4 (empty = planner)")
+    ap.add_argument("--ref-literal-append", action="store_true",
+                    help="prefill reference arm: the reference's literal 2*8*tokens 128-byte copies")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     global LAYERS
     LAYERS = args.layers
-    if args.impl == "reference":
+    if args.workload == "prefill2k":
+        run_prefill(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -44,7 +44,7 @@ constexpr int kOffQ = 0;
 constexpr int kOffKV = kOffQ + kQBytes;
 constexpr int kOffP = kOffKV + kStagesKV * (kKBytes + kVBytes);
 constexpr int kOffBar = kOffP + kPBytes;
-constexpr int kNumBars = 4 + 2 * kStagesKV;
+constexpr int kNumBars = 5 + 2 * kStagesKV;
 constexpr int kOffMisc = kOffBar + kNumBars * 8;  // tensor-memory base address, abort flag
 constexpr int kPrefillUsed = kOffMisc + 16;
 // Two CTAs per SM: 2 * (request + 1 KiB system reserve) must stay below 228 KiB,
@@ -176,7 +176,8 @@ prefill_kernel(PrefillParams p) {
   const uint32_t sQ = base + kOffQ, sKV = base + kOffKV, sP = base + kOffP;
   const uint32_t bar0 = base + kOffBar;
   const uint32_t bar_q = bar0, bar_s = bar0 + 8, bar_p = bar0 + 16, bar_pv = bar0 + 24;
-  const uint32_t bar_full = bar0 + 32, bar_empty = bar_full + 8 * kStagesKV;
+  const uint32_t bar_sfree = bar0 + 32;
+  const uint32_t bar_full = bar0 + 40, bar_empty = bar_full + 8 * kStagesKV;
   uint32_t* s_tmem_base = reinterpret_cast<uint32_t*>(sm + kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kOffMisc + 4);
 
@@ -199,6 +200,7 @@ prefill_kernel(PrefillParams p) {
     mbar_init(bar_s, 1);
     mbar_init(bar_p, 128);
     mbar_init(bar_pv, 1);
+    mbar_init(bar_sfree, 128);
     for (int s = 0; s < kStagesKV; s++) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
@@ -262,6 +264,11 @@ prefill_kernel(PrefillParams p) {
     if (ok) ok = issue_qk(0);
     for (int kt = 0; ok && kt < n_tiles; kt++) {
       const int st = kt % kStagesKV;
+      // S(kt) is in the softmax threads' registers: the next Q K^T may overwrite it
+      if (kt + 1 < n_tiles) {
+        if (!wait_or_abort(bar_sfree, (uint32_t)(kt & 1), abort_flag)) break;
+        if (!issue_qk(kt + 1)) break;
+      }
       if (!wait_or_abort(bar_p, (uint32_t)(kt & 1), abort_flag)) break;
       tc_fence_after();
       if (lane == 0) {
@@ -274,7 +281,6 @@ prefill_kernel(PrefillParams p) {
         tc_commit(bar_empty + 8 * st);
       }
       __syncwarp();
-      if (kt + 1 < n_tiles) ok = issue_qk(kt + 1);
     }
   } else {
     // ===================== softmax / epilogue (thread = query row) ===========
@@ -309,20 +315,29 @@ prefill_kernel(PrefillParams p) {
       const bool need_mask = (key0 + kBN - 1 > pos0) || (key0 + kBN > e.kv_len);
       const int limit = min(qpos, e.kv_len - 1) - key0;  // keys with index <= limit are visible
 
-      // pass 1: row maximum of the scaled scores
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c0 = 0; c0 < kBN; c0 += 32) {
-        uint32_t sreg[32];
-        tmem_ld32(tmem + lane_base + kColS + c0, sreg);
-        tmem_wait_ld();
+      // S -> registers in one go (four loads in flight, one wait); the tensor
+      // memory copy is then free for the next tile's Q K^T
+      uint32_t sreg[4][32];
 #pragma unroll
-        for (int j = 0; j < 32; j++) {
-          float s = __uint_as_float(sreg[j]) * p.scale_log2;
-          if (need_mask && c0 + j > limit) s = -INFINITY;
-          mx = fmaxf(mx, s);
-        }
+      for (int c = 0; c < 4; c++) tmem_ld32(tmem + lane_base + kColS + c * 32, sreg[c]);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bar_sfree);
+
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 4; c++)
+#pragma unroll
+          for (int j = 0; j < 32; j++)
+            if (c * 32 + j > limit) sreg[c][j] = 0xff800000u;  // -inf
       }
+      // row maximum (raw scores; the scale is positive)
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; c++)
+#pragma unroll
+        for (int j = 0; j < 32; j++) mx = fmaxf(mx, __uint_as_float(sreg[c][j]));
+      mx *= p.scale_log2;
       // lazy rescale: keep the old reference maximum unless it is off by > 2^8
       float corr = 1.f;
       if (mx > m_used + kRescaleThreshold) {
@@ -350,31 +365,23 @@ prefill_kernel(PrefillParams p) {
       }
       l_sum *= corr;
 
-      // pass 2: probabilities -> bf16 -> shared memory (K-major, swizzled)
-#pragma unroll 1
-      for (int c0 = 0; c0 < kBN; c0 += 32) {
-        uint32_t sreg[32];
-        tmem_ld32(tmem + lane_base + kColS + c0, sreg);
-        tmem_wait_ld();
-        uint32_t packed[16];
+      // probabilities -> bf16 -> shared memory (K-major, swizzled)
+      const float neg_m = -m_used;
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float s0 = __uint_as_float(sreg[j]) * p.scale_log2 - m_used;
-          float s1 = __uint_as_float(sreg[j + 1]) * p.scale_log2 - m_used;
-          if (need_mask) {
-            if (c0 + j > limit) s0 = -INFINITY;
-            if (c0 + j + 1 > limit) s1 = -INFINITY;
+      for (int c = 0; c < 4; c++) {
+        unsigned char* prow = sm + kOffP + (c >> 1) * (kBM * 128) + r * 128;
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+          uint32_t w[4];
+#pragma unroll
+          for (int u = 0; u < 4; u++) {
+            const float p0 = ex2(fmaf(__uint_as_float(sreg[c][g * 8 + 2 * u]), p.scale_log2, neg_m));
+            const float p1 = ex2(fmaf(__uint_as_float(sreg[c][g * 8 + 2 * u + 1]), p.scale_log2, neg_m));
+            l_sum += p0 + p1;
+            w[u] = pack_bf16(p0, p1);
           }
-          const float p0 = ex2(s0), p1 = ex2(s1);
-          l_sum += p0 + p1;
-          packed[j >> 1] = pack_bf16(p0, p1);
-        }
-        unsigned char* prow = sm + kOffP + (c0 >> 6) * (kBM * 128) + r * 128;
-#pragma unroll
-        for (int c = 0; c < 4; c++) {
-          const int chunk = ((c0 & 63) >> 3) + c;
-          *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) =
-              make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+          const int chunk = (c & 1) * 4 + g;
+          *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
       fence_proxy_async_smem();
