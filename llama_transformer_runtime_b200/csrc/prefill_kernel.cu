@@ -184,8 +184,10 @@ prefill_kernel(PrefillParams p) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const BatchEntry e = p.batch[0];
   const int n_q_tiles = (e.n_q + kBM - 1) / kBM;
-  const int q_tile = n_q_tiles - 1 - (int)blockIdx.x;  // heaviest tiles first
-  const int h = blockIdx.y;
+  // CTAs are dispatched in linear order (x fastest): all heads of the heaviest
+  // query tile first, the lightest tiles last, so the tail of the grid is short
+  const int q_tile = n_q_tiles - 1 - (int)blockIdx.y;
+  const int h = blockIdx.x;
   const int row0 = q_tile * kBM;
   const int rows = min(kBM, e.n_q - row0);
   const int pos0 = e.q_pos0 + row0;                            // position of row 0
@@ -346,6 +348,21 @@ prefill_kernel(PrefillParams p) {
       }
       const bool any_corr = __any_sync(0xffffffffu, corr != 1.f);
 
+      // probabilities -> bf16, kept in registers: the exponentials (the bulk of
+      // the work) run while the previous tile's P V is still in the tensor pipe
+      const float neg_m = -m_used;
+      float l_tile = 0.f;
+      uint32_t pk[4][16];
+#pragma unroll
+      for (int c = 0; c < 4; c++)
+#pragma unroll
+        for (int u = 0; u < 16; u++) {
+          const float p0 = ex2(fmaf(__uint_as_float(sreg[c][2 * u]), p.scale_log2, neg_m));
+          const float p1 = ex2(fmaf(__uint_as_float(sreg[c][2 * u + 1]), p.scale_log2, neg_m));
+          l_tile += p0 + p1;
+          pk[c][u] = pack_bf16(p0, p1);
+        }
+
       // P of the previous tile must have been consumed, O must be quiescent
       if (kt > 0) {
         if (!wait_or_abort(bar_pv, (uint32_t)((kt - 1) & 1), abort_flag)) { ok = false; break; }
@@ -363,25 +380,17 @@ prefill_kernel(PrefillParams p) {
           tmem_wait_st();
         }
       }
-      l_sum *= corr;
+      l_sum = l_sum * corr + l_tile;
 
-      // probabilities -> bf16 -> shared memory (K-major, swizzled)
-      const float neg_m = -m_used;
+      // P -> shared memory (K-major, swizzled)
 #pragma unroll
       for (int c = 0; c < 4; c++) {
         unsigned char* prow = sm + kOffP + (c >> 1) * (kBM * 128) + r * 128;
 #pragma unroll
         for (int g = 0; g < 4; g++) {
-          uint32_t w[4];
-#pragma unroll
-          for (int u = 0; u < 4; u++) {
-            const float p0 = ex2(fmaf(__uint_as_float(sreg[c][g * 8 + 2 * u]), p.scale_log2, neg_m));
-            const float p1 = ex2(fmaf(__uint_as_float(sreg[c][g * 8 + 2 * u + 1]), p.scale_log2, neg_m));
-            l_sum += p0 + p1;
-            w[u] = pack_bf16(p0, p1);
-          }
           const int chunk = (c & 1) * 4 + g;
-          *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) =
+              make_uint4(pk[c][4 * g], pk[c][4 * g + 1], pk[c][4 * g + 2], pk[c][4 * g + 3]);
         }
       }
       fence_proxy_async_smem();
@@ -439,7 +448,7 @@ cudaError_t launch_prefill(const PrefillParams& p, int n_q, cudaStream_t stream)
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  dim3 grid((n_q + kBM - 1) / kBM, p.kv_heads * kGroup);
+  dim3 grid(p.kv_heads * kGroup, (n_q + kBM - 1) / kBM);
   prefill_kernel<<<grid, kPrefillThreads, kPrefillSmem, stream>>>(p);
   return cudaGetLastError();
 }
