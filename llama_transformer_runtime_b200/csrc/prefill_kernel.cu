@@ -122,6 +122,31 @@ __device__ __forceinline__ void tmem_wait_st() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// ---- sm_100 scalar helpers: 3-input max and packed fp32x2 arithmetic -----------
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes
 // apart (version 1 = Blackwell, layout type 2 = SWIZZLE_128B).  The same
 // encoding serves K-major operands (rows = M or N index, 128 bytes of K per
@@ -334,12 +359,16 @@ prefill_kernel(PrefillParams p) {
             if (c * 32 + j > limit) sreg[c][j] = 0xff800000u;  // -inf
       }
       // row maximum (raw scores; the scale is positive)
-      float mx = -INFINITY;
+      // four independent chains of 3-input max
+      float mxc[4];
 #pragma unroll
-      for (int c = 0; c < 4; c++)
+      for (int c = 0; c < 4; c++) {
+        mxc[c] = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < 32; j++) mx = fmaxf(mx, __uint_as_float(sreg[c][j]));
-      mx *= p.scale_log2;
+        for (int j = 0; j < 32; j += 2)
+          mxc[c] = max3(mxc[c], __uint_as_float(sreg[c][j]), __uint_as_float(sreg[c][j + 1]));
+      }
+      float mx = fmaxf(fmaxf(mxc[0], mxc[1]), fmaxf(mxc[2], mxc[3])) * p.scale_log2;
       // lazy rescale: keep the old reference maximum unless it is off by > 2^8
       float corr = 1.f;
       if (mx > m_used + kRescaleThreshold) {
@@ -351,17 +380,30 @@ prefill_kernel(PrefillParams p) {
       // probabilities -> bf16, kept in registers: the exponentials (the bulk of
       // the work) run while the previous tile's P V is still in the tensor pipe
       const float neg_m = -m_used;
-      float l_tile = 0.f;
+      // packed fp32x2 arithmetic (two values per instruction) around the exp2
+      const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
+      const uint64_t negm2 = pack_f32x2(neg_m, neg_m);
+      uint64_t lacc[4];
       uint32_t pk[4][16];
 #pragma unroll
-      for (int c = 0; c < 4; c++)
+      for (int c = 0; c < 4; c++) {
+        lacc[c] = 0ull;
 #pragma unroll
         for (int u = 0; u < 16; u++) {
-          const float p0 = ex2(fmaf(__uint_as_float(sreg[c][2 * u]), p.scale_log2, neg_m));
-          const float p1 = ex2(fmaf(__uint_as_float(sreg[c][2 * u + 1]), p.scale_log2, neg_m));
-          l_tile += p0 + p1;
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sreg[c][2 * u]),
+                                            __uint_as_float(sreg[c][2 * u + 1])), scale2, negm2), x0, x1);
+          const float p0 = ex2(x0), p1 = ex2(x1);
+          lacc[c] = add_f32x2(lacc[c], pack_f32x2(p0, p1));
           pk[c][u] = pack_bf16(p0, p1);
         }
+      }
+      float l_tile;
+      {
+        float a0, a1;
+        unpack_f32x2(add_f32x2(add_f32x2(lacc[0], lacc[1]), add_f32x2(lacc[2], lacc[3])), a0, a1);
+        l_tile = a0 + a1;
+      }
 
       // P of the previous tile must have been consumed, O must be quiescent
       if (kt > 0) {
