@@ -190,6 +190,14 @@ def run_ours(args):
         o_parts = torch.zeros(world, Q_HEADS, D, dtype=torch.float32, device=dev)
         l_parts = torch.zeros(world, Q_HEADS, dtype=torch.float32, device=dev)
 
+    xchg = None
+    if world > 1 and args.exchange == "fused":
+        xchg = paged.Exchange(local_rank, rank, world, 1, KV_HEADS)
+        handles = [None] * world
+        dist.all_gather_object(handles, xchg.handle())
+        xchg.connect(handles)
+        dist.barrier()
+
     state = {"global_len": ctx, "launches": 0}
 
     def step(qs, ks, vs, outs):
@@ -205,6 +213,13 @@ def run_ours(args):
             state["launches"] += 2 * LAYERS
             return
         pool.batch_set_sharded([seq], [1 if rank == owner else 0], [1], [g - 1], [lo])
+        if xchg is not None:
+            # fused exchange: partials pushed to every rank by the decode kernel's epilogue
+            paged.decode_step_sharded(pool, xchg, 0, LAYERS, qs, ks if rank == owner else None,
+                                      vs if rank == owner else None, Q_HEADS * D, KV_HEADS * D, cos, sin,
+                                      q_rot, outs, Q_HEADS * D, Q_HEADS * D)
+            state["launches"] += 3 * LAYERS
+            return
         for layer in range(LAYERS):
             pool.append(layer, qs[layer], ks[layer], vs[layer], cos, sin, q_rot[layer])
             pool.decode(layer, q_rot[layer], None, 0, part[layer, :Q_HEADS * D], part[layer, Q_HEADS * D:])
@@ -267,11 +282,11 @@ def run_ours(args):
     # ---- dominant kernel alone: 16 back-to-back decode launches (one per layer) per event pair
     pool.batch_set_sharded([seq], [0], [1], [state["global_len"] - 1], [lo])
     L_local = pool.length(seq)
-    f32o = torch.zeros(1, Q_HEADS, D, dtype=torch.float32, device=dev)
+    local_out = out_dev if world == 1 else torch.zeros_like(out_dev)  # N>1: keep the merged rows
 
     def decode_only():
         for layer in range(LAYERS):
-            pool.decode(layer, q_rot[layer], out_dev[layer], Q_HEADS * D, None, None)
+            pool.decode(layer, q_rot[layer], local_out[layer], Q_HEADS * D, None, None)
 
     decode_only()
     reps = max(3, args.steps)
@@ -281,6 +296,17 @@ def run_ours(args):
     peak, peak_kind = measured_peak()
     pool.check()
     m1 = sampler.mark()
+    xchg_check = None
+    if world > 1:
+        # the last step's merged layer-0 row against an NCCL all-gather + merge of the same partials
+        pool.decode(0, q_rot[0], None, 0, part[0, :Q_HEADS * D], part[0, Q_HEADS * D:])
+        dist.all_gather_into_tensor(gathered[0].view(-1), part[0])
+        o_parts.copy_(gathered[0, :, :Q_HEADS * D].reshape(world, Q_HEADS, D))
+        l_parts.copy_(gathered[0, :, Q_HEADS * D:])
+        chk = torch.zeros(1, Q_HEADS * D, dtype=torch.bfloat16, device=dev)
+        paged.merge_partials(o_parts, l_parts, world, Q_HEADS, chk)
+        torch.cuda.synchronize()
+        xchg_check = float((chk.float() - out_dev[0].float()).abs().max().item())
 
     line = None
     if rank == 0:
@@ -296,7 +322,11 @@ def run_ours(args):
             "config": {"workload": wl["name"], "context": ctx, "layers": LAYERS, "batch": 1,
                        "q_heads": Q_HEADS, "kv_heads": KV_HEADS, "head_dim": D, "block_tokens": BLOCK,
                        "block_table": "seeded random permutation over a pool 25% larger than the sequence",
-                       "parallelism": "1 GPU" if world == 1 else f"sequence range split over {world} GPUs, NCCL all-gather of (O, LSE) per layer + merge",
+                       "parallelism": "1 GPU" if world == 1 else (
+                           f"sequence range split over {world} GPUs; per layer the decode epilogue pushes (O, LSE) "
+                           f"to every rank over NVLink (peer stores + flags), then a local merge"
+                           if xchg is not None else
+                           f"sequence range split over {world} GPUs, NCCL all-gather of (O, LSE) per layer + merge"),
                        "l2": f"inputs larger than L2 ({decode_bytes(ctx) * LAYERS / 1e9:.2f} GB streamed per step)"},
             "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": round(ms_e2e / args.steps, 4)},
@@ -310,8 +340,12 @@ def run_ours(args):
         }
         if world == 1:
             line["cpu_baseline"] = cpu_baseline(pool, seq, q_rot, out_dev, L_local)
+        else:
+            line["exchange_vs_allgather_max_abs_diff"] = xchg_check
         print(json.dumps(line), flush=True)
     barrier()
+    if xchg is not None:
+        xchg.close()
     pool.close()
     if world > 1:
         dist.destroy_process_group()
@@ -659,6 +693,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode128k", choices=sorted(WORKLOADS) + ["prefill2k"])
     ap.add_argument("--layers", type=int, default=16, help="fewer layers make a small case for profiling")
+    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
+                    help="N>1: partials pushed by the decode epilogue over NVLink (fused) or NCCL all-gather")
     ap.add_argument("--chunk-blocks", type=int, default=0, help="decode: blocks per split-KV chunk (0 = planner)")
     ap.add_argument("--decode-shape", default="", help="decode: WARPSxSTAGES, e.g. 8x4 (empty = planner)")
     ap.add_argument("--ref-literal-append", action="store_true",

@@ -175,6 +175,32 @@ int pa_merge_partials(const float* o_parts, const float* lse_parts, int n_parts,
 int pa_gather_kv(pa_pool* pool, int layer, int seq_id, void* k_out, void* v_out,
                  int out_stride_tokens, void* stream);
 
+/* ---- sequence-range sharding over several GPUs (one process per GPU) --------
+ * The reference is single-GPU; this is the exchange long-context decode needs
+ * once a sequence's cache is split by token range over n pools.  Each rank's
+ * decode kernel stores its partial (normalised O, LSE) into every rank's
+ * receive buffer with peer stores and raises a flag; pa_decode_step_sharded
+ * then waits (bounded, PA_ERR_TIMEOUT via pa_pool_check) for all ranks' flags
+ * and merges from local memory.  Buffers are shared through CUDA IPC handles of
+ * PA_EXCHANGE_HANDLE_BYTES bytes that the host passes between processes.
+ * All ranks must issue the same sequence of sharded steps. */
+typedef struct pa_exchange pa_exchange;
+#define PA_EXCHANGE_HANDLE_BYTES 64
+int pa_exchange_create(pa_exchange** out, int device, int rank, int world, int n_seqs,
+                       int kv_heads);
+int pa_exchange_handle(pa_exchange* x, void* handle64);
+/* handles: world * PA_EXCHANGE_HANDLE_BYTES bytes in rank order */
+int pa_exchange_connect(pa_exchange* x, const void* handles);
+int pa_exchange_destroy(pa_exchange* x);
+/* pa_decode_step for a range-sharded batch (see pa_batch_set_sharded); k_in and
+ * v_in may be NULL on ranks that append nothing.  out receives the merged rows. */
+int pa_decode_step_sharded(pa_pool* pool, pa_exchange* x, int layer_begin, int layer_end,
+                           const void* q_in, const void* k_in, const void* v_in,
+                           int64_t q_layer_stride, int64_t kv_layer_stride,
+                           const float* cos_table, const float* sin_table, void* q_rot,
+                           void* out, int64_t out_stride, int64_t out_layer_stride,
+                           float scale, void* stream);
+
 /* pa_decode_noalloc: pa_decode for hosts that are not allowed to allocate
  * device memory — a plug-in inside a serving process that owns the whole GPU
  * through its own arena, a latency-critical loop that cannot afford the

@@ -19,7 +19,8 @@ SYMBOLS = [
     "pa_seq_reserve", "pa_seq_length", "pa_seq_block_table", "pa_batch_set", "pa_batch_set_sharded", "pa_append",
     "pa_decode", "pa_decode_step", "pa_prefill", "pa_merge_partials", "pa_gather_kv", "pa_build_rope_tables",
     "pa_pool_check", "pa_pool_set_decode_chunk_blocks", "pa_pool_set_decode_shape",
-    "pa_decode_noalloc",
+    "pa_decode_noalloc", "pa_exchange_create", "pa_exchange_handle", "pa_exchange_connect",
+    "pa_exchange_destroy", "pa_decode_step_sharded",
 ]
 
 
@@ -65,6 +66,11 @@ def lib():
         "pa_pool_set_decode_chunk_blocks": [vp, i],
         "pa_pool_set_decode_shape": [vp, i, i],
         "pa_decode_noalloc": [vp, i, i, vp, i, vp, i, vp, vp, i64, vp, f, vp],
+        "pa_exchange_create": [C.POINTER(vp), i, i, i, i, i],
+        "pa_exchange_handle": [vp, vp],
+        "pa_exchange_connect": [vp, vp],
+        "pa_exchange_destroy": [vp],
+        "pa_decode_step_sharded": [vp, vp, i, i, vp, vp, vp, i64, i64, vp, vp, vp, vp, i64, i64, f, vp],
         "pa_debug_set_rope_variant": [vp, i],
     }
     for name, args in sigs.items():

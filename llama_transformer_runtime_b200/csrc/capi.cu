@@ -74,6 +74,13 @@ struct pa_pool {
   pa_pool(int nb, int ms, int mb) : host(nb, ms, mb) {}
 };
 
+struct pa_exchange;
+namespace pa {
+bool exchange_fill(pa_exchange* x, DecodeParams& d, ExchangeMergeParams& m);
+int exchange_rows(const pa_exchange* x);
+int exchange_groups(const pa_exchange* x);
+}  // namespace pa
+
 extern "C" {
 
 const char* pa_last_error(void) { return g_err; }
@@ -332,8 +339,8 @@ static DecodePlan pick_plan(const pa_pool* p) {
   return plan;
 }
 
-int pa_decode(pa_pool* p, int layer, const void* q, void* out, int64_t out_stride, float* out_f32,
-              float* lse, float scale, void* stream) {
+static int decode_impl(pa_pool* p, int layer, const void* q, void* out, int64_t out_stride, float* out_f32,
+                       float* lse, float scale, void* stream, pa_exchange* x) {
   if (!p || !q) return fail(PA_ERR_INVALID_ARG, "pa_decode: NULL argument");
   if (!out && !out_f32) return fail(PA_ERR_INVALID_ARG, "pa_decode: no output buffer");
   if (p->device < 0) return fail(PA_ERR_STATE, "pa_decode: host-only pool");
@@ -372,7 +379,53 @@ int pa_decode(pa_pool* p, int layer, const void* q, void* out, int64_t out_strid
   d.max_blocks_per_seq = p->host.max_blocks_per_seq();
   d.chunk_blocks = cb;
   d.max_chunks = max_chunks;
+  if (!x) {
+    PA_CUDA(pa::launch_decode(d, n_seqs, plan.warps, plan.stages, (cudaStream_t)stream));
+    return PA_OK;
+  }
+  // sequence-range sharding: partials go to every rank's receive buffer, the
+  // merge kernel writes the bf16 rows once all ranks' partials have landed
+  if (pa::exchange_rows(x) != n_seqs * p->kv_heads * pa::kGroup || pa::exchange_groups(x) != n_seqs * p->kv_heads)
+    return fail(PA_ERR_INVALID_ARG, "pa_decode_step_sharded: the exchange was created for another batch size or head count");
+  pa::ExchangeMergeParams m;
+  if (!pa::exchange_fill(x, d, m)) return fail(PA_ERR_STATE, "pa_decode_step_sharded: exchange not connected");
+  d.out = nullptr;
+  d.out_f32 = nullptr;
+  d.lse = nullptr;
+  m.out = (__nv_bfloat16*)out;
+  m.out_stride = out_stride;
+  m.status = p->d_status;
+  m.q_heads = p->kv_heads * pa::kGroup;
   PA_CUDA(pa::launch_decode(d, n_seqs, plan.warps, plan.stages, (cudaStream_t)stream));
+  PA_CUDA(pa::launch_exchange_merge(m, (cudaStream_t)stream));
+  return PA_OK;
+}
+
+int pa_decode(pa_pool* p, int layer, const void* q, void* out, int64_t out_stride, float* out_f32,
+              float* lse, float scale, void* stream) {
+  return decode_impl(p, layer, q, out, out_stride, out_f32, lse, scale, stream, nullptr);
+}
+
+int pa_decode_step_sharded(pa_pool* p, pa_exchange* x, int layer_begin, int layer_end, const void* q_in,
+                           const void* k_in, const void* v_in, int64_t q_layer_stride,
+                           int64_t kv_layer_stride, const float* cos_table, const float* sin_table,
+                           void* q_rot, void* out, int64_t out_stride, int64_t out_layer_stride,
+                           float scale, void* stream) {
+  if (!p || !x || !q_in || !q_rot || !out) return fail(PA_ERR_INVALID_ARG, "pa_decode_step_sharded: NULL argument");
+  if (layer_begin < 0 || layer_end > p->num_layers || layer_begin > layer_end)
+    return fail(PA_ERR_INVALID_ARG, "pa_decode_step_sharded: layers [%d, %d) out of range", layer_begin, layer_end);
+  for (int l = layer_begin; l < layer_end; l++) {
+    const int i = l - layer_begin;
+    const __nv_bfloat16* qi = (const __nv_bfloat16*)q_in + (size_t)i * q_layer_stride;
+    const __nv_bfloat16* ki = k_in ? (const __nv_bfloat16*)k_in + (size_t)i * kv_layer_stride : nullptr;
+    const __nv_bfloat16* vi = v_in ? (const __nv_bfloat16*)v_in + (size_t)i * kv_layer_stride : nullptr;
+    __nv_bfloat16* qr = (__nv_bfloat16*)q_rot + (size_t)i * q_layer_stride;
+    __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)i * out_layer_stride;
+    int r = pa_append(p, l, qi, ki, vi, cos_table, sin_table, qr, stream);
+    if (r != PA_OK) return r;
+    r = decode_impl(p, l, qr, o, out_stride, nullptr, nullptr, scale, stream, x);
+    if (r != PA_OK) return r;
+  }
   return PA_OK;
 }
 

@@ -47,6 +47,31 @@ __device__ __forceinline__ void write_row_outputs(const DecodeParams& p, int z, 
   if (p.out_f32) p.out_f32[((size_t)z * q_heads + head) * kHeadDim + d] = v;
   if (p.lse && d == 0)
     p.lse[(size_t)z * q_heads + head] = l > 0.f ? kLn2 * (m + log2f(l)) : -INFINITY;
+  if (p.xchg_world > 0) {
+    // sequence-range sharding: push this rank's normalised partial and its LSE
+    // into every rank's receive buffer (plain peer stores over NVLink; each
+    // rank later reads only its own memory)
+    const int row = z * q_heads + head;
+    const size_t at = ((size_t)(p.xchg_slot * p.xchg_world + p.xchg_rank) * p.xchg_rows + row) * kXchgRowFloats;
+    const float lse = l > 0.f ? kLn2 * (m + log2f(l)) : -INFINITY;
+    for (int g = 0; g < p.xchg_world; g++) {
+      p.xchg_peer[g][at + d] = v;
+      if (d == 0) p.xchg_peer[g][at + kHeadDim] = lse;
+    }
+  }
+}
+
+// After a (sequence, KV head) group's rows have been pushed: make them visible
+// system-wide, then publish the step number in every rank's flag for this
+// source rank and head.  Called by all threads of the CTA.
+__device__ __forceinline__ void publish_exchange(const DecodeParams& p, int z, int h) {
+  if (p.xchg_world <= 0) return;
+  __threadfence_system();
+  __syncthreads();
+  if ((int)threadIdx.x < p.xchg_world) {
+    unsigned int* flag = p.xchg_flag[threadIdx.x] + ((size_t)p.xchg_rank * p.xchg_groups + z * p.kv_heads + h);
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(p.xchg_seq) : "memory");
+  }
 }
 
 template <int WARPS, int STAGES>
@@ -244,7 +269,10 @@ decode_kernel(DecodeParams p) {
       }
     }
   }
-  if (n_chunks == 1) return;
+  if (n_chunks == 1) {
+    publish_exchange(p, z, h);
+    return;
+  }
 
   // ---- combine across chunks: the last CTA to arrive does it ---------------
   __threadfence();
@@ -327,6 +355,7 @@ decode_kernel(DecodeParams p) {
     write_row_outputs(p, z, h, idx >> 6, idx & 63, O, mrg_m[idx >> 6], mrg_l[idx >> 6]);
   }
   if (threadIdx.x == 0) p.ws_count[z * p.kv_heads + h] = 0u;
+  publish_exchange(p, z, h);
 }
 
 template <int WARPS, int STAGES>

@@ -48,7 +48,28 @@ struct DecodeParams {
   long long out_stride;
   float scale_log2;           // scale * log2(e)
   int kv_heads, num_blocks, max_blocks_per_seq, chunk_blocks, max_chunks;
+  // Cross-GPU exchange of split-KV partials (sequence-range sharding); off when
+  // xchg_world == 0.  Receive buffer of rank g: data [2 slots][world][rows][65]
+  // fp32 (64 normalised outputs + natural-log LSE), flags [world][groups] u32.
+  float* xchg_peer[8] = {};
+  unsigned int* xchg_flag[8] = {};
+  int xchg_world = 0, xchg_rank = 0, xchg_rows = 0, xchg_groups = 0, xchg_slot = 0;
+  unsigned int xchg_seq = 0;
 };
+constexpr int kXchgRowFloats = kHeadDim + 1;
+
+// Waits (bounded) until every rank's partial of step `seq` has landed in this
+// rank's receive buffer, then merges them: out rows bf16, stride out_stride.
+struct ExchangeMergeParams {
+  const float* data;           // this rank's receive buffer
+  const unsigned int* flags;   // [world][groups]
+  __nv_bfloat16* out;
+  int* status;
+  long long out_stride;
+  int world, rows, groups, slot, q_heads;
+  unsigned int seq;
+};
+cudaError_t launch_exchange_merge(const ExchangeMergeParams& p, cudaStream_t stream);
 cudaError_t launch_decode(const DecodeParams& p, int n_seqs, int warps, int stages,
                           cudaStream_t stream);
 bool decode_shape_supported(int warps, int stages);

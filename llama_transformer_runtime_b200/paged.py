@@ -162,6 +162,44 @@ class KVPool:
         check(lib().pa_debug_set_rope_variant(self._h, v))
 
 
+class Exchange:
+    """Receive buffer + peer mappings for sequence-range sharded decode (one per rank).
+
+    ``handle()`` gives the 64-byte CUDA IPC handle of this rank's buffer; after every
+    rank's handle has been gathered (in rank order) ``connect()`` maps the peers."""
+
+    HANDLE_BYTES = 64
+
+    def __init__(self, device: int, rank: int, world: int, n_seqs: int = 1, kv_heads: int = 8):
+        self._h = C.c_void_p()
+        self.rank, self.world = rank, world
+        check(lib().pa_exchange_create(C.byref(self._h), device, rank, world, n_seqs, kv_heads))
+
+    def handle(self) -> bytes:
+        buf = C.create_string_buffer(self.HANDLE_BYTES)
+        check(lib().pa_exchange_handle(self._h, buf))
+        return buf.raw
+
+    def connect(self, handles) -> None:
+        blob = b"".join(handles)
+        assert len(blob) == self.world * self.HANDLE_BYTES
+        check(lib().pa_exchange_connect(self._h, C.create_string_buffer(blob, len(blob))))
+
+    def close(self) -> None:
+        if self._h:
+            lib().pa_exchange_destroy(self._h)
+            self._h = C.c_void_p()
+
+
+def decode_step_sharded(pool: "KVPool", xchg: Exchange, layer_begin: int, layer_end: int, q_in, k_in,
+                        v_in, q_layer_stride: int, kv_layer_stride: int, cos, sin, q_rot, out,
+                        out_stride: int, out_layer_stride: int, scale: float = 0.125,
+                        stream: int = 0) -> None:
+    check(lib().pa_decode_step_sharded(pool._h, xchg._h, layer_begin, layer_end, _ptr(q_in), _ptr(k_in),
+                                       _ptr(v_in), q_layer_stride, kv_layer_stride, _ptr(cos), _ptr(sin),
+                                       _ptr(q_rot), _ptr(out), out_stride, out_layer_stride, scale, stream))
+
+
 def decode_noalloc(cache_layer, num_blocks: int, kv_heads: int, block_tables, table_stride: int,
                    kv_lens, q, out, out_stride: int, lse=None, scale: float = 0.125,
                    stream: int = 0) -> None:
