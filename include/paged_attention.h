@@ -191,7 +191,19 @@ int pa_exchange_create(pa_exchange** out, int device, int rank, int world, int n
 int pa_exchange_handle(pa_exchange* x, void* handle64);
 /* handles: world * PA_EXCHANGE_HANDLE_BYTES bytes in rank order */
 int pa_exchange_connect(pa_exchange* x, const void* handles);
+/* The same mapping for a host that drives several GPUs from ONE process (it has
+ * enabled peer access itself): every rank's receive buffer as a plain pointer. */
+int pa_exchange_buffer(pa_exchange* x, void** dev_ptr, uint64_t* bytes);
+int pa_exchange_connect_ptrs(pa_exchange* x, void* const* peer_buffers);
 int pa_exchange_destroy(pa_exchange* x);
+/* The two halves of a sharded decode of one layer: pa_decode_push runs the
+ * decode kernel, which pushes this rank's partials to all ranks;
+ * pa_exchange_merge waits for all ranks' partials of that step and writes the
+ * merged bf16 rows.  (pa_decode_step_sharded issues both per layer.) */
+int pa_decode_push(pa_pool* pool, pa_exchange* x, int layer, const void* q, float scale,
+                   void* stream);
+int pa_exchange_merge(pa_pool* pool, pa_exchange* x, void* out, int64_t out_stride,
+                      void* stream);
 /* pa_decode_step for a range-sharded batch (see pa_batch_set_sharded); k_in and
  * v_in may be NULL on ranks that append nothing.  out receives the merged rows. */
 int pa_decode_step_sharded(pa_pool* pool, pa_exchange* x, int layer_begin, int layer_end,

@@ -20,7 +20,8 @@ SYMBOLS = [
     "pa_decode", "pa_decode_step", "pa_prefill", "pa_merge_partials", "pa_gather_kv", "pa_build_rope_tables",
     "pa_pool_check", "pa_pool_set_decode_chunk_blocks", "pa_pool_set_decode_shape",
     "pa_decode_noalloc", "pa_exchange_create", "pa_exchange_handle", "pa_exchange_connect",
-    "pa_exchange_destroy", "pa_decode_step_sharded",
+    "pa_exchange_destroy", "pa_decode_step_sharded", "pa_exchange_buffer", "pa_exchange_connect_ptrs",
+    "pa_decode_push", "pa_exchange_merge",
 ]
 
 
@@ -70,6 +71,10 @@ def lib():
         "pa_exchange_handle": [vp, vp],
         "pa_exchange_connect": [vp, vp],
         "pa_exchange_destroy": [vp],
+        "pa_exchange_buffer": [vp, C.POINTER(vp), C.POINTER(C.c_uint64)],
+        "pa_exchange_connect_ptrs": [vp, C.POINTER(vp)],
+        "pa_decode_push": [vp, vp, i, vp, f, vp],
+        "pa_exchange_merge": [vp, vp, vp, i64, vp],
         "pa_decode_step_sharded": [vp, vp, i, i, vp, vp, vp, i64, i64, vp, vp, vp, vp, i64, i64, f, vp],
         "pa_debug_set_rope_variant": [vp, i],
     }

@@ -77,6 +77,7 @@ struct pa_pool {
 struct pa_exchange;
 namespace pa {
 bool exchange_fill(pa_exchange* x, DecodeParams& d, ExchangeMergeParams& m);
+bool exchange_current(pa_exchange* x, ExchangeMergeParams& m);
 int exchange_rows(const pa_exchange* x);
 int exchange_groups(const pa_exchange* x);
 }  // namespace pa
@@ -339,10 +340,12 @@ static DecodePlan pick_plan(const pa_pool* p) {
   return plan;
 }
 
+// x != nullptr: sequence-range sharded decode.  with_merge == false only pushes
+// the partials; the merge of that step is then launched by pa_exchange_merge.
 static int decode_impl(pa_pool* p, int layer, const void* q, void* out, int64_t out_stride, float* out_f32,
-                       float* lse, float scale, void* stream, pa_exchange* x) {
+                       float* lse, float scale, void* stream, pa_exchange* x, bool with_merge = true) {
   if (!p || !q) return fail(PA_ERR_INVALID_ARG, "pa_decode: NULL argument");
-  if (!out && !out_f32) return fail(PA_ERR_INVALID_ARG, "pa_decode: no output buffer");
+  if (!out && !out_f32 && !(x && !with_merge)) return fail(PA_ERR_INVALID_ARG, "pa_decode: no output buffer");
   if (p->device < 0) return fail(PA_ERR_STATE, "pa_decode: host-only pool");
   if (layer < 0 || layer >= p->num_layers) return fail(PA_ERR_INVALID_ARG, "pa_decode: layer %d out of range", layer);
   if (p->batch.empty()) return fail(PA_ERR_STATE, "pa_decode: no active batch (call pa_batch_set)");
@@ -397,6 +400,27 @@ static int decode_impl(pa_pool* p, int layer, const void* q, void* out, int64_t 
   m.status = p->d_status;
   m.q_heads = p->kv_heads * pa::kGroup;
   PA_CUDA(pa::launch_decode(d, n_seqs, plan.warps, plan.stages, (cudaStream_t)stream));
+  if (with_merge) PA_CUDA(pa::launch_exchange_merge(m, (cudaStream_t)stream));
+  return PA_OK;
+}
+
+int pa_decode_push(pa_pool* p, pa_exchange* x, int layer, const void* q, float scale, void* stream) {
+  if (!x) return fail(PA_ERR_INVALID_ARG, "pa_decode_push: NULL exchange");
+  return decode_impl(p, layer, q, nullptr, 0, nullptr, nullptr, scale, stream, x, false);
+}
+
+int pa_exchange_merge(pa_pool* p, pa_exchange* x, void* out, int64_t out_stride, void* stream) {
+  if (!p || !x || !out) return fail(PA_ERR_INVALID_ARG, "pa_exchange_merge: NULL argument");
+  if (p->device < 0) return fail(PA_ERR_STATE, "pa_exchange_merge: host-only pool");
+  pa::ExchangeMergeParams m;
+  if (!pa::exchange_current(x, m)) return fail(PA_ERR_STATE, "pa_exchange_merge: no exchange step in flight");
+  if (out_stride < (int64_t)p->kv_heads * pa::kGroup * pa::kHeadDim)
+    return fail(PA_ERR_INVALID_ARG, "pa_exchange_merge: out_stride shorter than a row");
+  DeviceGuard g(p->device);
+  m.out = (__nv_bfloat16*)out;
+  m.out_stride = out_stride;
+  m.status = p->d_status;
+  m.q_heads = p->kv_heads * pa::kGroup;
   PA_CUDA(pa::launch_exchange_merge(m, (cudaStream_t)stream));
   return PA_OK;
 }

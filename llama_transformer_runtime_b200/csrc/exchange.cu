@@ -105,7 +105,8 @@ cudaError_t launch_exchange_merge(const ExchangeMergeParams& p, cudaStream_t str
   return cudaGetLastError();
 }
 
-// Used by capi.cu to fill the decode launch descriptor.
+// Used by capi.cu: start the next exchange step (fills the decode launch
+// descriptor) and describe the matching merge.
 bool exchange_fill(pa_exchange* x, DecodeParams& d, ExchangeMergeParams& m) {
   if (!x || !x->connected) return false;
   x->seq++;
@@ -126,6 +127,18 @@ bool exchange_fill(pa_exchange* x, DecodeParams& d, ExchangeMergeParams& m) {
   m.rows = x->rows;
   m.groups = x->groups;
   m.slot = slot;
+  m.seq = x->seq;
+  return true;
+}
+// The merge of the step most recently started with exchange_fill.
+bool exchange_current(pa_exchange* x, ExchangeMergeParams& m) {
+  if (!x || !x->connected || x->seq == 0) return false;
+  m.data = reinterpret_cast<const float*>(x->local);
+  m.flags = reinterpret_cast<const unsigned int*>(x->local + x->data_bytes);
+  m.world = x->world;
+  m.rows = x->rows;
+  m.groups = x->groups;
+  m.slot = (int)(x->seq & 1u);
   m.seq = x->seq;
   return true;
 }
@@ -164,6 +177,26 @@ int pa_exchange_create(pa_exchange** out, int device, int rank, int world, int n
   x->peer[rank] = x->local;
   if (world == 1) x->connected = true;
   *out = x;
+  return PA_OK;
+}
+
+int pa_exchange_buffer(pa_exchange* x, void** dev_ptr, uint64_t* bytes) {
+  if (!x) return xfail(PA_ERR_INVALID_ARG, "pa_exchange_buffer: NULL argument");
+  if (dev_ptr) *dev_ptr = x->local;
+  if (bytes) *bytes = x->bytes;
+  return PA_OK;
+}
+
+// For hosts that drive several GPUs from one process (peer access enabled by
+// the caller) and for single-GPU tests: the ranks' buffers as plain pointers.
+int pa_exchange_connect_ptrs(pa_exchange* x, void* const* peer_buffers) {
+  if (!x || !peer_buffers) return xfail(PA_ERR_INVALID_ARG, "pa_exchange_connect_ptrs: NULL argument");
+  for (int g = 0; g < x->world; g++) {
+    if (g == x->rank) continue;
+    if (!peer_buffers[g]) return xfail(PA_ERR_INVALID_ARG, "pa_exchange_connect_ptrs: NULL peer buffer");
+    x->peer[g] = static_cast<unsigned char*>(peer_buffers[g]);
+  }
+  x->connected = true;
   return PA_OK;
 }
 

@@ -185,6 +185,22 @@ class Exchange:
         assert len(blob) == self.world * self.HANDLE_BYTES
         check(lib().pa_exchange_connect(self._h, C.create_string_buffer(blob, len(blob))))
 
+    def buffer(self):
+        p, b = C.c_void_p(), C.c_uint64()
+        check(lib().pa_exchange_buffer(self._h, C.byref(p), C.byref(b)))
+        return p.value, b.value
+
+    def connect_ptrs(self, peer_buffers) -> None:
+        """Same-process variant: every rank's receive buffer as a device address."""
+        arr = (C.c_void_p * self.world)(*[C.c_void_p(_ptr(b)) for b in peer_buffers])
+        check(lib().pa_exchange_connect_ptrs(self._h, arr))
+
+    def push(self, pool: "KVPool", layer: int, q, scale: float = 0.125, stream: int = 0) -> None:
+        check(lib().pa_decode_push(pool._h, self._h, layer, _ptr(q), scale, stream))
+
+    def merge(self, pool: "KVPool", out, out_stride: int, stream: int = 0) -> None:
+        check(lib().pa_exchange_merge(pool._h, self._h, _ptr(out), out_stride, stream))
+
     def close(self) -> None:
         if self._h:
             lib().pa_exchange_destroy(self._h)

@@ -1,0 +1,110 @@
+"""GPU tests of the cross-rank partial exchange used by sequence-range sharded
+decode, on ONE GPU: the ranks are pools in this process and every kernel that
+waits on a flag is launched only after the kernels that raise it, so nothing
+waits on a later launch.  Also: a wait that nothing satisfies runs out after
+about a second and comes back as PA_ERR_TIMEOUT with the context intact."""
+import numpy as np
+import pytest
+import torch
+
+from llama_transformer_runtime_b200 import _lib, paged
+from oracle import oracle as orc
+from tests.gpu_helpers import DEV, check_close, f32_dev, fill_cache, to_dev, to_u16
+
+pytestmark = pytest.mark.gpu
+
+
+def make_rank(rng, k, v, lo, hi, extra_tokens):
+    n = hi - lo
+    nb = (n + extra_tokens + 15) // 16 + 4
+    pool = paged.KVPool(1, nb, 8, 1)
+    pool.set_free_order(rng.permutation(nb))
+    s = pool.create_seq()
+    if n:
+        fill_cache(pool, 0, s, k[:, lo:hi], v[:, lo:hi])
+    return pool, s
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_decode_steps_match_whole_sequence(cuda, world):
+    rng = np.random.default_rng(90 + world)
+    L, steps = 700, 3
+    k = orc.randn_bf16(rng, (8, L + steps, 64), 0.5)
+    v = orc.randn_bf16(rng, (8, L + steps, 64), 0.5)
+    cos, sin = orc.build_rope_tables(L + steps)
+    cos_d, sin_d = f32_dev(cos), f32_dev(sin)
+    cuts = [0, 256, 256, L] if world == 3 else [0, 304, L]  # world 3 has an empty middle range
+    ranks = [make_rank(rng, k, v, cuts[r], cuts[r + 1], steps) for r in range(world)]
+    xs = [paged.Exchange(0, r, world, 1, 8) for r in range(world)]
+    bufs = [x.buffer()[0] for x in xs]
+    for x in xs:
+        x.connect_ptrs(bufs)
+    owner = world - 1
+    for step in range(steps):
+        pos = L + step
+        q_new = orc.randn_bf16(rng, (1, 32, 64))
+        k_new = orc.randn_bf16(rng, (1, 8, 64))
+        v_new = orc.randn_bf16(rng, (1, 8, 64))
+        k[:, pos] = orc.rope(k_new, cos, sin, pos, 1)[:, 0]  # the cache row the owner will hold
+        v[:, pos] = v_new[0]
+        q_rots = []
+        for r, (pool, s) in enumerate(ranks):
+            if r == owner:
+                pool.reserve(s, pool.length(s) + 1)
+            pool.batch_set_sharded([s], [1 if r == owner else 0], [1], [pos], [cuts[r]])
+            qd = to_dev(q_new)
+            pool.append(0, qd, to_dev(k_new) if r == owner else None, to_dev(v_new) if r == owner else None,
+                        cos_d, sin_d, qd)
+            q_rots.append(qd)
+        for r, (pool, s) in enumerate(ranks):  # every rank pushes its partial to all ranks ...
+            xs[r].push(pool, 0, q_rots[r])
+        outs = []
+        for r, (pool, s) in enumerate(ranks):  # ... only then does any rank wait and merge
+            o = torch.zeros(1, 2048, dtype=torch.bfloat16, device=DEV)
+            xs[r].merge(pool, o, 2048)
+            outs.append(o)
+        torch.cuda.synchronize()
+        for pool, _ in ranks:
+            pool.check()
+        q_rot = orc.rope(q_new, cos, sin, pos, 1)
+        O, _ = orc.attention(q_rot, k, v, pos + 1)
+        for r in range(world):
+            check_close(orc.bf16_to_f32(to_u16(outs[r]))[0], O[:, 0].reshape(-1), f"step {step} rank {r}")
+            assert torch.equal(outs[r], outs[0])  # every rank merges the same bits
+    for x in xs:
+        x.close()
+    for pool, _ in ranks:
+        pool.close()
+
+
+def test_wait_that_nothing_satisfies_times_out_cleanly(cuda):
+    rng = np.random.default_rng(95)
+    k = orc.randn_bf16(rng, (8, 100, 64), 0.5)
+    v = orc.randn_bf16(rng, (8, 100, 64), 0.5)
+    pool, s = make_rank(rng, k, v, 0, 100, 0)
+    x = paged.Exchange(0, 0, 2, 1, 8)
+    ptr, nbytes = x.buffer()
+    silent_peer = torch.zeros(nbytes, dtype=torch.uint8, device=DEV)  # a rank that never publishes
+    x.connect_ptrs([ptr, silent_peer])
+    q = to_dev(orc.randn_bf16(rng, (1, 32, 64)))
+    out = torch.zeros(1, 2048, dtype=torch.bfloat16, device=DEV)
+    pool.batch_set([s], [0])
+    x.push(pool, 0, q)
+    x.merge(pool, out, 2048)
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    torch.cuda.synchronize()
+    with pytest.raises(_lib.PagedAttentionError) as ei:
+        pool.check()
+    assert ei.value.code == 5
+    # the status word is cleared and the device still works
+    pool.check()
+    want = torch.zeros(1, 2048, dtype=torch.bfloat16, device=DEV)
+    pool.decode(0, q, want, 2048)
+    torch.cuda.synchronize()
+    pool.check()
+    O, _ = orc.attention(to_u16(q)[0][:, None, :], k, v, 100)
+    check_close(orc.bf16_to_f32(to_u16(want))[0], O[:, 0].reshape(-1), "decode after a timed-out wait")
+    x.close()
+    pool.close()
