@@ -25,6 +25,18 @@ SYMBOLS = [
 ]
 
 
+LEGACY_SYMBOLS = ["lt_launch_flash_attention", "lt_launch_rope_qkv", "lt_launch_flash_output_layout"]
+
+
+class FlashAttentionParams(C.Structure):
+    """lt_flash_attention_params of include/legacy_kernels.h."""
+    _fields_ = [("Q", C.c_void_p), ("K", C.c_void_p), ("V", C.c_void_p), ("O", C.c_void_p),
+                ("L", C.c_void_p), ("batch_size", C.c_int), ("num_heads", C.c_int),
+                ("num_kv_heads", C.c_int), ("q_seq_len", C.c_int), ("kv_seq_len", C.c_int),
+                ("kv_stride", C.c_int), ("d_head", C.c_int), ("scale", C.c_float),
+                ("causal", C.c_int), ("dtype", C.c_int), ("stream", C.c_void_p)]
+
+
 class PagedAttentionError(RuntimeError):
     def __init__(self, code: int, msg: str):
         super().__init__(f"[{code}] {msg}")
@@ -76,6 +88,9 @@ def lib():
         "pa_decode_push": [vp, vp, i, vp, f, vp],
         "pa_exchange_merge": [vp, vp, vp, i64, vp],
         "pa_decode_step_sharded": [vp, vp, i, i, vp, vp, vp, i64, i64, vp, vp, vp, vp, i64, i64, f, vp],
+        "lt_launch_flash_attention": [vp],
+        "lt_launch_rope_qkv": [vp, vp, vp, vp, vp, vp, vp, vp, i, i, vp],
+        "lt_launch_flash_output_layout": [vp, vp, i, vp],
         "pa_debug_set_rope_variant": [vp, i],
     }
     for name, args in sigs.items():

@@ -496,14 +496,62 @@ int pa_prefill(pa_pool* p, int layer, const void* q, void* out, float* lse, floa
   a.tables = p->d_tables;
   a.batch = p->d_batch;
   a.status = p->d_status;
-  a.out_stride = (long long)p->kv_heads * pa::kGroup * pa::kHeadDim;
+  const long long row = (long long)p->kv_heads * pa::kGroup * pa::kHeadDim;
+  a.q_seq_stride = a.o_seq_stride = a.lse_seq_stride = 0;
+  a.q_row_stride = a.o_row_stride = row;
+  a.q_head_stride = a.o_head_stride = pa::kHeadDim;
+  a.causal = 1;
   a.scale_log2 = scale * pa::kLog2e;
   a.kv_heads = p->kv_heads;
   a.num_blocks = p->host.num_blocks();
   a.max_blocks_per_seq = p->host.max_blocks_per_seq();
-  PA_CUDA(pa::launch_prefill(a, e.n_q, (cudaStream_t)stream));
+  PA_CUDA(pa::launch_prefill(a, 1, e.n_q, (cudaStream_t)stream));
   return PA_OK;
 }
+
+}  // extern "C"
+
+namespace pa {
+// Prefill of every sequence of the active batch with caller-given tensor
+// strides (used by the legacy launcher, whose Q/O are head-major).
+int prefill_strided(pa_pool* p, int layer, const void* q, void* out, float* lse, long long q_seq_stride,
+                    long long q_row_stride, long long q_head_stride, long long o_seq_stride,
+                    long long o_row_stride, long long o_head_stride, long long lse_seq_stride,
+                    int causal, float scale, void* stream) {
+  if (!p || !q || !out || p->device < 0 || p->batch.empty() || layer < 0 || layer >= p->num_layers)
+    return fail(PA_ERR_INVALID_ARG, "prefill_strided: bad argument");
+  int n_q = 0;
+  for (const auto& e : p->batch) {
+    if (e.n_q < 1 || e.kv_len < 1 || e.q_pos0 < 0) return fail(PA_ERR_INVALID_ARG, "prefill_strided: empty sequence");
+    if (e.n_q > n_q) n_q = e.n_q;
+  }
+  DeviceGuard g(p->device);
+  PrefillParams a;
+  a.q = (const __nv_bfloat16*)q;
+  a.out = (__nv_bfloat16*)out;
+  a.lse = lse;
+  a.storage = p->storage + (size_t)layer * p->layer_bytes;
+  a.tables = p->d_tables;
+  a.batch = p->d_batch;
+  a.status = p->d_status;
+  a.q_seq_stride = q_seq_stride;
+  a.q_row_stride = q_row_stride;
+  a.q_head_stride = q_head_stride;
+  a.o_seq_stride = o_seq_stride;
+  a.o_row_stride = o_row_stride;
+  a.o_head_stride = o_head_stride;
+  a.lse_seq_stride = lse_seq_stride;
+  a.causal = causal;
+  a.scale_log2 = scale * kLog2e;
+  a.kv_heads = p->kv_heads;
+  a.num_blocks = p->host.num_blocks();
+  a.max_blocks_per_seq = p->host.max_blocks_per_seq();
+  PA_CUDA(launch_prefill(a, (int)p->batch.size(), n_q, (cudaStream_t)stream));
+  return PA_OK;
+}
+}  // namespace pa
+
+extern "C" {
 
 int pa_merge_partials(const float* o_parts, const float* lse_parts, int n_parts, int rows, void* out,
                       float* out_f32, float* lse_out, void* stream) {

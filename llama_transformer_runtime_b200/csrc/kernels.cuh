@@ -75,21 +75,27 @@ cudaError_t launch_decode(const DecodeParams& p, int n_seqs, int warps, int stag
 bool decode_shape_supported(int warps, int stages);
 size_t decode_ws_acc_floats_per_item();
 
-// Causal prefill of the batch's single sequence: its n_q query rows (positions
-// q_pos0 ...) against keys [0, kv_len) of the paged cache.
+// Prefill attention: for every batch sequence z, its n_q query rows (positions
+// q_pos0 ...) against keys [0, kv_len) of its paged cache.  Row `row` of head h
+// of sequence z is at q + z*q_seq_stride + (q_row_off+row)*q_row_stride +
+// h*q_head_stride (elements), likewise for out: the token-major layout of the
+// native API and the head-major one of the reference's launcher are both strides.
 struct PrefillParams {
-  const __nv_bfloat16* q;   // [rows][q_heads][64], RoPE applied
-  __nv_bfloat16* out;       // [rows][out_stride], columns h*64+d
-  float* lse;               // [q_heads][n_q] (nullable)
+  const __nv_bfloat16* q;   // RoPE applied
+  __nv_bfloat16* out;
+  float* lse;               // [z][q_heads][n_q] (nullable)
   const char* storage;
   const int32_t* tables;
-  const BatchEntry* batch;  // entry 0 is used
+  const BatchEntry* batch;
   int* status;
-  long long out_stride;
+  long long q_seq_stride, q_row_stride, q_head_stride;
+  long long o_seq_stride, o_row_stride, o_head_stride;
+  long long lse_seq_stride;
   float scale_log2;
-  int kv_heads, num_blocks, max_blocks_per_seq;
+  int kv_heads, num_blocks, max_blocks_per_seq, causal;
 };
-cudaError_t launch_prefill(const PrefillParams& p, int n_q, cudaStream_t stream);
+// n_q: the largest query-row count of any batch sequence
+cudaError_t launch_prefill(const PrefillParams& p, int n_seqs, int n_q, cudaStream_t stream);
 
 struct MergeParams {
   const float* o_parts;    // [n_parts][rows][64]

@@ -207,16 +207,19 @@ prefill_kernel(PrefillParams p) {
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kOffMisc + 4);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const BatchEntry e = p.batch[0];
+  const int z = blockIdx.z;
+  const BatchEntry e = p.batch[z];
   const int n_q_tiles = (e.n_q + kBM - 1) / kBM;
   // CTAs are dispatched in linear order (x fastest): all heads of the heaviest
   // query tile first, the lightest tiles last, so the tail of the grid is short
   const int q_tile = n_q_tiles - 1 - (int)blockIdx.y;
   const int h = blockIdx.x;
+  if (q_tile < 0) return;  // the grid is sized for the sequence with the most query rows
   const int row0 = q_tile * kBM;
   const int rows = min(kBM, e.n_q - row0);
   const int pos0 = e.q_pos0 + row0;                            // position of row 0
-  const int last_pos = min(pos0 + rows - 1, e.kv_len - 1);
+  // causal: a query at position p sees keys 0..p; otherwise every cached key
+  const int last_pos = p.causal ? min(pos0 + rows - 1, e.kv_len - 1) : e.kv_len - 1;
   const int n_tiles = last_pos / kBN + 1;
   const int n_blocks = (e.kv_len + kBlockTok - 1) / kBlockTok;
   const int q_heads = p.kv_heads * kGroup;
@@ -318,7 +321,8 @@ prefill_kernel(PrefillParams p) {
       uint4 v[8];
       if (r < rows) {
         const uint4* src = reinterpret_cast<const uint4*>(
-            p.q + ((size_t)(e.q_row_off + row0 + r) * q_heads + h) * kHeadDim);
+            p.q + (size_t)z * p.q_seq_stride + (size_t)(e.q_row_off + row0 + r) * p.q_row_stride +
+            (size_t)h * p.q_head_stride);
 #pragma unroll
         for (int c = 0; c < 8; c++) v[c] = src[c];
       } else {
@@ -339,8 +343,8 @@ prefill_kernel(PrefillParams p) {
       if (!wait_or_abort(bar_s, (uint32_t)(kt & 1), abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int key0 = kt * kBN;
-      const bool need_mask = (key0 + kBN - 1 > pos0) || (key0 + kBN > e.kv_len);
-      const int limit = min(qpos, e.kv_len - 1) - key0;  // keys with index <= limit are visible
+      const bool need_mask = (p.causal && key0 + kBN - 1 > pos0) || (key0 + kBN > e.kv_len);
+      const int limit = (p.causal ? min(qpos, e.kv_len - 1) : e.kv_len - 1) - key0;  // keys <= limit are visible
 
       // S -> registers in one go (four loads in flight, one wait); the tensor
       // memory copy is then free for the next tile's Q K^T
@@ -444,7 +448,8 @@ prefill_kernel(PrefillParams p) {
     if (ok && wait_or_abort(bar_pv, (uint32_t)((n_tiles - 1) & 1), abort_flag)) {
       tc_fence_after();
       const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-      __nv_bfloat16* orow = p.out + (size_t)(e.q_row_off + row0 + r) * p.out_stride + h * kHeadDim;
+      __nv_bfloat16* orow = p.out + (size_t)z * p.o_seq_stride +
+                            (size_t)(e.q_row_off + row0 + r) * p.o_row_stride + (size_t)h * p.o_head_stride;
 #pragma unroll 1
       for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
         uint32_t oreg[32];
@@ -463,7 +468,7 @@ prefill_kernel(PrefillParams p) {
         }
       }
       if (p.lse && r < rows)
-        p.lse[(size_t)h * e.n_q + row0 + r] = l_sum > 0.f ? kLn2 * (m_used + log2f(l_sum)) : -INFINITY;
+        p.lse[(size_t)z * p.lse_seq_stride + (size_t)h * e.n_q + row0 + r] = l_sum > 0.f ? kLn2 * (m_used + log2f(l_sum)) : -INFINITY;
     }
   }
 
@@ -479,8 +484,8 @@ prefill_kernel(PrefillParams p) {
 
 }  // namespace
 
-cudaError_t launch_prefill(const PrefillParams& p, int n_q, cudaStream_t stream) {
-  if (n_q <= 0) return cudaSuccess;
+cudaError_t launch_prefill(const PrefillParams& p, int n_seqs, int n_q, cudaStream_t stream) {
+  if (n_q <= 0 || n_seqs <= 0) return cudaSuccess;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -490,7 +495,7 @@ cudaError_t launch_prefill(const PrefillParams& p, int n_q, cudaStream_t stream)
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  dim3 grid(p.kv_heads * kGroup, (n_q + kBM - 1) / kBM);
+  dim3 grid(p.kv_heads * kGroup, (n_q + kBM - 1) / kBM, n_seqs);
   prefill_kernel<<<grid, kPrefillThreads, kPrefillSmem, stream>>>(p);
   return cudaGetLastError();
 }

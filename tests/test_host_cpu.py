@@ -26,6 +26,9 @@ def test_library_exports_every_declared_symbol():
     assert len(names) >= 20
     for n in names:
         assert hasattr(L, n), n
+    for n in _declared("legacy_kernels.h"):
+        assert hasattr(L, n), n
+    assert sorted(_declared("legacy_kernels.h")) == sorted(_lib.LEGACY_SYMBOLS)
     assert sorted(set(_lib.SYMBOLS)) == [n for n in names if n in _lib.SYMBOLS]
     assert set(names) <= set(_lib.SYMBOLS) | {"pa_debug_set_rope_variant"}, set(names) - set(_lib.SYMBOLS)
 
@@ -135,3 +138,30 @@ def test_physical_layout_formula():
     assert offs == list(range(0, 2048, 16))
     assert paged.physical_chunk_offset(5, 8, 3, 1, 0, 0) == ((5 * 8 + 3) * 2 + 1) * 2048
     assert paged.physical_chunk_offset(0, 8, 0, 0, 9, 2) == 9 * 128 + ((2 ^ 1) << 4)
+
+
+def test_drop_in_headers_compile(tmp_path):
+    """A translation unit written against the reference's headers (same names,
+    namespace, struct fields) compiles against the shims in include/."""
+    import subprocess
+    src = tmp_path / "caller.cu"
+    src.write_text("""
+#include "flashattention.h"
+#include "rope.hpp"
+#include "layout.hpp"
+int caller(__nv_bfloat16* q, __nv_bfloat16* k, __nv_bfloat16* v, float* c, float* s) {
+  launch_rope_qkv(q, q, k, k, v, v, c, s, 1, 0);
+  transformer::FlashAttentionParams p = {};
+  p.Q = q; p.K = k; p.V = v; p.O = q; p.L = nullptr;
+  p.batch_size = 1; p.num_heads = ROPE_HEADS; p.num_kv_heads = ROPE_KV_HEADS;
+  p.q_seq_len = 1; p.kv_seq_len = 1; p.kv_stride = 1; p.d_head = ROPE_HEAD_DIM;
+  p.scale = 0.125f; p.causal = true; p.dtype = transformer::DType::BF16; p.stream = 0;
+  transformer::launch_flash_attention(p);
+  launch_flash_output_layout(q, q, 1);
+  return 0;
+}
+""")
+    r = subprocess.run(["nvcc", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I",
+                        os.path.join(ROOT, "include"), "-c", str(src), "-o", str(tmp_path / "caller.o")],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
