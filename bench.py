@@ -492,6 +492,202 @@ def run_reference(args):
 
 
 # =============================================================================
+# batched decode workload (config 5): 64 ragged sequences, shared fragmented pool
+# =============================================================================
+def run_batch(args):
+    """64 sequences with context lengths seeded-uniform in [1024, 32768], one
+    shared free-block pool; before timing, rounds of freeing and re-creating
+    sequences interleave their tables.  One step = every sequence appends one
+    token and attends over its cache, 16 layers.  With N GPUs the 8 KV heads are
+    sharded (8/N per GPU, each with the 4*8/N query heads of its groups); every
+    layer ends with an all-gather of the head outputs into [64, 2048] on every
+    rank.  Strong scaling: the same batch is split N ways."""
+    import torch
+    import torch.distributed as dist
+
+    from llama_transformer_runtime_b200 import paged
+
+    rank, local_rank, world = dist_env()
+    torch.cuda.set_device(local_rank)
+    dev = f"cuda:{local_rank}"
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable":
+                              "the reference is single-sequence and contiguous; this workload has no reference arm "
+                              "(see the decode128k and prefill2k workloads)"}))
+        return
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    n_seqs = args.seqs
+    kvh = KV_HEADS // world
+    qh = 4 * kvh
+    rng = np.random.default_rng(2024)  # the same allocator decisions on every rank
+    lens = rng.integers(1024, 32769, n_seqs).astype(int)
+    total_steps = args.warmup + 2 * args.steps + 8
+    cap = int(lens.max()) + total_steps + 64
+    blocks_needed = int(sum((l + total_steps + 15) // 16 for l in lens))
+    num_blocks = blocks_needed + blocks_needed // 8 + 64
+    pool = paged.KVPool(LAYERS, num_blocks, kvh, n_seqs, (cap + 15) // 16, device=local_rank)
+    pool.set_free_order(rng.permutation(num_blocks))
+
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(777 + rank)
+    max_len = int(lens.max())
+    ones = torch.ones(max_len + 1, 32, dtype=torch.float32, device=dev)
+    zeros = torch.zeros(max_len + 1, 32, dtype=torch.float32, device=dev)
+
+    def fill(seq, L):
+        for c0 in range(0, L, 8192):
+            n = min(8192, L - c0)
+            pool.reserve(seq, c0 + n)
+            pool.batch_set([seq], [n])
+            for layer in range(LAYERS):
+                kv = (torch.randn(2, n, kvh, D, generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+                pool.append(layer, None, kv[0], kv[1], ones, zeros, None)
+
+    # sequences created in a seeded order, then a third of them freed and re-created
+    # twice, so that tables interleave across the pool (fragmentation)
+    seqs = {}
+    for i in range(n_seqs):
+        s = pool.create_seq()
+        fill(s, int(lens[i]))
+        seqs[s] = int(lens[i])
+    for rnd in range(2):
+        victims = rng.choice(sorted(seqs), n_seqs // 3, replace=False)
+        new_lens = rng.integers(1024, 32769, len(victims)).astype(int)
+        for s in victims:
+            pool.free_seq(int(s))
+            del seqs[int(s)]
+        for L in new_lens:
+            if (int(L) + total_steps + 15) // 16 + 8 > pool.free_blocks():
+                L = 1024
+            s = pool.create_seq()
+            fill(s, int(L))
+            seqs[s] = int(L)
+    torch.cuda.synchronize()
+    del ones, zeros
+    ids = sorted(seqs)
+    cos_h, sin_h = paged.build_rope_tables(max(seqs.values()) + total_steps + 2)
+    cos, sin = torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev)
+
+    g7 = torch.Generator().manual_seed(7)
+    q_host = torch.randn(LAYERS, n_seqs, qh, D, generator=g7).to(torch.bfloat16).pin_memory()
+    k_host = torch.randn(LAYERS, n_seqs, kvh, D, generator=g7).to(torch.bfloat16).pin_memory()
+    v_host = torch.randn(LAYERS, n_seqs, kvh, D, generator=g7).to(torch.bfloat16).pin_memory()
+    q_dev, k_dev, v_dev = q_host.to(dev), k_host.to(dev), v_host.to(dev)
+    q_rot = torch.empty_like(q_dev)
+    # [layers][seqs][2048] on every rank; a rank's decode writes its own column slice
+    out_full = torch.zeros(LAYERS, n_seqs, Q_HEADS * D, dtype=torch.bfloat16, device=dev)
+    out_local = torch.zeros(LAYERS, n_seqs, qh * D, dtype=torch.bfloat16, device=dev)
+    gath = torch.zeros(LAYERS, world, n_seqs, qh * D, dtype=torch.bfloat16, device=dev)
+    out_host = torch.zeros(LAYERS, n_seqs, Q_HEADS * D, dtype=torch.bfloat16).pin_memory()
+    state = {"launches": 0, "bytes": 0}
+
+    def step():
+        for s in ids:
+            seqs[s] += 1
+            pool.reserve(s, seqs[s])
+        pool.batch_set(ids)
+        state["bytes"] += LAYERS * sum(decode_bytes(seqs[s]) for s in ids)
+        if world == 1:
+            pool.decode_step(0, LAYERS, q_dev, k_dev, v_dev, n_seqs * qh * D, n_seqs * kvh * D, cos, sin, q_rot,
+                             out_full, Q_HEADS * D, n_seqs * Q_HEADS * D)
+            state["launches"] += 2 * LAYERS
+            return
+        for layer in range(LAYERS):
+            pool.append(layer, q_dev[layer], k_dev[layer], v_dev[layer], cos, sin, q_rot[layer])
+            pool.decode(layer, q_rot[layer], out_local[layer], qh * D)
+            dist.all_gather_into_tensor(gath[layer].view(-1), out_local[layer].view(-1))
+            out_full[layer].view(n_seqs, world, qh * D).copy_(gath[layer].permute(1, 0, 2))
+            state["launches"] += 2
+
+    def e2e_step():
+        q_dev.copy_(q_host, non_blocking=True)
+        k_dev.copy_(k_host, non_blocking=True)
+        v_dev.copy_(v_host, non_blocking=True)
+        step()
+        out_host.copy_(out_full, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        state["bytes"] = 0
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, state["bytes"]
+
+    m0 = sampler.mark()
+    for _ in range(args.warmup):
+        step()
+    state["launches"] = 0
+    ms, nbytes = timed(step, args.steps)
+    launches = state["launches"]
+    ms_e2e, nbytes_e2e = timed(e2e_step, args.steps)
+
+    # dominant kernel alone (this rank's heads), one launch per layer
+    pool.batch_set(ids, [0] * n_seqs)
+
+    def decode_only():
+        for layer in range(LAYERS):
+            pool.decode(layer, q_rot[layer], out_local[layer], qh * D)
+
+    decode_only()
+    reps = max(3, args.steps // 2)
+    ms_k, _ = timed(decode_only, reps)
+    ms_k /= reps * LAYERS
+    kern_bytes = sum(decode_bytes(seqs[s]) for s in ids) // world
+    achieved = kern_bytes / (ms_k * 1e-3) / 1e9
+    peak, peak_kind = measured_peak()
+    pool.check()
+    m1 = sampler.mark()
+    if rank == 0:
+        line = {
+            "metric": "paged_decode_attn_hbm_gbs", "value": round(nbytes / (ms * 1e-3) / 1e9, 1), "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4),
+            "us_per_token": round(ms / args.steps * 1e3 / n_seqs, 2),
+            "us_per_step_per_layer": round(ms / args.steps * 1e3 / LAYERS, 2),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"decode_batch{n_seqs}_ctxU1024-32768_x{LAYERS}layers", "sequences": n_seqs,
+                       "tokens_in_cache": int(sum(seqs.values())), "layers": LAYERS, "block_tokens": BLOCK,
+                       "block_table": "shared pool, seeded free order, a third of the sequences freed and "
+                                      "re-created twice before timing",
+                       "parallelism": "1 GPU" if world == 1 else
+                                      f"{kvh} KV head(s) per GPU over {world} GPUs, NCCL all-gather of head outputs per layer",
+                       "l2": "inputs larger than L2"},
+            "e2e": {"value": round(nbytes_e2e / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
+                    "h2d_bytes_per_step": (q_host.numel() + k_host.numel() + v_host.numel()) * 2,
+                    "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": round(ms_e2e / args.steps, 4)},
+            "gpu_launches": launches, "clocks": sampler.stop(m0, m1),
+            "roofline": {"bound": "hbm", "kernel": "decode_kernel", "achieved": round(achieved, 1), "peak": peak,
+                         "unit": "GB/s", "frac": round(achieved / peak, 4), "peak_source": f"of {peak_kind}",
+                         "us_per_launch": round(ms_k * 1e3, 2), "bytes_per_launch": kern_bytes, "traffic": None},
+        }
+        print(json.dumps(line), flush=True)
+    barrier()
+    pool.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# =============================================================================
 # prefill workload (config 3): 2048 tokens x 16 layers, causal, batch 1
 # =============================================================================
 PREFILL_TOKENS = 2048
@@ -691,7 +887,8 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode128k", choices=sorted(WORKLOADS) + ["prefill2k"])
+    ap.add_argument("--workload", default="decode128k", choices=sorted(WORKLOADS) + ["prefill2k", "batch64"])
+    ap.add_argument("--seqs", type=int, default=64, help="batch64: number of sequences")
     ap.add_argument("--layers", type=int, default=16, help="fewer layers make a small case for profiling")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="N>1: partials pushed by the decode epilogue over NVLink (fused) or NCCL all-gather")
@@ -705,6 +902,8 @@ def main():
     LAYERS = args.layers
     if args.workload == "prefill2k":
         run_prefill(args)
+    elif args.workload == "batch64":
+        run_batch(args)
     elif args.impl == "reference":
         run_reference(args)
     else:
