@@ -68,7 +68,7 @@ def one_case(name, seed, position, tokens, max_seq, out_dir):
     print(name, "reference rope equals oracle y0 variants", variants)
     np.savez_compressed(
         os.path.join(out_dir, name + ".npz"), position=position, tokens=tokens, max_seq=max_seq,
-        y0_variant=variants[0] if variants else -1, y0_variants=np.array(variants, np.int32),
+        y0_variant=(1 if 1 in variants else (variants[0] if variants else -1)), y0_variants=np.array(variants, np.int32),
         cos=cos, sin=sin, q_in=q, k_in=k, v_in=v, q_flash=host(qf), k_flash=host(kf),
         v_flash=host(vf), k_cache_before=kc0, v_cache_before=vc0, k_cache_after=host(kc),
         v_cache_after=host(vc), o_flash=host(of), lse=lse.cpu().numpy(), o_layout=host(ol))
@@ -80,4 +80,4 @@ if __name__ == "__main__":
     one_case("prefill_37_at_0", 101, 0, 37, 48, out_dir)
     one_case("decode_1_at_100", 102, 100, 1, 112, out_dir)
     one_case("chunked_prefill_20_at_45", 103, 45, 20, 80, out_dir)
-    one_case("prefill_70_at_0", 104, 0, 70, 70, out_dir)
+    one_case("prefill_66_at_0", 104, 0, 66, 66, out_dir)
