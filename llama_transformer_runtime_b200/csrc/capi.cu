@@ -342,8 +342,29 @@ static DecodePlan pick_plan(const pa_pool* p) {
 
 // x != nullptr: sequence-range sharded decode.  with_merge == false only pushes
 // the partials; the merge of that step is then launched by pa_exchange_merge.
+// Inputs of the fused append (pa_decode_step): q is then the un-rotated query.
+struct FusedAppend {
+  const void* k_new;
+  const void* v_new;
+  const float* cos_table;
+  const float* sin_table;
+  void* q_rot_out;
+};
+
+// The append can ride inside the decode kernel when every sequence brings one
+// query row (row i = batch entry i) and at most one new token.
+static bool can_fuse_append(const pa_pool* p) {
+  int i = 0;
+  for (const auto& e : p->batch) {
+    if (e.n_q != 1 || e.q_row_off != i || e.n_new > 1) return false;
+    i++;
+  }
+  return true;
+}
+
 static int decode_impl(pa_pool* p, int layer, const void* q, void* out, int64_t out_stride, float* out_f32,
-                       float* lse, float scale, void* stream, pa_exchange* x, bool with_merge = true) {
+                       float* lse, float scale, void* stream, pa_exchange* x, bool with_merge = true,
+                       const FusedAppend* fz = nullptr) {
   if (!p || !q) return fail(PA_ERR_INVALID_ARG, "pa_decode: NULL argument");
   if (!out && !out_f32 && !(x && !with_merge)) return fail(PA_ERR_INVALID_ARG, "pa_decode: no output buffer");
   if (p->device < 0) return fail(PA_ERR_STATE, "pa_decode: host-only pool");
@@ -382,6 +403,15 @@ static int decode_impl(pa_pool* p, int layer, const void* q, void* out, int64_t 
   d.max_blocks_per_seq = p->host.max_blocks_per_seq();
   d.chunk_blocks = cb;
   d.max_chunks = max_chunks;
+  if (fz) {
+    d.fuse = 1;
+    d.k_new = (const __nv_bfloat16*)fz->k_new;
+    d.v_new = (const __nv_bfloat16*)fz->v_new;
+    d.cos_table = fz->cos_table;
+    d.sin_table = fz->sin_table;
+    d.storage_w = p->storage + (size_t)layer * p->layer_bytes;
+    d.q_rot_out = fz->q_rot_out == q ? nullptr : (__nv_bfloat16*)fz->q_rot_out;
+  }
   if (!x) {
     PA_CUDA(pa::launch_decode(d, n_seqs, plan.warps, plan.stages, (cudaStream_t)stream));
     return PA_OK;
@@ -399,8 +429,13 @@ static int decode_impl(pa_pool* p, int layer, const void* q, void* out, int64_t 
   m.out_stride = out_stride;
   m.status = p->d_status;
   m.q_heads = p->kv_heads * pa::kGroup;
+  if (with_merge) {
+    // the combining CTA of each (sequence, KV head) waits for the other ranks
+    // and merges its rows itself: no second launch
+    d.xchg_out = (__nv_bfloat16*)out;
+    d.xchg_out_stride = out_stride;
+  }
   PA_CUDA(pa::launch_decode(d, n_seqs, plan.warps, plan.stages, (cudaStream_t)stream));
-  if (with_merge) PA_CUDA(pa::launch_exchange_merge(m, (cudaStream_t)stream));
   return PA_OK;
 }
 
@@ -438,6 +473,10 @@ int pa_decode_step_sharded(pa_pool* p, pa_exchange* x, int layer_begin, int laye
   if (!p || !x || !q_in || !q_rot || !out) return fail(PA_ERR_INVALID_ARG, "pa_decode_step_sharded: NULL argument");
   if (layer_begin < 0 || layer_end > p->num_layers || layer_begin > layer_end)
     return fail(PA_ERR_INVALID_ARG, "pa_decode_step_sharded: layers [%d, %d) out of range", layer_begin, layer_end);
+  // fused when the batch allows it; k_in/v_in may only be missing if nothing is appended
+  bool fuse = cos_table && sin_table && can_fuse_append(p);
+  for (const auto& e : p->batch)
+    if (e.n_new > 0 && (!k_in || !v_in)) return fail(PA_ERR_INVALID_ARG, "decode step: the batch appends tokens but k_in/v_in is NULL");
   for (int l = layer_begin; l < layer_end; l++) {
     const int i = l - layer_begin;
     const __nv_bfloat16* qi = (const __nv_bfloat16*)q_in + (size_t)i * q_layer_stride;
@@ -445,9 +484,15 @@ int pa_decode_step_sharded(pa_pool* p, pa_exchange* x, int layer_begin, int laye
     const __nv_bfloat16* vi = v_in ? (const __nv_bfloat16*)v_in + (size_t)i * kv_layer_stride : nullptr;
     __nv_bfloat16* qr = (__nv_bfloat16*)q_rot + (size_t)i * q_layer_stride;
     __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)i * out_layer_stride;
-    int r = pa_append(p, l, qi, ki, vi, cos_table, sin_table, qr, stream);
-    if (r != PA_OK) return r;
-    r = decode_impl(p, l, qr, o, out_stride, nullptr, nullptr, scale, stream, x);
+    int r;
+    if (fuse) {
+      // one kernel per layer: RoPE(Q), RoPE(K) + append, decode, exchange, merge
+      const FusedAppend fz{ki, vi, cos_table, sin_table, qr};
+      r = decode_impl(p, l, qi, o, out_stride, nullptr, nullptr, scale, stream, x, true, &fz);
+    } else {
+      r = pa_append(p, l, qi, ki, vi, cos_table, sin_table, qr, stream);
+      if (r == PA_OK) r = decode_impl(p, l, qr, o, out_stride, nullptr, nullptr, scale, stream, x);
+    }
     if (r != PA_OK) return r;
   }
   return PA_OK;
@@ -463,6 +508,10 @@ int pa_decode_step(pa_pool* p, int layer_begin, int layer_end, const void* q_in,
     return fail(PA_ERR_INVALID_ARG, "pa_decode_step: layers [%d, %d) out of range", layer_begin, layer_end);
   const int n_seqs = (int)p->batch.size();
   const int q_heads = p->kv_heads * pa::kGroup;
+  // fused when the batch allows it; k_in/v_in may only be missing if nothing is appended
+  bool fuse = cos_table && sin_table && can_fuse_append(p);
+  for (const auto& e : p->batch)
+    if (e.n_new > 0 && (!k_in || !v_in)) return fail(PA_ERR_INVALID_ARG, "decode step: the batch appends tokens but k_in/v_in is NULL");
   for (int l = layer_begin; l < layer_end; l++) {
     const int i = l - layer_begin;
     const __nv_bfloat16* qi = (const __nv_bfloat16*)q_in + (size_t)i * q_layer_stride;
@@ -470,10 +519,15 @@ int pa_decode_step(pa_pool* p, int layer_begin, int layer_end, const void* q_in,
     const __nv_bfloat16* vi = v_in ? (const __nv_bfloat16*)v_in + (size_t)i * kv_layer_stride : nullptr;
     __nv_bfloat16* qr = (__nv_bfloat16*)q_rot + (size_t)i * q_layer_stride;
     __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)i * out_layer_stride;
-    int r = pa_append(p, l, qi, ki, vi, cos_table, sin_table, qr, stream);
-    if (r != PA_OK) return r;
-    r = pa_decode(p, l, qr, o, out_stride, nullptr, lse ? lse + (size_t)i * n_seqs * q_heads : nullptr,
-                  scale, stream);
+    float* lse_l = lse ? lse + (size_t)i * n_seqs * q_heads : nullptr;
+    int r;
+    if (fuse) {
+      const FusedAppend fz{ki, vi, cos_table, sin_table, qr};
+      r = decode_impl(p, l, qi, o, out_stride, nullptr, lse_l, scale, stream, nullptr, true, &fz);
+    } else {
+      r = pa_append(p, l, qi, ki, vi, cos_table, sin_table, qr, stream);
+      if (r == PA_OK) r = pa_decode(p, l, qr, o, out_stride, nullptr, lse_l, scale, stream);
+    }
     if (r != PA_OK) return r;
   }
   return PA_OK;

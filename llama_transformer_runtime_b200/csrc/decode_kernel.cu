@@ -24,6 +24,7 @@
 //     last CTA to arrive for a (sequence, KV head) does the combine and writes
 //     the [tokens, 2048]-layout row directly.
 #include "kernels.cuh"
+#include "rope.cuh"
 
 namespace pa {
 
@@ -74,6 +75,57 @@ __device__ __forceinline__ void publish_exchange(const DecodeParams& p, int z, i
   }
 }
 
+// In-kernel merge of a sharded decode: the CTA that has just published this
+// rank's partial of (sequence z, KV head h) waits — bounded — until every
+// rank's partial of that group has landed in THIS rank's buffer, merges the
+// group's 4 rows from local memory and writes them as bf16.
+__device__ __forceinline__ void exchange_wait_merge(const DecodeParams& p, int z, int h, int* s_flag) {
+  if (p.xchg_world <= 0 || !p.xchg_out) return;
+  if (threadIdx.x == 0) *s_flag = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < p.xchg_world) {
+    const unsigned int* flag =
+        p.xchg_flag[p.xchg_rank] + ((size_t)threadIdx.x * p.xchg_groups + z * p.kv_heads + h);
+    const uint64_t t0 = global_ns();
+    unsigned int spins = 0;
+    for (;;) {
+      unsigned int v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      if ((int)(v - p.xchg_seq) >= 0) break;
+      if ((++spins & 255u) == 0 && global_ns() - t0 > kWaitLimitNs) {
+        *s_flag = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (!*s_flag) {
+    if (threadIdx.x == 0) atomicExch(p.status, kStatusTimeout);
+    return;
+  }
+  const int q_heads = p.kv_heads * kGroup;
+  const float* base = p.xchg_peer[p.xchg_rank] + (size_t)p.xchg_slot * p.xchg_world * p.xchg_rows * kXchgRowFloats;
+  for (int idx = threadIdx.x; idx < kGroup * kHeadDim; idx += blockDim.x) {
+    const int r = idx >> 6, d = idx & 63;
+    const int head = h * kGroup + r;
+    const int row = z * q_heads + head;
+    float M = -INFINITY;
+    for (int g = 0; g < p.xchg_world; g++)
+      M = fmaxf(M, __ldcg(base + ((size_t)g * p.xchg_rows + row) * kXchgRowFloats + kHeadDim));
+    float L = 0.f, O = 0.f;
+    if (M > -INFINITY) {
+      for (int g = 0; g < p.xchg_world; g++) {
+        const float* rowp = base + ((size_t)g * p.xchg_rows + row) * kXchgRowFloats;
+        const float lse = __ldcg(rowp + kHeadDim);
+        const float w = lse == -INFINITY ? 0.f : __expf(lse - M);
+        L += w;
+        O += w * __ldcg(rowp + d);
+      }
+    }
+    p.xchg_out[(size_t)z * p.xchg_out_stride + head * kHeadDim + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+  }
+}
+
 template <int WARPS, int STAGES>
 __global__ void __launch_bounds__(WARPS * 32)
 decode_kernel(DecodeParams p) {
@@ -88,6 +140,7 @@ decode_kernel(DecodeParams p) {
   float* mrg_m = mrg + WARPS * kGroup * kHeadDim;     // [WARPS][4]
   float* mrg_l = mrg_m + WARPS * kGroup;              // [WARPS][4]
   __shared__ unsigned int s_ticket;
+  __shared__ int s_wait_ok;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int x = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
@@ -136,6 +189,41 @@ decode_kernel(DecodeParams p) {
     }
   };
 
+  // Fused append (pa_decode_step): the warp that owns the sequence's last block
+  // first writes the new token's K (RoPE applied) and V rows of this head into
+  // that block — the same arithmetic and placement as append_kernel — and
+  // orders those generic-proxy stores before its own bulk (async-proxy) reads.
+  if (p.fuse && e.n_new > 0 && x == n_chunks - 1 && cnt > 0 && warp == (cnt - 1) % WARPS) {
+    if (lane < 8) {
+      const int lpos = e.kv_len - 1;
+      const int pos = e.kv_pos_off + lpos;
+      const int blk = p.tables[(size_t)e.seq * p.max_blocks_per_seq + lpos / kBlockTok];
+      const int slot = lpos % kBlockTok;
+      const int c = lane & 3, is_v = lane >> 2;
+      if (blk < 0 || blk >= p.num_blocks) {
+        atomicExch(p.status, kStatusBadBlock);
+      } else {
+        const __nv_bfloat16* row = (is_v ? p.v_new : p.k_new) + ((size_t)e.kv_row_off * p.kv_heads + h) * kHeadDim;
+        const uint4* src = reinterpret_cast<const uint4*>(row);
+        char* tile = p.storage_w + tile_off(blk, p.kv_heads, h, is_v);
+        uint4 lo = src[c], hi = src[c + 4];
+        if (!is_v) {
+          const float4* cs = reinterpret_cast<const float4*>(p.cos_table + (size_t)pos * 32 + c * 8);
+          const float4* sn = reinterpret_cast<const float4*>(p.sin_table + (size_t)pos * 32 + c * 8);
+          float4 c8[2] = {cs[0], cs[1]}, s8[2] = {sn[0], sn[1]};
+          uint4 ylo, yhi;
+          rope_chunks<1>(lo, hi, reinterpret_cast<const float*>(c8), reinterpret_cast<const float*>(s8), ylo, yhi);
+          lo = ylo;
+          hi = yhi;
+        }
+        *reinterpret_cast<uint4*>(tile + tile_chunk_off(slot, c)) = lo;
+        *reinterpret_cast<uint4*>(tile + tile_chunk_off(slot, c + 4)) = hi;
+      }
+    }
+    asm volatile("fence.proxy.async;" ::: "memory");
+    __syncwarp();
+  }
+
   for (int i = 0; i < STAGES && i < my_n; i++) issue(i);
 
   // Query fragments: rows 0..3 are the group's heads, the rest zero.
@@ -149,6 +237,33 @@ decode_kernel(DecodeParams p) {
           p.q + ((size_t)z * q_heads + h * kGroup + qrow) * kHeadDim + ks * 16 + qcol;
       qa[ks][0] = *reinterpret_cast<const uint32_t*>(qp);
       qa[ks][2] = *reinterpret_cast<const uint32_t*>(qp + 8);
+    }
+  }
+  if (p.fuse && qrow < kGroup) {
+    // p.q is the un-rotated query: RoPE pairs element c with c+32, i.e. this
+    // thread's values of k-step ks with those of k-step ks+2
+    const float* cs = p.cos_table + (size_t)e.q_pos0 * 32;
+    const float* sn = p.sin_table + (size_t)e.q_pos0 * 32;
+#pragma unroll
+    for (int ks = 0; ks < 2; ks++)
+#pragma unroll
+      for (int half = 0; half < 2; half++) {
+        const int c0 = ks * 16 + qcol + half * 8;
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&qa[ks][half * 2]);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&qa[ks + 2][half * 2]);
+        float y0a, y1a, y0b, y1b;
+        rope_pair<1>(__low2float(a), __low2float(b), cs[c0], sn[c0], y0a, y1a);
+        rope_pair<1>(__high2float(a), __high2float(b), cs[c0 + 1], sn[c0 + 1], y0b, y1b);
+        qa[ks][half * 2] = pack_bf16(y0a, y0b);
+        qa[ks + 2][half * 2] = pack_bf16(y1a, y1b);
+      }
+    if (p.q_rot_out && x == 0 && warp == 0) {
+      __nv_bfloat16* qo = p.q_rot_out + ((size_t)z * q_heads + h * kGroup + qrow) * kHeadDim + qcol;
+#pragma unroll
+      for (int ks = 0; ks < 4; ks++) {
+        *reinterpret_cast<uint32_t*>(qo + ks * 16) = qa[ks][0];
+        *reinterpret_cast<uint32_t*>(qo + ks * 16 + 8) = qa[ks][2];
+      }
     }
   }
 
@@ -271,6 +386,7 @@ decode_kernel(DecodeParams p) {
   }
   if (n_chunks == 1) {
     publish_exchange(p, z, h);
+  exchange_wait_merge(p, z, h, &s_wait_ok);
     return;
   }
 
@@ -356,6 +472,7 @@ decode_kernel(DecodeParams p) {
   }
   if (threadIdx.x == 0) p.ws_count[z * p.kv_heads + h] = 0u;
   publish_exchange(p, z, h);
+  exchange_wait_merge(p, z, h, &s_wait_ok);
 }
 
 template <int WARPS, int STAGES>

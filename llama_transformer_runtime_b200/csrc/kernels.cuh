@@ -55,6 +55,20 @@ struct DecodeParams {
   unsigned int* xchg_flag[8] = {};
   int xchg_world = 0, xchg_rank = 0, xchg_rows = 0, xchg_groups = 0, xchg_slot = 0;
   unsigned int xchg_seq = 0;
+  // merged bf16 rows written by the combining CTA itself after it has waited
+  // for all ranks' partials of its (sequence, KV head); nullptr: a separate
+  // merge kernel does it
+  __nv_bfloat16* xchg_out = nullptr;
+  long long xchg_out_stride = 0;
+  // Fused append (one new token per sequence at most): q is un-rotated, the
+  // kernel rotates it and appends k_new/v_new rows (RoPE on K) to the cache.
+  int fuse = 0;
+  const __nv_bfloat16* k_new = nullptr;  // [rows][kv_heads][64], row e.kv_row_off
+  const __nv_bfloat16* v_new = nullptr;
+  const float* cos_table = nullptr;
+  const float* sin_table = nullptr;
+  char* storage_w = nullptr;             // == storage, writable
+  __nv_bfloat16* q_rot_out = nullptr;    // rotated Q [n_seqs][q_heads][64] (nullable, must not alias q)
 };
 constexpr int kXchgRowFloats = kHeadDim + 1;
 

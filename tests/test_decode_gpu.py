@@ -229,3 +229,59 @@ def test_decode_vs_reference_kernel(cuda, L):
     oracle_o, _ = oracle_decode(q[0], k, v, L)
     check_close(want, oracle_o, "reference kernel vs oracle")
     pool.close()
+
+
+@pytest.mark.parametrize("chunk_blocks", [0, 2, 5])
+def test_fused_step_equals_append_then_decode(cuda, chunk_blocks):
+    """pa_decode_step runs RoPE(Q), RoPE(K) + append and the decode in ONE kernel
+    per layer; cache contents, rotated Q and outputs must equal the two-kernel
+    path bit for bit (same arithmetic, same placement)."""
+    from tests.gpu_helpers import read_logical_pool
+    rng = np.random.default_rng(70 + chunk_blocks)
+    lens = [47, 16, 130, 1, 255]  # new tokens land mid-block, at slot 0 of a fresh block, ...
+    layers = 2
+    cos, sin = orc.build_rope_tables(300)
+    cos_d, sin_d = f32_dev(cos), f32_dev(sin)
+    n = len(lens)
+    q = to_dev(orc.randn_bf16(rng, (layers, n, 32, 64)))
+    k = to_dev(orc.randn_bf16(rng, (layers, n, 8, 64)))
+    v = to_dev(orc.randn_bf16(rng, (layers, n, 8, 64)))
+    results = []
+    for fused in (True, False):
+        prng = np.random.default_rng(71)
+        pool = paged.KVPool(layers, 64, 8, n, 20)
+        pool.set_free_order(prng.permutation(64))
+        pool.set_decode_chunk_blocks(chunk_blocks)
+        seqs = []
+        for L in lens:
+            s = pool.create_seq()
+            for layer in range(layers):
+                kk = orc.randn_bf16(prng, (8, L, 64), 0.5)
+                vv = orc.randn_bf16(prng, (8, L, 64), 0.5)
+                if layer == 0:
+                    fill_cache(pool, 0, s, kk, vv)
+                else:  # the same positions of the other layer
+                    pool.batch_set([s], [L])
+                    pool.append(layer, None, to_dev(kk.transpose(1, 0, 2)), to_dev(vv.transpose(1, 0, 2)),
+                                torch.ones(L, 32, device=DEV), torch.zeros(L, 32, device=DEV), None)
+            seqs.append(s)
+        for s, L in zip(seqs, lens):
+            pool.reserve(s, L + 1)
+        pool.batch_set(seqs)
+        out = torch.zeros(layers, n, 2048, dtype=torch.bfloat16, device=DEV)
+        q_rot = torch.zeros_like(q)
+        if fused:
+            pool.decode_step(0, layers, q, k, v, n * 2048, n * 512, cos_d, sin_d, q_rot, out, 2048, n * 2048)
+        else:
+            for layer in range(layers):
+                pool.append(layer, q[layer], k[layer], v[layer], cos_d, sin_d, q_rot[layer])
+                pool.decode(layer, q_rot[layer], out[layer], 2048)
+        torch.cuda.synchronize()
+        pool.check()
+        results.append((to_u16(out), to_u16(q_rot), [read_logical_pool(pool, l) for l in range(layers)]))
+        pool.close()
+    (of, qf, cf), (o2, q2, c2) = results
+    assert np.array_equal(qf, q2)
+    for l in range(layers):
+        assert np.array_equal(cf[l], c2[l])
+    assert np.array_equal(of, o2)
