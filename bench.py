@@ -210,7 +210,7 @@ def run_ours(args):
             pool.batch_set([seq])
             pool.decode_step(0, LAYERS, qs, ks, vs, Q_HEADS * D, KV_HEADS * D, cos, sin, q_rot, outs,
                              Q_HEADS * D, Q_HEADS * D)
-            state["launches"] += 2 * LAYERS
+            state["launches"] += LAYERS  # one fused kernel per layer
             return
         pool.batch_set_sharded([seq], [1 if rank == owner else 0], [1], [g - 1], [lo])
         if xchg is not None:
@@ -218,7 +218,7 @@ def run_ours(args):
             paged.decode_step_sharded(pool, xchg, 0, LAYERS, qs, ks if rank == owner else None,
                                       vs if rank == owner else None, Q_HEADS * D, KV_HEADS * D, cos, sin,
                                       q_rot, outs, Q_HEADS * D, Q_HEADS * D)
-            state["launches"] += 3 * LAYERS
+            state["launches"] += LAYERS  # one fused kernel per layer
             return
         for layer in range(LAYERS):
             pool.append(layer, qs[layer], ks[layer], vs[layer], cos, sin, q_rot[layer])
@@ -290,7 +290,19 @@ def run_ours(args):
 
     decode_only()
     reps = max(3, args.steps)
-    ms_k = timed(decode_only, reps) / (reps * LAYERS)
+    ms_iso = timed(decode_only, reps) / (reps * LAYERS)  # plain launches, nothing overlapped
+    ms_k = ms_iso
+    if world == 1:
+        # the step's own launches (one decode_kernel per layer with the append fused in and
+        # programmatic dependent launch between layers), without the host's table work
+        pool.batch_set([seq])
+
+        def step_kernels():
+            pool.decode_step(0, LAYERS, q_dev, k_dev, v_dev, Q_HEADS * D, KV_HEADS * D, cos, sin, q_rot,
+                             out_dev, Q_HEADS * D, Q_HEADS * D)
+
+        step_kernels()
+        ms_k = timed(step_kernels, reps) / (reps * LAYERS)
     kern_bytes = decode_bytes(L_local)
     achieved = kern_bytes / (ms_k * 1e-3) / 1e9
     peak, peak_kind = measured_peak()
@@ -336,6 +348,10 @@ def run_ours(args):
                          "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
                          "peak_source": f"of {peak_kind}", "frac_of_nominal_8000": round(achieved / 8000.0, 4),
                          "us_per_launch": round(ms_k * 1e3, 2), "bytes_per_launch": kern_bytes,
+                         "us_per_launch_isolated": round(ms_iso * 1e3, 2),
+                         "how": "CUDA events around the step's 16 decode_kernel launches (append fused in, "
+                                "programmatic dependent launch between layers), / 16" if world == 1 else
+                                "CUDA events around 16 plain decode_kernel launches on this rank's range, / 16",
                          "traffic": NCU_TRAFFIC_BYTES.get(args.workload)},
         }
         if world == 1:
@@ -595,7 +611,7 @@ def run_batch(args):
         if world == 1:
             pool.decode_step(0, LAYERS, q_dev, k_dev, v_dev, n_seqs * qh * D, n_seqs * kvh * D, cos, sin, q_rot,
                              out_full, Q_HEADS * D, n_seqs * Q_HEADS * D)
-            state["launches"] += 2 * LAYERS
+            state["launches"] += LAYERS  # one fused kernel per layer
             return
         for layer in range(LAYERS):
             pool.append(layer, q_dev[layer], k_dev[layer], v_dev[layer], cos, sin, q_rot[layer])

@@ -349,6 +349,7 @@ struct FusedAppend {
   const float* cos_table;
   const float* sin_table;
   void* q_rot_out;
+  int pdl;  // not the first layer of the step: may overlap the previous layer's tail
 };
 
 // The append can ride inside the decode kernel when every sequence brings one
@@ -411,6 +412,7 @@ static int decode_impl(pa_pool* p, int layer, const void* q, void* out, int64_t 
     d.sin_table = fz->sin_table;
     d.storage_w = p->storage + (size_t)layer * p->layer_bytes;
     d.q_rot_out = fz->q_rot_out == q ? nullptr : (__nv_bfloat16*)fz->q_rot_out;
+    d.pdl = fz->pdl;
   }
   if (!x) {
     PA_CUDA(pa::launch_decode(d, n_seqs, plan.warps, plan.stages, (cudaStream_t)stream));
@@ -487,7 +489,7 @@ int pa_decode_step_sharded(pa_pool* p, pa_exchange* x, int layer_begin, int laye
     int r;
     if (fuse) {
       // one kernel per layer: RoPE(Q), RoPE(K) + append, decode, exchange, merge
-      const FusedAppend fz{ki, vi, cos_table, sin_table, qr};
+      const FusedAppend fz{ki, vi, cos_table, sin_table, qr, l > layer_begin ? 1 : 0};
       r = decode_impl(p, l, qi, o, out_stride, nullptr, nullptr, scale, stream, x, true, &fz);
     } else {
       r = pa_append(p, l, qi, ki, vi, cos_table, sin_table, qr, stream);
@@ -522,7 +524,7 @@ int pa_decode_step(pa_pool* p, int layer_begin, int layer_end, const void* q_in,
     float* lse_l = lse ? lse + (size_t)i * n_seqs * q_heads : nullptr;
     int r;
     if (fuse) {
-      const FusedAppend fz{ki, vi, cos_table, sin_table, qr};
+      const FusedAppend fz{ki, vi, cos_table, sin_table, qr, l > layer_begin ? 1 : 0};
       r = decode_impl(p, l, qi, o, out_stride, nullptr, lse_l, scale, stream, nullptr, true, &fz);
     } else {
       r = pa_append(p, l, qi, ki, vi, cos_table, sin_table, qr, stream);

@@ -144,6 +144,8 @@ decode_kernel(DecodeParams p) {
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int x = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
+  // let the next layer's kernel take SMs as soon as this one's CTAs leave them
+  if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const BatchEntry e = p.batch[z];
   const int n_blocks = (e.kv_len + kBlockTok - 1) / kBlockTok;
   const int n_chunks = max(1, (n_blocks + p.chunk_blocks - 1) / p.chunk_blocks);
@@ -345,6 +347,12 @@ decode_kernel(DecodeParams p) {
   }
   if (failed && lane == 0) atomicExch(p.status, kStatusTimeout);
 
+  // Programmatic dependent launch (layers of one decode step): the streaming
+  // above only read the cache; everything written from here on (workspace,
+  // tickets, outputs, exchange) must wait until the previous layer's kernel —
+  // which shares the workspace — has completed.
+  if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
+
   // ---- merge the warps of this CTA -------------------------------------------
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
@@ -488,8 +496,21 @@ cudaError_t launch_decode_cfg(const DecodeParams& p, int n_seqs, cudaStream_t st
     configured[dev] = true;
   }
   dim3 grid(p.max_chunks, p.kv_heads, n_seqs);
-  decode_kernel<WARPS, STAGES><<<grid, WARPS * 32, S::kBytes, stream>>>(p);
-  return cudaGetLastError();
+  if (!p.pdl) {
+    decode_kernel<WARPS, STAGES><<<grid, WARPS * 32, S::kBytes, stream>>>(p);
+    return cudaGetLastError();
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(WARPS * 32);
+  cfg.dynamicSmemBytes = S::kBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, decode_kernel<WARPS, STAGES>, p);
 }
 
 }  // namespace

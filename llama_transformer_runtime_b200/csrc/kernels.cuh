@@ -62,6 +62,9 @@ struct DecodeParams {
   long long xchg_out_stride = 0;
   // Fused append (one new token per sequence at most): q is un-rotated, the
   // kernel rotates it and appends k_new/v_new rows (RoPE on K) to the cache.
+  // launched with programmatic stream serialization behind the previous
+  // layer's decode kernel (see the two griddepcontrol points in the kernel)
+  int pdl = 0;
   int fuse = 0;
   const __nv_bfloat16* k_new = nullptr;  // [rows][kv_heads][64], row e.kv_row_off
   const __nv_bfloat16* v_new = nullptr;
