@@ -67,9 +67,12 @@ __device__ __forceinline__ void write_row_outputs(const DecodeParams& p, int z, 
 // source rank and head.  Called by all threads of the CTA.
 __device__ __forceinline__ void publish_exchange(const DecodeParams& p, int z, int h) {
   if (p.xchg_world <= 0) return;
-  __threadfence_system();
+  // the CTA barrier orders every thread's peer stores before the publishing
+  // threads' system-scope fence, which is cumulative: one fence per flag
+  // instead of one per thread
   __syncthreads();
   if ((int)threadIdx.x < p.xchg_world) {
+    __threadfence_system();
     unsigned int* flag = p.xchg_flag[threadIdx.x] + ((size_t)p.xchg_rank * p.xchg_groups + z * p.kv_heads + h);
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(p.xchg_seq) : "memory");
   }
