@@ -11,19 +11,22 @@
 //
 // One CTA = 128 query rows of one query head (UMMA M = 128), walking 128-key
 // tiles of the cache up to the diagonal.
-//   warp 4      loader: per tile 8 K tiles + 8 V tiles (2 KiB each, one cache
+//   warp 8      loader: per tile 8 K tiles + 8 V tiles (2 KiB each, one cache
 //               block each) fetched through the block table with cp.async.bulk
 //               into a 2-stage ring.  The cache stores every tile already in
 //               the 128-byte swizzle, so the copies land as canonical UMMA
 //               operands: K as K-major, V as MN-major.
-//   warp 5      issues the MMAs: S = Q K^T (M128 N128 K64 -> TMEM columns
+//   warp 9      issues the MMAs: S = Q K^T (M128 N128 K64 -> TMEM columns
 //               0..127) and O += P V (M128 N64 K128 -> TMEM columns 128..191);
 //               completion is signalled to the other warps with tcgen05.commit.
-//   warps 0-3   softmax: thread r owns query row r = TMEM lane r; reads S with
-//               tcgen05.ld, writes P (bf16) into shared memory in K-major
-//               swizzled layout for the second MMA, rescales O in TMEM only
-//               when a row maximum moved by more than 2^8, and finally writes
-//               O / sum as bf16 straight into the [tokens, heads*64] layout.
+//   warps 0-7   softmax: S is read with tcgen05.ld in the 16x256b layout (the
+//               mma accumulator layout: a row is spread over the 4 threads of
+//               a quad, 16 TMEM lanes per warp), so row maxima and sums are
+//               quad shuffles and each thread carries only 64 scores; P (bf16)
+//               goes to shared memory with stmatrix in K-major swizzled layout
+//               for the second MMA; O is rescaled in TMEM only when a row
+//               maximum moved by more than 2^8; finally O / sum is written as
+//               bf16 straight into the [tokens, heads*64] layout.
 // Every wait is bounded; a wait that runs out raises the CTA's abort flag,
 // records PA_ERR_TIMEOUT in the status word, and all warps fall through to the
 // common exit, where tensor memory is released.
@@ -53,7 +56,9 @@ constexpr int kPrefillUsed = kOffMisc + 16;
 // it checks that at run time and refuses to run otherwise.
 constexpr int kPrefillSmem = kPrefillUsed + 112;
 static_assert(2 * (kPrefillSmem + 1024) <= 228 * 1024, "two CTAs per SM");
-constexpr int kPrefillThreads = 192;
+constexpr int kSoftmaxThreads = 256;  // warps 0..7
+constexpr int kLoadWarp = 8, kMmaWarp = 9;
+constexpr int kPrefillThreads = 320;
 constexpr uint32_t kTmemCols = 256;  // S: 128 columns, O: 64 columns, power of two
 constexpr uint32_t kColS = 0, kColO = 128;
 constexpr float kRescaleThreshold = 8.0f;  // log2: rescale O only if a row max moved by > 2^8
@@ -147,6 +152,42 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
   return r;
 }
 
+// 16 lanes x (8 groups of 8 columns): thread t gets, for group i, registers
+// 4i..4i+1 = (lane t/4, columns 8i + 2(t%4), +1) and 4i+2..4i+3 = the same
+// columns of lane t/4 + 8 (measured on B200; the mma accumulator layout).
+__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_16x256b_x8(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x256b.x8.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+        "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
+        "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]),
+        "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+// Four 8x8 bf16 matrices from accumulator-layout registers to shared memory;
+// lane l supplies the address of row l%8 of matrix l/8.
+__device__ __forceinline__ void stsm_x4(uint32_t addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(r0),
+               "r"(r1), "r"(r2), "r"(r3)
+               : "memory");
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes
 // apart (version 1 = Blackwell, layout type 2 = SWIZZLE_128B).  The same
 // encoding serves K-major operands (rows = M or N index, 128 bytes of K per
@@ -222,22 +263,21 @@ prefill_kernel(PrefillParams p) {
   const int last_pos = p.causal ? min(pos0 + rows - 1, e.kv_len - 1) : e.kv_len - 1;
   const int n_tiles = last_pos / kBN + 1;
   const int n_blocks = (e.kv_len + kBlockTok - 1) / kBlockTok;
-  const int q_heads = p.kv_heads * kGroup;
 
   if (tid == 0) {
     *abort_flag = 0;
-    mbar_init(bar_q, 128);
+    mbar_init(bar_q, kSoftmaxThreads);
     mbar_init(bar_s, 1);
-    mbar_init(bar_p, 128);
+    mbar_init(bar_p, kSoftmaxThreads);
     mbar_init(bar_pv, 1);
-    mbar_init(bar_sfree, 128);
+    mbar_init(bar_sfree, kSoftmaxThreads);
     for (int s = 0; s < kStagesKV; s++) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tmem_alloc(base + kOffMisc, kTmemCols);
     tmem_relinquish();
   }
@@ -246,7 +286,7 @@ prefill_kernel(PrefillParams p) {
   tc_fence_after();
   const uint32_t tmem = *s_tmem_base;
 
-  if (warp == 4) {
+  if (warp == kLoadWarp) {
     // ===================== loader ============================================
     const int32_t* table = p.tables + (size_t)e.seq * p.max_blocks_per_seq;
     const int hk = h / kGroup;
@@ -271,7 +311,7 @@ prefill_kernel(PrefillParams p) {
       }
       __syncwarp();
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ===================== MMA issue =========================================
     constexpr uint32_t kIdescQK = idesc_bf16(kBM, kBN, false);
     constexpr uint32_t kIdescPV = idesc_bf16(kBM, kHeadDim, true);
@@ -313,162 +353,197 @@ prefill_kernel(PrefillParams p) {
       __syncwarp();
     }
   } else {
-    // ===================== softmax / epilogue (thread = query row) ===========
-    const int r = tid;  // 0..127 = TMEM lane
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    // Q tile -> shared memory (K-major, swizzled); rows past the end are zero
+    // ===================== softmax / epilogue ==================================
+    // Warp w works on TMEM lanes [32*(w&3) + 16*(w>>2), +16) in the 16x256b
+    // register layout (the mma accumulator layout): thread t holds rows
+    // rA = first + t/4 and rB = rA + 8, and of every group of 8 columns the two
+    // at 2*(t%4).  A row is spread over the 4 threads of a quad, so row maxima
+    // and sums are quad shuffles, and P goes to shared memory with stmatrix.
+    const int first_row = (warp & 3) * 32 + (warp >> 2) * 16;
+    const uint32_t lane_base = (uint32_t)first_row << 16;
+    const int rA = first_row + (lane >> 2), rB = rA + 8;
+    const int cq = (lane & 3) * 2;
+    // Q tile -> shared memory (K-major, swizzled): thread = (row, half row)
     {
-      uint4 v[8];
+      const int r = tid >> 1, c0 = (tid & 1) * 4;
+      uint4 v[4];
       if (r < rows) {
         const uint4* src = reinterpret_cast<const uint4*>(
             p.q + (size_t)z * p.q_seq_stride + (size_t)(e.q_row_off + row0 + r) * p.q_row_stride +
             (size_t)h * p.q_head_stride);
 #pragma unroll
-        for (int c = 0; c < 8; c++) v[c] = src[c];
+        for (int c = 0; c < 4; c++) v[c] = src[c0 + c];
       } else {
 #pragma unroll
-        for (int c = 0; c < 8; c++) v[c] = make_uint4(0, 0, 0, 0);
+        for (int c = 0; c < 4; c++) v[c] = make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
-      for (int c = 0; c < 8; c++)
-        *reinterpret_cast<uint4*>(sm + kOffQ + r * 128 + ((c ^ (r & 7)) << 4)) = v[c];
+      for (int c = 0; c < 4; c++)
+        *reinterpret_cast<uint4*>(sm + kOffQ + r * 128 + (((c0 + c) ^ (r & 7)) << 4)) = v[c];
       fence_proxy_async_smem();
       mbar_arrive(bar_q);
     }
 
-    const int qpos = pos0 + r;
-    float m_used = -INFINITY, l_sum = 0.f;
+    // stmatrix addresses of this thread: matrix m = lane/8 of each x4 store is
+    // (rows first_row + 8*(m&1) .., column group g + (m>>1)), this thread gives its row lane%8
+    const int st_row = first_row + ((lane >> 3) & 1) * 8 + (lane & 7);
+    const int st_grp = lane >> 4;
+    const uint32_t st_base = sP + st_row * 128;
+    const int st_swz = st_row & 7;
+
+    const int qposA = pos0 + rA, qposB = pos0 + rB;
+    float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
     bool ok = true;
     for (int kt = 0; kt < n_tiles; kt++) {
       if (!wait_or_abort(bar_s, (uint32_t)(kt & 1), abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int key0 = kt * kBN;
       const bool need_mask = (p.causal && key0 + kBN - 1 > pos0) || (key0 + kBN > e.kv_len);
-      const int limit = (p.causal ? min(qpos, e.kv_len - 1) : e.kv_len - 1) - key0;  // keys <= limit are visible
 
-      // S -> registers in one go (four loads in flight, one wait); the tensor
+      // S -> registers (both column halves in flight, one wait); the tensor
       // memory copy is then free for the next tile's Q K^T
-      uint32_t sreg[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; c++) tmem_ld32(tmem + lane_base + kColS + c * 32, sreg[c]);
+      uint32_t s[2][32];
+      tmem_ld_16x256b_x8(tmem + lane_base + kColS, s[0]);
+      tmem_ld_16x256b_x8(tmem + lane_base + kColS + 64, s[1]);
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(bar_sfree);
 
       if (need_mask) {
+        const int limA = (p.causal ? min(qposA, e.kv_len - 1) : e.kv_len - 1) - key0;  // keys <= lim are visible
+        const int limB = (p.causal ? min(qposB, e.kv_len - 1) : e.kv_len - 1) - key0;
 #pragma unroll
-        for (int c = 0; c < 4; c++)
+        for (int hf = 0; hf < 2; hf++)
 #pragma unroll
-          for (int j = 0; j < 32; j++)
-            if (c * 32 + j > limit) sreg[c][j] = 0xff800000u;  // -inf
+          for (int i = 0; i < 8; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              const int col = hf * 64 + i * 8 + cq + (j & 1);
+              if (col > ((j & 2) ? limB : limA)) s[hf][4 * i + j] = 0xff800000u;  // -inf
+            }
       }
-      // row maximum (raw scores; the scale is positive)
-      // four independent chains of 3-input max
-      float mxc[4];
-#pragma unroll
-      for (int c = 0; c < 4; c++) {
-        mxc[c] = -INFINITY;
-#pragma unroll
-        for (int j = 0; j < 32; j += 2)
-          mxc[c] = max3(mxc[c], __uint_as_float(sreg[c][j]), __uint_as_float(sreg[c][j + 1]));
-      }
-      float mx = fmaxf(fmaxf(mxc[0], mxc[1]), fmaxf(mxc[2], mxc[3])) * p.scale_log2;
-      // lazy rescale: keep the old reference maximum unless it is off by > 2^8
-      float corr = 1.f;
-      if (mx > m_used + kRescaleThreshold) {
-        corr = ex2(m_used - mx);  // 0 on the first tile
-        m_used = mx;
-      }
-      const bool any_corr = __any_sync(0xffffffffu, corr != 1.f);
-
-      // probabilities -> bf16, kept in registers: the exponentials (the bulk of
-      // the work) run while the previous tile's P V is still in the tensor pipe
-      const float neg_m = -m_used;
-      // packed fp32x2 arithmetic (two values per instruction) around the exp2
-      const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
-      const uint64_t negm2 = pack_f32x2(neg_m, neg_m);
-      uint64_t lacc[4];
-      uint32_t pk[4][16];
-#pragma unroll
-      for (int c = 0; c < 4; c++) {
-        lacc[c] = 0ull;
-#pragma unroll
-        for (int u = 0; u < 16; u++) {
-          float x0, x1;
-          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sreg[c][2 * u]),
-                                            __uint_as_float(sreg[c][2 * u + 1])), scale2, negm2), x0, x1);
-          const float p0 = ex2(x0), p1 = ex2(x1);
-          lacc[c] = add_f32x2(lacc[c], pack_f32x2(p0, p1));
-          pk[c][u] = pack_bf16(p0, p1);
-        }
-      }
-      float l_tile;
+      // row maxima of the raw scores (the scale is positive): two chains per row
+      float mxA, mxB;
       {
-        float a0, a1;
-        unpack_f32x2(add_f32x2(add_f32x2(lacc[0], lacc[1]), add_f32x2(lacc[2], lacc[3])), a0, a1);
-        l_tile = a0 + a1;
+        float a0 = -INFINITY, a1 = -INFINITY, b0 = -INFINITY, b1 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          a0 = max3(a0, __uint_as_float(s[0][4 * i]), __uint_as_float(s[0][4 * i + 1]));
+          a1 = max3(a1, __uint_as_float(s[1][4 * i]), __uint_as_float(s[1][4 * i + 1]));
+          b0 = max3(b0, __uint_as_float(s[0][4 * i + 2]), __uint_as_float(s[0][4 * i + 3]));
+          b1 = max3(b1, __uint_as_float(s[1][4 * i + 2]), __uint_as_float(s[1][4 * i + 3]));
+        }
+        mxA = fmaxf(a0, a1);
+        mxB = fmaxf(b0, b1);
+        mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1));
+        mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
+        mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2)) * p.scale_log2;
+        mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2)) * p.scale_log2;
       }
+      // lazy rescale: keep the old reference maximum unless it is off by > 2^8
+      float corrA = 1.f, corrB = 1.f;
+      if (mxA > mA + kRescaleThreshold) {
+        corrA = ex2(mA - mxA);  // 0 on the first tile
+        mA = mxA;
+      }
+      if (mxB > mB + kRescaleThreshold) {
+        corrB = ex2(mB - mxB);
+        mB = mxB;
+      }
+      const bool any_corr = __any_sync(0xffffffffu, corrA != 1.f || corrB != 1.f);
+
+      // probabilities -> bf16 in registers: the exponentials (the bulk of the
+      // work) run while the previous tile's P V is still in the tensor pipe
+      const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
+      const uint64_t negA2 = pack_f32x2(-mA, -mA), negB2 = pack_f32x2(-mB, -mB);
+      uint64_t laccA = 0ull, laccB = 0ull;
+      uint32_t pkA[16], pkB[16];
+#pragma unroll
+      for (int hf = 0; hf < 2; hf++)
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          float x0, x1, y0, y1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[hf][4 * i]), __uint_as_float(s[hf][4 * i + 1])),
+                                 scale2, negA2), x0, x1);
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[hf][4 * i + 2]), __uint_as_float(s[hf][4 * i + 3])),
+                                 scale2, negB2), y0, y1);
+          const float p0 = ex2(x0), p1 = ex2(x1), p2 = ex2(y0), p3 = ex2(y1);
+          laccA = add_f32x2(laccA, pack_f32x2(p0, p1));
+          laccB = add_f32x2(laccB, pack_f32x2(p2, p3));
+          pkA[hf * 8 + i] = pack_bf16(p0, p1);
+          pkB[hf * 8 + i] = pack_bf16(p2, p3);
+        }
 
       // P of the previous tile must have been consumed, O must be quiescent
       if (kt > 0) {
         if (!wait_or_abort(bar_pv, (uint32_t)((kt - 1) & 1), abort_flag)) { ok = false; break; }
         tc_fence_after();
         if (any_corr) {
-#pragma unroll 1
-          for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
-            uint32_t oreg[32];
-            tmem_ld32(tmem + lane_base + kColO + c0, oreg);
-            tmem_wait_ld();
+          uint32_t o[32];
+          tmem_ld_16x256b_x8(tmem + lane_base + kColO, o);
+          tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; j++) oreg[j] = __float_as_uint(__uint_as_float(oreg[j]) * corr);
-            tmem_st32(tmem + lane_base + kColO + c0, oreg);
+          for (int i = 0; i < 8; i++) {
+            o[4 * i] = __float_as_uint(__uint_as_float(o[4 * i]) * corrA);
+            o[4 * i + 1] = __float_as_uint(__uint_as_float(o[4 * i + 1]) * corrA);
+            o[4 * i + 2] = __float_as_uint(__uint_as_float(o[4 * i + 2]) * corrB);
+            o[4 * i + 3] = __float_as_uint(__uint_as_float(o[4 * i + 3]) * corrB);
           }
+          tmem_st_16x256b_x8(tmem + lane_base + kColO, o);
           tmem_wait_st();
         }
       }
-      l_sum = l_sum * corr + l_tile;
+      {
+        float a0, a1, b0, b1;
+        unpack_f32x2(laccA, a0, a1);
+        unpack_f32x2(laccB, b0, b1);
+        lA = lA * corrA + (a0 + a1);
+        lB = lB * corrB + (b0 + b1);
+      }
 
-      // P -> shared memory (K-major, swizzled)
+      // P -> shared memory (K-major, swizzled), four 8x8 matrices per stmatrix
 #pragma unroll
-      for (int c = 0; c < 4; c++) {
-        unsigned char* prow = sm + kOffP + (c >> 1) * (kBM * 128) + r * 128;
-#pragma unroll
-        for (int g = 0; g < 4; g++) {
-          const int chunk = (c & 1) * 4 + g;
-          *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) =
-              make_uint4(pk[c][4 * g], pk[c][4 * g + 1], pk[c][4 * g + 2], pk[c][4 * g + 3]);
-        }
+      for (int g = 0; g < 16; g += 2) {
+        const int grp = g + st_grp;
+        stsm_x4(st_base + (grp >> 3) * (kBM * 128) + (((grp & 7) ^ st_swz) << 4), pkA[g], pkB[g], pkA[g + 1],
+                pkB[g + 1]);
       }
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(bar_p);
     }
 
-    // epilogue: O / sum -> bf16, [tokens, heads*64] layout
+    // epilogue: O / sum -> bf16, [tokens, heads*64] layout (or the caller's strides)
     if (ok && wait_or_abort(bar_pv, (uint32_t)((n_tiles - 1) & 1), abort_flag)) {
       tc_fence_after();
-      const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-      __nv_bfloat16* orow = p.out + (size_t)z * p.o_seq_stride +
-                            (size_t)(e.q_row_off + row0 + r) * p.o_row_stride + (size_t)h * p.o_head_stride;
-#pragma unroll 1
-      for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
-        uint32_t oreg[32];
-        tmem_ld32(tmem + lane_base + kColO + c0, oreg);
-        tmem_wait_ld();
-        if (r < rows) {
+      lA += __shfl_xor_sync(0xffffffffu, lA, 1);
+      lB += __shfl_xor_sync(0xffffffffu, lB, 1);
+      lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+      lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+      const float invA = lA > 0.f ? 1.f / lA : 0.f, invB = lB > 0.f ? 1.f / lB : 0.f;
+      uint32_t o[32];
+      tmem_ld_16x256b_x8(tmem + lane_base + kColO, o);
+      tmem_wait_ld();
+      __nv_bfloat16* obase = p.out + (size_t)z * p.o_seq_stride + (size_t)h * p.o_head_stride + cq;
+      if (rA < rows) {
+        __nv_bfloat16* orow = obase + (size_t)(e.q_row_off + row0 + rA) * p.o_row_stride;
 #pragma unroll
-          for (int c = 0; c < 4; c++) {
-            uint4 v;
-            v.x = pack_bf16(__uint_as_float(oreg[8 * c + 0]) * inv, __uint_as_float(oreg[8 * c + 1]) * inv);
-            v.y = pack_bf16(__uint_as_float(oreg[8 * c + 2]) * inv, __uint_as_float(oreg[8 * c + 3]) * inv);
-            v.z = pack_bf16(__uint_as_float(oreg[8 * c + 4]) * inv, __uint_as_float(oreg[8 * c + 5]) * inv);
-            v.w = pack_bf16(__uint_as_float(oreg[8 * c + 6]) * inv, __uint_as_float(oreg[8 * c + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c0 + 8 * c) = v;
-          }
-        }
+        for (int i = 0; i < 8; i++)
+          *reinterpret_cast<uint32_t*>(orow + 8 * i) =
+              pack_bf16(__uint_as_float(o[4 * i]) * invA, __uint_as_float(o[4 * i + 1]) * invA);
       }
-      if (p.lse && r < rows)
-        p.lse[(size_t)z * p.lse_seq_stride + (size_t)h * e.n_q + row0 + r] = l_sum > 0.f ? kLn2 * (m_used + log2f(l_sum)) : -INFINITY;
+      if (rB < rows) {
+        __nv_bfloat16* orow = obase + (size_t)(e.q_row_off + row0 + rB) * p.o_row_stride;
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+          *reinterpret_cast<uint32_t*>(orow + 8 * i) =
+              pack_bf16(__uint_as_float(o[4 * i + 2]) * invB, __uint_as_float(o[4 * i + 3]) * invB);
+      }
+      if (p.lse && (lane & 3) == 0) {
+        float* lrow = p.lse + (size_t)z * p.lse_seq_stride + (size_t)h * e.n_q + row0;
+        if (rA < rows) lrow[rA] = lA > 0.f ? kLn2 * (mA + log2f(lA)) : -INFINITY;
+        if (rB < rows) lrow[rB] = lB > 0.f ? kLn2 * (mB + log2f(lB)) : -INFINITY;
+      }
     }
   }
 
@@ -476,7 +551,7 @@ prefill_kernel(PrefillParams p) {
   tc_fence_before();
   __syncthreads();
   if (tid == 0 && *abort_flag) atomicExch(p.status, kStatusTimeout);
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
