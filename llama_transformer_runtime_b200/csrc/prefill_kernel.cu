@@ -47,7 +47,7 @@ constexpr int kOffQ = 0;
 constexpr int kOffKV = kOffQ + kQBytes;
 constexpr int kOffP = kOffKV + kStagesKV * (kKBytes + kVBytes);
 constexpr int kOffBar = kOffP + kPBytes;
-constexpr int kNumBars = 5 + 2 * kStagesKV;
+constexpr int kNumBars = 5 + 4 * kStagesKV;  // K and V halves of a stage fill and free separately
 constexpr int kOffMisc = kOffBar + kNumBars * 8;  // tensor-memory base address, abort flag
 constexpr int kPrefillUsed = kOffMisc + 16;
 // Two CTAs per SM: 2 * (request + 1 KiB system reserve) must stay below 228 KiB,
@@ -243,7 +243,8 @@ prefill_kernel(PrefillParams p) {
   const uint32_t bar0 = base + kOffBar;
   const uint32_t bar_q = bar0, bar_s = bar0 + 8, bar_p = bar0 + 16, bar_pv = bar0 + 24;
   const uint32_t bar_sfree = bar0 + 32;
-  const uint32_t bar_full = bar0 + 40, bar_empty = bar_full + 8 * kStagesKV;
+  const uint32_t bar_kfull = bar0 + 40, bar_kempty = bar_kfull + 8 * kStagesKV;
+  const uint32_t bar_vfull = bar_kempty + 8 * kStagesKV, bar_vempty = bar_vfull + 8 * kStagesKV;
   uint32_t* s_tmem_base = reinterpret_cast<uint32_t*>(sm + kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kOffMisc + 4);
 
@@ -272,8 +273,10 @@ prefill_kernel(PrefillParams p) {
     mbar_init(bar_pv, 1);
     mbar_init(bar_sfree, kSoftmaxThreads);
     for (int s = 0; s < kStagesKV; s++) {
-      mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_empty + 8 * s, 1);
+      mbar_init(bar_kfull + 8 * s, 1);
+      mbar_init(bar_kempty + 8 * s, 1);
+      mbar_init(bar_vfull + 8 * s, 1);
+      mbar_init(bar_vempty + 8 * s, 1);
     }
     mbar_fence_init();
   }
@@ -290,26 +293,63 @@ prefill_kernel(PrefillParams p) {
     // ===================== loader ============================================
     const int32_t* table = p.tables + (size_t)e.seq * p.max_blocks_per_seq;
     const int hk = h / kGroup;
-    for (int kt = 0; kt < n_tiles; kt++) {
-      const int st = kt % kStagesKV;
-      if (!wait_or_abort(bar_empty + 8 * st, (uint32_t)(((kt / kStagesKV) & 1) ^ 1), abort_flag)) break;
-      if (lane == 0) mbar_expect_tx(bar_full + 8 * st, kKBytes + kVBytes);
-      __syncwarp();
-      if (lane < 16) {
-        const int b = lane & 7, kv = lane >> 3;
-        // blocks past the end of the sequence re-read its last block: finite
-        // data whose keys are masked, never uninitialised shared memory
-        int bi = min(kt * (kBN / kBlockTok) + b, n_blocks - 1);
-        int blk = table[bi];
-        if (blk < 0 || blk >= p.num_blocks) {
-          atomicExch(p.status, kStatusBadBlock);
-          blk = 0;
-        }
-        const char* src = p.storage + tile_off(blk, p.kv_heads, hk, kv);
-        const uint32_t dst = sKV + st * (kKBytes + kVBytes) + kv * kKBytes + b * kTileBytes;
-        bulk_g2s(dst, src, kTileBytes, bar_full + 8 * st);
+    // K halves are released right after Q K^T, V halves after P V, so the two
+    // streams advance independently: one polling loop serves whichever half
+    // is free.  Lanes 0..7 copy the 8 blocks of a tile; the block ids of the
+    // next tile are fetched before the wait, off the critical path.
+    auto block_of = [&](int kt) {
+      // blocks past the end of the sequence re-read its last block: finite
+      // data whose keys are masked, never uninitialised shared memory
+      int blk = lane < 8 ? table[min(kt * (kBN / kBlockTok) + lane, n_blocks - 1)] : 0;
+      if (blk < 0 || blk >= p.num_blocks) {
+        atomicExch(p.status, kStatusBadBlock);
+        blk = 0;
       }
-      __syncwarp();
+      return blk;
+    };
+    int k_next = 0, v_next = 0;
+    int blk_k = block_of(0), blk_v = blk_k;
+    uint64_t t0 = global_ns();
+    uint32_t spins = 0;
+    bool ok = true;
+    while (ok && (k_next < n_tiles || v_next < n_tiles)) {
+      bool progressed = false;
+      if (k_next < n_tiles) {
+        const int st = k_next % kStagesKV;
+        if (__all_sync(0xffffffffu, mbar_test(bar_kempty + 8 * st, (uint32_t)(((k_next / kStagesKV) & 1) ^ 1)))) {
+          if (lane == 0) mbar_expect_tx(bar_kfull + 8 * st, kKBytes);
+          __syncwarp();
+          if (lane < 8)
+            bulk_g2s(sKV + st * (kKBytes + kVBytes) + lane * kTileBytes,
+                     p.storage + tile_off(blk_k, p.kv_heads, hk, 0), kTileBytes, bar_kfull + 8 * st);
+          k_next++;
+          if (k_next < n_tiles) blk_k = block_of(k_next);
+          progressed = true;
+        }
+      }
+      if (v_next < n_tiles) {
+        const int st = v_next % kStagesKV;
+        if (__all_sync(0xffffffffu, mbar_test(bar_vempty + 8 * st, (uint32_t)(((v_next / kStagesKV) & 1) ^ 1)))) {
+          if (lane == 0) mbar_expect_tx(bar_vfull + 8 * st, kVBytes);
+          __syncwarp();
+          if (lane < 8)
+            bulk_g2s(sKV + st * (kKBytes + kVBytes) + kKBytes + lane * kTileBytes,
+                     p.storage + tile_off(blk_v, p.kv_heads, hk, 1), kTileBytes, bar_vfull + 8 * st);
+          v_next++;
+          if (v_next < n_tiles) blk_v = block_of(v_next);
+          progressed = true;
+        }
+      }
+      if (progressed) {
+        t0 = global_ns();
+      } else if ((++spins & 31u) == 0) {
+        bool stop = *abort_flag != 0;
+        if (!stop && global_ns() - t0 > kWaitLimitNs) {  // nothing freed for a second
+          *abort_flag = 1;
+          stop = true;
+        }
+        if (__any_sync(0xffffffffu, stop)) ok = false;
+      }
     }
   } else if (warp == kMmaWarp) {
     // ===================== MMA issue =========================================
@@ -318,7 +358,7 @@ prefill_kernel(PrefillParams p) {
     bool ok = wait_or_abort(bar_q, 0, abort_flag);
     auto issue_qk = [&](int kt) {
       const int st = kt % kStagesKV;
-      if (!wait_or_abort(bar_full + 8 * st, (uint32_t)((kt / kStagesKV) & 1), abort_flag)) return false;
+      if (!wait_or_abort(bar_kfull + 8 * st, (uint32_t)((kt / kStagesKV) & 1), abort_flag)) return false;
       tc_fence_after();
       if (lane == 0) {
         const uint32_t sK = sKV + st * (kKBytes + kVBytes);
@@ -327,6 +367,7 @@ prefill_kernel(PrefillParams p) {
           umma_ss(tmem + kColS, smem_desc_sw128(sQ + ks * 32), smem_desc_sw128(sK + ks * 32),
                   kIdescQK, ks > 0 ? 1u : 0u);
         tc_commit(bar_s);
+        tc_commit(bar_kempty + 8 * st);  // this stage's K half may be refilled
       }
       __syncwarp();
       return true;
@@ -340,6 +381,7 @@ prefill_kernel(PrefillParams p) {
         if (!issue_qk(kt + 1)) break;
       }
       if (!wait_or_abort(bar_p, (uint32_t)(kt & 1), abort_flag)) break;
+      if (!wait_or_abort(bar_vfull + 8 * st, (uint32_t)((kt / kStagesKV) & 1), abort_flag)) break;
       tc_fence_after();
       if (lane == 0) {
         const uint32_t sV = sKV + st * (kKBytes + kVBytes) + kKBytes;
@@ -348,7 +390,7 @@ prefill_kernel(PrefillParams p) {
           umma_ss(tmem + kColO, smem_desc_sw128(sP + (kk >> 2) * (kBM * 128) + (kk & 3) * 32),
                   smem_desc_sw128(sV + kk * kTileBytes), kIdescPV, (kt > 0 || kk > 0) ? 1u : 0u);
         tc_commit(bar_pv);
-        tc_commit(bar_empty + 8 * st);
+        tc_commit(bar_vempty + 8 * st);
       }
       __syncwarp();
     }
