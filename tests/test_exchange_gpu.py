@@ -108,3 +108,52 @@ def test_wait_that_nothing_satisfies_times_out_cleanly(cuda):
     check_close(orc.bf16_to_f32(to_u16(want))[0], O[:, 0].reshape(-1), "decode after a timed-out wait")
     x.close()
     pool.close()
+
+
+def test_sharded_step_with_one_rank_equals_plain_step(cuda):
+    """pa_decode_step_sharded (append fused in, partials pushed, the combining CTA
+    waits for the flags and merges in the kernel) with a world of one rank: it
+    pushes to its own buffer and must reproduce pa_decode_step bit for bit."""
+    rng = np.random.default_rng(97)
+    layers, lens = 2, [300, 17, 1]
+    n = len(lens)
+    cos, sin = orc.build_rope_tables(400)
+    cos_d, sin_d = f32_dev(cos), f32_dev(sin)
+    q = to_dev(orc.randn_bf16(rng, (layers, n, 32, 64)))
+    k = to_dev(orc.randn_bf16(rng, (layers, n, 8, 64)))
+    v = to_dev(orc.randn_bf16(rng, (layers, n, 8, 64)))
+    outs = []
+    for sharded in (False, True):
+        prng = np.random.default_rng(98)
+        pool = paged.KVPool(layers, 64, 8, n, 24)
+        pool.set_free_order(prng.permutation(64))
+        seqs = []
+        for L in lens:
+            s = pool.create_seq()
+            pool.reserve(s, L)
+            pool.batch_set([s], [L])
+            for layer in range(layers):
+                pool.append(layer, None, to_dev(orc.randn_bf16(prng, (L, 8, 64), 0.5)),
+                            to_dev(orc.randn_bf16(prng, (L, 8, 64), 0.5)),
+                            torch.ones(L, 32, device=DEV), torch.zeros(L, 32, device=DEV), None)
+            seqs.append(s)
+        for s, L in zip(seqs, lens):
+            pool.reserve(s, L + 1)
+        pool.batch_set(seqs)
+        out = torch.zeros(layers, n, 2048, dtype=torch.bfloat16, device=DEV)
+        q_rot = torch.zeros_like(q)
+        if sharded:
+            x = paged.Exchange(0, 0, 1, n, 8)
+            paged.decode_step_sharded(pool, x, 0, layers, q, k, v, n * 2048, n * 512, cos_d, sin_d, q_rot, out,
+                                      2048, n * 2048)
+        else:
+            pool.decode_step(0, layers, q, k, v, n * 2048, n * 512, cos_d, sin_d, q_rot, out, 2048, n * 2048)
+        torch.cuda.synchronize()
+        pool.check()
+        outs.append((to_u16(out), to_u16(q_rot)))
+        if sharded:
+            x.close()
+        pool.close()
+    # the merge of a single partial renormalises through exp/log of the LSE: equal within bf16 rounding
+    check_close(orc.bf16_to_f32(outs[1][0]), orc.bf16_to_f32(outs[0][0]), "sharded (1 rank) vs plain step")
+    assert np.array_equal(outs[0][1], outs[1][1])
