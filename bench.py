@@ -600,7 +600,16 @@ def run_batch(args):
     out_local = torch.zeros(LAYERS, n_seqs, qh * D, dtype=torch.bfloat16, device=dev)
     gath = torch.zeros(LAYERS, world, n_seqs, qh * D, dtype=torch.bfloat16, device=dev)
     out_host = torch.zeros(LAYERS, n_seqs, Q_HEADS * D, dtype=torch.bfloat16).pin_memory()
-    state = {"launches": 0, "bytes": 0}
+    state = {"launches": 0, "bytes": 0, "rows": None}
+    hg = None
+    if world > 1 and args.exchange == "fused":
+        import ctypes
+        cudart = ctypes.CDLL("libcudart.so.12")
+        hg = paged.HeadGather(local_rank, rank, world, n_seqs, LAYERS, kvh)
+        handles = [None] * world
+        dist.all_gather_object(handles, hg.handle())
+        hg.connect(handles)
+        dist.barrier()
 
     def step():
         for s in ids:
@@ -612,6 +621,12 @@ def run_batch(args):
             pool.decode_step(0, LAYERS, q_dev, k_dev, v_dev, n_seqs * qh * D, n_seqs * kvh * D, cos, sin, q_rot,
                              out_full, Q_HEADS * D, n_seqs * Q_HEADS * D)
             state["launches"] += LAYERS  # one fused kernel per layer
+            return
+        if hg is not None:
+            # one fused kernel per layer; its epilogue stores this rank's columns into every
+            # rank's rows (peer stores over NVLink); one arrival wait at the end of the step
+            state["rows"] = hg.step(pool, q_dev, k_dev, v_dev, n_seqs * qh * D, n_seqs * kvh * D, cos, sin, q_rot)
+            state["launches"] += LAYERS + 1
             return
         for layer in range(LAYERS):
             pool.append(layer, q_dev[layer], k_dev[layer], v_dev[layer], cos, sin, q_rot[layer])
@@ -625,7 +640,11 @@ def run_batch(args):
         k_dev.copy_(k_host, non_blocking=True)
         v_dev.copy_(v_host, non_blocking=True)
         step()
-        out_host.copy_(out_full, non_blocking=True)
+        if hg is not None:  # the rows live in the gather's buffer: device-to-host on the same stream
+            assert cudart.cudaMemcpyAsync(ctypes.c_void_p(out_host.data_ptr()), ctypes.c_void_p(state["rows"]),
+                                          ctypes.c_size_t(out_host.numel() * 2), 2, None) == 0
+        else:
+            out_host.copy_(out_full, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     def barrier():
@@ -674,8 +693,19 @@ def run_batch(args):
     peak, peak_kind = measured_peak()
     pool.check()
     m1 = sampler.mark()
+    gather_check = None
+    if hg is not None:
+        # layer 0 of the last fused step against an NCCL all-gather of the same decode
+        dist.all_gather_into_tensor(gath[0].view(-1), out_local[0].view(-1))
+        want = gath[0].permute(1, 0, 2).reshape(n_seqs, Q_HEADS * D)
+        got = torch.empty(n_seqs, Q_HEADS * D, dtype=torch.bfloat16, device=dev)
+        torch.cuda.synchronize()
+        assert cudart.cudaMemcpy(ctypes.c_void_p(got.data_ptr()), ctypes.c_void_p(state["rows"]),
+                                 ctypes.c_size_t(got.numel() * 2), 3) == 0
+        gather_check = float((got.float() - want.float()).abs().max().item())
     if rank == 0:
         line = {
+            "fused_gather_vs_allgather_max_abs_diff": gather_check,
             "metric": "paged_decode_attn_hbm_gbs", "value": round(nbytes / (ms * 1e-3) / 1e9, 1), "unit": "GB/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4),
             "us_per_token": round(ms / args.steps * 1e3 / n_seqs, 2),
@@ -686,7 +716,10 @@ def run_batch(args):
                        "block_table": "shared pool, seeded free order, a third of the sequences freed and "
                                       "re-created twice before timing",
                        "parallelism": "1 GPU" if world == 1 else
-                                      f"{kvh} KV head(s) per GPU over {world} GPUs, NCCL all-gather of head outputs per layer",
+                                      (f"{kvh} KV head(s) per GPU over {world} GPUs; the decode epilogue stores each "
+                                       f"rank's head outputs into every rank's rows over NVLink, one arrival wait per step"
+                                       if hg is not None else
+                                       f"{kvh} KV head(s) per GPU over {world} GPUs, NCCL all-gather of head outputs per layer"),
                        "l2": "inputs larger than L2"},
             "e2e": {"value": round(nbytes_e2e / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
                     "h2d_bytes_per_step": (q_host.numel() + k_host.numel() + v_host.numel()) * 2,
@@ -698,6 +731,8 @@ def run_batch(args):
         }
         print(json.dumps(line), flush=True)
     barrier()
+    if hg is not None:
+        hg.close()
     pool.close()
     if world > 1:
         dist.destroy_process_group()

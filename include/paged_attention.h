@@ -213,6 +213,33 @@ int pa_decode_step_sharded(pa_pool* pool, pa_exchange* x, int layer_begin, int l
                            void* out, int64_t out_stride, int64_t out_layer_stride,
                            float scale, void* stream);
 
+/* ---- KV-head sharding over several GPUs ---------------------------------------
+ * Each rank's pool holds 8/n KV heads (kv_heads of pa_pool_create) and serves
+ * the 4*8/n query heads of those groups; every rank needs the full
+ * [sequences, 2048] attention rows afterwards.  The all-gather is fused into the
+ * decode kernel: finished rows are stored into the column slice of every rank's
+ * row buffer by peer stores and counted per (source rank, layer); one wait at
+ * the end of the step (bounded, PA_ERR_TIMEOUT via pa_pool_check) replaces all
+ * per-layer collectives.  Buffers travel between processes as CUDA IPC handles
+ * (PA_EXCHANGE_HANDLE_BYTES each), or as plain pointers inside one process. */
+typedef struct pa_gather pa_gather;
+int pa_gather_create(pa_gather** out, int device, int rank, int world, int n_seqs,
+                     int layers, int kv_heads);
+int pa_gather_handle(pa_gather* g, void* handle64);
+int pa_gather_connect(pa_gather* g, const void* handles);
+int pa_gather_buffer(pa_gather* g, void** dev_ptr, uint64_t* bytes);
+int pa_gather_connect_ptrs(pa_gather* g, void* const* peer_buffers);
+int pa_gather_destroy(pa_gather* g);
+/* One decode step over all layers of the gather (append fused in, see
+ * pa_decode_step).  With wait != 0 it ends with the arrival wait and *rows is
+ * this step's [layers][n_seqs][2048 * ...] bf16 rows on this device (valid until
+ * the step after next); with wait == 0 call pa_gather_wait later. */
+int pa_decode_step_gathered(pa_pool* pool, pa_gather* g, const void* q_in, const void* k_in,
+                            const void* v_in, int64_t q_layer_stride, int64_t kv_layer_stride,
+                            const float* cos_table, const float* sin_table, void* q_rot,
+                            float scale, int wait, void* stream, void** rows);
+int pa_gather_wait(pa_pool* pool, pa_gather* g, void* stream, void** rows);
+
 /* pa_decode_noalloc: pa_decode for hosts that are not allowed to allocate
  * device memory — a plug-in inside a serving process that owns the whole GPU
  * through its own arena, a latency-critical loop that cannot afford the

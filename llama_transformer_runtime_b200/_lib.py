@@ -21,7 +21,9 @@ SYMBOLS = [
     "pa_pool_check", "pa_pool_set_decode_chunk_blocks", "pa_pool_set_decode_shape",
     "pa_decode_noalloc", "pa_exchange_create", "pa_exchange_handle", "pa_exchange_connect",
     "pa_exchange_destroy", "pa_decode_step_sharded", "pa_exchange_buffer", "pa_exchange_connect_ptrs",
-    "pa_decode_push", "pa_exchange_merge",
+    "pa_decode_push", "pa_exchange_merge", "pa_gather_create", "pa_gather_handle", "pa_gather_connect",
+    "pa_gather_buffer", "pa_gather_connect_ptrs", "pa_gather_destroy", "pa_decode_step_gathered",
+    "pa_gather_wait",
 ]
 
 
@@ -88,6 +90,14 @@ def lib():
         "pa_decode_push": [vp, vp, i, vp, f, vp],
         "pa_exchange_merge": [vp, vp, vp, i64, vp],
         "pa_decode_step_sharded": [vp, vp, i, i, vp, vp, vp, i64, i64, vp, vp, vp, vp, i64, i64, f, vp],
+        "pa_gather_create": [C.POINTER(vp), i, i, i, i, i, i],
+        "pa_gather_handle": [vp, vp],
+        "pa_gather_connect": [vp, vp],
+        "pa_gather_buffer": [vp, C.POINTER(vp), C.POINTER(C.c_uint64)],
+        "pa_gather_connect_ptrs": [vp, C.POINTER(vp)],
+        "pa_gather_destroy": [vp],
+        "pa_decode_step_gathered": [vp, vp, vp, vp, vp, i64, i64, vp, vp, vp, f, i, vp, C.POINTER(vp)],
+        "pa_gather_wait": [vp, vp, vp, C.POINTER(vp)],
         "lt_launch_flash_attention": [vp],
         "lt_launch_rope_qkv": [vp, vp, vp, vp, vp, vp, vp, vp, i, i, vp],
         "lt_launch_flash_output_layout": [vp, vp, i, vp],

@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libpaged_attention.so")
 
-SOURCES = ["capi.cu", "append_kernel.cu", "decode_kernel.cu", "decode_noalloc.cu", "exchange.cu",
+SOURCES = ["capi.cu", "append_kernel.cu", "decode_kernel.cu", "decode_noalloc.cu", "exchange.cu", "head_gather.cu",
            "prefill_kernel.cu", "compat.cu", "block_pool.cpp"]
 
 NVCC_FLAGS = [

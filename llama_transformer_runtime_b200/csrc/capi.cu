@@ -81,6 +81,13 @@ bool exchange_current(pa_exchange* x, ExchangeMergeParams& m);
 int exchange_rows(const pa_exchange* x);
 int exchange_groups(const pa_exchange* x);
 }  // namespace pa
+struct pa_gather;
+namespace pa {
+bool gather_begin(pa_gather* g);
+bool gather_fill(pa_gather* g, int layer, int n_seqs, int kv_heads, DecodeParams& d);
+cudaError_t gather_wait(pa_gather* g, int* status, cudaStream_t stream, void** rows);
+int gather_layers(const pa_gather* g);
+}  // namespace pa
 
 extern "C" {
 
@@ -365,9 +372,9 @@ static bool can_fuse_append(const pa_pool* p) {
 
 static int decode_impl(pa_pool* p, int layer, const void* q, void* out, int64_t out_stride, float* out_f32,
                        float* lse, float scale, void* stream, pa_exchange* x, bool with_merge = true,
-                       const FusedAppend* fz = nullptr) {
+                       const FusedAppend* fz = nullptr, pa_gather* hg = nullptr, int hg_layer = 0) {
   if (!p || !q) return fail(PA_ERR_INVALID_ARG, "pa_decode: NULL argument");
-  if (!out && !out_f32 && !(x && !with_merge)) return fail(PA_ERR_INVALID_ARG, "pa_decode: no output buffer");
+  if (!out && !out_f32 && !(x && !with_merge) && !hg) return fail(PA_ERR_INVALID_ARG, "pa_decode: no output buffer");
   if (p->device < 0) return fail(PA_ERR_STATE, "pa_decode: host-only pool");
   if (layer < 0 || layer >= p->num_layers) return fail(PA_ERR_INVALID_ARG, "pa_decode: layer %d out of range", layer);
   if (p->batch.empty()) return fail(PA_ERR_STATE, "pa_decode: no active batch (call pa_batch_set)");
@@ -414,6 +421,8 @@ static int decode_impl(pa_pool* p, int layer, const void* q, void* out, int64_t 
     d.q_rot_out = fz->q_rot_out == q ? nullptr : (__nv_bfloat16*)fz->q_rot_out;
     d.pdl = fz->pdl;
   }
+  if (hg && !pa::gather_fill(hg, hg_layer, n_seqs, p->kv_heads, d))
+    return fail(PA_ERR_INVALID_ARG, "pa_decode_step_gathered: the gather was created for another batch, layer count or head count, or is not connected");
   if (!x) {
     PA_CUDA(pa::launch_decode(d, n_seqs, plan.warps, plan.stages, (cudaStream_t)stream));
     return PA_OK;
@@ -465,6 +474,36 @@ int pa_exchange_merge(pa_pool* p, pa_exchange* x, void* out, int64_t out_stride,
 int pa_decode(pa_pool* p, int layer, const void* q, void* out, int64_t out_stride, float* out_f32,
               float* lse, float scale, void* stream) {
   return decode_impl(p, layer, q, out, out_stride, out_f32, lse, scale, stream, nullptr);
+}
+
+int pa_gather_wait(pa_pool* p, pa_gather* g, void* stream, void** rows) {
+  if (!p || !g || p->device < 0) return fail(PA_ERR_INVALID_ARG, "pa_gather_wait: bad argument");
+  DeviceGuard guard(p->device);
+  PA_CUDA(pa::gather_wait(g, p->d_status, (cudaStream_t)stream, rows));
+  return PA_OK;
+}
+
+int pa_decode_step_gathered(pa_pool* p, pa_gather* g, const void* q_in, const void* k_in, const void* v_in,
+                            int64_t q_layer_stride, int64_t kv_layer_stride, const float* cos_table,
+                            const float* sin_table, void* q_rot, float scale, int wait, void* stream,
+                            void** rows) {
+  if (!p || !g || !q_in || !k_in || !v_in || !q_rot || !cos_table || !sin_table)
+    return fail(PA_ERR_INVALID_ARG, "pa_decode_step_gathered: NULL argument");
+  const int layers = pa::gather_layers(g);
+  if (layers > p->num_layers) return fail(PA_ERR_INVALID_ARG, "pa_decode_step_gathered: the pool has fewer layers than the gather");
+  if (!can_fuse_append(p)) return fail(PA_ERR_UNSUPPORTED, "pa_decode_step_gathered: needs one query row and at most one new token per sequence");
+  if (!pa::gather_begin(g)) return fail(PA_ERR_STATE, "pa_decode_step_gathered: gather not connected");
+  for (int l = 0; l < layers; l++) {
+    const __nv_bfloat16* qi = (const __nv_bfloat16*)q_in + (size_t)l * q_layer_stride;
+    const __nv_bfloat16* ki = (const __nv_bfloat16*)k_in + (size_t)l * kv_layer_stride;
+    const __nv_bfloat16* vi = (const __nv_bfloat16*)v_in + (size_t)l * kv_layer_stride;
+    __nv_bfloat16* qr = (__nv_bfloat16*)q_rot + (size_t)l * q_layer_stride;
+    const FusedAppend fz{ki, vi, cos_table, sin_table, qr, l > 0 ? 1 : 0};
+    int r = decode_impl(p, l, qi, nullptr, 0, nullptr, nullptr, scale, stream, nullptr, true, &fz, g, l);
+    if (r != PA_OK) return r;
+  }
+  if (wait) return pa_gather_wait(p, g, stream, rows);
+  return PA_OK;
 }
 
 int pa_decode_step_sharded(pa_pool* p, pa_exchange* x, int layer_begin, int layer_end, const void* q_in,

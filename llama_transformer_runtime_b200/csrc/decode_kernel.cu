@@ -48,6 +48,12 @@ __device__ __forceinline__ void write_row_outputs(const DecodeParams& p, int z, 
   if (p.out_f32) p.out_f32[((size_t)z * q_heads + head) * kHeadDim + d] = v;
   if (p.lse && d == 0)
     p.lse[(size_t)z * q_heads + head] = l > 0.f ? kLn2 * (m + log2f(l)) : -INFINITY;
+  if (p.hs_world > 0) {
+    // KV-head sharding: the all-gather of head outputs is these peer stores
+    const __nv_bfloat16 b = __float2bfloat16_rn(v);
+    const size_t at = (size_t)z * p.hs_stride + p.hs_col0 + head * kHeadDim + d;
+    for (int g = 0; g < p.hs_world; g++) p.hs_rows[g][at] = b;
+  }
   if (p.xchg_world > 0) {
     // sequence-range sharding: push this rank's normalised partial and its LSE
     // into every rank's receive buffer (plain peer stores over NVLink; each
@@ -66,6 +72,15 @@ __device__ __forceinline__ void write_row_outputs(const DecodeParams& p, int z, 
 // system-wide, then publish the step number in every rank's flag for this
 // source rank and head.  Called by all threads of the CTA.
 __device__ __forceinline__ void publish_exchange(const DecodeParams& p, int z, int h) {
+  if (p.hs_world > 0) {
+    // rows of this (sequence, KV head) are stored everywhere: count one arrival
+    // per rank, released at system scope after the CTA's stores
+    __syncthreads();
+    if ((int)threadIdx.x < p.hs_world) {
+      __threadfence_system();
+      asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.hs_counter[threadIdx.x]) : "memory");
+    }
+  }
   if (p.xchg_world <= 0) return;
   // the CTA barrier orders every thread's peer stores before the publishing
   // threads' system-scope fence, which is cumulative: one fence per flag

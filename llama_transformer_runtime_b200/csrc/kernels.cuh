@@ -60,6 +60,14 @@ struct DecodeParams {
   // merge kernel does it
   __nv_bfloat16* xchg_out = nullptr;
   long long xchg_out_stride = 0;
+  // KV-head sharding: this rank's heads are columns [hs_col0, hs_col0 + q_heads*64)
+  // of rows of hs_stride elements; the finished rows are stored into every
+  // rank's row buffer (all-gather by peer stores) and counted in every rank's
+  // arrival counter for (this rank, this layer).  Off when hs_world == 0.
+  __nv_bfloat16* hs_rows[8] = {};
+  unsigned int* hs_counter[8] = {};
+  int hs_world = 0, hs_col0 = 0;
+  long long hs_stride = 0;
   // Fused append (one new token per sequence at most): q is un-rotated, the
   // kernel rotates it and appends k_new/v_new rows (RoPE on K) to the cache.
   // launched with programmatic stream serialization behind the previous

@@ -207,6 +207,56 @@ class Exchange:
             self._h = C.c_void_p()
 
 
+class HeadGather:
+    """Row buffers + peer mappings for KV-head sharded decode (one per rank): the
+    decode kernels of a step store every rank's head outputs into every rank's
+    [layers, n_seqs, 2048] rows; ``step`` returns the device address of this
+    step's rows once all ranks' contributions have arrived."""
+
+    HANDLE_BYTES = 64
+
+    def __init__(self, device: int, rank: int, world: int, n_seqs: int, layers: int, kv_heads: int):
+        self._h = C.c_void_p()
+        self.rank, self.world = rank, world
+        check(lib().pa_gather_create(C.byref(self._h), device, rank, world, n_seqs, layers, kv_heads))
+
+    def handle(self) -> bytes:
+        buf = C.create_string_buffer(self.HANDLE_BYTES)
+        check(lib().pa_gather_handle(self._h, buf))
+        return buf.raw
+
+    def connect(self, handles) -> None:
+        blob = b"".join(handles)
+        check(lib().pa_gather_connect(self._h, C.create_string_buffer(blob, len(blob))))
+
+    def buffer(self):
+        p, b = C.c_void_p(), C.c_uint64()
+        check(lib().pa_gather_buffer(self._h, C.byref(p), C.byref(b)))
+        return p.value, b.value
+
+    def connect_ptrs(self, peer_buffers) -> None:
+        arr = (C.c_void_p * self.world)(*[C.c_void_p(_ptr(b)) for b in peer_buffers])
+        check(lib().pa_gather_connect_ptrs(self._h, arr))
+
+    def step(self, pool: "KVPool", q_in, k_in, v_in, q_layer_stride: int, kv_layer_stride: int, cos, sin,
+             q_rot, scale: float = 0.125, wait: bool = True, stream: int = 0):
+        rows = C.c_void_p()
+        check(lib().pa_decode_step_gathered(pool._h, self._h, _ptr(q_in), _ptr(k_in), _ptr(v_in),
+                                            q_layer_stride, kv_layer_stride, _ptr(cos), _ptr(sin), _ptr(q_rot),
+                                            scale, int(wait), stream, C.byref(rows)))
+        return rows.value
+
+    def wait(self, pool: "KVPool", stream: int = 0):
+        rows = C.c_void_p()
+        check(lib().pa_gather_wait(pool._h, self._h, stream, C.byref(rows)))
+        return rows.value
+
+    def close(self) -> None:
+        if self._h:
+            lib().pa_gather_destroy(self._h)
+            self._h = C.c_void_p()
+
+
 def decode_step_sharded(pool: "KVPool", xchg: Exchange, layer_begin: int, layer_end: int, q_in, k_in,
                         v_in, q_layer_stride: int, kv_layer_stride: int, cos, sin, q_rot, out,
                         out_stride: int, out_layer_stride: int, scale: float = 0.125,

@@ -157,3 +157,89 @@ def test_sharded_step_with_one_rank_equals_plain_step(cuda):
     # the merge of a single partial renormalises through exp/log of the LSE: equal within bf16 rounding
     check_close(orc.bf16_to_f32(outs[1][0]), orc.bf16_to_f32(outs[0][0]), "sharded (1 rank) vs plain step")
     assert np.array_equal(outs[0][1], outs[1][1])
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_head_sharded_step_gathers_full_rows(cuda, world):
+    """KV heads sharded over `world` pools (ranks in this process, one GPU): each
+    rank's decode kernels store its column slice into every rank's row buffer;
+    after all ranks' steps every rank holds the full [layers, seqs, 2048] rows."""
+    rng = np.random.default_rng(110 + world)
+    layers, lens, steps = 2, [70, 300, 16], 2
+    n = len(lens)
+    kvh = 8 // world
+    qh = 4 * kvh
+    max_len = max(lens) + steps
+    cos, sin = orc.build_rope_tables(max_len + 1)
+    cos_d, sin_d = f32_dev(cos), f32_dev(sin)
+    # full caches per layer and sequence (final, i.e. already rotated, values)
+    K = [[orc.randn_bf16(rng, (8, L + steps, 64), 0.5) for L in lens] for _ in range(layers)]
+    V = [[orc.randn_bf16(rng, (8, L + steps, 64), 0.5) for L in lens] for _ in range(layers)]
+    pools, seqs = [], []
+    for r in range(world):
+        prng = np.random.default_rng(5)  # the same allocator decisions on every rank
+        pool = paged.KVPool(layers, 80, kvh, n, 24)
+        pool.set_free_order(prng.permutation(80))
+        ids = []
+        for i, L in enumerate(lens):
+            s = pool.create_seq()
+            pool.reserve(s, L)
+            pool.batch_set([s], [L])
+            for layer in range(layers):
+                kk = K[layer][i][r * kvh:(r + 1) * kvh, :L].transpose(1, 0, 2)
+                vv = V[layer][i][r * kvh:(r + 1) * kvh, :L].transpose(1, 0, 2)
+                pool.append(layer, None, to_dev(kk), to_dev(vv), torch.ones(L, 32, device=DEV),
+                            torch.zeros(L, 32, device=DEV), None)
+            ids.append(s)
+        pools.append(pool)
+        seqs.append(ids)
+    gs = [paged.HeadGather(0, r, world, n, layers, kvh) for r in range(world)]
+    bufs = [g.buffer()[0] for g in gs]
+    for g in gs:
+        g.connect_ptrs(bufs)
+    cur = list(lens)
+    for step in range(steps):
+        q = orc.randn_bf16(rng, (layers, n, 32, 64))
+        k_new = orc.randn_bf16(rng, (layers, n, 8, 64))
+        v_new = orc.randn_bf16(rng, (layers, n, 8, 64))
+        keep = []
+        for r in range(world):
+            for s, L in zip(seqs[r], cur):
+                pools[r].reserve(s, L + 1)
+            pools[r].batch_set(seqs[r])
+            qd = to_dev(q[:, :, r * qh:(r + 1) * qh])
+            kd = to_dev(k_new[:, :, r * kvh:(r + 1) * kvh])
+            vd = to_dev(v_new[:, :, r * kvh:(r + 1) * kvh])
+            qr = torch.zeros_like(qd)
+            keep.append((qd, kd, vd, qr))
+            gs[r].step(pools[r], qd, kd, vd, n * qh * 64, n * kvh * 64, cos_d, sin_d, qr, wait=False)
+        rows = []
+        for r in range(world):  # all ranks have launched their stores: now each may wait
+            ptr = gs[r].wait(pools[r])
+            out = torch.empty(layers, n, 2048, dtype=torch.bfloat16, device=DEV)
+            import ctypes
+            cudart = ctypes.CDLL("libcudart.so.12")
+            torch.cuda.synchronize()
+            assert cudart.cudaMemcpy(ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(ptr),
+                                     ctypes.c_size_t(out.numel() * 2), 3) == 0
+            rows.append(out)
+        torch.cuda.synchronize()
+        for pool in pools:
+            pool.check()
+        for layer in range(layers):
+            for i in range(n):
+                pos = cur[i]
+                K[layer][i][:, pos] = orc.rope(k_new[layer, i][None], cos, sin, pos, 1)[:, 0]
+                V[layer][i][:, pos] = v_new[layer, i]
+                q_rot = orc.rope(q[layer, i][None], cos, sin, pos, 1)
+                O, _ = orc.attention(q_rot, K[layer][i], V[layer][i], pos + 1)
+                for r in range(world):
+                    check_close(orc.bf16_to_f32(to_u16(rows[r][layer, i])), O[:, 0].reshape(-1),
+                                f"step {step} layer {layer} seq {i} rank {r}")
+        for r in range(1, world):
+            assert torch.equal(rows[r], rows[0])
+        cur = [c + 1 for c in cur]
+    for g in gs:
+        g.close()
+    for pool in pools:
+        pool.close()
