@@ -104,13 +104,12 @@ __device__ __forceinline__ void exchange_wait_merge(const DecodeParams& p, int z
   if ((int)threadIdx.x < p.xchg_world) {
     const unsigned int* flag =
         p.xchg_flag[p.xchg_rank] + ((size_t)threadIdx.x * p.xchg_groups + z * p.kv_heads + h);
-    const uint64_t t0 = global_ns();
-    unsigned int spins = 0;
+    SpinDeadline dl;
     for (;;) {
       unsigned int v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
       if ((int)(v - p.xchg_seq) >= 0) break;
-      if ((++spins & 255u) == 0 && global_ns() - t0 > kWaitLimitNs) {
+      if (dl.expired()) {
         *s_flag = 0;
         break;
       }

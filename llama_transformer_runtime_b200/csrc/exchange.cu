@@ -60,11 +60,10 @@ exchange_merge_kernel(pa::ExchangeMergeParams p) {
   // one waiter per flag, all flags in parallel
   for (int f = threadIdx.x; f < p.world * p.groups; f += blockDim.x) {
     const unsigned int* flag = p.flags + f;
-    const unsigned long long t0 = pa::global_ns();
-    unsigned int spins = 0;
+    pa::SpinDeadline dl;
     // flags only grow; a later step's value also means this step has landed
     while ((int)(ld_acquire_sys(flag) - p.seq) < 0) {
-      if ((++spins & 255u) == 0 && pa::global_ns() - t0 > pa::kWaitLimitNs) {
+      if (dl.expired()) {
         s_ok = 0;
         break;
       }

@@ -48,13 +48,12 @@ gather_wait_kernel(const unsigned int* counters, int n_counters, unsigned int ta
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
   for (int i = threadIdx.x; i < n_counters; i += blockDim.x) {
-    const unsigned long long t0 = pa::global_ns();
-    unsigned int spins = 0;
+    pa::SpinDeadline dl;
     for (;;) {
       unsigned int v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(counters + i) : "memory");
       if ((int)(v - target) >= 0) break;
-      if ((++spins & 255u) == 0 && pa::global_ns() - t0 > pa::kWaitLimitNs) {
+      if (dl.expired()) {
         s_ok = 0;
         break;
       }

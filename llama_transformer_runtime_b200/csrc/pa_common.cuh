@@ -80,15 +80,34 @@ __device__ __forceinline__ uint64_t global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+// Deadline of a polling loop.  %globaltimer is a slow register, so it is not
+// read when a wait begins: the first read happens after 256 polls and starts
+// the clock, later reads (every 256 polls) compare against the limit.
+constexpr uint64_t kWaitLimitNs = 1000000000ull;
+struct SpinDeadline {
+  uint32_t spins = 0;
+  uint64_t t0 = 0;
+  // call once per failed poll; true = the limit (~1 s) ran out
+  __device__ __forceinline__ bool expired() {
+    if ((++spins & 255u) != 0) return false;
+    const uint64_t now = global_ns();
+    if (t0 == 0) {
+      t0 = now;
+      return false;
+    }
+    return now - t0 > kWaitLimitNs;
+  }
+  __device__ __forceinline__ void restart() {
+    spins = 0;
+    t0 = 0;
+  }
+};
 // Wait for the phase with the given parity, at most ~1 s.  Returns false when
 // the limit ran out (the caller records it and leaves).
-constexpr uint64_t kWaitLimitNs = 1000000000ull;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  if (mbar_test(bar, parity)) return true;
-  const uint64_t t0 = global_ns();
-  uint32_t spins = 0;
+  SpinDeadline dl;
   while (!mbar_test(bar, parity)) {
-    if ((++spins & 63u) == 0 && global_ns() - t0 > kWaitLimitNs) return false;
+    if (dl.expired()) return false;
   }
   return true;
 }

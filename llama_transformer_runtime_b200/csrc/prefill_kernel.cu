@@ -13,18 +13,20 @@
 // tiles of the cache up to the diagonal.
 //   warp 8      loader: per tile 8 K tiles + 8 V tiles (2 KiB each, one cache
 //               block each) fetched through the block table with cp.async.bulk
-//               into a 2-stage ring.  The cache stores every tile already in
+//               into a 3-stage ring.  The cache stores every tile already in
 //               the 128-byte swizzle, so the copies land as canonical UMMA
 //               operands: K as K-major, V as MN-major.
 //   warp 9      issues the MMAs: S = Q K^T (M128 N128 K64 -> TMEM columns
-//               0..127) and O += P V (M128 N64 K128 -> TMEM columns 128..191);
+//               0..127) and O += P V (M128 N64 K128 -> TMEM columns 128..191, P
+//               read from TMEM columns 192..255); one elected lane issues them;
 //               completion is signalled to the other warps with tcgen05.commit.
 //   warps 0-7   softmax: S is read with tcgen05.ld in the 16x256b layout (the
 //               mma accumulator layout: a row is spread over the 4 threads of
 //               a quad, 16 TMEM lanes per warp), so row maxima and sums are
 //               quad shuffles and each thread carries only 64 scores; P (bf16)
-//               goes to shared memory with stmatrix in K-major swizzled layout
-//               for the second MMA; O is rescaled in TMEM only when a row
+//               goes back to tensor memory (tcgen05.st 16x128b, two scores per
+//               column) as the A operand of the second MMA, so it never
+//               touches shared memory; O is rescaled in TMEM only when a row
 //               maximum moved by more than 2^8; finally O / sum is written as
 //               bf16 straight into the [tokens, heads*64] layout.
 // Every wait is bounded; a wait that runs out raises the CTA's abort flag,
@@ -38,15 +40,13 @@ namespace {
 
 constexpr int kBM = 128;            // query rows per CTA
 constexpr int kBN = 128;            // keys per tile
-constexpr int kStagesKV = 2;
+constexpr int kStagesKV = 3;
 constexpr int kQBytes = kBM * 128;          // 16 KiB
 constexpr int kKBytes = kBN * 128;          // 16 KiB
 constexpr int kVBytes = kBN * 128;          // 16 KiB
-constexpr int kPBytes = kBM * kBN * 2;      // 32 KiB (two 64-key halves)
 constexpr int kOffQ = 0;
 constexpr int kOffKV = kOffQ + kQBytes;
-constexpr int kOffP = kOffKV + kStagesKV * (kKBytes + kVBytes);
-constexpr int kOffBar = kOffP + kPBytes;
+constexpr int kOffBar = kOffKV + kStagesKV * (kKBytes + kVBytes);
 constexpr int kNumBars = 5 + 4 * kStagesKV;  // K and V halves of a stage fill and free separately
 constexpr int kOffMisc = kOffBar + kNumBars * 8;  // tensor-memory base address, abort flag
 constexpr int kPrefillUsed = kOffMisc + 16;
@@ -59,8 +59,9 @@ static_assert(2 * (kPrefillSmem + 1024) <= 228 * 1024, "two CTAs per SM");
 constexpr int kSoftmaxThreads = 256;  // warps 0..7
 constexpr int kLoadWarp = 8, kMmaWarp = 9;
 constexpr int kPrefillThreads = 320;
-constexpr uint32_t kTmemCols = 256;  // S: 128 columns, O: 64 columns, power of two
-constexpr uint32_t kColS = 0, kColO = 128;
+// S: 128 fp32 columns, O: 64 fp32 columns, P: 128 bf16 = 64 columns; power of two
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kColS = 0, kColO = 128, kColP = 192;
 constexpr float kRescaleThreshold = 8.0f;  // log2: rescale O only if a row max moved by > 2^8
 
 // ---- tcgen05 wrappers ---------------------------------------------------------
@@ -75,6 +76,16 @@ __device__ __forceinline__ void tmem_relinquish() {
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
                : "memory");
+}
+// One lane of a converged warp.  The MMA issue is guarded with this rather than
+// with a lane test: the compiler then knows a single thread runs the block and
+// keeps descriptors in uniform registers instead of looping over active lanes.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
 }
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -93,6 +104,15 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem desc]: A = 128 lanes x K bf16, two per 32-bit column
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                        uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -152,15 +172,14 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
   return r;
 }
 
-// exp2 of two values without the special-function unit (which is the busiest
-// pipe of this kernel): n = round(x) through the 1.5*2^23 trick, 2^(x-n) by a
-// degree-3 polynomial on [-0.5, 0.5] (relative error 7.5e-5, far below the bf16
-// rounding of P), the exponent added into the bits.  Inputs are clamped to
-// -126, so a masked score (-inf) gives 2^-126 instead of an exact zero.
-// Measured on B200 with 1 group in 4 on this path: 40.37 us per 2048-token layer
-// against 40.34 us without — the kernel is not limited by the special-function
-// pipe (52 % busy), so the path is compiled in but switched off.
-constexpr int kPolyEvery = 0;  // n > 0: 1 in n column groups (n = 1, 2 or 4) takes this path
+// exp2 of two values without the special-function unit (the busiest pipe of
+// this kernel): n = round(x) through the 1.5*2^23 trick, 2^(x-n) by a degree-3
+// polynomial on [-0.5, 0.5] (relative error 7.5e-5, far below the bf16 rounding
+// of P), the exponent added into the bits.  Inputs are clamped to -126, so a
+// masked score (-inf) gives 2^-126 instead of an exact zero.
+// Measured on B200, 2048-token causal layer: 37.9 us with 1 group in 4 on this
+// path, 39.3 us with 1 in 2, 40.7 us with none.
+constexpr int kPolyEvery = 4;  // n > 0: 1 in n column groups (n = 1, 2 or 4) takes this path
 __device__ __forceinline__ void exp2_poly_x2(float x0, float x1, float& p0, float& p1) {
   const uint64_t x = pack_f32x2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
   const uint64_t magic = pack_f32x2(12582912.f, 12582912.f);
@@ -205,12 +224,20 @@ __device__ __forceinline__ void tmem_st_16x256b_x8(uint32_t taddr, const uint32_
         "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
-// Four 8x8 bf16 matrices from accumulator-layout registers to shared memory;
-// lane l supplies the address of row l%8 of matrix l/8.
-__device__ __forceinline__ void stsm_x4(uint32_t addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
-  asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(r0),
-               "r"(r1), "r"(r2), "r"(r3)
-               : "memory");
+// 16 lanes x 64 columns: thread t gives, for column group j of 4, register 2j =
+// (lane t/4, column 4j + t%4) and 2j+1 = the same column of lane t/4 + 8.  With
+// two bf16 per column this is the accumulator layout of 128 scores packed in pairs.
+__device__ __forceinline__ void tmem_st_16x128b_x16(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x128b.x16.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+        "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
+        "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]),
+        "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
 }
 
 // Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes
@@ -234,16 +261,12 @@ __host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, bool b_mn_major)
 
 // mbarrier wait that also gives up when another warp raised the abort flag.
 __device__ __forceinline__ bool wait_one(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_test(bar, parity)) return true;
-  const uint64_t t0 = global_ns();
-  uint32_t spins = 0;
+  SpinDeadline dl;
   while (!mbar_test(bar, parity)) {
-    if ((++spins & 31u) == 0) {
-      if (*abort_flag) return false;
-      if (global_ns() - t0 > kWaitLimitNs) {
-        *abort_flag = 1;
-        return false;
-      }
+    if ((dl.spins & 31u) == 31u && *abort_flag) return false;
+    if (dl.expired()) {
+      *abort_flag = 1;
+      return false;
     }
   }
   return true;
@@ -264,7 +287,7 @@ prefill_kernel(PrefillParams p) {
     return;
   }
   unsigned char* sm = smem_raw;
-  const uint32_t sQ = base + kOffQ, sKV = base + kOffKV, sP = base + kOffP;
+  const uint32_t sQ = base + kOffQ, sKV = base + kOffKV;
   const uint32_t bar0 = base + kOffBar;
   const uint32_t bar_q = bar0, bar_s = bar0 + 8, bar_p = bar0 + 16, bar_pv = bar0 + 24;
   const uint32_t bar_sfree = bar0 + 32;
@@ -292,11 +315,13 @@ prefill_kernel(PrefillParams p) {
 
   if (tid == 0) {
     *abort_flag = 0;
-    mbar_init(bar_q, kSoftmaxThreads);
+    // the softmax warps arrive once per warp (lane 0 after a warp barrier): 256
+    // arrivals on one shared-memory word serialise and cost more than the tile's math
+    mbar_init(bar_q, kSoftmaxThreads / 32);
     mbar_init(bar_s, 1);
-    mbar_init(bar_p, kSoftmaxThreads);
+    mbar_init(bar_p, kSoftmaxThreads / 32);
     mbar_init(bar_pv, 1);
-    mbar_init(bar_sfree, kSoftmaxThreads);
+    mbar_init(bar_sfree, kSoftmaxThreads / 32);
     for (int s = 0; s < kStagesKV; s++) {
       mbar_init(bar_kfull + 8 * s, 1);
       mbar_init(bar_kempty + 8 * s, 1);
@@ -334,8 +359,7 @@ prefill_kernel(PrefillParams p) {
     };
     int k_next = 0, v_next = 0;
     int blk_k = block_of(0), blk_v = blk_k;
-    uint64_t t0 = global_ns();
-    uint32_t spins = 0;
+    SpinDeadline dl;
     bool ok = true;
     while (ok && (k_next < n_tiles || v_next < n_tiles)) {
       bool progressed = false;
@@ -366,14 +390,17 @@ prefill_kernel(PrefillParams p) {
         }
       }
       if (progressed) {
-        t0 = global_ns();
-      } else if ((++spins & 31u) == 0) {
-        bool stop = *abort_flag != 0;
-        if (!stop && global_ns() - t0 > kWaitLimitNs) {  // nothing freed for a second
-          *abort_flag = 1;
-          stop = true;
+        dl.restart();
+      } else {
+        const bool out_of_time = dl.expired();  // nothing freed for a second
+        if ((dl.spins & 31u) == 0) {
+          bool stop = *abort_flag != 0;
+          if (!stop && out_of_time) {
+            *abort_flag = 1;
+            stop = true;
+          }
+          if (__any_sync(0xffffffffu, stop)) ok = false;
         }
-        if (__any_sync(0xffffffffu, stop)) ok = false;
       }
     }
   } else if (warp == kMmaWarp) {
@@ -385,7 +412,7 @@ prefill_kernel(PrefillParams p) {
       const int st = kt % kStagesKV;
       if (!wait_or_abort(bar_kfull + 8 * st, (uint32_t)((kt / kStagesKV) & 1), abort_flag)) return false;
       tc_fence_after();
-      if (lane == 0) {
+      if (elect_one()) {
         const uint32_t sK = sKV + st * (kKBytes + kVBytes);
 #pragma unroll
         for (int ks = 0; ks < kHeadDim / 16; ks++)
@@ -408,12 +435,12 @@ prefill_kernel(PrefillParams p) {
       if (!wait_or_abort(bar_p, (uint32_t)(kt & 1), abort_flag)) break;
       if (!wait_or_abort(bar_vfull + 8 * st, (uint32_t)((kt / kStagesKV) & 1), abort_flag)) break;
       tc_fence_after();
-      if (lane == 0) {
+      if (elect_one()) {
         const uint32_t sV = sKV + st * (kKBytes + kVBytes) + kKBytes;
 #pragma unroll
         for (int kk = 0; kk < kBN / 16; kk++)
-          umma_ss(tmem + kColO, smem_desc_sw128(sP + (kk >> 2) * (kBM * 128) + (kk & 3) * 32),
-                  smem_desc_sw128(sV + kk * kTileBytes), kIdescPV, (kt > 0 || kk > 0) ? 1u : 0u);
+          umma_ts(tmem + kColO, tmem + kColP + kk * 8, smem_desc_sw128(sV + kk * kTileBytes), kIdescPV,
+                  (kt > 0 || kk > 0) ? 1u : 0u);
         tc_commit(bar_pv);
         tc_commit(bar_vempty + 8 * st);
       }
@@ -448,15 +475,9 @@ prefill_kernel(PrefillParams p) {
       for (int c = 0; c < 4; c++)
         *reinterpret_cast<uint4*>(sm + kOffQ + r * 128 + (((c0 + c) ^ (r & 7)) << 4)) = v[c];
       fence_proxy_async_smem();
-      mbar_arrive(bar_q);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_q);
     }
-
-    // stmatrix addresses of this thread: matrix m = lane/8 of each x4 store is
-    // (rows first_row + 8*(m&1) .., column group g + (m>>1)), this thread gives its row lane%8
-    const int st_row = first_row + ((lane >> 3) & 1) * 8 + (lane & 7);
-    const int st_grp = lane >> 4;
-    const uint32_t st_base = sP + st_row * 128;
-    const int st_swz = st_row & 7;
 
     const int qposA = pos0 + rA, qposB = pos0 + rB;
     float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
@@ -474,7 +495,8 @@ prefill_kernel(PrefillParams p) {
       tmem_ld_16x256b_x8(tmem + lane_base + kColS + 64, s[1]);
       tmem_wait_ld();
       tc_fence_before();
-      mbar_arrive(bar_sfree);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_sfree);
 
       if (need_mask) {
         const int limA = (p.causal ? min(qposA, e.kv_len - 1) : e.kv_len - 1) - key0;  // keys <= lim are visible
@@ -524,7 +546,7 @@ prefill_kernel(PrefillParams p) {
       const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
       const uint64_t negA2 = pack_f32x2(-mA, -mA), negB2 = pack_f32x2(-mB, -mB);
       uint64_t laccA = 0ull, laccB = 0ull;
-      uint32_t pkA[16], pkB[16];
+      uint32_t pk[32];  // register 2j: row A, 2j+1: row B of packed column 4j + lane%4
 #pragma unroll
       for (int hf = 0; hf < 2; hf++)
 #pragma unroll
@@ -547,8 +569,8 @@ prefill_kernel(PrefillParams p) {
           }
           laccA = add_f32x2(laccA, pack_f32x2(p0, p1));
           laccB = add_f32x2(laccB, pack_f32x2(p2, p3));
-          pkA[hf * 8 + i] = pack_bf16(p0, p1);
-          pkB[hf * 8 + i] = pack_bf16(p2, p3);
+          pk[2 * (hf * 8 + i)] = pack_bf16(p0, p1);
+          pk[2 * (hf * 8 + i) + 1] = pack_bf16(p2, p3);
         }
 
       // P of the previous tile must have been consumed, O must be quiescent
@@ -578,16 +600,12 @@ prefill_kernel(PrefillParams p) {
         lB = lB * corrB + (b0 + b1);
       }
 
-      // P -> shared memory (K-major, swizzled), four 8x8 matrices per stmatrix
-#pragma unroll
-      for (int g = 0; g < 16; g += 2) {
-        const int grp = g + st_grp;
-        stsm_x4(st_base + (grp >> 3) * (kBM * 128) + (((grp & 7) ^ st_swz) << 4), pkA[g], pkB[g], pkA[g + 1],
-                pkB[g + 1]);
-      }
-      fence_proxy_async_smem();
+      // P -> tensor memory, the A operand of the second MMA
+      tmem_st_16x128b_x16(tmem + lane_base + kColP, pk);
+      tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar_p);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p);
     }
 
     // epilogue: O / sum -> bf16, [tokens, heads*64] layout (or the caller's strides)
