@@ -329,11 +329,17 @@ static DecodePlan pick_plan(const pa_pool* p) {
   }
   if (plan.chunk_blocks == 0) {
     if (pairs <= sms) {
-      // smallest chunk for which every CTA is resident at once
+      // Smallest chunk for which every CTA is resident at once.  One SM per
+      // (sequence, head) pair stays free: the CTA that combines a pair outlives
+      // the others by the combine and the exchange, and in a multi-layer step
+      // the next layer's CTAs (programmatic dependent launch) would otherwise
+      // queue behind it — the whole step then advances at stream + combine
+      // instead of at the stream rate.
+      const int budget = pairs * 4 <= sms ? sms - (int)pairs : sms;
       int lo = 1, hi = p->max_kv_blocks > 1 ? p->max_kv_blocks : 1;
       while (lo < hi) {
         const int mid = (lo + hi) / 2;
-        if (plan_ctas(p, mid) <= sms) hi = mid; else lo = mid + 1;
+        if (plan_ctas(p, mid) <= budget) hi = mid; else lo = mid + 1;
       }
       plan.chunk_blocks = lo;
     } else {

@@ -38,6 +38,16 @@ struct DecodeSmem {
   static constexpr int kBytes = 128 + kTiles + kBars + kMergeFloats * 4 + 16;
 };
 
+// One 8-byte word {value, step number}, stored and loaded whole.
+__device__ __forceinline__ void st_word_sys(unsigned long long* p, float v, unsigned int seq) {
+  asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(seq) : "memory");
+}
+__device__ __forceinline__ void ld_word_sys(const unsigned long long* p, float& v, unsigned int& seq) {
+  unsigned int a;
+  asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(a), "=r"(seq) : "l"(p) : "memory");
+  v = __uint_as_float(a);
+}
+
 __device__ __forceinline__ void write_row_outputs(const DecodeParams& p, int z, int h, int r, int d,
                                                   float o, float m, float l) {
   const int q_heads = p.kv_heads * kGroup;
@@ -61,9 +71,17 @@ __device__ __forceinline__ void write_row_outputs(const DecodeParams& p, int z, 
     const int row = z * q_heads + head;
     const size_t at = ((size_t)(p.xchg_slot * p.xchg_world + p.xchg_rank) * p.xchg_rows + row) * kXchgRowFloats;
     const float lse = l > 0.f ? kLn2 * (m + log2f(l)) : -INFINITY;
-    for (int g = 0; g < p.xchg_world; g++) {
-      p.xchg_peer[g][at + d] = v;
-      if (d == 0) p.xchg_peer[g][at + kHeadDim] = lse;
+    if (p.xchg_out) {
+      // merged in this kernel: {value, step number} words, valid on arrival
+      for (int g = 0; g < p.xchg_world; g++) {
+        st_word_sys(p.xchg_ll[g] + at + d, v, p.xchg_seq);
+        if (d == 0) st_word_sys(p.xchg_ll[g] + at + kHeadDim, lse, p.xchg_seq);
+      }
+    } else {
+      for (int g = 0; g < p.xchg_world; g++) {
+        p.xchg_peer[g][at + d] = v;
+        if (d == 0) p.xchg_peer[g][at + kHeadDim] = lse;
+      }
     }
   }
 }
@@ -81,7 +99,7 @@ __device__ __forceinline__ void publish_exchange(const DecodeParams& p, int z, i
       asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.hs_counter[threadIdx.x]) : "memory");
     }
   }
-  if (p.xchg_world <= 0) return;
+  if (p.xchg_world <= 0 || p.xchg_out) return;  // words carry their own step number
   // the CTA barrier orders every thread's peer stores before the publishing
   // threads' system-scope fence, which is cumulative: one fence per flag
   // instead of one per thread
@@ -101,46 +119,54 @@ __device__ __forceinline__ void exchange_wait_merge(const DecodeParams& p, int z
   if (p.xchg_world <= 0 || !p.xchg_out) return;
   if (threadIdx.x == 0) *s_flag = 1;
   __syncthreads();
-  if ((int)threadIdx.x < p.xchg_world) {
-    const unsigned int* flag =
-        p.xchg_flag[p.xchg_rank] + ((size_t)threadIdx.x * p.xchg_groups + z * p.kv_heads + h);
-    SpinDeadline dl;
-    for (;;) {
-      unsigned int v;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-      if ((int)(v - p.xchg_seq) >= 0) break;
-      if (dl.expired()) {
-        *s_flag = 0;
-        break;
-      }
-    }
-  }
-  __syncthreads();
-  if (!*s_flag) {
-    if (threadIdx.x == 0) atomicExch(p.status, kStatusTimeout);
-    return;
-  }
   const int q_heads = p.kv_heads * kGroup;
-  const float* base = p.xchg_peer[p.xchg_rank] + (size_t)p.xchg_slot * p.xchg_world * p.xchg_rows * kXchgRowFloats;
+  const unsigned long long* base =
+      p.xchg_ll[p.xchg_rank] + (size_t)p.xchg_slot * p.xchg_world * p.xchg_rows * kXchgRowFloats;
   for (int idx = threadIdx.x; idx < kGroup * kHeadDim; idx += blockDim.x) {
     const int r = idx >> 6, d = idx & 63;
     const int head = h * kGroup + r;
     const int row = z * q_heads + head;
+    // every rank's LSE and value d of this row, each polled until it carries this step
+    float lse[8], val[8];
+    bool ok = true;
+#pragma unroll
+    for (int g = 0; g < 8; g++) {
+      if (g >= p.xchg_world || !ok) continue;
+      const unsigned long long* rowp = base + ((size_t)g * p.xchg_rows + row) * kXchgRowFloats;
+      SpinDeadline dl;
+      unsigned int s0 = 0, s1 = 0;
+      for (;;) {
+        if (s0 != p.xchg_seq) ld_word_sys(rowp + kHeadDim, lse[g], s0);
+        if (s1 != p.xchg_seq) ld_word_sys(rowp + d, val[g], s1);
+        if (s0 == p.xchg_seq && s1 == p.xchg_seq) break;
+        if (dl.expired()) {
+          ok = false;
+          break;
+        }
+      }
+    }
+    if (!ok) {
+      *s_flag = 0;
+      continue;
+    }
     float M = -INFINITY;
-    for (int g = 0; g < p.xchg_world; g++)
-      M = fmaxf(M, __ldcg(base + ((size_t)g * p.xchg_rows + row) * kXchgRowFloats + kHeadDim));
+#pragma unroll
+    for (int g = 0; g < 8; g++)
+      if (g < p.xchg_world) M = fmaxf(M, lse[g]);
     float L = 0.f, O = 0.f;
     if (M > -INFINITY) {
-      for (int g = 0; g < p.xchg_world; g++) {
-        const float* rowp = base + ((size_t)g * p.xchg_rows + row) * kXchgRowFloats;
-        const float lse = __ldcg(rowp + kHeadDim);
-        const float w = lse == -INFINITY ? 0.f : __expf(lse - M);
+#pragma unroll
+      for (int g = 0; g < 8; g++) {
+        if (g >= p.xchg_world) continue;
+        const float w = lse[g] == -INFINITY ? 0.f : __expf(lse[g] - M);
         L += w;
-        O += w * __ldcg(rowp + d);
+        O += w * val[g];
       }
     }
     p.xchg_out[(size_t)z * p.xchg_out_stride + head * kHeadDim + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
   }
+  __syncthreads();
+  if (!*s_flag && threadIdx.x == 0) atomicExch(p.status, kStatusTimeout);
 }
 
 template <int WARPS, int STAGES>

@@ -6,10 +6,17 @@
 // Instead of a library all-gather (a ~8 KiB message, where launch and protocol
 // latency dominate), the decode kernel's combine epilogue stores this rank's
 // partial (normalised O, LSE) straight into every rank's receive buffer with
-// plain peer stores over NVLink and then publishes the step number in a flag
-// (st.release.sys).  A small kernel on each rank waits for the flags of all
-// ranks (ld.acquire.sys, bounded to about a second, then PA_ERR_TIMEOUT in the
-// pool's status word) and merges from its OWN memory.  Nothing is ever loaded
+// plain peer stores over NVLink.  Two protocols share the buffer:
+//  * merge inside the decode kernel (pa_decode_step_sharded): every value
+//    travels as one 8-byte word {value, step number}; the combining CTA of a
+//    (sequence, KV head) polls its own memory until each word it needs carries
+//    the step number (bounded to about a second, then PA_ERR_TIMEOUT in the
+//    pool's status word) and merges.  No fence and no flag: a system-scope
+//    fence in that CTA cost about 7 us while the next layer was streaming.
+//  * push + separate merge kernel (pa_decode_push, pa_exchange_merge): fp32
+//    rows, then the step number in a flag (st.release.sys); the merge kernel
+//    waits for the flags of all ranks (ld.acquire.sys, bounded likewise).
+// Either way a rank reads only its OWN memory.  Nothing is ever loaded
 // from a peer, nothing is multicast.  Two slots alternate by step: a rank can
 // run at most one step ahead of the slowest one, because its own merge needs
 // everybody's partial.
@@ -29,7 +36,7 @@ void set_last_error(const char* msg);
 
 struct pa_exchange {
   int device = 0, rank = 0, world = 1, rows = 0, groups = 0;
-  size_t data_bytes = 0, bytes = 0;
+  size_t data_bytes = 0, ll_offset = 0, bytes = 0;
   unsigned char* local = nullptr;      // receive buffer of this rank
   unsigned char* peer[8] = {};         // every rank's buffer as mapped here (peer[rank] == local)
   bool opened[8] = {};
@@ -113,6 +120,7 @@ bool exchange_fill(pa_exchange* x, DecodeParams& d, ExchangeMergeParams& m) {
   for (int g = 0; g < x->world; g++) {
     d.xchg_peer[g] = reinterpret_cast<float*>(x->peer[g]);
     d.xchg_flag[g] = reinterpret_cast<unsigned int*>(x->peer[g] + x->data_bytes);
+    d.xchg_ll[g] = reinterpret_cast<unsigned long long*>(x->peer[g] + x->ll_offset);
   }
   d.xchg_world = x->world;
   d.xchg_rank = x->rank;
@@ -160,7 +168,10 @@ int pa_exchange_create(pa_exchange** out, int device, int rank, int world, int n
   x->rows = n_seqs * kv_heads * pa::kGroup;
   x->groups = n_seqs * kv_heads;
   x->data_bytes = ((size_t)2 * world * x->rows * pa::kXchgRowFloats * sizeof(float) + 255) & ~(size_t)255;
-  x->bytes = x->data_bytes + (((size_t)world * x->groups * sizeof(unsigned int) + 255) & ~(size_t)255);
+  // [data | flags | words]: the first two serve the push + separate merge
+  // kernel, the third the merge inside the decode kernel
+  x->ll_offset = x->data_bytes + (((size_t)world * x->groups * sizeof(unsigned int) + 255) & ~(size_t)255);
+  x->bytes = x->ll_offset + (size_t)2 * world * x->rows * pa::kXchgRowFloats * sizeof(unsigned long long);
   int prev = -1;
   cudaGetDevice(&prev);
   cudaError_t e = cudaSetDevice(device);

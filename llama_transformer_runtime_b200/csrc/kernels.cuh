@@ -60,6 +60,10 @@ struct DecodeParams {
   // merge kernel does it
   __nv_bfloat16* xchg_out = nullptr;
   long long xchg_out_stride = 0;
+  // In-kernel merge: partials travel as 8-byte words {value, step number}
+  // (xchg_ll[g] = rank g's word region, [2 slots][world][rows][65] words), so a
+  // word is valid as soon as it carries this step's number: no fence, no flag.
+  unsigned long long* xchg_ll[8] = {};
   // KV-head sharding: this rank's heads are columns [hs_col0, hs_col0 + q_heads*64)
   // of rows of hs_stride elements; the finished rows are stored into every
   // rank's row buffer (all-gather by peer stores) and counted in every rank's
