@@ -275,6 +275,10 @@ int pa_pool_check(pa_pool* pool, void* stream);
 
 /* Tuning knobs (0 keeps the built-in heuristic): blocks per split-KV chunk. */
 int pa_pool_set_decode_chunk_blocks(pa_pool* pool, int chunk_blocks);
+/* pa_decode_step and pa_decode_step_sharded run the layers of a step as one
+ * cooperative launch when the batch allows it (enable != 0, the default);
+ * enable == 0 keeps one kernel per layer.  No counterpart in the reference. */
+int pa_pool_set_step_kernel(pa_pool* pool, int enable);
 /* Warps per decode CTA and 4 KiB ring stages per warp (built shapes only). */
 int pa_pool_set_decode_shape(pa_pool* pool, int warps, int stages);
 

@@ -71,6 +71,7 @@ struct pa_pool {
   int decode_warps = 0, decode_stages = 0;  // 0: chosen per batch
   int sm_count = 0;
   int rope_variant = 1;
+  bool no_step_kernel = false;  // pa_pool_set_step_kernel(pool, 0): one kernel per layer
   pa_pool(int nb, int ms, int mb) : host(nb, ms, mb) {}
 };
 
@@ -78,6 +79,8 @@ struct pa_exchange;
 namespace pa {
 bool exchange_fill(pa_exchange* x, DecodeParams& d, ExchangeMergeParams& m);
 bool exchange_current(pa_exchange* x, ExchangeMergeParams& m);
+void exchange_advance(pa_exchange* x, int steps);
+void exchange_unfill(pa_exchange* x);
 int exchange_rows(const pa_exchange* x);
 int exchange_groups(const pa_exchange* x);
 }  // namespace pa
@@ -120,7 +123,7 @@ int pa_pool_create(pa_pool** out, int device, int num_layers, int num_blocks, in
     alloc((void**)&p->d_batch, (size_t)max_seqs * sizeof(pa::BatchEntry));
     alloc((void**)&p->ws_acc, (size_t)kWsItems * pa::decode_ws_acc_floats_per_item() * sizeof(float));
     alloc((void**)&p->ws_ml, (size_t)kWsItems * 2 * pa::kGroup * sizeof(float));
-    alloc((void**)&p->ws_count, (size_t)max_seqs * kv_heads * sizeof(unsigned int));
+    alloc((void**)&p->ws_count, (size_t)max_seqs * kv_heads * pa::kMaxStepLayers * sizeof(unsigned int));
     alloc((void**)&p->d_status, sizeof(int));
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&p->sm_count, cudaDevAttrMultiProcessorCount, device);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
@@ -378,7 +381,8 @@ static bool can_fuse_append(const pa_pool* p) {
 
 static int decode_impl(pa_pool* p, int layer, const void* q, void* out, int64_t out_stride, float* out_f32,
                        float* lse, float scale, void* stream, pa_exchange* x, bool with_merge = true,
-                       const FusedAppend* fz = nullptr, pa_gather* hg = nullptr, int hg_layer = 0) {
+                       const FusedAppend* fz = nullptr, pa_gather* hg = nullptr, int hg_layer = 0,
+                       pa::DecodeParams* capture = nullptr, DecodePlan* plan_out = nullptr) {
   if (!p || !q) return fail(PA_ERR_INVALID_ARG, "pa_decode: NULL argument");
   if (!out && !out_f32 && !(x && !with_merge) && !hg) return fail(PA_ERR_INVALID_ARG, "pa_decode: no output buffer");
   if (p->device < 0) return fail(PA_ERR_STATE, "pa_decode: host-only pool");
@@ -429,7 +433,12 @@ static int decode_impl(pa_pool* p, int layer, const void* q, void* out, int64_t 
   }
   if (hg && !pa::gather_fill(hg, hg_layer, n_seqs, p->kv_heads, d))
     return fail(PA_ERR_INVALID_ARG, "pa_decode_step_gathered: the gather was created for another batch, layer count or head count, or is not connected");
+  if (plan_out) *plan_out = plan;
   if (!x) {
+    if (capture) {
+      *capture = d;
+      return PA_OK;
+    }
     PA_CUDA(pa::launch_decode(d, n_seqs, plan.warps, plan.stages, (cudaStream_t)stream));
     return PA_OK;
   }
@@ -452,8 +461,62 @@ static int decode_impl(pa_pool* p, int layer, const void* q, void* out, int64_t 
     d.xchg_out = (__nv_bfloat16*)out;
     d.xchg_out_stride = out_stride;
   }
+  if (capture) {
+    *capture = d;
+    return PA_OK;
+  }
   PA_CUDA(pa::launch_decode(d, n_seqs, plan.warps, plan.stages, (cudaStream_t)stream));
   return PA_OK;
+}
+
+// The layers [layer_begin, layer_end) of a fused decode step as ONE cooperative
+// launch (decode_step_kernel), when the batch fits: every CTA resident at once
+// (streaming CTAs + one combining CTA per (sequence, head) <= SMs), a workspace
+// slice per layer.  Returns 1 when it launched, 0 when the caller should run
+// the layers one kernel each, < 0 on error.
+static int try_step_launch(pa_pool* p, pa_exchange* x, int layer_begin, int layer_end, const void* q_in,
+                           const void* k_in, const void* v_in, int64_t q_layer_stride, int64_t kv_layer_stride,
+                           const float* cos_table, const float* sin_table, void* q_rot, void* out,
+                           int64_t out_stride, int64_t out_layer_stride, float* lse, float scale, void* stream) {
+  const int layers = layer_end - layer_begin;
+  if (layers < 2 || layers > pa::kMaxStepLayers || p->device < 0 || p->batch.empty() || p->no_step_kernel) return 0;
+  const int n_seqs = (int)p->batch.size();
+  const int sms = p->sm_count > 0 ? p->sm_count : 148;
+  const long long pairs = (long long)n_seqs * p->kv_heads;
+  if (pairs * 4 > sms) return 0;
+  pa::DecodeStepParams sp;
+  DecodePlan plan{};
+  const FusedAppend fz{k_in, v_in, cos_table, sin_table, q_rot, 0};
+  int r = decode_impl(p, layer_begin, q_in, out, out_stride, nullptr, lse, scale, stream, x, true, &fz, nullptr, 0,
+                      &sp.base, &plan);
+  if (r != PA_OK) return r < 0 ? r : -r;
+  if (!((plan.warps == 8 && (plan.stages == 4 || plan.stages == 3)) || (plan.warps == 4 && plan.stages == 4)) ||
+      sp.base.max_chunks < 1) {
+    if (x) pa::exchange_unfill(x);
+    return 0;
+  }
+  sp.layers = layers;
+  sp.n_seqs = n_seqs;
+  sp.q_layer_stride = q_layer_stride;
+  sp.kv_layer_stride = kv_layer_stride;
+  sp.out_layer_stride = out_layer_stride;
+  sp.lse_layer_stride = (long long)n_seqs * p->kv_heads * pa::kGroup;
+  sp.layer_bytes = p->layer_bytes;
+  sp.ws_layer_items = n_seqs * p->kv_heads * sp.base.max_chunks;
+  // one CTA per SM (the ring of an 8-warp CTA fills most of an SM's shared memory)
+  if (pa::decode_step_ctas(sp) > sms || (long long)sp.ws_layer_items * layers > kWsItems) {
+    if (x) pa::exchange_unfill(x);
+    return 0;
+  }
+  sp.base.pdl = 0;
+  if (x) pa::exchange_advance(x, layers - 1);  // layer l is exchange step seq0 + l
+  DeviceGuard g(p->device);
+  cudaError_t e = pa::launch_decode_step(sp, plan.warps, plan.stages, (cudaStream_t)stream);
+  if (e != cudaSuccess) {
+    fail(PA_ERR_CUDA, "decode step launch: %s", cudaGetErrorString(e));
+    return -PA_ERR_CUDA;
+  }
+  return 1;
 }
 
 int pa_decode_push(pa_pool* p, pa_exchange* x, int layer, const void* q, float scale, void* stream) {
@@ -524,6 +587,12 @@ int pa_decode_step_sharded(pa_pool* p, pa_exchange* x, int layer_begin, int laye
   bool fuse = cos_table && sin_table && can_fuse_append(p);
   for (const auto& e : p->batch)
     if (e.n_new > 0 && (!k_in || !v_in)) return fail(PA_ERR_INVALID_ARG, "decode step: the batch appends tokens but k_in/v_in is NULL");
+  if (fuse && q_rot != q_in) {
+    const int t = try_step_launch(p, x, layer_begin, layer_end, q_in, k_in, v_in, q_layer_stride, kv_layer_stride,
+                                  cos_table, sin_table, q_rot, out, out_stride, out_layer_stride, nullptr, scale, stream);
+    if (t < 0) return -t;
+    if (t == 1) return PA_OK;
+  }
   for (int l = layer_begin; l < layer_end; l++) {
     const int i = l - layer_begin;
     const __nv_bfloat16* qi = (const __nv_bfloat16*)q_in + (size_t)i * q_layer_stride;
@@ -559,6 +628,13 @@ int pa_decode_step(pa_pool* p, int layer_begin, int layer_end, const void* q_in,
   bool fuse = cos_table && sin_table && can_fuse_append(p);
   for (const auto& e : p->batch)
     if (e.n_new > 0 && (!k_in || !v_in)) return fail(PA_ERR_INVALID_ARG, "decode step: the batch appends tokens but k_in/v_in is NULL");
+  if (fuse && q_rot != q_in) {
+    const int t = try_step_launch(p, nullptr, layer_begin, layer_end, q_in, k_in, v_in, q_layer_stride,
+                                  kv_layer_stride, cos_table, sin_table, q_rot, out, out_stride, out_layer_stride,
+                                  lse, scale, stream);
+    if (t < 0) return -t;
+    if (t == 1) return PA_OK;
+  }
   for (int l = layer_begin; l < layer_end; l++) {
     const int i = l - layer_begin;
     const __nv_bfloat16* qi = (const __nv_bfloat16*)q_in + (size_t)i * q_layer_stride;
@@ -731,6 +807,12 @@ int pa_pool_check(pa_pool* p, void* stream) {
 int pa_pool_set_decode_chunk_blocks(pa_pool* p, int chunk_blocks) {
   if (!p || chunk_blocks < 0) return fail(PA_ERR_INVALID_ARG, "pa_pool_set_decode_chunk_blocks: bad argument");
   p->chunk_blocks_override = chunk_blocks;
+  return PA_OK;
+}
+
+int pa_pool_set_step_kernel(pa_pool* p, int enable) {
+  if (!p) return fail(PA_ERR_INVALID_ARG, "pa_pool_set_step_kernel: NULL pool");
+  p->no_step_kernel = enable == 0;
   return PA_OK;
 }
 

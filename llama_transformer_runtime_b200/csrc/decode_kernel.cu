@@ -170,12 +170,41 @@ __device__ __forceinline__ void exchange_wait_merge(const DecodeParams& p, int z
 }
 
 template <int WARPS, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32)
-decode_kernel(DecodeParams p) {
+__device__ __forceinline__ void combine_pair(const DecodeParams& p, const int z, const int h, const int n_chunks,
+                                             unsigned char* smem, int* s_wait_ok_p);
+
+// Parameters of layer l of a persistent step: every per-layer pointer advanced.
+__device__ __forceinline__ DecodeParams step_layer_params(const DecodeStepParams& sp, int l) {
+  DecodeParams p = sp.base;
+  p.q += (size_t)l * sp.q_layer_stride;
+  if (p.k_new) p.k_new += (size_t)l * sp.kv_layer_stride;
+  if (p.v_new) p.v_new += (size_t)l * sp.kv_layer_stride;
+  if (p.q_rot_out) p.q_rot_out += (size_t)l * sp.q_layer_stride;
+  p.storage += (size_t)l * sp.layer_bytes;
+  p.storage_w += (size_t)l * sp.layer_bytes;
+  if (p.out) p.out += (size_t)l * sp.out_layer_stride;
+  if (p.xchg_out) p.xchg_out += (size_t)l * sp.out_layer_stride;
+  if (p.lse) p.lse += (size_t)l * sp.lse_layer_stride;
+  p.ws_acc += (size_t)l * sp.ws_layer_items * (kGroup * kHeadDim);
+  p.ws_ml += (size_t)l * sp.ws_layer_items * (2 * kGroup);
+  p.ws_count += (size_t)l * sp.n_seqs * sp.base.kv_heads;
+  p.xchg_seq = sp.base.xchg_seq + (unsigned)l;
+  p.xchg_slot = (int)(p.xchg_seq & 1u);
+  return p;
+}
+
+// Work of one CTA on chunk x of (sequence z, KV head h) of one layer.
+// kClassic: the kernel of one layer — partials meet through arrival tickets and
+// the last CTA of a (sequence, head) combines them.  kStepStream: a streaming
+// CTA of the persistent step kernel — it always leaves a partial, counts one
+// arrival for the pair's combining CTA and returns to take the next layer.
+// tile_base: tiles this warp has pulled through its ring so far (the ring and
+// its barrier phases run on across layers).
+enum { kClassic = 0, kStepStream = 1 };
+template <int WARPS, int STAGES, int MODE>
+__device__ __forceinline__ void decode_cta(const DecodeParams& p, const int x, const int h, const int z,
+                                           unsigned char* smem, uint32_t& tile_base) {
   using S = DecodeSmem<WARPS, STAGES>;
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem =
-      reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
   unsigned char* tiles = smem;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kTiles);
   float* mrg = reinterpret_cast<float*>(smem + S::kTiles + S::kBars);
@@ -186,9 +215,6 @@ decode_kernel(DecodeParams p) {
   __shared__ int s_wait_ok;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int x = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
-  // let the next layer's kernel take SMs as soon as this one's CTAs leave them
-  if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const BatchEntry e = p.batch[z];
   const int n_blocks = (e.kv_len + kBlockTok - 1) / kBlockTok;
   const int n_chunks = max(1, (n_blocks + p.chunk_blocks - 1) / p.chunk_blocks);
@@ -201,13 +227,17 @@ decode_kernel(DecodeParams p) {
 
   const uint32_t tile0 = smem_u32(tiles) + warp * STAGES * kPairBytes;
   const uint32_t bar0 = smem_u32(bars) + warp * STAGES * 8;
-  if (lane == 0) {
+  if (tile_base == 0) {  // first use of this warp's ring
+    if (lane == 0) {
 #pragma unroll
-    for (int s = 0; s < STAGES; s++) mbar_init(bar0 + s * 8, 1);
-    mbar_fence_init();
-    fence_proxy_async_smem();
+      for (int s = 0; s < STAGES; s++) mbar_init(bar0 + s * 8, 1);
+      mbar_fence_init();
+      fence_proxy_async_smem();
+    }
+    __syncwarp();
   }
-  __syncwarp();
+  const uint32_t ring0 = tile_base;  // ring position of this layer's tile 0
+  tile_base += (uint32_t)my_n;
 
   // Block-table entries of this warp's blocks, 32 at a time, one per lane.
   int tbase = 0;
@@ -227,7 +257,7 @@ decode_kernel(DecodeParams p) {
         atomicExch(p.status, kStatusBadBlock);
         blk = 0;
       }
-      const int st = i % STAGES;
+      const int st = (int)((ring0 + (uint32_t)i) % STAGES);
       mbar_expect_tx(bar0 + st * 8, kPairBytes);
       bulk_g2s(tile0 + st * kPairBytes, head_base + (size_t)blk * block_stride, kPairBytes,
                bar0 + st * 8);
@@ -323,8 +353,8 @@ decode_kernel(DecodeParams p) {
   bool failed = false;
 
   for (int i = 0; i < my_n; i++) {
-    const int st = i % STAGES;
-    const bool ok = mbar_wait(bar0 + st * 8, (uint32_t)((i / STAGES) & 1));
+    const int st = (int)((ring0 + (uint32_t)i) % STAGES);
+    const bool ok = mbar_wait(bar0 + st * 8, ((ring0 + (uint32_t)i) / STAGES) & 1u);
     if (!__all_sync(0xffffffffu, ok)) {
       failed = true;
       break;
@@ -425,7 +455,7 @@ decode_kernel(DecodeParams p) {
       L += wgt * mrg_l[w * kGroup + r];
       O += wgt * mrg_o[(w * kGroup + r) * kHeadDim + d];
     }
-    if (n_chunks == 1) {
+    if (MODE == kClassic && n_chunks == 1) {
       write_row_outputs(p, z, h, r, d, O, M, L);
     } else {
       p.ws_acc[(size_t)item * (kGroup * kHeadDim) + idx] = O;
@@ -435,9 +465,16 @@ decode_kernel(DecodeParams p) {
       }
     }
   }
+  if (MODE == kStepStream) {
+    // the pair's combining CTA polls this counter (acquire) and then reads the partials
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) atomicAdd(&p.ws_count[z * p.kv_heads + h], 1u);
+    return;
+  }
   if (n_chunks == 1) {
     publish_exchange(p, z, h);
-  exchange_wait_merge(p, z, h, &s_wait_ok);
+    exchange_wait_merge(p, z, h, &s_wait_ok);
     return;
   }
 
@@ -448,7 +485,22 @@ decode_kernel(DecodeParams p) {
   __syncthreads();
   if (s_ticket != (unsigned)(n_chunks - 1)) return;
   __threadfence();
+  combine_pair<WARPS, STAGES>(p, z, h, n_chunks, smem, &s_wait_ok);
+}
 
+// Combine the n_chunks partials of (sequence z, KV head h) from the workspace,
+// write the rows (and run the cross-GPU exchange when one is configured), and
+// clear the pair's arrival counter.  Called by all threads of a CTA.
+template <int WARPS, int STAGES>
+__device__ __forceinline__ void combine_pair(const DecodeParams& p, const int z, const int h, const int n_chunks,
+                                             unsigned char* smem, int* s_wait_ok_p) {
+  using S = DecodeSmem<WARPS, STAGES>;
+  unsigned char* tiles = smem;
+  float* mrg = reinterpret_cast<float*>(smem + S::kTiles + S::kBars);
+  float* mrg_o = mrg;
+  float* mrg_m = mrg + WARPS * kGroup * kHeadDim;
+  float* mrg_l = mrg_m + WARPS * kGroup;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // The tile ring is idle now and serves as scratch: (m, l) of every chunk,
   // then one weight per chunk and row.  All loads of a phase are independent,
   // so their latencies overlap instead of adding up.
@@ -523,7 +575,83 @@ decode_kernel(DecodeParams p) {
   }
   if (threadIdx.x == 0) p.ws_count[z * p.kv_heads + h] = 0u;
   publish_exchange(p, z, h);
-  exchange_wait_merge(p, z, h, &s_wait_ok);
+  exchange_wait_merge(p, z, h, s_wait_ok_p);
+}
+
+template <int WARPS, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32)
+decode_kernel(DecodeParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem =
+      reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+  // let the next layer's kernel take SMs as soon as this one's CTAs leave them
+  if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  uint32_t tile_base = 0;
+  decode_cta<WARPS, STAGES, kClassic>(p, blockIdx.x, blockIdx.y, blockIdx.z, smem, tile_base);
+}
+
+// ---- the whole multi-layer decode step as ONE launch --------------------------
+// Layers of a step are independent here (every layer has its own q, k, v rows,
+// cache layer, output rows and workspace slice), so nothing but the kernel
+// boundary made layer l+1 wait for the combine and the exchange of layer l.
+// CTAs [0, n_stream) stream: chunk x of (sequence, head), layer after layer,
+// never waiting on anybody.  One more CTA per (sequence, head) combines: for
+// each layer it waits — bounded — until the pair's n_chunks partials have been
+// counted, merges them, writes the rows and runs the cross-GPU exchange.  The
+// combining CTAs wait on the streaming ones of the same grid, so the launch is
+// cooperative (all CTAs resident).
+template <int WARPS, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32)
+decode_step_kernel(DecodeStepParams sp) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem =
+      reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+  __shared__ int s_ok;
+  __shared__ int s_wait_ok;
+  const int per_seq = sp.base.max_chunks * sp.base.kv_heads;
+  const int n_stream = per_seq * sp.n_seqs;
+  const int b = blockIdx.x;
+  if (b < n_stream) {
+    const int x = b % sp.base.max_chunks, h = (b / sp.base.max_chunks) % sp.base.kv_heads, z = b / per_seq;
+    uint32_t tile_base = 0;
+    for (int l = 0; l < sp.layers; l++) {
+      __syncthreads();  // the merge buffers of the previous layer are free
+      const DecodeParams p = step_layer_params(sp, l);
+      decode_cta<WARPS, STAGES, kStepStream>(p, x, h, z, smem, tile_base);
+    }
+    return;
+  }
+  const int pair = b - n_stream;
+  if (pair >= sp.n_seqs * sp.base.kv_heads) return;
+  const int z = pair / sp.base.kv_heads, h = pair % sp.base.kv_heads;
+  const BatchEntry e = sp.base.batch[z];
+  const int n_blocks = (e.kv_len + kBlockTok - 1) / kBlockTok;
+  const int n_chunks = max(1, (n_blocks + sp.base.chunk_blocks - 1) / sp.base.chunk_blocks);
+  for (int l = 0; l < sp.layers; l++) {
+    const DecodeParams p = step_layer_params(sp, l);
+    if (threadIdx.x == 0) {
+      const unsigned int* cnt = p.ws_count + pair;
+      SpinDeadline dl;
+      int ok = 1;
+      for (;;) {
+        unsigned int v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+        if (v >= (unsigned)n_chunks) break;
+        if (dl.expired()) {
+          ok = 0;
+          break;
+        }
+      }
+      s_ok = ok;
+    }
+    __syncthreads();
+    if (!s_ok) {  // a streaming CTA never arrived: record it and leave
+      if (threadIdx.x == 0) atomicExch(p.status, kStatusTimeout);
+      return;
+    }
+    combine_pair<WARPS, STAGES>(p, z, h, n_chunks, smem, &s_wait_ok);
+    __syncthreads();
+  }
 }
 
 template <int WARPS, int STAGES>
@@ -580,6 +708,33 @@ cudaError_t launch_decode(const DecodeParams& p, int n_seqs, int warps, int stag
     case 2 * 16 + 8: return launch_decode_cfg<2, 8>(p, n_seqs, stream);
     default: return launch_decode_cfg<4, 4>(p, n_seqs, stream);
   }
+}
+
+template <int WARPS, int STAGES>
+cudaError_t launch_decode_step_cfg(const DecodeStepParams& sp, cudaStream_t stream) {
+  using S = DecodeSmem<WARPS, STAGES>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(decode_step_kernel<WARPS, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  DecodeStepParams args = sp;
+  void* kargs[] = {&args};
+  // cooperative: the combining CTAs wait for the streaming CTAs of the same grid
+  return cudaLaunchCooperativeKernel((const void*)decode_step_kernel<WARPS, STAGES>, dim3(decode_step_ctas(sp)),
+                                     dim3(WARPS * 32), kargs, S::kBytes, stream);
+}
+
+cudaError_t launch_decode_step(const DecodeStepParams& sp, int warps, int stages, cudaStream_t stream) {
+  if (sp.n_seqs <= 0 || sp.layers <= 0) return cudaSuccess;
+  if (warps == 8 && stages == 4) return launch_decode_step_cfg<8, 4>(sp, stream);
+  if (warps == 8 && stages == 3) return launch_decode_step_cfg<8, 3>(sp, stream);
+  if (warps == 4 && stages == 4) return launch_decode_step_cfg<4, 4>(sp, stream);
+  return cudaErrorInvalidConfiguration;
 }
 
 // ---- merge of split-KV partials from disjoint key ranges ---------------------

@@ -137,6 +137,14 @@ bool exchange_fill(pa_exchange* x, DecodeParams& d, ExchangeMergeParams& m) {
   m.seq = x->seq;
   return true;
 }
+// A multi-layer step launched as one kernel uses `steps` more step numbers.
+void exchange_advance(pa_exchange* x, int steps) {
+  if (x && steps > 0) x->seq += (unsigned)steps;
+}
+// Take back the step number handed out by the last exchange_fill (nothing was launched).
+void exchange_unfill(pa_exchange* x) {
+  if (x && x->seq > 0) x->seq--;
+}
 // The merge of the step most recently started with exchange_fill.
 bool exchange_current(pa_exchange* x, ExchangeMergeParams& m) {
   if (!x || !x->connected || x->seq == 0) return false;

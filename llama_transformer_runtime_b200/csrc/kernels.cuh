@@ -87,6 +87,23 @@ struct DecodeParams {
 };
 constexpr int kXchgRowFloats = kHeadDim + 1;
 
+// A whole multi-layer decode step in one cooperative launch (decode_step_kernel):
+// `base` holds layer 0's parameters; layer l adds l strides to every per-layer
+// pointer, uses workspace slice l and exchange step base.xchg_seq + l.
+struct DecodeStepParams {
+  DecodeParams base;
+  int layers = 0, n_seqs = 0;
+  long long q_layer_stride = 0, kv_layer_stride = 0, out_layer_stride = 0, lse_layer_stride = 0;
+  unsigned long long layer_bytes = 0;  // cache bytes per layer
+  int ws_layer_items = 0;              // workspace items per layer (n_seqs * kv_heads * max_chunks)
+};
+constexpr int kMaxStepLayers = 64;
+// CTAs of the step launch: streaming ones plus one combining CTA per (sequence, head)
+inline int decode_step_ctas(const DecodeStepParams& sp) {
+  return sp.n_seqs * sp.base.kv_heads * (sp.base.max_chunks + 1);
+}
+cudaError_t launch_decode_step(const DecodeStepParams& sp, int warps, int stages, cudaStream_t stream);
+
 // Waits (bounded) until every rank's partial of step `seq` has landed in this
 // rank's receive buffer, then merges them: out rows bf16, stride out_stride.
 struct ExchangeMergeParams {

@@ -155,6 +155,10 @@ class KVPool:
     def set_decode_chunk_blocks(self, n: int) -> None:
         check(lib().pa_pool_set_decode_chunk_blocks(self._h, n))
 
+    def set_step_kernel(self, enable: bool) -> None:
+        """decode_step as one cooperative launch per step (default) or one kernel per layer."""
+        check(lib().pa_pool_set_step_kernel(self._h, 1 if enable else 0))
+
     def set_decode_shape(self, warps: int, stages: int) -> None:
         check(lib().pa_pool_set_decode_shape(self._h, warps, stages))
 
