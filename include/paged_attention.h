@@ -279,6 +279,8 @@ int pa_pool_set_decode_chunk_blocks(pa_pool* pool, int chunk_blocks);
  * cooperative launch when the batch allows it (enable != 0, the default);
  * enable == 0 keeps one kernel per layer.  No counterpart in the reference. */
 int pa_pool_set_step_kernel(pa_pool* pool, int enable);
+/* How many decode steps of this pool ran as one launch so far. */
+int pa_pool_step_launches(pa_pool* pool, long long* count);
 /* Warps per decode CTA and 4 KiB ring stages per warp (built shapes only). */
 int pa_pool_set_decode_shape(pa_pool* pool, int warps, int stages);
 

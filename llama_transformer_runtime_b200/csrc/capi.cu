@@ -72,6 +72,7 @@ struct pa_pool {
   int sm_count = 0;
   int rope_variant = 1;
   bool no_step_kernel = false;  // pa_pool_set_step_kernel(pool, 0): one kernel per layer
+  long long step_launches = 0;  // decode steps that ran as one cooperative launch
   pa_pool(int nb, int ms, int mb) : host(nb, ms, mb) {}
 };
 
@@ -481,6 +482,7 @@ static int try_step_launch(pa_pool* p, pa_exchange* x, int layer_begin, int laye
   const int layers = layer_end - layer_begin;
   if (layers < 2 || layers > pa::kMaxStepLayers || p->device < 0 || p->batch.empty() || p->no_step_kernel) return 0;
   const int n_seqs = (int)p->batch.size();
+  if (n_seqs > pa::kMaxStepSeqs) return 0;
   const int sms = p->sm_count > 0 ? p->sm_count : 148;
   const long long pairs = (long long)n_seqs * p->kv_heads;
   if (pairs * 4 > sms) return 0;
@@ -503,6 +505,18 @@ static int try_step_launch(pa_pool* p, pa_exchange* x, int layer_begin, int laye
   sp.lse_layer_stride = (long long)n_seqs * p->kv_heads * pa::kGroup;
   sp.layer_bytes = p->layer_bytes;
   sp.ws_layer_items = n_seqs * p->kv_heads * sp.base.max_chunks;
+  {
+    int first = 0;
+    for (int z = 0; z < n_seqs; z++) {
+      const int n_blocks = (p->batch[z].kv_len + pa::kBlockTokens - 1) / pa::kBlockTokens;
+      int chunks = (n_blocks + sp.base.chunk_blocks - 1) / sp.base.chunk_blocks;
+      if (chunks < 1) chunks = 1;
+      sp.seq_first[z] = (unsigned short)first;
+      first += chunks * p->kv_heads;
+    }
+    sp.seq_first[n_seqs] = (unsigned short)first;
+    sp.n_stream = first;
+  }
   // one CTA per SM (the ring of an 8-warp CTA fills most of an SM's shared memory)
   if (pa::decode_step_ctas(sp) > sms || (long long)sp.ws_layer_items * layers > kWsItems) {
     if (x) pa::exchange_unfill(x);
@@ -516,6 +530,7 @@ static int try_step_launch(pa_pool* p, pa_exchange* x, int layer_begin, int laye
     fail(PA_ERR_CUDA, "decode step launch: %s", cudaGetErrorString(e));
     return -PA_ERR_CUDA;
   }
+  p->step_launches++;
   return 1;
 }
 
@@ -813,6 +828,12 @@ int pa_pool_set_decode_chunk_blocks(pa_pool* p, int chunk_blocks) {
 int pa_pool_set_step_kernel(pa_pool* p, int enable) {
   if (!p) return fail(PA_ERR_INVALID_ARG, "pa_pool_set_step_kernel: NULL pool");
   p->no_step_kernel = enable == 0;
+  return PA_OK;
+}
+
+int pa_pool_step_launches(pa_pool* p, long long* count) {
+  if (!p || !count) return fail(PA_ERR_INVALID_ARG, "pa_pool_step_launches: NULL argument");
+  *count = p->step_launches;
   return PA_OK;
 }
 

@@ -608,11 +608,14 @@ decode_step_kernel(DecodeStepParams sp) {
       reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
   __shared__ int s_ok;
   __shared__ int s_wait_ok;
-  const int per_seq = sp.base.max_chunks * sp.base.kv_heads;
-  const int n_stream = per_seq * sp.n_seqs;
+  const int n_stream = sp.n_stream;
   const int b = blockIdx.x;
   if (b < n_stream) {
-    const int x = b % sp.base.max_chunks, h = (b / sp.base.max_chunks) % sp.base.kv_heads, z = b / per_seq;
+    int z = 0;
+    while (z + 1 < sp.n_seqs && b >= (int)sp.seq_first[z + 1]) z++;
+    const int local = b - (int)sp.seq_first[z];
+    const int chunks_z = ((int)sp.seq_first[z + 1] - (int)sp.seq_first[z]) / sp.base.kv_heads;
+    const int x = local % chunks_z, h = local / chunks_z;
     uint32_t tile_base = 0;
     for (int l = 0; l < sp.layers; l++) {
       __syncthreads();  // the merge buffers of the previous layer are free

@@ -96,11 +96,16 @@ struct DecodeStepParams {
   long long q_layer_stride = 0, kv_layer_stride = 0, out_layer_stride = 0, lse_layer_stride = 0;
   unsigned long long layer_bytes = 0;  // cache bytes per layer
   int ws_layer_items = 0;              // workspace items per layer (n_seqs * kv_heads * max_chunks)
+  // streaming CTAs of sequence z: [seq_first[z], seq_first[z+1]) = its chunks x its heads
+  // (ragged batches get exactly the CTAs they need); n_stream = seq_first[n_seqs]
+  int n_stream = 0;
+  unsigned short seq_first[41] = {};
 };
 constexpr int kMaxStepLayers = 64;
+constexpr int kMaxStepSeqs = 40;
 // CTAs of the step launch: streaming ones plus one combining CTA per (sequence, head)
 inline int decode_step_ctas(const DecodeStepParams& sp) {
-  return sp.n_seqs * sp.base.kv_heads * (sp.base.max_chunks + 1);
+  return sp.n_stream + sp.n_seqs * sp.base.kv_heads;
 }
 cudaError_t launch_decode_step(const DecodeStepParams& sp, int warps, int stages, cudaStream_t stream);
 

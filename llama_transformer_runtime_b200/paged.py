@@ -159,6 +159,12 @@ class KVPool:
         """decode_step as one cooperative launch per step (default) or one kernel per layer."""
         check(lib().pa_pool_set_step_kernel(self._h, 1 if enable else 0))
 
+    def step_launches(self) -> int:
+        """Decode steps of this pool that ran as one launch."""
+        n = C.c_longlong(0)
+        check(lib().pa_pool_step_launches(self._h, C.byref(n)))
+        return int(n.value)
+
     def set_decode_shape(self, warps: int, stages: int) -> None:
         check(lib().pa_pool_set_decode_shape(self._h, warps, stages))
 

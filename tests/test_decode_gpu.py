@@ -285,3 +285,68 @@ def test_fused_step_equals_append_then_decode(cuda, chunk_blocks):
     for l in range(layers):
         assert np.array_equal(cf[l], c2[l])
     assert np.array_equal(of, o2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("chunk_blocks", [0, 5])
+def test_step_kernel_equals_one_kernel_per_layer(cuda, chunk_blocks):
+    """A decode step of several layers runs as ONE cooperative launch (streaming
+    CTAs layer after layer, one combining CTA per (sequence, head)); outputs,
+    rotated Q, LSE-free rows and cache contents must equal the one-kernel-per-layer
+    path and the separate append + decode path bit for bit."""
+    from tests.gpu_helpers import read_logical_pool
+    rng = np.random.default_rng(170 + chunk_blocks)
+    lens = [47, 130, 255]
+    layers = 3
+    cos, sin = orc.build_rope_tables(300)
+    cos_d, sin_d = f32_dev(cos), f32_dev(sin)
+    n = len(lens)
+    q = to_dev(orc.randn_bf16(rng, (layers, n, 32, 64)))
+    k = to_dev(orc.randn_bf16(rng, (layers, n, 8, 64)))
+    v = to_dev(orc.randn_bf16(rng, (layers, n, 8, 64)))
+    results = []
+    for mode in ("step", "per_layer", "separate"):
+        prng = np.random.default_rng(171)
+        pool = paged.KVPool(layers, 64, 8, n, 20)
+        pool.set_free_order(prng.permutation(64))
+        pool.set_decode_chunk_blocks(chunk_blocks)
+        pool.set_step_kernel(mode == "step")
+        seqs = []
+        for L in lens:
+            s = pool.create_seq()
+            for layer in range(layers):
+                kk = orc.randn_bf16(prng, (8, L, 64), 0.5)
+                vv = orc.randn_bf16(prng, (8, L, 64), 0.5)
+                if layer == 0:
+                    fill_cache(pool, 0, s, kk, vv)
+                else:
+                    pool.batch_set([s], [L])
+                    pool.append(layer, None, to_dev(kk.transpose(1, 0, 2)), to_dev(vv.transpose(1, 0, 2)),
+                                torch.ones(L, 32, device=DEV), torch.zeros(L, 32, device=DEV), None)
+            seqs.append(s)
+        outs = []
+        for step in range(2):  # two steps in a row: counters and rings start clean each launch
+            for s, L in zip(seqs, lens):
+                pool.reserve(s, L + 1 + step)
+            pool.batch_set(seqs)
+            out = torch.zeros(layers, n, 2048, dtype=torch.bfloat16, device=DEV)
+            q_rot = torch.zeros_like(q)
+            if mode == "separate":
+                for layer in range(layers):
+                    pool.append(layer, q[layer], k[layer], v[layer], cos_d, sin_d, q_rot[layer])
+                    pool.decode(layer, q_rot[layer], out[layer], 2048)
+            else:
+                pool.decode_step(0, layers, q, k, v, n * 2048, n * 512, cos_d, sin_d, q_rot, out, 2048, n * 2048)
+            torch.cuda.synchronize()
+            pool.check()
+            outs.append((to_u16(out), to_u16(q_rot)))
+        assert pool.step_launches() == (2 if mode == "step" else 0)
+        results.append((outs, [read_logical_pool(pool, l) for l in range(layers)]))
+        pool.close()
+    (o_a, c_a), (o_b, c_b), (o_c, c_c) = results
+    for step in range(2):
+        for other in (o_b, o_c):
+            assert np.array_equal(o_a[step][0], other[step][0])
+            assert np.array_equal(o_a[step][1], other[step][1])
+    for l in range(layers):
+        assert np.array_equal(c_a[l], c_b[l]) and np.array_equal(c_a[l], c_c[l])
