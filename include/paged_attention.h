@@ -284,6 +284,20 @@ int pa_pool_step_launches(pa_pool* pool, long long* count);
 /* Warps per decode CTA and 4 KiB ring stages per warp (built shapes only). */
 int pa_pool_set_decode_shape(pa_pool* pool, int warps, int stages);
 
+/* ---- producer side of the path: Q/K/V projections of a decode step -----------
+ * Replaces, for decode shapes (rows = sequences of the step, at most 8), the
+ * reference's launch_gemm_2048x2048 + 2 x launch_gemm_2048x512 per layer
+ * (src/runtime/attention.cu:138-191; src/kernels/gemm/gemm_2048x2048.hpp,
+ * gemm_2048x512.hpp: A [M, K] row-major, B [K, N] row-major, bf16 in, fp32
+ * accumulation, bf16 out).  x [layers][rows, hidden]; wq [layers][hidden, q_cols];
+ * wk, wv [layers][hidden, kv_cols]; q [layers][rows, q_cols]; k, v
+ * [layers][rows, kv_cols]; all bf16, layer strides in elements.  One launch for
+ * all layers; the outputs are what pa_decode_step takes as q_in, k_in, v_in. */
+int pa_qkv_project(const void* x, const void* wq, const void* wk, const void* wv, void* q, void* k,
+                   void* v, int rows, int layers, int hidden, int q_cols, int kv_cols,
+                   int64_t x_layer_stride, int64_t wq_layer_stride, int64_t wkv_layer_stride,
+                   int64_t q_layer_stride, int64_t kv_layer_stride, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -291,3 +291,13 @@ def merge_partials(o_parts, lse_parts, n_parts: int, rows: int, out=None, out_f3
                    lse_out=None, stream: int = 0) -> None:
     check(lib().pa_merge_partials(_ptr(o_parts), _ptr(lse_parts), n_parts, rows, _ptr(out),
                                   _ptr(out_f32), _ptr(lse_out), stream))
+
+
+def qkv_project(x, wq, wk, wv, q, k, v, rows: int, layers: int = 1, hidden: int = 2048, stream: int = 0) -> None:
+    """q, k, v = x Wq, x Wk, x Wv for the rows of a decode step, all layers in one launch.
+    x [layers, rows, hidden]; wq [layers, hidden, q_cols]; wk, wv [layers, hidden, kv_cols]
+    (the reference's row-major weights); outputs [layers, rows, cols]; contiguous bf16 tensors."""
+    q_cols, kv_cols = int(wq.shape[-1]), int(wk.shape[-1])
+    check(lib().pa_qkv_project(_ptr(x), _ptr(wq), _ptr(wk), _ptr(wv), _ptr(q), _ptr(k), _ptr(v), rows, layers,
+                               hidden, q_cols, kv_cols, rows * hidden, hidden * q_cols, hidden * kv_cols,
+                               rows * q_cols, rows * kv_cols, stream))

@@ -16,6 +16,17 @@
 #define R ORC_ROTARY_DIM
 #define BT ORC_BLOCK_TOKENS
 
+void orc_gemm_bf16(const uint16_t* A, const uint16_t* B, uint16_t* C, int M, int N, int K) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int m = 0; m < M; m++)
+    for (int n = 0; n < N; n++) {
+      double acc = 0.0;
+      for (int k = 0; k < K; k++)
+        acc += (double)orc_bf16_to_f32(A[(size_t)m * K + k]) * (double)orc_bf16_to_f32(B[(size_t)k * N + n]);
+      C[(size_t)m * N + n] = orc_f32_to_bf16((float)acc);
+    }
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

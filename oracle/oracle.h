@@ -103,6 +103,14 @@ void orc_output_layout_f32(const float* in, float* out, int heads, int tokens);
 void orc_output_layout_bf16(const uint16_t* in, uint16_t* out, int heads,
                             int tokens);
 
+/* C = A B as the reference's projection GEMMs define it
+ * (src/kernels/gemm/gemm_2048x512.cu:82-290, gemm_2048x2048.cu:95-331: A [M, K]
+ * row-major bf16, B [K, N] row-major bf16, fp32 tensor-core accumulation, C bf16
+ * by round-to-nearest).  Here every dot product is accumulated in double and
+ * rounded once, so a GPU result may differ by one bf16 ulp where its fp32
+ * accumulation order lands on the other side of a rounding boundary. */
+void orc_gemm_bf16(const uint16_t* A, const uint16_t* B, uint16_t* C, int M, int N, int K);
+
 int orc_num_threads(void);
 
 #ifdef __cplusplus

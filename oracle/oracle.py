@@ -182,6 +182,18 @@ def output_layout(x: np.ndarray) -> np.ndarray:
     return out
 
 
+def gemm_bf16(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """bf16 bit patterns: a [M, K] times b [K, N] -> [M, N] (double accumulation, one rounding)."""
+    a = np.ascontiguousarray(a, dtype=np.uint16)
+    b = np.ascontiguousarray(b, dtype=np.uint16)
+    M, K = a.shape
+    K2, N = b.shape
+    assert K == K2
+    out = np.empty((M, N), np.uint16)
+    lib().orc_gemm_bf16(_p(a), _p(b), _p(out), C.c_int(M), C.c_int(N), C.c_int(K))
+    return out
+
+
 def num_threads() -> int:
     return int(lib().orc_num_threads())
 
@@ -232,8 +244,8 @@ def ref_available() -> bool:
 
 
 def ref():
-    """Load ``_ref/libref.so`` (the reference's flashattention.cu, rope.cu and
-    layout.cu compiled unmodified for sm_100a).  Needs a GPU."""
+    """Load ``_ref/libref.so`` (the reference's flashattention.cu, rope.cu, layout.cu
+    and its two projection GEMMs compiled unmodified for sm_100a).  Needs a GPU."""
     global _REF
     if _REF is None:
         r = C.CDLL(os.path.join(_HERE, "_ref", "libref.so"))
@@ -248,5 +260,7 @@ def ref():
         r.ref_append_memcpy_loop.restype = i
         r.ref_append_strided.argtypes = [vp] * 4 + [i] * 3 + [vp]
         r.ref_append_strided.restype = i
+        r.ref_gemm.argtypes = [vp, vp, vp, i, i, i]
+        r.ref_gemm.restype = i
         _REF = r
     return _REF

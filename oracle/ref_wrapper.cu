@@ -21,6 +21,8 @@
 #include <cuda_runtime.h>
 
 #include "flashattention.h"
+#include "gemm_2048x2048.hpp"
+#include "gemm_2048x512.hpp"
 #include "layout.hpp"
 #include "rope.hpp"
 
@@ -59,6 +61,18 @@ void ref_flash_attention(const void* Q, const void* K, const void* V, void* O,
   p.dtype = transformer::DType::BF16;
   p.stream = (cudaStream_t)stream;
   transformer::launch_flash_attention(p);
+}
+
+// The projection GEMMs as Attention::forward calls them (src/runtime/attention.cu:138-191):
+// N = 2048 -> launch_gemm_2048x2048, N = 512 -> launch_gemm_2048x512.
+int ref_gemm(const void* A, const void* B, void* C, int M, int N, int K) {
+  if (N == 2048)
+    launch_gemm_2048x2048((const __nv_bfloat16*)A, (const __nv_bfloat16*)B, (__nv_bfloat16*)C, M, N, K);
+  else if (N == 512)
+    launch_gemm_2048x512((const __nv_bfloat16*)A, (const __nv_bfloat16*)B, (__nv_bfloat16*)C, M, N, K);
+  else
+    return 1;
+  return (int)cudaGetLastError();
 }
 
 void ref_flash_output_layout(const void* in, void* out, int tokens) {

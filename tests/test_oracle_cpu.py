@@ -199,3 +199,15 @@ def test_golden_vectors_from_reference_kernels():
         assert np.all(err <= 2e-2 + 1e-2 * np.abs(O)), (path, err.max())
         assert np.max(np.abs(g["lse"] - L)) < 2e-2, path
         assert np.array_equal(orc.output_layout(g["o_flash"]), g["o_layout"]), path
+
+
+def test_gemm_restatement_against_numpy():
+    """orc_gemm_bf16 (the projection GEMMs' contract) against float64 numpy, rounded once."""
+    rng = np.random.default_rng(77)
+    a = orc.randn_bf16(rng, (3, 256))
+    b = orc.randn_bf16(rng, (256, 96), 0.05)
+    got = orc.gemm_bf16(a, b)
+    ref = orc.bf16_to_f32(a).astype(np.float64) @ orc.bf16_to_f32(b).astype(np.float64)
+    want = orc.f32_to_bf16(ref.astype(np.float32))
+    # float64 -> float32 -> bf16 can differ from the oracle's path only by double rounding: none here
+    assert np.array_equal(got, want)
