@@ -357,7 +357,7 @@ def run_ours(args):
                           "us_per_layer_plain_decode_kernel": round(ms_iso * 1e3, 2),
                           "how": f"CUDA events around the step's one launch (all {LAYERS} layers, append fused in)",
                           "traffic": (NCU_TRAFFIC_BYTES[args.workload] * LAYERS
-                                      if args.workload in NCU_TRAFFIC_BYTES else None),
+                                      if NCU_TRAFFIC_BYTES.get(args.workload) else None),
                           "traffic_note": "ncu capture of the 1-layer decode_kernel launch x layers"}
                          if world == 1 and LAYERS >= 2 else
                          {"bound": "hbm", "kernel": "decode_kernel", "achieved": round(achieved, 1),
@@ -757,6 +757,159 @@ def run_batch(args):
 PREFILL_TOKENS = 2048
 
 
+def run_qkv(args):
+    """Q/K/V projections of a decode step (the producer in front of the attention path): batch 1,
+    hidden 2048 -> q 2048 + k 512 + v 512 columns, all layers of the step.  A step reads every layer's
+    weights once (12.6 MB per layer), so the metric is achieved HBM GB/s.  N>1: independent replicas."""
+    import torch
+    import torch.distributed as dist
+
+    from llama_transformer_runtime_b200 import paged
+
+    rank, local_rank, world = dist_env()
+    torch.cuda.set_device(local_rank)
+    dev = f"cuda:{local_rank}"
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+    if args.impl == "reference" and rank != 0:
+        return
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    H, NQ, NKV, rows = 2048, 2048, 512, 1
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(99 + rank)
+    # 8 rotating weight sets (1.6 GB) so that no step finds its weights in L2 (126 MB)
+    SETS = 8 if args.impl == "ours" else 2
+    wq = [(torch.randn(LAYERS, H, NQ, generator=gen, device=dev) * 0.03).to(torch.bfloat16) for _ in range(SETS)]
+    wk = [(torch.randn(LAYERS, H, NKV, generator=gen, device=dev) * 0.03).to(torch.bfloat16) for _ in range(SETS)]
+    wv = [(torch.randn(LAYERS, H, NKV, generator=gen, device=dev) * 0.03).to(torch.bfloat16) for _ in range(SETS)]
+    x_host = torch.randn(LAYERS, rows, H, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).pin_memory()
+    x_dev = x_host.to(dev)
+    q = torch.zeros(LAYERS, rows, NQ, dtype=torch.bfloat16, device=dev)
+    k = torch.zeros(LAYERS, rows, NKV, dtype=torch.bfloat16, device=dev)
+    v = torch.zeros(LAYERS, rows, NKV, dtype=torch.bfloat16, device=dev)
+    out_host = torch.zeros(LAYERS, rows, NQ + 2 * NKV, dtype=torch.bfloat16).pin_memory()
+    bytes_layer = (H * (NQ + 2 * NKV) + rows * H + rows * (NQ + 2 * NKV)) * 2
+    state = {"i": 0}
+
+    if args.impl == "reference":
+        from oracle import oracle as orc
+        ref = orc.ref()
+
+        def step():
+            # as Attention::forward drives it (src/runtime/attention.cu:138-191): three GEMM launches
+            # per layer, a device synchronisation after each
+            s = state["i"] % SETS
+            state["i"] += 1
+            for l in range(LAYERS):
+                for w, o, n in ((wq[s], q, NQ), (wk[s], k, NKV), (wv[s], v, NKV)):
+                    ref.ref_gemm(x_dev[l].data_ptr(), w[l].data_ptr(), o[l].data_ptr(), rows, n, H)
+                    torch.cuda.synchronize()
+        launches_per_step = 3 * LAYERS
+    else:
+        def step():
+            s = state["i"] % SETS
+            state["i"] += 1
+            paged.qkv_project(x_dev, wq[s], wk[s], wv[s], q, k, v, rows, LAYERS)
+        launches_per_step = 1
+
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        step()
+        out_host[:, :, :NQ].copy_(q, non_blocking=True)
+        out_host[:, :, NQ:NQ + NKV].copy_(k, non_blocking=True)
+        out_host[:, :, NQ + NKV:].copy_(v, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1 and args.impl == "ours":
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1 and args.impl == "ours":
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    m0 = sampler.mark()
+    for _ in range(args.warmup):
+        step()
+    ms = timed(step, args.steps)
+    ms_e2e = timed(e2e_step, args.steps)
+    m1 = sampler.mark()
+    n_rep = world if args.impl == "ours" else 1
+    value = n_rep * LAYERS * bytes_layer * args.steps / (ms * 1e-3) / 1e9
+    e2e_value = n_rep * LAYERS * bytes_layer * args.steps / (ms_e2e * 1e-3) / 1e9
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        line = {
+            "metric": "qkv_project_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4),
+            "us_per_layer": round(ms / args.steps * 1e3 / LAYERS, 2),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"qkv_projection_decode_batch1_x{LAYERS}layers", "hidden": H, "q_cols": NQ,
+                       "kv_cols": NKV, "rows": rows, "layers": LAYERS,
+                       "parallelism": "1 GPU" if world == 1 else f"{world} independent replicas",
+                       "l2": f"{SETS} weight sets in rotation ({SETS * LAYERS * bytes_layer / 1e9:.2f} GB), larger than L2"},
+            "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": x_host.numel() * 2,
+                    "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": round(ms_e2e / args.steps, 4)},
+            "gpu_launches": launches_per_step * args.steps, "clocks": sampler.stop(m0, m1),
+        }
+        if args.impl == "reference":
+            line["impl"] = "reference"
+            line["cpu_baseline"] = {"value": line["value"], "unit": "GB/s", "cores": os.cpu_count(), "kind": "reference",
+                                    "sample": "the reference has no CPU implementation of its GEMMs: its own CUDA "
+                                              "kernels (gemm_2048x2048.cu, gemm_2048x512.cu) run on the GPU, driven "
+                                              "as Attention::forward drives them"}
+            line["e2e"]["h2d_bytes_per_step"] = 0
+            line["e2e"]["d2h_bytes_per_step"] = 0
+            line["e2e"]["value"] = line["value"]
+        else:
+            line["roofline"] = {"bound": "hbm", "kernel": "qkv_project_kernel", "achieved": round(value / n_rep, 1),
+                                "peak": peak, "unit": "GB/s", "frac": round(value / n_rep / peak, 4),
+                                "peak_source": f"of {peak_kind}", "us_per_launch": round(ms / args.steps * 1e3, 2),
+                                "bytes_per_launch": LAYERS * bytes_layer, "traffic": None}
+            # CPU baseline: the oracle's GEMM restatement (double accumulation, OpenMP) on layer 0
+            from oracle import oracle as orc
+            import time
+            xs = x_host[0].view(torch.int16).numpy().view(np.uint16)
+            ws = [w[0][0].cpu().view(torch.int16).numpy().view(np.uint16) for w in (wq, wk, wv)]
+            t0 = time.perf_counter()
+            reps = 0
+            while time.perf_counter() - t0 < 10.0:
+                outs = [orc.gemm_bf16(xs, w) for w in ws]
+                reps += 1
+            dt = (time.perf_counter() - t0) / reps
+            got = torch.cat([q[0], k[0], v[0]], dim=1).cpu().view(torch.int16).numpy().view(np.uint16)
+            # the last timed step used weight set (i - 1) % SETS; recompute layer 0 with set 0 for the check
+            paged.qkv_project(x_dev, wq[0], wk[0], wv[0], q, k, v, rows, LAYERS)
+            torch.cuda.synchronize()
+            got = torch.cat([q[0], k[0], v[0]], dim=1).cpu().view(torch.int16).numpy().view(np.uint16)
+            want = np.concatenate(outs, axis=1)
+            err = float(np.abs(orc.bf16_to_f32(got) - orc.bf16_to_f32(want)).max())
+            line["cpu_baseline"] = {"value": round(bytes_layer / dt / 1e9, 2), "unit": "GB/s",
+                                    "cores": orc.num_threads(), "kind": "port",
+                                    "sample": f"layer 0 of the workload, {reps} repetitions in {dt * reps:.1f} s",
+                                    "gpu_vs_cpu_max_abs_err": err}
+        print(json.dumps(line), flush=True)
+    barrier()
+    if world > 1 and dist.is_initialized():
+        dist.destroy_process_group()
+
+
+
 def prefill_flops(S: int) -> float:
     """Causal-useful flops of one layer: 4 * Hq * D * S (S + 1) / 2."""
     return 4.0 * Q_HEADS * D * S * (S + 1) / 2.0
@@ -951,7 +1104,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode128k", choices=sorted(WORKLOADS) + ["prefill2k", "batch64"])
+    ap.add_argument("--workload", default="decode128k", choices=sorted(WORKLOADS) + ["prefill2k", "batch64", "qkv_decode"])
     ap.add_argument("--seqs", type=int, default=64, help="batch64: number of sequences")
     ap.add_argument("--layers", type=int, default=16, help="fewer layers make a small case for profiling")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
@@ -964,7 +1117,9 @@ def main():
     args.warmup = max(args.warmup, 3)
     global LAYERS
     LAYERS = args.layers
-    if args.workload == "prefill2k":
+    if args.workload == "qkv_decode":
+        run_qkv(args)
+    elif args.workload == "prefill2k":
         run_prefill(args)
     elif args.workload == "batch64":
         run_batch(args)

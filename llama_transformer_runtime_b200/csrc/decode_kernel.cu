@@ -200,21 +200,10 @@ __device__ __forceinline__ DecodeParams step_layer_params(const DecodeStepParams
 // arrival for the pair's combining CTA and returns to take the next layer.
 // tile_base: tiles this warp has pulled through its ring so far (the ring and
 // its barrier phases run on across layers).
-// nx / ahead: in the step kernel a warp keeps its ring full across the layer
-// boundary — once this layer's tiles are all issued it goes on with the next
-// layer's (nx), and `ahead` tells the next call how many of its tiles are
-// already in flight.
 enum { kClassic = 0, kStepStream = 1 };
-struct NextLayer {
-  const char* storage = nullptr;   // next layer's cache; nullptr: there is no next layer
-  char* storage_w = nullptr;
-  const __nv_bfloat16* k_new = nullptr;
-  const __nv_bfloat16* v_new = nullptr;
-};
 template <int WARPS, int STAGES, int MODE>
 __device__ __forceinline__ void decode_cta(const DecodeParams& p, const int x, const int h, const int z,
-                                           unsigned char* smem, uint32_t& tile_base, const NextLayer nx,
-                                           uint32_t& ahead) {
+                                           unsigned char* smem, uint32_t& tile_base) {
   using S = DecodeSmem<WARPS, STAGES>;
   unsigned char* tiles = smem;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kTiles);
@@ -250,20 +239,15 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const int x, c
   const uint32_t ring0 = tile_base;  // ring position of this layer's tile 0
   tile_base += (uint32_t)my_n;
 
-  // Block-table entries of this warp's blocks, a window of 32, one per lane.
+  // Block-table entries of this warp's blocks, 32 at a time, one per lane.
   int tbase = 0;
   int tbl_reg = lane < my_n ? table[(size_t)lane * WARPS] : 0;
+  const char* head_base = p.storage + (size_t)h * kPairBytes;
   const size_t block_stride = (size_t)p.kv_heads * kPairBytes;
-  const bool has_next = MODE == kStepStream && nx.storage != nullptr;
 
-  // Tile r of this warp counted from this layer's tile 0; r >= my_n is tile
-  // r - my_n of the next layer (same table: a block id means the same tokens in
-  // every layer).
-  auto issue = [&](int r) {
-    const bool nxt = r >= my_n;
-    const int i = nxt ? r - my_n : r;
-    if (i < tbase || i >= tbase + 32) {
-      tbase = i & ~31;
+  auto issue = [&](int i) {
+    if (i >= tbase + 32) {
+      tbase += 32;
       const int ii = tbase + lane;
       tbl_reg = ii < my_n ? table[(size_t)ii * WARPS] : 0;
     }
@@ -273,10 +257,9 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const int x, c
         atomicExch(p.status, kStatusBadBlock);
         blk = 0;
       }
-      const int st = (int)((ring0 + (uint32_t)r) % STAGES);
+      const int st = (int)((ring0 + (uint32_t)i) % STAGES);
       mbar_expect_tx(bar0 + st * 8, kPairBytes);
-      bulk_g2s(tile0 + st * kPairBytes,
-               (nxt ? nx.storage : p.storage) + (size_t)h * kPairBytes + (size_t)blk * block_stride, kPairBytes,
+      bulk_g2s(tile0 + st * kPairBytes, head_base + (size_t)blk * block_stride, kPairBytes,
                bar0 + st * 8);
     }
   };
@@ -285,8 +268,7 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const int x, c
   // first writes the new token's K (RoPE applied) and V rows of this head into
   // that block — the same arithmetic and placement as append_kernel — and
   // orders those generic-proxy stores before its own bulk (async-proxy) reads.
-  const bool appends = p.fuse && e.n_new > 0 && x == n_chunks - 1 && cnt > 0 && warp == (cnt - 1) % WARPS;
-  auto append_row = [&](const __nv_bfloat16* k_new, const __nv_bfloat16* v_new, char* storage_w) {
+  if (p.fuse && e.n_new > 0 && x == n_chunks - 1 && cnt > 0 && warp == (cnt - 1) % WARPS) {
     if (lane < 8) {
       const int lpos = e.kv_len - 1;
       const int pos = e.kv_pos_off + lpos;
@@ -296,9 +278,9 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const int x, c
       if (blk < 0 || blk >= p.num_blocks) {
         atomicExch(p.status, kStatusBadBlock);
       } else {
-        const __nv_bfloat16* row = (is_v ? v_new : k_new) + ((size_t)e.kv_row_off * p.kv_heads + h) * kHeadDim;
+        const __nv_bfloat16* row = (is_v ? p.v_new : p.k_new) + ((size_t)e.kv_row_off * p.kv_heads + h) * kHeadDim;
         const uint4* src = reinterpret_cast<const uint4*>(row);
-        char* tile = storage_w + tile_off(blk, p.kv_heads, h, is_v);
+        char* tile = p.storage_w + tile_off(blk, p.kv_heads, h, is_v);
         uint4 lo = src[c], hi = src[c + 4];
         if (!is_v) {
           const float4* cs = reinterpret_cast<const float4*>(p.cos_table + (size_t)pos * 32 + c * 8);
@@ -315,19 +297,9 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const int x, c
     }
     asm volatile("fence.proxy.async;" ::: "memory");
     __syncwarp();
-  };
-  // A layer's row is appended right before the warp issues that layer's first tile.
-  int r_issue = (int)ahead;
-  const int r_limit = has_next ? 2 * my_n : my_n;
-  if (appends && r_issue == 0) append_row(p.k_new, p.v_new, p.storage_w);
-  auto fill = [&](int consumed) {
-    while (r_issue < consumed + STAGES && r_issue < r_limit) {
-      if (r_issue == my_n && appends) append_row(nx.k_new, nx.v_new, nx.storage_w);
-      issue(r_issue);
-      r_issue++;
-    }
-  };
-  fill(0);
+  }
+
+  for (int i = 0; i < STAGES && i < my_n; i++) issue(i);
 
   // Query fragments: rows 0..3 are the group's heads, the rest zero.
   const int qrow = lane >> 2, qcol = (lane & 3) * 2;
@@ -441,12 +413,11 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const int x, c
     }
 
     __syncwarp();
-    if (r_issue < i + 1 + STAGES && r_issue < r_limit) {
+    if (i + STAGES < my_n) {
       if (lane == 0) fence_proxy_async_smem();
-      fill(i + 1);
+      issue(i + STAGES);
     }
   }
-  ahead = (uint32_t)max(0, r_issue - my_n);
   if (failed && lane == 0) atomicExch(p.status, kStatusTimeout);
 
   // Programmatic dependent launch (layers of one decode step): the streaming
@@ -615,8 +586,8 @@ decode_kernel(DecodeParams p) {
       reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
   // let the next layer's kernel take SMs as soon as this one's CTAs leave them
   if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  uint32_t tile_base = 0, ahead = 0;
-  decode_cta<WARPS, STAGES, kClassic>(p, blockIdx.x, blockIdx.y, blockIdx.z, smem, tile_base, NextLayer{}, ahead);
+  uint32_t tile_base = 0;
+  decode_cta<WARPS, STAGES, kClassic>(p, blockIdx.x, blockIdx.y, blockIdx.z, smem, tile_base);
 }
 
 // ---- the whole multi-layer decode step as ONE launch --------------------------
@@ -645,18 +616,11 @@ decode_step_kernel(DecodeStepParams sp) {
     const int local = b - (int)sp.seq_first[z];
     const int chunks_z = ((int)sp.seq_first[z + 1] - (int)sp.seq_first[z]) / sp.base.kv_heads;
     const int x = local % chunks_z, h = local / chunks_z;
-    uint32_t tile_base = 0, ahead = 0;
+    uint32_t tile_base = 0;
     for (int l = 0; l < sp.layers; l++) {
       __syncthreads();  // the merge buffers of the previous layer are free
       const DecodeParams p = step_layer_params(sp, l);
-      NextLayer nx;
-      if (l + 1 < sp.layers) {
-        nx.storage = p.storage + sp.layer_bytes;
-        nx.storage_w = p.storage_w + sp.layer_bytes;
-        nx.k_new = p.k_new ? p.k_new + sp.kv_layer_stride : nullptr;
-        nx.v_new = p.v_new ? p.v_new + sp.kv_layer_stride : nullptr;
-      }
-      decode_cta<WARPS, STAGES, kStepStream>(p, x, h, z, smem, tile_base, nx, ahead);
+      decode_cta<WARPS, STAGES, kStepStream>(p, x, h, z, smem, tile_base);
     }
     return;
   }
