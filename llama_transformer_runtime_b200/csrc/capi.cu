@@ -73,6 +73,8 @@ struct pa_pool {
   int rope_variant = 1;
   bool no_step_kernel = false;  // pa_pool_set_step_kernel(pool, 0): one kernel per layer
   long long step_launches = 0;  // decode steps that ran as one cooperative launch
+  int* prefill_work = nullptr;  // 64 item counters, one per prefill launch in rotation, zero when idle
+  unsigned prefill_launches = 0;
   pa_pool(int nb, int ms, int mb) : host(nb, ms, mb) {}
 };
 
@@ -125,6 +127,7 @@ int pa_pool_create(pa_pool** out, int device, int num_layers, int num_blocks, in
     alloc((void**)&p->ws_acc, (size_t)kWsItems * pa::decode_ws_acc_floats_per_item() * sizeof(float));
     alloc((void**)&p->ws_ml, (size_t)kWsItems * 2 * pa::kGroup * sizeof(float));
     alloc((void**)&p->ws_count, (size_t)max_seqs * kv_heads * pa::kMaxStepLayers * sizeof(unsigned int));
+    alloc((void**)&p->prefill_work, 64 * sizeof(int));
     alloc((void**)&p->d_status, sizeof(int));
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&p->sm_count, cudaDevAttrMultiProcessorCount, device);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
@@ -149,6 +152,7 @@ int pa_pool_destroy(pa_pool* p) {
     cudaFree(p->ws_acc);
     cudaFree(p->ws_ml);
     cudaFree(p->ws_count);
+    cudaFree(p->prefill_work);
     cudaFree(p->d_status);
   }
   delete p;
@@ -697,6 +701,10 @@ int pa_prefill(pa_pool* p, int layer, const void* q, void* out, float* lse, floa
   a.kv_heads = p->kv_heads;
   a.num_blocks = p->host.num_blocks();
   a.max_blocks_per_seq = p->host.max_blocks_per_seq();
+  // launch i draws items from counter i % 64 and clears counter (i + 32) % 64
+  a.work = p->prefill_work + (p->prefill_launches % 64u);
+  a.work_clear = p->prefill_work + ((p->prefill_launches + 32u) % 64u);
+  p->prefill_launches++;
   PA_CUDA(pa::launch_prefill(a, 1, e.n_q, (cudaStream_t)stream));
   return PA_OK;
 }
@@ -738,6 +746,9 @@ int prefill_strided(pa_pool* p, int layer, const void* q, void* out, float* lse,
   a.kv_heads = p->kv_heads;
   a.num_blocks = p->host.num_blocks();
   a.max_blocks_per_seq = p->host.max_blocks_per_seq();
+  a.work = p->prefill_work + (p->prefill_launches % 64u);
+  a.work_clear = p->prefill_work + ((p->prefill_launches + 32u) % 64u);
+  p->prefill_launches++;
   PA_CUDA(launch_prefill(a, (int)p->batch.size(), n_q, (cudaStream_t)stream));
   return PA_OK;
 }

@@ -144,6 +144,12 @@ struct PrefillParams {
   long long lse_seq_stride;
   float scale_log2;
   int kv_heads, num_blocks, max_blocks_per_seq, causal;
+  // Work distribution of the persistent CTAs: *work counts the items handed
+  // out and must be zero at launch; the launch clears *work_clear, the counter
+  // a later launch will use.  grid_y and n_items are filled by launch_prefill.
+  int* work = nullptr;
+  int* work_clear = nullptr;
+  int grid_y = 0, n_items = 0;
 };
 // n_q: the largest query-row count of any batch sequence
 cudaError_t launch_prefill(const PrefillParams& p, int n_seqs, int n_q, cudaStream_t stream);

@@ -47,8 +47,8 @@ constexpr int kVBytes = kBN * 128;          // 16 KiB
 constexpr int kOffQ = 0;
 constexpr int kOffKV = kOffQ + kQBytes;
 constexpr int kOffBar = kOffKV + kStagesKV * (kKBytes + kVBytes);
-constexpr int kNumBars = 5 + 4 * kStagesKV;  // K and V halves of a stage fill and free separately
-constexpr int kOffMisc = kOffBar + kNumBars * 8;  // tensor-memory base address, abort flag
+constexpr int kNumBars = 9 + 4 * kStagesKV;  // K and V halves of a stage fill and free separately
+constexpr int kOffMisc = kOffBar + kNumBars * 8;  // tensor-memory base address, abort flag, 2 work items
 constexpr int kPrefillUsed = kOffMisc + 16;
 // Two CTAs per SM: 2 * (request + 1 KiB system reserve) must stay below 228 KiB,
 // so there is no room for alignment slack.  The kernel declares no static
@@ -278,6 +278,40 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
   return __all_sync(0xffffffffu, wait_one(bar, parity, abort_flag));
 }
 
+// One unit of work: 128 query rows of one head of one sequence.  Items are
+// numbered so that drawing them in order takes the heaviest query tiles first.
+struct PrefillItem {
+  BatchEntry e;
+  int z, h, row0, rows, pos0, n_tiles, n_blocks;
+  bool valid;
+};
+__device__ __forceinline__ PrefillItem prefill_item(const PrefillParams& p, int w) {
+  PrefillItem it;
+  const int heads = p.kv_heads * kGroup;
+  it.h = w % heads;
+  const int y = (w / heads) % p.grid_y;
+  it.z = w / (heads * p.grid_y);
+  it.e = p.batch[it.z];
+  const int n_q_tiles = (it.e.n_q + kBM - 1) / kBM;
+  const int q_tile = n_q_tiles - 1 - y;
+  it.valid = q_tile >= 0;  // the item space is sized for the sequence with the most query rows
+  it.row0 = q_tile * kBM;
+  it.rows = min(kBM, it.e.n_q - it.row0);
+  it.pos0 = it.e.q_pos0 + it.row0;  // position of row 0
+  // causal: a query at position p sees keys 0..p; otherwise every cached key
+  const int last_pos = p.causal ? min(it.pos0 + it.rows - 1, it.e.kv_len - 1) : it.e.kv_len - 1;
+  it.n_tiles = last_pos / kBN + 1;
+  it.n_blocks = (it.e.kv_len + kBlockTok - 1) / kBlockTok;
+  return it;
+}
+
+// Persistent CTAs (two per SM) draw items from a counter until none is left,
+// so the SMs stay evenly loaded whatever the mix of 1..16-tile items, and a
+// CTA's set-up (tensor-memory allocation, barriers) happens once.  The loader
+// warp draws an item, publishes it to the other warps through a two-slot
+// mailbox and starts on its K/V tiles at once — while the softmax warps are
+// still in the previous item's epilogue.  Barrier phases and ring positions run
+// on across items.
 __global__ void __launch_bounds__(kPrefillThreads, 2)
 prefill_kernel(PrefillParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -293,28 +327,21 @@ prefill_kernel(PrefillParams p) {
   const uint32_t bar_sfree = bar0 + 32;
   const uint32_t bar_kfull = bar0 + 40, bar_kempty = bar_kfull + 8 * kStagesKV;
   const uint32_t bar_vfull = bar_kempty + 8 * kStagesKV, bar_vempty = bar_vfull + 8 * kStagesKV;
+  const uint32_t bar_item_full = bar_vempty + 8 * kStagesKV;  // [2]: the loader has published an item
+  const uint32_t bar_item_empty = bar_item_full + 16;         // [2]: every other warp has read it
   uint32_t* s_tmem_base = reinterpret_cast<uint32_t*>(sm + kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kOffMisc + 4);
+  volatile int* s_item = reinterpret_cast<volatile int*>(sm + kOffMisc + 8);  // [2]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int z = blockIdx.z;
-  const BatchEntry e = p.batch[z];
-  const int n_q_tiles = (e.n_q + kBM - 1) / kBM;
-  // CTAs are dispatched in linear order (x fastest): all heads of the heaviest
-  // query tile first, the lightest tiles last, so the tail of the grid is short
-  const int q_tile = n_q_tiles - 1 - (int)blockIdx.y;
-  const int h = blockIdx.x;
-  if (q_tile < 0) return;  // the grid is sized for the sequence with the most query rows
-  const int row0 = q_tile * kBM;
-  const int rows = min(kBM, e.n_q - row0);
-  const int pos0 = e.q_pos0 + row0;                            // position of row 0
-  // causal: a query at position p sees keys 0..p; otherwise every cached key
-  const int last_pos = p.causal ? min(pos0 + rows - 1, e.kv_len - 1) : e.kv_len - 1;
-  const int n_tiles = last_pos / kBN + 1;
-  const int n_blocks = (e.kv_len + kBlockTok - 1) / kBlockTok;
 
   if (tid == 0) {
     *abort_flag = 0;
+    if (blockIdx.x == 0) *p.work_clear = 0;  // the counter of a launch far from this one
+    for (int s = 0; s < 2; s++) {
+      mbar_init(bar_item_full + 8 * s, 1);
+      mbar_init(bar_item_empty + 8 * s, 1 + kSoftmaxThreads / 32);
+    }
     // the softmax warps arrive once per warp (lane 0 after a warp barrier): 256
     // arrivals on one shared-memory word serialise and cost more than the tile's math
     mbar_init(bar_q, kSoftmaxThreads / 32);
@@ -341,6 +368,24 @@ prefill_kernel(PrefillParams p) {
 
   if (warp == kLoadWarp) {
     // ===================== loader ============================================
+    uint32_t k_cnt = 0, v_cnt = 0;  // tiles put into the K and V rings so far
+    bool ok = true;
+    for (int it = 0; ok; it++) {
+    const int slot = it & 1;
+    if (!wait_or_abort(bar_item_empty + 8 * slot, (uint32_t)(((it >> 1) & 1) ^ 1), abort_flag)) break;
+    int w = 0;
+    if (lane == 0) {
+      w = atomicAdd(p.work, 1);
+      if (w >= p.n_items) w = -1;
+      s_item[slot] = w;
+      mbar_arrive(bar_item_full + 8 * slot);
+    }
+    w = __shfl_sync(0xffffffffu, w, 0);
+    if (w < 0) break;
+    const PrefillItem item = prefill_item(p, w);
+    if (!item.valid) continue;
+    const BatchEntry e = item.e;
+    const int h = item.h, n_tiles = item.n_tiles, n_blocks = item.n_blocks;
     const int32_t* table = p.tables + (size_t)e.seq * p.max_blocks_per_seq;
     const int hk = h / kGroup;
     // K halves are released right after Q K^T, V halves after P V, so the two
@@ -360,12 +405,12 @@ prefill_kernel(PrefillParams p) {
     int k_next = 0, v_next = 0;
     int blk_k = block_of(0), blk_v = blk_k;
     SpinDeadline dl;
-    bool ok = true;
     while (ok && (k_next < n_tiles || v_next < n_tiles)) {
       bool progressed = false;
       if (k_next < n_tiles) {
-        const int st = k_next % kStagesKV;
-        if (__all_sync(0xffffffffu, mbar_test(bar_kempty + 8 * st, (uint32_t)(((k_next / kStagesKV) & 1) ^ 1)))) {
+        const uint32_t ring = k_cnt + (uint32_t)k_next;
+        const int st = (int)(ring % kStagesKV);
+        if (__all_sync(0xffffffffu, mbar_test(bar_kempty + 8 * st, ((ring / kStagesKV) & 1u) ^ 1u))) {
           if (lane == 0) mbar_expect_tx(bar_kfull + 8 * st, kKBytes);
           __syncwarp();
           if (lane < 8)
@@ -377,8 +422,9 @@ prefill_kernel(PrefillParams p) {
         }
       }
       if (v_next < n_tiles) {
-        const int st = v_next % kStagesKV;
-        if (__all_sync(0xffffffffu, mbar_test(bar_vempty + 8 * st, (uint32_t)(((v_next / kStagesKV) & 1) ^ 1)))) {
+        const uint32_t ring = v_cnt + (uint32_t)v_next;
+        const int st = (int)(ring % kStagesKV);
+        if (__all_sync(0xffffffffu, mbar_test(bar_vempty + 8 * st, ((ring / kStagesKV) & 1u) ^ 1u))) {
           if (lane == 0) mbar_expect_tx(bar_vfull + 8 * st, kVBytes);
           __syncwarp();
           if (lane < 8)
@@ -403,14 +449,34 @@ prefill_kernel(PrefillParams p) {
         }
       }
     }
+    k_cnt += (uint32_t)n_tiles;
+    v_cnt += (uint32_t)n_tiles;
+    }
   } else if (warp == kMmaWarp) {
     // ===================== MMA issue =========================================
     constexpr uint32_t kIdescQK = idesc_bf16(kBM, kBN, false);
     constexpr uint32_t kIdescPV = idesc_bf16(kBM, kHeadDim, true);
-    bool ok = wait_or_abort(bar_q, 0, abort_flag);
+    uint32_t t_run = 0;  // tiles of all items so far: ring positions and barrier phases run on
+    bool ok = true;
+    int n_items_done = 0;
+    for (int it = 0; ok; it++) {
+    const int slot = it & 1;
+    if (!wait_or_abort(bar_item_full + 8 * slot, (uint32_t)((it >> 1) & 1), abort_flag)) break;
+    const int w = s_item[slot];
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_item_empty + 8 * slot);
+    if (w < 0) break;
+    const PrefillItem item = prefill_item(p, w);
+    if (!item.valid) continue;
+    const int n_tiles = item.n_tiles;
+    // the softmax warps have read the previous item's last scores: S may be overwritten
+    if (n_items_done > 0 && !wait_or_abort(bar_sfree, (t_run - 1u) & 1u, abort_flag)) break;
+    ok = wait_or_abort(bar_q, (uint32_t)(n_items_done & 1), abort_flag);
+    n_items_done++;
     auto issue_qk = [&](int kt) {
-      const int st = kt % kStagesKV;
-      if (!wait_or_abort(bar_kfull + 8 * st, (uint32_t)((kt / kStagesKV) & 1), abort_flag)) return false;
+      const uint32_t ring = t_run + (uint32_t)kt;
+      const int st = (int)(ring % kStagesKV);
+      if (!wait_or_abort(bar_kfull + 8 * st, (ring / kStagesKV) & 1u, abort_flag)) return false;
       tc_fence_after();
       if (elect_one()) {
         const uint32_t sK = sKV + st * (kKBytes + kVBytes);
@@ -426,14 +492,15 @@ prefill_kernel(PrefillParams p) {
     };
     if (ok) ok = issue_qk(0);
     for (int kt = 0; ok && kt < n_tiles; kt++) {
-      const int st = kt % kStagesKV;
+      const uint32_t ring = t_run + (uint32_t)kt;
+      const int st = (int)(ring % kStagesKV);
       // S(kt) is in the softmax threads' registers: the next Q K^T may overwrite it
       if (kt + 1 < n_tiles) {
-        if (!wait_or_abort(bar_sfree, (uint32_t)(kt & 1), abort_flag)) break;
-        if (!issue_qk(kt + 1)) break;
+        if (!wait_or_abort(bar_sfree, ring & 1u, abort_flag)) { ok = false; break; }
+        if (!issue_qk(kt + 1)) { ok = false; break; }
       }
-      if (!wait_or_abort(bar_p, (uint32_t)(kt & 1), abort_flag)) break;
-      if (!wait_or_abort(bar_vfull + 8 * st, (uint32_t)((kt / kStagesKV) & 1), abort_flag)) break;
+      if (!wait_or_abort(bar_p, ring & 1u, abort_flag)) { ok = false; break; }
+      if (!wait_or_abort(bar_vfull + 8 * st, (ring / kStagesKV) & 1u, abort_flag)) { ok = false; break; }
       tc_fence_after();
       if (elect_one()) {
         const uint32_t sV = sKV + st * (kKBytes + kVBytes) + kKBytes;
@@ -446,6 +513,8 @@ prefill_kernel(PrefillParams p) {
       }
       __syncwarp();
     }
+    t_run += (uint32_t)n_tiles;
+    }
   } else {
     // ===================== softmax / epilogue ==================================
     // Warp w works on TMEM lanes [32*(w&3) + 16*(w>>2), +16) in the 16x256b
@@ -457,7 +526,23 @@ prefill_kernel(PrefillParams p) {
     const uint32_t lane_base = (uint32_t)first_row << 16;
     const int rA = first_row + (lane >> 2), rB = rA + 8;
     const int cq = (lane & 3) * 2;
-    // Q tile -> shared memory (K-major, swizzled): thread = (row, half row)
+    uint32_t t_run = 0;
+    int n_items_done = 0;
+    bool ok = true;
+    for (int it = 0; ok; it++) {
+    const int slot = it & 1;
+    if (!wait_or_abort(bar_item_full + 8 * slot, (uint32_t)((it >> 1) & 1), abort_flag)) break;
+    const int w = s_item[slot];
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_item_empty + 8 * slot);
+    if (w < 0) break;
+    const PrefillItem item = prefill_item(p, w);
+    if (!item.valid) continue;
+    const BatchEntry e = item.e;
+    const int z = item.z, h = item.h, row0 = item.row0, rows = item.rows, pos0 = item.pos0, n_tiles = item.n_tiles;
+    n_items_done++;
+    // Q tile -> shared memory (K-major, swizzled): thread = (row, half row).  Every
+    // Q K^T of the previous item is complete: this thread has seen its last scores.
     {
       const int r = tid >> 1, c0 = (tid & 1) * 4;
       uint4 v[4];
@@ -481,9 +566,8 @@ prefill_kernel(PrefillParams p) {
 
     const int qposA = pos0 + rA, qposB = pos0 + rB;
     float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
-    bool ok = true;
     for (int kt = 0; kt < n_tiles; kt++) {
-      if (!wait_or_abort(bar_s, (uint32_t)(kt & 1), abort_flag)) { ok = false; break; }
+      if (!wait_or_abort(bar_s, (t_run + (uint32_t)kt) & 1u, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int key0 = kt * kBN;
       const bool need_mask = (p.causal && key0 + kBN - 1 > pos0) || (key0 + kBN > e.kv_len);
@@ -575,7 +659,7 @@ prefill_kernel(PrefillParams p) {
 
       // P of the previous tile must have been consumed, O must be quiescent
       if (kt > 0) {
-        if (!wait_or_abort(bar_pv, (uint32_t)((kt - 1) & 1), abort_flag)) { ok = false; break; }
+        if (!wait_or_abort(bar_pv, (t_run + (uint32_t)kt - 1u) & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
         if (any_corr) {
           uint32_t o[32];
@@ -609,7 +693,8 @@ prefill_kernel(PrefillParams p) {
     }
 
     // epilogue: O / sum -> bf16, [tokens, heads*64] layout (or the caller's strides)
-    if (ok && wait_or_abort(bar_pv, (uint32_t)((n_tiles - 1) & 1), abort_flag)) {
+    if (ok) ok = wait_or_abort(bar_pv, (t_run + (uint32_t)n_tiles - 1u) & 1u, abort_flag);
+    if (ok) {
       tc_fence_after();
       lA += __shfl_xor_sync(0xffffffffu, lA, 1);
       lB += __shfl_xor_sync(0xffffffffu, lB, 1);
@@ -640,6 +725,8 @@ prefill_kernel(PrefillParams p) {
         if (rB < rows) lrow[rB] = lB > 0.f ? kLn2 * (mB + log2f(lB)) : -INFINITY;
       }
     }
+    t_run += (uint32_t)n_tiles;
+    }
   }
 
   // ---- common exit: release tensor memory -----------------------------------
@@ -665,8 +752,15 @@ cudaError_t launch_prefill(const PrefillParams& p, int n_seqs, int n_q, cudaStre
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  dim3 grid(p.kv_heads * kGroup, (n_q + kBM - 1) / kBM, n_seqs);
-  prefill_kernel<<<grid, kPrefillThreads, kPrefillSmem, stream>>>(p);
+  static int sm_count[64] = {};
+  if (dev >= 0 && dev < 64 && sm_count[dev] == 0)
+    cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+  const int sms = (dev >= 0 && dev < 64 && sm_count[dev] > 0) ? sm_count[dev] : 148;
+  PrefillParams q = p;
+  q.grid_y = (n_q + kBM - 1) / kBM;
+  q.n_items = p.kv_heads * kGroup * q.grid_y * n_seqs;
+  const int ctas = q.n_items < 2 * sms ? q.n_items : 2 * sms;  // two CTAs per SM stay resident
+  prefill_kernel<<<ctas, kPrefillThreads, kPrefillSmem, stream>>>(q);
   return cudaGetLastError();
 }
 

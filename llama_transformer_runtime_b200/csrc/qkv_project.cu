@@ -13,8 +13,9 @@
 //
 // Grid (column tile, layer): a CTA owns 32 adjacent output columns (64 bytes of
 // every weight row) of the concatenated [q | k | v] output and walks all K rows:
-// warp w, lane (kr, c) reads the 16-byte chunk c of rows 64 j + 8 w + kr, 16
-// independent loads in flight per thread (64 KiB per CTA).  x sits in shared
+// warp w, lane (kr, c) reads the 16-byte chunk c of rows 64 j + 8 w + kr, a
+// rolling window of 16 independent loads in flight per thread (64 KiB per CTA),
+// the first of them issued before x is staged.  x sits in shared
 // memory as bf16.  Partial sums are reduced over the 8 row lanes by shuffles
 // and over the 8 warps through shared memory in a fixed order, so the result
 // does not depend on scheduling.
@@ -55,6 +56,15 @@ __global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kr = lane >> 2, c = lane & 3;
 
+  // the first 16 weight loads go out before anything else: they do not depend on x
+  const uint4* wp = reinterpret_cast<const uint4*>(w + (size_t)(warp * 8 + kr) * n + col0) + c;
+  const size_t step = (size_t)64 * n / 8;  // 64 rows further, in 16-byte units
+  const int n_steps = p.hidden / 64;
+  uint4 wv[16];
+#pragma unroll
+  for (int u = 0; u < 16; u++)
+    if (u < n_steps) wv[u] = __ldg(wp + (size_t)u * step);
+
   // x rows of this layer -> shared memory (rows beyond p.rows are zero)
   const __nv_bfloat16* x = p.x + (size_t)layer * p.x_layer_stride;
   for (int i = threadIdx.x; i < ROWS * (p.hidden / 8); i += kThreads) {
@@ -71,14 +81,8 @@ __global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
 #pragma unroll
     for (int i = 0; i < 8; i++) acc[r][i] = 0.f;
 
-  const uint4* wp = reinterpret_cast<const uint4*>(w + (size_t)(warp * 8 + kr) * n + col0) + c;
-  const size_t step = (size_t)64 * n / 8;  // 64 rows further, in 16-byte units
-  const int n_steps = p.hidden / 64;
+  // rolling window: as soon as a register's row is consumed, the row 16 steps on is requested
   for (int j0 = 0; j0 < n_steps; j0 += 16) {
-    uint4 wv[16];
-#pragma unroll
-    for (int u = 0; u < 16; u++)
-      if (j0 + u < n_steps) wv[u] = __ldg(wp + (size_t)(j0 + u) * step);
 #pragma unroll
     for (int u = 0; u < 16; u++) {
       if (j0 + u >= n_steps) break;
@@ -91,6 +95,7 @@ __global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
         wf[2 * i] = f.x;
         wf[2 * i + 1] = f.y;
       }
+      if (j0 + u + 16 < n_steps) wv[u] = __ldg(wp + (size_t)(j0 + u + 16) * step);
 #pragma unroll
       for (int r = 0; r < ROWS; r++) {
         const float xv = __bfloat162float(sx[r][k]);
