@@ -61,9 +61,10 @@ def measured_peak():
     return 6650.0, "fallback"
 
 
-# ncu capture of decode_kernel (profiles/): dram read+write bytes per launch for
-# the workload, or None when not captured.
-NCU_TRAFFIC_BYTES = {"decode128k": 272993536, "decode4k": None}  # 268.55 MB read + 4.45 MB written
+# ncu capture (profiles/): dram read+write bytes per layer of the workload, or
+# None when not captured.
+# per layer: the 2-layer decode_step_kernel capture read 537.09 MB and wrote 6.00 MB
+NCU_TRAFFIC_BYTES = {"decode128k": 271544320, "decode4k": None}
 
 
 class ClockSampler:
@@ -358,7 +359,7 @@ def run_ours(args):
                           "how": f"CUDA events around the step's one launch (all {LAYERS} layers, append fused in)",
                           "traffic": (NCU_TRAFFIC_BYTES[args.workload] * LAYERS
                                       if NCU_TRAFFIC_BYTES.get(args.workload) else None),
-                          "traffic_note": "ncu capture of the 1-layer decode_kernel launch x layers"}
+                          "traffic_note": "ncu capture of a 2-layer decode_step_kernel launch, per layer x layers"}
                          if world == 1 and LAYERS >= 2 else
                          {"bound": "hbm", "kernel": "decode_kernel", "achieved": round(achieved, 1),
                           "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
