@@ -842,6 +842,48 @@ int pa_pool_set_step_kernel(pa_pool* p, int enable) {
   return PA_OK;
 }
 
+int pa_qkv_project_append(pa_pool* p, int layer, const void* x, const void* wq, const void* wk, const void* wv,
+                          const float* cos_table, const float* sin_table, void* q_out, int hidden, void* stream) {
+  if (!p || !x || !wq || !wk || !wv || !cos_table || !sin_table || !q_out)
+    return fail(PA_ERR_INVALID_ARG, "pa_qkv_project_append: NULL argument");
+  if (p->device < 0) return fail(PA_ERR_STATE, "pa_qkv_project_append: host-only pool");
+  if (layer < 0 || layer >= p->num_layers) return fail(PA_ERR_INVALID_ARG, "pa_qkv_project_append: layer %d out of range", layer);
+  if (p->batch.empty()) return fail(PA_ERR_STATE, "pa_qkv_project_append: no active batch (call pa_batch_set)");
+  if (hidden < 64 || hidden % 64 != 0) return fail(PA_ERR_UNSUPPORTED, "pa_qkv_project_append: hidden must be a multiple of 64");
+  if (p->kv_heads % 4 != 0)
+    return fail(PA_ERR_UNSUPPORTED, "pa_qkv_project_append: needs a multiple of 4 KV heads per pool (256-column tiles)");
+  int rows = 0;
+  for (const auto& e : p->batch) {
+    if (e.n_q != e.n_new || e.q_row_off != e.kv_row_off)
+      return fail(PA_ERR_UNSUPPORTED, "pa_qkv_project_append: every sequence must bring the same rows as queries and as new tokens");
+    rows += e.n_new;
+  }
+  if (rows == 0) return PA_OK;
+  DeviceGuard g(p->device);
+  pa::QkvGemmParams a;
+  a.x = (const __nv_bfloat16*)x;
+  a.wq = (const __nv_bfloat16*)wq;
+  a.wk = (const __nv_bfloat16*)wk;
+  a.wv = (const __nv_bfloat16*)wv;
+  a.q_out = (__nv_bfloat16*)q_out;
+  a.storage = p->storage + (size_t)layer * p->layer_bytes;
+  a.tables = p->d_tables;
+  a.batch = p->d_batch;
+  a.cos_table = cos_table;
+  a.sin_table = sin_table;
+  a.status = p->d_status;
+  a.rows = rows;
+  a.hidden = hidden;
+  a.q_cols = p->kv_heads * pa::kGroup * pa::kHeadDim;
+  a.kv_cols = p->kv_heads * pa::kHeadDim;
+  a.kv_heads = p->kv_heads;
+  a.n_seqs = (int)p->batch.size();
+  a.num_blocks = p->host.num_blocks();
+  a.max_blocks_per_seq = p->host.max_blocks_per_seq();
+  PA_CUDA(pa::launch_qkv_gemm(a, (cudaStream_t)stream));
+  return PA_OK;
+}
+
 int pa_pool_step_launches(pa_pool* p, long long* count) {
   if (!p || !count) return fail(PA_ERR_INVALID_ARG, "pa_pool_step_launches: NULL argument");
   *count = p->step_launches;

@@ -154,6 +154,23 @@ struct PrefillParams {
 // n_q: the largest query-row count of any batch sequence
 cudaError_t launch_prefill(const PrefillParams& p, int n_seqs, int n_q, cudaStream_t stream);
 
+// Projection GEMM with RoPE + paged append epilogue (qkv_gemm.cu).
+struct QkvGemmParams {
+  const __nv_bfloat16* x;      // [rows, hidden]
+  const __nv_bfloat16* wq;     // [hidden, q_cols] row-major
+  const __nv_bfloat16* wk;     // [hidden, kv_cols]
+  const __nv_bfloat16* wv;     // [hidden, kv_cols]
+  __nv_bfloat16* q_out;        // [rows, q_cols], RoPE applied
+  char* storage;               // the layer's cache
+  const int32_t* tables;
+  const BatchEntry* batch;
+  const float* cos_table;
+  const float* sin_table;
+  int* status;
+  int rows, hidden, q_cols, kv_cols, kv_heads, n_seqs, num_blocks, max_blocks_per_seq;
+};
+cudaError_t launch_qkv_gemm(const QkvGemmParams& p, cudaStream_t stream);
+
 struct MergeParams {
   const float* o_parts;    // [n_parts][rows][64]
   const float* lse_parts;  // [n_parts][rows]

@@ -141,6 +141,12 @@ class KVPool:
                                    _ptr(q_rot), _ptr(out), out_stride, out_layer_stride, _ptr(lse),
                                    scale, stream))
 
+    def qkv_project_append(self, layer: int, x, wq, wk, wv, cos, sin, q_out, hidden: int = 2048,
+                           stream: int = 0) -> None:
+        """Projections of the batch's new tokens on the tensor cores, RoPE and cache append fused in."""
+        check(lib().pa_qkv_project_append(self._h, layer, _ptr(x), _ptr(wq), _ptr(wk), _ptr(wv), _ptr(cos),
+                                          _ptr(sin), _ptr(q_out), hidden, stream))
+
     def prefill(self, layer: int, q, out, lse=None, scale: float = 0.125, stream: int = 0) -> None:
         check(lib().pa_prefill(self._h, layer, _ptr(q), _ptr(out), _ptr(lse), scale, stream))
 

@@ -71,3 +71,92 @@ def test_qkv_project_rejects_prefill_shapes(cuda):
     ok = torch.zeros(1, 9, 512, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(PagedAttentionError):
         paged.qkv_project(t, w, wk, wk, o, ok, ok, 9, 1)
+
+
+def _project_append_case(rng, position, tokens):
+    """Cache holds `position` tokens; `tokens` new rows are projected, rotated and appended by ONE
+    tcgen05 GEMM launch.  Returns GPU results and the oracle chain (GEMM -> bf16 -> RoPE -> placement)."""
+    from tests.gpu_helpers import f32_dev, fill_cache
+    L = position + tokens
+    cos, sin = orc.build_rope_tables(L)
+    nb = (L + 15) // 16 + 4
+    pool = paged.KVPool(1, nb, 8, 1)
+    pool.set_free_order(rng.permutation(nb))
+    s = pool.create_seq()
+    k_old = orc.randn_bf16(rng, (8, position, 64), 0.5)
+    v_old = orc.randn_bf16(rng, (8, position, 64), 0.5)
+    if position:
+        fill_cache(pool, 0, s, k_old, v_old)
+    x = orc.randn_bf16(rng, (tokens, 2048))
+    wq = orc.randn_bf16(rng, (2048, 2048), 0.03)
+    wk = orc.randn_bf16(rng, (2048, 512), 0.03)
+    wv = orc.randn_bf16(rng, (2048, 512), 0.03)
+    pool.reserve(s, L)
+    pool.batch_set([s], [tokens])
+    q_out = torch.full((tokens, 2048), 3.0, dtype=torch.bfloat16, device=DEV)
+    pool.qkv_project_append(0, to_dev(x), to_dev(wq), to_dev(wk), to_dev(wv), f32_dev(cos), f32_dev(sin), q_out)
+    torch.cuda.synchronize()
+    pool.check()
+    gk = torch.zeros(8, L, 64, dtype=torch.bfloat16, device=DEV)
+    gv = torch.zeros_like(gk)
+    pool.gather_kv(0, s, gk, gv, L)
+    torch.cuda.synchronize()
+    got = (to_u16(q_out), to_u16(gk), to_u16(gv))
+    pool.close()
+    # oracle chain
+    q_lin = orc.gemm_bf16(x, wq).reshape(tokens, 32, 64)
+    k_lin = orc.gemm_bf16(x, wk).reshape(tokens, 8, 64)
+    v_lin = orc.gemm_bf16(x, wv).reshape(tokens, 8, 64)
+    q_want = orc.rope(q_lin, cos, sin, position, 1, out_token_major=True).reshape(tokens, 2048)
+    k_want = np.concatenate([k_old, orc.rope(k_lin, cos, sin, position, 1)], 1)
+    v_want = np.concatenate([v_old, orc.transpose_v(v_lin)], 1)
+    return got, (q_want, k_want, v_want), (x, wq, wk, wv, cos, sin)
+
+
+def rotated_close(got_u16, want_u16, what):
+    """RoPE mixes two GEMM outputs, each within one bf16 ulp of the oracle's: allow two ulps of
+    the larger partner (bounded by 2^-6 of 4 sigma here) and ask that most values are bit-equal."""
+    g = orc.bf16_to_f32(got_u16).astype(np.float64)
+    w = orc.bf16_to_f32(want_u16).astype(np.float64)
+    tol = np.abs(w) * 2.0 ** -6 + 0.05
+    bad = np.abs(g - w) > tol
+    assert not bad.any(), f"{what}: {int(bad.sum())} of {bad.size} differ, worst {np.abs(g - w).max()}"
+    assert float((got_u16 == want_u16).mean()) > 0.85, f"{what}: too few bit-equal values"
+
+
+@pytest.mark.parametrize("position,tokens", [(0, 128), (0, 37), (45, 200), (16, 300)])
+def test_qkv_project_append_vs_oracle_chain(cuda, position, tokens):
+    rng = np.random.default_rng(600 + position + tokens)
+    (q, k, v), (qw, kw, vw), _ = _project_append_case(rng, position, tokens)
+    # tokens that were already in the cache are untouched, bit for bit
+    assert np.array_equal(k[:, :position], kw[:, :position]) and np.array_equal(v[:, :position], vw[:, :position])
+    rotated_close(q, qw, "rotated Q")
+    rotated_close(k[:, position:], kw[:, position:], "rotated K in the cache")
+    bf16_close(v[:, position:], vw[:, position:], "V in the cache")
+
+
+@pytest.mark.skipif(not orc.ref_available(), reason="reference kernels were not built")
+def test_qkv_project_append_vs_reference_chain(cuda):
+    """Against the reference's own kernels: its GEMMs, then its RoPE kernels on their outputs."""
+    rng = np.random.default_rng(650)
+    tokens = 200
+    (q, k, v), _, (x, wq, wk, wv, cos, sin) = _project_append_case(rng, 0, tokens)
+    from tests.gpu_helpers import f32_dev
+    r = orc.ref()
+    xd = to_dev(x)
+    lin = {}
+    for name, w, n in (("q", wq, 2048), ("k", wk, 512), ("v", wv, 512)):
+        o = torch.zeros(tokens, n, dtype=torch.bfloat16, device=DEV)
+        assert r.ref_gemm(xd.data_ptr(), to_dev(w).data_ptr(), o.data_ptr(), tokens, n, 2048) == 0
+        lin[name] = o
+    qo = torch.zeros(32, tokens, 64, dtype=torch.bfloat16, device=DEV)
+    ko = torch.zeros(8, tokens, 64, dtype=torch.bfloat16, device=DEV)
+    vo = torch.zeros(8, tokens, 64, dtype=torch.bfloat16, device=DEV)
+    cd, sd = f32_dev(cos), f32_dev(sin)
+    r.ref_rope_qkv(lin["q"].data_ptr(), qo.data_ptr(), lin["k"].data_ptr(), ko.data_ptr(), lin["v"].data_ptr(),
+                   vo.data_ptr(), cd.data_ptr(), sd.data_ptr(), tokens, 0)
+    torch.cuda.synchronize()
+    q_ref = to_u16(qo).transpose(1, 0, 2).reshape(tokens, 2048)  # [heads, tokens, 64] -> token-major
+    rotated_close(q, q_ref, "rotated Q against the reference chain")
+    rotated_close(k, to_u16(ko), "rotated K against the reference chain")
+    bf16_close(v, to_u16(vo), "V against the reference chain")
