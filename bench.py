@@ -911,6 +911,151 @@ def run_qkv(args):
 
 
 
+def run_qkv_prefill(args):
+    """Q/K/V projections of a 2048-token prompt, 16 layers: x [2048, 2048] times Wq, Wk, Wv, RoPE on Q and
+    K, K/V appended to the paged cache.  Ours: one tcgen05 GEMM launch per layer with RoPE and the append
+    as its epilogue.  Reference arm: its 3 GEMM launches (a device synchronisation after each, as
+    Attention::forward does), its RoPE/transpose kernels and the strided form of its append copies."""
+    import torch
+
+    rank, local_rank, world = dist_env()
+    if rank != 0:
+        return  # independent replicas only
+    torch.cuda.set_device(local_rank)
+    dev = f"cuda:{local_rank}"
+    S, H, NQ, NKV = PREFILL_TOKENS, 2048, Q_HEADS * D, KV_HEADS * D
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(123)
+    x = torch.randn(LAYERS, S, H, generator=gen, device=dev).to(torch.bfloat16)
+    wq = (torch.randn(LAYERS, H, NQ, generator=gen, device=dev) * 0.03).to(torch.bfloat16)
+    wk = (torch.randn(LAYERS, H, NKV, generator=gen, device=dev) * 0.03).to(torch.bfloat16)
+    wv = (torch.randn(LAYERS, H, NKV, generator=gen, device=dev) * 0.03).to(torch.bfloat16)
+    x_host = x.cpu().pin_memory()
+    q_rot = torch.zeros(LAYERS, S, NQ, dtype=torch.bfloat16, device=dev)
+    q_host = torch.zeros(S, NQ, dtype=torch.bfloat16).pin_memory()
+    burst, sustained, kind = measured_tflops()
+    flops_layer = 2.0 * S * H * (NQ + 2 * NKV)
+
+    if args.impl == "reference":
+        from oracle import oracle as orc
+        if not orc.ref_available():
+            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libref.so was not built"}))
+            return
+        ref = orc.ref()
+        cos_h, sin_h = orc.build_rope_tables(S)
+        cos, sin = torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev)
+        ql = torch.empty(S, NQ, dtype=torch.bfloat16, device=dev)
+        kl = torch.empty(S, NKV, dtype=torch.bfloat16, device=dev)
+        vl = torch.empty(S, NKV, dtype=torch.bfloat16, device=dev)
+        qf = torch.empty(Q_HEADS, S, D, dtype=torch.bfloat16, device=dev)
+        kf = torch.empty(KV_HEADS, S, D, dtype=torch.bfloat16, device=dev)
+        vf = torch.empty_like(kf)
+        kc = torch.zeros(LAYERS, KV_HEADS, S, D, dtype=torch.bfloat16, device=dev)
+        vc = torch.zeros_like(kc)
+
+        def step():
+            for l in range(LAYERS):
+                for w, o, n in ((wq, ql, NQ), (wk, kl, NKV), (wv, vl, NKV)):
+                    ref.ref_gemm(x[l].data_ptr(), w[l].data_ptr(), o.data_ptr(), S, n, H)
+                    torch.cuda.synchronize()
+                ref.ref_rope_qkv(ql.data_ptr(), qf.data_ptr(), kl.data_ptr(), kf.data_ptr(), vl.data_ptr(),
+                                 vf.data_ptr(), cos.data_ptr(), sin.data_ptr(), S, 0)
+                ref.ref_append_strided(kc[l].data_ptr(), vc[l].data_ptr(), kf.data_ptr(), vf.data_ptr(), S, 0, S, None)
+        launches_per_step = LAYERS * 8
+    else:
+        from llama_transformer_runtime_b200 import paged
+        nb = (S + BLOCK - 1) // BLOCK
+        num_blocks = nb + nb // 4 + 8
+        pool = paged.KVPool(LAYERS, num_blocks, KV_HEADS, 1, nb + 1, device=local_rank)
+        pool.set_free_order(np.random.default_rng(5).permutation(num_blocks))
+        seq = pool.create_seq()
+        pool.reserve(seq, S)
+        pool.batch_set([seq], [S])
+        cos_h, sin_h = paged.build_rope_tables(S)
+        cos, sin = torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev)
+
+        # weights are repacked once, at load time, into the tile image the GEMM bulk-copies
+        pq, pk, pv = (paged.pack_projection_weights(w) for w in (wq, wk, wv))
+        torch.cuda.synchronize()
+
+        def step():
+            # the same prompt positions are rewritten every step (the table is fixed)
+            for l in range(LAYERS):
+                pool.qkv_project_append(l, x[l], pq[l], pk[l], pv[l], cos, sin, q_rot[l], H)
+        launches_per_step = LAYERS
+
+    def e2e_step():
+        x.copy_(x_host, non_blocking=True)
+        step()
+        if args.impl != "reference":
+            q_host.copy_(q_rot[LAYERS - 1], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def timed(fn, n):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    m0 = sampler.mark()
+    for _ in range(args.warmup):
+        step()
+    ms = timed(step, args.steps) / args.steps
+    ms_e2e = timed(e2e_step, args.steps) / args.steps
+    value = flops_layer * LAYERS / (ms * 1e-3) / 1e12
+    line = {
+        "metric": "qkv_project_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
+        "us_per_layer": round(ms * 1e3 / LAYERS, 2), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"qkv_projection_rope_append_{S}tokens_x{LAYERS}layers", "tokens": S, "hidden": H,
+                   "q_cols": NQ, "kv_cols": NKV, "layers": LAYERS, "flops": "2*tokens*hidden*(q_cols+2*kv_cols) per layer",
+                   "l2": "per-layer inputs and weights are distinct tensors (20.6 MB per layer, 330 MB per step)"},
+        "e2e": {"value": round(flops_layer * LAYERS / (ms_e2e * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": x_host.numel() * 2,
+                "d2h_bytes_per_step": 0 if args.impl == "reference" else q_host.numel() * 2,
+                "ms_per_step": round(ms_e2e, 4)},
+        "gpu_launches": launches_per_step * args.steps,
+    }
+    if args.impl == "reference":
+        line["impl"] = "reference"
+        line["cpu_baseline"] = {"value": line["value"], "unit": "TFLOP/s", "cores": 0, "kind": "reference",
+                                "sample": "whole workload on the GPU: the reference has no CPU implementation of its GEMMs"}
+        line["e2e"]["h2d_bytes_per_step"] = 0
+        line["e2e"]["value"] = line["value"]
+    else:
+        line["roofline"] = {"bound": "tensor", "kernel": "qkv_gemm_kernel", "achieved": round(value, 2), "peak": burst,
+                            "unit": "TFLOP/s", "frac": round(value / burst, 4),
+                            "peak_source": f"of {kind} (cuBLAS bf16 burst)", "us_per_launch": round(ms * 1e3 / LAYERS, 2),
+                            "flops_per_launch": flops_layer, "traffic": None}
+        pool.check()
+        # CPU baseline and check: the oracle's GEMM on the first 64 rows of layer 0, q columns
+        from oracle import oracle as orc
+        import time
+        rows = 64
+        xs = x_host[0, :rows].contiguous().view(torch.int16).numpy().view(np.uint16)
+        ws = wq[0].cpu().view(torch.int16).numpy().view(np.uint16)
+        t0 = time.perf_counter()
+        lin = orc.gemm_bf16(xs, ws)
+        dt = time.perf_counter() - t0
+        want = orc.rope(lin.reshape(rows, Q_HEADS, D), cos_h, sin_h, 0, 1, out_token_major=True).reshape(rows, NQ)
+        got = q_rot[0, :rows].cpu().view(torch.int16).numpy().view(np.uint16)
+        err = float(np.abs(orc.bf16_to_f32(got) - orc.bf16_to_f32(want)).max())
+        line["cpu_baseline"] = {"value": round(2.0 * rows * H * NQ / dt / 1e12, 5), "unit": "TFLOP/s",
+                                "cores": orc.num_threads(), "kind": "port",
+                                "sample": f"{rows} rows x {NQ} columns of layer 0 (double accumulation), {dt:.2f} s",
+                                "gpu_vs_cpu_max_abs_err": err}
+        pool.close()
+    line["clocks"] = sampler.stop(m0, None)
+    print(json.dumps(line), flush=True)
+
+
 def prefill_flops(S: int) -> float:
     """Causal-useful flops of one layer: 4 * Hq * D * S (S + 1) / 2."""
     return 4.0 * Q_HEADS * D * S * (S + 1) / 2.0
@@ -1105,7 +1250,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode128k", choices=sorted(WORKLOADS) + ["prefill2k", "batch64", "qkv_decode"])
+    ap.add_argument("--workload", default="decode128k", choices=sorted(WORKLOADS) + ["prefill2k", "batch64", "qkv_decode", "qkv_prefill"])
     ap.add_argument("--seqs", type=int, default=64, help="batch64: number of sequences")
     ap.add_argument("--layers", type=int, default=16, help="fewer layers make a small case for profiling")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
@@ -1120,6 +1265,8 @@ def main():
     LAYERS = args.layers
     if args.workload == "qkv_decode":
         run_qkv(args)
+    elif args.workload == "qkv_prefill":
+        run_qkv_prefill(args)
     elif args.workload == "prefill2k":
         run_prefill(args)
     elif args.workload == "batch64":

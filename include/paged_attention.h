@@ -298,12 +298,18 @@ int pa_qkv_project(const void* x, const void* wq, const void* wk, const void* wv
                    int64_t x_layer_stride, int64_t wq_layer_stride, int64_t wkv_layer_stride,
                    int64_t q_layer_stride, int64_t kv_layer_stride, void* stream);
 
+/* One-time repacking of a row-major [hidden, cols] bf16 weight matrix (the
+ * reference's layout) into the tile image pa_qkv_project_append copies with one
+ * bulk copy per k-step: per 64 rows and 64 columns an 8 KiB block of 128-byte
+ * rows, 16-byte chunk c of row r at c ^ (r & 7).  Same size as the input, must
+ * not alias it.  Done at model load; no counterpart in the reference. */
+int pa_pack_projection_weights(const void* w, void* packed, int hidden, int cols, void* stream);
 /* The same projections for the new tokens of the active batch (prefill shapes),
  * on the tensor cores, with RoPE and the cache append as the epilogue: one launch
  * for what the reference does with 3 GEMM launches, 3 RoPE/transpose kernels and
  * 2*8*tokens copies per layer (src/runtime/attention.cu:138-262).  x [rows, hidden]
  * in batch order (rows = the batch's new tokens, which must also be its query
- * rows); weights as above; q_out [rows, q_heads*64] receives the rotated queries,
+ * rows); weights packed by pa_pack_projection_weights; q_out [rows, q_heads*64] receives the rotated queries,
  * K (rotated) and V go straight into the layer's paged cache.  Needs 4 or 8 KV
  * heads in the pool. */
 int pa_qkv_project_append(pa_pool* pool, int layer, const void* x, const void* wq, const void* wk,

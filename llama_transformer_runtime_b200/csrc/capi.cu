@@ -73,6 +73,8 @@ struct pa_pool {
   int rope_variant = 1;
   bool no_step_kernel = false;  // pa_pool_set_step_kernel(pool, 0): one kernel per layer
   long long step_launches = 0;  // decode steps that ran as one cooperative launch
+  void* x_pack = nullptr;       // activations in tile-image form for pa_qkv_project_append (grown on demand)
+  size_t x_pack_bytes = 0;
   int* prefill_work = nullptr;  // 64 item counters, one per prefill launch in rotation, zero when idle
   unsigned prefill_launches = 0;
   pa_pool(int nb, int ms, int mb) : host(nb, ms, mb) {}
@@ -153,6 +155,7 @@ int pa_pool_destroy(pa_pool* p) {
     cudaFree(p->ws_ml);
     cudaFree(p->ws_count);
     cudaFree(p->prefill_work);
+    cudaFree(p->x_pack);
     cudaFree(p->d_status);
   }
   delete p;
@@ -842,6 +845,14 @@ int pa_pool_set_step_kernel(pa_pool* p, int enable) {
   return PA_OK;
 }
 
+int pa_pack_projection_weights(const void* w, void* packed, int hidden, int cols, void* stream) {
+  if (!w || !packed || w == packed) return fail(PA_ERR_INVALID_ARG, "pa_pack_projection_weights: NULL or aliased argument");
+  if (hidden < 64 || hidden % 64 != 0 || cols < 64 || cols % 64 != 0)
+    return fail(PA_ERR_UNSUPPORTED, "pa_pack_projection_weights: hidden and cols must be multiples of 64");
+  PA_CUDA(pa::launch_pack_weights(w, packed, hidden, cols, (cudaStream_t)stream));
+  return PA_OK;
+}
+
 int pa_qkv_project_append(pa_pool* p, int layer, const void* x, const void* wq, const void* wk, const void* wv,
                           const float* cos_table, const float* sin_table, void* q_out, int hidden, void* stream) {
   if (!p || !x || !wq || !wk || !wv || !cos_table || !sin_table || !q_out)
@@ -860,8 +871,22 @@ int pa_qkv_project_append(pa_pool* p, int layer, const void* x, const void* wq, 
   }
   if (rows == 0) return PA_OK;
   DeviceGuard g(p->device);
+  // the activations go through a tile-image copy first (bulk-copyable by the GEMM); the buffer
+  // belongs to the pool and only grows (first call, or a larger chunk than any before)
+  const size_t need = (size_t)((rows + 127) / 128) * 128 * hidden * sizeof(__nv_bfloat16);
+  if (need > p->x_pack_bytes) {
+    if (p->x_pack) {
+      PA_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+      cudaFree(p->x_pack);
+      p->x_pack = nullptr;
+      p->x_pack_bytes = 0;
+    }
+    PA_CUDA(cudaMalloc(&p->x_pack, need));
+    p->x_pack_bytes = need;
+  }
+  PA_CUDA(pa::launch_pack_x(x, p->x_pack, rows, hidden, (cudaStream_t)stream));
   pa::QkvGemmParams a;
-  a.x = (const __nv_bfloat16*)x;
+  a.x = (const __nv_bfloat16*)p->x_pack;
   a.wq = (const __nv_bfloat16*)wq;
   a.wk = (const __nv_bfloat16*)wk;
   a.wv = (const __nv_bfloat16*)wv;

@@ -13,13 +13,18 @@
 //
 // One CTA computes 128 tokens x 256 output columns (4 heads of one of Wq, Wk,
 // Wv) over K = 2048 in steps of 64:
-//   warps 0-3   load: per step the A tile (128 rows x 128 bytes of x) and the B
-//               tile (64 weight rows x 512 bytes) go to shared memory with 16-byte
-//               cp.async into the 128-byte-swizzle layouts the tensor cores read
-//               (A K-major, B MN-major, one 8 KiB block per head), 4 stages;
-//               a stage is handed over (wait_group, fence.proxy.async, mbarrier
-//               arrive) two steps after it was issued.  After the last step the
-//               same warps run the epilogue: thread = token row = TMEM lane.
+//   warp 0      load: per step ONE 16 KiB bulk (TMA) copy for the A tile (128 token
+//               rows x 64 k) and ONE 32 KiB bulk copy for the B tile (64 weight rows
+//               x 4 heads), 4 stages.  Both operands are read from tile images of
+//               the shared-memory layout the tensor cores want (rows of 128 bytes,
+//               16-byte chunks XOR-swizzled; A K-major, B MN-major), the same idea
+//               as the KV cache's tile layout: the weights are packed once, at load
+//               time (pack_weights_kernel), the activations by a small kernel in
+//               front of the GEMM (pack_x_kernel, 8 MB in, 8 MB out per layer).
+//               With 16-byte cp.async from the row-major arrays instead the kernel
+//               ran at 96 us per layer: lg_throttle and long_scoreboard stalls on
+//               the load path, tensor pipe 18 % busy.
+//   warps 0-3   epilogue after the last step: thread = token row = TMEM lane.
 //   warp 4      issues 16 tcgen05.mma (M128 N64 K16) per step from one elected
 //               lane into 4 x 64 TMEM columns and frees the stage with
 //               tcgen05.commit.
@@ -85,7 +90,7 @@ qkv_gemm_kernel(QkvGemmParams p) {
   if (tid == 0) {
     *abort_flag = 0;
     for (int s = 0; s < kGStages; s++) {
-      mbar_init(bar_full + 8 * s, kLoadThreads);
+      mbar_init(bar_full + 8 * s, 1);  // one arrival (with the byte count of both bulk copies)
       mbar_init(bar_empty + 8 * s, 1);
     }
     mbar_init(bar_acc, 1);
@@ -103,51 +108,24 @@ qkv_gemm_kernel(QkvGemmParams p) {
   if (warp < 4) {
     // ===================== loads ==============================================
     bool ok = true;
-    auto hand_over = [&](int ks) {  // stage of step ks has landed: make it visible to the tensor cores
-      fence_proxy_async_smem();
-      mbar_arrive(bar_full + 8 * (ks % kGStages));
-    };
-    for (int ks = 0; ks < k_steps && ok; ks++) {
-      const int st = ks % kGStages;
-      if (!wait_or_abort(bar_empty + 8 * st, (uint32_t)(((ks / kGStages) & 1) ^ 1), abort_flag)) {
-        ok = false;
-        break;
+    if (warp == 0) {
+      const char* a_img = reinterpret_cast<const char*>(p.x) + (size_t)blockIdx.y * k_steps * kABytes;
+      const char* b_img = reinterpret_cast<const char*>(w) + (size_t)(n0 / 64) * (kGK * 128);
+      for (int ks = 0; ks < k_steps; ks++) {
+        const int st = ks % kGStages;
+        if (!wait_or_abort(bar_empty + 8 * st, (uint32_t)(((ks / kGStages) & 1) ^ 1), abort_flag)) {
+          ok = false;
+          break;
+        }
+        if (lane == 0) {
+          const uint32_t sA = base + st * (kABytes + kBBytes), sB = sA + kABytes;
+          mbar_expect_tx(bar_full + 8 * st, kABytes + kBBytes);
+          bulk_g2s(sA, a_img + (size_t)ks * kABytes, kABytes, bar_full + 8 * st);
+          // the 4 head blocks of this k-step are adjacent in the packed weights
+          bulk_g2s(sB, b_img + (size_t)ks * (n_cols / 64) * (kGK * 128), kBBytes, bar_full + 8 * st);
+        }
+        __syncwarp();
       }
-      const uint32_t sA = base + st * (kABytes + kBBytes), sB = sA + kABytes;
-      const int k0 = ks * kGK;
-      // A: 128 rows x 8 chunks
-#pragma unroll
-      for (int j = 0; j < 8; j++) {
-        const int q = tid + kLoadThreads * j;
-        const int r = q >> 3, c = q & 7;
-        const bool valid = m0 + r < p.rows;
-        const __nv_bfloat16* src = p.x + (size_t)(valid ? m0 + r : 0) * p.hidden + k0 + c * 8;
-        cp_async16(sA + r * 128 + ((c ^ (r & 7)) << 4), src, valid);
-      }
-      // B: 64 weight rows x (4 head blocks x 8 chunks); 32 consecutive threads read 512 contiguous bytes
-#pragma unroll
-      for (int j = 0; j < 16; j++) {
-        const int q = tid + kLoadThreads * j;
-        const int r = q >> 5, rem = q & 31;
-        const int hb = rem >> 3, c = rem & 7;
-        const __nv_bfloat16* src = w + (size_t)(k0 + r) * n_cols + n0 + hb * 64 + c * 8;
-        cp_async16(sB + hb * (kGK * 128) + r * 128 + ((c ^ (r & 7)) << 4), src, true);
-      }
-      cp_async_commit();
-      if (ks >= 2) {
-        cp_async_wait<2>();
-        hand_over(ks - 2);
-      }
-    }
-    if (ok) {
-      if (k_steps >= 2) {
-        cp_async_wait<1>();
-        hand_over(k_steps - 2);
-      }
-      cp_async_wait<0>();
-      hand_over(k_steps - 1);
-    } else {
-      cp_async_wait<0>();
     }
 
     // ===================== epilogue ============================================
@@ -180,7 +158,10 @@ qkv_gemm_kernel(QkvGemmParams p) {
         tmem_ld32(tmem + lane_base + hb * 64, acc[0]);
         tmem_ld32(tmem + lane_base + hb * 64 + 32, acc[1]);
         tmem_wait_ld();
-        if (seq < 0) continue;
+        // rows without a token skip the stores; the warp meets again before the next
+        // (warp-wide, aligned) tensor-memory load
+        __syncwarp();
+        if (seq >= 0) {
         const int head = n0 / 64 + hb;
         // the GEMM's bf16 output, then RoPE on it: element i pairs with i + 32
         uint32_t lo[16], hi[16];  // bf16 pairs of elements 0..31 and 32..63
@@ -223,6 +204,8 @@ qkv_gemm_kernel(QkvGemmParams p) {
                 make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
           }
         }
+        }
+        __syncwarp();
       }
     }
   } else {
@@ -257,7 +240,54 @@ qkv_gemm_kernel(QkvGemmParams p) {
   }
 }
 
+
+// Row-major [hidden, cols] weights -> the shared-memory image the GEMM copies:
+// block (k-tile of 64 rows, head of 64 columns) = 64 rows of 128 bytes, 16-byte
+// chunk c of row r stored at c ^ (r & 7).  One thread per 16-byte chunk.
+__global__ void __launch_bounds__(256)
+pack_weights_kernel(const __nv_bfloat16* src, char* dst, int hidden, int cols) {
+  const size_t total = (size_t)hidden * cols / 8;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i & 7);
+    const size_t rc = i >> 3;                       // (row, head)
+    const int head = (int)(rc % (cols / 64));
+    const int row = (int)(rc / (cols / 64));
+    const int r = row & 63, kt = row >> 6;
+    const uint4 v = *reinterpret_cast<const uint4*>(src + (size_t)row * cols + head * 64 + c * 8);
+    *reinterpret_cast<uint4*>(dst + ((size_t)kt * (cols / 64) + head) * (kGK * 128) + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+  }
+}
+
+// Row-major activations [rows, hidden] -> per (128-row tile, 64-k tile) a 16 KiB block of 128-byte
+// rows, 16-byte chunk c of row r stored at c ^ (r & 7); rows beyond `rows` are zero.
+__global__ void __launch_bounds__(256)
+pack_x_kernel(const __nv_bfloat16* x, char* dst, int rows, int hidden) {
+  const int cpr = hidden / 8;  // chunks per row
+  const size_t total = (size_t)((rows + kGM - 1) / kGM) * kGM * cpr;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int cg = (int)(i % cpr);
+    const int row = (int)(i / cpr);
+    const int r = row % kGM, mt = row / kGM, kt = cg >> 3, c = cg & 7;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < rows) v = *reinterpret_cast<const uint4*>(x + (size_t)row * hidden + cg * 8);
+    *reinterpret_cast<uint4*>(dst + ((size_t)mt * (hidden / kGK) + kt) * kABytes + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_pack_x(const void* x, void* dst, int rows, int hidden, cudaStream_t stream) {
+  const size_t total = (size_t)((rows + kGM - 1) / kGM) * kGM * (hidden / 8);
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  pack_x_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, (char*)dst, rows, hidden);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pack_weights(const void* src, void* dst, int hidden, int cols, cudaStream_t stream) {
+  pack_weights_kernel<<<148 * 4, 256, 0, stream>>>((const __nv_bfloat16*)src, (char*)dst, hidden, cols);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_qkv_gemm(const QkvGemmParams& p, cudaStream_t stream) {
   if (p.rows <= 0) return cudaSuccess;

@@ -307,3 +307,15 @@ def qkv_project(x, wq, wk, wv, q, k, v, rows: int, layers: int = 1, hidden: int 
     check(lib().pa_qkv_project(_ptr(x), _ptr(wq), _ptr(wk), _ptr(wv), _ptr(q), _ptr(k), _ptr(v), rows, layers,
                                hidden, q_cols, kv_cols, rows * hidden, hidden * q_cols, hidden * kv_cols,
                                rows * q_cols, rows * kv_cols, stream))
+
+
+def pack_projection_weights(w, stream: int = 0):
+    """Row-major [..., hidden, cols] bf16 weights -> the tile image qkv_project_append reads (a new tensor)."""
+    import torch
+    packed = torch.empty_like(w)
+    hidden, cols = int(w.shape[-2]), int(w.shape[-1])
+    flat_in = w.reshape(-1, hidden, cols)
+    flat_out = packed.reshape(-1, hidden, cols)
+    for i in range(flat_in.shape[0]):
+        check(lib().pa_pack_projection_weights(_ptr(flat_in[i]), _ptr(flat_out[i]), hidden, cols, stream))
+    return packed

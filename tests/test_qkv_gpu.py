@@ -94,7 +94,8 @@ def _project_append_case(rng, position, tokens):
     pool.reserve(s, L)
     pool.batch_set([s], [tokens])
     q_out = torch.full((tokens, 2048), 3.0, dtype=torch.bfloat16, device=DEV)
-    pool.qkv_project_append(0, to_dev(x), to_dev(wq), to_dev(wk), to_dev(wv), f32_dev(cos), f32_dev(sin), q_out)
+    pq, pk, pv = (paged.pack_projection_weights(to_dev(w)) for w in (wq, wk, wv))
+    pool.qkv_project_append(0, to_dev(x), pq, pk, pv, f32_dev(cos), f32_dev(sin), q_out)
     torch.cuda.synchronize()
     pool.check()
     gk = torch.zeros(8, L, 64, dtype=torch.bfloat16, device=DEV)
