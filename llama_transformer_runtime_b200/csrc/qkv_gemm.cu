@@ -11,8 +11,11 @@
 // in fp32 on those bf16 values with the same rounding as append_kernel, V is
 // stored as it comes out.
 //
-// One CTA computes 128 tokens x 256 output columns (4 heads of one of Wq, Wk,
-// Wv) over K = 2048 in steps of 64:
+// One CTA computes 256 tokens (two M = 128 halves) x 256 output columns (4 heads
+// of one of Wq, Wk, Wv) over K = 2048 in steps of 64.  The tile is that large
+// because every byte of it comes through L2: with 128 x 256 tiles (85 flop per
+// loaded byte, 295 MB of L2-to-SM traffic per layer) the kernel sat at 96 us per
+// layer whatever the load mechanism; 256 x 256 tiles move 197 MB.
 //   warp 0      load: per step ONE 16 KiB bulk (TMA) copy for the A tile (128 token
 //               rows x 64 k) and ONE 32 KiB bulk copy for the B tile (64 weight rows
 //               x 4 heads), 4 stages.  Both operands are read from tile images of
@@ -39,28 +42,19 @@ namespace pa {
 
 namespace {
 
-constexpr int kGM = 128;        // tokens per CTA
+constexpr int kGM = 128;        // tokens per UMMA (M = 128) and per packed activation tile
+constexpr int kGMH = 2;         // row halves per CTA: 256 tokens share every weight tile
 constexpr int kGN = 256;        // output columns per CTA (4 heads)
 constexpr int kGK = 64;         // k per stage
-constexpr int kGStages = 4;
+constexpr int kGStages = 3;
 constexpr int kABytes = kGM * 128;            // 16 KiB
 constexpr int kBBytes = (kGN / 64) * kGK * 128;  // 4 head blocks x 8 KiB
-constexpr int kGOffBar = kGStages * (kABytes + kBBytes);
+constexpr int kStageBytes = kGMH * kABytes + kBBytes;  // 64 KiB
+constexpr int kGOffBar = kGStages * kStageBytes;
 constexpr int kGOffMisc = kGOffBar + (2 * kGStages + 1) * 8;
 constexpr int kGSmem = kGOffMisc + 16 + 112;
-constexpr int kLoadThreads = 128;
-constexpr int kGemmThreads = 160;  // 4 load/epilogue warps + the MMA warp
-constexpr uint32_t kGTmemCols = 256;
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
-  const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are zero-filled
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
+constexpr int kGemmThreads = 160;  // 4 epilogue warps (warp 0 also loads) + the MMA warp
+constexpr uint32_t kGTmemCols = 512;  // 2 row halves x 4 heads x 64 fp32 columns
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
 qkv_gemm_kernel(QkvGemmParams p) {
@@ -77,7 +71,7 @@ qkv_gemm_kernel(QkvGemmParams p) {
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kGOffMisc + 4);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int m0 = blockIdx.y * kGM;
+  const int m0 = blockIdx.y * (kGMH * kGM);
   // column tile -> matrix and first column: tiles of Wq, then Wk, then Wv
   const int tq = p.q_cols / kGN, tk = p.kv_cols / kGN;
   const int ct = blockIdx.x;
@@ -109,7 +103,8 @@ qkv_gemm_kernel(QkvGemmParams p) {
     // ===================== loads ==============================================
     bool ok = true;
     if (warp == 0) {
-      const char* a_img = reinterpret_cast<const char*>(p.x) + (size_t)blockIdx.y * k_steps * kABytes;
+      const char* a_img = reinterpret_cast<const char*>(p.x) + (size_t)blockIdx.y * kGMH * k_steps * kABytes;
+      const int tiles_m = (p.rows + kGM - 1) / kGM;  // packed activation tiles that exist
       const char* b_img = reinterpret_cast<const char*>(w) + (size_t)(n0 / 64) * (kGK * 128);
       for (int ks = 0; ks < k_steps; ks++) {
         const int st = ks % kGStages;
@@ -118,9 +113,12 @@ qkv_gemm_kernel(QkvGemmParams p) {
           break;
         }
         if (lane == 0) {
-          const uint32_t sA = base + st * (kABytes + kBBytes), sB = sA + kABytes;
-          mbar_expect_tx(bar_full + 8 * st, kABytes + kBBytes);
+          const uint32_t sA = base + st * kStageBytes, sB = sA + kGMH * kABytes;
+          const bool second = (int)blockIdx.y * kGMH + 1 < tiles_m;  // the last CTA row may have one half only
+          mbar_expect_tx(bar_full + 8 * st, (second ? 2 : 1) * kABytes + kBBytes);
           bulk_g2s(sA, a_img + (size_t)ks * kABytes, kABytes, bar_full + 8 * st);
+          if (second)
+            bulk_g2s(sA + kABytes, a_img + ((size_t)k_steps + ks) * kABytes, kABytes, bar_full + 8 * st);
           // the 4 head blocks of this k-step are adjacent in the packed weights
           bulk_g2s(sB, b_img + (size_t)ks * (n_cols / 64) * (kGK * 128), kBBytes, bar_full + 8 * st);
         }
@@ -131,8 +129,10 @@ qkv_gemm_kernel(QkvGemmParams p) {
     // ===================== epilogue ============================================
     if (ok && wait_or_abort(bar_acc, 0, abort_flag)) {
       tc_fence_after();
-      const int row = m0 + warp * 32 + lane;  // token row = TMEM lane
-      const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+#pragma unroll 1
+      for (int mh = 0; mh < kGMH; mh++) {
+      const int row = m0 + mh * kGM + warp * 32 + lane;  // token row; TMEM lane = warp * 32 + lane
+      const uint32_t lane_base = ((uint32_t)(warp * 32) << 16) + (uint32_t)(mh * kGN);
       // which sequence and position this row is
       int seq = -1, lpos = 0, pos = 0;
       for (int s = 0; s < p.n_seqs; s++) {
@@ -152,6 +152,33 @@ qkv_gemm_kernel(QkvGemmParams p) {
         }
       }
       const int slot = lpos % kBlockTok;
+      // This row's RoPE factors, once per row: 16 vector loads into a private row of the (now
+      // idle) stage ring, 65 floats apart so that the 32 lanes of a warp hit 32 banks.  Read per
+      // element from global memory instead (scalar, one 128-byte line per lane and load, 4 heads
+      // over) they made the epilogue longer than the whole MMA loop.
+      float* trow = reinterpret_cast<float*>(sm) + (warp * 32 + lane) * 65;
+      if (which != 2 && seq >= 0) {
+        const float4* cs4 = reinterpret_cast<const float4*>(p.cos_table + (size_t)pos * 32);
+        const float4* sn4 = reinterpret_cast<const float4*>(p.sin_table + (size_t)pos * 32);
+        float4 cv[8], sv[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          cv[i] = cs4[i];
+          sv[i] = sn4[i];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          trow[4 * i] = cv[i].x;
+          trow[4 * i + 1] = cv[i].y;
+          trow[4 * i + 2] = cv[i].z;
+          trow[4 * i + 3] = cv[i].w;
+          trow[32 + 4 * i] = sv[i].x;
+          trow[32 + 4 * i + 1] = sv[i].y;
+          trow[32 + 4 * i + 2] = sv[i].z;
+          trow[32 + 4 * i + 3] = sv[i].w;
+        }
+      }
+      __syncwarp();
 #pragma unroll 1
       for (int hb = 0; hb < kGN / 64; hb++) {
         uint32_t acc[2][32];
@@ -172,8 +199,8 @@ qkv_gemm_kernel(QkvGemmParams p) {
             hi[i] = pack_bf16(__uint_as_float(acc[1][2 * i]), __uint_as_float(acc[1][2 * i + 1]));
           }
         } else {
-          const float* cs = p.cos_table + (size_t)pos * 32;
-          const float* sn = p.sin_table + (size_t)pos * 32;
+          const float* cs = trow;
+          const float* sn = trow + 32;
 #pragma unroll
           for (int i = 0; i < 16; i++) {
             const float x0a = __bfloat162float(__float2bfloat16_rn(__uint_as_float(acc[0][2 * i])));
@@ -207,22 +234,27 @@ qkv_gemm_kernel(QkvGemmParams p) {
         }
         __syncwarp();
       }
+      }
     }
   } else {
     // ===================== MMA issue =========================================
     constexpr uint32_t kIdesc = idesc_bf16(kGM, 64, true);
+    // the last CTA row may hold one 128-row half only: its second half is never loaded nor multiplied
+    const int n_halves = ((int)blockIdx.y * kGMH + 1 < (p.rows + kGM - 1) / kGM) ? kGMH : 1;
     for (int ks = 0; ks < k_steps; ks++) {
       const int st = ks % kGStages;
       if (!wait_or_abort(bar_full + 8 * st, (uint32_t)((ks / kGStages) & 1), abort_flag)) break;
       tc_fence_after();
       if (elect_one()) {
-        const uint32_t sA = base + st * (kABytes + kBBytes), sB = sA + kABytes;
+        const uint32_t sA = base + st * kStageBytes, sB = sA + kGMH * kABytes;
+#pragma unroll 1
+        for (int mh = 0; mh < n_halves; mh++)
 #pragma unroll
-        for (int hb = 0; hb < kGN / 64; hb++)
+          for (int hb = 0; hb < kGN / 64; hb++)
 #pragma unroll
-          for (int kk = 0; kk < kGK / 16; kk++)
-            umma_ss(tmem + hb * 64, smem_desc_sw128(sA + kk * 32),
-                    smem_desc_sw128(sB + hb * (kGK * 128) + kk * 2048), kIdesc, (ks > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 0; kk < kGK / 16; kk++)
+              umma_ss(tmem + mh * kGN + hb * 64, smem_desc_sw128(sA + mh * kABytes + kk * 32),
+                      smem_desc_sw128(sB + hb * (kGK * 128) + kk * 2048), kIdesc, (ks > 0 || kk > 0) ? 1u : 0u);
         tc_commit(bar_empty + 8 * st);
         if (ks + 1 == k_steps) tc_commit(bar_acc);
       }
@@ -299,7 +331,7 @@ cudaError_t launch_qkv_gemm(const QkvGemmParams& p, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  const dim3 grid((p.q_cols + 2 * p.kv_cols) / kGN, (p.rows + kGM - 1) / kGM);
+  const dim3 grid((p.q_cols + 2 * p.kv_cols) / kGN, (p.rows + kGMH * kGM - 1) / (kGMH * kGM));
   qkv_gemm_kernel<<<grid, kGemmThreads, kGSmem, stream>>>(p);
   return cudaGetLastError();
 }
