@@ -238,9 +238,10 @@ qkv_gemm_kernel(QkvGemmParams p) {
     }
   } else {
     // ===================== MMA issue =========================================
-    // N = 128: two heads per MMA.  The B operand then spans two 128-byte atoms along N, 8 KiB
-    // apart (the next head's block): that distance is the descriptor's leading byte offset.
-    constexpr uint32_t kIdesc = idesc_bf16(kGM, 128, true);
+    // N = 256: the CTA's four heads in one MMA.  The B operand then spans four 128-byte atoms
+    // along N, 8 KiB apart (the next head's block): that distance is the descriptor's leading
+    // byte offset.  (N = 64 per MMA: 55.8 us per layer, shared-memory operand bandwidth; N = 128: 46.6.)
+    constexpr uint32_t kIdesc = idesc_bf16(kGM, kGN, true);
     constexpr uint64_t kLboNextHead = (uint64_t)((kGK * 128) >> 4) << 16;
     // the last CTA row may hold one 128-row half only: its second half is never loaded nor multiplied
     const int n_halves = ((int)blockIdx.y * kGMH + 1 < (p.rows + kGM - 1) / kGM) ? kGMH : 1;
@@ -253,12 +254,10 @@ qkv_gemm_kernel(QkvGemmParams p) {
 #pragma unroll 1
         for (int mh = 0; mh < n_halves; mh++)
 #pragma unroll
-          for (int hb = 0; hb < kGN / 64; hb += 2)
-#pragma unroll
-            for (int kk = 0; kk < kGK / 16; kk++)
-              umma_ss(tmem + mh * kGN + hb * 64, smem_desc_sw128(sA + mh * kABytes + kk * 32),
-                      (smem_desc_sw128(sB + hb * (kGK * 128) + kk * 2048) & ~((uint64_t)0x3FFF << 16)) | kLboNextHead,
-                      kIdesc, (ks > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < kGK / 16; kk++)
+            umma_ss(tmem + mh * kGN, smem_desc_sw128(sA + mh * kABytes + kk * 32),
+                    (smem_desc_sw128(sB + kk * 2048) & ~((uint64_t)0x3FFF << 16)) | kLboNextHead, kIdesc,
+                    (ks > 0 || kk > 0) ? 1u : 0u);
         tc_commit(bar_empty + 8 * st);
         if (ks + 1 == k_steps) tc_commit(bar_acc);
       }
