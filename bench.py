@@ -809,10 +809,20 @@ def run_qkv(args):
                     torch.cuda.synchronize()
         launches_per_step = 3 * LAYERS
     else:
+        # weights repacked once, at load time, into the tile images both projection kernels read
+        pq = [paged.pack_projection_weights(w) for w in wq]
+        pk = [paged.pack_projection_weights(w) for w in wk]
+        pv = [paged.pack_projection_weights(w) for w in wv]
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        torch.cuda.synchronize()
+
         def step():
             s = state["i"] % SETS
             state["i"] += 1
-            paged.qkv_project(x_dev, wq[s], wk[s], wv[s], q, k, v, rows, LAYERS)
+            if (not args.qkv_packed):
+                paged.qkv_project(x_dev, wq[s], wk[s], wv[s], q, k, v, rows, LAYERS)
+            else:
+                paged.qkv_project_packed(x_dev, pq[s], pk[s], pv[s], q, k, v, rows, status, LAYERS)
         launches_per_step = 1
 
     def e2e_step():
@@ -878,7 +888,7 @@ def run_qkv(args):
             line["e2e"]["d2h_bytes_per_step"] = 0
             line["e2e"]["value"] = line["value"]
         else:
-            line["roofline"] = {"bound": "hbm", "kernel": "qkv_project_kernel", "achieved": round(value / n_rep, 1),
+            line["roofline"] = {"bound": "hbm", "kernel": "qkv_project_kernel" if (not args.qkv_packed) else "qkv_project_packed_kernel", "achieved": round(value / n_rep, 1),
                                 "peak": peak, "unit": "GB/s", "frac": round(value / n_rep / peak, 4),
                                 "peak_source": f"of {peak_kind}", "us_per_launch": round(ms / args.steps * 1e3, 2),
                                 "bytes_per_launch": LAYERS * bytes_layer, "traffic": None}
@@ -895,8 +905,12 @@ def run_qkv(args):
             dt = (time.perf_counter() - t0) / reps
             got = torch.cat([q[0], k[0], v[0]], dim=1).cpu().view(torch.int16).numpy().view(np.uint16)
             # the last timed step used weight set (i - 1) % SETS; recompute layer 0 with set 0 for the check
-            paged.qkv_project(x_dev, wq[0], wk[0], wv[0], q, k, v, rows, LAYERS)
+            if (not args.qkv_packed):
+                paged.qkv_project(x_dev, wq[0], wk[0], wv[0], q, k, v, rows, LAYERS)
+            else:
+                paged.qkv_project_packed(x_dev, pq[0], pk[0], pv[0], q, k, v, rows, status, LAYERS)
             torch.cuda.synchronize()
+            assert (not args.qkv_packed) or int(status.item()) == 0
             got = torch.cat([q[0], k[0], v[0]], dim=1).cpu().view(torch.int16).numpy().view(np.uint16)
             want = np.concatenate(outs, axis=1)
             err = float(np.abs(orc.bf16_to_f32(got) - orc.bf16_to_f32(want)).max())
@@ -1257,6 +1271,9 @@ def main():
                     help="N>1: partials pushed by the decode epilogue over NVLink (fused) or NCCL all-gather")
     ap.add_argument("--chunk-blocks", type=int, default=0, help="decode: blocks per split-KV chunk (0 = planner)")
     ap.add_argument("--decode-shape", default="", help="decode: WARPSxSTAGES, e.g. 8x4 (empty = planner)")
+    ap.add_argument("--qkv-packed", action="store_true",
+                    help="qkv_decode: the kernel that reads the packed weight tiles (shared with the prefill GEMM) "
+                         "instead of the reference's row-major weights")
     ap.add_argument("--ref-literal-append", action="store_true",
                     help="prefill reference arm: the reference's literal 2*8*tokens 128-byte copies")
     args = ap.parse_args()

@@ -298,6 +298,16 @@ int pa_qkv_project(const void* x, const void* wq, const void* wk, const void* wv
                    int64_t x_layer_stride, int64_t wq_layer_stride, int64_t wkv_layer_stride,
                    int64_t q_layer_stride, int64_t kv_layer_stride, void* stream);
 
+/* pa_qkv_project on weights repacked by pa_pack_projection_weights (the format
+ * pa_qkv_project_append reads, so one copy of the weights serves decode and
+ * prefill): the stream becomes 8 KiB contiguous bursts through a bulk-copy ring.
+ * status_word: device int that receives PA_ERR_TIMEOUT if a bounded wait runs
+ * out (a pool's status word or the caller's own). */
+int pa_qkv_project_packed(const void* x, const void* wq_packed, const void* wk_packed, const void* wv_packed,
+                          void* q, void* k, void* v, int rows, int layers, int hidden, int q_cols,
+                          int kv_cols, int64_t x_layer_stride, int64_t wq_layer_stride,
+                          int64_t wkv_layer_stride, int64_t q_layer_stride, int64_t kv_layer_stride,
+                          int* status_word, void* stream);
 /* One-time repacking of a row-major [hidden, cols] bf16 weight matrix (the
  * reference's layout) into the tile image pa_qkv_project_append copies with one
  * bulk copy per k-step: per 64 rows and 64 columns an 8 KiB block of 128-byte

@@ -42,6 +42,7 @@ struct QkvParams {
   int n[3];                    // columns of q, k, v
   int tiles_q, tiles_qk;       // column tiles before k, before v
   int rows, hidden;
+  int* status = nullptr;       // packed kernel: a wait that ran out is recorded here (nullable: then only the loop ends)
 };
 
 template <int ROWS>
@@ -134,6 +135,150 @@ __global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
   }
 }
 
+// ---- the same projections from PACKED weights (the tile images of pa_pack_projection_weights) --
+// One weight format then serves decode and prefill, and the stream becomes 8 KiB contiguous
+// bursts: a CTA owns one head (64 output columns) and pulls its 32 blocks (64 k-rows x 128 bytes,
+// chunks XOR-swizzled) through an 8-stage ring with bulk (TMA) copies on mbarriers, as the decode
+// attention kernel does; warp w takes rows 16w..16w+15 of every block, lane (rsub, c) the 16-byte
+// chunk c of rows rsub + 4j.  Sums are reduced over lanes and warps in a fixed order.
+constexpr int kPkStages = 8;
+constexpr int kPkBlock = 64 * 128;  // 8 KiB
+constexpr int kPkThreads = 128;
+
+template <int ROWS>
+__global__ void __launch_bounds__(kPkThreads) qkv_project_packed_kernel(QkvParams p) {
+  extern __shared__ __align__(128) unsigned char pk_smem[];
+  unsigned char* ring = pk_smem;
+  __nv_bfloat16* sx = reinterpret_cast<__nv_bfloat16*>(pk_smem + kPkStages * kPkBlock);  // [ROWS][hidden]
+  float* red = reinterpret_cast<float*>(pk_smem + kPkStages * kPkBlock + ROWS * kMaxHidden * 2);  // [4][ROWS][64]
+  __shared__ __align__(8) unsigned long long bars[2 * kPkStages];
+  const uint32_t bar_full = pa::smem_u32(bars), bar_empty = bar_full + 8 * kPkStages;
+  const uint32_t ring_u32 = pa::smem_u32(ring);
+
+  const int t = blockIdx.x, layer = blockIdx.y;
+  const int hq = p.n[0] / 64, hkv = p.n[1] / 64;
+  const int which = t < hq ? 0 : (t < hq + hkv ? 1 : 2);
+  const int head = t - (which == 0 ? 0 : (which == 1 ? hq : hq + hkv));
+  const int n = p.n[which];
+  const char* w = reinterpret_cast<const char*>(p.w[which] + (size_t)layer * p.w_layer_stride[which]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_kb = p.hidden / 64;
+  auto block_src = [&](int kb) { return w + ((size_t)kb * (n / 64) + head) * kPkBlock; };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPkStages; s++) {
+      pa::mbar_init(bar_full + 8 * s, 1);
+      pa::mbar_init(bar_empty + 8 * s, kPkThreads / 32);
+    }
+    pa::mbar_fence_init();
+    pa::fence_proxy_async_smem();
+    for (int kb = 0; kb < kPkStages && kb < n_kb; kb++) {  // fill the ring: the copies do not depend on x
+      pa::mbar_expect_tx(bar_full + 8 * kb, kPkBlock);
+      pa::bulk_g2s(ring_u32 + kb * kPkBlock, block_src(kb), kPkBlock, bar_full + 8 * kb);
+    }
+  }
+  const __nv_bfloat16* x = p.x + (size_t)layer * p.x_layer_stride;
+  for (int i = threadIdx.x; i < ROWS * (p.hidden / 8); i += kPkThreads) {
+    const int r = i / (p.hidden / 8), ch = i % (p.hidden / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < p.rows) v = reinterpret_cast<const uint4*>(x + (size_t)r * p.hidden)[ch];
+    reinterpret_cast<uint4*>(sx + (size_t)r * kMaxHidden)[ch] = v;
+  }
+  __syncthreads();
+
+  float acc[ROWS][8];
+#pragma unroll
+  for (int r = 0; r < ROWS; r++)
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[r][i] = 0.f;
+  const int c = lane & 7, rsub = lane >> 3;
+  bool ok = true;
+  for (int kb = 0; kb < n_kb; kb++) {
+    const int st = kb % kPkStages;
+    if (!__all_sync(0xffffffffu, pa::mbar_wait(bar_full + 8 * st, (uint32_t)((kb / kPkStages) & 1)))) {
+      ok = false;
+      break;
+    }
+    const unsigned char* blk = ring + st * kPkBlock;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int r = warp * 16 + rsub + 4 * j;
+      const uint4 wv = *reinterpret_cast<const uint4*>(blk + r * 128 + ((c ^ (r & 7)) << 4));
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+      float wf[8];
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const float2 f = __bfloat1622float2(h2[i]);
+        wf[2 * i] = f.x;
+        wf[2 * i + 1] = f.y;
+      }
+      const int k = kb * 64 + r;
+#pragma unroll
+      for (int rr = 0; rr < ROWS; rr++) {
+        const float xv = __bfloat162float(sx[(size_t)rr * kMaxHidden + k]);
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc[rr][i] = fmaf(xv, wf[i], acc[rr][i]);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) pa::mbar_arrive(bar_empty + 8 * st);
+    // the thread that owns the ring refills this stage once every warp has left it
+    if (threadIdx.x == 0 && kb + kPkStages < n_kb) {
+      if (!pa::mbar_wait(bar_empty + 8 * st, (uint32_t)((kb / kPkStages) & 1))) {
+        ok = false;
+      } else {
+        pa::mbar_expect_tx(bar_full + 8 * st, kPkBlock);
+        pa::bulk_g2s(ring_u32 + st * kPkBlock, block_src(kb + kPkStages), kPkBlock, bar_full + 8 * st);
+      }
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) break;
+  }
+  if (!ok && lane == 0) atomicExch(p.status, pa::kStatusTimeout);
+  // over the 4 row groups of the warp, then over the warps in warp order
+#pragma unroll
+  for (int r = 0; r < ROWS; r++)
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      float v = acc[r][i];
+      v += __shfl_xor_sync(0xffffffffu, v, 8);
+      v += __shfl_xor_sync(0xffffffffu, v, 16);
+      acc[r][i] = v;
+    }
+  if (rsub == 0) {
+#pragma unroll
+    for (int r = 0; r < ROWS; r++)
+#pragma unroll
+      for (int i = 0; i < 8; i++) red[(warp * ROWS + r) * 64 + c * 8 + i] = acc[r][i];
+  }
+  __syncthreads();
+  __nv_bfloat16* out = p.out[which] + (size_t)layer * p.out_layer_stride[which];
+  for (int i = threadIdx.x; i < ROWS * 64; i += kPkThreads) {
+    const int r = i / 64, cc = i % 64;
+    if (r >= p.rows) continue;
+    float s = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < kPkThreads / 32; wi++) s += red[(wi * ROWS + r) * 64 + cc];
+    out[(size_t)r * n + head * 64 + cc] = __float2bfloat16_rn(s);
+  }
+}
+
+template <int ROWS>
+cudaError_t launch_packed(const QkvParams& p, int layers, cudaStream_t st) {
+  const int smem = kPkStages * kPkBlock + ROWS * kMaxHidden * 2 + 4 * ROWS * 64 * 4;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(qkv_project_packed_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  const dim3 grid((p.n[0] + 2 * p.n[1]) / 64, layers);
+  qkv_project_packed_kernel<ROWS><<<grid, kPkThreads, smem, st>>>(p);
+  return cudaGetLastError();
+}
+
 int qfail(int code, const char* msg) {
   pa::set_last_error(msg);
   return code;
@@ -187,6 +332,56 @@ extern "C" int pa_qkv_project(const void* x, const void* wq, const void* wk, con
   if (e != cudaSuccess) {
     char msg[256];
     snprintf(msg, sizeof(msg), "pa_qkv_project: %s", cudaGetErrorString(e));
+    return qfail(PA_ERR_CUDA, msg);
+  }
+  return PA_OK;
+}
+
+extern "C" int pa_qkv_project_packed(const void* x, const void* wq_packed, const void* wk_packed,
+                                     const void* wv_packed, void* q, void* k, void* v, int rows, int layers,
+                                     int hidden, int q_cols, int kv_cols, int64_t x_layer_stride,
+                                     int64_t wq_layer_stride, int64_t wkv_layer_stride, int64_t q_layer_stride,
+                                     int64_t kv_layer_stride, int* status_word, void* stream) {
+  if (!x || !wq_packed || !wk_packed || !wv_packed || !q || !k || !v || !status_word)
+    return qfail(PA_ERR_INVALID_ARG, "pa_qkv_project_packed: NULL argument");
+  if (rows < 1 || layers < 1 || layers > 65535) return qfail(PA_ERR_INVALID_ARG, "pa_qkv_project_packed: rows >= 1, 1 <= layers <= 65535");
+  if (rows > 8) return qfail(PA_ERR_UNSUPPORTED, "pa_qkv_project_packed: at most 8 rows per call (decode shapes)");
+  if (hidden < 64 || hidden > kMaxHidden || hidden % 64 != 0)
+    return qfail(PA_ERR_UNSUPPORTED, "pa_qkv_project_packed: hidden must be a multiple of 64, at most 2048");
+  if (q_cols < 64 || kv_cols < 64 || q_cols % 64 != 0 || kv_cols % 64 != 0)
+    return qfail(PA_ERR_UNSUPPORTED, "pa_qkv_project_packed: q_cols and kv_cols must be multiples of 64");
+  QkvParams p;
+  p.x = (const __nv_bfloat16*)x;
+  p.w[0] = (const __nv_bfloat16*)wq_packed;
+  p.w[1] = (const __nv_bfloat16*)wk_packed;
+  p.w[2] = (const __nv_bfloat16*)wv_packed;
+  p.out[0] = (__nv_bfloat16*)q;
+  p.out[1] = (__nv_bfloat16*)k;
+  p.out[2] = (__nv_bfloat16*)v;
+  p.x_layer_stride = x_layer_stride;
+  p.w_layer_stride[0] = wq_layer_stride;
+  p.w_layer_stride[1] = p.w_layer_stride[2] = wkv_layer_stride;
+  p.out_layer_stride[0] = q_layer_stride;
+  p.out_layer_stride[1] = p.out_layer_stride[2] = kv_layer_stride;
+  p.n[0] = q_cols;
+  p.n[1] = p.n[2] = kv_cols;
+  p.tiles_q = p.tiles_qk = 0;
+  p.rows = rows;
+  p.hidden = hidden;
+  p.status = status_word;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e;
+  if (rows == 1)
+    e = launch_packed<1>(p, layers, st);
+  else if (rows == 2)
+    e = launch_packed<2>(p, layers, st);
+  else if (rows <= 4)
+    e = launch_packed<4>(p, layers, st);
+  else
+    e = launch_packed<8>(p, layers, st);
+  if (e != cudaSuccess) {
+    char msg[256];
+    snprintf(msg, sizeof(msg), "pa_qkv_project_packed: %s", cudaGetErrorString(e));
     return qfail(PA_ERR_CUDA, msg);
   }
   return PA_OK;

@@ -319,3 +319,14 @@ def pack_projection_weights(w, stream: int = 0):
     for i in range(flat_in.shape[0]):
         check(lib().pa_pack_projection_weights(_ptr(flat_in[i]), _ptr(flat_out[i]), hidden, cols, stream))
     return packed
+
+
+def qkv_project_packed(x, wq_packed, wk_packed, wv_packed, q, k, v, rows: int, status, layers: int = 1,
+                       hidden: int = 2048, stream: int = 0) -> None:
+    """qkv_project on weights repacked by pack_projection_weights; `status` is a device int32 tensor
+    that receives the timeout code if a bounded wait runs out."""
+    q_cols, kv_cols = int(wq_packed.shape[-1]), int(wk_packed.shape[-1])
+    check(lib().pa_qkv_project_packed(_ptr(x), _ptr(wq_packed), _ptr(wk_packed), _ptr(wv_packed), _ptr(q), _ptr(k),
+                                      _ptr(v), rows, layers, hidden, q_cols, kv_cols, rows * hidden,
+                                      hidden * q_cols, hidden * kv_cols, rows * q_cols, rows * kv_cols,
+                                      _ptr(status), stream))

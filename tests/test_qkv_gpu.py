@@ -42,6 +42,39 @@ def test_qkv_project_vs_oracle(cuda, rows, layers):
         bf16_close(to_u16(v[l]), orc.gemm_bf16(x[l], wv[l]), f"v layer {l}")
 
 
+@pytest.mark.parametrize("rows,layers", [(1, 2), (3, 1), (8, 2)])
+def test_qkv_project_packed_equals_row_major(cuda, rows, layers):
+    """The packed-weight kernel adds the same products in a different order: compare with the
+    oracle like the row-major kernel, and require near-complete bit agreement between the two."""
+    rng = np.random.default_rng(520 + rows + layers)
+    x = orc.randn_bf16(rng, (layers, rows, 2048))
+    wq = orc.randn_bf16(rng, (layers, 2048, 2048), 0.03)
+    wk = orc.randn_bf16(rng, (layers, 2048, 512), 0.03)
+    wv = orc.randn_bf16(rng, (layers, 2048, 512), 0.03)
+    xd, wqd, wkd, wvd = to_dev(x), to_dev(wq), to_dev(wk), to_dev(wv)
+    outs = []
+    for packed in (False, True):
+        q = torch.full((layers, rows, 2048), 7.0, dtype=torch.bfloat16, device=DEV)
+        k = torch.full((layers, rows, 512), 7.0, dtype=torch.bfloat16, device=DEV)
+        v = torch.full((layers, rows, 512), 7.0, dtype=torch.bfloat16, device=DEV)
+        if packed:
+            status = torch.zeros(1, dtype=torch.int32, device=DEV)
+            pq, pk, pv = (paged.pack_projection_weights(w) for w in (wqd, wkd, wvd))
+            paged.qkv_project_packed(xd, pq, pk, pv, q, k, v, rows, status, layers)
+            torch.cuda.synchronize()
+            assert int(status.item()) == 0
+        else:
+            paged.qkv_project(xd, wqd, wkd, wvd, q, k, v, rows, layers)
+            torch.cuda.synchronize()
+        outs.append((to_u16(q), to_u16(k), to_u16(v)))
+    for l in range(layers):
+        bf16_close(outs[1][0][l], orc.gemm_bf16(x[l], wq[l]), f"packed q layer {l}")
+        bf16_close(outs[1][1][l], orc.gemm_bf16(x[l], wk[l]), f"packed k layer {l}")
+        bf16_close(outs[1][2][l], orc.gemm_bf16(x[l], wv[l]), f"packed v layer {l}")
+    for a_, b_ in zip(outs[0], outs[1]):
+        assert float((a_ == b_).mean()) > 0.9
+
+
 @pytest.mark.skipif(not orc.ref_available(), reason="reference kernels were not built")
 @pytest.mark.parametrize("rows", [1, 4])
 def test_qkv_project_vs_reference_gemm(cuda, rows):
