@@ -194,3 +194,56 @@ def test_qkv_project_append_vs_reference_chain(cuda):
     rotated_close(q, q_ref, "rotated Q against the reference chain")
     rotated_close(k, to_u16(ko), "rotated K against the reference chain")
     bf16_close(v, to_u16(vo), "V against the reference chain")
+
+
+def test_qkv_project_append_two_sequences(cuda):
+    """A batch of two sequences with different lengths and cache positions: rows of x are in batch
+    order, every row finds its own sequence, position and cache block."""
+    from tests.gpu_helpers import f32_dev, fill_cache
+    rng = np.random.default_rng(700)
+    positions, news = [19, 0], [70, 133]
+    cos, sin = orc.build_rope_tables(256)
+    pool = paged.KVPool(1, 40, 8, 2)
+    pool.set_free_order(rng.permutation(40))
+    seqs, olds = [], []
+    for pos in positions:
+        s = pool.create_seq()
+        k_old = orc.randn_bf16(rng, (8, pos, 64), 0.5)
+        v_old = orc.randn_bf16(rng, (8, pos, 64), 0.5)
+        if pos:
+            fill_cache(pool, 0, s, k_old, v_old)
+        seqs.append(s)
+        olds.append((k_old, v_old))
+    rows = sum(news)
+    x = orc.randn_bf16(rng, (rows, 2048))
+    wq = orc.randn_bf16(rng, (2048, 2048), 0.03)
+    wk = orc.randn_bf16(rng, (2048, 512), 0.03)
+    wv = orc.randn_bf16(rng, (2048, 512), 0.03)
+    for s, pos, n in zip(seqs, positions, news):
+        pool.reserve(s, pos + n)
+    pool.batch_set(seqs, news)
+    q_out = torch.zeros(rows, 2048, dtype=torch.bfloat16, device=DEV)
+    pq, pk, pv = (paged.pack_projection_weights(to_dev(w)) for w in (wq, wk, wv))
+    pool.qkv_project_append(0, to_dev(x), pq, pk, pv, f32_dev(cos), f32_dev(sin), q_out)
+    torch.cuda.synchronize()
+    pool.check()
+    q_lin = orc.gemm_bf16(x, wq).reshape(rows, 32, 64)
+    k_lin = orc.gemm_bf16(x, wk).reshape(rows, 8, 64)
+    v_lin = orc.gemm_bf16(x, wv).reshape(rows, 8, 64)
+    got_q = to_u16(q_out)
+    r0 = 0
+    for s, pos, n, (k_old, v_old) in zip(seqs, positions, news, olds):
+        L = pos + n
+        gk = torch.zeros(8, L, 64, dtype=torch.bfloat16, device=DEV)
+        gv = torch.zeros_like(gk)
+        pool.gather_kv(0, s, gk, gv, L)
+        torch.cuda.synchronize()
+        k, v = to_u16(gk), to_u16(gv)
+        assert np.array_equal(k[:, :pos], k_old) and np.array_equal(v[:, :pos], v_old)
+        rotated_close(got_q[r0:r0 + n],
+                      orc.rope(q_lin[r0:r0 + n], cos, sin, pos, 1, out_token_major=True).reshape(n, 2048),
+                      f"rotated Q of sequence {s}")
+        rotated_close(k[:, pos:], orc.rope(k_lin[r0:r0 + n], cos, sin, pos, 1), f"rotated K of sequence {s}")
+        bf16_close(v[:, pos:], orc.transpose_v(v_lin[r0:r0 + n]), f"V of sequence {s}")
+        r0 += n
+    pool.close()
