@@ -298,6 +298,17 @@ int pa_qkv_project(const void* x, const void* wq, const void* wk, const void* wv
                    int64_t x_layer_stride, int64_t wq_layer_stride, int64_t wkv_layer_stride,
                    int64_t q_layer_stride, int64_t kv_layer_stride, void* stream);
 
+/* ---- consumer side of the path: output projection + attention residual ---------
+ * out = bf16(residual + bf16(attn W_o)) for the rows of a decode step (at most 8),
+ * all layers in one launch.  Replaces launch_gemm_2048x2048 on the attention
+ * output (src/runtime/attention.cu:367-375) and transformer::residual_add
+ * (src/runtime/transformer_block.cu:76-81; src/kernels/residual_add/residual_add.cu:14-38)
+ * with their rounding: the GEMM result is rounded to bf16, the sum once more.
+ * attn [layers][rows, hidden]; wo [layers][hidden, cols] row-major; residual
+ * (nullable) and out [layers][rows, cols], both with out_layer_stride. */
+int pa_out_project(const void* attn, const void* wo, const void* residual, void* out, int rows, int layers,
+                   int hidden, int cols, int64_t attn_layer_stride, int64_t wo_layer_stride,
+                   int64_t out_layer_stride, void* stream);
 /* pa_qkv_project on weights repacked by pa_pack_projection_weights (the format
  * pa_qkv_project_append reads, so one copy of the weights serves decode and
  * prefill): the stream becomes 8 KiB contiguous bursts through a bulk-copy ring.

@@ -43,6 +43,8 @@ struct QkvParams {
   int tiles_q, tiles_qk;       // column tiles before k, before v
   int rows, hidden;
   int* status = nullptr;       // packed kernel: a wait that ran out is recorded here (nullable: then only the loop ends)
+  // optional residual of output 0 (the output projection): out = bf16(residual + bf16(x W)), same strides as out[0]
+  const __nv_bfloat16* residual = nullptr;
 };
 
 template <int ROWS>
@@ -131,7 +133,14 @@ __global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
     float s = 0.f;
 #pragma unroll
     for (int wi = 0; wi < 8; wi++) s += red[wi][r][cc];
-    out[(size_t)r * n + col0 + cc] = __float2bfloat16_rn(s);
+    __nv_bfloat16 y = __float2bfloat16_rn(s);  // the GEMM's bf16 output
+    if (which == 0 && p.residual) {
+      // the reference adds the residual in a second kernel on the bf16 GEMM output
+      // (src/kernels/residual_add/residual_add.cu:14-38): fp32 sum of two bf16, rounded once
+      const __nv_bfloat16 rv = p.residual[(size_t)layer * p.out_layer_stride[0] + (size_t)r * n + col0 + cc];
+      y = __float2bfloat16_rn(__bfloat162float(rv) + __bfloat162float(y));
+    }
+    out[(size_t)r * n + col0 + cc] = y;
   }
 }
 
@@ -382,6 +391,49 @@ extern "C" int pa_qkv_project_packed(const void* x, const void* wq_packed, const
   if (e != cudaSuccess) {
     char msg[256];
     snprintf(msg, sizeof(msg), "pa_qkv_project_packed: %s", cudaGetErrorString(e));
+    return qfail(PA_ERR_CUDA, msg);
+  }
+  return PA_OK;
+}
+
+// Output projection of a decode step with the attention residual folded in: out = bf16(residual +
+// bf16(attn W_o)).  Replaces launch_gemm_2048x2048 (src/runtime/attention.cu:367-375) and
+// transformer::residual_add (src/runtime/transformer_block.cu:76-81) for decode shapes.
+extern "C" int pa_out_project(const void* attn, const void* wo, const void* residual, void* out, int rows,
+                              int layers, int hidden, int cols, int64_t attn_layer_stride,
+                              int64_t wo_layer_stride, int64_t out_layer_stride, void* stream) {
+  if (!attn || !wo || !out) return qfail(PA_ERR_INVALID_ARG, "pa_out_project: NULL argument");
+  if (rows < 1 || layers < 1 || layers > 65535) return qfail(PA_ERR_INVALID_ARG, "pa_out_project: rows >= 1, 1 <= layers <= 65535");
+  if (rows > 8) return qfail(PA_ERR_UNSUPPORTED, "pa_out_project: at most 8 rows per call (decode shapes)");
+  if (hidden < 64 || hidden > kMaxHidden || hidden % 64 != 0)
+    return qfail(PA_ERR_UNSUPPORTED, "pa_out_project: hidden must be a multiple of 64, at most 2048");
+  if (cols < kColsPerCta || cols % kColsPerCta != 0) return qfail(PA_ERR_UNSUPPORTED, "pa_out_project: cols must be a multiple of 32");
+  QkvParams p;
+  p.x = (const __nv_bfloat16*)attn;
+  p.w[0] = p.w[1] = p.w[2] = (const __nv_bfloat16*)wo;
+  p.out[0] = p.out[1] = p.out[2] = (__nv_bfloat16*)out;
+  p.x_layer_stride = attn_layer_stride;
+  p.w_layer_stride[0] = p.w_layer_stride[1] = p.w_layer_stride[2] = wo_layer_stride;
+  p.out_layer_stride[0] = p.out_layer_stride[1] = p.out_layer_stride[2] = out_layer_stride;
+  p.n[0] = p.n[1] = p.n[2] = cols;
+  p.tiles_q = p.tiles_qk = cols / kColsPerCta;  // every tile belongs to output 0
+  p.rows = rows;
+  p.hidden = hidden;
+  p.residual = (const __nv_bfloat16*)residual;
+  const dim3 grid(p.tiles_q, layers);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (rows == 1)
+    qkv_project_kernel<1><<<grid, kThreads, 0, st>>>(p);
+  else if (rows == 2)
+    qkv_project_kernel<2><<<grid, kThreads, 0, st>>>(p);
+  else if (rows <= 4)
+    qkv_project_kernel<4><<<grid, kThreads, 0, st>>>(p);
+  else
+    qkv_project_kernel<8><<<grid, kThreads, 0, st>>>(p);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    char msg[256];
+    snprintf(msg, sizeof(msg), "pa_out_project: %s", cudaGetErrorString(e));
     return qfail(PA_ERR_CUDA, msg);
   }
   return PA_OK;

@@ -330,3 +330,11 @@ def qkv_project_packed(x, wq_packed, wk_packed, wv_packed, q, k, v, rows: int, s
                                       _ptr(v), rows, layers, hidden, q_cols, kv_cols, rows * hidden,
                                       hidden * q_cols, hidden * kv_cols, rows * q_cols, rows * kv_cols,
                                       _ptr(status), stream))
+
+
+def out_project(attn, wo, residual, out, rows: int, layers: int = 1, hidden: int = 2048, stream: int = 0) -> None:
+    """out = bf16(residual + bf16(attn W_o)) for the rows of a decode step, all layers in one launch.
+    attn [layers, rows, hidden]; wo [layers, hidden, cols]; residual (or None) and out [layers, rows, cols]."""
+    cols = int(wo.shape[-1])
+    check(lib().pa_out_project(_ptr(attn), _ptr(wo), _ptr(residual), _ptr(out), rows, layers, hidden, cols,
+                               rows * hidden, hidden * cols, rows * cols, stream))

@@ -247,3 +247,29 @@ def test_qkv_project_append_two_sequences(cuda):
         bf16_close(v[:, pos:], orc.transpose_v(v_lin[r0:r0 + n]), f"V of sequence {s}")
         r0 += n
     pool.close()
+
+
+@pytest.mark.parametrize("rows,layers,with_residual", [(1, 2, True), (4, 1, True), (2, 1, False)])
+def test_out_project_with_residual(cuda, rows, layers, with_residual):
+    """Output projection of a decode step with the attention residual folded in, against the oracle
+    (GEMM rounded to bf16, fp32 sum of two bf16 rounded once) and the reference GEMM kernel."""
+    rng = np.random.default_rng(800 + rows + layers)
+    a = orc.randn_bf16(rng, (layers, rows, 2048))
+    wo = orc.randn_bf16(rng, (layers, 2048, 2048), 0.03)
+    res = orc.randn_bf16(rng, (layers, rows, 2048))
+    out = torch.full((layers, rows, 2048), 5.0, dtype=torch.bfloat16, device=DEV)
+    ad, wd, rd = to_dev(a), to_dev(wo), to_dev(res)
+    paged.out_project(ad, wd, rd if with_residual else None, out, rows, layers)
+    torch.cuda.synchronize()
+    got = to_u16(out)
+    for l in range(layers):
+        lin = orc.gemm_bf16(a[l], wo[l])
+        want = orc.f32_to_bf16(orc.bf16_to_f32(res[l]) + orc.bf16_to_f32(lin)) if with_residual else lin
+        bf16_close(got[l], want, f"out_project layer {l}")
+    if orc.ref_available():
+        r = orc.ref()
+        lin = torch.zeros(rows, 2048, dtype=torch.bfloat16, device=DEV)
+        assert r.ref_gemm(ad[0].data_ptr(), wd[0].data_ptr(), lin.data_ptr(), rows, 2048, 2048) == 0
+        torch.cuda.synchronize()
+        want = (rd[0].float() + lin.float()).to(torch.bfloat16) if with_residual else lin
+        bf16_close(got[0], to_u16(want), "out_project against the reference GEMM + residual")
