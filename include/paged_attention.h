@@ -309,6 +309,12 @@ int pa_qkv_project(const void* x, const void* wq, const void* wk, const void* wv
 int pa_out_project(const void* attn, const void* wo, const void* residual, void* out, int rows, int layers,
                    int hidden, int cols, int64_t attn_layer_stride, int64_t wo_layer_stride,
                    int64_t out_layer_stride, void* stream);
+/* The same for prompt chunks (any number of rows), on the tensor cores: the projection GEMM of
+ * pa_qkv_project_append with a plain epilogue.  wo_packed from pa_pack_projection_weights; cols a
+ * multiple of 256; attn [rows, hidden], residual (nullable) and out [rows, cols].  Uses the pool's
+ * activation staging buffer and status word. */
+int pa_out_project_rows(pa_pool* pool, const void* attn, const void* wo_packed, const void* residual,
+                        void* out, int rows, int hidden, int cols, void* stream);
 /* pa_qkv_project on weights repacked by pa_pack_projection_weights (the format
  * pa_qkv_project_append reads, so one copy of the weights serves decode and
  * prefill): the stream becomes 8 KiB contiguous bursts through a bulk-copy ring.

@@ -909,6 +909,41 @@ int pa_qkv_project_append(pa_pool* p, int layer, const void* x, const void* wq, 
   return PA_OK;
 }
 
+int pa_out_project_rows(pa_pool* p, const void* attn, const void* wo_packed, const void* residual, void* out,
+                        int rows, int hidden, int cols, void* stream) {
+  if (!p || !attn || !wo_packed || !out) return fail(PA_ERR_INVALID_ARG, "pa_out_project_rows: NULL argument");
+  if (p->device < 0) return fail(PA_ERR_STATE, "pa_out_project_rows: host-only pool");
+  if (rows < 1) return PA_OK;
+  if (hidden < 64 || hidden % 64 != 0 || cols < 256 || cols % 256 != 0)
+    return fail(PA_ERR_UNSUPPORTED, "pa_out_project_rows: hidden must be a multiple of 64, cols a multiple of 256");
+  DeviceGuard g(p->device);
+  const size_t need = (size_t)((rows + 127) / 128) * 128 * hidden * sizeof(__nv_bfloat16);
+  if (need > p->x_pack_bytes) {
+    if (p->x_pack) {
+      PA_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+      cudaFree(p->x_pack);
+      p->x_pack = nullptr;
+      p->x_pack_bytes = 0;
+    }
+    PA_CUDA(cudaMalloc(&p->x_pack, need));
+    p->x_pack_bytes = need;
+  }
+  PA_CUDA(pa::launch_pack_x(attn, p->x_pack, rows, hidden, (cudaStream_t)stream));
+  pa::QkvGemmParams a = {};
+  a.x = (const __nv_bfloat16*)p->x_pack;
+  a.wq = a.wk = a.wv = (const __nv_bfloat16*)wo_packed;
+  a.q_out = (__nv_bfloat16*)out;
+  a.status = p->d_status;
+  a.rows = rows;
+  a.hidden = hidden;
+  a.q_cols = cols;
+  a.kv_cols = 256;
+  a.linear = 1;
+  a.residual = (const __nv_bfloat16*)residual;
+  PA_CUDA(pa::launch_qkv_gemm(a, (cudaStream_t)stream));
+  return PA_OK;
+}
+
 int pa_pool_step_launches(pa_pool* p, long long* count) {
   if (!p || !count) return fail(PA_ERR_INVALID_ARG, "pa_pool_step_launches: NULL argument");
   *count = p->step_launches;

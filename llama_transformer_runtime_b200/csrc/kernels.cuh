@@ -168,6 +168,10 @@ struct QkvGemmParams {
   const float* sin_table;
   int* status;
   int rows, hidden, q_cols, kv_cols, kv_heads, n_seqs, num_blocks, max_blocks_per_seq;
+  // linear != 0: one matrix (wq, q_cols columns), q_out = bf16(residual + bf16(x wq)) with plain
+  // [rows, q_cols] rows; no RoPE, no cache, the batch and table fields are unused
+  int linear = 0;
+  const __nv_bfloat16* residual = nullptr;  // [rows, q_cols], nullable
 };
 cudaError_t launch_qkv_gemm(const QkvGemmParams& p, cudaStream_t stream);
 // row-major [hidden, cols] -> per (64 k-rows, 64 columns) an 8 KiB block in the GEMM's shared-memory layout

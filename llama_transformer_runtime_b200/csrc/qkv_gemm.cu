@@ -75,10 +75,11 @@ qkv_gemm_kernel(QkvGemmParams p) {
   // column tile -> matrix and first column: tiles of Wq, then Wk, then Wv
   const int tq = p.q_cols / kGN, tk = p.kv_cols / kGN;
   const int ct = blockIdx.x;
-  const int which = ct < tq ? 0 : (ct < tq + tk ? 1 : 2);
-  const int n0 = (ct - (which == 0 ? 0 : (which == 1 ? tq : tq + tk))) * kGN;
-  const int n_cols = which == 0 ? p.q_cols : p.kv_cols;
-  const __nv_bfloat16* w = which == 0 ? p.wq : (which == 1 ? p.wk : p.wv);
+  // which: 0 Q, 1 K, 2 V (projection with RoPE + append); 3: plain linear layer with residual
+  const int which = p.linear ? 3 : (ct < tq ? 0 : (ct < tq + tk ? 1 : 2));
+  const int n0 = (ct - ((which == 0 || which == 3) ? 0 : (which == 1 ? tq : tq + tk))) * kGN;
+  const int n_cols = (which == 0 || which == 3) ? p.q_cols : p.kv_cols;
+  const __nv_bfloat16* w = (which == 0 || which == 3) ? p.wq : (which == 1 ? p.wk : p.wv);
   const int k_steps = p.hidden / kGK;
 
   if (tid == 0) {
@@ -134,8 +135,8 @@ qkv_gemm_kernel(QkvGemmParams p) {
       const int row = m0 + mh * kGM + warp * 32 + lane;  // token row; TMEM lane = warp * 32 + lane
       const uint32_t lane_base = ((uint32_t)(warp * 32) << 16) + (uint32_t)(mh * kGN);
       // which sequence and position this row is
-      int seq = -1, lpos = 0, pos = 0;
-      for (int s = 0; s < p.n_seqs; s++) {
+      int seq = (which == 3 && row < p.rows) ? 0 : -1, lpos = 0, pos = 0;
+      for (int s = 0; which != 3 && s < p.n_seqs; s++) {
         const BatchEntry e = p.batch[s];
         if (row >= e.kv_row_off && row < e.kv_row_off + e.n_new) {
           seq = e.seq;
@@ -144,7 +145,7 @@ qkv_gemm_kernel(QkvGemmParams p) {
         }
       }
       int blk = 0;
-      if (seq >= 0 && which != 0) {
+      if (seq >= 0 && (which == 1 || which == 2)) {
         blk = p.tables[(size_t)seq * p.max_blocks_per_seq + lpos / kBlockTok];
         if (blk < 0 || blk >= p.num_blocks) {
           atomicExch(p.status, kStatusBadBlock);
@@ -157,7 +158,7 @@ qkv_gemm_kernel(QkvGemmParams p) {
       // element from global memory instead (scalar, one 128-byte line per lane and load, 4 heads
       // over) they made the epilogue longer than the whole MMA loop.
       float* trow = reinterpret_cast<float*>(sm) + (warp * 32 + lane) * 65;
-      if (which != 2 && seq >= 0) {
+      if (which < 2 && seq >= 0) {
         const float4* cs4 = reinterpret_cast<const float4*>(p.cos_table + (size_t)pos * 32);
         const float4* sn4 = reinterpret_cast<const float4*>(p.sin_table + (size_t)pos * 32);
         float4 cv[8], sv[8];
@@ -192,7 +193,35 @@ qkv_gemm_kernel(QkvGemmParams p) {
         const int head = n0 / 64 + hb;
         // the GEMM's bf16 output, then RoPE on it: element i pairs with i + 32
         uint32_t lo[16], hi[16];  // bf16 pairs of elements 0..31 and 32..63
-        if (which == 2) {
+        if (which == 3) {
+          // plain output: bf16 of the accumulator, then (optionally) the residual added in fp32 and
+          // rounded once more, as the reference's GEMM and residual_add kernels do in turn
+          const size_t at = (size_t)row * p.q_cols + n0 + hb * 64;
+          uint4 rl[4], rh[4];
+          if (p.residual) {
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+              rl[c] = reinterpret_cast<const uint4*>(p.residual + at)[c];
+              rh[c] = reinterpret_cast<const uint4*>(p.residual + at)[c + 4];
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 16; i++) {
+            float a0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(acc[0][2 * i])));
+            float a1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(acc[0][2 * i + 1])));
+            float b0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(acc[1][2 * i])));
+            float b1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(acc[1][2 * i + 1])));
+            if (p.residual) {
+              const uint32_t ra = reinterpret_cast<const uint32_t*>(rl)[i], rb = reinterpret_cast<const uint32_t*>(rh)[i];
+              a0 += __uint_as_float(ra << 16);
+              a1 += __uint_as_float(ra & 0xffff0000u);
+              b0 += __uint_as_float(rb << 16);
+              b1 += __uint_as_float(rb & 0xffff0000u);
+            }
+            lo[i] = pack_bf16(a0, a1);
+            hi[i] = pack_bf16(b0, b1);
+          }
+        } else if (which == 2) {
 #pragma unroll
           for (int i = 0; i < 16; i++) {
             lo[i] = pack_bf16(__uint_as_float(acc[0][2 * i]), __uint_as_float(acc[0][2 * i + 1]));
@@ -214,7 +243,7 @@ qkv_gemm_kernel(QkvGemmParams p) {
             hi[i] = pack_bf16(y1a, y1b);
           }
         }
-        if (which == 0) {
+        if (which == 0 || which == 3) {
           uint4* dst = reinterpret_cast<uint4*>(p.q_out + ((size_t)row * (p.q_cols / 64) + head) * kHeadDim);
 #pragma unroll
           for (int c = 0; c < 4; c++) {
@@ -334,7 +363,7 @@ cudaError_t launch_qkv_gemm(const QkvGemmParams& p, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  const dim3 grid((p.q_cols + 2 * p.kv_cols) / kGN, (p.rows + kGMH * kGM - 1) / (kGMH * kGM));
+  const dim3 grid((p.linear ? p.q_cols : p.q_cols + 2 * p.kv_cols) / kGN, (p.rows + kGMH * kGM - 1) / (kGMH * kGM));
   qkv_gemm_kernel<<<grid, kGemmThreads, kGSmem, stream>>>(p);
   return cudaGetLastError();
 }

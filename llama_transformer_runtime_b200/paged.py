@@ -147,6 +147,11 @@ class KVPool:
         check(lib().pa_qkv_project_append(self._h, layer, _ptr(x), _ptr(wq), _ptr(wk), _ptr(wv), _ptr(cos),
                                           _ptr(sin), _ptr(q_out), hidden, stream))
 
+    def out_project_rows(self, attn, wo_packed, residual, out, rows: int, hidden: int = 2048, stream: int = 0) -> None:
+        """out = bf16(residual + bf16(attn W_o)) for a prompt chunk, on the tensor cores."""
+        check(lib().pa_out_project_rows(self._h, _ptr(attn), _ptr(wo_packed), _ptr(residual), _ptr(out), rows,
+                                        hidden, int(wo_packed.shape[-1]), stream))
+
     def prefill(self, layer: int, q, out, lse=None, scale: float = 0.125, stream: int = 0) -> None:
         check(lib().pa_prefill(self._h, layer, _ptr(q), _ptr(out), _ptr(lse), scale, stream))
 

@@ -273,3 +273,31 @@ def test_out_project_with_residual(cuda, rows, layers, with_residual):
         torch.cuda.synchronize()
         want = (rd[0].float() + lin.float()).to(torch.bfloat16) if with_residual else lin
         bf16_close(got[0], to_u16(want), "out_project against the reference GEMM + residual")
+
+
+@pytest.mark.parametrize("rows,with_residual", [(300, True), (128, False)])
+def test_out_project_rows_on_tensor_cores(cuda, rows, with_residual):
+    """Output projection of a prompt chunk (the projection GEMM with a plain epilogue) against the
+    oracle and the reference GEMM + residual."""
+    rng = np.random.default_rng(900 + rows)
+    a = orc.randn_bf16(rng, (rows, 2048))
+    wo = orc.randn_bf16(rng, (2048, 2048), 0.03)
+    res = orc.randn_bf16(rng, (rows, 2048))
+    pool = paged.KVPool(1, 8, 8, 1)
+    out = torch.full((rows, 2048), 5.0, dtype=torch.bfloat16, device=DEV)
+    ad, wd, rd = to_dev(a), to_dev(wo), to_dev(res)
+    pool.out_project_rows(ad, paged.pack_projection_weights(wd), rd if with_residual else None, out, rows)
+    torch.cuda.synchronize()
+    pool.check()
+    got = to_u16(out)
+    lin = orc.gemm_bf16(a, wo)
+    want = orc.f32_to_bf16(orc.bf16_to_f32(res) + orc.bf16_to_f32(lin)) if with_residual else lin
+    bf16_close(got, want, "out_project_rows")
+    if orc.ref_available():
+        r = orc.ref()
+        lr = torch.zeros(rows, 2048, dtype=torch.bfloat16, device=DEV)
+        assert r.ref_gemm(ad.data_ptr(), wd.data_ptr(), lr.data_ptr(), rows, 2048, 2048) == 0
+        torch.cuda.synchronize()
+        wr = (rd.float() + lr.float()).to(torch.bfloat16) if with_residual else lr
+        bf16_close(got, to_u16(wr), "out_project_rows against the reference GEMM + residual")
+    pool.close()
