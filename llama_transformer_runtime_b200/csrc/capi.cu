@@ -845,6 +845,23 @@ int pa_pool_set_step_kernel(pa_pool* p, int enable) {
   return PA_OK;
 }
 
+// The GEMM reads its activations from a tile-image copy (bulk-copyable).  The staging buffer belongs
+// to the pool and only grows: the first call allocates it, a later larger chunk synchronises the
+// stream, frees it and allocates the larger one.
+static int ensure_activation_staging(pa_pool* p, int rows, int hidden, void* stream) {
+  const size_t need = (size_t)((rows + 127) / 128) * 128 * hidden * sizeof(__nv_bfloat16);
+  if (need <= p->x_pack_bytes) return PA_OK;
+  if (p->x_pack) {
+    PA_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    cudaFree(p->x_pack);
+    p->x_pack = nullptr;
+    p->x_pack_bytes = 0;
+  }
+  PA_CUDA(cudaMalloc(&p->x_pack, need));
+  p->x_pack_bytes = need;
+  return PA_OK;
+}
+
 int pa_pack_projection_weights(const void* w, void* packed, int hidden, int cols, void* stream) {
   if (!w || !packed || w == packed) return fail(PA_ERR_INVALID_ARG, "pa_pack_projection_weights: NULL or aliased argument");
   if (hidden < 64 || hidden % 64 != 0 || cols < 64 || cols % 64 != 0)
@@ -871,19 +888,7 @@ int pa_qkv_project_append(pa_pool* p, int layer, const void* x, const void* wq, 
   }
   if (rows == 0) return PA_OK;
   DeviceGuard g(p->device);
-  // the activations go through a tile-image copy first (bulk-copyable by the GEMM); the buffer
-  // belongs to the pool and only grows (first call, or a larger chunk than any before)
-  const size_t need = (size_t)((rows + 127) / 128) * 128 * hidden * sizeof(__nv_bfloat16);
-  if (need > p->x_pack_bytes) {
-    if (p->x_pack) {
-      PA_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
-      cudaFree(p->x_pack);
-      p->x_pack = nullptr;
-      p->x_pack_bytes = 0;
-    }
-    PA_CUDA(cudaMalloc(&p->x_pack, need));
-    p->x_pack_bytes = need;
-  }
+  { const int r = ensure_activation_staging(p, rows, hidden, stream); if (r != PA_OK) return r; }
   PA_CUDA(pa::launch_pack_x(x, p->x_pack, rows, hidden, (cudaStream_t)stream));
   pa::QkvGemmParams a;
   a.x = (const __nv_bfloat16*)p->x_pack;
@@ -917,17 +922,7 @@ int pa_out_project_rows(pa_pool* p, const void* attn, const void* wo_packed, con
   if (hidden < 64 || hidden % 64 != 0 || cols < 256 || cols % 256 != 0)
     return fail(PA_ERR_UNSUPPORTED, "pa_out_project_rows: hidden must be a multiple of 64, cols a multiple of 256");
   DeviceGuard g(p->device);
-  const size_t need = (size_t)((rows + 127) / 128) * 128 * hidden * sizeof(__nv_bfloat16);
-  if (need > p->x_pack_bytes) {
-    if (p->x_pack) {
-      PA_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
-      cudaFree(p->x_pack);
-      p->x_pack = nullptr;
-      p->x_pack_bytes = 0;
-    }
-    PA_CUDA(cudaMalloc(&p->x_pack, need));
-    p->x_pack_bytes = need;
-  }
+  { const int r = ensure_activation_staging(p, rows, hidden, stream); if (r != PA_OK) return r; }
   PA_CUDA(pa::launch_pack_x(attn, p->x_pack, rows, hidden, (cudaStream_t)stream));
   pa::QkvGemmParams a = {};
   a.x = (const __nv_bfloat16*)p->x_pack;
