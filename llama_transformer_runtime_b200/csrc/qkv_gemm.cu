@@ -16,9 +16,9 @@
 // because every byte of it comes through L2: with 128 x 256 tiles (85 flop per
 // loaded byte, 295 MB of L2-to-SM traffic per layer) the kernel sat at 96 us per
 // layer whatever the load mechanism; 256 x 256 tiles move 197 MB.
-//   warp 0      load: per step ONE 16 KiB bulk (TMA) copy for the A tile (128 token
-//               rows x 64 k) and ONE 32 KiB bulk copy for the B tile (64 weight rows
-//               x 4 heads), 4 stages.  Both operands are read from tile images of
+//   warp 0      load: per step one 16 KiB bulk (TMA) copy per row half for the A tile (128
+//               token rows x 64 k) and ONE 32 KiB bulk copy for the B tile (64 weight rows
+//               x 4 heads), 3 stages of 64 KiB.  Both operands are read from tile images of
 //               the shared-memory layout the tensor cores want (rows of 128 bytes,
 //               16-byte chunks XOR-swizzled; A K-major, B MN-major), the same idea
 //               as the KV cache's tile layout: the weights are packed once, at load
@@ -28,9 +28,11 @@
 //               ran at 96 us per layer: lg_throttle and long_scoreboard stalls on
 //               the load path, tensor pipe 18 % busy.
 //   warps 0-3   epilogue after the last step: thread = token row = TMEM lane.
-//   warp 4      issues 16 tcgen05.mma (M128 N64 K16) per step from one elected
-//               lane into 4 x 64 TMEM columns and frees the stage with
-//               tcgen05.commit.
+//   warp 4      issues, per step, row half and 16-wide k-slice, one tcgen05.mma
+//               M128 N256 K16 from an elected lane (8 per step) into the half's 256
+//               TMEM columns — B spans four 128-byte atoms along N, 8 KiB apart,
+//               which is the descriptor's leading byte offset — and frees the
+//               stage with tcgen05.commit.
 // Every wait is bounded; on expiry the CTA raises its abort flag, the status
 // word gets PA_ERR_TIMEOUT and all warps leave through the common exit, where
 // tensor memory is released.
