@@ -165,3 +165,28 @@ int caller(__nv_bfloat16* q, __nv_bfloat16* k, __nv_bfloat16* v, float* c, float
                         os.path.join(ROOT, "include"), "-c", str(src), "-o", str(tmp_path / "caller.o")],
                        capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
+
+
+def test_projection_entries_validate_before_touching_a_device():
+    """Argument checks of the projection entries run on the host, before any CUDA call: they must
+    answer with a status and a message, never crash, with no GPU present."""
+    import ctypes as C
+    from llama_transformer_runtime_b200 import _lib
+    L = _lib.lib()
+    buf = (C.c_char * 64)()
+    ptr = C.addressof(buf)
+    # NULL argument
+    assert L.pa_qkv_project(None, ptr, ptr, ptr, ptr, ptr, ptr, 1, 1, 2048, 2048, 512, 0, 0, 0, 0, 0, None) == 1
+    assert b"NULL" in L.pa_last_error()
+    # more rows than a decode step may bring
+    rc = L.pa_qkv_project(ptr, ptr, ptr, ptr, ptr, ptr, ptr, 9, 1, 2048, 2048, 512, 0, 0, 0, 0, 0, None)
+    assert rc != 0 and b"at most 8 rows" in L.pa_last_error()
+    # hidden not a multiple of 64
+    rc = L.pa_qkv_project(ptr, ptr, ptr, ptr, ptr, ptr, ptr, 1, 1, 2000, 2048, 512, 0, 0, 0, 0, 0, None)
+    assert rc != 0 and b"hidden" in L.pa_last_error()
+    rc = L.pa_out_project(ptr, ptr, None, ptr, 1, 1, 2048, 2040, 0, 0, 0, None)
+    assert rc != 0 and b"cols" in L.pa_last_error()
+    rc = L.pa_pack_projection_weights(ptr, ptr, 2048, 2048, None)
+    assert rc != 0 and b"aliased" in L.pa_last_error()
+    rc = L.pa_qkv_project_packed(ptr, ptr, ptr, ptr, ptr, ptr, ptr, 1, 1, 2048, 2048, 500, 0, 0, 0, 0, 0, ptr, None)
+    assert rc != 0 and b"multiples of 64" in L.pa_last_error()
