@@ -179,9 +179,13 @@ int pa_gather_kv(pa_pool* pool, int layer, int seq_id, void* k_out, void* v_out,
  * The reference is single-GPU; this is the exchange long-context decode needs
  * once a sequence's cache is split by token range over n pools.  Each rank's
  * decode kernel stores its partial (normalised O, LSE) into every rank's
- * receive buffer with peer stores and raises a flag; pa_decode_step_sharded
- * then waits (bounded, PA_ERR_TIMEOUT via pa_pool_check) for all ranks' flags
- * and merges from local memory.  Buffers are shared through CUDA IPC handles of
+ * receive buffer with peer stores.  In pa_decode_step_sharded every value
+ * travels as an 8-byte word {value, step number}; the CTA that combined a
+ * (sequence, head) polls its own memory (bounded, PA_ERR_TIMEOUT via
+ * pa_pool_check) until all ranks' words of its rows carry the step number and
+ * merges them.  pa_decode_push / pa_exchange_merge use fp32 rows and one flag
+ * per (rank, head) instead.  No rank ever loads from a peer.  Buffers are shared
+ * through CUDA IPC handles of
  * PA_EXCHANGE_HANDLE_BYTES bytes that the host passes between processes.
  * All ranks must issue the same sequence of sharded steps. */
 typedef struct pa_exchange pa_exchange;
@@ -199,7 +203,8 @@ int pa_exchange_destroy(pa_exchange* x);
 /* The two halves of a sharded decode of one layer: pa_decode_push runs the
  * decode kernel, which pushes this rank's partials to all ranks;
  * pa_exchange_merge waits for all ranks' partials of that step and writes the
- * merged bf16 rows.  (pa_decode_step_sharded issues both per layer.) */
+ * merged bf16 rows.  (pa_decode_step_sharded does both inside one kernel, for
+ * all layers of the step in one cooperative launch when the batch allows it.) */
 int pa_decode_push(pa_pool* pool, pa_exchange* x, int layer, const void* q, float scale,
                    void* stream);
 int pa_exchange_merge(pa_pool* pool, pa_exchange* x, void* out, int64_t out_stride,
