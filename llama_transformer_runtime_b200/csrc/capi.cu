@@ -340,13 +340,13 @@ static DecodePlan pick_plan(const pa_pool* p) {
   }
   if (plan.chunk_blocks == 0) {
     if (pairs <= sms) {
-      // Smallest chunk for which every CTA is resident at once.  One SM per
+      // Smallest chunk for which every CTA is resident at once.  Two SMs per
       // (sequence, head) pair stays free: the CTA that combines a pair outlives
       // the others by the combine and the exchange, and in a multi-layer step
       // the next layer's CTAs (programmatic dependent launch) would otherwise
       // queue behind it — the whole step then advances at stream + combine
       // instead of at the stream rate.
-      const int budget = pairs * 4 <= sms ? sms - (int)pairs : sms;
+      const int budget = pairs * 4 <= sms ? sms - 2 * (int)pairs : sms;
       int lo = 1, hi = p->max_kv_blocks > 1 ? p->max_kv_blocks : 1;
       while (lo < hi) {
         const int mid = (lo + hi) / 2;
@@ -524,7 +524,9 @@ static int try_step_launch(pa_pool* p, pa_exchange* x, int layer_begin, int laye
     sp.seq_first[n_seqs] = (unsigned short)first;
     sp.n_stream = first;
   }
-  // one CTA per SM (the ring of an 8-warp CTA fills most of an SM's shared memory)
+  // one CTA per SM (the ring of an 8-warp CTA fills most of an SM's shared memory); two combining
+  // CTAs per pair when they fit
+  sp.combiners = sp.n_stream + 2 * n_seqs * p->kv_heads <= sms ? 2 : 1;
   if (pa::decode_step_ctas(sp) > sms || (long long)sp.ws_layer_items * layers > kWsItems) {
     if (x) pa::exchange_unfill(x);
     return 0;

@@ -72,10 +72,12 @@ __device__ __forceinline__ void write_row_outputs(const DecodeParams& p, int z, 
     const size_t at = ((size_t)(p.xchg_slot * p.xchg_world + p.xchg_rank) * p.xchg_rows + row) * kXchgRowFloats;
     const float lse = l > 0.f ? kLn2 * (m + log2f(l)) : -INFINITY;
     if (p.xchg_out) {
-      // merged in this kernel: {value, step number} words, valid on arrival
+      // merged in this kernel: {value, step number} words, valid on arrival; the word region has
+      // four slots (step number mod 4)
+      const size_t atw = ((size_t)((p.xchg_seq & 3u) * p.xchg_world + p.xchg_rank) * p.xchg_rows + row) * kXchgRowFloats;
       for (int g = 0; g < p.xchg_world; g++) {
-        st_word_sys(p.xchg_ll[g] + at + d, v, p.xchg_seq);
-        if (d == 0) st_word_sys(p.xchg_ll[g] + at + kHeadDim, lse, p.xchg_seq);
+        st_word_sys(p.xchg_ll[g] + atw + d, v, p.xchg_seq);
+        if (d == 0) st_word_sys(p.xchg_ll[g] + atw + kHeadDim, lse, p.xchg_seq);
       }
     } else {
       for (int g = 0; g < p.xchg_world; g++) {
@@ -121,7 +123,7 @@ __device__ __forceinline__ void exchange_wait_merge(const DecodeParams& p, int z
   __syncthreads();
   const int q_heads = p.kv_heads * kGroup;
   const unsigned long long* base =
-      p.xchg_ll[p.xchg_rank] + (size_t)p.xchg_slot * p.xchg_world * p.xchg_rows * kXchgRowFloats;
+      p.xchg_ll[p.xchg_rank] + (size_t)(p.xchg_seq & 3u) * p.xchg_world * p.xchg_rows * kXchgRowFloats;
   for (int idx = threadIdx.x; idx < kGroup * kHeadDim; idx += blockDim.x) {
     const int r = idx >> 6, d = idx & 63;
     const int head = h * kGroup + r;
@@ -624,13 +626,17 @@ decode_step_kernel(DecodeStepParams sp) {
     }
     return;
   }
-  const int pair = b - n_stream;
-  if (pair >= sp.n_seqs * sp.base.kv_heads) return;
+  // Combining CTAs: sp.combiners per (sequence, head), taking the layers in turn.  One CTA needs
+  // about 5 us per layer (2.2 us of combine, the rest waiting on its own loads and polls), more
+  // than a streaming CTA needs at short contexts (3.5 us), so with one the combiners set the pace.
+  const int n_pairs = sp.n_seqs * sp.base.kv_heads;
+  const int pair = (b - n_stream) % n_pairs, turn = (b - n_stream) / n_pairs;
+  if (turn >= sp.combiners) return;
   const int z = pair / sp.base.kv_heads, h = pair % sp.base.kv_heads;
   const BatchEntry e = sp.base.batch[z];
   const int n_blocks = (e.kv_len + kBlockTok - 1) / kBlockTok;
   const int n_chunks = max(1, (n_blocks + sp.base.chunk_blocks - 1) / sp.base.chunk_blocks);
-  for (int l = 0; l < sp.layers; l++) {
+  for (int l = turn; l < sp.layers; l += sp.combiners) {
     const DecodeParams p = step_layer_params(sp, l);
     if (threadIdx.x == 0) {
       const unsigned int* cnt = p.ws_count + pair;

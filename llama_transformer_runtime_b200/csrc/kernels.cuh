@@ -61,7 +61,7 @@ struct DecodeParams {
   __nv_bfloat16* xchg_out = nullptr;
   long long xchg_out_stride = 0;
   // In-kernel merge: partials travel as 8-byte words {value, step number}
-  // (xchg_ll[g] = rank g's word region, [2 slots][world][rows][65] words), so a
+  // (xchg_ll[g] = rank g's word region, [4 slots][world][rows][65] words, slot = step mod 4), so a
   // word is valid as soon as it carries this step's number: no fence, no flag.
   unsigned long long* xchg_ll[8] = {};
   // KV-head sharding: this rank's heads are columns [hs_col0, hs_col0 + q_heads*64)
@@ -100,12 +100,13 @@ struct DecodeStepParams {
   // (ragged batches get exactly the CTAs they need); n_stream = seq_first[n_seqs]
   int n_stream = 0;
   unsigned short seq_first[41] = {};
+  int combiners = 1;  // combining CTAs per (sequence, head): they take the layers in turn
 };
 constexpr int kMaxStepLayers = 64;
 constexpr int kMaxStepSeqs = 40;
 // CTAs of the step launch: streaming ones plus one combining CTA per (sequence, head)
 inline int decode_step_ctas(const DecodeStepParams& sp) {
-  return sp.n_stream + sp.n_seqs * sp.base.kv_heads;
+  return sp.n_stream + sp.combiners * sp.n_seqs * sp.base.kv_heads;
 }
 cudaError_t launch_decode_step(const DecodeStepParams& sp, int warps, int stages, cudaStream_t stream);
 
