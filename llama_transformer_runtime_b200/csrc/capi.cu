@@ -330,6 +330,16 @@ static long long plan_ctas(const pa_pool* p, int cb) {
   return n * p->kv_heads;
 }
 
+// Combining CTAs per (sequence, head) in the one-launch step: a combining CTA needs about 5 us per
+// layer; when a layer streams for less than that (short contexts, or a long one split over many
+// GPUs) two of them take the layers in turn, otherwise the second would only take SMs from the stream.
+static int step_combiners(const pa_pool* p) {
+  long long tokens = 0;
+  for (const auto& e : p->batch) tokens += e.kv_len;
+  const long long bytes_per_layer = tokens * p->kv_heads * 2 * pa::kHeadDim * 2;
+  return bytes_per_layer <= 48ll * 1000 * 1000 ? 2 : 1;  // 48 MB: about 8 us of streaming
+}
+
 static DecodePlan pick_plan(const pa_pool* p) {
   DecodePlan plan{p->decode_warps, p->decode_stages, p->chunk_blocks_override};
   const int sms = p->sm_count > 0 ? p->sm_count : 148;
@@ -340,13 +350,13 @@ static DecodePlan pick_plan(const pa_pool* p) {
   }
   if (plan.chunk_blocks == 0) {
     if (pairs <= sms) {
-      // Smallest chunk for which every CTA is resident at once.  Two SMs per
-      // (sequence, head) pair stays free: the CTA that combines a pair outlives
+      // Smallest chunk for which every CTA is resident at once.  One or two SMs per
+      // (sequence, head) pair stay free: the CTA that combines a pair outlives
       // the others by the combine and the exchange, and in a multi-layer step
       // the next layer's CTAs (programmatic dependent launch) would otherwise
       // queue behind it — the whole step then advances at stream + combine
       // instead of at the stream rate.
-      const int budget = pairs * 4 <= sms ? sms - 2 * (int)pairs : sms;
+      const int budget = pairs * 4 <= sms ? sms - step_combiners(p) * (int)pairs : sms;
       int lo = 1, hi = p->max_kv_blocks > 1 ? p->max_kv_blocks : 1;
       while (lo < hi) {
         const int mid = (lo + hi) / 2;
@@ -526,7 +536,8 @@ static int try_step_launch(pa_pool* p, pa_exchange* x, int layer_begin, int laye
   }
   // one CTA per SM (the ring of an 8-warp CTA fills most of an SM's shared memory); two combining
   // CTAs per pair when they fit
-  sp.combiners = sp.n_stream + 2 * n_seqs * p->kv_heads <= sms ? 2 : 1;
+  sp.combiners = step_combiners(p);
+  if (sp.n_stream + sp.combiners * n_seqs * p->kv_heads > sms) sp.combiners = 1;
   if (pa::decode_step_ctas(sp) > sms || (long long)sp.ws_layer_items * layers > kWsItems) {
     if (x) pa::exchange_unfill(x);
     return 0;
