@@ -22,7 +22,11 @@
 //     probabilities rounded to bf16 for P*V, flashattention.cu:249-336);
 //   * warps merge through shared memory; chunks merge through a workspace, the
 //     last CTA to arrive for a (sequence, KV head) does the combine and writes
-//     the [tokens, 2048]-layout row directly.
+//     the [tokens, 2048]-layout row directly;
+//   * a multi-layer decode step is ONE cooperative launch (decode_step_kernel):
+//     streaming CTAs go from layer to layer without waiting, one or two extra
+//     CTAs per (sequence, KV head) combine (and, across GPUs, exchange and
+//     merge) the layers behind them.
 #include "kernels.cuh"
 #include "rope.cuh"
 
