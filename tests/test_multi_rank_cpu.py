@@ -74,3 +74,43 @@ def test_range_sharded_decode_over_gloo(world, L):
         p.join(120)
         assert p.exitcode == 0
     assert q_out.get(timeout=5) is True
+
+
+def _exchange_schedule_is_safe(world, layers, combiners, slots, rng, steps=20000):
+    """Model of the in-kernel exchange under a random schedule.  Every rank has `combiners` actors;
+    actor c handles layers c, c + combiners, ...: it pushes its words of layer l (tagged l) into slot
+    l % slots of EVERY rank's buffer, then polls its own buffer until the words of all ranks in that
+    slot carry l.  A word tagged with a later layer in a slot somebody still polls means the protocol
+    overwrote data in use.  Returns False on such an overwrite, True when all actors finish."""
+    buf = [[[-1] * world for _ in range(slots)] for _ in range(world)]   # buf[rank][slot][src] = tag
+    state = {(r, c): ("push", c) for r in range(world) for c in range(combiners)}
+    for _ in range(steps):
+        live = [a for a, (_, l) in state.items() if l < layers]
+        if not live:
+            return True
+        r, c = live[rng.integers(len(live))]
+        phase, l = state[(r, c)]
+        if phase == "push":
+            for dst in range(world):
+                buf[dst][l % slots][r] = l
+            state[(r, c)] = ("poll", l)
+        else:
+            tags = buf[r][l % slots]
+            if any(t > l for t in tags):
+                return False            # a needed word was overwritten before it was read
+            if all(t == l for t in tags):
+                state[(r, c)] = ("push", l + combiners)
+    return all(l >= layers for _, l in state.values())
+
+
+def test_exchange_slot_count_is_enough_for_two_combining_ctas():
+    """One combining CTA per (sequence, head) is safe with two word slots; two CTAs on alternate
+    layers need four (a peer can be two layers ahead of a slot still being polled): the model finds
+    an overwrite with two slots and none with four, over many random schedules."""
+    rng = np.random.default_rng(2024)
+    for world in (1, 2, 3, 8):
+        for _ in range(60):
+            assert _exchange_schedule_is_safe(world, 16, 1, 2, rng)
+            assert _exchange_schedule_is_safe(world, 16, 2, 4, rng)
+    unsafe = sum(not _exchange_schedule_is_safe(2, 16, 2, 2, rng) for _ in range(200))
+    assert unsafe > 0, "two slots with two combining CTAs should be caught by some schedule"
