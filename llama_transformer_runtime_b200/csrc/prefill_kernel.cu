@@ -9,8 +9,9 @@
 // un-rounded probabilities, probabilities rounded to bf16 for P*V, O / sum
 // rounded to bf16; a query at position p sees keys 0..p.
 //
-// One CTA = 128 query rows of one query head (UMMA M = 128), walking 128-key
-// tiles of the cache up to the diagonal.
+// One work item = 128 query rows of one query head (UMMA M = 128), walking
+// 128-key tiles of the cache up to the diagonal; persistent CTAs (two per SM)
+// draw items from a counter, heaviest query tiles first.
 //   warp 8      loader: per tile 8 K tiles + 8 V tiles (2 KiB each, one cache
 //               block each) fetched through the block table with cp.async.bulk
 //               into a 3-stage ring.  The cache stores every tile already in
