@@ -986,6 +986,7 @@ def run_qkv_prefill(args):
         pool.set_free_order(np.random.default_rng(5).permutation(num_blocks))
         seq = pool.create_seq()
         pool.reserve(seq, S)
+        pool.reserve_rows(S, H)
         pool.batch_set([seq], [S])
         cos_h, sin_h = paged.build_rope_tables(S)
         cos, sin = torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev)

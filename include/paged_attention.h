@@ -8,7 +8,9 @@
  * Every entry returns a status (PA_OK == 0) and never exits or throws;
  * pa_last_error() gives the message of the calling thread's last failure.
  * Kernel entries are asynchronous on the stream they are given and do no
- * device synchronisation and no allocation.  A pool's host-side calls are not
+ * device synchronisation and no allocation: device memory is allocated only by
+ * the set-up calls (pa_pool_create, pa_pool_reserve_rows, pa_exchange_create,
+ * pa_gather_create).  A pool's host-side calls are not
  * thread-safe per pool; calls on one pool that overlap on the GPU share its
  * split-KV workspace and therefore must be ordered on one stream.
  *
@@ -68,6 +70,12 @@ const char* pa_last_error(void);
 int pa_pool_create(pa_pool** out, int device, int num_layers, int num_blocks,
                    int kv_heads, int max_seqs, int max_blocks_per_seq);
 int pa_pool_destroy(pa_pool* pool);
+/* Set-up call for the tensor-core projections (pa_qkv_project_append,
+ * pa_out_project_rows): sizes the pool's activation staging buffer for chunks of
+ * up to max_rows rows of `hidden` columns.  Synchronises the device when it has
+ * to replace a smaller buffer; the projection entries themselves never allocate
+ * and answer PA_ERR_STATE when the chunk is larger than what was reserved. */
+int pa_pool_reserve_rows(pa_pool* pool, int max_rows, int hidden);
 int pa_pool_free_blocks(const pa_pool* pool, int* n_free);
 /* Order in which free blocks are handed out (order[0] first).  Only valid
  * while no block is in use; lets a seeded permutation reproduce a shuffled or
@@ -149,7 +157,15 @@ int pa_decode(pa_pool* pool, int layer, const void* q, void* out,
  * trip per layer.  Layer l reads q_in + l*q_layer_stride, k_in/v_in +
  * l*kv_layer_stride, writes the rotated Q to q_rot + l*q_layer_stride (may
  * alias q_in) and its output rows to out + l*out_layer_stride (strides in
- * elements).  lse, if given, is [layers][n_seqs][q_heads]. */
+ * elements).  lse, if given, is [layers][n_seqs][q_heads].
+ * A call over SEVERAL layers needs every layer's q/k/v before it starts, i.e.
+ * inputs that do not depend on an earlier layer's output (a benchmark, a
+ * speculative or layer-parallel schedule): the one-launch step streams layer
+ * l+1 while layer l is still being combined.  In a real forward pass layer
+ * l+1's projections consume layer l's output, so the host calls it one layer
+ * at a time (layer_end = layer_begin + 1) between its projection launches, or
+ * uses pa_attention_step, which chains projections, attention and output
+ * projection per layer with the true data flow. */
 int pa_decode_step(pa_pool* pool, int layer_begin, int layer_end, const void* q_in,
                    const void* k_in, const void* v_in, int64_t q_layer_stride,
                    int64_t kv_layer_stride, const float* cos_table,
@@ -218,6 +234,24 @@ int pa_decode_step_sharded(pa_pool* pool, pa_exchange* x, int layer_begin, int l
                            void* out, int64_t out_stride, int64_t out_layer_stride,
                            float scale, void* stream);
 
+/* The same step for `world` (at most 4) ranks whose pools live on ONE GPU — a
+ * rehearsal of a multi-GPU deployment on a single device, and the way the
+ * in-kernel exchange is exercised where only one GPU is available.  Ranks wait
+ * on each other's words, and separate launches on one GPU are not guaranteed to
+ * run at the same time, so all ranks' steps run as ONE cooperative launch:
+ * every rank's step must fit SMs/world CTAs (at least 2 layers, one query row
+ * and at most one new token per sequence, q_rot apart from q_in; force fewer
+ * split-KV chunks with pa_pool_set_decode_chunk_blocks).  Arrays are indexed by
+ * rank; the exchanges are connected with pa_exchange_connect_ptrs.  No
+ * counterpart in the reference. */
+int pa_decode_step_sharded_colocated(pa_pool* const* pools, pa_exchange* const* xs, int world,
+                                     int layer_begin, int layer_end, const void* const* q_in,
+                                     const void* const* k_in, const void* const* v_in,
+                                     int64_t q_layer_stride, int64_t kv_layer_stride,
+                                     const float* cos_table, const float* sin_table,
+                                     void* const* q_rot, void* const* out, int64_t out_stride,
+                                     int64_t out_layer_stride, float scale, void* stream);
+
 /* ---- KV-head sharding over several GPUs ---------------------------------------
  * Each rank's pool holds 8/n KV heads (kv_heads of pa_pool_create) and serves
  * the 4*8/n query heads of those groups; every rank needs the full
@@ -255,20 +289,30 @@ int pa_gather_wait(pa_pool* pool, pa_gather* g, void* stream, void** rows);
  * layout (see pa_pool_layer_storage), device block tables
  * [n_seqs][table_stride], host kv_lens[n_seqs], q [n_seqs][4*kv_heads][64],
  * out rows of out_stride elements, optional lse [n_seqs][4*kv_heads].
- * The split-KV scratch is a fixed array inside the library image (about
- * 266 KiB, held by every GPU that loads the library until exit), hence the
+ * The split-KV scratch is a fixed array inside the library image (271104
+ * bytes = 264.75 KiB, held by every GPU that loads the library until exit), hence the
  * limit: at most PA_NOALLOC_MAX_SEQS sequences per call, larger batches are
  * rejected with PA_ERR_UNSUPPORTED.  No cudaMalloc/cudaFree or allocating
  * library routine is called.  All calls on a device share that array and it
  * keeps the previous call's contents (the entry re-zeroes what must start at
  * zero): calls that overlap on the GPU — different streams, no ordering —
  * race.  The first call on each device also resolves the array's device
- * address; make it before any stream capture begins. */
+ * address; make it before any stream capture begins.  A stream that is being
+ * captured is refused with PA_ERR_STATE: the entry copies its batch descriptor
+ * from host memory that does not outlive the call and plans its split from
+ * the host array kv_lens.
+ * The kernels record a block id outside [0, num_blocks) (block 0 is read in its
+ * place, so that call's rows are wrong) or a bounded wait that ran out in a status word of
+ * the same array; it stays there until pa_decode_noalloc_check(stream), which
+ * synchronises the stream, returns PA_ERR_INVALID_ARG / PA_ERR_TIMEOUT / PA_OK
+ * and clears the word.  It allocates nothing either and has no counterpart in
+ * the reference. */
 #define PA_NOALLOC_MAX_SEQS 8
 int pa_decode_noalloc(const void* cache_layer, int num_blocks, int kv_heads,
                       const int32_t* block_tables, int table_stride,
                       const int32_t* kv_lens, int n_seqs, const void* q, void* out,
                       int64_t out_stride, float* lse, float scale, void* stream);
+int pa_decode_noalloc_check(void* stream);
 
 /* Host: fp32 cos/sin tables [seq_len][32], Llama-3 frequency scaling. */
 int pa_build_rope_tables(float* cos_table, float* sin_table, int seq_len);
@@ -317,7 +361,7 @@ int pa_out_project(const void* attn, const void* wo, const void* residual, void*
 /* The same for prompt chunks (any number of rows), on the tensor cores: the projection GEMM of
  * pa_qkv_project_append with a plain epilogue.  wo_packed from pa_pack_projection_weights; cols a
  * multiple of 256; attn [rows, hidden], residual (nullable) and out [rows, cols].  Uses the pool's
- * activation staging buffer and status word. */
+ * activation staging buffer (pa_pool_reserve_rows) and status word. */
 int pa_out_project_rows(pa_pool* pool, const void* attn, const void* wo_packed, const void* residual,
                         void* out, int rows, int hidden, int cols, void* stream);
 /* pa_qkv_project on weights repacked by pa_pack_projection_weights (the format
@@ -343,7 +387,7 @@ int pa_pack_projection_weights(const void* w, void* packed, int hidden, int cols
  * in batch order (rows = the batch's new tokens, which must also be its query
  * rows); weights packed by pa_pack_projection_weights; q_out [rows, q_heads*64] receives the rotated queries,
  * K (rotated) and V go straight into the layer's paged cache.  Needs 4 or 8 KV
- * heads in the pool. */
+ * heads in the pool and a staging buffer of at least `rows` rows (pa_pool_reserve_rows). */
 int pa_qkv_project_append(pa_pool* pool, int layer, const void* x, const void* wq, const void* wk,
                           const void* wv, const float* cos_table, const float* sin_table, void* q_out,
                           int hidden, void* stream);

@@ -19,7 +19,7 @@ SYMBOLS = [
     "pa_seq_reserve", "pa_seq_length", "pa_seq_block_table", "pa_batch_set", "pa_batch_set_sharded", "pa_append",
     "pa_decode", "pa_decode_step", "pa_prefill", "pa_merge_partials", "pa_gather_kv", "pa_build_rope_tables",
     "pa_pool_check", "pa_pool_set_decode_chunk_blocks", "pa_pool_set_decode_shape", "pa_pool_set_step_kernel", "pa_pool_step_launches", "pa_qkv_project", "pa_out_project", "pa_out_project_rows", "pa_qkv_project_packed", "pa_qkv_project_append", "pa_pack_projection_weights",
-    "pa_decode_noalloc", "pa_exchange_create", "pa_exchange_handle", "pa_exchange_connect",
+    "pa_decode_noalloc", "pa_decode_noalloc_check", "pa_pool_reserve_rows", "pa_decode_step_sharded_colocated", "pa_exchange_create", "pa_exchange_handle", "pa_exchange_connect",
     "pa_exchange_destroy", "pa_decode_step_sharded", "pa_exchange_buffer", "pa_exchange_connect_ptrs",
     "pa_decode_push", "pa_exchange_merge", "pa_gather_create", "pa_gather_handle", "pa_gather_connect",
     "pa_gather_buffer", "pa_gather_connect_ptrs", "pa_gather_destroy", "pa_decode_step_gathered",
@@ -89,6 +89,9 @@ def lib():
         "pa_qkv_project_packed": [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i64, i64, i64, i64, i64, vp, vp],
         "pa_pack_projection_weights": [vp, vp, i, i, vp],
         "pa_decode_noalloc": [vp, i, i, vp, i, vp, i, vp, vp, i64, vp, f, vp],
+        "pa_decode_noalloc_check": [vp],
+        "pa_pool_reserve_rows": [vp, i, i],
+        "pa_decode_step_sharded_colocated": [vp, vp, i, i, i, vp, vp, vp, i64, i64, vp, vp, vp, vp, i64, i64, f, vp],
         "pa_exchange_create": [C.POINTER(vp), i, i, i, i, i],
         "pa_exchange_handle": [vp, vp],
         "pa_exchange_connect": [vp, vp],
@@ -109,7 +112,6 @@ def lib():
         "lt_launch_flash_attention": [vp],
         "lt_launch_rope_qkv": [vp, vp, vp, vp, vp, vp, vp, vp, i, i, vp],
         "lt_launch_flash_output_layout": [vp, vp, i, vp],
-        "pa_debug_set_rope_variant": [vp, i],
     }
     for name, args in sigs.items():
         fn = getattr(L, name)

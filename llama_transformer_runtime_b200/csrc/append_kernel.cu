@@ -14,9 +14,9 @@ namespace pa {
 constexpr int kAppendThreads = 256;
 constexpr int kAppendTokPerCta = 4;
 
-template <int VARIANT>
 __global__ void __launch_bounds__(kAppendThreads)
 append_kernel(AppendParams p) {
+  constexpr int VARIANT = 1;  // the rounding of the reference's compiled kernel (rope.cuh)
   const BatchEntry e = p.batch[blockIdx.y];
   const int tok0 = blockIdx.x * kAppendTokPerCta;
   const int n_q = p.q_out ? e.n_q : 0;
@@ -86,15 +86,10 @@ append_kernel(AppendParams p) {
   }
 }
 
-cudaError_t launch_append(const AppendParams& p, int n_seqs, int max_new, int rope_variant,
-                          cudaStream_t stream) {
+cudaError_t launch_append(const AppendParams& p, int n_seqs, int max_new, cudaStream_t stream) {
   if (n_seqs <= 0 || max_new <= 0) return cudaSuccess;
   dim3 grid((max_new + kAppendTokPerCta - 1) / kAppendTokPerCta, n_seqs);
-  switch (rope_variant) {
-    case 0: append_kernel<0><<<grid, kAppendThreads, 0, stream>>>(p); break;
-    case 2: append_kernel<2><<<grid, kAppendThreads, 0, stream>>>(p); break;
-    default: append_kernel<1><<<grid, kAppendThreads, 0, stream>>>(p); break;
-  }
+  append_kernel<<<grid, kAppendThreads, 0, stream>>>(p);
   return cudaGetLastError();
 }
 

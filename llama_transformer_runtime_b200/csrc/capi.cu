@@ -1,6 +1,6 @@
 // C-ABI layer (include/paged_attention.h): argument checks, pool ownership and
 // launches.  No torch types, no exceptions across the boundary, no allocation
-// outside pa_pool_create.
+// outside the set-up calls pa_pool_create and pa_pool_reserve_rows.
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -70,10 +70,9 @@ struct pa_pool {
   int chunk_blocks_override = 0;
   int decode_warps = 0, decode_stages = 0;  // 0: chosen per batch
   int sm_count = 0;
-  int rope_variant = 1;
   bool no_step_kernel = false;  // pa_pool_set_step_kernel(pool, 0): one kernel per layer
   long long step_launches = 0;  // decode steps that ran as one cooperative launch
-  void* x_pack = nullptr;       // activations in tile-image form for pa_qkv_project_append (grown on demand)
+  void* x_pack = nullptr;       // activations in tile-image form for the projection GEMM (pa_pool_reserve_rows)
   size_t x_pack_bytes = 0;
   int* prefill_work = nullptr;  // 64 item counters, one per prefill launch in rotation, zero when idle
   unsigned prefill_launches = 0;
@@ -305,7 +304,7 @@ int pa_append(pa_pool* p, int layer, const void* q_in, const void* k_in, const v
   a.kv_heads = p->kv_heads;
   a.num_blocks = p->host.num_blocks();
   a.max_blocks_per_seq = p->host.max_blocks_per_seq();
-  PA_CUDA(pa::launch_append(a, (int)p->batch.size(), p->max_new, p->rope_variant, (cudaStream_t)stream));
+  PA_CUDA(pa::launch_append(a, (int)p->batch.size(), p->max_new, (cudaStream_t)stream));
   return PA_OK;
 }
 
@@ -487,27 +486,30 @@ static int decode_impl(pa_pool* p, int layer, const void* q, void* out, int64_t 
   return PA_OK;
 }
 
-// The layers [layer_begin, layer_end) of a fused decode step as ONE cooperative
-// launch (decode_step_kernel), when the batch fits: every CTA resident at once
-// (streaming CTAs + one combining CTA per (sequence, head) <= SMs), a workspace
-// slice per layer.  Returns 1 when it launched, 0 when the caller should run
-// the layers one kernel each, < 0 on error.
-static int try_step_launch(pa_pool* p, pa_exchange* x, int layer_begin, int layer_end, const void* q_in,
-                           const void* k_in, const void* v_in, int64_t q_layer_stride, int64_t kv_layer_stride,
-                           const float* cos_table, const float* sin_table, void* q_rot, void* out,
-                           int64_t out_stride, int64_t out_layer_stride, float* lse, float scale, void* stream) {
+// Launch descriptor of the layers [layer_begin, layer_end) of a fused decode step as ONE
+// cooperative launch (decode_step_kernel), when the batch fits `sm_budget` SMs: every CTA resident
+// at once (streaming CTAs + one or two combining CTAs per (sequence, head)), a workspace slice per
+// layer.  Returns 1 when sp/plan describe the launch, 0 when the caller should run the layers one
+// kernel each, < 0 on error.  With an exchange it has taken ONE step number (exchange_fill); the
+// caller adds layers - 1 more when it launches, or hands the one back (exchange_unfill).
+static int build_step_params(pa_pool* p, pa_exchange* x, int layer_begin, int layer_end, const void* q_in,
+                             const void* k_in, const void* v_in, int64_t q_layer_stride, int64_t kv_layer_stride,
+                             const float* cos_table, const float* sin_table, void* q_rot, void* out,
+                             int64_t out_stride, int64_t out_layer_stride, float* lse, float scale, int sm_budget,
+                             pa::DecodeStepParams& sp, DecodePlan& plan) {
   const int layers = layer_end - layer_begin;
   if (layers < 2 || layers > pa::kMaxStepLayers || p->device < 0 || p->batch.empty() || p->no_step_kernel) return 0;
   const int n_seqs = (int)p->batch.size();
   if (n_seqs > pa::kMaxStepSeqs) return 0;
-  const int sms = p->sm_count > 0 ? p->sm_count : 148;
+  const int sms = sm_budget;
   const long long pairs = (long long)n_seqs * p->kv_heads;
   if (pairs * 4 > sms) return 0;
-  pa::DecodeStepParams sp;
-  DecodePlan plan{};
   const FusedAppend fz{k_in, v_in, cos_table, sin_table, q_rot, 0};
-  int r = decode_impl(p, layer_begin, q_in, out, out_stride, nullptr, lse, scale, stream, x, true, &fz, nullptr, 0,
+  const int saved_sms = p->sm_count;
+  p->sm_count = sms;  // the split plan aims at the SMs this step may use
+  int r = decode_impl(p, layer_begin, q_in, out, out_stride, nullptr, lse, scale, nullptr, x, true, &fz, nullptr, 0,
                       &sp.base, &plan);
+  p->sm_count = saved_sms;
   if (r != PA_OK) return r < 0 ? r : -r;
   if (!((plan.warps == 8 && (plan.stages == 4 || plan.stages == 3)) || (plan.warps == 4 && plan.stages == 4)) ||
       sp.base.max_chunks < 1) {
@@ -543,7 +545,21 @@ static int try_step_launch(pa_pool* p, pa_exchange* x, int layer_begin, int laye
     return 0;
   }
   sp.base.pdl = 0;
-  if (x) pa::exchange_advance(x, layers - 1);  // layer l is exchange step seq0 + l
+  return 1;
+}
+
+static int try_step_launch(pa_pool* p, pa_exchange* x, int layer_begin, int layer_end, const void* q_in,
+                           const void* k_in, const void* v_in, int64_t q_layer_stride, int64_t kv_layer_stride,
+                           const float* cos_table, const float* sin_table, void* q_rot, void* out,
+                           int64_t out_stride, int64_t out_layer_stride, float* lse, float scale, void* stream) {
+  pa::DecodeStepParams sp;
+  DecodePlan plan{};
+  const int sms = p->sm_count > 0 ? p->sm_count : 148;
+  const int t = build_step_params(p, x, layer_begin, layer_end, q_in, k_in, v_in, q_layer_stride, kv_layer_stride,
+                                  cos_table, sin_table, q_rot, out, out_stride, out_layer_stride, lse, scale, sms, sp,
+                                  plan);
+  if (t != 1) return t;
+  if (x) pa::exchange_advance(x, sp.layers - 1);  // layer l is exchange step seq0 + l
   DeviceGuard g(p->device);
   cudaError_t e = pa::launch_decode_step(sp, plan.warps, plan.stages, (cudaStream_t)stream);
   if (e != cudaSuccess) {
@@ -646,6 +662,73 @@ int pa_decode_step_sharded(pa_pool* p, pa_exchange* x, int layer_begin, int laye
     }
     if (r != PA_OK) return r;
   }
+  return PA_OK;
+}
+
+int pa_decode_step_sharded_colocated(pa_pool* const* pools, pa_exchange* const* xs, int world, int layer_begin,
+                                     int layer_end, const void* const* q_in, const void* const* k_in,
+                                     const void* const* v_in, int64_t q_layer_stride, int64_t kv_layer_stride,
+                                     const float* cos_table, const float* sin_table, void* const* q_rot,
+                                     void* const* out, int64_t out_stride, int64_t out_layer_stride, float scale,
+                                     void* stream) {
+  if (!pools || !xs || !q_in || !q_rot || !out || !cos_table || !sin_table)
+    return fail(PA_ERR_INVALID_ARG, "pa_decode_step_sharded_colocated: NULL argument");
+  if (world < 1 || world > pa::kMaxColocatedRanks)
+    return fail(PA_ERR_UNSUPPORTED, "pa_decode_step_sharded_colocated: 1..%d ranks per GPU", pa::kMaxColocatedRanks);
+  pa::ColocatedStepParams cp;
+  cp.world = world;
+  const int dev = pools[0] ? pools[0]->device : -1;
+  if (dev < 0) return fail(PA_ERR_STATE, "pa_decode_step_sharded_colocated: host-only pool");
+  const int sms = pools[0]->sm_count > 0 ? pools[0]->sm_count : 148;
+  int built = 0, rc = PA_OK;
+  for (int r = 0; r < world && rc == PA_OK; r++) {
+    pa_pool* p = pools[r];
+    if (!p || !xs[r] || !q_in[r] || !q_rot[r] || !out[r] || p->device != dev) {
+      rc = fail(PA_ERR_INVALID_ARG, "pa_decode_step_sharded_colocated: rank %d: NULL argument or a pool of another device", r);
+      break;
+    }
+    if (layer_begin < 0 || layer_end > p->num_layers || layer_begin > layer_end) {
+      rc = fail(PA_ERR_INVALID_ARG, "pa_decode_step_sharded_colocated: layers [%d, %d) out of range", layer_begin, layer_end);
+      break;
+    }
+    const void* ki = k_in ? k_in[r] : nullptr;
+    const void* vi = v_in ? v_in[r] : nullptr;
+    bool ok = can_fuse_append(p) && q_rot[r] != q_in[r];
+    for (const auto& e : p->batch)
+      if (e.n_new > 0 && (!ki || !vi)) ok = false;
+    if (!ok) {
+      rc = fail(PA_ERR_UNSUPPORTED, "pa_decode_step_sharded_colocated: rank %d: needs one query row and at most one new token "
+                                    "per sequence, k_in/v_in where tokens are appended, and q_rot apart from q_in", r);
+      break;
+    }
+    DecodePlan plan{};
+    const int t = build_step_params(p, xs[r], layer_begin, layer_end, q_in[r], ki, vi, q_layer_stride, kv_layer_stride,
+                                    cos_table, sin_table, q_rot[r], out[r], out_stride, out_layer_stride, nullptr, scale,
+                                    sms / world, cp.rank[r], plan);
+    if (t < 0) {
+      rc = -t;
+      break;
+    }
+    if (t == 1) built++;  // this rank holds one exchange step number now
+    if (t == 0 || plan.warps != 8 || plan.stages != 4) {
+      rc = fail(PA_ERR_UNSUPPORTED, "pa_decode_step_sharded_colocated: rank %d's step does not fit %d SMs as one launch of "
+                                    "8-warp CTAs (at least 2 layers; fewer chunks via pa_pool_set_decode_chunk_blocks)",
+                r, sms / world);
+      break;
+    }
+    const int ctas = pa::decode_step_ctas(cp.rank[r]);
+    if (ctas > cp.ctas_per_rank) cp.ctas_per_rank = ctas;
+  }
+  if (rc == PA_OK && cp.world * cp.ctas_per_rank > sms)
+    rc = fail(PA_ERR_UNSUPPORTED, "pa_decode_step_sharded_colocated: %d CTAs do not fit %d SMs", cp.world * cp.ctas_per_rank, sms);
+  if (rc != PA_OK) {
+    for (int r = 0; r < built; r++) pa::exchange_unfill(xs[r]);
+    return rc;
+  }
+  for (int r = 0; r < world; r++) pa::exchange_advance(xs[r], layer_end - layer_begin - 1);
+  DeviceGuard g(dev);
+  PA_CUDA(pa::launch_decode_step_colocated(cp, (cudaStream_t)stream));
+  for (int r = 0; r < world; r++) pools[r]->step_launches++;
   return PA_OK;
 }
 
@@ -842,6 +925,9 @@ int pa_pool_check(pa_pool* p, void* stream) {
   PA_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
   if (st == 0) return PA_OK;
   PA_CUDA(cudaMemsetAsync(p->d_status, 0, sizeof(int), (cudaStream_t)stream));
+  // a kernel that gave up may have left arrival counts behind; the next launch must find zeros
+  PA_CUDA(cudaMemsetAsync(p->ws_count, 0, (size_t)p->host.max_seqs() * p->kv_heads * pa::kMaxStepLayers * sizeof(unsigned int),
+                          (cudaStream_t)stream));
   if (st == pa::kStatusTimeout) return fail(PA_ERR_TIMEOUT, "a kernel gave up waiting for a bulk copy");
   return fail(PA_ERR_INVALID_ARG, "a kernel met a block id outside the pool");
 }
@@ -858,18 +944,27 @@ int pa_pool_set_step_kernel(pa_pool* p, int enable) {
   return PA_OK;
 }
 
-// The GEMM reads its activations from a tile-image copy (bulk-copyable).  The staging buffer belongs
-// to the pool and only grows: the first call allocates it, a later larger chunk synchronises the
-// stream, frees it and allocates the larger one.
-static int ensure_activation_staging(pa_pool* p, int rows, int hidden, void* stream) {
+// The GEMM reads its activations from a tile-image copy (bulk-copyable) in a staging buffer the
+// pool owns.  It is sized by pa_pool_reserve_rows, never by a kernel entry.
+static int check_activation_staging(pa_pool* p, int rows, int hidden, const char* who) {
   const size_t need = (size_t)((rows + 127) / 128) * 128 * hidden * sizeof(__nv_bfloat16);
   if (need <= p->x_pack_bytes) return PA_OK;
-  if (p->x_pack) {
-    PA_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
-    cudaFree(p->x_pack);
-    p->x_pack = nullptr;
-    p->x_pack_bytes = 0;
-  }
+  return fail(PA_ERR_STATE, "%s: %d rows x %d need a %zu-byte staging buffer, the pool has %zu "
+                            "(call pa_pool_reserve_rows first)", who, rows, hidden, need, p->x_pack_bytes);
+}
+
+int pa_pool_reserve_rows(pa_pool* p, int max_rows, int hidden) {
+  if (!p || max_rows < 1 || hidden < 64 || hidden % 64 != 0)
+    return fail(PA_ERR_INVALID_ARG, "pa_pool_reserve_rows: bad argument");
+  if (p->device < 0) return fail(PA_ERR_STATE, "pa_pool_reserve_rows: host-only pool");
+  const size_t need = (size_t)((max_rows + 127) / 128) * 128 * hidden * sizeof(__nv_bfloat16);
+  if (need <= p->x_pack_bytes) return PA_OK;
+  DeviceGuard g(p->device);
+  // set-up call: work that still reads the old buffer must have finished
+  PA_CUDA(cudaDeviceSynchronize());
+  if (p->x_pack) cudaFree(p->x_pack);
+  p->x_pack = nullptr;
+  p->x_pack_bytes = 0;
   PA_CUDA(cudaMalloc(&p->x_pack, need));
   p->x_pack_bytes = need;
   return PA_OK;
@@ -901,7 +996,7 @@ int pa_qkv_project_append(pa_pool* p, int layer, const void* x, const void* wq, 
   }
   if (rows == 0) return PA_OK;
   DeviceGuard g(p->device);
-  { const int r = ensure_activation_staging(p, rows, hidden, stream); if (r != PA_OK) return r; }
+  { const int r = check_activation_staging(p, rows, hidden, "pa_qkv_project_append"); if (r != PA_OK) return r; }
   PA_CUDA(pa::launch_pack_x(x, p->x_pack, rows, hidden, (cudaStream_t)stream));
   pa::QkvGemmParams a;
   a.x = (const __nv_bfloat16*)p->x_pack;
@@ -935,7 +1030,7 @@ int pa_out_project_rows(pa_pool* p, const void* attn, const void* wo_packed, con
   if (hidden < 64 || hidden % 64 != 0 || cols < 256 || cols % 256 != 0)
     return fail(PA_ERR_UNSUPPORTED, "pa_out_project_rows: hidden must be a multiple of 64, cols a multiple of 256");
   DeviceGuard g(p->device);
-  { const int r = ensure_activation_staging(p, rows, hidden, stream); if (r != PA_OK) return r; }
+  { const int r = check_activation_staging(p, rows, hidden, "pa_out_project_rows"); if (r != PA_OK) return r; }
   PA_CUDA(pa::launch_pack_x(attn, p->x_pack, rows, hidden, (cudaStream_t)stream));
   pa::QkvGemmParams a = {};
   a.x = (const __nv_bfloat16*)p->x_pack;
@@ -964,14 +1059,6 @@ int pa_pool_set_decode_shape(pa_pool* p, int warps, int stages) {
     return fail(PA_ERR_UNSUPPORTED, "pa_pool_set_decode_shape: %d warps x %d stages is not built", warps, stages);
   p->decode_warps = warps;
   p->decode_stages = stages;
-  return PA_OK;
-}
-
-// Test hook: selects how y0 = x0*c - x1*s is rounded in pa_append (0, 1, 2 as
-// in rope_pair); the default is the form that matches the reference kernel.
-int pa_debug_set_rope_variant(pa_pool* p, int variant) {
-  if (!p || variant < 0 || variant > 2) return fail(PA_ERR_INVALID_ARG, "pa_debug_set_rope_variant: bad argument");
-  p->rope_variant = variant;
   return PA_OK;
 }
 

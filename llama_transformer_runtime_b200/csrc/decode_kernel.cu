@@ -42,14 +42,18 @@ struct DecodeSmem {
   static constexpr int kBytes = 128 + kTiles + kBars + kMergeFloats * 4 + 16;
 };
 
-// One 8-byte word {value, step number}, stored and loaded whole.
+// One 8-byte word {value, step number}: value in the low half, step number in the high half,
+// moved by ONE scalar 64-bit access, which the ISA makes single-copy atomic (a vector access is a
+// set of scalar accesses that may formally be seen in parts).
 __device__ __forceinline__ void st_word_sys(unsigned long long* p, float v, unsigned int seq) {
-  asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(seq) : "memory");
+  const unsigned long long w = ((unsigned long long)seq << 32) | (unsigned long long)__float_as_uint(v);
+  asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
 __device__ __forceinline__ void ld_word_sys(const unsigned long long* p, float& v, unsigned int& seq) {
-  unsigned int a;
-  asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(a), "=r"(seq) : "l"(p) : "memory");
-  v = __uint_as_float(a);
+  unsigned long long w;
+  asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+  v = __uint_as_float((unsigned int)(w & 0xffffffffull));
+  seq = (unsigned int)(w >> 32);
 }
 
 __device__ __forceinline__ void write_row_outputs(const DecodeParams& p, int z, int h, int r, int d,
@@ -607,15 +611,10 @@ decode_kernel(DecodeParams p) {
 // combining CTAs wait on the streaming ones of the same grid, so the launch is
 // cooperative (all CTAs resident).
 template <int WARPS, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32)
-decode_step_kernel(DecodeStepParams sp) {
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem =
-      reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+__device__ __forceinline__ void decode_step_body(const DecodeStepParams& sp, const int b, unsigned char* smem) {
   __shared__ int s_ok;
   __shared__ int s_wait_ok;
   const int n_stream = sp.n_stream;
-  const int b = blockIdx.x;
   if (b < n_stream) {
     int z = 0;
     while (z + 1 < sp.n_seqs && b >= (int)sp.seq_first[z + 1]) z++;
@@ -665,6 +664,30 @@ decode_step_kernel(DecodeStepParams sp) {
     combine_pair<WARPS, STAGES>(p, z, h, n_chunks, smem, &s_wait_ok);
     __syncthreads();
   }
+}
+
+template <int WARPS, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32)
+decode_step_kernel(const __grid_constant__ DecodeStepParams sp) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem =
+      reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+  decode_step_body<WARPS, STAGES>(sp, blockIdx.x, smem);
+}
+
+// Several ranks of a range-sharded batch whose pools live on the SAME GPU, as one cooperative
+// launch: CTAs [r * ctas_per_rank, (r + 1) * ctas_per_rank) are rank r's step.  The ranks wait on
+// each other's exchange words, so they must be co-resident, which separate launches on one GPU
+// would not guarantee.
+template <int WARPS, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32)
+decode_step_ranks_kernel(const __grid_constant__ ColocatedStepParams cp) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem =
+      reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+  const int r = blockIdx.x / cp.ctas_per_rank;
+  if (r >= cp.world) return;
+  decode_step_body<WARPS, STAGES>(cp.rank[r], blockIdx.x - r * cp.ctas_per_rank, smem);
 }
 
 template <int WARPS, int STAGES>
@@ -740,6 +763,23 @@ cudaError_t launch_decode_step_cfg(const DecodeStepParams& sp, cudaStream_t stre
   // cooperative: the combining CTAs wait for the streaming CTAs of the same grid
   return cudaLaunchCooperativeKernel((const void*)decode_step_kernel<WARPS, STAGES>, dim3(decode_step_ctas(sp)),
                                      dim3(WARPS * 32), kargs, S::kBytes, stream);
+}
+
+cudaError_t launch_decode_step_colocated(const ColocatedStepParams& cp, cudaStream_t stream) {
+  using S = DecodeSmem<8, 4>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(decode_step_ranks_kernel<8, 4>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  ColocatedStepParams args = cp;
+  void* kargs[] = {&args};
+  return cudaLaunchCooperativeKernel((const void*)decode_step_ranks_kernel<8, 4>, dim3(cp.world * cp.ctas_per_rank),
+                                     dim3(8 * 32), kargs, S::kBytes, stream);
 }
 
 cudaError_t launch_decode_step(const DecodeStepParams& sp, int warps, int stages, cudaStream_t stream) {

@@ -12,7 +12,7 @@
 // descriptor and a status word — lives in the fixed array below.
 //
 // The array is part of the loaded library image: every GPU that loads the
-// library holds kScratchBytes (about 266 KiB) until the process exits.
+// library holds kScratchBytes (271104 bytes, 264.75 KiB) until the process exits.
 #include <cstdio>
 #include <mutex>
 
@@ -57,7 +57,10 @@ extern "C" {
 
 // First call on a device resolves the device address of the scratch array
 // (cudaGetSymbolAddress, with that device current) and reads the SM count.
-// It allocates nothing; make this first call outside any stream capture.
+// It allocates nothing.  No call may be made while `stream` is being captured:
+// the batch descriptor is copied from this function's stack and the split plan
+// is derived from the host array kv_lens, so a replay would read a dead address
+// and a frozen plan; a capturing stream is refused with PA_ERR_STATE.
 int pa_decode_noalloc(const void* cache_layer, int num_blocks, int kv_heads,
                       const int32_t* block_tables, int table_stride, const int32_t* kv_lens,
                       int n_seqs, const void* q, void* out, int64_t out_stride, float* lse,
@@ -82,6 +85,14 @@ int pa_decode_noalloc(const void* cache_layer, int num_blocks, int kv_heads,
   if (num_blocks < 1 || table_stride < 1) return fail(PA_ERR_INVALID_ARG, "num_blocks and table_stride must be positive");
   if (out_stride < (int64_t)kv_heads * pa::kGroup * pa::kHeadDim) return fail(PA_ERR_INVALID_ARG, "out_stride shorter than a row");
 
+  {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing((cudaStream_t)stream, &cap) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(PA_ERR_CUDA, "cannot query the stream");
+    }
+    if (cap != cudaStreamCaptureStatusNone) return fail(PA_ERR_STATE, "the stream is being captured; this entry cannot be recorded in a graph");
+  }
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return fail(PA_ERR_CUDA, "no current device");
   DeviceSetup* su = &g_setup[dev];
@@ -146,8 +157,10 @@ int pa_decode_noalloc(const void* cache_layer, int num_blocks, int kv_heads,
   cudaStream_t st = (cudaStream_t)stream;
   unsigned char* s = su->scratch;
   // Every call shares the array and finds the previous call's contents in it:
-  // tickets and the status word must start at zero, the descriptor is rewritten.
-  cudaError_t e = cudaMemsetAsync(s + kOffCount, 0, (kOffStatus + 256) - kOffCount, st);
+  // tickets must start at zero, the descriptor is rewritten.  The status word
+  // is left alone: it keeps what a kernel recorded until
+  // pa_decode_noalloc_check reads and clears it.
+  cudaError_t e = cudaMemsetAsync(s + kOffCount, 0, kOffStatus - kOffCount, st);
   if (e == cudaSuccess)
     e = cudaMemcpyAsync(s + kOffBatch, entries, (size_t)n_seqs * sizeof(pa::BatchEntry), cudaMemcpyHostToDevice, st);
   if (e != cudaSuccess) {
@@ -182,6 +195,39 @@ int pa_decode_noalloc(const void* cache_layer, int num_blocks, int kv_heads,
     return PA_ERR_CUDA;
   }
   return PA_OK;
+}
+
+// Reads and clears the status word the kernels of pa_decode_noalloc record in
+// the scratch array (this entry's callers have no pool, so pa_pool_check cannot
+// serve them).  Synchronises `stream`; allocates nothing.
+int pa_decode_noalloc_check(void* stream) {
+  char g_msg[256];
+  auto fail = [&](int code, const char* what) {
+    snprintf(g_msg, sizeof(g_msg), "pa_decode_noalloc_check: %s", what);
+    pa::set_last_error(g_msg);
+    return code;
+  };
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return fail(PA_ERR_CUDA, "no current device");
+  unsigned char* s = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    if (g_setup[dev].done) s = g_setup[dev].scratch;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!s) {  // pa_decode_noalloc never ran on this device
+    if (cudaStreamSynchronize(st) != cudaSuccess) return fail(PA_ERR_CUDA, "stream synchronisation failed");
+    return PA_OK;
+  }
+  int word = 0;
+  cudaError_t e = cudaMemcpyAsync(&word, s + kOffStatus, sizeof(int), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return fail(PA_ERR_CUDA, cudaGetErrorString(e));
+  if (word == 0) return PA_OK;
+  e = cudaMemsetAsync(s + kOffStatus, 0, sizeof(int), st);
+  if (e != cudaSuccess) return fail(PA_ERR_CUDA, cudaGetErrorString(e));
+  if (word == pa::kStatusTimeout) return fail(PA_ERR_TIMEOUT, "a kernel gave up waiting for a bulk copy");
+  return fail(PA_ERR_INVALID_ARG, "a kernel met a block id outside the cache (num_blocks); the rows of that call are not valid");
 }
 
 }  // extern "C"

@@ -17,8 +17,7 @@ struct AppendParams {
   int* status;
   int kv_heads, num_blocks, max_blocks_per_seq;
 };
-cudaError_t launch_append(const AppendParams& p, int n_seqs, int max_new, int rope_variant,
-                          cudaStream_t stream);
+cudaError_t launch_append(const AppendParams& p, int n_seqs, int max_new, cudaStream_t stream);
 
 struct GatherParams {
   const char* storage;
@@ -109,6 +108,15 @@ inline int decode_step_ctas(const DecodeStepParams& sp) {
   return sp.n_stream + sp.combiners * sp.n_seqs * sp.base.kv_heads;
 }
 cudaError_t launch_decode_step(const DecodeStepParams& sp, int warps, int stages, cudaStream_t stream);
+// The steps of up to kMaxColocatedRanks ranks whose pools share one GPU, as ONE cooperative launch
+// (8-warp, 4-stage CTAs): rank r owns CTAs [r * ctas_per_rank, (r + 1) * ctas_per_rank).
+constexpr int kMaxColocatedRanks = 4;
+struct ColocatedStepParams {
+  DecodeStepParams rank[kMaxColocatedRanks];
+  int world = 0, ctas_per_rank = 0;
+};
+static_assert(sizeof(ColocatedStepParams) <= 4000, "kernel parameter space");
+cudaError_t launch_decode_step_colocated(const ColocatedStepParams& cp, cudaStream_t stream);
 
 // Waits (bounded) until every rank's partial of step `seq` has landed in this
 // rank's receive buffer, then merges them: out rows bf16, stride out_stride.

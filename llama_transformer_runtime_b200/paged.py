@@ -179,8 +179,9 @@ class KVPool:
     def set_decode_shape(self, warps: int, stages: int) -> None:
         check(lib().pa_pool_set_decode_shape(self._h, warps, stages))
 
-    def _set_rope_variant(self, v: int) -> None:
-        check(lib().pa_debug_set_rope_variant(self._h, v))
+    def reserve_rows(self, max_rows: int, hidden: int = 2048) -> None:
+        """Set-up call: size the activation staging buffer of the tensor-core projections."""
+        check(lib().pa_pool_reserve_rows(self._h, max_rows, hidden))
 
 
 class Exchange:
@@ -285,6 +286,25 @@ def decode_step_sharded(pool: "KVPool", xchg: Exchange, layer_begin: int, layer_
     check(lib().pa_decode_step_sharded(pool._h, xchg._h, layer_begin, layer_end, _ptr(q_in), _ptr(k_in),
                                        _ptr(v_in), q_layer_stride, kv_layer_stride, _ptr(cos), _ptr(sin),
                                        _ptr(q_rot), _ptr(out), out_stride, out_layer_stride, scale, stream))
+
+
+def decode_step_sharded_colocated(pools, xchgs, layer_begin: int, layer_end: int, q_in, k_in, v_in,
+                                  q_layer_stride: int, kv_layer_stride: int, cos, sin, q_rot, out,
+                                  out_stride: int, out_layer_stride: int, scale: float = 0.125,
+                                  stream: int = 0) -> None:
+    """The sharded step of several ranks whose pools share one GPU, as one cooperative launch.
+    pools, xchgs, q_in, k_in, v_in, q_rot, out are per-rank lists (k_in/v_in entries may be None)."""
+    n = len(pools)
+    arr = lambda xs: (C.c_void_p * n)(*[C.c_void_p(_ptr(x)) for x in xs])
+    check(lib().pa_decode_step_sharded_colocated(
+        (C.c_void_p * n)(*[p._h for p in pools]), (C.c_void_p * n)(*[x._h for x in xchgs]), n, layer_begin,
+        layer_end, arr(q_in), arr(k_in), arr(v_in), q_layer_stride, kv_layer_stride, _ptr(cos), _ptr(sin),
+        arr(q_rot), arr(out), out_stride, out_layer_stride, scale, stream))
+
+
+def decode_noalloc_check(stream: int = 0) -> None:
+    """Read and clear the status word of pa_decode_noalloc's scratch (raises on a recorded error)."""
+    check(lib().pa_decode_noalloc_check(stream))
 
 
 def decode_noalloc(cache_layer, num_blocks: int, kv_heads: int, block_tables, table_stride: int,

@@ -30,7 +30,7 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(L, n), n
     assert sorted(_declared("legacy_kernels.h")) == sorted(_lib.LEGACY_SYMBOLS)
     assert sorted(set(_lib.SYMBOLS)) == [n for n in names if n in _lib.SYMBOLS]
-    assert set(names) <= set(_lib.SYMBOLS) | {"pa_debug_set_rope_variant"}, set(names) - set(_lib.SYMBOLS)
+    assert set(names) <= set(_lib.SYMBOLS), set(names) - set(_lib.SYMBOLS)
 
 
 def test_rope_tables_equal_oracle_bits():
