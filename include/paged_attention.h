@@ -328,6 +328,12 @@ int pa_pool_set_decode_chunk_blocks(pa_pool* pool, int chunk_blocks);
  * cooperative launch when the batch allows it (enable != 0, the default);
  * enable == 0 keeps one kernel per layer.  No counterpart in the reference. */
 int pa_pool_set_step_kernel(pa_pool* pool, int enable);
+/* allow == 0: the layers of a multi-layer decode step neither share a launch nor overlap (no
+ * programmatic dependent launch): layer l+1 starts when layer l's rows are final, as it must when
+ * its inputs depend on them.  The default (allow != 0) lets independent layers overlap. */
+int pa_pool_set_layer_overlap(pa_pool* pool, int allow);
+/* Combining CTAs per (sequence, KV head) in the one-launch step: 1, 2 or 4; 0 = heuristic. */
+int pa_pool_set_step_combiners(pa_pool* pool, int combiners);
 /* How many decode steps of this pool ran as one launch so far. */
 int pa_pool_step_launches(pa_pool* pool, long long* count);
 /* Warps per decode CTA and 4 KiB ring stages per warp (built shapes only). */

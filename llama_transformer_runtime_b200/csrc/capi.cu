@@ -71,6 +71,8 @@ struct pa_pool {
   int decode_warps = 0, decode_stages = 0;  // 0: chosen per batch
   int sm_count = 0;
   bool no_step_kernel = false;  // pa_pool_set_step_kernel(pool, 0): one kernel per layer
+  bool no_layer_overlap = false;  // pa_pool_set_layer_overlap(pool, 0): a layer starts after the previous one has finished
+  int step_combiners_override = 0;  // pa_pool_set_step_combiners
   long long step_launches = 0;  // decode steps that ran as one cooperative launch
   void* x_pack = nullptr;       // activations in tile-image form for the projection GEMM (pa_pool_reserve_rows)
   size_t x_pack_bytes = 0;
@@ -329,14 +331,19 @@ static long long plan_ctas(const pa_pool* p, int cb) {
   return n * p->kv_heads;
 }
 
-// Combining CTAs per (sequence, head) in the one-launch step: a combining CTA needs about 5 us per
-// layer; when a layer streams for less than that (short contexts, or a long one split over many
-// GPUs) two of them take the layers in turn, otherwise the second would only take SMs from the stream.
+// Combining CTAs per (sequence, head) in the one-launch step.  A combining CTA needs about 4 us
+// per layer (wait, combine, exchange); the streaming CTAs finish a layer in (bytes per layer) /
+// (HBM rate).  When a layer streams for less than that, 2 or 4 combining CTAs take the layers in
+// turn; when it streams for longer a second one would only take SMs from the stream.  The count is
+// 1, 2 or 4: the exchange's word slots must be a multiple of it (kXchgWordSlots).
 static int step_combiners(const pa_pool* p) {
+  if (p->step_combiners_override > 0) return p->step_combiners_override;
   long long tokens = 0;
   for (const auto& e : p->batch) tokens += e.kv_len;
   const long long bytes_per_layer = tokens * p->kv_heads * 2 * pa::kHeadDim * 2;
-  return bytes_per_layer <= 48ll * 1000 * 1000 ? 2 : 1;  // 48 MB: about 8 us of streaming
+  if (bytes_per_layer > 48ll * 1000 * 1000) return 1;  // more than about 8 us of streaming
+  if (bytes_per_layer > 16ll * 1000 * 1000) return 2;
+  return 4;
 }
 
 static DecodePlan pick_plan(const pa_pool* p) {
@@ -498,7 +505,9 @@ static int build_step_params(pa_pool* p, pa_exchange* x, int layer_begin, int la
                              int64_t out_stride, int64_t out_layer_stride, float* lse, float scale, int sm_budget,
                              pa::DecodeStepParams& sp, DecodePlan& plan) {
   const int layers = layer_end - layer_begin;
-  if (layers < 2 || layers > pa::kMaxStepLayers || p->device < 0 || p->batch.empty() || p->no_step_kernel) return 0;
+  if (layers < 2 || layers > pa::kMaxStepLayers || p->device < 0 || p->batch.empty() || p->no_step_kernel ||
+      p->no_layer_overlap)
+    return 0;
   const int n_seqs = (int)p->batch.size();
   if (n_seqs > pa::kMaxStepSeqs) return 0;
   const int sms = sm_budget;
@@ -539,7 +548,7 @@ static int build_step_params(pa_pool* p, pa_exchange* x, int layer_begin, int la
   // one CTA per SM (the ring of an 8-warp CTA fills most of an SM's shared memory); two combining
   // CTAs per pair when they fit
   sp.combiners = step_combiners(p);
-  if (sp.n_stream + sp.combiners * n_seqs * p->kv_heads > sms) sp.combiners = 1;
+  while (sp.combiners > 1 && sp.n_stream + sp.combiners * n_seqs * p->kv_heads > sms) sp.combiners /= 2;
   if (pa::decode_step_ctas(sp) > sms || (long long)sp.ws_layer_items * layers > kWsItems) {
     if (x) pa::exchange_unfill(x);
     return 0;
@@ -618,7 +627,7 @@ int pa_decode_step_gathered(pa_pool* p, pa_gather* g, const void* q_in, const vo
     const __nv_bfloat16* ki = (const __nv_bfloat16*)k_in + (size_t)l * kv_layer_stride;
     const __nv_bfloat16* vi = (const __nv_bfloat16*)v_in + (size_t)l * kv_layer_stride;
     __nv_bfloat16* qr = (__nv_bfloat16*)q_rot + (size_t)l * q_layer_stride;
-    const FusedAppend fz{ki, vi, cos_table, sin_table, qr, l > 0 ? 1 : 0};
+    const FusedAppend fz{ki, vi, cos_table, sin_table, qr, l > 0 && !p->no_layer_overlap ? 1 : 0};
     int r = decode_impl(p, l, qi, nullptr, 0, nullptr, nullptr, scale, stream, nullptr, true, &fz, g, l);
     if (r != PA_OK) return r;
   }
@@ -654,7 +663,7 @@ int pa_decode_step_sharded(pa_pool* p, pa_exchange* x, int layer_begin, int laye
     int r;
     if (fuse) {
       // one kernel per layer: RoPE(Q), RoPE(K) + append, decode, exchange, merge
-      const FusedAppend fz{ki, vi, cos_table, sin_table, qr, l > layer_begin ? 1 : 0};
+      const FusedAppend fz{ki, vi, cos_table, sin_table, qr, l > layer_begin && !p->no_layer_overlap ? 1 : 0};
       r = decode_impl(p, l, qi, o, out_stride, nullptr, nullptr, scale, stream, x, true, &fz);
     } else {
       r = pa_append(p, l, qi, ki, vi, cos_table, sin_table, qr, stream);
@@ -763,7 +772,7 @@ int pa_decode_step(pa_pool* p, int layer_begin, int layer_end, const void* q_in,
     float* lse_l = lse ? lse + (size_t)i * n_seqs * q_heads : nullptr;
     int r;
     if (fuse) {
-      const FusedAppend fz{ki, vi, cos_table, sin_table, qr, l > layer_begin ? 1 : 0};
+      const FusedAppend fz{ki, vi, cos_table, sin_table, qr, l > layer_begin && !p->no_layer_overlap ? 1 : 0};
       r = decode_impl(p, l, qi, o, out_stride, nullptr, lse_l, scale, stream, nullptr, true, &fz);
     } else {
       r = pa_append(p, l, qi, ki, vi, cos_table, sin_table, qr, stream);
@@ -1044,6 +1053,19 @@ int pa_out_project_rows(pa_pool* p, const void* attn, const void* wo_packed, con
   a.linear = 1;
   a.residual = (const __nv_bfloat16*)residual;
   PA_CUDA(pa::launch_qkv_gemm(a, (cudaStream_t)stream));
+  return PA_OK;
+}
+
+int pa_pool_set_layer_overlap(pa_pool* p, int allow) {
+  if (!p) return fail(PA_ERR_INVALID_ARG, "pa_pool_set_layer_overlap: NULL pool");
+  p->no_layer_overlap = allow == 0;
+  return PA_OK;
+}
+
+int pa_pool_set_step_combiners(pa_pool* p, int combiners) {
+  if (!p || (combiners != 0 && combiners != 1 && combiners != 2 && combiners != 4))
+    return fail(PA_ERR_INVALID_ARG, "pa_pool_set_step_combiners: 0 (heuristic), 1, 2 or 4");
+  p->step_combiners_override = combiners;
   return PA_OK;
 }
 

@@ -40,6 +40,9 @@ struct DecodeSmem {
   static constexpr int kBars = WARPS * STAGES * 8;
   static constexpr int kMergeFloats = WARPS * (kGroup * kHeadDim + 2 * kGroup);
   static constexpr int kBytes = 128 + kTiles + kBars + kMergeFloats * 4 + 16;
+  // the step kernel appends every layer's rotated query rows: [layers][4][64] bf16
+  static constexpr int kStepQ = (kTiles + kBars + kMergeFloats * 4 + 16 + 127) & ~127;
+  static constexpr int step_bytes(int layers) { return 128 + kStepQ + layers * kGroup * kHeadDim * 2; }
 };
 
 // One 8-byte word {value, step number}: value in the low half, step number in the high half,
@@ -81,8 +84,8 @@ __device__ __forceinline__ void write_row_outputs(const DecodeParams& p, int z, 
     const float lse = l > 0.f ? kLn2 * (m + log2f(l)) : -INFINITY;
     if (p.xchg_out) {
       // merged in this kernel: {value, step number} words, valid on arrival; the word region has
-      // four slots (step number mod 4)
-      const size_t atw = ((size_t)((p.xchg_seq & 3u) * p.xchg_world + p.xchg_rank) * p.xchg_rows + row) * kXchgRowFloats;
+      // kXchgWordSlots slots (step number modulo that)
+      const size_t atw = ((size_t)((p.xchg_seq & (kXchgWordSlots - 1u)) * p.xchg_world + p.xchg_rank) * p.xchg_rows + row) * kXchgRowFloats;
       for (int g = 0; g < p.xchg_world; g++) {
         st_word_sys(p.xchg_ll[g] + atw + d, v, p.xchg_seq);
         if (d == 0) st_word_sys(p.xchg_ll[g] + atw + kHeadDim, lse, p.xchg_seq);
@@ -131,28 +134,42 @@ __device__ __forceinline__ void exchange_wait_merge(const DecodeParams& p, int z
   __syncthreads();
   const int q_heads = p.kv_heads * kGroup;
   const unsigned long long* base =
-      p.xchg_ll[p.xchg_rank] + (size_t)(p.xchg_seq & 3u) * p.xchg_world * p.xchg_rows * kXchgRowFloats;
+      p.xchg_ll[p.xchg_rank] + (size_t)(p.xchg_seq & (kXchgWordSlots - 1u)) * p.xchg_world * p.xchg_rows * kXchgRowFloats;
   for (int idx = threadIdx.x; idx < kGroup * kHeadDim; idx += blockDim.x) {
     const int r = idx >> 6, d = idx & 63;
     const int head = h * kGroup + r;
     const int row = z * q_heads + head;
-    // every rank's LSE and value d of this row, each polled until it carries this step
+    // every rank's LSE and value d of this row: all still-missing words are loaded in one go (the
+    // loads overlap), then checked; a word is valid once it carries this step's number
     float lse[8], val[8];
     bool ok = true;
+    unsigned int need_l = (1u << p.xchg_world) - 1u, need_v = need_l;
+    SpinDeadline dl;
+    while (need_l | need_v) {
+      float tl[8], tv[8];
+      unsigned int sl[8], sv[8];
 #pragma unroll
-    for (int g = 0; g < 8; g++) {
-      if (g >= p.xchg_world || !ok) continue;
-      const unsigned long long* rowp = base + ((size_t)g * p.xchg_rows + row) * kXchgRowFloats;
-      SpinDeadline dl;
-      unsigned int s0 = 0, s1 = 0;
-      for (;;) {
-        if (s0 != p.xchg_seq) ld_word_sys(rowp + kHeadDim, lse[g], s0);
-        if (s1 != p.xchg_seq) ld_word_sys(rowp + d, val[g], s1);
-        if (s0 == p.xchg_seq && s1 == p.xchg_seq) break;
-        if (dl.expired()) {
-          ok = false;
-          break;
+      for (int g = 0; g < 8; g++) {
+        if (g >= p.xchg_world) continue;
+        const unsigned long long* rowp = base + ((size_t)g * p.xchg_rows + row) * kXchgRowFloats;
+        if ((need_l >> g) & 1u) ld_word_sys(rowp + kHeadDim, tl[g], sl[g]);
+        if ((need_v >> g) & 1u) ld_word_sys(rowp + d, tv[g], sv[g]);
+      }
+#pragma unroll
+      for (int g = 0; g < 8; g++) {
+        if (g >= p.xchg_world) continue;
+        if (((need_l >> g) & 1u) && sl[g] == p.xchg_seq) {
+          lse[g] = tl[g];
+          need_l &= ~(1u << g);
         }
+        if (((need_v >> g) & 1u) && sv[g] == p.xchg_seq) {
+          val[g] = tv[g];
+          need_v &= ~(1u << g);
+        }
+      }
+      if ((need_l | need_v) && dl.expired()) {
+        ok = false;
+        break;
       }
     }
     if (!ok) {
@@ -203,17 +220,12 @@ __device__ __forceinline__ DecodeParams step_layer_params(const DecodeStepParams
   return p;
 }
 
-// Work of one CTA on chunk x of (sequence z, KV head h) of one layer.
-// kClassic: the kernel of one layer — partials meet through arrival tickets and
-// the last CTA of a (sequence, head) combines them.  kStepStream: a streaming
-// CTA of the persistent step kernel — it always leaves a partial, counts one
-// arrival for the pair's combining CTA and returns to take the next layer.
-// tile_base: tiles this warp has pulled through its ring so far (the ring and
-// its barrier phases run on across layers).
-enum { kClassic = 0, kStepStream = 1 };
-template <int WARPS, int STAGES, int MODE>
+// Work of one CTA on chunk x of (sequence z, KV head h) of one layer (the kernel of one layer):
+// partials meet through arrival tickets and the last CTA of a (sequence, head) combines them.
+template <int WARPS, int STAGES>
 __device__ __forceinline__ void decode_cta(const DecodeParams& p, const int x, const int h, const int z,
-                                           unsigned char* smem, uint32_t& tile_base) {
+                                           unsigned char* smem) {
+  uint32_t tile_base = 0;
   using S = DecodeSmem<WARPS, STAGES>;
   unsigned char* tiles = smem;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kTiles);
@@ -465,7 +477,7 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const int x, c
       L += wgt * mrg_l[w * kGroup + r];
       O += wgt * mrg_o[(w * kGroup + r) * kHeadDim + d];
     }
-    if (MODE == kClassic && n_chunks == 1) {
+    if (n_chunks == 1) {
       write_row_outputs(p, z, h, r, d, O, M, L);
     } else {
       p.ws_acc[(size_t)item * (kGroup * kHeadDim) + idx] = O;
@@ -474,13 +486,6 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const int x, c
         p.ws_ml[(size_t)item * (2 * kGroup) + kGroup + r] = L;
       }
     }
-  }
-  if (MODE == kStepStream) {
-    // the pair's combining CTA polls this counter (acquire) and then reads the partials
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) atomicAdd(&p.ws_count[z * p.kv_heads + h], 1u);
-    return;
   }
   if (n_chunks == 1) {
     publish_exchange(p, z, h);
@@ -525,6 +530,17 @@ __device__ __forceinline__ void combine_pair(const DecodeParams& p, const int z,
   const size_t item0 = (size_t)(z * p.kv_heads + h) * p.max_chunks;
   float* cm = reinterpret_cast<float*>(tiles);  // [n_chunks][8]
   float* cw = cm + (size_t)n_chunks * 8;        // [n_chunks][4]
+  // thread = (chunk group g, float4 column q): 64 float4 columns cover the 4x64 outputs.  The
+  // first four partial loads of every thread do not depend on the weights: they are issued
+  // together with the (m, l) loads, so the two latencies overlap.
+  constexpr int G = T / 64;
+  const int q4 = threadIdx.x & 63, g = threadIdx.x >> 6;
+  const int r4 = q4 >> 4;
+  const float4* src = reinterpret_cast<const float4*>(p.ws_acc + item0 * (kGroup * kHeadDim)) + q4;
+  float4 v0[4];
+#pragma unroll
+  for (int u = 0; u < 4; u++)
+    v0[u] = g + u * G < n_chunks ? __ldcg(src + (size_t)(g + u * G) * 64) : make_float4(0.f, 0.f, 0.f, 0.f);
   for (int i = threadIdx.x; i < n_chunks * 8; i += T) cm[i] = __ldcg(p.ws_ml + item0 * 8 + i);
   __syncthreads();
   for (int r = warp; r < kGroup; r += WARPS) {
@@ -547,13 +563,17 @@ __device__ __forceinline__ void combine_pair(const DecodeParams& p, const int z,
     }
   }
   __syncthreads();
-  // thread = (chunk group g, float4 column q): 64 float4 columns cover the 4x64 outputs
-  constexpr int G = T / 64;
-  const int q4 = threadIdx.x & 63, g = threadIdx.x >> 6;
-  const int r4 = q4 >> 4;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  const float4* src = reinterpret_cast<const float4*>(p.ws_acc + item0 * (kGroup * kHeadDim)) + q4;
-  int c = g;
+#pragma unroll
+  for (int u = 0; u < 4; u++) {
+    if (g + u * G >= n_chunks) continue;
+    const float wgt = cw[(g + u * G) * 4 + r4];
+    acc.x += wgt * v0[u].x;
+    acc.y += wgt * v0[u].y;
+    acc.z += wgt * v0[u].z;
+    acc.w += wgt * v0[u].w;
+  }
+  int c = g + 4 * G;
   for (; c + 3 * G < n_chunks; c += 4 * G) {
     float4 v[4];
 #pragma unroll
@@ -596,8 +616,7 @@ decode_kernel(DecodeParams p) {
       reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
   // let the next layer's kernel take SMs as soon as this one's CTAs leave them
   if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  uint32_t tile_base = 0;
-  decode_cta<WARPS, STAGES, kClassic>(p, blockIdx.x, blockIdx.y, blockIdx.z, smem, tile_base);
+  decode_cta<WARPS, STAGES>(p, blockIdx.x, blockIdx.y, blockIdx.z, smem);
 }
 
 // ---- the whole multi-layer decode step as ONE launch --------------------------
@@ -610,6 +629,291 @@ decode_kernel(DecodeParams p) {
 // counted, merges them, writes the rows and runs the cross-GPU exchange.  The
 // combining CTAs wait on the streaming ones of the same grid, so the launch is
 // cooperative (all CTAs resident).
+// A streaming CTA of the one-launch step: chunk x of (sequence z, KV head h), layer after layer.
+// Everything that does not depend on the tiles is done ONCE, before the first layer: the batch
+// entry, the rotation of every layer's 4 query rows (kept in shared memory as bf16, ready to be
+// picked up as A fragments), the rotated-query output rows and the appended K/V rows of all layers.
+// After that the CTA is a flat stream of tiles: the per-warp rings run on across the layer
+// boundary (the tiles of layer l+1 are already in flight while the warps merge layer l; the block
+// table is the same for every layer, only the cache base moves), so a layer end costs two CTA
+// barriers, one partial and one released arrival count, not a drained and refilled pipeline.
+template <int WARPS, int STAGES>
+__device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, const int x, const int h, const int z,
+                                                unsigned char* smem) {
+  using S = DecodeSmem<WARPS, STAGES>;
+  const DecodeParams& b = sp.base;
+  unsigned char* tiles = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kTiles);
+  float* mrg = reinterpret_cast<float*>(smem + S::kTiles + S::kBars);
+  float* mrg_o = mrg;                                // [WARPS][4][64]
+  float* mrg_m = mrg + WARPS * kGroup * kHeadDim;     // [WARPS][4]
+  float* mrg_l = mrg_m + WARPS * kGroup;              // [WARPS][4]
+  __nv_bfloat16* qsm = reinterpret_cast<__nv_bfloat16*>(smem + S::kStepQ);  // [layers][4][64] rotated
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int layers = sp.layers;
+  const BatchEntry e = b.batch[z];
+  const int n_blocks = (e.kv_len + kBlockTok - 1) / kBlockTok;
+  const int n_chunks = max(1, (n_blocks + b.chunk_blocks - 1) / b.chunk_blocks);
+  if (x >= n_chunks) return;  // the grid holds exactly the chunks of every sequence
+  const int blk_lo = x * b.chunk_blocks;
+  const int cnt = max(0, min(n_blocks, blk_lo + b.chunk_blocks) - blk_lo);
+  const int my_n = cnt > warp ? (cnt - warp + WARPS - 1) / WARPS : 0;
+  const int32_t* table = b.tables + (size_t)e.seq * b.max_blocks_per_seq + blk_lo + warp;
+  const int q_heads = b.kv_heads * kGroup;
+
+  const uint32_t tile0 = smem_u32(tiles) + warp * STAGES * kPairBytes;
+  const uint32_t bar0 = smem_u32(bars) + warp * STAGES * 8;
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; s++) mbar_init(bar0 + s * 8, 1);
+    mbar_fence_init();
+    fence_proxy_async_smem();
+  }
+  __syncwarp();
+
+  // Block-table entries of this warp's blocks, 32 per window, one per lane; the window after the
+  // one in use is fetched ahead (after the last window comes the first again: next layer).
+  const int n_win = max(1, (my_n + 31) >> 5);
+  auto load_window = [&](int w) {
+    const int ii = (w << 5) + lane;
+    return ii < my_n ? table[(size_t)ii * WARPS] : 0;
+  };
+  int tbl_cur = 0, tbl_next = load_window(0);
+
+  // ---- appended rows of ALL layers (the warp that owns the sequence's last block) -------------
+  // Same arithmetic and placement as append_kernel; generic-proxy stores ordered before this
+  // warp's own bulk (async-proxy) reads of that block by one proxy fence.
+  if (e.n_new > 0 && x == n_chunks - 1 && cnt > 0 && warp == (cnt - 1) % WARPS) {
+    if (lane < 8) {
+      const int lpos = e.kv_len - 1;
+      const int pos = e.kv_pos_off + lpos;
+      const int blk = b.tables[(size_t)e.seq * b.max_blocks_per_seq + lpos / kBlockTok];
+      const int slot = lpos % kBlockTok;
+      const int c = lane & 3, is_v = lane >> 2;
+      if (blk < 0 || blk >= b.num_blocks) {
+        atomicExch(b.status, kStatusBadBlock);
+      } else {
+        float4 c8[2], s8[2];
+        if (!is_v) {
+          const float4* cs = reinterpret_cast<const float4*>(b.cos_table + (size_t)pos * 32 + c * 8);
+          const float4* sn = reinterpret_cast<const float4*>(b.sin_table + (size_t)pos * 32 + c * 8);
+          c8[0] = cs[0], c8[1] = cs[1], s8[0] = sn[0], s8[1] = sn[1];
+        }
+        for (int l = 0; l < layers; l++) {
+          const __nv_bfloat16* row = (is_v ? b.v_new : b.k_new) + (size_t)l * sp.kv_layer_stride +
+                                     ((size_t)e.kv_row_off * b.kv_heads + h) * kHeadDim;
+          const uint4* src = reinterpret_cast<const uint4*>(row);
+          char* tile = b.storage_w + (size_t)l * sp.layer_bytes + tile_off(blk, b.kv_heads, h, is_v);
+          uint4 lo = src[c], hi = src[c + 4];
+          if (!is_v) {
+            uint4 ylo, yhi;
+            rope_chunks<1>(lo, hi, reinterpret_cast<const float*>(c8), reinterpret_cast<const float*>(s8), ylo, yhi);
+            lo = ylo;
+            hi = yhi;
+          }
+          *reinterpret_cast<uint4*>(tile + tile_chunk_off(slot, c)) = lo;
+          *reinterpret_cast<uint4*>(tile + tile_chunk_off(slot, c + 4)) = hi;
+        }
+      }
+    }
+    asm volatile("fence.proxy.async;" ::: "memory");
+    __syncwarp();
+  }
+
+  // ---- the tile stream: issue pointer (layer is_l, tile is_i, ring position is_t) --------------
+  const char* head_base = b.storage + (size_t)h * kPairBytes;
+  const size_t block_stride = (size_t)b.kv_heads * kPairBytes;
+  int is_l = my_n > 0 ? 0 : layers, is_i = 0;
+  uint32_t is_t = 0;
+  auto issue_next = [&]() {
+    if ((is_i & 31) == 0 && (n_win > 1 || is_t == 0)) {
+      tbl_cur = tbl_next;
+      tbl_next = load_window(((is_i >> 5) + 1) % n_win);
+    }
+    int blk = __shfl_sync(0xffffffffu, tbl_cur, is_i & 31);
+    if (lane == 0) {
+      if (blk < 0 || blk >= b.num_blocks) {
+        atomicExch(b.status, kStatusBadBlock);
+        blk = 0;
+      }
+      const int st = (int)(is_t % STAGES);
+      mbar_expect_tx(bar0 + st * 8, kPairBytes);
+      bulk_g2s(tile0 + st * kPairBytes, head_base + (size_t)is_l * sp.layer_bytes + (size_t)blk * block_stride,
+               kPairBytes, bar0 + st * 8);
+    }
+    is_t++;
+    if (++is_i == my_n) {
+      is_i = 0;
+      is_l++;
+    }
+  };
+  for (int s = 0; s < STAGES && is_l < layers; s++) issue_next();
+
+  // ---- every layer's query rows, rotated once (fp32, the rounding of append_kernel) ------------
+  {
+    const float* cs = b.cos_table + (size_t)e.q_pos0 * 32;
+    const float* sn = b.sin_table + (size_t)e.q_pos0 * 32;
+    const size_t qrow0 = ((size_t)z * q_heads + h * kGroup) * kHeadDim;
+    for (int idx = threadIdx.x; idx < layers * kGroup * 32; idx += WARPS * 32) {
+      const int c = idx & 31, r = (idx >> 5) & 3, l = idx >> 7;
+      const __nv_bfloat16* qp = b.q + (size_t)l * sp.q_layer_stride + qrow0 + r * kHeadDim;
+      float y0, y1;
+      rope_pair<1>(__bfloat162float(qp[c]), __bfloat162float(qp[c + 32]), cs[c], sn[c], y0, y1);
+      const __nv_bfloat16 b0 = __float2bfloat16_rn(y0), b1 = __float2bfloat16_rn(y1);
+      qsm[(l * kGroup + r) * kHeadDim + c] = b0;
+      qsm[(l * kGroup + r) * kHeadDim + c + 32] = b1;
+      if (b.q_rot_out && x == 0) {
+        __nv_bfloat16* qo = b.q_rot_out + (size_t)l * sp.q_layer_stride + qrow0 + r * kHeadDim;
+        qo[c] = b0;
+        qo[c + 32] = b1;
+      }
+    }
+  }
+  __syncthreads();
+
+  const int qrow = lane >> 2, qcol = (lane & 3) * 2;
+  const int mj = lane >> 3, rr = lane & 7;
+  const uint32_t k_row_off = (uint32_t)(((mj >> 1) * 8 + rr) * 128);
+  const uint32_t v_row_off = (uint32_t)(kTileBytes + ((mj & 1) * 8 + rr) * 128);
+  const int pair = z * b.kv_heads + h;
+  const int item = pair * b.max_chunks + x;
+  bool failed = false;
+  uint32_t t = 0;
+
+  for (int l = 0; l < layers; l++) {
+    // Query fragments of this layer: rows 0..3 are the group's heads, the rest zero.
+    uint32_t qa[4][4];
+#pragma unroll
+    for (int ks = 0; ks < 4; ks++) {
+      qa[ks][0] = qa[ks][1] = qa[ks][2] = qa[ks][3] = 0u;
+      if (qrow < kGroup) {
+        const __nv_bfloat16* qp = qsm + (l * kGroup + qrow) * kHeadDim + ks * 16 + qcol;
+        qa[ks][0] = *reinterpret_cast<const uint32_t*>(qp);
+        qa[ks][2] = *reinterpret_cast<const uint32_t*>(qp + 8);
+      }
+    }
+    float o[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; nt++) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+
+    for (int i = 0; i < my_n; i++, t++) {
+      const int st = (int)(t % STAGES);
+      if (!failed) {
+        const bool ok = mbar_wait(bar0 + st * 8, (t / STAGES) & 1u);
+        if (!__all_sync(0xffffffffu, ok)) {
+          failed = true;
+          if (lane == 0) atomicExch(b.status, kStatusTimeout);
+        }
+      }
+      if (failed) continue;  // keeps joining the layer barriers, issues nothing more
+      const uint32_t tile = tile0 + st * kPairBytes;
+
+      float s[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; nt++) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 4; ks++) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(b0, b1, b2, b3, tile + k_row_off + ((((ks * 2 + (mj & 1)) ^ rr)) << 4));
+        mma_bf16(s[0], qa[ks], b0, b1);
+        mma_bf16(s[1], qa[ks], b2, b3);
+      }
+
+      // scaled scores (base 2), tail mask, online softmax on rows lane/4
+      const int key0 = (blk_lo + warp + i * WARPS) * kBlockTok + qcol;
+      float tt[4];
+      tt[0] = s[0][0] * b.scale_log2;
+      tt[1] = s[0][1] * b.scale_log2;
+      tt[2] = s[1][0] * b.scale_log2;
+      tt[3] = s[1][1] * b.scale_log2;
+      if (key0 + 9 >= e.kv_len) {
+        if (key0 >= e.kv_len) tt[0] = -INFINITY;
+        if (key0 + 1 >= e.kv_len) tt[1] = -INFINITY;
+        if (key0 + 8 >= e.kv_len) tt[2] = -INFINITY;
+        if (key0 + 9 >= e.kv_len) tt[3] = -INFINITY;
+      }
+      float mx = fmaxf(fmaxf(tt[0], tt[1]), fmaxf(tt[2], tt[3]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run, mx);
+      const float corr = ex2(m_run - m_new);
+      m_run = m_new;
+      const float p0 = ex2(tt[0] - m_new), p1 = ex2(tt[1] - m_new);
+      const float p2 = ex2(tt[2] - m_new), p3 = ex2(tt[3] - m_new);
+      l_run = l_run * corr + ((p0 + p1) + (p2 + p3));
+      uint32_t pa[4];
+      pa[0] = pack_bf16(p0, p1);
+      pa[1] = 0u;
+      pa[2] = pack_bf16(p2, p3);
+      pa[3] = 0u;
+#pragma unroll
+      for (int nt = 0; nt < 8; nt++) {
+        o[nt][0] *= corr;
+        o[nt][1] *= corr;
+      }
+#pragma unroll
+      for (int np = 0; np < 4; np++) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(b0, b1, b2, b3, tile + v_row_off + ((((np * 2 + (mj >> 1)) ^ rr)) << 4));
+        mma_bf16(o[2 * np], pa, b0, b1);
+        mma_bf16(o[2 * np + 1], pa, b2, b3);
+      }
+
+      __syncwarp();
+      if (is_l < layers) {
+        if (lane == 0) fence_proxy_async_smem();
+        issue_next();
+      }
+    }
+
+    // ---- end of the layer: merge the warps, leave the partial, count one arrival ---------------
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (qrow < kGroup) {
+      float* orow = mrg_o + (warp * kGroup + qrow) * kHeadDim;
+#pragma unroll
+      for (int nt = 0; nt < 8; nt++)
+        *reinterpret_cast<float2*>(orow + nt * 8 + qcol) = make_float2(o[nt][0], o[nt][1]);
+      if ((lane & 3) == 0) {
+        mrg_m[warp * kGroup + qrow] = m_run;
+        mrg_l[warp * kGroup + qrow] = l_run;
+      }
+    }
+    __syncthreads();
+    float* ws_acc = b.ws_acc + ((size_t)l * sp.ws_layer_items + item) * (kGroup * kHeadDim);
+    float* ws_ml = b.ws_ml + ((size_t)l * sp.ws_layer_items + item) * (2 * kGroup);
+    for (int idx = threadIdx.x; idx < kGroup * kHeadDim; idx += WARPS * 32) {
+      const int r = idx >> 6, d = idx & 63;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < WARPS; w++) M = fmaxf(M, mrg_m[w * kGroup + r]);
+      float L = 0.f, O = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; w++) {
+        const float mw = mrg_m[w * kGroup + r];
+        const float wgt = mw == -INFINITY ? 0.f : ex2(mw - M);
+        L += wgt * mrg_l[w * kGroup + r];
+        O += wgt * mrg_o[(w * kGroup + r) * kHeadDim + d];
+      }
+      ws_acc[idx] = O;
+      if (d == 0) {
+        ws_ml[r] = M;
+        ws_ml[kGroup + r] = L;
+      }
+    }
+    // The barrier orders every thread's partial stores before thread 0's release (cumulative at
+    // gpu scope); the pair's combining CTA acquires the count and then reads the partials.  It
+    // also frees the merge buffers for the next layer.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned int* cntp = b.ws_count + (size_t)l * sp.n_seqs * b.kv_heads + pair;
+      asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(cntp) : "memory");
+    }
+  }
+}
+
 template <int WARPS, int STAGES>
 __device__ __forceinline__ void decode_step_body(const DecodeStepParams& sp, const int b, unsigned char* smem) {
   __shared__ int s_ok;
@@ -621,12 +925,7 @@ __device__ __forceinline__ void decode_step_body(const DecodeStepParams& sp, con
     const int local = b - (int)sp.seq_first[z];
     const int chunks_z = ((int)sp.seq_first[z + 1] - (int)sp.seq_first[z]) / sp.base.kv_heads;
     const int x = local % chunks_z, h = local / chunks_z;
-    uint32_t tile_base = 0;
-    for (int l = 0; l < sp.layers; l++) {
-      __syncthreads();  // the merge buffers of the previous layer are free
-      const DecodeParams p = step_layer_params(sp, l);
-      decode_cta<WARPS, STAGES, kStepStream>(p, x, h, z, smem, tile_base);
-    }
+    stream_step_cta<WARPS, STAGES>(sp, x, h, z, smem);
     return;
   }
   // Combining CTAs: sp.combiners per (sequence, head), taking the layers in turn.  One CTA needs
@@ -754,7 +1053,7 @@ cudaError_t launch_decode_step_cfg(const DecodeStepParams& sp, cudaStream_t stre
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(decode_step_kernel<WARPS, STAGES>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::step_bytes(kMaxStepLayers));
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
@@ -762,7 +1061,7 @@ cudaError_t launch_decode_step_cfg(const DecodeStepParams& sp, cudaStream_t stre
   void* kargs[] = {&args};
   // cooperative: the combining CTAs wait for the streaming CTAs of the same grid
   return cudaLaunchCooperativeKernel((const void*)decode_step_kernel<WARPS, STAGES>, dim3(decode_step_ctas(sp)),
-                                     dim3(WARPS * 32), kargs, S::kBytes, stream);
+                                     dim3(WARPS * 32), kargs, S::step_bytes(sp.layers), stream);
 }
 
 cudaError_t launch_decode_step_colocated(const ColocatedStepParams& cp, cudaStream_t stream) {
@@ -772,14 +1071,14 @@ cudaError_t launch_decode_step_colocated(const ColocatedStepParams& cp, cudaStre
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(decode_step_ranks_kernel<8, 4>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::step_bytes(kMaxStepLayers));
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
   ColocatedStepParams args = cp;
   void* kargs[] = {&args};
   return cudaLaunchCooperativeKernel((const void*)decode_step_ranks_kernel<8, 4>, dim3(cp.world * cp.ctas_per_rank),
-                                     dim3(8 * 32), kargs, S::kBytes, stream);
+                                     dim3(8 * 32), kargs, S::step_bytes(cp.rank[0].layers), stream);
 }
 
 cudaError_t launch_decode_step(const DecodeStepParams& sp, int warps, int stages, cudaStream_t stream) {

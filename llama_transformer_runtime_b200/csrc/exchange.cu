@@ -179,9 +179,9 @@ int pa_exchange_create(pa_exchange** out, int device, int rank, int world, int n
   // [data | flags | words]: the first two serve the push + separate merge
   // kernel, the third the merge inside the decode kernel
   x->ll_offset = x->data_bytes + (((size_t)world * x->groups * sizeof(unsigned int) + 255) & ~(size_t)255);
-  // four slots of words: two combining CTAs per (sequence, head) work on alternate layers, so a
-  // peer may already be two steps ahead of the slot a rank is still polling
-  x->bytes = x->ll_offset + (size_t)4 * world * x->rows * pa::kXchgRowFloats * sizeof(unsigned long long);
+  // kXchgWordSlots slots of words: up to four combining CTAs per (sequence, head) work on
+  // alternate layers, so a peer may already be that many steps ahead of a slot a rank still polls
+  x->bytes = x->ll_offset + (size_t)pa::kXchgWordSlots * world * x->rows * pa::kXchgRowFloats * sizeof(unsigned long long);
   int prev = -1;
   cudaGetDevice(&prev);
   cudaError_t e = cudaSetDevice(device);

@@ -60,7 +60,7 @@ struct DecodeParams {
   __nv_bfloat16* xchg_out = nullptr;
   long long xchg_out_stride = 0;
   // In-kernel merge: partials travel as 8-byte words {value, step number}
-  // (xchg_ll[g] = rank g's word region, [4 slots][world][rows][65] words, slot = step mod 4), so a
+  // (xchg_ll[g] = rank g's word region, [kXchgWordSlots][world][rows][65] words, slot = step modulo kXchgWordSlots), so a
   // word is valid as soon as it carries this step's number: no fence, no flag.
   unsigned long long* xchg_ll[8] = {};
   // KV-head sharding: this rank's heads are columns [hs_col0, hs_col0 + q_heads*64)
@@ -85,6 +85,10 @@ struct DecodeParams {
   __nv_bfloat16* q_rot_out = nullptr;    // rotated Q [n_seqs][q_heads][64] (nullable, must not alias q)
 };
 constexpr int kXchgRowFloats = kHeadDim + 1;
+// Slots of the {value, step} word region (slot = step number modulo this).  With C combining CTAs
+// per (sequence, head) on alternate layers a peer can be C layers ahead of a slot a rank still
+// polls: the slot count must be a multiple of C and at least 2 C.  C is 1, 2 or 4.
+constexpr unsigned int kXchgWordSlots = 8;
 
 // A whole multi-layer decode step in one cooperative launch (decode_step_kernel):
 // `base` holds layer 0's parameters; layer l adds l strides to every per-layer

@@ -170,6 +170,13 @@ class KVPool:
         """decode_step as one cooperative launch per step (default) or one kernel per layer."""
         check(lib().pa_pool_set_step_kernel(self._h, 1 if enable else 0))
 
+    def set_layer_overlap(self, allow: bool) -> None:
+        """False: layers of a decode step run strictly one after the other (dependent layers)."""
+        check(lib().pa_pool_set_layer_overlap(self._h, 1 if allow else 0))
+
+    def set_step_combiners(self, n: int) -> None:
+        check(lib().pa_pool_set_step_combiners(self._h, n))
+
     def step_launches(self) -> int:
         """Decode steps of this pool that ran as one launch."""
         n = C.c_longlong(0)

@@ -103,14 +103,20 @@ def _exchange_schedule_is_safe(world, layers, combiners, slots, rng, steps=20000
     return all(l >= layers for _, l in state.values())
 
 
-def test_exchange_slot_count_is_enough_for_two_combining_ctas():
-    """One combining CTA per (sequence, head) is safe with two word slots; two CTAs on alternate
-    layers need four (a peer can be two layers ahead of a slot still being polled): the model finds
-    an overwrite with two slots and none with four, over many random schedules."""
+def test_exchange_slot_count_is_enough_for_the_combining_ctas():
+    """C combining CTAs per (sequence, head) on alternate layers need a slot count that is a
+    multiple of C and at least 2 C (a peer can be C layers ahead of a slot still being polled): the
+    library uses 8 slots with C in {1, 2, 4}.  The model finds no overwrite for those over many
+    random schedules, and does find one with too few slots."""
     rng = np.random.default_rng(2024)
     for world in (1, 2, 3, 8):
-        for _ in range(60):
+        for _ in range(40):
             assert _exchange_schedule_is_safe(world, 16, 1, 2, rng)
             assert _exchange_schedule_is_safe(world, 16, 2, 4, rng)
+            for combiners in (1, 2, 4):
+                assert _exchange_schedule_is_safe(world, 16, combiners, 8, rng)
+                assert _exchange_schedule_is_safe(world, 3, combiners, 8, rng)   # fewer layers than slots
     unsafe = sum(not _exchange_schedule_is_safe(2, 16, 2, 2, rng) for _ in range(200))
     assert unsafe > 0, "two slots with two combining CTAs should be caught by some schedule"
+    unsafe = sum(not _exchange_schedule_is_safe(2, 16, 4, 4, rng) for _ in range(200))
+    assert unsafe > 0, "four slots with four combining CTAs should be caught by some schedule"
