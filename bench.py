@@ -154,6 +154,8 @@ def run_ours(args):
     if args.decode_shape:
         w, s = args.decode_shape.lower().split("x")
         pool.set_decode_shape(int(w), int(s))
+    if args.combiners:
+        pool.set_step_combiners(args.combiners)
 
     # ---- fill the cache: N(0,1)*0.5, generated on the device, appended with the identity rotation
     gen = torch.Generator(device=dev)
@@ -1271,6 +1273,7 @@ def main():
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="N>1: partials pushed by the decode epilogue over NVLink (fused) or NCCL all-gather")
     ap.add_argument("--chunk-blocks", type=int, default=0, help="decode: blocks per split-KV chunk (0 = planner)")
+    ap.add_argument("--combiners", type=int, default=0, help="decode: combining CTAs per (sequence, head) in the one-launch step (0 = planner)")
     ap.add_argument("--decode-shape", default="", help="decode: WARPSxSTAGES, e.g. 8x4 (empty = planner)")
     ap.add_argument("--qkv-packed", action="store_true",
                     help="qkv_decode: the kernel that reads the packed weight tiles (shared with the prefill GEMM) "

@@ -40,9 +40,15 @@ struct DecodeSmem {
   static constexpr int kBars = WARPS * STAGES * 8;
   static constexpr int kMergeFloats = WARPS * (kGroup * kHeadDim + 2 * kGroup);
   static constexpr int kBytes = 128 + kTiles + kBars + kMergeFloats * 4 + 16;
-  // the step kernel appends every layer's rotated query rows: [layers][4][64] bf16
-  static constexpr int kStepQ = (kTiles + kBars + kMergeFloats * 4 + 16 + 127) & ~127;
+  // the step kernel appends: "stage free" barriers + the publisher's word, the CTA's slice of
+  // the block table (entries beyond kStepTblCap are read from global memory), and every layer's
+  // rotated query rows [layers][4][64] bf16
+  static constexpr int kStepTblCap = 1024;
+  static constexpr int kStepEmpty = (kTiles + kBars + kMergeFloats * 4 + 16 + 127) & ~127;
+  static constexpr int kStepTbl = kStepEmpty + ((kBars + 8 + 127) & ~127);
+  static constexpr int kStepQ = kStepTbl + kStepTblCap * 4;
   static constexpr int step_bytes(int layers) { return 128 + kStepQ + layers * kGroup * kHeadDim * 2; }
+  static constexpr int kStepThreads = (WARPS + 2) * 32;  // consumers + producer warp + publisher warp
 };
 
 // One 8-byte word {value, step number}: value in the low half, step number in the high half,
@@ -630,13 +636,18 @@ decode_kernel(DecodeParams p) {
 // combining CTAs wait on the streaming ones of the same grid, so the launch is
 // cooperative (all CTAs resident).
 // A streaming CTA of the one-launch step: chunk x of (sequence z, KV head h), layer after layer.
-// Everything that does not depend on the tiles is done ONCE, before the first layer: the batch
-// entry, the rotation of every layer's 4 query rows (kept in shared memory as bf16, ready to be
-// picked up as A fragments), the rotated-query output rows and the appended K/V rows of all layers.
-// After that the CTA is a flat stream of tiles: the per-warp rings run on across the layer
-// boundary (the tiles of layer l+1 are already in flight while the warps merge layer l; the block
-// table is the same for every layer, only the cache base moves), so a layer end costs two CTA
-// barriers, one partial and one released arrival count, not a drained and refilled pipeline.
+// WARPS consumer warps, one producer warp, one publisher warp.
+//  * Everything that does not depend on the tiles is done ONCE, before the first layer: the batch
+//    entry, the CTA's slice of the block table (shared memory; it is the same for every layer,
+//    only the cache base moves), the rotation of every layer's 4 query rows (kept in shared memory
+//    as bf16, ready to be picked up as A fragments), the rotated-query output rows and the
+//    appended K/V rows of all layers.
+//  * The producer warp's lane w feeds consumer warp w's ring: it waits for a freed stage (empty
+//    barrier) and issues the next bulk copy, across layer borders, so the tiles of layer l+1 are
+//    in flight while the consumers merge layer l.  Arming a barrier and issuing a bulk copy costs
+//    a thread about 300 cycles; in the consumers' loop that was a quarter of the time per tile.
+//  * A layer end costs the consumers two barriers among themselves and one partial; the arrival
+//    count is released by the publisher warp, off their path (a gpu-scope release takes ~0.6 us).
 template <int WARPS, int STAGES>
 __device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, const int x, const int h, const int z,
                                                 unsigned char* smem) {
@@ -648,6 +659,8 @@ __device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, cons
   float* mrg_o = mrg;                                // [WARPS][4][64]
   float* mrg_m = mrg + WARPS * kGroup * kHeadDim;     // [WARPS][4]
   float* mrg_l = mrg_m + WARPS * kGroup;              // [WARPS][4]
+  uint64_t* empty_bars = reinterpret_cast<uint64_t*>(smem + S::kStepEmpty);
+  int32_t* tbl_s = reinterpret_cast<int32_t*>(smem + S::kStepTbl);
   __nv_bfloat16* qsm = reinterpret_cast<__nv_bfloat16*>(smem + S::kStepQ);  // [layers][4][64] rotated
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -655,37 +668,33 @@ __device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, cons
   const BatchEntry e = b.batch[z];
   const int n_blocks = (e.kv_len + kBlockTok - 1) / kBlockTok;
   const int n_chunks = max(1, (n_blocks + b.chunk_blocks - 1) / b.chunk_blocks);
-  if (x >= n_chunks) return;  // the grid holds exactly the chunks of every sequence
+  if (x >= n_chunks) return;  // the grid holds exactly the chunks of every sequence (CTA-uniform)
   const int blk_lo = x * b.chunk_blocks;
   const int cnt = max(0, min(n_blocks, blk_lo + b.chunk_blocks) - blk_lo);
-  const int my_n = cnt > warp ? (cnt - warp + WARPS - 1) / WARPS : 0;
-  const int32_t* table = b.tables + (size_t)e.seq * b.max_blocks_per_seq + blk_lo + warp;
+  const int32_t* table = b.tables + (size_t)e.seq * b.max_blocks_per_seq + blk_lo;
   const int q_heads = b.kv_heads * kGroup;
+  // layers whose partial this CTA has stored: written by consumer thread 0, polled by the publisher
+  const uint32_t pub_word = smem_u32(empty_bars) + WARPS * STAGES * 8;
 
-  const uint32_t tile0 = smem_u32(tiles) + warp * STAGES * kPairBytes;
-  const uint32_t bar0 = smem_u32(bars) + warp * STAGES * 8;
-  if (lane == 0) {
-#pragma unroll
-    for (int s = 0; s < STAGES; s++) mbar_init(bar0 + s * 8, 1);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < WARPS * STAGES; s++) {
+      mbar_init(smem_u32(bars) + s * 8, 1);
+      mbar_init(smem_u32(empty_bars) + s * 8, 1);
+    }
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(pub_word), "r"(0u) : "memory");
     mbar_fence_init();
     fence_proxy_async_smem();
   }
-  __syncwarp();
+  __syncthreads();
 
-  // Block-table entries of this warp's blocks, 32 per window, one per lane; the window after the
-  // one in use is fetched ahead (after the last window comes the first again: next layer).
-  const int n_win = max(1, (my_n + 31) >> 5);
-  auto load_window = [&](int w) {
-    const int ii = (w << 5) + lane;
-    return ii < my_n ? table[(size_t)ii * WARPS] : 0;
-  };
-  int tbl_cur = 0, tbl_next = load_window(0);
-
-  // ---- appended rows of ALL layers (the warp that owns the sequence's last block) -------------
-  // Same arithmetic and placement as append_kernel; generic-proxy stores ordered before this
-  // warp's own bulk (async-proxy) reads of that block by one proxy fence.
-  if (e.n_new > 0 && x == n_chunks - 1 && cnt > 0 && warp == (cnt - 1) % WARPS) {
-    if (lane < 8) {
+  if (warp == WARPS) {
+    // ================================ producer warp ==============================================
+    const int held = min(cnt, S::kStepTblCap);
+    for (int j = lane; j < held; j += 32) tbl_s[j] = table[j];
+    // Appended rows of ALL layers (the CTA that owns the sequence's last block): same arithmetic
+    // and placement as append_kernel; the generic-proxy stores are ordered before this warp's own
+    // bulk (async-proxy) reads of that block by the proxy fence below.
+    if (e.n_new > 0 && x == n_chunks - 1 && cnt > 0 && lane < 8) {
       const int lpos = e.kv_len - 1;
       const int pos = e.kv_pos_off + lpos;
       const int blk = b.tables[(size_t)e.seq * b.max_blocks_per_seq + lpos / kBlockTok];
@@ -719,36 +728,72 @@ __device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, cons
     }
     asm volatile("fence.proxy.async;" ::: "memory");
     __syncwarp();
+    if (lane < WARPS) {
+      const int w = lane;
+      const int my_n = cnt > w ? (cnt - w + WARPS - 1) / WARPS : 0;
+      const uint32_t tile0 = smem_u32(tiles) + w * STAGES * kPairBytes;
+      const uint32_t full0 = smem_u32(bars) + w * STAGES * 8;
+      const uint32_t empty0 = smem_u32(empty_bars) + w * STAGES * 8;
+      const char* head_base = b.storage + (size_t)h * kPairBytes;
+      const size_t block_stride = (size_t)b.kv_heads * kPairBytes;
+      const uint32_t total = (uint32_t)layers * (uint32_t)my_n;
+      int i = 0;
+      const char* layer_base = head_base;
+      for (uint32_t t = 0; t < total; t++) {
+        const int st = (int)(t % STAGES);
+        if (t >= (uint32_t)STAGES && !mbar_wait(empty0 + st * 8, ((t / STAGES) - 1u) & 1u)) {
+          atomicExch(b.status, kStatusTimeout);
+          break;
+        }
+        const int j = w + i * WARPS;
+        int blk = j < S::kStepTblCap ? tbl_s[j] : table[j];
+        if (blk < 0 || blk >= b.num_blocks) {
+          atomicExch(b.status, kStatusBadBlock);
+          blk = 0;
+        }
+        mbar_expect_tx(full0 + st * 8, kPairBytes);
+        bulk_g2s(tile0 + st * kPairBytes, layer_base + (size_t)blk * block_stride, kPairBytes, full0 + st * 8);
+        if (++i == my_n) {
+          i = 0;
+          layer_base += sp.layer_bytes;
+        }
+      }
+    }
+    return;
+  }
+  if (warp == WARPS + 1) {
+    // ================================ publisher warp =============================================
+    // Consumer thread 0 stores the number of finished layers (release, CTA scope) after the barrier
+    // that follows the CTA's partial stores; acquiring that word and then releasing at gpu scope
+    // makes the stores visible (the release is cumulative) to the pair's combining CTA, which
+    // acquires the count.  A word, not a barrier phase: the consumers may finish several short
+    // layers while one release is still under way.
+    if (lane == 0) {
+      const int pair = z * b.kv_heads + h;
+      unsigned int done = 0;
+      for (int l = 0; l < layers; l++) {
+        SpinDeadline dl;
+        while (done <= (unsigned)l) {
+          asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(done) : "r"(pub_word) : "memory");
+          if (done <= (unsigned)l && dl.expired()) break;
+        }
+        if (done <= (unsigned)l) {
+          atomicExch(b.status, kStatusTimeout);
+          break;
+        }
+        unsigned int* cntp = b.ws_count + (size_t)l * sp.n_seqs * b.kv_heads + pair;
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(cntp) : "memory");
+      }
+    }
+    return;
   }
 
-  // ---- the tile stream: issue pointer (layer is_l, tile is_i, ring position is_t) --------------
-  const char* head_base = b.storage + (size_t)h * kPairBytes;
-  const size_t block_stride = (size_t)b.kv_heads * kPairBytes;
-  int is_l = my_n > 0 ? 0 : layers, is_i = 0;
-  uint32_t is_t = 0;
-  auto issue_next = [&]() {
-    if ((is_i & 31) == 0 && (n_win > 1 || is_t == 0)) {
-      tbl_cur = tbl_next;
-      tbl_next = load_window(((is_i >> 5) + 1) % n_win);
-    }
-    int blk = __shfl_sync(0xffffffffu, tbl_cur, is_i & 31);
-    if (lane == 0) {
-      if (blk < 0 || blk >= b.num_blocks) {
-        atomicExch(b.status, kStatusBadBlock);
-        blk = 0;
-      }
-      const int st = (int)(is_t % STAGES);
-      mbar_expect_tx(bar0 + st * 8, kPairBytes);
-      bulk_g2s(tile0 + st * kPairBytes, head_base + (size_t)is_l * sp.layer_bytes + (size_t)blk * block_stride,
-               kPairBytes, bar0 + st * 8);
-    }
-    is_t++;
-    if (++is_i == my_n) {
-      is_i = 0;
-      is_l++;
-    }
-  };
-  for (int s = 0; s < STAGES && is_l < layers; s++) issue_next();
+  // ================================== consumer warps =============================================
+  const int my_n = cnt > warp ? (cnt - warp + WARPS - 1) / WARPS : 0;
+  const uint32_t tile0 = smem_u32(tiles) + warp * STAGES * kPairBytes;
+  const uint32_t bar0 = smem_u32(bars) + warp * STAGES * 8;
+  const uint32_t empty0 = smem_u32(empty_bars) + warp * STAGES * 8;
+  auto consumer_barrier = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(WARPS * 32) : "memory"); };
 
   // ---- every layer's query rows, rotated once (fp32, the rounding of append_kernel) ------------
   {
@@ -770,7 +815,7 @@ __device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, cons
       }
     }
   }
-  __syncthreads();
+  consumer_barrier();
 
   const int qrow = lane >> 2, qcol = (lane & 3) * 2;
   const int mj = lane >> 3, rr = lane & 7;
@@ -807,7 +852,7 @@ __device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, cons
           if (lane == 0) atomicExch(b.status, kStatusTimeout);
         }
       }
-      if (failed) continue;  // keeps joining the layer barriers, issues nothing more
+      if (failed) continue;  // keeps joining the layer barriers; its producer lane runs into its own limit
       const uint32_t tile = tile0 + st * kPairBytes;
 
       float s[2][4];
@@ -861,11 +906,9 @@ __device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, cons
         mma_bf16(o[2 * np + 1], pa, b2, b3);
       }
 
+      // all lanes have read the stage (their ldmatrix results are in registers): hand it back
       __syncwarp();
-      if (is_l < layers) {
-        if (lane == 0) fence_proxy_async_smem();
-        issue_next();
-      }
+      if (lane == 0) mbar_arrive(empty0 + st * 8);
     }
 
     // ---- end of the layer: merge the warps, leave the partial, count one arrival ---------------
@@ -881,7 +924,7 @@ __device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, cons
         mrg_l[warp * kGroup + qrow] = l_run;
       }
     }
-    __syncthreads();
+    consumer_barrier();
     float* ws_acc = b.ws_acc + ((size_t)l * sp.ws_layer_items + item) * (kGroup * kHeadDim);
     float* ws_ml = b.ws_ml + ((size_t)l * sp.ws_layer_items + item) * (2 * kGroup);
     for (int idx = threadIdx.x; idx < kGroup * kHeadDim; idx += WARPS * 32) {
@@ -903,14 +946,11 @@ __device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, cons
         ws_ml[kGroup + r] = L;
       }
     }
-    // The barrier orders every thread's partial stores before thread 0's release (cumulative at
-    // gpu scope); the pair's combining CTA acquires the count and then reads the partials.  It
-    // also frees the merge buffers for the next layer.
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      unsigned int* cntp = b.ws_count + (size_t)l * sp.n_seqs * b.kv_heads + pair;
-      asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(cntp) : "memory");
-    }
+    // orders every consumer's partial stores before thread 0's store of the layer count (which the
+    // publisher warp turns into the released arrival) and frees the merge buffers for the next layer
+    consumer_barrier();
+    if (threadIdx.x == 0)
+      asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(pub_word), "r"((unsigned)(l + 1)) : "memory");
   }
 }
 
@@ -928,6 +968,7 @@ __device__ __forceinline__ void decode_step_body(const DecodeStepParams& sp, con
     stream_step_cta<WARPS, STAGES>(sp, x, h, z, smem);
     return;
   }
+  if ((int)threadIdx.x >= WARPS * 32) return;  // the producer and publisher warps have no part in combining
   // Combining CTAs: sp.combiners per (sequence, head), taking the layers in turn.  One CTA needs
   // about 5 us per layer (2.2 us of combine, the rest waiting on its own loads and polls), more
   // than a streaming CTA needs at short contexts (3.5 us), so with one the combiners set the pace.
@@ -966,7 +1007,7 @@ __device__ __forceinline__ void decode_step_body(const DecodeStepParams& sp, con
 }
 
 template <int WARPS, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(DecodeSmem<WARPS, STAGES>::kStepThreads, 1)
 decode_step_kernel(const __grid_constant__ DecodeStepParams sp) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem =
@@ -979,7 +1020,7 @@ decode_step_kernel(const __grid_constant__ DecodeStepParams sp) {
 // each other's exchange words, so they must be co-resident, which separate launches on one GPU
 // would not guarantee.
 template <int WARPS, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(DecodeSmem<WARPS, STAGES>::kStepThreads, 1)
 decode_step_ranks_kernel(const __grid_constant__ ColocatedStepParams cp) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem =
@@ -1061,7 +1102,7 @@ cudaError_t launch_decode_step_cfg(const DecodeStepParams& sp, cudaStream_t stre
   void* kargs[] = {&args};
   // cooperative: the combining CTAs wait for the streaming CTAs of the same grid
   return cudaLaunchCooperativeKernel((const void*)decode_step_kernel<WARPS, STAGES>, dim3(decode_step_ctas(sp)),
-                                     dim3(WARPS * 32), kargs, S::step_bytes(sp.layers), stream);
+                                     dim3(S::kStepThreads), kargs, S::step_bytes(sp.layers), stream);
 }
 
 cudaError_t launch_decode_step_colocated(const ColocatedStepParams& cp, cudaStream_t stream) {
@@ -1078,7 +1119,7 @@ cudaError_t launch_decode_step_colocated(const ColocatedStepParams& cp, cudaStre
   ColocatedStepParams args = cp;
   void* kargs[] = {&args};
   return cudaLaunchCooperativeKernel((const void*)decode_step_ranks_kernel<8, 4>, dim3(cp.world * cp.ctas_per_rank),
-                                     dim3(8 * 32), kargs, S::step_bytes(cp.rank[0].layers), stream);
+                                     dim3(S::kStepThreads), kargs, S::step_bytes(cp.rank[0].layers), stream);
 }
 
 cudaError_t launch_decode_step(const DecodeStepParams& sp, int warps, int stages, cudaStream_t stream) {
