@@ -1,27 +1,37 @@
-"""Benchmark of the paged KV-cache decode path.
+"""Benchmark of the paged KV-cache attention path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload decode128k|decode4k]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-Default workload (decode128k): long-context decode, batch 1, context 131072 x 16
-layers (about 4.3 GB of bf16 paged KV, 16-token blocks, seeded random fragmented
-block table), KV values N(0,1)*0.5.  One step = one new token: per layer a fused
-RoPE + paged append, then paged GQA decode attention over the whole cache.
-With N GPUs the sequence is split by token range over the ranks (strong
-scaling); every layer ends with an exchange of the ranks' (O, LSE) partials and
-a log-sum-exp merge.
+Default workload (decode128k): long-context decode, batch 1, context 131072 x 16 layers (about
+4.3 GB of bf16 paged KV, 16-token blocks, seeded random fragmented block table), KV values
+N(0,1)*0.5.  One step = one new token: per layer a fused RoPE + paged append, then paged GQA decode
+attention over the whole cache.  With N GPUs the sequence is split by token range over the ranks
+(strong scaling); every layer ends with an exchange of the ranks' (O, LSE) partials and a
+log-sum-exp merge, both inside the decode kernel.
 
-metric  paged_decode_attn_hbm_gbs = algorithmic cache bytes streamed per second,
-        sum over ranks: steps x layers x (2048 L + 8192 + 4 ceil(L/16)) / time.
-        The line also carries us_per_token (time per step).
-value   inputs resident in HBM.      e2e   host buffers: per step the new
-        token's q/k/v for all layers go host->device from pinned memory and the
-        attention outputs come back, inside the timed region.
-The cache is 4.3 GB per step (268 MB per layer) — larger than L2, no flush needed.
+metric  paged_decode_attn_hbm_gbs = algorithmic cache bytes streamed per second, sum over ranks:
+        steps x layers x (2048 L + 8192 + 4 ceil(L/16)) / time.  The line also carries
+        us_per_token (time per step).
+value   inputs resident in HBM; the K timed steps are repeated `--repeats` times (default 15) and
+        the median block is reported, so the region under load lasts a few tenths of a second.
+e2e     host buffers: per step the new token's q/k/v for all layers go host->device from pinned
+        memory and the attention outputs come back, inside the timed region.
+dependent_layers
+        the same step with the layers strictly one after the other (layer l+1 starts when layer
+        l's rows are final): what a forward pass whose layers depend on each other can use.  The
+        headline value lets the layers of a step overlap, which needs every layer's q/k/v up front.
+The cache is 4.3 GB per step (268 MB per layer): larger than L2, no flush needed.
+
+The default run (one GPU) also measures, after the main region, the other parts of the metric as
+sub-blocks of the same JSON line: decode4k (context 4096), prefill (2048 tokens, TFLOP/s), append
+(the fused RoPE + append kernel alone), out_project and qkv (the projections either side of the
+path), each with its roofline and the reference's own kernels timed in the same run.  With more
+than one GPU it adds batch64 (64 ragged sequences, KV heads sharded over the ranks).
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -39,10 +49,13 @@ if ROOT not in sys.path:
 LAYERS = 16
 Q_HEADS, KV_HEADS, D = 32, 8, 64
 BLOCK = 16
+HIDDEN = 2048
 WORKLOADS = {
     "decode128k": dict(ctx=131072, name="decode_ctx131072_x16layers_batch1"),
     "decode4k": dict(ctx=4096, name="decode_ctx4096_x16layers_batch1"),
 }
+PREFILL_TOKENS = 2048
+ROW_REL = 2.0 ** -7  # scale-aware bar: max error of a 64-wide head row over the row's largest value
 
 
 def decode_bytes(L: int) -> int:
@@ -51,20 +64,42 @@ def decode_bytes(L: int) -> int:
     return 2 * KV_HEADS * L * D * 2 + 2 * Q_HEADS * D * 2 + 4 * ((L + BLOCK - 1) // BLOCK)
 
 
-def measured_peak():
+def prefill_flops(S: int) -> float:
+    """Causal-useful flops of one layer: 4 * Hq * D * S (S + 1) / 2."""
+    return 4.0 * Q_HEADS * D * S * (S + 1) / 2.0
+
+
+def _peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         try:
-            return float(json.load(open(path))["hbm_gbs"]), "measured"
+            return json.load(open(path)), "measured"
         except Exception:
             pass
-    return 6650.0, "fallback"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
 
 
-# ncu capture (profiles/): dram read+write bytes per layer of the workload, or
-# None when not captured.
-# per layer: the 2-layer decode_step_kernel capture read 537.09 MB and wrote 6.00 MB
+def measured_peak():
+    j, kind = _peaks()
+    return float(j["hbm_gbs"]), kind
+
+
+def measured_tflops():
+    j, kind = _peaks()
+    return float(j["bf16_tflops"]), float(j.get("bf16_tflops_sustained", j["bf16_tflops"])), kind
+
+
+# ncu captures (profiles/): dram read+write bytes per layer of a workload's dominant kernel.
+# decode128k: the 2-layer decode_step_kernel capture read 537.09 MB and wrote 6.00 MB.
 NCU_TRAFFIC_BYTES = {"decode128k": 271544320, "decode4k": None}
+NCU_APPEND_TRAFFIC = None  # dram bytes of one 2048-token append_kernel launch, from the ncu capture
+
+
+def row_rel_err(got: np.ndarray, want: np.ndarray, row: int = 64) -> float:
+    """max over 64-wide head rows of max|got - want| / max|want|."""
+    err = np.abs(np.asarray(got, np.float64) - np.asarray(want, np.float64)).reshape(-1, row).max(axis=1)
+    m = np.abs(np.asarray(want, np.float64)).reshape(-1, row).max(axis=1)
+    return float(np.max(err / np.maximum(m, 1e-30)))
 
 
 class ClockSampler:
@@ -92,10 +127,9 @@ class ClockSampler:
     def mark(self):
         return len(self.rows)
 
-    def stop(self, lo: int = 0, hi: int | None = None):
+    def summary(self, lo: int = 0, hi: int | None = None):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
         rows = [r for r in self.rows[lo:hi] if len(r) >= 6] or [r for r in self.rows if len(r) >= 6]
         if not rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
@@ -105,6 +139,10 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm) if sm else None,
                 "sm_max_mhz": float(rows[0][1]) if rows[0][1].replace(".", "").isdigit() else None,
                 "reasons": reasons, "samples": len(rows)}
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
 
 
 def dist_env():
@@ -118,26 +156,97 @@ def token_ranges(L: int, n: int):
     return [(cuts[r], cuts[r + 1]) for r in range(n)]
 
 
-# =============================================================================
-# our arm
-# =============================================================================
-def run_ours(args):
-    import torch
-    import torch.distributed as dist
+class Env:
+    """Rank, device, process group and clock sampler of this process."""
 
+    def __init__(self, want_group: bool):
+        import torch
+        self.torch = torch
+        self.rank, self.local_rank, self.world = dist_env()
+        torch.cuda.set_device(self.local_rank)
+        self.dev = f"cuda:{self.local_rank}"
+        self.dist = None
+        if self.world > 1 and want_group:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=torch.device(self.dev))
+            self.dist = dist
+        self.sampler = ClockSampler(self.local_rank)
+        if self.rank == 0:
+            self.sampler.start()
+
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.dist is not None:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def timed(self, fn, n: int) -> float:
+        """n calls of fn between a barrier + synchronize on both sides; CUDA events on the launching
+        stream; max over ranks.  Milliseconds."""
+        torch = self.torch
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        self.barrier()
+        ms = e0.elapsed_time(e1)
+        if self.dist is not None:
+            t = torch.tensor([ms], device=self.dev)
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def close(self):
+        if self.dist is not None:
+            self.dist.destroy_process_group()
+            self.dist = None
+
+
+def local_timed(torch, fn, n: int) -> float:
+    """n calls of fn on this GPU alone: synchronize on both sides, CUDA events.  Milliseconds."""
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1)
+
+
+def _u16(t):
+    import torch
+    return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def decode_config(wl, ctx, world, exchange):
+    return {"workload": wl["name"], "context": ctx, "layers": LAYERS, "batch": 1,
+            "q_heads": Q_HEADS, "kv_heads": KV_HEADS, "head_dim": D, "block_tokens": BLOCK,
+            "block_table": "seeded random permutation over a pool 25% larger than the sequence",
+            "parallelism": "1 GPU" if world == 1 else (
+                f"sequence range split over {world} GPUs; one launch per step, per layer the combining CTAs "
+                f"push (O, LSE) to every rank over NVLink (peer stores of value+step words) and merge locally"
+                if exchange == "fused" else
+                f"sequence range split over {world} GPUs, NCCL all-gather of (O, LSE) per layer + merge"),
+            "l2": f"inputs larger than L2 ({decode_bytes(ctx) * LAYERS / 1e9:.2f} GB streamed per step)"}
+
+
+# =============================================================================
+# decode, one sequence, range-sharded over the ranks (decode128k, decode4k)
+# =============================================================================
+def run_decode(env: Env, args, workload: str, sub: bool = False):
+    torch, dist = env.torch, env.dist
     from llama_transformer_runtime_b200 import paged
 
-    rank, local_rank, world = dist_env()
-    torch.cuda.set_device(local_rank)
-    dev = f"cuda:{local_rank}"
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device(dev))
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    wl = WORKLOADS[args.workload]
+    rank, local_rank, world, dev = env.rank, env.local_rank, env.world, env.dev
+    wl = WORKLOADS[workload]
     ctx = wl["ctx"]
-    total_steps = args.warmup + 2 * args.steps + 8
+    steps = args.steps
+    repeats = 5 if sub else max(1, args.repeats)
+    e2e_repeats = 2 if sub else min(5, repeats)
+    total_steps = args.warmup + steps * (repeats + e2e_repeats + 6) + 16
     lo, hi = token_ranges(ctx, world)[rank]
     local_len = hi - lo
     owner = world - 1  # the last range takes the appended tokens
@@ -161,7 +270,6 @@ def run_ours(args):
     gen = torch.Generator(device=dev)
     gen.manual_seed(4321 + rank)
     chunk = 8192
-    # tables are indexed by absolute position, so they cover the whole local range
     ones = torch.ones(local_len + 1, 32, dtype=torch.float32, device=dev)
     zeros = torch.zeros(local_len + 1, 32, dtype=torch.float32, device=dev)
     for c0 in range(0, local_len, chunk):
@@ -201,9 +309,7 @@ def run_ours(args):
         xchg.connect(handles)
         dist.barrier()
 
-    state = {"global_len": ctx, "launches": 0}
-    # A fused step is ONE cooperative launch of decode_step_kernel when the library takes that path
-    # (the pool counts those steps); otherwise it is one decode_kernel launch per layer.
+    state = {"global_len": ctx, "launches": 0, "fused_steps": 0}
 
     def step(qs, ks, vs, outs):
         """One token: every layer appends and attends over the whole context."""
@@ -215,15 +321,14 @@ def run_ours(args):
             pool.batch_set([seq])
             pool.decode_step(0, LAYERS, qs, ks, vs, Q_HEADS * D, KV_HEADS * D, cos, sin, q_rot, outs,
                              Q_HEADS * D, Q_HEADS * D)
-            state["fused_steps"] = state.get("fused_steps", 0) + 1
+            state["fused_steps"] += 1
             return
         pool.batch_set_sharded([seq], [1 if rank == owner else 0], [1], [g - 1], [lo])
         if xchg is not None:
-            # fused exchange: partials pushed to every rank by the decode kernel's epilogue
             paged.decode_step_sharded(pool, xchg, 0, LAYERS, qs, ks if rank == owner else None,
                                       vs if rank == owner else None, Q_HEADS * D, KV_HEADS * D, cos, sin,
                                       q_rot, outs, Q_HEADS * D, Q_HEADS * D)
-            state["fused_steps"] = state.get("fused_steps", 0) + 1
+            state["fused_steps"] += 1
             return
         for layer in range(LAYERS):
             pool.append(layer, qs[layer], ks[layer], vs[layer], cos, sin, q_rot[layer])
@@ -233,27 +338,6 @@ def run_ours(args):
             l_parts.copy_(gathered[layer, :, Q_HEADS * D:])
             paged.merge_partials(o_parts, l_parts, world, Q_HEADS, outs[layer])
             state["launches"] += 3
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, n):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(n):
-            fn()
-        e1.record()
-        barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
 
     def resident_step():
         step(q_dev, k_dev, v_dev, out_dev)
@@ -266,177 +350,204 @@ def run_ours(args):
         out_host.copy_(out_dev, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller reads the result every step
 
-    m0 = sampler.mark()  # clock samples from here on are taken under load
+    def block(fn):
+        """One timed block of `steps` steps -> (ms, algorithmic bytes of those steps)."""
+        l0 = state["global_len"]
+        ms = env.timed(fn, steps)
+        return ms, sum(LAYERS * decode_bytes(L) for L in range(l0 + 1, state["global_len"] + 1))
+
+    m0 = env.sampler.mark()  # clock samples from here on are taken under load
     for _ in range(args.warmup):
         resident_step()
-    len_before = state["global_len"]
     state["launches"] = 0
     state["fused_steps"] = 0
     one_launch_before = pool.step_launches()
-    ms = timed(resident_step, args.steps)
+    blocks = [block(resident_step) for _ in range(repeats)]
     one_launch = pool.step_launches() - one_launch_before
-    launches = state["launches"] + one_launch + (state["fused_steps"] - one_launch) * LAYERS
-    len_after = state["global_len"]
-    bytes_timed = sum(LAYERS * decode_bytes(L) for L in range(len_before + 1, len_after + 1))
-    value = bytes_timed / (ms * 1e-3) / 1e9
+    launches = (state["launches"] + one_launch + (state["fused_steps"] - one_launch) * LAYERS) // repeats
+    rates = sorted(b / (ms * 1e-3) / 1e9 for ms, b in blocks)
+    value = statistics.median(rates)
+    ms = statistics.median(m for m, _ in blocks)
 
-    len_before = state["global_len"]
-    ms_e2e = timed(e2e_step, args.steps)
-    bytes_e2e = sum(LAYERS * decode_bytes(L) for L in range(len_before + 1, state["global_len"] + 1))
-    e2e_value = bytes_e2e / (ms_e2e * 1e-3) / 1e9
+    e2e_blocks = [block(e2e_step) for _ in range(e2e_repeats)]
+    e2e_value = statistics.median(b / (m * 1e-3) / 1e9 for m, b in e2e_blocks)
+    ms_e2e = statistics.median(m for m, _ in e2e_blocks)
     h2d = (q_host.numel() + k_host.numel() + v_host.numel()) * 2
     d2h = out_host.numel() * 2
 
-    # ---- dominant kernel alone: 16 back-to-back decode launches (one per layer) per event pair
+    # ---- the same step with layers strictly one after the other (no shared launch, no overlap)
+    pool.set_layer_overlap(False)
+    resident_step()
+    dep_blocks = [block(resident_step) for _ in range(2 if sub else 3)]
+    pool.set_layer_overlap(True)
+    dep_value = statistics.median(b / (m * 1e-3) / 1e9 for m, b in dep_blocks)
+    dep_ms = statistics.median(m for m, _ in dep_blocks)
+
+    # ---- dominant kernel alone
     pool.batch_set_sharded([seq], [0], [1], [state["global_len"] - 1], [lo])
     L_local = pool.length(seq)
-    local_out = out_dev if world == 1 else torch.zeros_like(out_dev)  # N>1: keep the merged rows
+    local_out = torch.zeros_like(out_dev)
 
     def decode_only():
         for layer in range(LAYERS):
             pool.decode(layer, q_rot[layer], local_out[layer], Q_HEADS * D, None, None)
 
     decode_only()
-    reps = max(3, args.steps)
-    ms_iso = timed(decode_only, reps) / (reps * LAYERS)  # plain launches, nothing overlapped
-    ms_k = ms_iso
-    if world == 1:
-        # the step's own launch (decode_step_kernel: all layers, append fused in), without the
-        # host's table work
-        pool.batch_set([seq])
+    reps = max(3, steps)
+    ms_iso = env.timed(decode_only, reps) / (reps * LAYERS)  # plain launches of one layer each
 
-        def step_kernels():
-            pool.decode_step(0, LAYERS, q_dev, k_dev, v_dev, Q_HEADS * D, KV_HEADS * D, cos, sin, q_rot,
-                             out_dev, Q_HEADS * D, Q_HEADS * D)
+    # the step's own launch on this rank's range without the host's table work and without the
+    # cross-rank exchange (decode_step_kernel: all layers, query rotation fused in)
+    def step_kernels():
+        pool.decode_step(0, LAYERS, q_dev, None, None, Q_HEADS * D, KV_HEADS * D, cos, sin, q_rot,
+                         local_out, Q_HEADS * D, Q_HEADS * D)
 
-        step_kernels()
-        ms_k = timed(step_kernels, reps) / (reps * LAYERS)
+    step_kernels()
+    ms_k = env.timed(step_kernels, reps) / (reps * LAYERS)
     kern_bytes = decode_bytes(L_local)
     achieved = kern_bytes / (ms_k * 1e-3) / 1e9
     peak, peak_kind = measured_peak()
     pool.check()
-    m1 = sampler.mark()
-    xchg_check = None
+    m1 = env.sampler.mark()
+
+    # ---- checks of the last step's rows (one more one-launch step so they come from that path)
+    resident_step()
+    torch.cuda.synchronize()
+    pool.check()
+    checks = {}
     if world > 1:
-        # the last step's merged layer-0 row against an NCCL all-gather + merge of the same partials
-        pool.decode(0, q_rot[0], None, 0, part[0, :Q_HEADS * D], part[0, Q_HEADS * D:])
-        dist.all_gather_into_tensor(gathered[0].view(-1), part[0])
-        o_parts.copy_(gathered[0, :, :Q_HEADS * D].reshape(world, Q_HEADS, D))
-        l_parts.copy_(gathered[0, :, Q_HEADS * D:])
-        chk = torch.zeros(1, Q_HEADS * D, dtype=torch.bfloat16, device=dev)
-        paged.merge_partials(o_parts, l_parts, world, Q_HEADS, chk)
-        torch.cuda.synchronize()
-        xchg_check = float((chk.float() - out_dev[0].float()).abs().max().item())
+        # every layer: the merged rows against an NCCL all-gather + merge of the same partials
+        pool.batch_set_sharded([seq], [0], [1], [state["global_len"] - 1], [lo])
+        worst = 0.0
+        for layer in range(LAYERS):
+            pool.decode(layer, q_rot[layer], None, 0, part[layer, :Q_HEADS * D], part[layer, Q_HEADS * D:])
+            dist.all_gather_into_tensor(gathered[layer].view(-1), part[layer])
+            o_parts.copy_(gathered[layer, :, :Q_HEADS * D].reshape(world, Q_HEADS, D))
+            l_parts.copy_(gathered[layer, :, Q_HEADS * D:])
+            chk = torch.zeros(1, Q_HEADS * D, dtype=torch.bfloat16, device=dev)
+            paged.merge_partials(o_parts, l_parts, world, Q_HEADS, chk)
+            torch.cuda.synchronize()
+            worst = max(worst, float((chk.float() - out_dev[layer].float()).abs().max().item()))
+        t = torch.tensor([worst], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        checks["exchange_vs_allgather_max_abs_diff_all_layers"] = float(t.item())
+    cpu = cpu_check_and_baseline(env, pool, seq, q_rot, out_dev, pool.length(seq), budget_s=(2.0 if sub else 10.0))
 
     line = None
     if rank == 0:
-        clocks = sampler.stop(m0, m1)
+        clocks = env.sampler.summary(m0, m1)
+        roof = {"bound": "hbm", "kernel": "decode_step_kernel", "achieved": round(achieved, 1),
+                "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                "peak_source": f"of {peak_kind}", "frac_of_nominal_8000": round(achieved / 8000.0, 4),
+                "us_per_launch": round(ms_k * 1e3 * LAYERS, 2), "bytes_per_launch": kern_bytes * LAYERS,
+                "layers_per_launch": LAYERS, "us_per_layer": round(ms_k * 1e3, 2),
+                "us_per_layer_plain_decode_kernel": round(ms_iso * 1e3, 2),
+                "how": (f"CUDA events around this rank's one-launch step over its own token range (all {LAYERS} layers, "
+                        f"no cross-rank exchange), {reps} launches"),
+                "traffic": (NCU_TRAFFIC_BYTES[workload] * LAYERS
+                            if world == 1 and NCU_TRAFFIC_BYTES.get(workload) and LAYERS >= 2 else None)}
+        if world == 1:
+            roof["traffic_note"] = "ncu capture of a 2-layer decode_step_kernel launch, per layer x layers"
+        else:
+            # what the exchange adds per layer on top of this rank's own stream + combine
+            roof["per_rank_gbs_in_the_step"] = round(value / world, 1)
+            roof["exchange_share"] = round(max(0.0, 1.0 - (ms_k * LAYERS) / (ms / steps)), 4)
         line = {
             "metric": "paged_decode_attn_hbm_gbs", "value": round(value, 1), "unit": "GB/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": round(ms / args.steps, 4),
-            "us_per_token": round(ms / args.steps * 1e3, 2),
-            "us_per_token_per_layer": round(ms / args.steps * 1e3 / LAYERS, 2),
+            "n_gpus": world, "steps": steps, "warmup": args.warmup,
+            "ms_per_step": round(ms / steps, 4),
+            "us_per_token": round(ms / steps * 1e3, 2),
+            "us_per_token_per_layer": round(ms / steps * 1e3 / LAYERS, 2),
+            "repeats": repeats, "value_min": round(rates[0], 1), "value_max": round(rates[-1], 1),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": wl["name"], "context": ctx, "layers": LAYERS, "batch": 1,
-                       "q_heads": Q_HEADS, "kv_heads": KV_HEADS, "head_dim": D, "block_tokens": BLOCK,
-                       "block_table": "seeded random permutation over a pool 25% larger than the sequence",
-                       "parallelism": "1 GPU" if world == 1 else (
-                           f"sequence range split over {world} GPUs; one launch per step, per layer the combining CTAs "
-                           f"push (O, LSE) to every rank over NVLink (peer stores of value+step words) and merge locally"
-                           if xchg is not None else
-                           f"sequence range split over {world} GPUs, NCCL all-gather of (O, LSE) per layer + merge"),
-                       "l2": f"inputs larger than L2 ({decode_bytes(ctx) * LAYERS / 1e9:.2f} GB streamed per step)"},
+            "config": decode_config(wl, ctx, world, args.exchange),
             "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": round(ms_e2e / args.steps, 4)},
+                    "d2h_bytes_per_step": d2h, "ms_per_step": round(ms_e2e / steps, 4)},
+            "dependent_layers": {"value": round(dep_value, 1), "unit": "GB/s", "ms_per_step": round(dep_ms / steps, 4),
+                                 "us_per_token_per_layer": round(dep_ms / steps * 1e3 / LAYERS, 2),
+                                 "how": "one kernel per layer, layer l+1 launched behind layer l with no overlap "
+                                        "(pa_pool_set_layer_overlap(pool, 0)); the exchange and merge stay in the kernel"},
             "gpu_launches": launches,
             "clocks": clocks,
-            "roofline": ({"bound": "hbm", "kernel": "decode_step_kernel", "achieved": round(achieved, 1),
-                          "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                          "peak_source": f"of {peak_kind}", "frac_of_nominal_8000": round(achieved / 8000.0, 4),
-                          "us_per_launch": round(ms_k * 1e3 * LAYERS, 2), "bytes_per_launch": kern_bytes * LAYERS,
-                          "layers_per_launch": LAYERS, "us_per_layer": round(ms_k * 1e3, 2),
-                          "us_per_layer_plain_decode_kernel": round(ms_iso * 1e3, 2),
-                          "how": f"CUDA events around the step's one launch (all {LAYERS} layers, append fused in)",
-                          "traffic": (NCU_TRAFFIC_BYTES[args.workload] * LAYERS
-                                      if NCU_TRAFFIC_BYTES.get(args.workload) else None),
-                          "traffic_note": "ncu capture of a 2-layer decode_step_kernel launch, per layer x layers"}
-                         if world == 1 and LAYERS >= 2 else
-                         {"bound": "hbm", "kernel": "decode_kernel", "achieved": round(achieved, 1),
-                          "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                          "peak_source": f"of {peak_kind}", "frac_of_nominal_8000": round(achieved / 8000.0, 4),
-                          "us_per_launch": round(ms_k * 1e3, 2), "bytes_per_launch": kern_bytes,
-                          "how": f"CUDA events around {LAYERS} plain decode_kernel launches on this rank's range, / {LAYERS}",
-                          "traffic": NCU_TRAFFIC_BYTES.get(args.workload)}),
+            "roofline": roof,
+            "checks": {**checks, **{k: v for k, v in cpu.items() if k.startswith("oracle_")}},
         }
         if world == 1:
-            line["cpu_baseline"] = cpu_baseline(pool, seq, q_rot, out_dev, L_local)
-        else:
-            line["exchange_vs_allgather_max_abs_diff"] = xchg_check
-        print(json.dumps(line), flush=True)
-    barrier()
+            line["cpu_baseline"] = {k: v for k, v in cpu.items() if not k.startswith("oracle_")}
+    env.barrier()
     if xchg is not None:
         xchg.close()
     pool.close()
-    if world > 1:
-        dist.destroy_process_group()
+    return line
 
 
-def cpu_baseline(pool, seq, q_rot, out_dev, L):
-    """The CPU oracle (fp32 naive attention, OpenMP) on a bounded sample: layer
-    0 of this workload, repeated for about ten seconds; its answer is also the
-    check of the GPU output of that layer."""
-    import torch
-
+def cpu_check_and_baseline(env: Env, pool, seq, q_rot, out_dev, L, budget_s=10.0):
+    """The CPU oracle (fp32 naive attention, OpenMP) on layer 0 of this rank's token range.  Every
+    rank computes its partial (O, LSE); the partials are merged on the host with the oracle's
+    log-sum-exp merge and compared with the GPU's merged row.  On one GPU the same passes, repeated
+    for about `budget_s` seconds, are also the timed CPU baseline."""
+    torch, dist = env.torch, env.dist
     from oracle import oracle as orc
 
     dev = q_rot.device
-    k = torch.zeros(KV_HEADS, L, D, dtype=torch.bfloat16, device=dev)
-    v = torch.zeros_like(k)
-    pool.gather_kv(0, seq, k, v, L)
-    torch.cuda.synchronize()
-    k_h = k.view(torch.int16).cpu().numpy().view(np.uint16)
-    v_h = v.view(torch.int16).cpu().numpy().view(np.uint16)
-    q_h = q_rot[0].view(torch.int16).cpu().numpy().view(np.uint16).reshape(Q_HEADS, 1, D)
-    del k, v
-    t0 = time.perf_counter()
-    O, _ = orc.attention(q_h, k_h, v_h, L)
-    t1 = time.perf_counter() - t0
-    reps = 1
-    budget = 10.0
-    while t1 * reps < budget and reps < 64:
-        orc.attention(q_h, k_h, v_h, L)
-        reps += 1
-    total = time.perf_counter() - t0
-    got = orc.bf16_to_f32(out_dev[0].view(torch.int16).cpu().numpy().view(np.uint16)).reshape(-1)
-    err = float(np.max(np.abs(got - O[:, 0].reshape(-1))))
-    return {"value": round(decode_bytes(L) * reps / total / 1e9, 3), "unit": "GB/s",
-            "cores": orc.num_threads(), "kind": "port",
-            "sample": f"layer 0 of the workload (context {L}), {reps} passes of the fp32 CPU oracle",
-            "gpu_vs_cpu_max_abs_err": err}
+    q_h = _u16(q_rot[0]).reshape(Q_HEADS, 1, D)
+    reps, total = 1, 0.0
+    if L > 0:
+        k = torch.zeros(KV_HEADS, L, D, dtype=torch.bfloat16, device=dev)
+        v = torch.zeros_like(k)
+        pool.gather_kv(0, seq, k, v, L)
+        torch.cuda.synchronize()
+        k_h, v_h = _u16(k), _u16(v)
+        del k, v
+        t0 = time.perf_counter()
+        O, lse = orc.attention(q_h, k_h, v_h, L, causal=False)
+        t1 = time.perf_counter() - t0
+        if env.world == 1:
+            while t1 * reps < budget_s and reps < 64:
+                orc.attention(q_h, k_h, v_h, L, causal=False)
+                reps += 1
+        total = time.perf_counter() - t0
+    else:
+        O = np.zeros((Q_HEADS, 1, D), np.float32)
+        lse = np.full((Q_HEADS, 1), -np.inf, np.float32)
+    if env.world > 1:
+        mine = torch.from_numpy(np.concatenate([O[:, 0].reshape(-1), lse[:, 0]]).astype(np.float32)).to(dev)
+        allp = torch.zeros(env.world, mine.numel(), dtype=torch.float32, device=dev)
+        dist.all_gather_into_tensor(allp.view(-1), mine)
+        a = allp.cpu().numpy()
+        want, _ = orc.lse_merge(a[:, :Q_HEADS * D].reshape(env.world, Q_HEADS, D), a[:, Q_HEADS * D:])
+        want = want.reshape(-1)
+    else:
+        want = O[:, 0].reshape(-1)
+    got = orc.bf16_to_f32(_u16(out_dev[0])).reshape(-1)
+    res = {"oracle_layer0_max_abs_err": float(np.max(np.abs(got - want))),
+           "oracle_layer0_max_row_rel_err": row_rel_err(got, want),
+           "oracle_row_rel_bar": ROW_REL}
+    res["oracle_layer0_ok"] = bool(res["oracle_layer0_max_row_rel_err"] <= ROW_REL)
+    if env.world == 1:
+        res.update({"value": round(decode_bytes(L) * reps / total / 1e9, 3), "unit": "GB/s",
+                    "cores": orc.num_threads(), "kind": "port",
+                    "sample": f"layer 0 of the workload (context {L}), {reps} passes of the fp32 CPU oracle",
+                    "gpu_vs_cpu_max_abs_err": res["oracle_layer0_max_abs_err"]})
+    return res
 
 
 # =============================================================================
 # reference arm: the reference's own CUDA kernels (oracle/_ref/libref.so) on this GPU
 # =============================================================================
-def run_reference(args):
-    rank, local_rank, world = dist_env()
-    if rank != 0:
-        return
+def reference_decode(env: Env, workload: str, steps: int, warmup: int, with_e2e: bool = True):
+    """What Attention::forward does per layer for one token (steps 5-7): launch_rope_qkv, the
+    128-byte append copies, launch_flash_attention with q_seq_len 1, launch_flash_output_layout.
+    Returns a dict of rates and times, or None when the reference kernels were not built."""
     from oracle import oracle as orc
-
+    torch = env.torch
     if not orc.ref_available():
-        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libref.so was not built (no reference checkout at build time)"}))
-        return
-    import torch
-
-    torch.cuda.set_device(local_rank)
-    dev = f"cuda:{local_rank}"
+        return None
+    dev = env.dev
     ref = orc.ref()
-    wl = WORKLOADS[args.workload]
-    ctx = wl["ctx"]
-    total_steps = args.warmup + 2 * args.steps + 4
+    ctx = WORKLOADS[workload]["ctx"]
+    total_steps = warmup + 2 * steps + 4
     max_seq = ctx + total_steps + 1
     gen = torch.Generator(device=dev)
     gen.manual_seed(4321)
@@ -461,9 +572,6 @@ def run_reference(args):
     state = {"len": ctx}
 
     def step():
-        """What Attention::forward does per layer for one token (steps 5-7):
-        launch_rope_qkv, the 128-byte append copies, launch_flash_attention with
-        q_seq_len 1, launch_flash_output_layout."""
         pos = state["len"]
         state["len"] += 1
         for layer in range(LAYERS):
@@ -484,81 +592,73 @@ def run_reference(args):
         torch.cuda.current_stream().synchronize()
 
     def timed(fn, n):
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         l0 = state["len"]
-        e0.record()
-        for _ in range(n):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        b = sum(LAYERS * decode_bytes(L) for L in range(l0 + 1, state["len"] + 1))
-        return e0.elapsed_time(e1), b
+        ms = local_timed(torch, fn, n)
+        return ms, sum(LAYERS * decode_bytes(L) for L in range(l0 + 1, state["len"] + 1))
 
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    time.sleep(0.3)
-    ms, b = timed(step, args.steps)
-    clocks = sampler.stop()
-    ms2, b2 = timed(e2e_step, args.steps)
-    value = b / (ms * 1e-3) / 1e9
-    e2e = b2 / (ms2 * 1e-3) / 1e9
-    print(json.dumps({
-        "impl": "reference", "metric": "paged_decode_attn_hbm_gbs", "value": round(value, 2), "unit": "GB/s",
-        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4),
-        "us_per_token": round(ms / args.steps * 1e3, 2), "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": wl["name"], "context": ctx, "layers": LAYERS, "batch": 1,
-                   "note": "the reference's own CUDA kernels (flashattention.cu, rope.cu, layout.cu compiled "
-                           "unmodified for sm_100a) on this GPU, contiguous cache, single GPU only"},
-        "e2e": {"value": round(e2e, 2), "unit": "GB/s",
-                "h2d_bytes_per_step": (q_host.numel() + k_host.numel() + v_host.numel()) * 2,
-                "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": round(ms2 / args.steps, 4)},
-        "gpu_launches": args.steps * LAYERS * 5, "clocks": clocks,
-        "cpu_baseline": {"value": round(value, 2), "unit": "GB/s", "cores": 0, "kind": "reference",
+    ms, b = timed(step, steps)
+    res = {"value": b / (ms * 1e-3) / 1e9, "ms_per_step": ms / steps,
+           "h2d": (q_host.numel() + k_host.numel() + v_host.numel()) * 2, "d2h": out_host.numel() * 2}
+    if with_e2e:
+        ms2, b2 = timed(e2e_step, steps)
+        res.update({"e2e_value": b2 / (ms2 * 1e-3) / 1e9, "e2e_ms_per_step": ms2 / steps})
+    return res
+
+
+def run_reference(env: Env, args, workload: str):
+    if env.rank != 0:
+        return None
+    m0 = env.sampler.mark()
+    time.sleep(0.2)
+    r = reference_decode(env, workload, args.steps, args.warmup)
+    if r is None:
+        return {"impl": "reference", "unavailable": "oracle/_ref/libref.so was not built (no reference checkout at build time)"}
+    wl = WORKLOADS[workload]
+    cfg = decode_config(wl, wl["ctx"], 1, "fused")
+    cfg["note"] = ("the reference's own CUDA kernels (flashattention.cu, rope.cu, layout.cu compiled unmodified for "
+                   "sm_100a) on this GPU, contiguous cache, single GPU only")
+    return {
+        "impl": "reference", "metric": "paged_decode_attn_hbm_gbs", "value": round(r["value"], 2), "unit": "GB/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(r["ms_per_step"], 4),
+        "us_per_token": round(r["ms_per_step"] * 1e3, 2), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg,
+        "e2e": {"value": round(r["e2e_value"], 2), "unit": "GB/s", "h2d_bytes_per_step": r["h2d"],
+                "d2h_bytes_per_step": r["d2h"], "ms_per_step": round(r["e2e_ms_per_step"], 4)},
+        "gpu_launches": args.steps * LAYERS * 5, "clocks": env.sampler.summary(m0, None),
+        "cpu_baseline": {"value": round(r["value"], 2), "unit": "GB/s", "cores": 0, "kind": "reference",
                          "sample": "whole workload; the reference has no CPU implementation of this path, "
                                    "so its CUDA kernels run on the GPU (host cores only drive the launches)"},
-    }), flush=True)
+    }
 
 
 # =============================================================================
-# batched decode workload (config 5): 64 ragged sequences, shared fragmented pool
+# batched decode workload: 64 ragged sequences, shared fragmented pool, KV heads sharded
 # =============================================================================
-def run_batch(args):
-    """64 sequences with context lengths seeded-uniform in [1024, 32768], one
-    shared free-block pool; before timing, rounds of freeing and re-creating
-    sequences interleave their tables.  One step = every sequence appends one
-    token and attends over its cache, 16 layers.  With N GPUs the 8 KV heads are
-    sharded (8/N per GPU, each with the 4*8/N query heads of its groups); every
-    layer ends with an all-gather of the head outputs into [64, 2048] on every
-    rank.  Strong scaling: the same batch is split N ways."""
-    import torch
-    import torch.distributed as dist
-
+def run_batch(env: Env, args, sub: bool = False):
+    """64 sequences with context lengths seeded-uniform in [1024, 32768], one shared free-block
+    pool; before timing, rounds of freeing and re-creating sequences interleave their tables.  One
+    step = every sequence appends one token and attends over its cache, 16 layers.  With N GPUs the
+    8 KV heads are sharded (8/N per GPU, each with the 4*8/N query heads of its groups); every
+    layer's head outputs are gathered into [64, 2048] on every rank by the decode kernel's own
+    peer stores.  Strong scaling: the same batch is split N ways."""
+    torch, dist = env.torch, env.dist
     from llama_transformer_runtime_b200 import paged
 
-    rank, local_rank, world = dist_env()
-    torch.cuda.set_device(local_rank)
-    dev = f"cuda:{local_rank}"
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device(dev))
+    rank, local_rank, world, dev = env.rank, env.local_rank, env.world, env.dev
     if args.impl == "reference":
-        if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable":
-                              "the reference is single-sequence and contiguous; this workload has no reference arm "
-                              "(see the decode128k and prefill2k workloads)"}))
-        return
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
+        return {"impl": "reference", "unavailable":
+                "the reference is single-sequence and contiguous; this workload has no reference arm "
+                "(see the decode128k and prefill2k workloads)"} if rank == 0 else None
     n_seqs = args.seqs
+    steps = max(2, args.steps // 4) if sub else args.steps
+    warmup = 3 if sub else args.warmup
     kvh = KV_HEADS // world
     qh = 4 * kvh
     rng = np.random.default_rng(2024)  # the same allocator decisions on every rank
     lens = rng.integers(1024, 32769, n_seqs).astype(int)
-    total_steps = args.warmup + 2 * args.steps + 8
+    total_steps = warmup + 2 * steps + 8
     cap = int(lens.max()) + total_steps + 64
     blocks_needed = int(sum((l + total_steps + 15) // 16 for l in lens))
     num_blocks = blocks_needed + blocks_needed // 8 + 64
@@ -618,9 +718,8 @@ def run_batch(args):
     out_host = torch.zeros(LAYERS, n_seqs, Q_HEADS * D, dtype=torch.bfloat16).pin_memory()
     state = {"launches": 0, "bytes": 0, "rows": None}
     hg = None
+    cudart = ctypes.CDLL("libcudart.so.12")
     if world > 1 and args.exchange == "fused":
-        import ctypes
-        cudart = ctypes.CDLL("libcudart.so.12")
         hg = paged.HeadGather(local_rank, rank, world, n_seqs, LAYERS, kvh)
         handles = [None] * world
         dist.all_gather_object(handles, hg.handle())
@@ -663,35 +762,18 @@ def run_batch(args):
             out_host.copy_(out_full, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
     def timed(fn, n):
-        barrier()
         state["bytes"] = 0
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(n):
-            fn()
-        e1.record()
-        barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
+        ms = env.timed(fn, n)
         return ms, state["bytes"]
 
-    m0 = sampler.mark()
-    for _ in range(args.warmup):
+    m0 = env.sampler.mark()
+    for _ in range(warmup):
         step()
     state["launches"] = 0
-    ms, nbytes = timed(step, args.steps)
+    ms, nbytes = timed(step, steps)
     launches = state["launches"]
-    ms_e2e, nbytes_e2e = timed(e2e_step, args.steps)
+    ms_e2e, nbytes_e2e = timed(e2e_step, steps)
 
     # dominant kernel alone (this rank's heads), one launch per layer
     pool.batch_set(ids, [0] * n_seqs)
@@ -701,31 +783,46 @@ def run_batch(args):
             pool.decode(layer, q_rot[layer], out_local[layer], qh * D)
 
     decode_only()
-    reps = max(3, args.steps // 2)
+    reps = max(3, steps // 2)
     ms_k, _ = timed(decode_only, reps)
     ms_k /= reps * LAYERS
     kern_bytes = sum(decode_bytes(seqs[s]) for s in ids) // world
     achieved = kern_bytes / (ms_k * 1e-3) / 1e9
     peak, peak_kind = measured_peak()
     pool.check()
-    m1 = sampler.mark()
+    m1 = env.sampler.mark()
     gather_check = None
     if hg is not None:
-        # layer 0 of the last fused step against an NCCL all-gather of the same decode
-        dist.all_gather_into_tensor(gath[0].view(-1), out_local[0].view(-1))
-        want = gath[0].permute(1, 0, 2).reshape(n_seqs, Q_HEADS * D)
-        got = torch.empty(n_seqs, Q_HEADS * D, dtype=torch.bfloat16, device=dev)
+        # every layer of the last fused step against an NCCL all-gather of the same decode
+        gather_check = 0.0
         torch.cuda.synchronize()
-        assert cudart.cudaMemcpy(ctypes.c_void_p(got.data_ptr()), ctypes.c_void_p(state["rows"]),
-                                 ctypes.c_size_t(got.numel() * 2), 3) == 0
-        gather_check = float((got.float() - want.float()).abs().max().item())
+        got_all = torch.empty(LAYERS, n_seqs, Q_HEADS * D, dtype=torch.bfloat16, device=dev)
+        assert cudart.cudaMemcpy(ctypes.c_void_p(got_all.data_ptr()), ctypes.c_void_p(state["rows"]),
+                                 ctypes.c_size_t(got_all.numel() * 2), 3) == 0
+        for layer in range(LAYERS):
+            dist.all_gather_into_tensor(gath[layer].view(-1), out_local[layer].view(-1))
+            want = gath[layer].permute(1, 0, 2).reshape(n_seqs, Q_HEADS * D)
+            gather_check = max(gather_check, float((got_all[layer].float() - want.float()).abs().max().item()))
+    # CPU oracle on this rank's heads of a few sequences of layer 0
+    from oracle import oracle as orc
+    worst_rel, worst_abs = 0.0, 0.0
+    for i in (0, n_seqs // 2, n_seqs - 1):
+        s, L = ids[i], seqs[ids[i]]
+        kk = torch.zeros(kvh, L, D, dtype=torch.bfloat16, device=dev)
+        vv = torch.zeros_like(kk)
+        pool.gather_kv(0, s, kk, vv, L)
+        torch.cuda.synchronize()
+        O, _ = orc.attention(_u16(q_rot[0, i]).reshape(qh, 1, D), _u16(kk), _u16(vv), L, causal=False)
+        got = orc.bf16_to_f32(_u16(out_local[0, i])).reshape(-1)
+        worst_rel = max(worst_rel, row_rel_err(got, O[:, 0].reshape(-1)))
+        worst_abs = max(worst_abs, float(np.max(np.abs(got - O[:, 0].reshape(-1)))))
+    line = None
     if rank == 0:
         line = {
-            "fused_gather_vs_allgather_max_abs_diff": gather_check,
             "metric": "paged_decode_attn_hbm_gbs", "value": round(nbytes / (ms * 1e-3) / 1e9, 1), "unit": "GB/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4),
-            "us_per_token": round(ms / args.steps * 1e3 / n_seqs, 2),
-            "us_per_step_per_layer": round(ms / args.steps * 1e3 / LAYERS, 2),
+            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": round(ms / steps, 4),
+            "us_per_token": round(ms / steps * 1e3 / n_seqs, 2),
+            "us_per_step_per_layer": round(ms / steps * 1e3 / LAYERS, 2),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"decode_batch{n_seqs}_ctxU1024-32768_x{LAYERS}layers", "sequences": n_seqs,
                        "tokens_in_cache": int(sum(seqs.values())), "layers": LAYERS, "block_tokens": BLOCK,
@@ -739,209 +836,222 @@ def run_batch(args):
                        "l2": "inputs larger than L2"},
             "e2e": {"value": round(nbytes_e2e / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
                     "h2d_bytes_per_step": (q_host.numel() + k_host.numel() + v_host.numel()) * 2,
-                    "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": round(ms_e2e / args.steps, 4)},
-            "gpu_launches": launches, "clocks": sampler.stop(m0, m1),
+                    "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": round(ms_e2e / steps, 4)},
+            "gpu_launches": launches, "clocks": env.sampler.summary(m0, m1),
             "roofline": {"bound": "hbm", "kernel": "decode_kernel", "achieved": round(achieved, 1), "peak": peak,
                          "unit": "GB/s", "frac": round(achieved / peak, 4), "peak_source": f"of {peak_kind}",
                          "us_per_launch": round(ms_k * 1e3, 2), "bytes_per_launch": kern_bytes, "traffic": None},
+            "checks": {"fused_gather_vs_allgather_max_abs_diff_all_layers": gather_check,
+                       "oracle_layer0_max_abs_err": worst_abs, "oracle_layer0_max_row_rel_err": worst_rel,
+                       "oracle_row_rel_bar": ROW_REL, "oracle_layer0_ok": bool(worst_rel <= ROW_REL)},
         }
-        print(json.dumps(line), flush=True)
-    barrier()
+    env.barrier()
     if hg is not None:
         hg.close()
     pool.close()
-    if world > 1:
-        dist.destroy_process_group()
+    return line
 
 
 # =============================================================================
-# prefill workload (config 3): 2048 tokens x 16 layers, causal, batch 1
+# Q/K/V projections of a decode step, output projection (weight streams)
 # =============================================================================
-PREFILL_TOKENS = 2048
-
-
-def run_qkv(args):
-    """Q/K/V projections of a decode step (the producer in front of the attention path): batch 1,
-    hidden 2048 -> q 2048 + k 512 + v 512 columns, all layers of the step.  A step reads every layer's
-    weights once (12.6 MB per layer), so the metric is achieved HBM GB/s.  N>1: independent replicas."""
-    import torch
-    import torch.distributed as dist
-
+def run_qkv(env: Env, args, sub: bool = False, which: str = "qkv"):
+    """which == "qkv": Q/K/V projections of a decode step (the producer in front of the attention
+    path): batch 1, hidden 2048 -> q 2048 + k 512 + v 512 columns, all layers of the step.
+    which == "out": the output projection + residual behind it (2048 -> 2048).  A step reads every
+    layer's weights once, so the metric is achieved HBM GB/s.  N>1: independent replicas."""
+    torch = env.torch
     from llama_transformer_runtime_b200 import paged
+    from oracle import oracle as orc
 
-    rank, local_rank, world = dist_env()
-    torch.cuda.set_device(local_rank)
-    dev = f"cuda:{local_rank}"
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device(dev))
-    if args.impl == "reference" and rank != 0:
-        return
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    H, NQ, NKV, rows = 2048, 2048, 512, 1
+    rank, world, dev = env.rank, env.world, env.dev
+    ref_arm = args.impl == "reference" and not sub
+    if ref_arm and rank != 0:
+        return None
+    steps = max(5, args.steps // 2) if sub else args.steps
+    warmup = 3 if sub else args.warmup
+    H, NQ, NKV, rows = HIDDEN, 2048, 512, 1
     gen = torch.Generator(device=dev)
     gen.manual_seed(99 + rank)
-    # 8 rotating weight sets (1.6 GB) so that no step finds its weights in L2 (126 MB)
-    SETS = 8 if args.impl == "ours" else 2
-    wq = [(torch.randn(LAYERS, H, NQ, generator=gen, device=dev) * 0.03).to(torch.bfloat16) for _ in range(SETS)]
-    wk = [(torch.randn(LAYERS, H, NKV, generator=gen, device=dev) * 0.03).to(torch.bfloat16) for _ in range(SETS)]
-    wv = [(torch.randn(LAYERS, H, NKV, generator=gen, device=dev) * 0.03).to(torch.bfloat16) for _ in range(SETS)]
+    # rotating weight sets so that no step finds its weights in L2 (126 MB)
+    SETS = 2 if ref_arm else (4 if sub else 8)
     x_host = torch.randn(LAYERS, rows, H, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).pin_memory()
     x_dev = x_host.to(dev)
-    q = torch.zeros(LAYERS, rows, NQ, dtype=torch.bfloat16, device=dev)
-    k = torch.zeros(LAYERS, rows, NKV, dtype=torch.bfloat16, device=dev)
-    v = torch.zeros(LAYERS, rows, NKV, dtype=torch.bfloat16, device=dev)
-    out_host = torch.zeros(LAYERS, rows, NQ + 2 * NKV, dtype=torch.bfloat16).pin_memory()
-    bytes_layer = (H * (NQ + 2 * NKV) + rows * H + rows * (NQ + 2 * NKV)) * 2
     state = {"i": 0}
+    ref = orc.ref() if orc.ref_available() else None
+    if ref_arm and ref is None:
+        return {"impl": "reference", "unavailable": "oracle/_ref/libref.so was not built"}
+    if which == "qkv":
+        wq = [(torch.randn(LAYERS, H, NQ, generator=gen, device=dev) * 0.03).to(torch.bfloat16) for _ in range(SETS)]
+        wk = [(torch.randn(LAYERS, H, NKV, generator=gen, device=dev) * 0.03).to(torch.bfloat16) for _ in range(SETS)]
+        wv = [(torch.randn(LAYERS, H, NKV, generator=gen, device=dev) * 0.03).to(torch.bfloat16) for _ in range(SETS)]
+        q = torch.zeros(LAYERS, rows, NQ, dtype=torch.bfloat16, device=dev)
+        k = torch.zeros(LAYERS, rows, NKV, dtype=torch.bfloat16, device=dev)
+        v = torch.zeros(LAYERS, rows, NKV, dtype=torch.bfloat16, device=dev)
+        out_host = torch.zeros(LAYERS, rows, NQ + 2 * NKV, dtype=torch.bfloat16).pin_memory()
+        bytes_layer = (H * (NQ + 2 * NKV) + rows * H + rows * (NQ + 2 * NKV)) * 2
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        if args.qkv_packed:
+            pq = [paged.pack_projection_weights(w) for w in wq]
+            pk = [paged.pack_projection_weights(w) for w in wk]
+            pv = [paged.pack_projection_weights(w) for w in wv]
+            torch.cuda.synchronize()
 
-    if args.impl == "reference":
-        from oracle import oracle as orc
-        ref = orc.ref()
+        def ours_step(s):
+            if not args.qkv_packed:
+                paged.qkv_project(x_dev, wq[s], wk[s], wv[s], q, k, v, rows, LAYERS)
+            else:
+                paged.qkv_project_packed(x_dev, pq[s], pk[s], pv[s], q, k, v, rows, status, LAYERS)
 
-        def step():
+        def ref_step(s):
             # as Attention::forward drives it (src/runtime/attention.cu:138-191): three GEMM launches
             # per layer, a device synchronisation after each
-            s = state["i"] % SETS
-            state["i"] += 1
             for l in range(LAYERS):
                 for w, o, n in ((wq[s], q, NQ), (wk[s], k, NKV), (wv[s], v, NKV)):
                     ref.ref_gemm(x_dev[l].data_ptr(), w[l].data_ptr(), o[l].data_ptr(), rows, n, H)
                     torch.cuda.synchronize()
-        launches_per_step = 3 * LAYERS
-    else:
-        # weights repacked once, at load time, into the tile images both projection kernels read
-        pq = [paged.pack_projection_weights(w) for w in wq]
-        pk = [paged.pack_projection_weights(w) for w in wk]
-        pv = [paged.pack_projection_weights(w) for w in wv]
-        status = torch.zeros(1, dtype=torch.int32, device=dev)
-        torch.cuda.synchronize()
 
+        def copy_out():
+            out_host[:, :, :NQ].copy_(q, non_blocking=True)
+            out_host[:, :, NQ:NQ + NKV].copy_(k, non_blocking=True)
+            out_host[:, :, NQ + NKV:].copy_(v, non_blocking=True)
+        ref_launches, kernel = 3 * LAYERS, ("qkv_project_kernel" if not args.qkv_packed else "qkv_project_packed_kernel")
+        metric, wname = "qkv_project_hbm_gbs", f"qkv_projection_decode_batch1_x{LAYERS}layers"
+    else:
+        wo = [(torch.randn(LAYERS, H, H, generator=gen, device=dev) * 0.03).to(torch.bfloat16) for _ in range(SETS)]
+        res = (torch.randn(LAYERS, rows, H, generator=gen, device=dev)).to(torch.bfloat16)
+        o = torch.zeros(LAYERS, rows, H, dtype=torch.bfloat16, device=dev)
+        lin = torch.zeros(rows, H, dtype=torch.bfloat16, device=dev)
+        out_host = torch.zeros(LAYERS, rows, H, dtype=torch.bfloat16).pin_memory()
+        bytes_layer = (H * H + 3 * rows * H) * 2
+
+        def ours_step(s):
+            paged.out_project(x_dev, wo[s], res, o, rows, LAYERS)
+
+        def ref_step(s):
+            # o_proj GEMM + synchronisation (src/runtime/attention.cu:367-375), then the residual add
+            # of TransformerBlock::forward (src/runtime/transformer_block.cu:76-81)
+            for l in range(LAYERS):
+                ref.ref_gemm(x_dev[l].data_ptr(), wo[s][l].data_ptr(), lin.data_ptr(), rows, H, H)
+                torch.cuda.synchronize()
+                ref.ref_residual_add(res[l].data_ptr(), lin.data_ptr(), o[l].data_ptr(), rows * H)
+                torch.cuda.synchronize()
+
+        def copy_out():
+            out_host.copy_(o, non_blocking=True)
+        ref_launches, kernel = 2 * LAYERS, "qkv_project_kernel (output projection + residual epilogue)"
+        metric, wname = "out_project_hbm_gbs", f"out_projection_residual_decode_batch1_x{LAYERS}layers"
+
+    def make_step(fn):
         def step():
             s = state["i"] % SETS
             state["i"] += 1
-            if (not args.qkv_packed):
-                paged.qkv_project(x_dev, wq[s], wk[s], wv[s], q, k, v, rows, LAYERS)
-            else:
-                paged.qkv_project_packed(x_dev, pq[s], pk[s], pv[s], q, k, v, rows, status, LAYERS)
-        launches_per_step = 1
+            fn(s)
+        return step
 
-    def e2e_step():
-        x_dev.copy_(x_host, non_blocking=True)
-        step()
-        out_host[:, :, :NQ].copy_(q, non_blocking=True)
-        out_host[:, :, NQ:NQ + NKV].copy_(k, non_blocking=True)
-        out_host[:, :, NQ + NKV:].copy_(v, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+    def make_e2e(step):
+        def e2e_step():
+            x_dev.copy_(x_host, non_blocking=True)
+            step()
+            copy_out()
+            torch.cuda.current_stream().synchronize()
+        return e2e_step
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1 and args.impl == "ours":
-            dist.barrier()
-        torch.cuda.synchronize()
+    grouped = env.dist is not None and not ref_arm and not sub
 
     def timed(fn, n):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(n):
-            fn()
-        e1.record()
-        barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1 and args.impl == "ours":
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
+        return env.timed(fn, n) if grouped else local_timed(torch, fn, n)
 
-    m0 = sampler.mark()
-    for _ in range(args.warmup):
+    m0 = env.sampler.mark()
+    step = make_step(ref_step if ref_arm else ours_step)
+    for _ in range(warmup):
         step()
-    ms = timed(step, args.steps)
-    ms_e2e = timed(e2e_step, args.steps)
-    m1 = sampler.mark()
-    n_rep = world if args.impl == "ours" else 1
-    value = n_rep * LAYERS * bytes_layer * args.steps / (ms * 1e-3) / 1e9
-    e2e_value = n_rep * LAYERS * bytes_layer * args.steps / (ms_e2e * 1e-3) / 1e9
-    if rank == 0:
-        peak, peak_kind = measured_peak()
-        line = {
-            "metric": "qkv_project_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4),
-            "us_per_layer": round(ms / args.steps * 1e3 / LAYERS, 2),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"qkv_projection_decode_batch1_x{LAYERS}layers", "hidden": H, "q_cols": NQ,
-                       "kv_cols": NKV, "rows": rows, "layers": LAYERS,
-                       "parallelism": "1 GPU" if world == 1 else f"{world} independent replicas",
-                       "l2": f"{SETS} weight sets in rotation ({SETS * LAYERS * bytes_layer / 1e9:.2f} GB), larger than L2"},
-            "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": x_host.numel() * 2,
-                    "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": round(ms_e2e / args.steps, 4)},
-            "gpu_launches": launches_per_step * args.steps, "clocks": sampler.stop(m0, m1),
-        }
-        if args.impl == "reference":
-            line["impl"] = "reference"
-            line["cpu_baseline"] = {"value": line["value"], "unit": "GB/s", "cores": os.cpu_count(), "kind": "reference",
-                                    "sample": "the reference has no CPU implementation of its GEMMs: its own CUDA "
-                                              "kernels (gemm_2048x2048.cu, gemm_2048x512.cu) run on the GPU, driven "
-                                              "as Attention::forward drives them"}
-            line["e2e"]["h2d_bytes_per_step"] = 0
-            line["e2e"]["d2h_bytes_per_step"] = 0
-            line["e2e"]["value"] = line["value"]
-        else:
-            line["roofline"] = {"bound": "hbm", "kernel": "qkv_project_kernel" if (not args.qkv_packed) else "qkv_project_packed_kernel", "achieved": round(value / n_rep, 1),
-                                "peak": peak, "unit": "GB/s", "frac": round(value / n_rep / peak, 4),
-                                "peak_source": f"of {peak_kind}", "us_per_launch": round(ms / args.steps * 1e3, 2),
-                                "bytes_per_launch": LAYERS * bytes_layer, "traffic": None}
-            # CPU baseline: the oracle's GEMM restatement (double accumulation, OpenMP) on layer 0
-            from oracle import oracle as orc
-            import time
-            xs = x_host[0].view(torch.int16).numpy().view(np.uint16)
-            ws = [w[0][0].cpu().view(torch.int16).numpy().view(np.uint16) for w in (wq, wk, wv)]
-            t0 = time.perf_counter()
-            reps = 0
-            while time.perf_counter() - t0 < 10.0:
-                outs = [orc.gemm_bf16(xs, w) for w in ws]
-                reps += 1
-            dt = (time.perf_counter() - t0) / reps
-            got = torch.cat([q[0], k[0], v[0]], dim=1).cpu().view(torch.int16).numpy().view(np.uint16)
-            # the last timed step used weight set (i - 1) % SETS; recompute layer 0 with set 0 for the check
-            if (not args.qkv_packed):
-                paged.qkv_project(x_dev, wq[0], wk[0], wv[0], q, k, v, rows, LAYERS)
-            else:
-                paged.qkv_project_packed(x_dev, pq[0], pk[0], pv[0], q, k, v, rows, status, LAYERS)
-            torch.cuda.synchronize()
-            assert (not args.qkv_packed) or int(status.item()) == 0
-            got = torch.cat([q[0], k[0], v[0]], dim=1).cpu().view(torch.int16).numpy().view(np.uint16)
-            want = np.concatenate(outs, axis=1)
-            err = float(np.abs(orc.bf16_to_f32(got) - orc.bf16_to_f32(want)).max())
-            line["cpu_baseline"] = {"value": round(bytes_layer / dt / 1e9, 2), "unit": "GB/s",
-                                    "cores": orc.num_threads(), "kind": "port",
-                                    "sample": f"layer 0 of the workload, {reps} repetitions in {dt * reps:.1f} s",
-                                    "gpu_vs_cpu_max_abs_err": err}
-        print(json.dumps(line), flush=True)
-    barrier()
-    if world > 1 and dist.is_initialized():
-        dist.destroy_process_group()
-
-
-
-def run_qkv_prefill(args):
-    """Q/K/V projections of a 2048-token prompt, 16 layers: x [2048, 2048] times Wq, Wk, Wv, RoPE on Q and
-    K, K/V appended to the paged cache.  Ours: one tcgen05 GEMM launch per layer with RoPE and the append
-    as its epilogue.  Reference arm: its 3 GEMM launches (a device synchronisation after each, as
-    Attention::forward does), its RoPE/transpose kernels and the strided form of its append copies."""
-    import torch
-
-    rank, local_rank, world = dist_env()
+    ms = timed(step, steps)
+    ms_e2e = timed(make_e2e(step), steps)
+    m1 = env.sampler.mark()
+    n_rep = world if grouped else 1
+    value = n_rep * LAYERS * bytes_layer * steps / (ms * 1e-3) / 1e9
+    e2e_value = n_rep * LAYERS * bytes_layer * steps / (ms_e2e * 1e-3) / 1e9
     if rank != 0:
-        return  # independent replicas only
-    torch.cuda.set_device(local_rank)
-    dev = f"cuda:{local_rank}"
-    S, H, NQ, NKV = PREFILL_TOKENS, 2048, Q_HEADS * D, KV_HEADS * D
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+        return None
+    peak, peak_kind = measured_peak()
+    line = {
+        "metric": metric, "value": round(value, 1), "unit": "GB/s", "n_gpus": n_rep,
+        "steps": steps, "warmup": warmup, "ms_per_step": round(ms / steps, 4),
+        "us_per_layer": round(ms / steps * 1e3 / LAYERS, 2),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": wname, "hidden": H, "q_cols": NQ, "kv_cols": NKV, "rows": rows, "layers": LAYERS,
+                   "parallelism": "1 GPU" if n_rep == 1 else f"{world} independent replicas",
+                   "l2": f"{SETS} weight sets in rotation ({SETS * LAYERS * bytes_layer / 1e9:.2f} GB), larger than L2"},
+        "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": x_host.numel() * 2,
+                "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": round(ms_e2e / steps, 4)},
+        "gpu_launches": (ref_launches if ref_arm else 1) * steps, "clocks": env.sampler.summary(m0, m1),
+    }
+    if ref_arm:
+        line["impl"] = "reference"
+        line["cpu_baseline"] = {"value": line["value"], "unit": "GB/s", "cores": os.cpu_count(), "kind": "reference",
+                                "sample": "the reference has no CPU implementation of its GEMMs: its own CUDA "
+                                          "kernels run on the GPU, driven as Attention::forward drives them"}
+        line["e2e"].update({"h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0, "value": line["value"]})
+        return line
+    line["roofline"] = {"bound": "hbm", "kernel": kernel, "achieved": round(value / n_rep, 1),
+                        "peak": peak, "unit": "GB/s", "frac": round(value / n_rep / peak, 4),
+                        "peak_source": f"of {peak_kind}", "us_per_launch": round(ms / steps * 1e3, 2),
+                        "bytes_per_launch": LAYERS * bytes_layer, "traffic": None}
+    # check + CPU baseline: the oracle's GEMM restatement (double accumulation, OpenMP) on layer 0 with set 0
+    ours_step(0)
+    torch.cuda.synchronize()
+    if which == "qkv" and args.qkv_packed:
+        assert int(status.item()) == 0
+    xs = _u16(x_host[0])
+    t0 = time.perf_counter()
+    reps = 0
+    budget = 2.0 if sub else 10.0
+    while True:
+        if which == "qkv":
+            outs = [orc.gemm_bf16(xs, _u16(w[0][0])) for w in (wq, wk, wv)]
+        else:
+            outs = [orc.gemm_bf16(xs, _u16(wo[0][0]))]
+        reps += 1
+        if time.perf_counter() - t0 >= budget:
+            break
+    dt = (time.perf_counter() - t0) / reps
+    if which == "qkv":
+        got = np.concatenate([_u16(q[0]), _u16(k[0]), _u16(v[0])], axis=1)
+        want = np.concatenate(outs, axis=1)
+    else:
+        got = _u16(o[0])
+        want = orc.f32_to_bf16(orc.bf16_to_f32(_u16(res[0])) + orc.bf16_to_f32(outs[0]))
+    err = float(np.abs(orc.bf16_to_f32(got) - orc.bf16_to_f32(want)).max())
+    line["cpu_baseline"] = {"value": round(bytes_layer / dt / 1e9, 2), "unit": "GB/s",
+                            "cores": orc.num_threads(), "kind": "port",
+                            "sample": f"layer 0 of the workload, {reps} repetitions in {dt * reps:.1f} s",
+                            "gpu_vs_cpu_max_abs_err": err}
+    if sub and ref is not None:
+        rstep = make_step(ref_step)
+        rstep()
+        rn = 2
+        rms = local_timed(torch, rstep, rn)
+        line["reference"] = {"value": round(LAYERS * bytes_layer * rn / (rms * 1e-3) / 1e9, 2), "unit": "GB/s",
+                             "us_per_layer": round(rms / rn * 1e3 / LAYERS, 2),
+                             "how": "the reference's GEMM kernels with its device synchronisation after each, same weights"}
+    return line
+
+
+def run_qkv_prefill(env: Env, args, sub: bool = False):
+    """Q/K/V projections of a 2048-token prompt, 16 layers: x [2048, 2048] times Wq, Wk, Wv, RoPE on Q
+    and K, K/V appended to the paged cache.  Ours: one tcgen05 GEMM launch per layer with RoPE and the
+    append as its epilogue.  Reference arm: its 3 GEMM launches (a device synchronisation after each,
+    as Attention::forward does), its RoPE/transpose kernels and the strided form of its append copies."""
+    torch = env.torch
+    if env.rank != 0:
+        return None  # independent replicas only
+    from oracle import oracle as orc
+    dev = env.dev
+    S, H, NQ, NKV = PREFILL_TOKENS, HIDDEN, Q_HEADS * D, KV_HEADS * D
+    steps = max(3, args.steps // 5) if sub else args.steps
+    warmup = 3 if sub else args.warmup
+    ref_arm = args.impl == "reference" and not sub
     gen = torch.Generator(device=dev)
     gen.manual_seed(123)
     x = torch.randn(LAYERS, S, H, generator=gen, device=dev).to(torch.bfloat16)
@@ -953,15 +1063,13 @@ def run_qkv_prefill(args):
     q_host = torch.zeros(S, NQ, dtype=torch.bfloat16).pin_memory()
     burst, sustained, kind = measured_tflops()
     flops_layer = 2.0 * S * H * (NQ + 2 * NKV)
+    ref = orc.ref() if orc.ref_available() else None
+    if ref_arm and ref is None:
+        return {"impl": "reference", "unavailable": "oracle/_ref/libref.so was not built"}
+    cos_h, sin_h = orc.build_rope_tables(S)
+    cos, sin = torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev)
 
-    if args.impl == "reference":
-        from oracle import oracle as orc
-        if not orc.ref_available():
-            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libref.so was not built"}))
-            return
-        ref = orc.ref()
-        cos_h, sin_h = orc.build_rope_tables(S)
-        cos, sin = torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev)
+    if ref is not None:
         ql = torch.empty(S, NQ, dtype=torch.bfloat16, device=dev)
         kl = torch.empty(S, NKV, dtype=torch.bfloat16, device=dev)
         vl = torch.empty(S, NKV, dtype=torch.bfloat16, device=dev)
@@ -971,64 +1079,55 @@ def run_qkv_prefill(args):
         kc = torch.zeros(LAYERS, KV_HEADS, S, D, dtype=torch.bfloat16, device=dev)
         vc = torch.zeros_like(kc)
 
-        def step():
-            for l in range(LAYERS):
-                for w, o, n in ((wq, ql, NQ), (wk, kl, NKV), (wv, vl, NKV)):
-                    ref.ref_gemm(x[l].data_ptr(), w[l].data_ptr(), o.data_ptr(), S, n, H)
-                    torch.cuda.synchronize()
-                ref.ref_rope_qkv(ql.data_ptr(), qf.data_ptr(), kl.data_ptr(), kf.data_ptr(), vl.data_ptr(),
-                                 vf.data_ptr(), cos.data_ptr(), sin.data_ptr(), S, 0)
-                ref.ref_append_strided(kc[l].data_ptr(), vc[l].data_ptr(), kf.data_ptr(), vf.data_ptr(), S, 0, S, None)
-        launches_per_step = LAYERS * 8
-    else:
+    def ref_step():
+        for l in range(LAYERS):
+            for w, o, n in ((wq, ql, NQ), (wk, kl, NKV), (wv, vl, NKV)):
+                ref.ref_gemm(x[l].data_ptr(), w[l].data_ptr(), o.data_ptr(), S, n, H)
+                torch.cuda.synchronize()
+            ref.ref_rope_qkv(ql.data_ptr(), qf.data_ptr(), kl.data_ptr(), kf.data_ptr(), vl.data_ptr(),
+                             vf.data_ptr(), cos.data_ptr(), sin.data_ptr(), S, 0)
+            ref.ref_append_strided(kc[l].data_ptr(), vc[l].data_ptr(), kf.data_ptr(), vf.data_ptr(), S, 0, S, None)
+
+    pool = None
+    if not ref_arm:
         from llama_transformer_runtime_b200 import paged
         nb = (S + BLOCK - 1) // BLOCK
         num_blocks = nb + nb // 4 + 8
-        pool = paged.KVPool(LAYERS, num_blocks, KV_HEADS, 1, nb + 1, device=local_rank)
+        pool = paged.KVPool(LAYERS, num_blocks, KV_HEADS, 1, nb + 1, device=env.local_rank)
         pool.set_free_order(np.random.default_rng(5).permutation(num_blocks))
         seq = pool.create_seq()
         pool.reserve(seq, S)
         pool.reserve_rows(S, H)
         pool.batch_set([seq], [S])
-        cos_h, sin_h = paged.build_rope_tables(S)
-        cos, sin = torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev)
-
         # weights are repacked once, at load time, into the tile image the GEMM bulk-copies
         pq, pk, pv = (paged.pack_projection_weights(w) for w in (wq, wk, wv))
         torch.cuda.synchronize()
 
-        def step():
-            # the same prompt positions are rewritten every step (the table is fixed)
-            for l in range(LAYERS):
-                pool.qkv_project_append(l, x[l], pq[l], pk[l], pv[l], cos, sin, q_rot[l], H)
-        launches_per_step = LAYERS
+    def ours_step():
+        # the same prompt positions are rewritten every step (the table is fixed)
+        for l in range(LAYERS):
+            pool.qkv_project_append(l, x[l], pq[l], pk[l], pv[l], cos, sin, q_rot[l], H)
+
+    step = ref_step if ref_arm else ours_step
+    launches_per_step = LAYERS * 8 if ref_arm else LAYERS * 2
 
     def e2e_step():
         x.copy_(x_host, non_blocking=True)
         step()
-        if args.impl != "reference":
+        if not ref_arm:
             q_host.copy_(q_rot[LAYERS - 1], non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    def timed(fn, n):
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(n):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1)
-
-    m0 = sampler.mark()
-    for _ in range(args.warmup):
+    m0 = env.sampler.mark()
+    for _ in range(warmup):
         step()
-    ms = timed(step, args.steps) / args.steps
-    ms_e2e = timed(e2e_step, args.steps) / args.steps
+    ms = local_timed(torch, step, steps) / steps
+    ms_e2e = local_timed(torch, e2e_step, steps) / steps
+    m1 = env.sampler.mark()
     value = flops_layer * LAYERS / (ms * 1e-3) / 1e12
     line = {
         "metric": "qkv_project_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": 1,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
+        "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4),
         "us_per_layer": round(ms * 1e3 / LAYERS, 2), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"qkv_projection_rope_append_{S}tokens_x{LAYERS}layers", "tokens": S, "hidden": H,
@@ -1036,74 +1135,63 @@ def run_qkv_prefill(args):
                    "l2": "per-layer inputs and weights are distinct tensors (20.6 MB per layer, 330 MB per step)"},
         "e2e": {"value": round(flops_layer * LAYERS / (ms_e2e * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
                 "h2d_bytes_per_step": x_host.numel() * 2,
-                "d2h_bytes_per_step": 0 if args.impl == "reference" else q_host.numel() * 2,
+                "d2h_bytes_per_step": 0 if ref_arm else q_host.numel() * 2,
                 "ms_per_step": round(ms_e2e, 4)},
-        "gpu_launches": launches_per_step * args.steps,
+        "gpu_launches": launches_per_step * steps, "clocks": env.sampler.summary(m0, m1),
     }
-    if args.impl == "reference":
+    if ref_arm:
         line["impl"] = "reference"
         line["cpu_baseline"] = {"value": line["value"], "unit": "TFLOP/s", "cores": 0, "kind": "reference",
                                 "sample": "whole workload on the GPU: the reference has no CPU implementation of its GEMMs"}
-        line["e2e"]["h2d_bytes_per_step"] = 0
-        line["e2e"]["value"] = line["value"]
-    else:
-        line["roofline"] = {"bound": "tensor", "kernel": "qkv_gemm_kernel", "achieved": round(value, 2), "peak": burst,
-                            "unit": "TFLOP/s", "frac": round(value / burst, 4),
-                            "peak_source": f"of {kind} (cuBLAS bf16 burst)", "us_per_launch": round(ms * 1e3 / LAYERS, 2),
-                            "flops_per_launch": flops_layer, "traffic": None}
-        pool.check()
-        # CPU baseline and check: the oracle's GEMM on the first 64 rows of layer 0, q columns
-        from oracle import oracle as orc
-        import time
-        rows = 64
-        xs = x_host[0, :rows].contiguous().view(torch.int16).numpy().view(np.uint16)
-        ws = wq[0].cpu().view(torch.int16).numpy().view(np.uint16)
-        t0 = time.perf_counter()
-        lin = orc.gemm_bf16(xs, ws)
-        dt = time.perf_counter() - t0
-        want = orc.rope(lin.reshape(rows, Q_HEADS, D), cos_h, sin_h, 0, 1, out_token_major=True).reshape(rows, NQ)
-        got = q_rot[0, :rows].cpu().view(torch.int16).numpy().view(np.uint16)
-        err = float(np.abs(orc.bf16_to_f32(got) - orc.bf16_to_f32(want)).max())
-        line["cpu_baseline"] = {"value": round(2.0 * rows * H * NQ / dt / 1e12, 5), "unit": "TFLOP/s",
-                                "cores": orc.num_threads(), "kind": "port",
-                                "sample": f"{rows} rows x {NQ} columns of layer 0 (double accumulation), {dt:.2f} s",
-                                "gpu_vs_cpu_max_abs_err": err}
-        pool.close()
-    line["clocks"] = sampler.stop(m0, None)
-    print(json.dumps(line), flush=True)
+        line["e2e"].update({"h2d_bytes_per_step": 0, "value": line["value"]})
+        return line
+    line["roofline"] = {"bound": "tensor", "kernel": "qkv_gemm_kernel", "achieved": round(value, 2), "peak": burst,
+                        "unit": "TFLOP/s", "frac": round(value / burst, 4),
+                        "peak_source": f"of {kind} (cuBLAS bf16 burst)", "us_per_launch": round(ms * 1e3 / LAYERS, 2),
+                        "flops_per_launch": flops_layer, "traffic": None}
+    pool.check()
+    # CPU baseline and check: the oracle's GEMM on the first 64 rows of layer 0, q columns
+    rows = 64
+    xs = _u16(x_host[0, :rows])
+    ws = _u16(wq[0])
+    t0 = time.perf_counter()
+    lin = orc.gemm_bf16(xs, ws)
+    dt = time.perf_counter() - t0
+    want = orc.rope(lin.reshape(rows, Q_HEADS, D), cos_h, sin_h, 0, 1, out_token_major=True).reshape(rows, NQ)
+    got = _u16(q_rot[0, :rows])
+    err = float(np.abs(orc.bf16_to_f32(got) - orc.bf16_to_f32(want)).max())
+    line["cpu_baseline"] = {"value": round(2.0 * rows * H * NQ / dt / 1e12, 5), "unit": "TFLOP/s",
+                            "cores": orc.num_threads(), "kind": "port",
+                            "sample": f"{rows} rows x {NQ} columns of layer 0 (double accumulation), {dt:.2f} s",
+                            "gpu_vs_cpu_max_abs_err": err}
+    if sub and ref is not None:
+        ref_step()
+        rms = local_timed(torch, ref_step, 1)
+        line["reference"] = {"value": round(flops_layer * LAYERS / (rms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+                             "us_per_layer": round(rms * 1e3 / LAYERS, 2),
+                             "how": "the reference's 3 GEMM launches + synchronisations, RoPE kernels and strided append copies"}
+    pool.close()
+    return line
 
 
-def prefill_flops(S: int) -> float:
-    """Causal-useful flops of one layer: 4 * Hq * D * S (S + 1) / 2."""
-    return 4.0 * Q_HEADS * D * S * (S + 1) / 2.0
-
-
-def measured_tflops():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(path):
-        try:
-            j = json.load(open(path))
-            return float(j["bf16_tflops"]), float(j.get("bf16_tflops_sustained", j["bf16_tflops"])), "measured"
-        except Exception:
-            pass
-    return 1590.0, 1400.0, "fallback"
-
-
-def run_prefill(args):
-    """One step = one 2048-token prompt through 16 layers: per layer fused RoPE +
-    paged append of the prompt's K/V, then causal GQA attention over the cache,
-    output [2048, 2048] bf16.  Both arms: ours (pa_append + pa_prefill) and the
-    reference's kernels (rope kernels + append copies + flash kernel + layout)."""
-    import torch
-
-    rank, local_rank, world = dist_env()
-    if rank != 0:
-        return  # independent replicas only: prefill is not sharded here
-    torch.cuda.set_device(local_rank)
-    dev = f"cuda:{local_rank}"
+# =============================================================================
+# prefill attention (2048 tokens x 16 layers, causal, batch 1) and the append kernel alone
+# =============================================================================
+def run_prefill(env: Env, args, sub: bool = False, append_only: bool = False):
+    """One step = one 2048-token prompt through 16 layers: per layer fused RoPE + paged append of the
+    prompt's K/V, then causal GQA attention over the cache, output [2048, 2048] bf16.  Both arms: ours
+    (pa_append + pa_prefill) and the reference's kernels (rope kernels + append copies + flash kernel
+    + layout).  append_only: only the RoPE + append part, an HBM stream of
+    tokens x (4096 + 2 x 1024 read, 4096 + 2 x 1024 written) bytes per layer."""
+    torch = env.torch
+    if env.rank != 0:
+        return None  # independent replicas only: prefill is not sharded here
+    from oracle import oracle as orc
+    dev = env.dev
     S = PREFILL_TOKENS
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    steps = max(3, args.steps // 5) if sub else args.steps
+    warmup = 3 if sub else args.warmup
+    ref_arm = args.impl == "reference" and not sub
     gen = torch.Generator(device=dev)
     gen.manual_seed(99)
     # per-layer inputs differ so that no layer finds its operands in L2 from the previous one
@@ -1114,15 +1202,13 @@ def run_prefill(args):
     q_host, k_host, v_host = q_in.cpu().pin_memory(), k_in.cpu().pin_memory(), v_in.cpu().pin_memory()
     out_host = torch.zeros(S, Q_HEADS * D, dtype=torch.bfloat16).pin_memory()
     burst, sustained, kind = measured_tflops()
+    ref = orc.ref() if orc.ref_available() else None
+    if ref_arm and ref is None:
+        return {"impl": "reference", "unavailable": "oracle/_ref/libref.so was not built"}
+    cos_h, sin_h = orc.build_rope_tables(S)
+    cos, sin = torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev)
 
-    if args.impl == "reference":
-        from oracle import oracle as orc
-        if not orc.ref_available():
-            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libref.so was not built"}))
-            return
-        ref = orc.ref()
-        cos_h, sin_h = orc.build_rope_tables(S)
-        cos, sin = torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev)
+    if ref is not None:
         kc = torch.zeros(LAYERS, KV_HEADS, S, D, dtype=torch.bfloat16, device=dev)
         vc = torch.zeros_like(kc)
         qf = torch.empty(Q_HEADS, S, D, dtype=torch.bfloat16, device=dev)
@@ -1130,109 +1216,148 @@ def run_prefill(args):
         vf = torch.empty_like(kf)
         of = torch.empty(Q_HEADS, S, D, dtype=torch.bfloat16, device=dev)
 
-        def step():
-            for layer in range(LAYERS):
-                ref.ref_rope_qkv(q_in[layer].data_ptr(), qf.data_ptr(), k_in[layer].data_ptr(), kf.data_ptr(),
-                                 v_in[layer].data_ptr(), vf.data_ptr(), cos.data_ptr(), sin.data_ptr(), S, 0)
-                # the reference's own append is 2*8*2048 copies of 128 bytes per layer; the
-                # strided form moves the same bytes in 16 calls (kernel-to-kernel comparison)
-                if args.ref_literal_append:
-                    ref.ref_append_memcpy_loop(kc[layer].data_ptr(), vc[layer].data_ptr(), kf.data_ptr(),
-                                               vf.data_ptr(), S, 0, S)
-                else:
-                    ref.ref_append_strided(kc[layer].data_ptr(), vc[layer].data_ptr(), kf.data_ptr(),
-                                           vf.data_ptr(), S, 0, S, None)
-                ref.ref_flash_attention(qf.data_ptr(), kc[layer].data_ptr(), vc[layer].data_ptr(), of.data_ptr(),
-                                        None, 1, Q_HEADS, KV_HEADS, S, S, S, 0.125, 1, None)
-                ref.ref_flash_output_layout(of.data_ptr(), out[layer].data_ptr(), S)
-        launches_per_step = LAYERS * 5
-        kernel_name = "flash_attention_fat_kernel (reference)"
-    else:
+    def ref_step():
+        for layer in range(LAYERS):
+            ref.ref_rope_qkv(q_in[layer].data_ptr(), qf.data_ptr(), k_in[layer].data_ptr(), kf.data_ptr(),
+                             v_in[layer].data_ptr(), vf.data_ptr(), cos.data_ptr(), sin.data_ptr(), S, 0)
+            # the reference's own append is 2*8*2048 copies of 128 bytes per layer; the
+            # strided form moves the same bytes in 16 calls (kernel-to-kernel comparison)
+            if args.ref_literal_append:
+                ref.ref_append_memcpy_loop(kc[layer].data_ptr(), vc[layer].data_ptr(), kf.data_ptr(),
+                                           vf.data_ptr(), S, 0, S)
+            else:
+                ref.ref_append_strided(kc[layer].data_ptr(), vc[layer].data_ptr(), kf.data_ptr(),
+                                       vf.data_ptr(), S, 0, S, None)
+            if append_only:
+                continue
+            ref.ref_flash_attention(qf.data_ptr(), kc[layer].data_ptr(), vc[layer].data_ptr(), of.data_ptr(),
+                                    None, 1, Q_HEADS, KV_HEADS, S, S, S, 0.125, 1, None)
+            ref.ref_flash_output_layout(of.data_ptr(), out[layer].data_ptr(), S)
+
+    pool = None
+    if not ref_arm:
         from llama_transformer_runtime_b200 import paged
         nb = (S + BLOCK - 1) // BLOCK
         num_blocks = nb + nb // 4 + 8
-        pool = paged.KVPool(LAYERS, num_blocks, KV_HEADS, 1, nb + 1, device=local_rank)
+        pool = paged.KVPool(LAYERS, num_blocks, KV_HEADS, 1, nb + 1, device=env.local_rank)
         pool.set_free_order(np.random.default_rng(5).permutation(num_blocks))
         seq = pool.create_seq()
         pool.reserve(seq, S)
         pool.batch_set([seq], [S])
-        cos_h, sin_h = paged.build_rope_tables(S)
-        cos, sin = torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev)
         q_rot = torch.empty_like(q_in)
 
-        def step():
-            # the same prompt positions are rewritten every step (the table is fixed)
-            for layer in range(LAYERS):
-                pool.append(layer, q_in[layer], k_in[layer], v_in[layer], cos, sin, q_rot[layer])
+    def ours_step():
+        # the same prompt positions are rewritten every step (the table is fixed)
+        for layer in range(LAYERS):
+            pool.append(layer, q_in[layer], k_in[layer], v_in[layer], cos, sin, q_rot[layer])
+            if not append_only:
                 pool.prefill(layer, q_rot[layer], out[layer], None, 0.125)
-        launches_per_step = LAYERS * 2
-        kernel_name = "prefill_kernel"
+
+    step = ref_step if ref_arm else ours_step
+    if append_only:
+        launches_per_step = LAYERS * 19 if ref_arm else LAYERS
+    else:
+        launches_per_step = LAYERS * 5 if ref_arm else LAYERS * 2
 
     def e2e_step():
         q_in.copy_(q_host, non_blocking=True)
         k_in.copy_(k_host, non_blocking=True)
         v_in.copy_(v_host, non_blocking=True)
         step()
-        out_host.copy_(out[LAYERS - 1], non_blocking=True)  # the last layer's attention output
+        if append_only:
+            if not ref_arm:
+                out_host.copy_(q_rot[LAYERS - 1].view(S, Q_HEADS * D), non_blocking=True)
+        else:
+            out_host.copy_(out[LAYERS - 1], non_blocking=True)  # the last layer's attention output
         torch.cuda.current_stream().synchronize()
 
-    def timed(fn, n):
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(n):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1)
-
-    m0 = sampler.mark()
-    for _ in range(args.warmup):
+    m0 = env.sampler.mark()
+    for _ in range(warmup):
         step()
-    ms = timed(step, args.steps) / args.steps
-    ms_e2e = timed(e2e_step, args.steps) / args.steps
-    flops = prefill_flops(S) * LAYERS
-    value = flops / (ms * 1e-3) / 1e12
+    ms = local_timed(torch, step, steps) / steps
+    ms_e2e = local_timed(torch, e2e_step, steps) / steps
+    m1 = env.sampler.mark()
+    append_bytes = S * ((Q_HEADS + 2 * KV_HEADS) * D * 2) * 2  # read q, k, v rows; write rotated q and the cache tiles
+    if append_only:
+        work, unit, metric = append_bytes * LAYERS / 1e9, "GB/s", "rope_append_hbm_gbs"
+        wname = f"rope_append_{S}tokens_x{LAYERS}layers_batch1"
+    else:
+        work, unit, metric = prefill_flops(S) * LAYERS / 1e12, "TFLOP/s", "prefill_attn_tflops"
+        wname = f"prefill_{S}tokens_x{LAYERS}layers_batch1_causal"
+    value = work / (ms * 1e-3)
     line = {
-        "metric": "prefill_attn_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": 1,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
+        "metric": metric, "value": round(value, 2), "unit": unit, "n_gpus": 1,
+        "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4),
         "us_per_layer": round(ms * 1e3 / LAYERS, 2), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"prefill_{S}tokens_x{LAYERS}layers_batch1_causal", "tokens": S, "layers": LAYERS,
+        "config": {"workload": wname, "tokens": S, "layers": LAYERS,
                    "q_heads": Q_HEADS, "kv_heads": KV_HEADS, "head_dim": D,
-                   "flops": "causal-useful 4*Hq*D*S(S+1)/2 per layer",
-                   "dense_count_tflops": round(4.0 * Q_HEADS * D * S * S * LAYERS / (ms * 1e-3) / 1e12, 2),
                    "l2": "per-layer inputs are distinct tensors (24 MiB per layer, 384 MiB per step)"},
-        "e2e": {"value": round(flops / (ms_e2e * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+        "e2e": {"value": round(work / (ms_e2e * 1e-3), 2), "unit": unit,
                 "h2d_bytes_per_step": (q_host.numel() + k_host.numel() + v_host.numel()) * 2,
                 "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": round(ms_e2e, 4)},
-        "gpu_launches": launches_per_step * args.steps,
+        "gpu_launches": launches_per_step * steps, "clocks": env.sampler.summary(m0, m1),
     }
-    if args.impl == "reference":
-        line["impl"] = "reference"
-        line["cpu_baseline"] = {"value": line["value"], "unit": "TFLOP/s", "cores": 0, "kind": "reference",
-                                "sample": "whole workload on the GPU: the reference has no CPU implementation of this path"}
+    if append_only:
+        line["config"]["bytes"] = "tokens x (4096 + 2 x 1024) read + the same written, per layer"
     else:
-        # dominant kernel alone
+        line["config"]["flops"] = "causal-useful 4*Hq*D*S(S+1)/2 per layer"
+        line["config"]["dense_count_tflops"] = round(4.0 * Q_HEADS * D * S * S * LAYERS / (ms * 1e-3) / 1e12, 2)
+    if ref_arm:
+        line["impl"] = "reference"
+        line["cpu_baseline"] = {"value": line["value"], "unit": unit, "cores": 0, "kind": "reference",
+                                "sample": "whole workload on the GPU: the reference has no CPU implementation of this path"}
+        return line
+    # dominant kernel alone
+    if append_only:
+        def kern_only():
+            for layer in range(LAYERS):
+                pool.append(layer, q_in[layer], k_in[layer], v_in[layer], cos, sin, q_rot[layer])
+        kern_only()
+        reps = max(3, steps)
+        ms_k = local_timed(torch, kern_only, reps) / (reps * LAYERS)
+        peak, pk = measured_peak()
+        achieved = append_bytes / (ms_k * 1e-3) / 1e9
+        line["roofline"] = {"bound": "hbm", "kernel": "append_kernel", "achieved": round(achieved, 1), "peak": peak,
+                            "unit": "GB/s", "frac": round(achieved / peak, 4), "peak_source": f"of {pk}",
+                            "us_per_launch": round(ms_k * 1e3, 2), "bytes_per_launch": append_bytes,
+                            "traffic": NCU_APPEND_TRAFFIC,
+                            "traffic_note": "ncu capture of one 2048-token append_kernel launch (profiles/)"}
+        # check: rotated Q rows of layer 0 against the oracle, bit for bit (first 64 tokens); the CPU
+        # baseline is the oracle's RoPE + placement of those tokens
+        t0 = time.perf_counter()
+        want = orc.rope(_u16(q_in[0, :64]), cos_h, sin_h, 0, 1, out_token_major=True)
+        orc.rope(_u16(k_in[0, :64]), cos_h, sin_h, 0, 1)
+        dt = time.perf_counter() - t0
+        line["checks"] = {"rotated_q_bit_exact_vs_oracle": bool(np.array_equal(_u16(q_rot[0, :64]), want))}
+        line["cpu_baseline"] = {"value": round(64 * ((Q_HEADS + KV_HEADS) * D * 2) * 2 / dt / 1e9, 4), "unit": "GB/s",
+                                "cores": 1, "kind": "port", "sample": "RoPE of 64 tokens' Q and K rows of layer 0 (scalar C loop)"}
+    else:
         def attn_only():
             for layer in range(LAYERS):
                 pool.prefill(layer, q_rot[layer], out[layer], None, 0.125)
         attn_only()
-        reps = max(3, args.steps)
-        ms_k = timed(attn_only, reps) / (reps * LAYERS)
+        reps = max(3, steps)
+        ms_k = local_timed(torch, attn_only, reps) / (reps * LAYERS)
         achieved = prefill_flops(S) / (ms_k * 1e-3) / 1e12
-        line["roofline"] = {"bound": "tensor", "kernel": kernel_name, "achieved": round(achieved, 2),
+        line["roofline"] = {"bound": "tensor", "kernel": "prefill_kernel", "achieved": round(achieved, 2),
                             "peak": burst, "unit": "TFLOP/s", "frac": round(achieved / burst, 4),
                             "peak_source": f"of {kind} (cuBLAS bf16 burst)", "us_per_launch": round(ms_k * 1e3, 2),
                             "flops_per_launch": prefill_flops(S), "traffic": None}
-        pool.check()
-        line["cpu_baseline"] = prefill_cpu_baseline(q_rot, out, pool, seq, S)
-        pool.close()
-    line["clocks"] = sampler.stop(m0, None)
-    print(json.dumps(line), flush=True)
+        line["cpu_baseline"] = prefill_cpu_baseline(q_rot, out, pool, seq, S, budget_s=(2.0 if sub else 10.0))
+    pool.check()
+    if sub and ref is not None:
+        ref_step()
+        rms = local_timed(torch, ref_step, 2) / 2
+        line["reference"] = {"value": round(work / (rms * 1e-3), 2), "unit": unit,
+                             "us_per_layer": round(rms * 1e3 / LAYERS, 2),
+                             "how": "the reference's RoPE kernels + strided append copies" +
+                                    ("" if append_only else " + attention kernel + layout kernel")}
+    pool.close()
+    return line
 
 
-def prefill_cpu_baseline(q_rot, out, pool, seq, S):
+def prefill_cpu_baseline(q_rot, out, pool, seq, S, budget_s=10.0):
     """fp32 CPU oracle on a bounded sample: the first 512 query rows of layer 0
     (all 32 heads) against their causal keys; also checks the GPU output."""
     import torch
@@ -1244,36 +1369,71 @@ def prefill_cpu_baseline(q_rot, out, pool, seq, S):
     v = torch.zeros_like(k)
     pool.gather_kv(0, seq, k, v, S)
     torch.cuda.synchronize()
-    to_u16 = lambda t: t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
-    qh = to_u16(q_rot[0][:n].permute(1, 0, 2))  # [32, n, 64]
-    kh, vh = to_u16(k[:, :n]), to_u16(v[:, :n])
+    qh = _u16(q_rot[0][:n].permute(1, 0, 2))  # [32, n, 64]
+    kh, vh = _u16(k[:, :n]), _u16(v[:, :n])
     t0 = time.perf_counter()
     O, _ = orc.attention(qh, kh, vh, n, causal=True)
     reps = 1
-    while time.perf_counter() - t0 < 10.0 and reps < 200:
+    while time.perf_counter() - t0 < budget_s and reps < 200:
         orc.attention(qh, kh, vh, n, causal=True)
         reps += 1
     total = time.perf_counter() - t0
-    got = orc.bf16_to_f32(to_u16(out[0][:n]))
-    err = float(np.max(np.abs(got - orc.output_layout(O))))
+    got = orc.bf16_to_f32(_u16(out[0][:n]))
+    want = orc.output_layout(O)
+    err = float(np.max(np.abs(got - want)))
     return {"value": round(prefill_flops(n) * reps / total / 1e12, 4), "unit": "TFLOP/s", "cores": orc.num_threads(),
             "kind": "port", "sample": f"first {n} query rows of layer 0, {reps} passes of the fp32 CPU oracle",
-            "gpu_vs_cpu_max_abs_err": err}
+            "gpu_vs_cpu_max_abs_err": err, "gpu_vs_cpu_max_row_rel_err": row_rel_err(got, want)}
+
+
+# =============================================================================
+def decode4k_sub(env: Env, args):
+    line = run_decode(env, args, "decode4k", sub=True)
+    r = reference_decode(env, "decode4k", 3, 2, with_e2e=False)
+    if line is not None and r is not None:
+        line["reference"] = {"value": round(r["value"], 2), "unit": "GB/s",
+                             "us_per_token_per_layer": round(r["ms_per_step"] * 1e3 / LAYERS, 2),
+                             "how": "the reference's RoPE kernels, 16 append copies, attention kernel at q_seq_len 1 "
+                                    "and layout kernel per layer, as Attention::forward drives them"}
+    return line
+
+
+SUB_BLOCKS = {
+    "decode4k": decode4k_sub,
+    "prefill": lambda env, a: run_prefill(env, a, sub=True),
+    "append": lambda env, a: run_prefill(env, a, sub=True, append_only=True),
+    "out_project": lambda env, a: run_qkv(env, a, sub=True, which="out"),
+    "qkv_decode": lambda env, a: run_qkv(env, a, sub=True, which="qkv"),
+    "qkv_prefill": lambda env, a: run_qkv_prefill(env, a, sub=True),
+}
+
+
+def compact(line):
+    """A sub-block of the default line: the full line minus the keys the outer line already carries."""
+    if line is None:
+        return None
+    drop = {"higher_is_better", "vs_baseline", "dtype", "data", "n_gpus", "warmup"}
+    return {k: v for k, v in line.items() if k not in drop}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--repeats", type=int, default=15, help="decode: timed blocks of --steps steps; the median is reported")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode128k", choices=sorted(WORKLOADS) + ["prefill2k", "batch64", "qkv_decode", "qkv_prefill"])
+    ap.add_argument("--workload", default="decode128k",
+                    choices=sorted(WORKLOADS) + ["prefill2k", "append2k", "batch64", "qkv_decode", "out_project", "qkv_prefill"])
+    ap.add_argument("--no-sub", action="store_true", help="default workload: skip the sub-blocks")
+    ap.add_argument("--sub", default="", help="default workload: comma-separated sub-blocks to run (default: all)")
     ap.add_argument("--seqs", type=int, default=64, help="batch64: number of sequences")
     ap.add_argument("--layers", type=int, default=16, help="fewer layers make a small case for profiling")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="N>1: partials pushed by the decode epilogue over NVLink (fused) or NCCL all-gather")
     ap.add_argument("--chunk-blocks", type=int, default=0, help="decode: blocks per split-KV chunk (0 = planner)")
-    ap.add_argument("--combiners", type=int, default=0, help="decode: combining CTAs per (sequence, head) in the one-launch step (0 = planner)")
+    ap.add_argument("--combiners", type=int, default=0,
+                    help="decode: combining CTAs per (sequence, head) in the one-launch step (0 = planner)")
     ap.add_argument("--decode-shape", default="", help="decode: WARPSxSTAGES, e.g. 8x4 (empty = planner)")
     ap.add_argument("--qkv-packed", action="store_true",
                     help="qkv_decode: the kernel that reads the packed weight tiles (shared with the prefill GEMM) "
@@ -1284,18 +1444,49 @@ def main():
     args.warmup = max(args.warmup, 3)
     global LAYERS
     LAYERS = args.layers
-    if args.workload == "qkv_decode":
-        run_qkv(args)
+    rank, _, world = dist_env()
+    if args.impl == "reference" and rank != 0:
+        return  # the reference is single-GPU: rank 0 alone runs it
+    sharded = args.workload in WORKLOADS or args.workload in ("batch64", "qkv_decode", "out_project")
+    env = Env(want_group=(args.impl == "ours" and sharded))
+    line = None
+    if args.workload in WORKLOADS:
+        if args.impl == "reference":
+            line = run_reference(env, args, args.workload)
+        else:
+            line = run_decode(env, args, args.workload)
+            default = args.workload == "decode128k" and not args.no_sub and LAYERS == 16
+            if default and world == 1:
+                names = [n for n in (args.sub.split(",") if args.sub else SUB_BLOCKS) if n in SUB_BLOCKS]
+                line["sub"] = {}
+                for n in names:
+                    try:
+                        line["sub"][n] = compact(SUB_BLOCKS[n](env, args))
+                    except Exception as exc:  # a failing sub-block must not lose the main line
+                        line["sub"][n] = {"error": f"{type(exc).__name__}: {exc}"}
+            elif default and world > 1:
+                try:
+                    b = run_batch(env, args, sub=True)
+                except Exception as exc:
+                    b = {"error": f"{type(exc).__name__}: {exc}"}
+                if rank == 0:
+                    line["batch64"] = compact(b)
+    elif args.workload == "qkv_decode":
+        line = run_qkv(env, args, which="qkv")
+    elif args.workload == "out_project":
+        line = run_qkv(env, args, which="out")
     elif args.workload == "qkv_prefill":
-        run_qkv_prefill(args)
+        line = run_qkv_prefill(env, args)
     elif args.workload == "prefill2k":
-        run_prefill(args)
+        line = run_prefill(env, args)
+    elif args.workload == "append2k":
+        line = run_prefill(env, args, append_only=True)
     elif args.workload == "batch64":
-        run_batch(args)
-    elif args.impl == "reference":
-        run_reference(args)
-    else:
-        run_ours(args)
+        line = run_batch(env, args)
+    if rank == 0 and line is not None:
+        print(json.dumps(line), flush=True)
+    env.sampler.stop()
+    env.close()
 
 
 if __name__ == "__main__":

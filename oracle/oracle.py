@@ -262,5 +262,9 @@ def ref():
         r.ref_append_strided.restype = i
         r.ref_gemm.argtypes = [vp, vp, vp, i, i, i]
         r.ref_gemm.restype = i
+        r.ref_residual_add.argtypes = [vp, vp, vp, C.c_longlong]
+        r.ref_residual_add.restype = i
+        r.ref_rmsnorm.argtypes = [vp, vp, vp, i, f]
+        r.ref_rmsnorm.restype = None
         _REF = r
     return _REF

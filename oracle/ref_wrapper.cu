@@ -10,6 +10,8 @@
 //   ref_flash_attention     -> transformer::launch_flash_attention
 //                              (src/kernels/flashattention/flashattention.h:54-76)
 //   ref_flash_output_layout -> launch_flash_output_layout (src/runtime/layout.hpp:5-9)
+//   ref_residual_add        -> transformer::residual_add  (src/kernels/residual_add/residual_add.hpp)
+//   ref_rmsnorm             -> rmsnorm_launch<2048>       (src/kernels/rmsnorm/rmsnorm.hpp:6-14)
 //   ref_append_*            -> the append the reference performs inline in
 //                              Attention::forward (src/runtime/attention.cu:239-262):
 //                              2*8*tokens device-to-device copies of 128 bytes.
@@ -24,6 +26,8 @@
 #include "gemm_2048x2048.hpp"
 #include "gemm_2048x512.hpp"
 #include "layout.hpp"
+#include "residual_add.hpp"
+#include "rmsnorm.hpp"
 #include "rope.hpp"
 
 extern "C" {
@@ -73,6 +77,22 @@ int ref_gemm(const void* A, const void* B, void* C, int M, int N, int K) {
   else
     return 1;
   return (int)cudaGetLastError();
+}
+
+// out = a + b as TransformerBlock::forward adds the attention output to the block input
+// (src/runtime/transformer_block.cu:76-81).  The reference throws on bad arguments.
+int ref_residual_add(const void* a, const void* b, void* out, long long n) {
+  try {
+    transformer::residual_add((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)out, (int64_t)n);
+  } catch (...) {
+    return 1;
+  }
+  return 0;
+}
+
+// RMSNorm over rows of 2048 as Attention::forward calls it (src/runtime/attention.cu:123).
+void ref_rmsnorm(const void* in, const void* weight, void* out, int rows, float eps) {
+  rmsnorm_launch<2048>((const __nv_bfloat16*)in, (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, rows, eps, 256);
 }
 
 void ref_flash_output_layout(const void* in, void* out, int tokens) {
