@@ -314,6 +314,39 @@ int pa_decode_noalloc(const void* cache_layer, int num_blocks, int kv_heads,
                       int64_t out_stride, float* lse, float scale, void* stream);
 int pa_decode_noalloc_check(void* stream);
 
+/* ---- one decode step through the attention blocks, layers chained by their data ----
+ * Replaces Attention::forward at seq_len == 1 (src/runtime/attention.cu:99-390: RMSNorm, three
+ * projection GEMMs, RoPE kernels, append copies, attention kernel, layout kernel, output
+ * projection, with a device synchronisation after each and per-call allocations), the attention
+ * residual of TransformerBlock::forward (src/runtime/transformer_block.cu:76-81) and the layer
+ * loop of Transformer::forward (src/runtime/transformer.cu:47-89) as far as attention goes.
+ * Per layer l of [layer_begin, layer_end):
+ *     xn      = RMSNorm(x_l, input_norm[l])             (skipped when input_norm is NULL)
+ *     q, k, v = xn Wq[l], xn Wk[l], xn Wv[l]
+ *     attn    = append (RoPE on K) + decode attention (RoPE on Q) over the layer's cache
+ *     x_{l+1} = attn Wo[l] (+ x_l when add_residual != 0)
+ * x_l of the first layer is x_in [rows, hidden], the last layer's result goes to x_out; rows =
+ * sequences of the active batch (at most 8, one query row each).  A caller with an FFN between
+ * the attention blocks calls it one layer at a time.  Three launches per layer, chained by
+ * programmatic dependent launch; intermediate rows live in the pool (no allocation, no host
+ * synchronisation).  `exchange` (nullable) is the range-sharded variant: every rank projects the
+ * same rows, the rank that appends does so, partials are exchanged and merged in the decode
+ * kernel.  Weight pointers address layer 0 of the model. */
+typedef struct pa_attention_weights {
+  const void* input_norm; /* [layers][hidden] bf16, nullable */
+  const void* wq;         /* [layers][hidden, q_heads*64] row-major (the reference's layout) */
+  const void* wk;         /* [layers][hidden, kv_heads*64] */
+  const void* wv;
+  const void* wo;         /* [layers][q_heads*64, hidden] */
+  int64_t norm_layer_stride, wq_layer_stride, wkv_layer_stride, wo_layer_stride; /* elements */
+  float rms_eps;          /* the reference passes 1e-5 */
+  int hidden;
+} pa_attention_weights;
+int pa_attention_step(pa_pool* pool, pa_exchange* exchange, int layer_begin, int layer_end,
+                      const pa_attention_weights* weights, const void* x_in, void* x_out,
+                      int add_residual, const float* cos_table, const float* sin_table, float scale,
+                      void* stream);
+
 /* Host: fp32 cos/sin tables [seq_len][32], Llama-3 frequency scaling. */
 int pa_build_rope_tables(float* cos_table, float* sin_table, int seq_len);
 
@@ -352,6 +385,20 @@ int pa_qkv_project(const void* x, const void* wq, const void* wk, const void* wv
                    void* v, int rows, int layers, int hidden, int q_cols, int kv_cols,
                    int64_t x_layer_stride, int64_t wq_layer_stride, int64_t wkv_layer_stride,
                    int64_t q_layer_stride, int64_t kv_layer_stride, void* stream);
+
+/* The same projections with the RMSNorm that precedes them in Attention::forward
+ * (src/runtime/attention.cu:118-131 calling rmsnorm_launch<2048>, src/kernels/rmsnorm/rmsnorm.cu:51-148)
+ * as the kernel's prologue: x <- bf16((x * rsqrt(mean(x^2) + eps)) * norm_weight) on the staged
+ * rows, with the reference kernel's arithmetic and summation order (bit-equal normalised rows for
+ * hidden 2048).  norm_weight [layers][hidden] bf16. */
+int pa_rmsnorm_qkv_project(const void* x, const void* norm_weight, int64_t norm_layer_stride, float eps,
+                           const void* wq, const void* wk, const void* wv, void* q, void* k, void* v,
+                           int rows, int layers, int hidden, int q_cols, int kv_cols,
+                           int64_t x_layer_stride, int64_t wq_layer_stride, int64_t wkv_layer_stride,
+                           int64_t q_layer_stride, int64_t kv_layer_stride, void* stream);
+/* RMSNorm over any number of rows (prompt chunks, whose projections run on the tensor cores):
+ * y [rows, hidden] = the same arithmetic; hidden a multiple of 256, at most 2048; y may alias x. */
+int pa_rmsnorm(const void* x, const void* weight, void* y, int rows, int hidden, float eps, void* stream);
 
 /* ---- consumer side of the path: output projection + attention residual ---------
  * out = bf16(residual + bf16(attn W_o)) for the rows of a decode step (at most 8),

@@ -18,7 +18,7 @@ SYMBOLS = [
     "pa_pool_set_free_order", "pa_pool_layer_storage", "pa_seq_create", "pa_seq_free",
     "pa_seq_reserve", "pa_seq_length", "pa_seq_block_table", "pa_batch_set", "pa_batch_set_sharded", "pa_append",
     "pa_decode", "pa_decode_step", "pa_prefill", "pa_merge_partials", "pa_gather_kv", "pa_build_rope_tables",
-    "pa_pool_check", "pa_pool_set_decode_chunk_blocks", "pa_pool_set_decode_shape", "pa_pool_set_step_kernel", "pa_pool_set_layer_overlap", "pa_pool_set_step_combiners", "pa_pool_step_launches", "pa_qkv_project", "pa_out_project", "pa_out_project_rows", "pa_qkv_project_packed", "pa_qkv_project_append", "pa_pack_projection_weights",
+    "pa_pool_check", "pa_pool_set_decode_chunk_blocks", "pa_pool_set_decode_shape", "pa_pool_set_step_kernel", "pa_pool_set_layer_overlap", "pa_pool_set_step_combiners", "pa_pool_step_launches", "pa_qkv_project", "pa_rmsnorm_qkv_project", "pa_rmsnorm", "pa_attention_step", "pa_out_project", "pa_out_project_rows", "pa_qkv_project_packed", "pa_qkv_project_append", "pa_pack_projection_weights",
     "pa_decode_noalloc", "pa_decode_noalloc_check", "pa_pool_reserve_rows", "pa_decode_step_sharded_colocated", "pa_exchange_create", "pa_exchange_handle", "pa_exchange_connect",
     "pa_exchange_destroy", "pa_decode_step_sharded", "pa_exchange_buffer", "pa_exchange_connect_ptrs",
     "pa_decode_push", "pa_exchange_merge", "pa_gather_create", "pa_gather_handle", "pa_gather_connect",
@@ -37,6 +37,14 @@ class FlashAttentionParams(C.Structure):
                 ("num_kv_heads", C.c_int), ("q_seq_len", C.c_int), ("kv_seq_len", C.c_int),
                 ("kv_stride", C.c_int), ("d_head", C.c_int), ("scale", C.c_float),
                 ("causal", C.c_int), ("dtype", C.c_int), ("stream", C.c_void_p)]
+
+
+class AttentionWeights(C.Structure):
+    """pa_attention_weights of include/paged_attention.h."""
+    _fields_ = [("input_norm", C.c_void_p), ("wq", C.c_void_p), ("wk", C.c_void_p), ("wv", C.c_void_p),
+                ("wo", C.c_void_p), ("norm_layer_stride", C.c_int64), ("wq_layer_stride", C.c_int64),
+                ("wkv_layer_stride", C.c_int64), ("wo_layer_stride", C.c_int64), ("rms_eps", C.c_float),
+                ("hidden", C.c_int)]
 
 
 class PagedAttentionError(RuntimeError):
@@ -86,6 +94,9 @@ def lib():
         "pa_pool_step_launches": [vp, C.POINTER(C.c_longlong)],
         "pa_qkv_project": [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i64, i64, i64, i64, i64, vp],
         "pa_qkv_project_append": [vp, i, vp, vp, vp, vp, vp, vp, vp, i, vp],
+        "pa_rmsnorm_qkv_project": [vp, vp, i64, f, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i64, i64, i64, i64, i64, vp],
+        "pa_rmsnorm": [vp, vp, vp, i, i, f, vp],
+        "pa_attention_step": [vp, vp, i, i, vp, vp, vp, i, vp, vp, f, vp],
         "pa_out_project": [vp, vp, vp, vp, i, i, i, i, i64, i64, i64, vp],
         "pa_out_project_rows": [vp, vp, vp, vp, vp, i, i, i, vp],
         "pa_qkv_project_packed": [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i64, i64, i64, i64, i64, vp, vp],

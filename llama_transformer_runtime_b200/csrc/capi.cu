@@ -33,6 +33,8 @@ int fail(int code, const char* fmt, ...) {
   } while (0)
 
 constexpr int kWsItems = 148 * 64;  // split-KV partials the workspace can hold
+constexpr int kMaxStepRows = 8;     // sequences of a decode step that pa_attention_step chains
+constexpr int kMaxStepHidden = 2048;
 
 // Restores the caller's current device on scope exit.
 struct DeviceGuard {
@@ -76,6 +78,9 @@ struct pa_pool {
   long long step_launches = 0;  // decode steps that ran as one cooperative launch
   void* x_pack = nullptr;       // activations in tile-image form for the projection GEMM (pa_pool_reserve_rows)
   size_t x_pack_bytes = 0;
+  // rows of a decode step between the kernels of pa_attention_step: q, k, v, rotated q, attention
+  // output and two block inputs in turn, kMaxStepRows rows each
+  __nv_bfloat16* step_ws = nullptr;
   int* prefill_work = nullptr;  // 64 item counters, one per prefill launch in rotation, zero when idle
   unsigned prefill_launches = 0;
   pa_pool(int nb, int ms, int mb) : host(nb, ms, mb) {}
@@ -90,6 +95,17 @@ void exchange_unfill(pa_exchange* x);
 int exchange_rows(const pa_exchange* x);
 int exchange_groups(const pa_exchange* x);
 }  // namespace pa
+// projection launchers of qkv_project.cu, with the programmatic-dependent-launch flag
+namespace pa {
+int qkv_project_impl(const void* x, const void* norm_weight, int64_t norm_layer_stride, float eps, const void* wq,
+                     const void* wk, const void* wv, void* q, void* k, void* v, int rows, int layers, int hidden,
+                     int q_cols, int kv_cols, int64_t x_layer_stride, int64_t wq_layer_stride,
+                     int64_t wkv_layer_stride, int64_t q_layer_stride, int64_t kv_layer_stride, int pdl, void* stream);
+int out_project_impl(const void* attn, const void* wo, const void* residual, void* out, int rows, int layers,
+                     int hidden, int cols, int64_t attn_layer_stride, int64_t wo_layer_stride,
+                     int64_t residual_layer_stride, int64_t out_layer_stride, int pdl, void* stream);
+}  // namespace pa
+
 struct pa_gather;
 namespace pa {
 bool gather_begin(pa_gather* g);
@@ -131,6 +147,9 @@ int pa_pool_create(pa_pool** out, int device, int num_layers, int num_blocks, in
     alloc((void**)&p->ws_ml, (size_t)kWsItems * 2 * pa::kGroup * sizeof(float));
     alloc((void**)&p->ws_count, (size_t)max_seqs * kv_heads * pa::kMaxStepLayers * sizeof(unsigned int));
     alloc((void**)&p->prefill_work, 64 * sizeof(int));
+    alloc((void**)&p->step_ws, (size_t)kMaxStepRows * (3 * kv_heads * pa::kGroup * pa::kHeadDim +
+                                                        2 * kv_heads * pa::kHeadDim + 2 * kMaxStepHidden) *
+                                   sizeof(__nv_bfloat16));
     alloc((void**)&p->d_status, sizeof(int));
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&p->sm_count, cudaDevAttrMultiProcessorCount, device);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
@@ -156,6 +175,7 @@ int pa_pool_destroy(pa_pool* p) {
     cudaFree(p->ws_ml);
     cudaFree(p->ws_count);
     cudaFree(p->prefill_work);
+    cudaFree(p->step_ws);
     cudaFree(p->x_pack);
     cudaFree(p->d_status);
   }
@@ -389,7 +409,7 @@ struct FusedAppend {
   const float* cos_table;
   const float* sin_table;
   void* q_rot_out;
-  int pdl;  // not the first layer of the step: may overlap the previous layer's tail
+  int pdl;  // 1: may overlap the previous layer's decode kernel; 2: waits for the kernel that made q, k, v
 };
 
 // The append can ride inside the decode kernel when every sequence brings one
@@ -738,6 +758,66 @@ int pa_decode_step_sharded_colocated(pa_pool* const* pools, pa_exchange* const* 
   DeviceGuard g(dev);
   PA_CUDA(pa::launch_decode_step_colocated(cp, (cudaStream_t)stream));
   for (int r = 0; r < world; r++) pools[r]->step_launches++;
+  return PA_OK;
+}
+
+// One decode step through the attention blocks of layers [layer_begin, layer_end) with the true
+// data flow: per layer three launches — projections (RMSNorm in front when a norm weight is given),
+// decode attention with the append fused in, output projection (+ residual) — chained by
+// programmatic dependent launch: each kernel starts the part of its work that does not depend on
+// the kernel in front (weight loads, cache copies) while that kernel finishes, and waits before it
+// reads its output.  All intermediate rows live in the pool's step workspace.
+int pa_attention_step(pa_pool* p, pa_exchange* x, int layer_begin, int layer_end, const pa_attention_weights* w,
+                      const void* x_in, void* x_out, int add_residual, const float* cos_table,
+                      const float* sin_table, float scale, void* stream) {
+  if (!p || !w || !x_in || !x_out || !cos_table || !sin_table)
+    return fail(PA_ERR_INVALID_ARG, "pa_attention_step: NULL argument");
+  if (!w->wq || !w->wk || !w->wv || !w->wo) return fail(PA_ERR_INVALID_ARG, "pa_attention_step: NULL weight");
+  if (p->device < 0) return fail(PA_ERR_STATE, "pa_attention_step: host-only pool");
+  if (layer_begin < 0 || layer_end > p->num_layers || layer_begin >= layer_end)
+    return fail(PA_ERR_INVALID_ARG, "pa_attention_step: layers [%d, %d) out of range", layer_begin, layer_end);
+  if (p->batch.empty()) return fail(PA_ERR_STATE, "pa_attention_step: no active batch (call pa_batch_set)");
+  const int rows = (int)p->batch.size();
+  if (rows > kMaxStepRows) return fail(PA_ERR_UNSUPPORTED, "pa_attention_step: at most %d sequences per step", kMaxStepRows);
+  if (!can_fuse_append(p))
+    return fail(PA_ERR_UNSUPPORTED, "pa_attention_step: needs one query row and at most one new token per sequence");
+  const int hidden = w->hidden;
+  if (hidden < 64 || hidden > kMaxStepHidden || hidden % 64 != 0)
+    return fail(PA_ERR_UNSUPPORTED, "pa_attention_step: hidden must be a multiple of 64, at most %d", kMaxStepHidden);
+  if (layer_end - layer_begin > 1 && x_out == x_in)
+    return fail(PA_ERR_INVALID_ARG, "pa_attention_step: x_out must not alias x_in over several layers");
+  const int q_cols = p->kv_heads * pa::kGroup * pa::kHeadDim, kv_cols = p->kv_heads * pa::kHeadDim;
+  __nv_bfloat16* ws = p->step_ws;
+  __nv_bfloat16* q = ws;
+  __nv_bfloat16* k = q + (size_t)kMaxStepRows * q_cols;
+  __nv_bfloat16* v = k + (size_t)kMaxStepRows * kv_cols;
+  __nv_bfloat16* q_rot = v + (size_t)kMaxStepRows * kv_cols;
+  __nv_bfloat16* attn = q_rot + (size_t)kMaxStepRows * q_cols;
+  __nv_bfloat16* xpp[2] = {attn + (size_t)kMaxStepRows * q_cols,
+                           attn + (size_t)kMaxStepRows * q_cols + (size_t)kMaxStepRows * kMaxStepHidden};
+  bool appends = false;
+  for (const auto& e : p->batch) appends = appends || e.n_new > 0;
+  DeviceGuard g(p->device);
+  const __nv_bfloat16* cur = (const __nv_bfloat16*)x_in;
+  for (int l = layer_begin; l < layer_end; l++) {
+    const bool first = l == layer_begin;
+    const __nv_bfloat16* norm = w->input_norm ? (const __nv_bfloat16*)w->input_norm + (size_t)l * w->norm_layer_stride : nullptr;
+    const __nv_bfloat16* wq = (const __nv_bfloat16*)w->wq + (size_t)l * w->wq_layer_stride;
+    const __nv_bfloat16* wk = (const __nv_bfloat16*)w->wk + (size_t)l * w->wkv_layer_stride;
+    const __nv_bfloat16* wv = (const __nv_bfloat16*)w->wv + (size_t)l * w->wkv_layer_stride;
+    const __nv_bfloat16* wo = (const __nv_bfloat16*)w->wo + (size_t)l * w->wo_layer_stride;
+    // the first kernel of the call follows work this library knows nothing about: plain launch
+    int r = pa::qkv_project_impl(cur, norm, 0, w->rms_eps, wq, wk, wv, q, k, v, rows, 1, hidden, q_cols, kv_cols, 0, 0, 0,
+                                 0, 0, first ? 0 : 1, stream);
+    if (r != PA_OK) return r;
+    const FusedAppend fz{appends ? k : nullptr, appends ? v : nullptr, cos_table, sin_table, q_rot, 2};
+    r = decode_impl(p, l, q, attn, q_cols, nullptr, nullptr, scale, stream, x, true, &fz);
+    if (r != PA_OK) return r;
+    __nv_bfloat16* out = l == layer_end - 1 ? (__nv_bfloat16*)x_out : xpp[(l - layer_begin) & 1];
+    r = pa::out_project_impl(attn, wo, add_residual ? cur : nullptr, out, rows, 1, q_cols, hidden, 0, 0, 0, 0, 1, stream);
+    if (r != PA_OK) return r;
+    cur = out;
+  }
   return PA_OK;
 }
 

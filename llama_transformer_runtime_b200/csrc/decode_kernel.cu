@@ -296,7 +296,12 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const int x, c
   // first writes the new token's K (RoPE applied) and V rows of this head into
   // that block — the same arithmetic and placement as append_kernel — and
   // orders those generic-proxy stores before its own bulk (async-proxy) reads.
-  if (p.fuse && e.n_new > 0 && x == n_chunks - 1 && cnt > 0 && warp == (cnt - 1) % WARPS) {
+  // pdl == 2: q, k_new and v_new are the output of the kernel in front (the projections of this
+  // layer).  The cache, the tables and the batch are not: every warp but the one that appends
+  // starts its first bulk copies before it waits for that kernel.
+  const bool appends = p.fuse && e.n_new > 0 && x == n_chunks - 1 && cnt > 0 && warp == (cnt - 1) % WARPS;
+  if (p.pdl == 2 && appends) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (appends) {
     if (lane < 8) {
       const int lpos = e.kv_len - 1;
       const int pos = e.kv_pos_off + lpos;
@@ -328,6 +333,7 @@ __device__ __forceinline__ void decode_cta(const DecodeParams& p, const int x, c
   }
 
   for (int i = 0; i < STAGES && i < my_n; i++) issue(i);
+  if (p.pdl == 2 && !appends) asm volatile("griddepcontrol.wait;" ::: "memory");
 
   // Query fragments: rows 0..3 are the group's heads, the rest zero.
   const int qrow = lane >> 2, qcol = (lane & 3) * 2;

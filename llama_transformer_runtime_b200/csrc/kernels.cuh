@@ -73,8 +73,10 @@ struct DecodeParams {
   long long hs_stride = 0;
   // Fused append (one new token per sequence at most): q is un-rotated, the
   // kernel rotates it and appends k_new/v_new rows (RoPE on K) to the cache.
-  // launched with programmatic stream serialization behind the previous
-  // layer's decode kernel (see the two griddepcontrol points in the kernel)
+  // launched with programmatic stream serialization (see the griddepcontrol points in the
+  // kernel).  1: behind the previous layer's decode kernel, whose workspace it shares — the
+  // inputs are ready, it waits before it writes.  2: behind the kernel that produces q, k_new and
+  // v_new — it waits before it reads them, after its first cache copies are under way.
   int pdl = 0;
   int fuse = 0;
   const __nv_bfloat16* k_new = nullptr;  // [rows][kv_heads][64], row e.kv_row_off

@@ -45,6 +45,14 @@ struct QkvParams {
   int* status = nullptr;       // packed kernel: a wait that ran out is recorded here (nullable: then only the loop ends)
   // optional residual of output 0 (the output projection): out = bf16(residual + bf16(x W)), same strides as out[0]
   const __nv_bfloat16* residual = nullptr;
+  long long residual_layer_stride = 0;
+  // optional RMSNorm in front of the projections: x <- bf16(x * rsqrt(mean(x^2) + eps) * norm_w)
+  const __nv_bfloat16* norm_w = nullptr;  // [layers][hidden]
+  long long norm_layer_stride = 0;
+  float eps = 0.f;
+  // launched with programmatic stream serialization: x (and the residual) come from the kernel in
+  // front, the weights do not; see the two griddepcontrol points in the kernel
+  int pdl = 0;
 };
 
 template <int ROWS>
@@ -68,6 +76,13 @@ __global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
   for (int u = 0; u < 16; u++)
     if (u < n_steps) wv[u] = __ldg(wp + (size_t)u * step);
 
+  // The weight loads above are all this kernel may do before the kernel in front has finished:
+  // x is its output.  The kernel behind may start its own weight loads from here on.
+  if (p.pdl) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
+
   // x rows of this layer -> shared memory (rows beyond p.rows are zero)
   const __nv_bfloat16* x = p.x + (size_t)layer * p.x_layer_stride;
   for (int i = threadIdx.x; i < ROWS * (p.hidden / 8); i += kThreads) {
@@ -77,6 +92,57 @@ __global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
     reinterpret_cast<uint4*>(&sx[r][0])[ch] = v;
   }
   __syncthreads();
+  if (p.norm_w) {
+    // RMSNorm of the staged rows, in place, with the arithmetic AND the summation order of the
+    // reference's kernel (src/kernels/rmsnorm/rmsnorm.cu:51-110, launched with 256 threads): a
+    // thread sums the squares of its 8-element chunks in order, lanes combine by shuffle-down
+    // (16, 8, 4, 2, 1), warp sums combine the same way in warp 0; y = bf16((x * r) * w).
+    const uint4* nw = reinterpret_cast<const uint4*>(p.norm_w + (size_t)layer * p.norm_layer_stride);
+#pragma unroll
+    for (int r = 0; r < ROWS; r++) {
+      if (r >= p.rows) break;  // uniform
+      float sum_sq = 0.0f;
+      for (int i = threadIdx.x; i < p.hidden / 8; i += kThreads) {
+        const uint4 data = reinterpret_cast<const uint4*>(&sx[r][0])[i];
+        const __nv_bfloat162* bf = reinterpret_cast<const __nv_bfloat162*>(&data);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          const float2 v = __bfloat1622float2(bf[j]);
+          sum_sq = __fmaf_rn(v.x, v.x, sum_sq);
+          sum_sq = __fmaf_rn(v.y, v.y, sum_sq);
+        }
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) sum_sq += __shfl_down_sync(0xffffffffu, sum_sq, off);
+      if (lane == 0) red[0][0][warp] = sum_sq;
+      __syncthreads();
+      float tot = lane < kThreads / 32 ? red[0][0][lane] : 0.0f;
+      if (warp == 0) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) tot += __shfl_down_sync(0xffffffffu, tot, off);
+        if (lane == 0) red[0][0][8] = tot;
+      }
+      __syncthreads();
+      const float rms_recip = rsqrtf(red[0][0][8] / static_cast<float>(p.hidden) + p.eps);
+      for (int i = threadIdx.x; i < p.hidden / 8; i += kThreads) {
+        const uint4 xd = reinterpret_cast<const uint4*>(&sx[r][0])[i];
+        const uint4 wd = nw[i];
+        const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&xd);
+        const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wd);
+        uint4 yd;
+        __nv_bfloat162* yb = reinterpret_cast<__nv_bfloat162*>(&yd);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          const float2 xf = __bfloat1622float2(xb[j]);
+          const float2 wf = __bfloat1622float2(wb[j]);
+          yb[j] = __floats2bfloat162_rn(__fmul_rn(__fmul_rn(xf.x, rms_recip), wf.x),
+                                        __fmul_rn(__fmul_rn(xf.y, rms_recip), wf.y));
+        }
+        reinterpret_cast<uint4*>(&sx[r][0])[i] = yd;  // a thread rewrites only chunks it alone read
+      }
+    }
+    __syncthreads();
+  }
 
   float acc[ROWS][8];
 #pragma unroll
@@ -137,7 +203,7 @@ __global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
     if (which == 0 && p.residual) {
       // the reference adds the residual in a second kernel on the bf16 GEMM output
       // (src/kernels/residual_add/residual_add.cu:14-38): fp32 sum of two bf16, rounded once
-      const __nv_bfloat16 rv = p.residual[(size_t)layer * p.out_layer_stride[0] + (size_t)r * n + col0 + cc];
+      const __nv_bfloat16 rv = p.residual[(size_t)layer * p.residual_layer_stride + (size_t)r * n + col0 + cc];
       y = __float2bfloat16_rn(__bfloat162float(rv) + __bfloat162float(y));
     }
     out[(size_t)r * n + col0 + cc] = y;
@@ -293,12 +359,42 @@ int qfail(int code, const char* msg) {
   return code;
 }
 
+// Launch of the row-major projection kernel for 1..8 rows, with programmatic stream serialization
+// when p.pdl is set (the kernel then waits for the kernel in front before it reads x).
+cudaError_t launch_rows(const QkvParams& p, dim3 grid, cudaStream_t st) {
+  void (*kern)(QkvParams) = p.rows == 1 ? qkv_project_kernel<1>
+                            : p.rows == 2 ? qkv_project_kernel<2>
+                            : p.rows <= 4 ? qkv_project_kernel<4>
+                                          : qkv_project_kernel<8>;
+  if (!p.pdl) {
+    kern<<<grid, kThreads, 0, st>>>(p);
+    return cudaGetLastError();
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
 }  // namespace
 
-extern "C" int pa_qkv_project(const void* x, const void* wq, const void* wk, const void* wv, void* q, void* k,
-                              void* v, int rows, int layers, int hidden, int q_cols, int kv_cols,
-                              int64_t x_layer_stride, int64_t wq_layer_stride, int64_t wkv_layer_stride,
-                              int64_t q_layer_stride, int64_t kv_layer_stride, void* stream) {
+namespace pa {
+int out_project_impl(const void* attn, const void* wo, const void* residual, void* out, int rows, int layers,
+                     int hidden, int cols, int64_t attn_layer_stride, int64_t wo_layer_stride,
+                     int64_t residual_layer_stride, int64_t out_layer_stride, int pdl, void* stream);
+
+int qkv_project_impl(const void* x, const void* norm_weight, int64_t norm_layer_stride, float eps, const void* wq,
+                     const void* wk, const void* wv, void* q, void* k, void* v, int rows, int layers, int hidden,
+                     int q_cols, int kv_cols, int64_t x_layer_stride, int64_t wq_layer_stride,
+                     int64_t wkv_layer_stride, int64_t q_layer_stride, int64_t kv_layer_stride, int pdl,
+                     void* stream) {
   if (!x || !wq || !wk || !wv || !q || !k || !v) return qfail(PA_ERR_INVALID_ARG, "pa_qkv_project: NULL argument");
   if (rows < 1 || layers < 1) return qfail(PA_ERR_INVALID_ARG, "pa_qkv_project: rows and layers must be >= 1");
   if (rows > 8)
@@ -327,23 +423,39 @@ extern "C" int pa_qkv_project(const void* x, const void* wq, const void* wk, con
   p.tiles_qk = p.tiles_q + kv_cols / kColsPerCta;
   p.rows = rows;
   p.hidden = hidden;
+  p.norm_w = (const __nv_bfloat16*)norm_weight;
+  p.norm_layer_stride = norm_layer_stride;
+  p.eps = eps;
+  p.pdl = pdl;
   const dim3 grid(p.tiles_qk + kv_cols / kColsPerCta, layers);
-  cudaStream_t st = (cudaStream_t)stream;
-  if (rows == 1)
-    qkv_project_kernel<1><<<grid, kThreads, 0, st>>>(p);
-  else if (rows == 2)
-    qkv_project_kernel<2><<<grid, kThreads, 0, st>>>(p);
-  else if (rows <= 4)
-    qkv_project_kernel<4><<<grid, kThreads, 0, st>>>(p);
-  else
-    qkv_project_kernel<8><<<grid, kThreads, 0, st>>>(p);
-  const cudaError_t e = cudaGetLastError();
+  const cudaError_t e = launch_rows(p, grid, (cudaStream_t)stream);
   if (e != cudaSuccess) {
     char msg[256];
     snprintf(msg, sizeof(msg), "pa_qkv_project: %s", cudaGetErrorString(e));
     return qfail(PA_ERR_CUDA, msg);
   }
   return PA_OK;
+}
+}  // namespace pa
+
+extern "C" int pa_qkv_project(const void* x, const void* wq, const void* wk, const void* wv, void* q, void* k,
+                              void* v, int rows, int layers, int hidden, int q_cols, int kv_cols,
+                              int64_t x_layer_stride, int64_t wq_layer_stride, int64_t wkv_layer_stride,
+                              int64_t q_layer_stride, int64_t kv_layer_stride, void* stream) {
+  return pa::qkv_project_impl(x, nullptr, 0, 0.f, wq, wk, wv, q, k, v, rows, layers, hidden, q_cols, kv_cols,
+                              x_layer_stride, wq_layer_stride, wkv_layer_stride, q_layer_stride, kv_layer_stride, 0,
+                              stream);
+}
+
+extern "C" int pa_rmsnorm_qkv_project(const void* x, const void* norm_weight, int64_t norm_layer_stride, float eps,
+                                      const void* wq, const void* wk, const void* wv, void* q, void* k, void* v,
+                                      int rows, int layers, int hidden, int q_cols, int kv_cols,
+                                      int64_t x_layer_stride, int64_t wq_layer_stride, int64_t wkv_layer_stride,
+                                      int64_t q_layer_stride, int64_t kv_layer_stride, void* stream) {
+  if (!norm_weight) return qfail(PA_ERR_INVALID_ARG, "pa_rmsnorm_qkv_project: NULL norm weight");
+  return pa::qkv_project_impl(x, norm_weight, norm_layer_stride, eps, wq, wk, wv, q, k, v, rows, layers, hidden,
+                              q_cols, kv_cols, x_layer_stride, wq_layer_stride, wkv_layer_stride, q_layer_stride,
+                              kv_layer_stride, 0, stream);
 }
 
 extern "C" int pa_qkv_project_packed(const void* x, const void* wq_packed, const void* wk_packed,
@@ -402,6 +514,13 @@ extern "C" int pa_qkv_project_packed(const void* x, const void* wq_packed, const
 extern "C" int pa_out_project(const void* attn, const void* wo, const void* residual, void* out, int rows,
                               int layers, int hidden, int cols, int64_t attn_layer_stride,
                               int64_t wo_layer_stride, int64_t out_layer_stride, void* stream) {
+  return pa::out_project_impl(attn, wo, residual, out, rows, layers, hidden, cols, attn_layer_stride, wo_layer_stride,
+                              out_layer_stride, out_layer_stride, 0, stream);
+}
+
+int pa::out_project_impl(const void* attn, const void* wo, const void* residual, void* out, int rows, int layers,
+                         int hidden, int cols, int64_t attn_layer_stride, int64_t wo_layer_stride,
+                         int64_t residual_layer_stride, int64_t out_layer_stride, int pdl, void* stream) {
   if (!attn || !wo || !out) return qfail(PA_ERR_INVALID_ARG, "pa_out_project: NULL argument");
   if (rows < 1 || layers < 1 || layers > 65535) return qfail(PA_ERR_INVALID_ARG, "pa_out_project: rows >= 1, 1 <= layers <= 65535");
   if (rows > 8) return qfail(PA_ERR_UNSUPPORTED, "pa_out_project: at most 8 rows per call (decode shapes)");
@@ -420,17 +539,10 @@ extern "C" int pa_out_project(const void* attn, const void* wo, const void* resi
   p.rows = rows;
   p.hidden = hidden;
   p.residual = (const __nv_bfloat16*)residual;
+  p.residual_layer_stride = residual_layer_stride;
+  p.pdl = pdl;
   const dim3 grid(p.tiles_q, layers);
-  cudaStream_t st = (cudaStream_t)stream;
-  if (rows == 1)
-    qkv_project_kernel<1><<<grid, kThreads, 0, st>>>(p);
-  else if (rows == 2)
-    qkv_project_kernel<2><<<grid, kThreads, 0, st>>>(p);
-  else if (rows <= 4)
-    qkv_project_kernel<4><<<grid, kThreads, 0, st>>>(p);
-  else
-    qkv_project_kernel<8><<<grid, kThreads, 0, st>>>(p);
-  const cudaError_t e = cudaGetLastError();
+  const cudaError_t e = launch_rows(p, grid, (cudaStream_t)stream);
   if (e != cudaSuccess) {
     char msg[256];
     snprintf(msg, sizeof(msg), "pa_out_project: %s", cudaGetErrorString(e));

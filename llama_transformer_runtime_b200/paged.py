@@ -10,7 +10,7 @@ import ctypes as C
 
 import numpy as np
 
-from ._lib import check, lib
+from ._lib import AttentionWeights, check, lib
 
 HEAD_DIM = 64
 GROUP = 4
@@ -339,6 +339,44 @@ def qkv_project(x, wq, wk, wv, q, k, v, rows: int, layers: int = 1, hidden: int 
     check(lib().pa_qkv_project(_ptr(x), _ptr(wq), _ptr(wk), _ptr(wv), _ptr(q), _ptr(k), _ptr(v), rows, layers,
                                hidden, q_cols, kv_cols, rows * hidden, hidden * q_cols, hidden * kv_cols,
                                rows * q_cols, rows * kv_cols, stream))
+
+
+def rmsnorm_qkv_project(x, norm_w, wq, wk, wv, q, k, v, rows: int, layers: int = 1, hidden: int = 2048,
+                        eps: float = 1e-5, stream: int = 0) -> None:
+    """qkv_project with the RMSNorm in front of it as the kernel's prologue; norm_w [layers, hidden]."""
+    q_cols, kv_cols = int(wq.shape[-1]), int(wk.shape[-1])
+    check(lib().pa_rmsnorm_qkv_project(_ptr(x), _ptr(norm_w), hidden, eps, _ptr(wq), _ptr(wk), _ptr(wv), _ptr(q),
+                                       _ptr(k), _ptr(v), rows, layers, hidden, q_cols, kv_cols, rows * hidden,
+                                       hidden * q_cols, hidden * kv_cols, rows * q_cols, rows * kv_cols, stream))
+
+
+def rmsnorm(x, w, y, rows: int, hidden: int = 2048, eps: float = 1e-5, stream: int = 0) -> None:
+    check(lib().pa_rmsnorm(_ptr(x), _ptr(w), _ptr(y), rows, hidden, eps, stream))
+
+
+def attention_weights(input_norm, wq, wk, wv, wo, hidden: int = 2048, eps: float = 1e-5) -> AttentionWeights:
+    """Descriptor of per-layer weights stacked along a leading layer dimension (contiguous bf16 tensors):
+    input_norm [layers, hidden] or None, wq [layers, hidden, q_cols], wk/wv [layers, hidden, kv_cols],
+    wo [layers, q_cols, hidden]."""
+    w = AttentionWeights()
+    w.input_norm = _ptr(input_norm)
+    w.wq, w.wk, w.wv, w.wo = _ptr(wq), _ptr(wk), _ptr(wv), _ptr(wo)
+    w.norm_layer_stride = hidden
+    w.wq_layer_stride = int(wq.shape[-2]) * int(wq.shape[-1])
+    w.wkv_layer_stride = int(wk.shape[-2]) * int(wk.shape[-1])
+    w.wo_layer_stride = int(wo.shape[-2]) * int(wo.shape[-1])
+    w.rms_eps = eps
+    w.hidden = hidden
+    return w
+
+
+def attention_step(pool: "KVPool", weights: AttentionWeights, layer_begin: int, layer_end: int, x_in, x_out,
+                   cos, sin, add_residual: bool = True, xchg: "Exchange | None" = None, scale: float = 0.125,
+                   stream: int = 0) -> None:
+    """One decode step through the attention blocks of [layer_begin, layer_end), layers chained by their data."""
+    check(lib().pa_attention_step(pool._h, xchg._h if xchg is not None else None, layer_begin, layer_end,
+                                  C.byref(weights), _ptr(x_in), _ptr(x_out), int(add_residual), _ptr(cos), _ptr(sin),
+                                  scale, stream))
 
 
 def pack_projection_weights(w, stream: int = 0):

@@ -373,3 +373,50 @@ void orc_output_layout_bf16(const uint16_t* in, uint16_t* out, int heads,
       memcpy(out + ((size_t)t * heads + h) * D, in + ((size_t)h * tokens + t) * D,
              D * sizeof(uint16_t));
 }
+
+/* ---- RMSNorm: src/kernels/rmsnorm/rmsnorm.cu:51-110 -------------------------
+ * y = bf16((x * r) * w), r = 1/sqrt(mean(x^2) + eps), all in fp32.  The sum of squares follows
+ * the kernel's order for its launch with 256 threads: thread t sums the squares of its 8-element
+ * chunks (t, t + 256, ...) with fused multiply-adds (the compiler contracts `s += v*v`), the 32
+ * lanes of a warp combine by shuffle-down 16, 8, 4, 2, 1 (lane i adds lane i + offset), and the
+ * warp totals combine the same way in the first warp (:9-46).  The kernel's rsqrtf is a hardware
+ * approximation (2 ulp); 1/sqrtf here can differ from it in the last bits, which moves an output
+ * by at most one bf16 ulp. */
+static float shuffle_down_sum(const float* lanes_in) {
+  float v[64];
+  for (int i = 0; i < 32; i++) v[i] = lanes_in[i];
+  for (int i = 32; i < 64; i++) v[i] = 0.f;
+  for (int off = 16; off > 0; off >>= 1) {
+    float nv[32];
+    /* a lane beyond the warp (i + off >= 32) reads its own value back */
+    for (int i = 0; i < 32; i++) nv[i] = v[i] + (i + off < 32 ? v[i + off] : v[i]);
+    for (int i = 0; i < 32; i++) v[i] = nv[i];
+  }
+  return v[0];
+}
+
+void orc_rmsnorm(const uint16_t* x, const uint16_t* w, uint16_t* y, int rows, int hidden, float eps) {
+  const int chunks = hidden / 8;
+  for (int r = 0; r < rows; r++) {
+    const uint16_t* xr = x + (size_t)r * hidden;
+    float thread_sum[256];
+    for (int t = 0; t < 256; t++) {
+      float s = 0.f;
+      for (int i = t; i < chunks; i += 256)
+        for (int j = 0; j < 8; j++) {
+          const float v = orc_bf16_to_f32(xr[i * 8 + j]);
+          s = fmaf(v, v, s);
+        }
+      thread_sum[t] = s;
+    }
+    float warp_sum[32];
+    for (int i = 0; i < 32; i++) warp_sum[i] = 0.f;
+    for (int wdx = 0; wdx < 8; wdx++) warp_sum[wdx] = shuffle_down_sum(thread_sum + 32 * wdx);
+    const float total = shuffle_down_sum(warp_sum);
+    const float recip = 1.0f / sqrtf(total / (float)hidden + eps);
+    for (int k = 0; k < hidden; k++) {
+      const float xr_k = orc_bf16_to_f32(xr[k]);
+      y[(size_t)r * hidden + k] = orc_f32_to_bf16((xr_k * recip) * orc_bf16_to_f32(w[k]));
+    }
+  }
+}

@@ -111,6 +111,11 @@ void orc_output_layout_bf16(const uint16_t* in, uint16_t* out, int heads,
  * accumulation order lands on the other side of a rounding boundary. */
 void orc_gemm_bf16(const uint16_t* A, const uint16_t* B, uint16_t* C, int M, int N, int K);
 
+/* RMSNorm of rows of `hidden` bf16 values: y = bf16((x * r) * w), r = 1/sqrt(mean(x^2) + eps).
+ * Follows rmsnorm_fwd_kernel, src/kernels/rmsnorm/rmsnorm.cu:51-110, including the order in which
+ * its 256 threads add up the squares. */
+void orc_rmsnorm(const uint16_t* x, const uint16_t* w, uint16_t* y, int rows, int hidden, float eps);
+
 int orc_num_threads(void);
 
 #ifdef __cplusplus

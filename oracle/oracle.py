@@ -194,6 +194,16 @@ def gemm_bf16(a: np.ndarray, b: np.ndarray) -> np.ndarray:
     return out
 
 
+def rmsnorm(x: np.ndarray, w: np.ndarray, eps: float = 1e-5) -> np.ndarray:
+    """bf16 bit patterns: x [rows, hidden], w [hidden] -> y [rows, hidden] (the reference kernel's arithmetic)."""
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    w = np.ascontiguousarray(w, dtype=np.uint16)
+    rows, hidden = x.shape
+    y = np.empty_like(x)
+    lib().orc_rmsnorm(_p(x), _p(w), _p(y), C.c_int(rows), C.c_int(hidden), C.c_float(eps))
+    return y
+
+
 def num_threads() -> int:
     return int(lib().orc_num_threads())
 
