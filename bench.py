@@ -25,7 +25,8 @@ The cache is 4.3 GB per step (268 MB per layer): larger than L2, no flush needed
 The default run (one GPU) also measures, after the main region, the other parts of the metric as
 sub-blocks of the same JSON line: decode4k (context 4096), prefill (2048 tokens, TFLOP/s), append
 (the fused RoPE + append kernel alone), out_project and qkv (the projections either side of the
-path), each with its roofline and the reference's own kernels timed in the same run.  With more
+path), decode_chain (projections -> attention -> output projection per layer with the true data
+flow), each with its roofline and the reference's own kernels timed in the same run.  With more
 than one GPU it adds batch64 (64 ragged sequences, KV heads sharded over the ranks).
 """
 from __future__ import annotations
@@ -1386,6 +1387,246 @@ def prefill_cpu_baseline(q_rot, out, pool, seq, S, budget_s=10.0):
             "gpu_vs_cpu_max_abs_err": err, "gpu_vs_cpu_max_row_rel_err": row_rel_err(got, want)}
 
 
+
+# =============================================================================
+# the decode step with its true data flow: projections -> attention -> output projection per layer
+# =============================================================================
+def run_chain(env: Env, args, sub: bool = False):
+    """One token through 16 attention blocks, each layer fed by the one before it (no FFN in between:
+    x_{l+1} = x_l + attention(RMSNorm(x_l)) W_o): per layer RMSNorm + Q/K/V projections (one launch),
+    RoPE + append + paged decode attention (one launch), output projection + residual (one launch),
+    chained by programmatic dependent launch.  Context 4096 by default (--chain-ctx).  Per layer the
+    step reads the projection weights (21 MB) and the layer's cache once: the metric is HBM GB/s over
+    those bytes.  With N GPUs the cache is split by token range (weights replicated, every rank
+    projects the same rows), partials exchanged and merged in the decode kernel.
+    Reference arm: the reference's own kernels in the order of Attention::forward +
+    TransformerBlock's residual add, with its device synchronisations."""
+    torch, dist = env.torch, env.dist
+    from oracle import oracle as orc
+    rank, local_rank, world, dev = env.rank, env.local_rank, env.world, env.dev
+    ctx = args.chain_ctx
+    steps = max(5, args.steps // 2) if sub else args.steps
+    warmup = 3 if sub else args.warmup
+    ref_arm = args.impl == "reference" and not sub
+    if ref_arm and rank != 0:
+        return None
+    H, NQ, NKV = HIDDEN, Q_HEADS * D, KV_HEADS * D
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(31)  # the same weights on every rank
+    SETS = 2 if (sub or ref_arm) else 4  # weight sets in rotation: 2 x 16 x 21 MB is already larger than L2
+    mk = lambda *shape, s=0.03: (torch.randn(*shape, generator=gen, device=dev) * s).to(torch.bfloat16)
+    Ws = [dict(nw=mk(LAYERS, H, s=0.7), wq=mk(LAYERS, H, NQ), wk=mk(LAYERS, H, NKV), wv=mk(LAYERS, H, NKV),
+               wo=mk(LAYERS, NQ, H)) for _ in range(SETS)]
+    x_host = torch.randn(1, H, generator=torch.Generator().manual_seed(6)).to(torch.bfloat16).pin_memory()
+    y_host = torch.zeros(1, H, dtype=torch.bfloat16).pin_memory()
+    x_dev = x_host.to(dev)
+    y_dev = torch.zeros(1, H, dtype=torch.bfloat16, device=dev)
+    weight_bytes = (H * (NQ + 2 * NKV) + NQ * H + H) * 2
+    total_steps = warmup + 2 * steps + 12
+    state = {"len": ctx, "i": 0}
+    ref = orc.ref() if orc.ref_available() else None
+    if ref_arm and ref is None:
+        return {"impl": "reference", "unavailable": "oracle/_ref/libref.so was not built"}
+    cos_h, sin_h = orc.build_rope_tables(ctx + total_steps + 2)
+    cos, sin = torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev)
+    kvgen = torch.Generator(device=dev)
+    kvgen.manual_seed(4321 + rank)
+
+    pool = xchg = None
+    lo = 0
+    if not ref_arm:
+        from llama_transformer_runtime_b200 import paged
+        lo, hi = token_ranges(ctx, world)[rank]
+        local_len = hi - lo
+        owner = world - 1
+        need_blocks = (local_len + (total_steps if rank == owner else 0) + BLOCK - 1) // BLOCK
+        num_blocks = need_blocks + need_blocks // 4 + 8
+        pool = paged.KVPool(LAYERS, num_blocks, KV_HEADS, 1, need_blocks + 1, device=local_rank)
+        pool.set_free_order(np.random.default_rng(1234 + rank).permutation(num_blocks))
+        seq = pool.create_seq()
+        ones = torch.ones(local_len + 1, 32, dtype=torch.float32, device=dev)
+        zeros = torch.zeros(local_len + 1, 32, dtype=torch.float32, device=dev)
+        for c0 in range(0, local_len, 8192):
+            n = min(8192, local_len - c0)
+            pool.reserve(seq, c0 + n)
+            pool.batch_set([seq], [n])
+            for layer in range(LAYERS):
+                k = (torch.randn(n, KV_HEADS, D, generator=kvgen, device=dev) * 0.5).to(torch.bfloat16)
+                v = (torch.randn(n, KV_HEADS, D, generator=kvgen, device=dev) * 0.5).to(torch.bfloat16)
+                pool.append(layer, None, k, v, ones, zeros, None)
+        torch.cuda.synchronize()
+        del ones, zeros
+        descs = [paged.attention_weights(w["nw"], w["wq"], w["wk"], w["wv"], w["wo"]) for w in Ws]
+        if world > 1:
+            xchg = paged.Exchange(local_rank, rank, world, 1, KV_HEADS)
+            handles = [None] * world
+            dist.all_gather_object(handles, xchg.handle())
+            xchg.connect(handles)
+            dist.barrier()
+
+        def ours_step():
+            state["len"] += 1
+            s = state["i"] % SETS
+            state["i"] += 1
+            if rank == owner:
+                pool.reserve(seq, pool.length(seq) + 1)
+            if world == 1:
+                pool.batch_set([seq])
+            else:
+                pool.batch_set_sharded([seq], [1 if rank == owner else 0], [1], [state["len"] - 1], [lo])
+            paged.attention_step(pool, descs[s], 0, LAYERS, x_dev, y_dev, cos, sin, add_residual=True, xchg=xchg)
+
+    if ref is not None and (ref_arm or sub) and rank == 0:
+        max_seq = ctx + total_steps + 2
+        kc = torch.zeros(LAYERS, KV_HEADS, max_seq, D, dtype=torch.bfloat16, device=dev)
+        vc = torch.zeros_like(kc)
+        for layer in range(LAYERS):
+            kc[layer, :, :ctx] = (torch.randn(KV_HEADS, ctx, D, generator=kvgen, device=dev) * 0.5).to(torch.bfloat16)
+            vc[layer, :, :ctx] = (torch.randn(KV_HEADS, ctx, D, generator=kvgen, device=dev) * 0.5).to(torch.bfloat16)
+        bufs = {n: torch.zeros(1, c, dtype=torch.bfloat16, device=dev) for n, c in
+                (("xn", H), ("q", NQ), ("k", NKV), ("v", NKV), ("arow", NQ), ("lin", H), ("xa", H), ("xb", H))}
+        qf = torch.empty(Q_HEADS, 1, D, dtype=torch.bfloat16, device=dev)
+        kf = torch.empty(KV_HEADS, 1, D, dtype=torch.bfloat16, device=dev)
+        vf = torch.empty(KV_HEADS, 1, D, dtype=torch.bfloat16, device=dev)
+        of = torch.empty(Q_HEADS, 1, D, dtype=torch.bfloat16, device=dev)
+        rstate = {"len": ctx, "i": 0}
+
+        def ref_step():
+            pos = rstate["len"]
+            rstate["len"] += 1
+            w = Ws[rstate["i"] % SETS]
+            rstate["i"] += 1
+            cur = x_dev
+            for l in range(LAYERS):
+                ref.ref_rmsnorm(cur.data_ptr(), w["nw"][l].data_ptr(), bufs["xn"].data_ptr(), 1, 1e-5)
+                torch.cuda.synchronize()
+                for wm, o, n in ((w["wq"], bufs["q"], NQ), (w["wk"], bufs["k"], NKV), (w["wv"], bufs["v"], NKV)):
+                    ref.ref_gemm(bufs["xn"].data_ptr(), wm[l].data_ptr(), o.data_ptr(), 1, n, H)
+                    torch.cuda.synchronize()
+                ref.ref_rope_qkv(bufs["q"].data_ptr(), qf.data_ptr(), bufs["k"].data_ptr(), kf.data_ptr(),
+                                 bufs["v"].data_ptr(), vf.data_ptr(), cos.data_ptr(), sin.data_ptr(), 1, pos)
+                ref.ref_append_memcpy_loop(kc[l].data_ptr(), vc[l].data_ptr(), kf.data_ptr(), vf.data_ptr(), max_seq, pos, 1)
+                ref.ref_flash_attention(qf.data_ptr(), kc[l].data_ptr(), vc[l].data_ptr(), of.data_ptr(), None, 1,
+                                        Q_HEADS, KV_HEADS, 1, pos + 1, max_seq, 0.125, 1, None)
+                torch.cuda.synchronize()
+                ref.ref_flash_output_layout(of.data_ptr(), bufs["arow"].data_ptr(), 1)
+                torch.cuda.synchronize()
+                ref.ref_gemm(bufs["arow"].data_ptr(), w["wo"][l].data_ptr(), bufs["lin"].data_ptr(), 1, H, NQ)
+                torch.cuda.synchronize()
+                nxt = bufs["xa"] if l % 2 == 0 else bufs["xb"]
+                ref.ref_residual_add(cur.data_ptr(), bufs["lin"].data_ptr(), nxt.data_ptr(), H)
+                torch.cuda.synchronize()
+                cur = nxt
+            y_dev.copy_(cur)
+
+    step = ref_step if ref_arm else ours_step
+
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        step()
+        y_host.copy_(y_dev, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def block(fn, n):
+        st = rstate if ref_arm else state
+        l0 = st["len"]
+        ms = local_timed(torch, fn, n) if ref_arm else env.timed(fn, n)
+        return ms, sum(LAYERS * (decode_bytes(L) + weight_bytes) for L in range(l0 + 1, st["len"] + 1))
+
+    m0 = env.sampler.mark()
+    for _ in range(warmup):
+        step()
+    ms, nbytes = block(step, steps)
+    ms_e2e, nbytes_e2e = block(e2e_step, steps)
+    m1 = env.sampler.mark()
+    value = nbytes / (ms * 1e-3) / 1e9
+    peak, peak_kind = measured_peak()
+    line = None
+    if rank == 0:
+        line = {
+            "metric": "decode_chain_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": 1 if ref_arm else world,
+            "steps": steps, "warmup": warmup, "ms_per_step": round(ms / steps, 4),
+            "us_per_token": round(ms / steps * 1e3, 2), "us_per_layer": round(ms / steps * 1e3 / LAYERS, 2),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"decode_chain_ctx{ctx}_x{LAYERS}layers_batch1", "context": ctx, "layers": LAYERS,
+                       "batch": 1, "hidden": H, "bytes": "per layer: Wq, Wk, Wv, Wo, norm weight + the layer's cache (2048 L + ...)",
+                       "parallelism": "1 GPU" if world == 1 or ref_arm else
+                                      f"cache split by token range over {world} GPUs, weights replicated",
+                       "l2": f"{SETS} weight sets in rotation ({SETS * LAYERS * weight_bytes / 1e9:.2f} GB) + "
+                             f"{LAYERS * decode_bytes(ctx) / 1e9:.2f} GB of cache per step"},
+            "e2e": {"value": round(nbytes_e2e / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
+                    "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2,
+                    "ms_per_step": round(ms_e2e / steps, 4)},
+            "gpu_launches": (LAYERS * 11 if ref_arm else LAYERS * 3) * steps, "clocks": env.sampler.summary(m0, m1),
+        }
+    if ref_arm:
+        line["impl"] = "reference"
+        line["cpu_baseline"] = {"value": line["value"], "unit": "GB/s", "cores": 0, "kind": "reference",
+                                "sample": "whole workload on the GPU: the reference has no CPU implementation of this path"}
+        line["e2e"].update({"h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0, "value": line["value"]})
+        return line
+    # ---- check (one GPU): layer 0 of one more step against the oracle layer on the same input, and
+    # the final row against the oracle's 16-layer chain (reported; roundings build up over layers)
+    if world == 1:
+        w = Ws[0]
+        L0 = pool.length(seq)
+        kk = torch.zeros(KV_HEADS, L0 + 1, D, dtype=torch.bfloat16, device=dev)
+        vv = torch.zeros_like(kk)
+        caches = []
+        for l in range(LAYERS):
+            pool.gather_kv(l, seq, kk, vv, L0 + 1)
+            torch.cuda.synchronize()
+            caches.append((_u16(kk), _u16(vv)))
+        pool.reserve(seq, L0 + 1)
+        pool.batch_set([seq])
+        y0 = torch.zeros(1, H, dtype=torch.bfloat16, device=dev)
+        paged.attention_step(pool, descs[0], 0, 1, x_dev, y0, cos, sin)
+        paged.attention_step(pool, descs[0], 1, LAYERS, y0, y_dev, cos, sin)
+        torch.cuda.synchronize()
+        pool.check()
+        t0 = time.perf_counter()
+        cur = _u16(x_host)
+        first = None
+        for l in range(LAYERS):
+            K, V = caches[l]
+            xn = orc.rmsnorm(cur, _u16(w["nw"][l]), 1e-5)
+            q = orc.gemm_bf16(xn, _u16(w["wq"][l])).reshape(1, Q_HEADS, D)
+            k = orc.gemm_bf16(xn, _u16(w["wk"][l])).reshape(1, KV_HEADS, D)
+            v = orc.gemm_bf16(xn, _u16(w["wv"][l])).reshape(1, KV_HEADS, D)
+            K[:, L0] = orc.rope(k, cos_h, sin_h, L0, 1)[:, 0]
+            V[:, L0] = v[0]
+            O, _ = orc.attention(orc.rope(q, cos_h, sin_h, L0, 1), K, V, L0 + 1)
+            lin = orc.gemm_bf16(orc.f32_to_bf16(O[:, 0].reshape(1, NQ)), _u16(w["wo"][l]))
+            cur = orc.f32_to_bf16(orc.bf16_to_f32(cur) + orc.bf16_to_f32(lin))
+            if l == 0:
+                first = cur
+        dt = time.perf_counter() - t0
+        e0 = row_rel_err(orc.bf16_to_f32(_u16(y0)), orc.bf16_to_f32(first), row=H)
+        e15 = row_rel_err(orc.bf16_to_f32(_u16(y_dev)), orc.bf16_to_f32(cur), row=H)
+        line["checks"] = {"oracle_layer0_max_err_over_row_max": e0, "oracle_layer0_ok": bool(e0 <= 2.0 ** -6),
+                          "oracle_16_layer_chain_max_err_over_row_max": e15}
+        line["cpu_baseline"] = {"value": round(LAYERS * (decode_bytes(L0 + 1) + weight_bytes) / dt / 1e9, 3), "unit": "GB/s",
+                                "cores": orc.num_threads(), "kind": "port",
+                                "sample": f"one token through all {LAYERS} layers with the CPU oracle chain, {dt:.2f} s"}
+        line["roofline"] = {"bound": "hbm", "kernel": "qkv_project_kernel + decode_kernel + qkv_project_kernel (3 launches per layer)",
+                            "achieved": round(value, 1), "peak": peak, "unit": "GB/s", "frac": round(value / peak, 4),
+                            "peak_source": f"of {peak_kind}", "us_per_launch": round(ms / steps * 1e3 / LAYERS / 3, 2),
+                            "bytes_per_launch": (decode_bytes(ctx) + weight_bytes) // 3, "traffic": None}
+        if sub and ref is not None:
+            ref_step()
+            rms = local_timed(torch, ref_step, 2) / 2
+            rb = LAYERS * (decode_bytes(ctx) + weight_bytes)
+            line["reference"] = {"value": round(rb / (rms * 1e-3) / 1e9, 2), "unit": "GB/s",
+                                 "us_per_layer": round(rms * 1e3 / LAYERS, 2),
+                                 "how": "the reference's RMSNorm, 3 GEMMs, RoPE kernels, append copies, attention kernel, "
+                                        "layout kernel, output GEMM and residual add per layer, with its synchronisations"}
+    env.barrier()
+    if xchg is not None:
+        xchg.close()
+    if pool is not None:
+        pool.close()
+    return line
+
 # =============================================================================
 def decode4k_sub(env: Env, args):
     line = run_decode(env, args, "decode4k", sub=True)
@@ -1405,6 +1646,7 @@ SUB_BLOCKS = {
     "out_project": lambda env, a: run_qkv(env, a, sub=True, which="out"),
     "qkv_decode": lambda env, a: run_qkv(env, a, sub=True, which="qkv"),
     "qkv_prefill": lambda env, a: run_qkv_prefill(env, a, sub=True),
+    "decode_chain": lambda env, a: run_chain(env, a, sub=True),
 }
 
 
@@ -1424,7 +1666,9 @@ def main():
     ap.add_argument("--repeats", type=int, default=15, help="decode: timed blocks of --steps steps; the median is reported")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode128k",
-                    choices=sorted(WORKLOADS) + ["prefill2k", "append2k", "batch64", "qkv_decode", "out_project", "qkv_prefill"])
+                    choices=sorted(WORKLOADS) + ["prefill2k", "append2k", "batch64", "qkv_decode", "out_project", "qkv_prefill",
+                                                  "decode_chain"])
+    ap.add_argument("--chain-ctx", type=int, default=4096, help="decode_chain: context length")
     ap.add_argument("--no-sub", action="store_true", help="default workload: skip the sub-blocks")
     ap.add_argument("--sub", default="", help="default workload: comma-separated sub-blocks to run (default: all)")
     ap.add_argument("--seqs", type=int, default=64, help="batch64: number of sequences")
@@ -1447,7 +1691,7 @@ def main():
     rank, _, world = dist_env()
     if args.impl == "reference" and rank != 0:
         return  # the reference is single-GPU: rank 0 alone runs it
-    sharded = args.workload in WORKLOADS or args.workload in ("batch64", "qkv_decode", "out_project")
+    sharded = args.workload in WORKLOADS or args.workload in ("batch64", "qkv_decode", "out_project", "decode_chain")
     env = Env(want_group=(args.impl == "ours" and sharded))
     line = None
     if args.workload in WORKLOADS:
@@ -1483,6 +1727,8 @@ def main():
         line = run_prefill(env, args, append_only=True)
     elif args.workload == "batch64":
         line = run_batch(env, args)
+    elif args.workload == "decode_chain":
+        line = run_chain(env, args)
     if rank == 0 and line is not None:
         print(json.dumps(line), flush=True)
     env.sampler.stop()
