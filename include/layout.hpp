@@ -6,12 +6,5 @@
 #include <cstdlib>
 #include <cuda_bf16.h>
 
-#include "legacy_kernels.h"
-#include "paged_attention.h"
-
-inline void launch_flash_output_layout(const __nv_bfloat16* input, __nv_bfloat16* output, int tokens) {
-  if (lt_launch_flash_output_layout(input, output, tokens, nullptr) != PA_OK) {
-    printf("CUDA Error: %s\n", pa_last_error());
-    exit(EXIT_FAILURE);
-  }
-}
+// Defined in libpaged_attention.so (csrc/compat_cxx.cu) with this exact C++ signature.
+void launch_flash_output_layout(const __nv_bfloat16* input, __nv_bfloat16* output, int tokens);

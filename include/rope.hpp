@@ -9,9 +9,6 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
-#include "legacy_kernels.h"
-#include "paged_attention.h"
-
 constexpr int ROPE_HEADS = 32;
 constexpr int ROPE_KV_HEADS = 8;
 constexpr int ROPE_HEAD_DIM = 64;
@@ -31,18 +28,11 @@ do {                                                          \
 } while(0)
 #endif
 
-inline void launch_rope_qkv(const __nv_bfloat16* q_in, __nv_bfloat16* q_out,
-                            const __nv_bfloat16* k_in, __nv_bfloat16* k_out,
-                            const __nv_bfloat16* v_in, __nv_bfloat16* v_out,
-                            float* cos_table, float* sin_table, int tokens,
-                            int position_offset) {
-  const int rc = lt_launch_rope_qkv(q_in, q_out, k_in, k_out, v_in, v_out, cos_table, sin_table,
-                                    tokens, position_offset, nullptr);
-  if (rc != PA_OK) {
-    printf("CUDA Error %s:%d : %s\n", __FILE__, __LINE__, pa_last_error());
-    exit(EXIT_FAILURE);
-  }
-  CUDA_CHECK(cudaDeviceSynchronize());
-}
+// Defined in libpaged_attention.so (csrc/compat_cxx.cu) with this exact C++ signature.
+void launch_rope_qkv(const __nv_bfloat16* q_in, __nv_bfloat16* q_out,
+                     const __nv_bfloat16* k_in, __nv_bfloat16* k_out,
+                     const __nv_bfloat16* v_in, __nv_bfloat16* v_out,
+                     float* cos_table, float* sin_table, int tokens,
+                     int position_offset);
 
 #endif

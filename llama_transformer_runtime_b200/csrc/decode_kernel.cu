@@ -8,11 +8,15 @@
 //
 // Decode is an HBM stream: 4 KiB (K tile + V tile of one block and KV head)
 // per 16 tokens, read exactly once for the 4 query heads that share it.
-//   * grid (chunk, kv head, sequence); a CTA owns a contiguous run of blocks of
-//     the sequence's table, its warps take them round-robin;
-//   * every warp runs its own ring of STAGES 4 KiB buffers filled by bulk
-//     (TMA) copies that complete on per-stage mbarriers, so WARPS*STAGES*4 KiB
-//     are in flight per CTA and no CTA-wide barrier sits in the loop;
+//   * a CTA owns a contiguous run of blocks (a chunk) of one sequence's table
+//     for one KV head; its WARPS consumer warps take the blocks round-robin;
+//   * every consumer warp has its own ring of STAGES 4 KiB buffers.  A producer
+//     warp fills them: its lane w waits for a stage of warp w to be handed back
+//     (empty barrier) and issues the next bulk (TMA) copy, which completes on
+//     the stage's full barrier.  Arming a barrier and issuing a bulk copy costs
+//     a thread about 300 cycles — a quarter of a tile's time when the consumers
+//     did it themselves.  WARPS*STAGES*4 KiB are in flight per CTA and no
+//     CTA-wide barrier sits in the loop;
 //   * tiles land in shared memory exactly as stored (rows of 128 bytes, chunks
 //     XOR-swizzled), which ldmatrix reads without bank conflicts;
 //   * the 4 query heads are rows 0..3 of an m16n8k16 A fragment (rows 4..15
@@ -20,13 +24,13 @@
 //     fragments with quad shuffles, base 2, fp32 (numerics of the reference
 //     kernel: scale after the dot product, sum of un-rounded probabilities,
 //     probabilities rounded to bf16 for P*V, flashattention.cu:249-336);
-//   * warps merge through shared memory; chunks merge through a workspace, the
-//     last CTA to arrive for a (sequence, KV head) does the combine and writes
-//     the [tokens, 2048]-layout row directly;
+//   * warps merge through shared memory; chunks merge through a workspace.  In
+//     the kernel of one layer (decode_kernel) the last CTA to take a ticket for
+//     a (sequence, KV head) combines and writes the [tokens, 2048]-layout row;
 //   * a multi-layer decode step is ONE cooperative launch (decode_step_kernel):
-//     streaming CTAs go from layer to layer without waiting, one or two extra
-//     CTAs per (sequence, KV head) combine (and, across GPUs, exchange and
-//     merge) the layers behind them.
+//     the streaming CTAs go from layer to layer as one flat stream of tiles,
+//     1, 2 or 4 extra CTAs per (sequence, KV head) combine (and, across GPUs,
+//     exchange and merge) the layers behind them.
 #include "kernels.cuh"
 #include "rope.cuh"
 
@@ -50,6 +54,12 @@ struct DecodeSmem {
   static constexpr int step_bytes(int layers) { return 128 + kStepQ + layers * kGroup * kHeadDim * 2; }
   static constexpr int kStepThreads = (WARPS + 2) * 32;  // consumers + producer warp + publisher warp
 };
+
+// Barrier among the first `threads` threads of the CTA (the consumer warps); the producer and
+// publisher warps of a streaming CTA never take part, so __syncthreads is not used past set-up.
+__device__ __forceinline__ void consumer_sync(int threads) {
+  asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
+}
 
 // One 8-byte word {value, step number}: value in the low half, step number in the high half,
 // moved by ONE scalar 64-bit access, which the ISA makes single-copy atomic (a vector access is a
@@ -107,12 +117,12 @@ __device__ __forceinline__ void write_row_outputs(const DecodeParams& p, int z, 
 
 // After a (sequence, KV head) group's rows have been pushed: make them visible
 // system-wide, then publish the step number in every rank's flag for this
-// source rank and head.  Called by all threads of the CTA.
-__device__ __forceinline__ void publish_exchange(const DecodeParams& p, int z, int h) {
+// source rank and head.  Called by all `nthreads` consumer threads of the CTA.
+__device__ __forceinline__ void publish_exchange(const DecodeParams& p, int z, int h, int nthreads) {
   if (p.hs_world > 0) {
     // rows of this (sequence, KV head) are stored everywhere: count one arrival
     // per rank, released at system scope after the CTA's stores
-    __syncthreads();
+    consumer_sync(nthreads);
     if ((int)threadIdx.x < p.hs_world) {
       __threadfence_system();
       asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.hs_counter[threadIdx.x]) : "memory");
@@ -122,7 +132,7 @@ __device__ __forceinline__ void publish_exchange(const DecodeParams& p, int z, i
   // the CTA barrier orders every thread's peer stores before the publishing
   // threads' system-scope fence, which is cumulative: one fence per flag
   // instead of one per thread
-  __syncthreads();
+  consumer_sync(nthreads);
   if ((int)threadIdx.x < p.xchg_world) {
     __threadfence_system();
     unsigned int* flag = p.xchg_flag[threadIdx.x] + ((size_t)p.xchg_rank * p.xchg_groups + z * p.kv_heads + h);
@@ -134,14 +144,14 @@ __device__ __forceinline__ void publish_exchange(const DecodeParams& p, int z, i
 // rank's partial of (sequence z, KV head h) waits — bounded — until every
 // rank's partial of that group has landed in THIS rank's buffer, merges the
 // group's 4 rows from local memory and writes them as bf16.
-__device__ __forceinline__ void exchange_wait_merge(const DecodeParams& p, int z, int h, int* s_flag) {
+__device__ __forceinline__ void exchange_wait_merge(const DecodeParams& p, int z, int h, int* s_flag, int nthreads) {
   if (p.xchg_world <= 0 || !p.xchg_out) return;
   if (threadIdx.x == 0) *s_flag = 1;
-  __syncthreads();
+  consumer_sync(nthreads);
   const int q_heads = p.kv_heads * kGroup;
   const unsigned long long* base =
       p.xchg_ll[p.xchg_rank] + (size_t)(p.xchg_seq & (kXchgWordSlots - 1u)) * p.xchg_world * p.xchg_rows * kXchgRowFloats;
-  for (int idx = threadIdx.x; idx < kGroup * kHeadDim; idx += blockDim.x) {
+  for (int idx = threadIdx.x; idx < kGroup * kHeadDim; idx += nthreads) {
     const int r = idx >> 6, d = idx & 63;
     const int head = h * kGroup + r;
     const int row = z * q_heads + head;
@@ -198,7 +208,7 @@ __device__ __forceinline__ void exchange_wait_merge(const DecodeParams& p, int z
     }
     p.xchg_out[(size_t)z * p.xchg_out_stride + head * kHeadDim + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
   }
-  __syncthreads();
+  consumer_sync(nthreads);
   if (!*s_flag && threadIdx.x == 0) atomicExch(p.status, kStatusTimeout);
 }
 
@@ -226,298 +236,9 @@ __device__ __forceinline__ DecodeParams step_layer_params(const DecodeStepParams
   return p;
 }
 
-// Work of one CTA on chunk x of (sequence z, KV head h) of one layer (the kernel of one layer):
-// partials meet through arrival tickets and the last CTA of a (sequence, head) combines them.
-template <int WARPS, int STAGES>
-__device__ __forceinline__ void decode_cta(const DecodeParams& p, const int x, const int h, const int z,
-                                           unsigned char* smem) {
-  uint32_t tile_base = 0;
-  using S = DecodeSmem<WARPS, STAGES>;
-  unsigned char* tiles = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kTiles);
-  float* mrg = reinterpret_cast<float*>(smem + S::kTiles + S::kBars);
-  float* mrg_o = mrg;                                // [WARPS][4][64]
-  float* mrg_m = mrg + WARPS * kGroup * kHeadDim;     // [WARPS][4]
-  float* mrg_l = mrg_m + WARPS * kGroup;              // [WARPS][4]
-  __shared__ unsigned int s_ticket;
-  __shared__ int s_wait_ok;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const BatchEntry e = p.batch[z];
-  const int n_blocks = (e.kv_len + kBlockTok - 1) / kBlockTok;
-  const int n_chunks = max(1, (n_blocks + p.chunk_blocks - 1) / p.chunk_blocks);
-  if (x >= n_chunks) return;
-  const int blk_lo = x * p.chunk_blocks;
-  const int cnt = max(0, min(n_blocks, blk_lo + p.chunk_blocks) - blk_lo);
-  const int my_n = cnt > warp ? (cnt - warp + WARPS - 1) / WARPS : 0;
-  const int32_t* table = p.tables + (size_t)e.seq * p.max_blocks_per_seq + blk_lo + warp;
-  const int q_heads = p.kv_heads * kGroup;
-
-  const uint32_t tile0 = smem_u32(tiles) + warp * STAGES * kPairBytes;
-  const uint32_t bar0 = smem_u32(bars) + warp * STAGES * 8;
-  if (tile_base == 0) {  // first use of this warp's ring
-    if (lane == 0) {
-#pragma unroll
-      for (int s = 0; s < STAGES; s++) mbar_init(bar0 + s * 8, 1);
-      mbar_fence_init();
-      fence_proxy_async_smem();
-    }
-    __syncwarp();
-  }
-  const uint32_t ring0 = tile_base;  // ring position of this layer's tile 0
-  tile_base += (uint32_t)my_n;
-
-  // Block-table entries of this warp's blocks, 32 at a time, one per lane.
-  int tbase = 0;
-  int tbl_reg = lane < my_n ? table[(size_t)lane * WARPS] : 0;
-  const char* head_base = p.storage + (size_t)h * kPairBytes;
-  const size_t block_stride = (size_t)p.kv_heads * kPairBytes;
-
-  auto issue = [&](int i) {
-    if (i >= tbase + 32) {
-      tbase += 32;
-      const int ii = tbase + lane;
-      tbl_reg = ii < my_n ? table[(size_t)ii * WARPS] : 0;
-    }
-    int blk = __shfl_sync(0xffffffffu, tbl_reg, i - tbase);
-    if (lane == 0) {
-      if (blk < 0 || blk >= p.num_blocks) {
-        atomicExch(p.status, kStatusBadBlock);
-        blk = 0;
-      }
-      const int st = (int)((ring0 + (uint32_t)i) % STAGES);
-      mbar_expect_tx(bar0 + st * 8, kPairBytes);
-      bulk_g2s(tile0 + st * kPairBytes, head_base + (size_t)blk * block_stride, kPairBytes,
-               bar0 + st * 8);
-    }
-  };
-
-  // Fused append (pa_decode_step): the warp that owns the sequence's last block
-  // first writes the new token's K (RoPE applied) and V rows of this head into
-  // that block — the same arithmetic and placement as append_kernel — and
-  // orders those generic-proxy stores before its own bulk (async-proxy) reads.
-  // pdl == 2: q, k_new and v_new are the output of the kernel in front (the projections of this
-  // layer).  The cache, the tables and the batch are not: every warp but the one that appends
-  // starts its first bulk copies before it waits for that kernel.
-  const bool appends = p.fuse && e.n_new > 0 && x == n_chunks - 1 && cnt > 0 && warp == (cnt - 1) % WARPS;
-  if (p.pdl == 2 && appends) asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (appends) {
-    if (lane < 8) {
-      const int lpos = e.kv_len - 1;
-      const int pos = e.kv_pos_off + lpos;
-      const int blk = p.tables[(size_t)e.seq * p.max_blocks_per_seq + lpos / kBlockTok];
-      const int slot = lpos % kBlockTok;
-      const int c = lane & 3, is_v = lane >> 2;
-      if (blk < 0 || blk >= p.num_blocks) {
-        atomicExch(p.status, kStatusBadBlock);
-      } else {
-        const __nv_bfloat16* row = (is_v ? p.v_new : p.k_new) + ((size_t)e.kv_row_off * p.kv_heads + h) * kHeadDim;
-        const uint4* src = reinterpret_cast<const uint4*>(row);
-        char* tile = p.storage_w + tile_off(blk, p.kv_heads, h, is_v);
-        uint4 lo = src[c], hi = src[c + 4];
-        if (!is_v) {
-          const float4* cs = reinterpret_cast<const float4*>(p.cos_table + (size_t)pos * 32 + c * 8);
-          const float4* sn = reinterpret_cast<const float4*>(p.sin_table + (size_t)pos * 32 + c * 8);
-          float4 c8[2] = {cs[0], cs[1]}, s8[2] = {sn[0], sn[1]};
-          uint4 ylo, yhi;
-          rope_chunks<1>(lo, hi, reinterpret_cast<const float*>(c8), reinterpret_cast<const float*>(s8), ylo, yhi);
-          lo = ylo;
-          hi = yhi;
-        }
-        *reinterpret_cast<uint4*>(tile + tile_chunk_off(slot, c)) = lo;
-        *reinterpret_cast<uint4*>(tile + tile_chunk_off(slot, c + 4)) = hi;
-      }
-    }
-    asm volatile("fence.proxy.async;" ::: "memory");
-    __syncwarp();
-  }
-
-  for (int i = 0; i < STAGES && i < my_n; i++) issue(i);
-  if (p.pdl == 2 && !appends) asm volatile("griddepcontrol.wait;" ::: "memory");
-
-  // Query fragments: rows 0..3 are the group's heads, the rest zero.
-  const int qrow = lane >> 2, qcol = (lane & 3) * 2;
-  uint32_t qa[4][4];
-#pragma unroll
-  for (int ks = 0; ks < 4; ks++) {
-    qa[ks][0] = qa[ks][1] = qa[ks][2] = qa[ks][3] = 0u;
-    if (qrow < kGroup) {
-      const __nv_bfloat16* qp =
-          p.q + ((size_t)z * q_heads + h * kGroup + qrow) * kHeadDim + ks * 16 + qcol;
-      qa[ks][0] = *reinterpret_cast<const uint32_t*>(qp);
-      qa[ks][2] = *reinterpret_cast<const uint32_t*>(qp + 8);
-    }
-  }
-  if (p.fuse && qrow < kGroup) {
-    // p.q is the un-rotated query: RoPE pairs element c with c+32, i.e. this
-    // thread's values of k-step ks with those of k-step ks+2
-    const float* cs = p.cos_table + (size_t)e.q_pos0 * 32;
-    const float* sn = p.sin_table + (size_t)e.q_pos0 * 32;
-#pragma unroll
-    for (int ks = 0; ks < 2; ks++)
-#pragma unroll
-      for (int half = 0; half < 2; half++) {
-        const int c0 = ks * 16 + qcol + half * 8;
-        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&qa[ks][half * 2]);
-        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&qa[ks + 2][half * 2]);
-        float y0a, y1a, y0b, y1b;
-        rope_pair<1>(__low2float(a), __low2float(b), cs[c0], sn[c0], y0a, y1a);
-        rope_pair<1>(__high2float(a), __high2float(b), cs[c0 + 1], sn[c0 + 1], y0b, y1b);
-        qa[ks][half * 2] = pack_bf16(y0a, y0b);
-        qa[ks + 2][half * 2] = pack_bf16(y1a, y1b);
-      }
-    if (p.q_rot_out && x == 0 && warp == 0) {
-      __nv_bfloat16* qo = p.q_rot_out + ((size_t)z * q_heads + h * kGroup + qrow) * kHeadDim + qcol;
-#pragma unroll
-      for (int ks = 0; ks < 4; ks++) {
-        *reinterpret_cast<uint32_t*>(qo + ks * 16) = qa[ks][0];
-        *reinterpret_cast<uint32_t*>(qo + ks * 16 + 8) = qa[ks][2];
-      }
-    }
-  }
-
-  float o[8][4];
-#pragma unroll
-  for (int nt = 0; nt < 8; nt++) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
-  float m_run = -INFINITY, l_run = 0.f;
-
-  const int mj = lane >> 3, rr = lane & 7;
-  const uint32_t k_row_off = (uint32_t)(((mj >> 1) * 8 + rr) * 128);
-  const uint32_t v_row_off = (uint32_t)(kTileBytes + ((mj & 1) * 8 + rr) * 128);
-  bool failed = false;
-
-  for (int i = 0; i < my_n; i++) {
-    const int st = (int)((ring0 + (uint32_t)i) % STAGES);
-    const bool ok = mbar_wait(bar0 + st * 8, ((ring0 + (uint32_t)i) / STAGES) & 1u);
-    if (!__all_sync(0xffffffffu, ok)) {
-      failed = true;
-      break;
-    }
-    const uint32_t tile = tile0 + st * kPairBytes;
-
-    float s[2][4];
-#pragma unroll
-    for (int nt = 0; nt < 2; nt++) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-#pragma unroll
-    for (int ks = 0; ks < 4; ks++) {
-      uint32_t b0, b1, b2, b3;
-      ldsm_x4(b0, b1, b2, b3, tile + k_row_off + ((((ks * 2 + (mj & 1)) ^ rr)) << 4));
-      mma_bf16(s[0], qa[ks], b0, b1);
-      mma_bf16(s[1], qa[ks], b2, b3);
-    }
-
-    // scaled scores (base 2), tail mask, online softmax on rows lane/4
-    const int key0 = (blk_lo + warp + i * WARPS) * kBlockTok + qcol;
-    float t[4];
-    t[0] = s[0][0] * p.scale_log2;
-    t[1] = s[0][1] * p.scale_log2;
-    t[2] = s[1][0] * p.scale_log2;
-    t[3] = s[1][1] * p.scale_log2;
-    if (key0 + 9 >= e.kv_len) {
-      if (key0 >= e.kv_len) t[0] = -INFINITY;
-      if (key0 + 1 >= e.kv_len) t[1] = -INFINITY;
-      if (key0 + 8 >= e.kv_len) t[2] = -INFINITY;
-      if (key0 + 9 >= e.kv_len) t[3] = -INFINITY;
-    }
-    float mx = fmaxf(fmaxf(t[0], t[1]), fmaxf(t[2], t[3]));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    const float m_new = fmaxf(m_run, mx);
-    const float corr = ex2(m_run - m_new);
-    m_run = m_new;
-    const float p0 = ex2(t[0] - m_new), p1 = ex2(t[1] - m_new);
-    const float p2 = ex2(t[2] - m_new), p3 = ex2(t[3] - m_new);
-    l_run = l_run * corr + ((p0 + p1) + (p2 + p3));
-    uint32_t pa[4];
-    pa[0] = pack_bf16(p0, p1);
-    pa[1] = 0u;
-    pa[2] = pack_bf16(p2, p3);
-    pa[3] = 0u;
-#pragma unroll
-    for (int nt = 0; nt < 8; nt++) {
-      o[nt][0] *= corr;
-      o[nt][1] *= corr;
-    }
-#pragma unroll
-    for (int np = 0; np < 4; np++) {
-      uint32_t b0, b1, b2, b3;
-      ldsm_x4_t(b0, b1, b2, b3, tile + v_row_off + ((((np * 2 + (mj >> 1)) ^ rr)) << 4));
-      mma_bf16(o[2 * np], pa, b0, b1);
-      mma_bf16(o[2 * np + 1], pa, b2, b3);
-    }
-
-    __syncwarp();
-    if (i + STAGES < my_n) {
-      if (lane == 0) fence_proxy_async_smem();
-      issue(i + STAGES);
-    }
-  }
-  if (failed && lane == 0) atomicExch(p.status, kStatusTimeout);
-
-  // Programmatic dependent launch (layers of one decode step): the streaming
-  // above only read the cache; everything written from here on (workspace,
-  // tickets, outputs, exchange) must wait until the previous layer's kernel —
-  // which shares the workspace — has completed.
-  if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
-
-  // ---- merge the warps of this CTA -------------------------------------------
-  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-  if (qrow < kGroup) {
-    float* orow = mrg_o + (warp * kGroup + qrow) * kHeadDim;
-#pragma unroll
-    for (int nt = 0; nt < 8; nt++)
-      *reinterpret_cast<float2*>(orow + nt * 8 + qcol) = make_float2(o[nt][0], o[nt][1]);
-    if ((lane & 3) == 0) {
-      mrg_m[warp * kGroup + qrow] = m_run;
-      mrg_l[warp * kGroup + qrow] = l_run;
-    }
-  }
-  __syncthreads();
-
-  const int item = (z * p.kv_heads + h) * p.max_chunks + x;
-  for (int idx = threadIdx.x; idx < kGroup * kHeadDim; idx += WARPS * 32) {
-    const int r = idx >> 6, d = idx & 63;
-    float M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < WARPS; w++) M = fmaxf(M, mrg_m[w * kGroup + r]);
-    float L = 0.f, O = 0.f;
-#pragma unroll
-    for (int w = 0; w < WARPS; w++) {
-      const float mw = mrg_m[w * kGroup + r];
-      const float wgt = mw == -INFINITY ? 0.f : ex2(mw - M);
-      L += wgt * mrg_l[w * kGroup + r];
-      O += wgt * mrg_o[(w * kGroup + r) * kHeadDim + d];
-    }
-    if (n_chunks == 1) {
-      write_row_outputs(p, z, h, r, d, O, M, L);
-    } else {
-      p.ws_acc[(size_t)item * (kGroup * kHeadDim) + idx] = O;
-      if (d == 0) {
-        p.ws_ml[(size_t)item * (2 * kGroup) + r] = M;
-        p.ws_ml[(size_t)item * (2 * kGroup) + kGroup + r] = L;
-      }
-    }
-  }
-  if (n_chunks == 1) {
-    publish_exchange(p, z, h);
-    exchange_wait_merge(p, z, h, &s_wait_ok);
-    return;
-  }
-
-  // ---- combine across chunks: the last CTA to arrive does it ---------------
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) s_ticket = atomicAdd(&p.ws_count[z * p.kv_heads + h], 1u);
-  __syncthreads();
-  if (s_ticket != (unsigned)(n_chunks - 1)) return;
-  __threadfence();
-  combine_pair<WARPS, STAGES>(p, z, h, n_chunks, smem, &s_wait_ok);
-}
-
 // Combine the n_chunks partials of (sequence z, KV head h) from the workspace,
 // write the rows (and run the cross-GPU exchange when one is configured), and
-// clear the pair's arrival counter.  Called by all threads of a CTA.
+// clear the pair's arrival counter.  Called by the WARPS * 32 consumer threads of a CTA.
 template <int WARPS, int STAGES>
 __device__ __forceinline__ void combine_pair(const DecodeParams& p, const int z, const int h, const int n_chunks,
                                              unsigned char* smem, int* s_wait_ok_p) {
@@ -554,7 +275,7 @@ __device__ __forceinline__ void combine_pair(const DecodeParams& p, const int z,
   for (int u = 0; u < 4; u++)
     v0[u] = g + u * G < n_chunks ? __ldcg(src + (size_t)(g + u * G) * 64) : make_float4(0.f, 0.f, 0.f, 0.f);
   for (int i = threadIdx.x; i < n_chunks * 8; i += T) cm[i] = __ldcg(p.ws_ml + item0 * 8 + i);
-  __syncthreads();
+  consumer_sync(T);
   for (int r = warp; r < kGroup; r += WARPS) {
     float M = -INFINITY;
     for (int c = lane; c < n_chunks; c += 32) M = fmaxf(M, cm[c * 8 + r]);
@@ -574,7 +295,7 @@ __device__ __forceinline__ void combine_pair(const DecodeParams& p, const int z,
       mrg_l[r] = L;
     }
   }
-  __syncthreads();
+  consumer_sync(T);
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
   for (int u = 0; u < 4; u++) {
@@ -608,7 +329,7 @@ __device__ __forceinline__ void combine_pair(const DecodeParams& p, const int z,
     acc.w += wgt * v.w;
   }
   reinterpret_cast<float4*>(mrg_o)[g * 64 + q4] = acc;
-  __syncthreads();
+  consumer_sync(T);
   for (int idx = threadIdx.x; idx < kGroup * kHeadDim; idx += T) {
     float O = 0.f;
 #pragma unroll
@@ -616,49 +337,38 @@ __device__ __forceinline__ void combine_pair(const DecodeParams& p, const int z,
     write_row_outputs(p, z, h, idx >> 6, idx & 63, O, mrg_m[idx >> 6], mrg_l[idx >> 6]);
   }
   if (threadIdx.x == 0) p.ws_count[z * p.kv_heads + h] = 0u;
-  publish_exchange(p, z, h);
-  exchange_wait_merge(p, z, h, s_wait_ok_p);
+  publish_exchange(p, z, h, T);
+  exchange_wait_merge(p, z, h, s_wait_ok_p, T);
 }
 
-template <int WARPS, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32)
-decode_kernel(DecodeParams p) {
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem =
-      reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
-  // let the next layer's kernel take SMs as soon as this one's CTAs leave them
-  if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  decode_cta<WARPS, STAGES>(p, blockIdx.x, blockIdx.y, blockIdx.z, smem);
-}
+// What a streaming CTA needs beyond the layer-0 launch descriptor: how many layers it walks and
+// how far apart the layers' tensors are.  The kernel of one layer uses layers = 1.
+struct StreamArgs {
+  int layers, n_seqs, ws_layer_items;
+  long long q_layer_stride, kv_layer_stride;
+  unsigned long long layer_bytes;
+};
 
-// ---- the whole multi-layer decode step as ONE launch --------------------------
-// Layers of a step are independent here (every layer has its own q, k, v rows,
-// cache layer, output rows and workspace slice), so nothing but the kernel
-// boundary made layer l+1 wait for the combine and the exchange of layer l.
-// CTAs [0, n_stream) stream: chunk x of (sequence, head), layer after layer,
-// never waiting on anybody.  One more CTA per (sequence, head) combines: for
-// each layer it waits — bounded — until the pair's n_chunks partials have been
-// counted, merges them, writes the rows and runs the cross-GPU exchange.  The
-// combining CTAs wait on the streaming ones of the same grid, so the launch is
-// cooperative (all CTAs resident).
-// A streaming CTA of the one-launch step: chunk x of (sequence z, KV head h), layer after layer.
+// A streaming CTA: chunk x of (sequence z, KV head h), over a.layers layers.
 // WARPS consumer warps, one producer warp, one publisher warp.
 //  * Everything that does not depend on the tiles is done ONCE, before the first layer: the batch
 //    entry, the CTA's slice of the block table (shared memory; it is the same for every layer,
-//    only the cache base moves), the rotation of every layer's 4 query rows (kept in shared memory
-//    as bf16, ready to be picked up as A fragments), the rotated-query output rows and the
-//    appended K/V rows of all layers.
+//    only the cache base moves), every layer's 4 query rows (rotated here when the append is
+//    fused in; kept in shared memory as bf16, ready to be picked up as A fragments), the
+//    rotated-query output rows and the appended K/V rows of all layers.
 //  * The producer warp's lane w feeds consumer warp w's ring: it waits for a freed stage (empty
 //    barrier) and issues the next bulk copy, across layer borders, so the tiles of layer l+1 are
-//    in flight while the consumers merge layer l.  Arming a barrier and issuing a bulk copy costs
-//    a thread about 300 cycles; in the consumers' loop that was a quarter of the time per tile.
-//  * A layer end costs the consumers two barriers among themselves and one partial; the arrival
-//    count is released by the publisher warp, off their path (a gpu-scope release takes ~0.6 us).
-template <int WARPS, int STAGES>
-__device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, const int x, const int h, const int z,
-                                                unsigned char* smem) {
+//    in flight while the consumers merge layer l.
+//  * STEP (the one-launch step): a layer end costs the consumers two barriers among themselves and
+//    one partial; the arrival count is released by the publisher warp, off their path (a
+//    gpu-scope release takes about 0.6 us), and the pair's combining CTA does the rest.
+//  * !STEP (the kernel of one layer): a single chunk writes its rows directly; otherwise partials
+//    meet through arrival tickets and the last CTA of a (sequence, head) combines them.
+template <int WARPS, int STAGES, bool STEP>
+__device__ __forceinline__ void stream_cta(const DecodeParams& b, const StreamArgs& a, const int x, const int h,
+                                           const int z, unsigned char* smem) {
   using S = DecodeSmem<WARPS, STAGES>;
-  const DecodeParams& b = sp.base;
+  constexpr int T = WARPS * 32;  // consumer threads
   unsigned char* tiles = smem;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kTiles);
   float* mrg = reinterpret_cast<float*>(smem + S::kTiles + S::kBars);
@@ -667,20 +377,24 @@ __device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, cons
   float* mrg_l = mrg_m + WARPS * kGroup;              // [WARPS][4]
   uint64_t* empty_bars = reinterpret_cast<uint64_t*>(smem + S::kStepEmpty);
   int32_t* tbl_s = reinterpret_cast<int32_t*>(smem + S::kStepTbl);
-  __nv_bfloat16* qsm = reinterpret_cast<__nv_bfloat16*>(smem + S::kStepQ);  // [layers][4][64] rotated
+  __nv_bfloat16* qsm = reinterpret_cast<__nv_bfloat16*>(smem + S::kStepQ);  // [layers][4][64], rotated
+  __shared__ unsigned int s_ticket;
+  __shared__ int s_wait_ok;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int layers = sp.layers;
+  const int layers = a.layers;
   const BatchEntry e = b.batch[z];
   const int n_blocks = (e.kv_len + kBlockTok - 1) / kBlockTok;
   const int n_chunks = max(1, (n_blocks + b.chunk_blocks - 1) / b.chunk_blocks);
-  if (x >= n_chunks) return;  // the grid holds exactly the chunks of every sequence (CTA-uniform)
+  if (x >= n_chunks) return;  // CTA-uniform
   const int blk_lo = x * b.chunk_blocks;
   const int cnt = max(0, min(n_blocks, blk_lo + b.chunk_blocks) - blk_lo);
   const int32_t* table = b.tables + (size_t)e.seq * b.max_blocks_per_seq + blk_lo;
   const int q_heads = b.kv_heads * kGroup;
   // layers whose partial this CTA has stored: written by consumer thread 0, polled by the publisher
   const uint32_t pub_word = smem_u32(empty_bars) + WARPS * STAGES * 8;
+  // this CTA writes the new token's K/V rows into the sequence's last block before streaming it
+  const bool appends = b.fuse && e.n_new > 0 && x == n_chunks - 1 && cnt > 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < WARPS * STAGES; s++) {
@@ -697,42 +411,46 @@ __device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, cons
     // ================================ producer warp ==============================================
     const int held = min(cnt, S::kStepTblCap);
     for (int j = lane; j < held; j += 32) tbl_s[j] = table[j];
-    // Appended rows of ALL layers (the CTA that owns the sequence's last block): same arithmetic
-    // and placement as append_kernel; the generic-proxy stores are ordered before this warp's own
-    // bulk (async-proxy) reads of that block by the proxy fence below.
-    if (e.n_new > 0 && x == n_chunks - 1 && cnt > 0 && lane < 8) {
-      const int lpos = e.kv_len - 1;
-      const int pos = e.kv_pos_off + lpos;
-      const int blk = b.tables[(size_t)e.seq * b.max_blocks_per_seq + lpos / kBlockTok];
-      const int slot = lpos % kBlockTok;
-      const int c = lane & 3, is_v = lane >> 2;
-      if (blk < 0 || blk >= b.num_blocks) {
-        atomicExch(b.status, kStatusBadBlock);
-      } else {
-        float4 c8[2], s8[2];
-        if (!is_v) {
-          const float4* cs = reinterpret_cast<const float4*>(b.cos_table + (size_t)pos * 32 + c * 8);
-          const float4* sn = reinterpret_cast<const float4*>(b.sin_table + (size_t)pos * 32 + c * 8);
-          c8[0] = cs[0], c8[1] = cs[1], s8[0] = sn[0], s8[1] = sn[1];
-        }
-        for (int l = 0; l < layers; l++) {
-          const __nv_bfloat16* row = (is_v ? b.v_new : b.k_new) + (size_t)l * sp.kv_layer_stride +
-                                     ((size_t)e.kv_row_off * b.kv_heads + h) * kHeadDim;
-          const uint4* src = reinterpret_cast<const uint4*>(row);
-          char* tile = b.storage_w + (size_t)l * sp.layer_bytes + tile_off(blk, b.kv_heads, h, is_v);
-          uint4 lo = src[c], hi = src[c + 4];
+    if (appends) {
+      // Appended rows of ALL layers: same arithmetic and placement as append_kernel; the
+      // generic-proxy stores are ordered before this warp's own bulk (async-proxy) reads of that
+      // block by the proxy fence below.  pdl == 2: k_new and v_new are the output of the kernel
+      // in front, so this CTA's producer waits for it first; all other CTAs stream at once.
+      if (b.pdl == 2) asm volatile("griddepcontrol.wait;" ::: "memory");
+      if (lane < 8) {
+        const int lpos = e.kv_len - 1;
+        const int pos = e.kv_pos_off + lpos;
+        const int blk = b.tables[(size_t)e.seq * b.max_blocks_per_seq + lpos / kBlockTok];
+        const int slot = lpos % kBlockTok;
+        const int c = lane & 3, is_v = lane >> 2;
+        if (blk < 0 || blk >= b.num_blocks) {
+          atomicExch(b.status, kStatusBadBlock);
+        } else {
+          float4 c8[2], s8[2];
           if (!is_v) {
-            uint4 ylo, yhi;
-            rope_chunks<1>(lo, hi, reinterpret_cast<const float*>(c8), reinterpret_cast<const float*>(s8), ylo, yhi);
-            lo = ylo;
-            hi = yhi;
+            const float4* cs = reinterpret_cast<const float4*>(b.cos_table + (size_t)pos * 32 + c * 8);
+            const float4* sn = reinterpret_cast<const float4*>(b.sin_table + (size_t)pos * 32 + c * 8);
+            c8[0] = cs[0], c8[1] = cs[1], s8[0] = sn[0], s8[1] = sn[1];
           }
-          *reinterpret_cast<uint4*>(tile + tile_chunk_off(slot, c)) = lo;
-          *reinterpret_cast<uint4*>(tile + tile_chunk_off(slot, c + 4)) = hi;
+          for (int l = 0; l < layers; l++) {
+            const __nv_bfloat16* row = (is_v ? b.v_new : b.k_new) + (size_t)l * a.kv_layer_stride +
+                                       ((size_t)e.kv_row_off * b.kv_heads + h) * kHeadDim;
+            const uint4* src = reinterpret_cast<const uint4*>(row);
+            char* tile = b.storage_w + (size_t)l * a.layer_bytes + tile_off(blk, b.kv_heads, h, is_v);
+            uint4 lo = src[c], hi = src[c + 4];
+            if (!is_v) {
+              uint4 ylo, yhi;
+              rope_chunks<1>(lo, hi, reinterpret_cast<const float*>(c8), reinterpret_cast<const float*>(s8), ylo, yhi);
+              lo = ylo;
+              hi = yhi;
+            }
+            *reinterpret_cast<uint4*>(tile + tile_chunk_off(slot, c)) = lo;
+            *reinterpret_cast<uint4*>(tile + tile_chunk_off(slot, c + 4)) = hi;
+          }
         }
       }
+      asm volatile("fence.proxy.async;" ::: "memory");
     }
-    asm volatile("fence.proxy.async;" ::: "memory");
     __syncwarp();
     if (lane < WARPS) {
       const int w = lane;
@@ -740,11 +458,10 @@ __device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, cons
       const uint32_t tile0 = smem_u32(tiles) + w * STAGES * kPairBytes;
       const uint32_t full0 = smem_u32(bars) + w * STAGES * 8;
       const uint32_t empty0 = smem_u32(empty_bars) + w * STAGES * 8;
-      const char* head_base = b.storage + (size_t)h * kPairBytes;
       const size_t block_stride = (size_t)b.kv_heads * kPairBytes;
       const uint32_t total = (uint32_t)layers * (uint32_t)my_n;
       int i = 0;
-      const char* layer_base = head_base;
+      const char* layer_base = b.storage + (size_t)h * kPairBytes;
       for (uint32_t t = 0; t < total; t++) {
         const int st = (int)(t % STAGES);
         if (t >= (uint32_t)STAGES && !mbar_wait(empty0 + st * 8, ((t / STAGES) - 1u) & 1u)) {
@@ -761,7 +478,7 @@ __device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, cons
         bulk_g2s(tile0 + st * kPairBytes, layer_base + (size_t)blk * block_stride, kPairBytes, full0 + st * 8);
         if (++i == my_n) {
           i = 0;
-          layer_base += sp.layer_bytes;
+          layer_base += a.layer_bytes;
         }
       }
     }
@@ -773,8 +490,8 @@ __device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, cons
     // that follows the CTA's partial stores; acquiring that word and then releasing at gpu scope
     // makes the stores visible (the release is cumulative) to the pair's combining CTA, which
     // acquires the count.  A word, not a barrier phase: the consumers may finish several short
-    // layers while one release is still under way.
-    if (lane == 0) {
+    // layers while one release is still under way.  The kernel of one layer has no use for it.
+    if (STEP && lane == 0) {
       const int pair = z * b.kv_heads + h;
       unsigned int done = 0;
       for (int l = 0; l < layers; l++) {
@@ -787,7 +504,7 @@ __device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, cons
           atomicExch(b.status, kStatusTimeout);
           break;
         }
-        unsigned int* cntp = b.ws_count + (size_t)l * sp.n_seqs * b.kv_heads + pair;
+        unsigned int* cntp = b.ws_count + (size_t)l * a.n_seqs * b.kv_heads + pair;
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(cntp) : "memory");
       }
     }
@@ -799,29 +516,39 @@ __device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, cons
   const uint32_t tile0 = smem_u32(tiles) + warp * STAGES * kPairBytes;
   const uint32_t bar0 = smem_u32(bars) + warp * STAGES * 8;
   const uint32_t empty0 = smem_u32(empty_bars) + warp * STAGES * 8;
-  auto consumer_barrier = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(WARPS * 32) : "memory"); };
 
-  // ---- every layer's query rows, rotated once (fp32, the rounding of append_kernel) ------------
+  // pdl == 2: the query rows are the output of the kernel in front
+  if (b.pdl == 2) asm volatile("griddepcontrol.wait;" ::: "memory");
+  // ---- every layer's query rows into shared memory: rotated here (fp32, the rounding of
+  // append_kernel) when the append is fused in, copied as they are otherwise
   {
-    const float* cs = b.cos_table + (size_t)e.q_pos0 * 32;
-    const float* sn = b.sin_table + (size_t)e.q_pos0 * 32;
     const size_t qrow0 = ((size_t)z * q_heads + h * kGroup) * kHeadDim;
-    for (int idx = threadIdx.x; idx < layers * kGroup * 32; idx += WARPS * 32) {
-      const int c = idx & 31, r = (idx >> 5) & 3, l = idx >> 7;
-      const __nv_bfloat16* qp = b.q + (size_t)l * sp.q_layer_stride + qrow0 + r * kHeadDim;
-      float y0, y1;
-      rope_pair<1>(__bfloat162float(qp[c]), __bfloat162float(qp[c + 32]), cs[c], sn[c], y0, y1);
-      const __nv_bfloat16 b0 = __float2bfloat16_rn(y0), b1 = __float2bfloat16_rn(y1);
-      qsm[(l * kGroup + r) * kHeadDim + c] = b0;
-      qsm[(l * kGroup + r) * kHeadDim + c + 32] = b1;
-      if (b.q_rot_out && x == 0) {
-        __nv_bfloat16* qo = b.q_rot_out + (size_t)l * sp.q_layer_stride + qrow0 + r * kHeadDim;
-        qo[c] = b0;
-        qo[c + 32] = b1;
+    if (b.fuse) {
+      const float* cs = b.cos_table + (size_t)e.q_pos0 * 32;
+      const float* sn = b.sin_table + (size_t)e.q_pos0 * 32;
+      for (int idx = threadIdx.x; idx < layers * kGroup * 32; idx += T) {
+        const int c = idx & 31, r = (idx >> 5) & 3, l = idx >> 7;
+        const __nv_bfloat16* qp = b.q + (size_t)l * a.q_layer_stride + qrow0 + r * kHeadDim;
+        float y0, y1;
+        rope_pair<1>(__bfloat162float(qp[c]), __bfloat162float(qp[c + 32]), cs[c], sn[c], y0, y1);
+        const __nv_bfloat16 b0 = __float2bfloat16_rn(y0), b1 = __float2bfloat16_rn(y1);
+        qsm[(l * kGroup + r) * kHeadDim + c] = b0;
+        qsm[(l * kGroup + r) * kHeadDim + c + 32] = b1;
+        if (b.q_rot_out && x == 0) {
+          __nv_bfloat16* qo = b.q_rot_out + (size_t)l * a.q_layer_stride + qrow0 + r * kHeadDim;
+          qo[c] = b0;
+          qo[c + 32] = b1;
+        }
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < layers * kGroup * 32; idx += T) {
+        const int c = idx & 31, r = (idx >> 5) & 3, l = idx >> 7;
+        const uint32_t* qp = reinterpret_cast<const uint32_t*>(b.q + (size_t)l * a.q_layer_stride + qrow0 + r * kHeadDim);
+        reinterpret_cast<uint32_t*>(qsm + (l * kGroup + r) * kHeadDim)[c] = qp[c];
       }
     }
   }
-  consumer_barrier();
+  consumer_sync(T);
 
   const int qrow = lane >> 2, qcol = (lane & 3) * 2;
   const int mj = lane >> 3, rr = lane & 7;
@@ -917,7 +644,12 @@ __device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, cons
       if (lane == 0) mbar_arrive(empty0 + st * 8);
     }
 
-    // ---- end of the layer: merge the warps, leave the partial, count one arrival ---------------
+    // pdl == 1 (the layers of a step as one kernel each): the streaming above only read the
+    // cache; the workspace, tickets and outputs written from here on are shared with the previous
+    // layer's kernel, which must have completed
+    if (!STEP && b.pdl == 1) asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    // ---- end of the layer: merge the warps of this CTA --------------------------------------------
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
     if (qrow < kGroup) {
@@ -930,10 +662,10 @@ __device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, cons
         mrg_l[warp * kGroup + qrow] = l_run;
       }
     }
-    consumer_barrier();
-    float* ws_acc = b.ws_acc + ((size_t)l * sp.ws_layer_items + item) * (kGroup * kHeadDim);
-    float* ws_ml = b.ws_ml + ((size_t)l * sp.ws_layer_items + item) * (2 * kGroup);
-    for (int idx = threadIdx.x; idx < kGroup * kHeadDim; idx += WARPS * 32) {
+    consumer_sync(T);
+    float* ws_acc = b.ws_acc + ((size_t)l * a.ws_layer_items + item) * (kGroup * kHeadDim);
+    float* ws_ml = b.ws_ml + ((size_t)l * a.ws_layer_items + item) * (2 * kGroup);
+    for (int idx = threadIdx.x; idx < kGroup * kHeadDim; idx += T) {
       const int r = idx >> 6, d = idx & 63;
       float M = -INFINITY;
 #pragma unroll
@@ -946,18 +678,53 @@ __device__ __forceinline__ void stream_step_cta(const DecodeStepParams& sp, cons
         L += wgt * mrg_l[w * kGroup + r];
         O += wgt * mrg_o[(w * kGroup + r) * kHeadDim + d];
       }
-      ws_acc[idx] = O;
-      if (d == 0) {
-        ws_ml[r] = M;
-        ws_ml[kGroup + r] = L;
+      if (!STEP && n_chunks == 1) {
+        write_row_outputs(b, z, h, r, d, O, M, L);
+      } else {
+        ws_acc[idx] = O;
+        if (d == 0) {
+          ws_ml[r] = M;
+          ws_ml[kGroup + r] = L;
+        }
       }
     }
-    // orders every consumer's partial stores before thread 0's store of the layer count (which the
-    // publisher warp turns into the released arrival) and frees the merge buffers for the next layer
-    consumer_barrier();
-    if (threadIdx.x == 0)
-      asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(pub_word), "r"((unsigned)(l + 1)) : "memory");
+    if (STEP) {
+      // orders every consumer's partial stores before thread 0's store of the layer count (which the
+      // publisher warp turns into the released arrival) and frees the merge buffers for the next layer
+      consumer_sync(T);
+      if (threadIdx.x == 0)
+        asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(pub_word), "r"((unsigned)(l + 1)) : "memory");
+    }
   }
+  if (STEP) return;
+
+  // ---- the kernel of one layer: finish the (sequence, head) --------------------------------------
+  if (n_chunks == 1) {
+    publish_exchange(b, z, h, T);
+    exchange_wait_merge(b, z, h, &s_wait_ok, T);
+    return;
+  }
+  // combine across chunks: the last CTA to arrive does it
+  __threadfence();
+  consumer_sync(T);
+  if (threadIdx.x == 0) s_ticket = atomicAdd(&b.ws_count[pair], 1u);
+  consumer_sync(T);
+  if (s_ticket != (unsigned)(n_chunks - 1)) return;
+  __threadfence();
+  combine_pair<WARPS, STAGES>(b, z, h, n_chunks, smem, &s_wait_ok);
+}
+
+template <int WARPS, int STAGES>
+__global__ void __launch_bounds__(DecodeSmem<WARPS, STAGES>::kStepThreads)
+decode_kernel(const __grid_constant__ DecodeParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem =
+      reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+  // let the kernel behind take SMs (and start the part of its work that does not depend on this
+  // one) as soon as this one's CTAs leave them
+  if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const StreamArgs a{1, (int)gridDim.z, 0, 0, 0, 0ull};
+  stream_cta<WARPS, STAGES, false>(p, a, blockIdx.x, blockIdx.y, blockIdx.z, smem);
 }
 
 template <int WARPS, int STAGES>
@@ -971,7 +738,8 @@ __device__ __forceinline__ void decode_step_body(const DecodeStepParams& sp, con
     const int local = b - (int)sp.seq_first[z];
     const int chunks_z = ((int)sp.seq_first[z + 1] - (int)sp.seq_first[z]) / sp.base.kv_heads;
     const int x = local % chunks_z, h = local / chunks_z;
-    stream_step_cta<WARPS, STAGES>(sp, x, h, z, smem);
+    const StreamArgs a{sp.layers, sp.n_seqs, sp.ws_layer_items, sp.q_layer_stride, sp.kv_layer_stride, sp.layer_bytes};
+    stream_cta<WARPS, STAGES, true>(sp.base, a, x, h, z, smem);
     return;
   }
   if ((int)threadIdx.x >= WARPS * 32) return;  // the producer and publisher warps have no part in combining
@@ -1002,13 +770,13 @@ __device__ __forceinline__ void decode_step_body(const DecodeStepParams& sp, con
       }
       s_ok = ok;
     }
-    __syncthreads();
+    consumer_sync(WARPS * 32);
     if (!s_ok) {  // a streaming CTA never arrived: record it and leave
       if (threadIdx.x == 0) atomicExch(p.status, kStatusTimeout);
       return;
     }
     combine_pair<WARPS, STAGES>(p, z, h, n_chunks, smem, &s_wait_ok);
-    __syncthreads();
+    consumer_sync(WARPS * 32);
   }
 }
 
@@ -1044,19 +812,19 @@ cudaError_t launch_decode_cfg(const DecodeParams& p, int n_seqs, cudaStream_t st
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(decode_kernel<WARPS, STAGES>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::step_bytes(1));
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
   dim3 grid(p.max_chunks, p.kv_heads, n_seqs);
   if (!p.pdl) {
-    decode_kernel<WARPS, STAGES><<<grid, WARPS * 32, S::kBytes, stream>>>(p);
+    decode_kernel<WARPS, STAGES><<<grid, S::kStepThreads, S::step_bytes(1), stream>>>(p);
     return cudaGetLastError();
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(WARPS * 32);
-  cfg.dynamicSmemBytes = S::kBytes;
+  cfg.blockDim = dim3(S::kStepThreads);
+  cfg.dynamicSmemBytes = S::step_bytes(1);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

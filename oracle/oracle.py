@@ -31,6 +31,8 @@ def build(ref_dir: str | None = None) -> None:
     if ref_dir:
         cmd.append(f"REF={ref_dir}")
     subprocess.run(cmd, check=True, capture_output=True)
+    cmd[3] = "callers"
+    subprocess.run(cmd, check=True, capture_output=True)
 
 
 def _p(a, t=C.c_void_p):
