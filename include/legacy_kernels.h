@@ -16,8 +16,11 @@
  * contiguous K/V it is handed are first repacked into the paged layout (one
  * extra pass over the cache, and an allocation whenever a larger cache than
  * before arrives), then the paged decode (q_seq_len == 1) or prefill kernel
- * runs.  It exists so that existing callers keep working; callers that care
- * about speed hold a pa_pool themselves and never pay the repack.
+ * runs.  Calls on one device share that pool: a call waits (on the device,
+ * through an event) for the previous call's work even when it is given
+ * another stream, and growing the pool synchronises the device.  It exists so
+ * that existing callers keep working; callers that care about speed hold a
+ * pa_pool themselves and never pay the repack.
  * Supported: bf16, d_head 64, num_heads == 4 * num_kv_heads, num_kv_heads in
  * {1, 2, 4, 8}; anything else returns PA_ERR_UNSUPPORTED. */
 #ifndef LEGACY_KERNELS_H

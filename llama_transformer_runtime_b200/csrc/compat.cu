@@ -107,6 +107,10 @@ struct CompatState {
   pa_pool* pool = nullptr;
   int kv_heads = 0, max_seqs = 0, blocks_per_seq = 0;
   std::vector<int> seqs;
+  // Calls on one device share the private pool (cache, tables, split-KV workspace): a call on
+  // another stream first waits for the previous call's work (recorded here), so concurrent
+  // streams are serialised on the pool instead of racing on it.
+  cudaEvent_t last = nullptr;
 };
 CompatState g_state[64];
 std::mutex g_mutex;
@@ -161,11 +165,16 @@ int lt_launch_flash_attention(const lt_flash_attention_params* a) {
   const int nb = (a->kv_seq_len + pa::kBlockTok - 1) / pa::kBlockTok;
   cudaStream_t st = (cudaStream_t)a->stream;
   int rc;
+  if (!s.last && cudaEventCreateWithFlags(&s.last, cudaEventDisableTiming) != cudaSuccess)
+    return cfail(PA_ERR_CUDA, "lt_launch_flash_attention: cannot create an event");
+  if (cudaStreamWaitEvent(st, s.last, 0) != cudaSuccess) return cfail(PA_ERR_CUDA, "lt_launch_flash_attention: cudaStreamWaitEvent failed");
   if (!s.pool || s.kv_heads != kvh || s.max_seqs < a->batch_size || s.blocks_per_seq < nb) {
     if (s.pool) {
       cudaDeviceSynchronize();  // earlier calls may still read the old pool
       pa_pool_destroy(s.pool);
+      cudaEvent_t keep = s.last;
       s = CompatState();
+      s.last = keep;
     }
     const int cap = nb + nb / 4 + 16;  // room to grow without reallocating every call
     rc = pa_pool_create(&s.pool, dev, 1, a->batch_size * cap, kvh, a->batch_size, cap);
@@ -206,15 +215,20 @@ int lt_launch_flash_attention(const lt_flash_attention_params* a) {
   rc = pa_batch_set_sharded(s.pool, ids.data(), zeros.data(), qrows.data(), qpos.data(), nullptr, a->batch_size, st);
   if (rc != PA_OK) return rc;
   const long long hq = a->num_heads;
-  if (a->q_seq_len == 1)
-    return pa_decode(s.pool, 0, a->Q, a->O, hq * 64, nullptr, a->L, a->scale, st);
+  if (a->q_seq_len == 1) {
+    rc = pa_decode(s.pool, 0, a->Q, a->O, hq * 64, nullptr, a->L, a->scale, st);
+    cudaEventRecord(s.last, st);
+    return rc;
+  }
   // head-major Q/O: row r of head h of sequence b is at ((b*heads + h)*q_seq_len + r)*64.
   // The kernel adds the batch's running row offset (b*q_seq_len rows) on top of
   // the per-sequence stride, so that part is taken out of the stride here.
   const long long sq = a->q_seq_len;
   const long long seq_stride = hq * sq * 64 - sq * 64;
-  return pa::prefill_strided(s.pool, 0, a->Q, a->O, a->L, seq_stride, 64, sq * 64, seq_stride, 64, sq * 64,
-                             hq * sq, a->causal ? 1 : 0, a->scale, st);
+  rc = pa::prefill_strided(s.pool, 0, a->Q, a->O, a->L, seq_stride, 64, sq * 64, seq_stride, 64, sq * 64, hq * sq,
+                           a->causal ? 1 : 0, a->scale, st);
+  cudaEventRecord(s.last, st);
+  return rc;
 }
 
 }  // extern "C"
