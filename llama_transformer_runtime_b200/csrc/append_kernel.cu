@@ -13,17 +13,6 @@ namespace pa {
 
 constexpr int kAppendThreads = 256;
 constexpr int kAppendTokPerCta = 4;
-// units of one token: (32 query heads + 8 K heads + 8 V heads) x 4 chunk pairs at most
-constexpr int kAppendMaxIters = (kAppendTokPerCta * (32 + 8 + 8) * 4 + kAppendThreads - 1) / kAppendThreads;
-
-// What one thread moves: chunk pair (c, c + 4) of one head row of one token.
-struct AppendUnit {
-  const uint4* src;   // the 64-element row in q_in / k_in / v_in
-  uint4* dst_lo;      // where chunk c goes (rotated-Q row or cache tile)
-  uint4* dst_hi;      // where chunk c + 4 goes
-  const float* cs;    // 8 cos values of pairs 8c..8c+7 (nullptr: V, no rotation)
-  const float* sn;
-};
 
 __global__ void __launch_bounds__(kAppendThreads)
 append_kernel(AppendParams p) {
@@ -40,27 +29,30 @@ append_kernel(AppendParams p) {
   const int units_per_tok = q_units + 2 * k_units;
   const int32_t* table = p.tables + (size_t)e.seq * p.max_blocks_per_seq;
 
-  // Where a unit reads and writes.  A unit with nothing to do (a token beyond this sequence's
-  // query rows or new tokens, a block id outside the pool) comes back with src == nullptr.
-  auto unit_of = [&](int u) {
-    AppendUnit a{nullptr, nullptr, nullptr, nullptr, nullptr};
+  for (int u = threadIdx.x; u < ntok * units_per_tok; u += kAppendThreads) {
     const int t = u / units_per_tok;
     int w = u - t * units_per_tok;
     const int tok = tok0 + t;
     const int c = w & 3;  // chunk pair (c, c+4)
+
     if (w < q_units) {
-      if (tok >= n_q) return a;
+      if (tok >= n_q) continue;
       const int h = w >> 2;
       const size_t row = (size_t)e.q_row_off + tok;
       const int pos = e.q_pos0 + tok;
-      a.src = reinterpret_cast<const uint4*>(p.q_in + (row * q_heads + h) * kHeadDim) + c;
-      a.dst_lo = reinterpret_cast<uint4*>(p.q_out + (row * q_heads + h) * kHeadDim) + c;
-      a.dst_hi = a.dst_lo + 4;
-      a.cs = p.cos_table + (size_t)pos * 32 + c * 8;
-      a.sn = p.sin_table + (size_t)pos * 32 + c * 8;
-      return a;
+      const uint4* src = reinterpret_cast<const uint4*>(p.q_in + (row * q_heads + h) * kHeadDim);
+      uint4* dst = reinterpret_cast<uint4*>(p.q_out + (row * q_heads + h) * kHeadDim);
+      const float4* cs = reinterpret_cast<const float4*>(p.cos_table + (size_t)pos * 32 + c * 8);
+      const float4* sn = reinterpret_cast<const float4*>(p.sin_table + (size_t)pos * 32 + c * 8);
+      float4 c8[2] = {cs[0], cs[1]}, s8[2] = {sn[0], sn[1]};
+      uint4 lo = src[c], hi = src[c + 4], ylo, yhi;
+      rope_chunks<VARIANT>(lo, hi, reinterpret_cast<const float*>(c8),
+                           reinterpret_cast<const float*>(s8), ylo, yhi);
+      dst[c] = ylo;
+      dst[c + 4] = yhi;
+      continue;
     }
-    if (tok >= e.n_new) return a;
+    if (tok >= e.n_new) continue;
     w -= q_units;
     const size_t row = (size_t)e.kv_row_off + tok;
     const int lpos = e.kv_len - e.n_new + tok;  // position inside the local cache
@@ -69,55 +61,27 @@ append_kernel(AppendParams p) {
     const int slot = lpos % kBlockTok;
     if (blk < 0 || blk >= p.num_blocks) {
       atomicExch(p.status, kStatusBadBlock);
-      return a;
+      continue;
     }
-    const int is_v = w >= k_units;
-    const int h = (is_v ? w - k_units : w) >> 2;
-    a.src = reinterpret_cast<const uint4*>((is_v ? p.v_in : p.k_in) + (row * p.kv_heads + h) * kHeadDim) + c;
-    char* tile = p.storage + tile_off(blk, p.kv_heads, h, is_v);
-    a.dst_lo = reinterpret_cast<uint4*>(tile + tile_chunk_off(slot, c));
-    a.dst_hi = reinterpret_cast<uint4*>(tile + tile_chunk_off(slot, c + 4));
-    if (!is_v) {
-      a.cs = p.cos_table + (size_t)pos * 32 + c * 8;
-      a.sn = p.sin_table + (size_t)pos * 32 + c * 8;
-    }
-    return a;
-  };
-
-  // All loads of a thread's units are issued before the first store (q_out may alias q_in, so the
-  // compiler cannot move them itself): the thread has every load in flight at once instead of one
-  // load-rotate-store chain after another.
-  const int total = ntok * units_per_tok;
-  // kAppendMaxIters covers the model's head counts in one pass; other head counts take more passes
-#pragma unroll 1
-  for (int base = 0; base < total; base += kAppendMaxIters * kAppendThreads) {
-    AppendUnit un[kAppendMaxIters];
-    uint4 lo[kAppendMaxIters], hi[kAppendMaxIters];
-    float4 c8[kAppendMaxIters][2], s8[kAppendMaxIters][2];
-#pragma unroll
-    for (int it = 0; it < kAppendMaxIters; it++) {
-      const int u = base + threadIdx.x + it * kAppendThreads;
-      un[it] = u < total ? unit_of(u) : AppendUnit{nullptr, nullptr, nullptr, nullptr, nullptr};
-      if (un[it].src) {
-        lo[it] = un[it].src[0];
-        hi[it] = un[it].src[4];
-        if (un[it].cs) {
-          c8[it][0] = reinterpret_cast<const float4*>(un[it].cs)[0];
-          c8[it][1] = reinterpret_cast<const float4*>(un[it].cs)[1];
-          s8[it][0] = reinterpret_cast<const float4*>(un[it].sn)[0];
-          s8[it][1] = reinterpret_cast<const float4*>(un[it].sn)[1];
-        }
-      }
-    }
-#pragma unroll
-    for (int it = 0; it < kAppendMaxIters; it++) {
-      if (!un[it].src) continue;
-      uint4 ylo = lo[it], yhi = hi[it];
-      if (un[it].cs)
-        rope_chunks<VARIANT>(lo[it], hi[it], reinterpret_cast<const float*>(c8[it]),
-                             reinterpret_cast<const float*>(s8[it]), ylo, yhi);
-      *un[it].dst_lo = ylo;
-      *un[it].dst_hi = yhi;
+    if (w < k_units) {
+      const int h = w >> 2;
+      const uint4* src = reinterpret_cast<const uint4*>(p.k_in + (row * p.kv_heads + h) * kHeadDim);
+      char* tile = p.storage + tile_off(blk, p.kv_heads, h, 0);
+      const float4* cs = reinterpret_cast<const float4*>(p.cos_table + (size_t)pos * 32 + c * 8);
+      const float4* sn = reinterpret_cast<const float4*>(p.sin_table + (size_t)pos * 32 + c * 8);
+      float4 c8[2] = {cs[0], cs[1]}, s8[2] = {sn[0], sn[1]};
+      uint4 lo = src[c], hi = src[c + 4], ylo, yhi;
+      rope_chunks<VARIANT>(lo, hi, reinterpret_cast<const float*>(c8),
+                           reinterpret_cast<const float*>(s8), ylo, yhi);
+      *reinterpret_cast<uint4*>(tile + tile_chunk_off(slot, c)) = ylo;
+      *reinterpret_cast<uint4*>(tile + tile_chunk_off(slot, c + 4)) = yhi;
+    } else {
+      w -= k_units;
+      const int h = w >> 2;
+      const uint4* src = reinterpret_cast<const uint4*>(p.v_in + (row * p.kv_heads + h) * kHeadDim);
+      char* tile = p.storage + tile_off(blk, p.kv_heads, h, 1);
+      *reinterpret_cast<uint4*>(tile + tile_chunk_off(slot, c)) = src[c];
+      *reinterpret_cast<uint4*>(tile + tile_chunk_off(slot, c + 4)) = src[c + 4];
     }
   }
 }

@@ -1086,9 +1086,8 @@ int pa_qkv_project_append(pa_pool* p, int layer, const void* x, const void* wq, 
   if (rows == 0) return PA_OK;
   DeviceGuard g(p->device);
   { const int r = check_activation_staging(p, rows, hidden, "pa_qkv_project_append"); if (r != PA_OK) return r; }
-  PA_CUDA(pa::launch_pack_x(x, p->x_pack, rows, hidden, (cudaStream_t)stream));
   pa::QkvGemmParams a;
-  a.x = (const __nv_bfloat16*)p->x_pack;
+  a.x = (const __nv_bfloat16*)x;
   a.wq = (const __nv_bfloat16*)wq;
   a.wk = (const __nv_bfloat16*)wk;
   a.wv = (const __nv_bfloat16*)wv;
@@ -1120,9 +1119,8 @@ int pa_out_project_rows(pa_pool* p, const void* attn, const void* wo_packed, con
     return fail(PA_ERR_UNSUPPORTED, "pa_out_project_rows: hidden must be a multiple of 64, cols a multiple of 256");
   DeviceGuard g(p->device);
   { const int r = check_activation_staging(p, rows, hidden, "pa_out_project_rows"); if (r != PA_OK) return r; }
-  PA_CUDA(pa::launch_pack_x(attn, p->x_pack, rows, hidden, (cudaStream_t)stream));
   pa::QkvGemmParams a = {};
-  a.x = (const __nv_bfloat16*)p->x_pack;
+  a.x = (const __nv_bfloat16*)attn;
   a.wq = a.wk = a.wv = (const __nv_bfloat16*)wo_packed;
   a.q_out = (__nv_bfloat16*)out;
   a.status = p->d_status;

@@ -11,31 +11,38 @@
 // in fp32 on those bf16 values with the same rounding as append_kernel, V is
 // stored as it comes out.
 //
-// One CTA computes 256 tokens (two M = 128 halves) x 256 output columns (4 heads
-// of one of Wq, Wk, Wv) over K = 2048 in steps of 64.  The tile is that large
-// because every byte of it comes through L2: with 128 x 256 tiles (85 flop per
-// loaded byte, 295 MB of L2-to-SM traffic per layer) the kernel sat at 96 us per
-// layer whatever the load mechanism; 256 x 256 tiles move 197 MB.
-//   warp 0      load: per step one 16 KiB bulk (TMA) copy per row half for the A tile (128
-//               token rows x 64 k) and ONE 32 KiB bulk copy for the B tile (64 weight rows
-//               x 4 heads), 3 stages of 64 KiB.  Both operands are read from tile images of
-//               the shared-memory layout the tensor cores want (rows of 128 bytes,
-//               16-byte chunks XOR-swizzled; A K-major, B MN-major), the same idea
-//               as the KV cache's tile layout: the weights are packed once, at load
-//               time (pack_weights_kernel), the activations by a small kernel in
-//               front of the GEMM (pack_x_kernel, 8 MB in, 8 MB out per layer).
-//               With 16-byte cp.async from the row-major arrays instead the kernel
-//               ran at 96 us per layer: lg_throttle and long_scoreboard stalls on
-//               the load path, tensor pipe 18 % busy.
-//   warps 0-3   epilogue after the last step: thread = token row = TMEM lane.
-//   warp 4      issues, per step, row half and 16-wide k-slice, one tcgen05.mma
-//               M128 N256 K16 from an elected lane (8 per step) into the half's 256
-//               TMEM columns — B spans four 128-byte atoms along N, 8 KiB apart,
-//               which is the descriptor's leading byte offset — and frees the
-//               stage with tcgen05.commit.
-// Every wait is bounded; on expiry the CTA raises its abort flag, the status
-// word gets PA_ERR_TIMEOUT and all warps leave through the common exit, where
+// A PAIR of CTAs (a cluster of two, on the two SMs of one TPC) computes 256 tokens x 384 output
+// columns (6 heads of the concatenation Wq | Wk | Wv) over K = 2048 in steps of 64 with
+// tcgen05.mma.cta_group::2: M = 256 rows, 128 from each CTA's activation tile, accumulating in
+// each CTA's own tensor memory; of every B operand each CTA loads only half of the N columns.  Per
+// k-step a CTA therefore moves 16 KiB of activations and 24 KiB of weights for 128 x 384 x 64
+// multiply-adds.  Every byte comes through L2, and that traffic is what bounds this kernel: one
+// CTA per 256 x 256 tile (64 KiB per step for 256 x 256 x 64, 96 CTAs, 206.6 MB per layer) ran at
+// 38.8 us per layer; 128 x 256 tiles (295 MB) at 96 us.  2048 tokens x 3072 columns are 8 x 8
+// pair tiles = 128 CTAs.
+//   warp 8      load: per step one 16 KiB bulk (TMA) copy for the A tile (128 token rows x 64 k)
+//               and one 8 KiB bulk copy per head block of B (64 weight rows x 64 columns), issued
+//               by different lanes, 5 stages of 40 KiB.  Both operands are read from tile images
+//               of the shared-memory layout the tensor cores want (rows of 128 bytes, 16-byte
+//               chunks XOR-swizzled; A K-major, B MN-major), the same idea as the KV cache's tile
+//               layout: the weights are packed once, at load time (pack_weights_kernel), the
+//               activations by a small kernel in front of the GEMM (pack_x_kernel, 8 MB in, 8 MB
+//               out per layer).  With 16-byte cp.async from the row-major arrays instead the
+//               kernel ran at 96 us per layer: lg_throttle and long_scoreboard stalls on the load
+//               path, tensor pipe 18 % busy.
+//   warps 0-7   epilogue after the last step: thread = token row = TMEM lane; the two warps of a
+//               32-lane quarter take every other head of the tile.
+//   warp 9      first CTA of the pair: waits for its own stage and for the peer's (the peer's warp
+//               9 forwards its "stage full" barrier with a remote arrive), then one elected lane
+//               issues per 16-wide k-slice one MMA M256 N256 K16 (heads 0..3 of the tile; a CTA
+//               holds two of them, 8 KiB apart: the descriptor's leading byte offset) and one
+//               M256 N128 K16 (heads 4, 5), and frees the stage in BOTH CTAs with a multicast
+//               tcgen05.commit.
+// Every wait is bounded; on expiry the CTA raises its abort flag, the status word gets
+// PA_ERR_TIMEOUT and all warps leave through the common exit, where the pair meets once more and
 // tensor memory is released.
+#include <cuda.h>  // CUtensorMap and the encode function's type; the function itself comes from the runtime's driver entry point
+
 #include "kernels.cuh"
 #include "rope.cuh"
 #include "tc05.cuh"
@@ -44,101 +51,129 @@ namespace pa {
 
 namespace {
 
-constexpr int kGM = 128;        // tokens per UMMA (M = 128) and per packed activation tile
-constexpr int kGMH = 2;         // row halves per CTA: 256 tokens share every weight tile
-constexpr int kGN = 256;        // output columns per CTA (4 heads)
+constexpr int kGM = 128;        // tokens per CTA = per packed activation tile; the pair's MMA has M = 256
+constexpr int kTileHeads = 6;   // heads (64 output columns) per pair tile: 4 in the first MMA, 2 in the second
 constexpr int kGK = 64;         // k per stage
-constexpr int kGStages = 3;
+constexpr int kGStages = 5;
 constexpr int kABytes = kGM * 128;            // 16 KiB
-constexpr int kBBytes = (kGN / 64) * kGK * 128;  // 4 head blocks x 8 KiB
-constexpr int kStageBytes = kGMH * kABytes + kBBytes;  // 64 KiB
+constexpr int kBBlock = kGK * 128;            // 8 KiB: 64 weight rows x one head
+constexpr int kBSlots = 3;                    // head blocks a CTA holds per stage: 2 of the first MMA, 1 of the second
+constexpr int kStageBytes = kABytes + kBSlots * kBBlock;  // 40 KiB
 constexpr int kGOffBar = kGStages * kStageBytes;
-constexpr int kGOffMisc = kGOffBar + (2 * kGStages + 1) * 8;
+constexpr int kGOffMisc = kGOffBar + (3 * kGStages + 1) * 8;
 constexpr int kGSmem = kGOffMisc + 16 + 112;
-constexpr int kGemmThreads = 160;  // 4 epilogue warps (warp 0 also loads) + the MMA warp
-constexpr uint32_t kGTmemCols = 512;  // 2 row halves x 4 heads x 64 fp32 columns
+constexpr int kEpiWarps = 8;      // two per 32-lane quarter of tensor memory, each takes every other head
+constexpr int kLoadWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1;
+constexpr int kGemmThreads = (kEpiWarps + 2) * 32;
+constexpr uint32_t kGTmemCols = 512;  // 6 heads x 64 fp32 columns, rounded up to a power of two
 
-__global__ void __launch_bounds__(kGemmThreads, 1)
-qkv_gemm_kernel(QkvGemmParams p) {
+// Head g of the concatenated output (Q heads, then K heads, then V heads; or the one matrix of a
+// plain linear layer): which matrix it comes from and where.
+struct HeadSrc {
+  const __nv_bfloat16* w;  // packed weights of its matrix
+  int heads;               // heads (64-column blocks) of that matrix
+  int head;                // head index inside the matrix
+  int which;               // 0 Q, 1 K, 2 V (projection with RoPE + append); 3: plain linear layer with residual
+};
+__device__ __forceinline__ HeadSrc head_src(const QkvGemmParams& p, int g) {
+  const int hq = p.q_cols / 64, hk = p.kv_cols / 64;
+  if (p.linear) return HeadSrc{p.wq, hq, g, 3};
+  if (g < hq) return HeadSrc{p.wq, hq, g, 0};
+  if (g < hq + hk) return HeadSrc{p.wk, hk, g - hq, 1};
+  return HeadSrc{p.wv, hk, g - hq - hk, 2};
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+qkv_gemm_kernel(const __grid_constant__ CUtensorMap x_map, QkvGemmParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
-  if (base & 1023u) {  // swizzle atoms need 1024-byte alignment
+  if (base & 1023u) {  // swizzle atoms need 1024-byte alignment (the same in both CTAs of the pair)
     if (threadIdx.x == 0) atomicExch(p.status, kStatusBadBlock);
     return;
   }
   unsigned char* sm = smem_raw;
   const uint32_t bar_full = base + kGOffBar, bar_empty = bar_full + 8 * kGStages;
-  const uint32_t bar_acc = bar_empty + 8 * kGStages;
+  const uint32_t bar_peer = bar_empty + 8 * kGStages;  // first CTA only: the peer's stage is full
+  const uint32_t bar_acc = bar_peer + 8 * kGStages;
   uint32_t* s_tmem_base = reinterpret_cast<uint32_t*>(sm + kGOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kGOffMisc + 4);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int m0 = blockIdx.y * (kGMH * kGM);
-  // column tile -> matrix and first column: tiles of Wq, then Wk, then Wv
-  const int tq = p.q_cols / kGN, tk = p.kv_cols / kGN;
-  const int ct = blockIdx.x;
-  // which: 0 Q, 1 K, 2 V (projection with RoPE + append); 3: plain linear layer with residual
-  const int which = p.linear ? 3 : (ct < tq ? 0 : (ct < tq + tk ? 1 : 2));
-  const int n0 = (ct - ((which == 0 || which == 3) ? 0 : (which == 1 ? tq : tq + tk))) * kGN;
-  const int n_cols = (which == 0 || which == 3) ? p.q_cols : p.kv_cols;
-  const __nv_bfloat16* w = (which == 0 || which == 3) ? p.wq : (which == 1 ? p.wk : p.wv);
+  const uint32_t rank = cluster_ctarank();  // 0: issues the MMAs; 1: the peer
+  const int tile_m = (int)blockIdx.y * 2 + (int)rank;  // this CTA's 128-row activation tile
+  const int m0 = tile_m * kGM;
+  const bool have_rows = m0 < p.rows;  // the last pair may have one row half only: the peer then loads no A
+  const int total_heads = p.linear ? p.q_cols / 64 : (p.q_cols + 2 * p.kv_cols) / 64;
+  const int g0 = (int)(blockIdx.x >> 1) * kTileHeads;
+  const int n_heads = min(kTileHeads, total_heads - g0);  // 2, 4 or 6
+  const int n1 = min(n_heads, 4);                          // heads of the first MMA
   const int k_steps = p.hidden / kGK;
+  // head blocks this CTA loads: slots 0 .. n1/2-1 = its half of the first MMA's heads,
+  // slot 2 = its head of the second MMA
+  const int my_first = g0 + (int)rank * (n1 / 2);
+  const int my_second = n_heads > 4 ? g0 + 4 + (int)rank : -1;
 
   if (tid == 0) {
     *abort_flag = 0;
     for (int s = 0; s < kGStages; s++) {
-      mbar_init(bar_full + 8 * s, 1);  // one arrival (with the byte count of both bulk copies)
-      mbar_init(bar_empty + 8 * s, 1);
+      mbar_init(bar_full + 8 * s, 1);   // one arrival (with the byte count of all bulk copies of the stage)
+      mbar_init(bar_empty + 8 * s, 1);  // the first CTA's commit, multicast to both
+      mbar_init(bar_peer + 8 * s, 1);   // the peer's remote arrive
     }
     mbar_init(bar_acc, 1);
     mbar_fence_init();
   }
-  if (warp == 4) {
-    tmem_alloc(base + kGOffMisc, kGTmemCols);
-    tmem_relinquish();
+  if (warp == kMmaWarp) {
+    tmem_alloc_pair(base + kGOffMisc, kGTmemCols);
+    tmem_relinquish_pair();
   }
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before a remote arrive or a multicast commit reaches them
   tc_fence_after();
   const uint32_t tmem = *s_tmem_base;
 
-  if (warp < 4) {
+  if (warp == kLoadWarp) {
     // ===================== loads ==============================================
-    bool ok = true;
-    if (warp == 0) {
-      const char* a_img = reinterpret_cast<const char*>(p.x) + (size_t)blockIdx.y * kGMH * k_steps * kABytes;
-      const int tiles_m = (p.rows + kGM - 1) / kGM;  // packed activation tiles that exist
-      const char* b_img = reinterpret_cast<const char*>(w) + (size_t)(n0 / 64) * (kGK * 128);
-      for (int ks = 0; ks < k_steps; ks++) {
-        const int st = ks % kGStages;
-        if (!wait_or_abort(bar_empty + 8 * st, (uint32_t)(((ks / kGStages) & 1) ^ 1), abort_flag)) {
-          ok = false;
-          break;
-        }
-        if (lane == 0) {
-          const uint32_t sA = base + st * kStageBytes, sB = sA + kGMH * kABytes;
-          const bool second = (int)blockIdx.y * kGMH + 1 < tiles_m;  // the last CTA row may have one half only
-          mbar_expect_tx(bar_full + 8 * st, (second ? 2 : 1) * kABytes + kBBytes);
-          bulk_g2s(sA, a_img + (size_t)ks * kABytes, kABytes, bar_full + 8 * st);
-          if (second)
-            bulk_g2s(sA + kABytes, a_img + ((size_t)k_steps + ks) * kABytes, kABytes, bar_full + 8 * st);
-          // the 4 head blocks of this k-step are adjacent in the packed weights
-          bulk_g2s(sB, b_img + (size_t)ks * (n_cols / 64) * (kGK * 128), kBBytes, bar_full + 8 * st);
-        }
-        __syncwarp();
-      }
+    // lane 0: the A tile, through the tensor map of the row-major activations (box 64 k x 128
+    // rows, 128-byte swizzle: the copy lands as the canonical K-major operand, rows past the end
+    // read as zeros); lane 1 + s: the head block of slot s, from the packed weights
+    const int slot = lane - 1;
+    int g = -1;
+    if (slot >= 0 && slot < n1 / 2) g = my_first + slot;
+    if (slot == 2) g = my_second;
+    const char* b_img = nullptr;
+    size_t b_step = 0;
+    if (g >= 0) {
+      const HeadSrc h = head_src(p, g);
+      b_img = reinterpret_cast<const char*>(h.w) + (size_t)h.head * kBBlock;
+      b_step = (size_t)h.heads * kBBlock;
     }
-
+    const uint32_t tx = (have_rows ? kABytes : 0) + (uint32_t)(n1 / 2 + (my_second >= 0 ? 1 : 0)) * kBBlock;
+    for (int ks = 0; ks < k_steps; ks++) {
+      const int st = ks % kGStages;
+      if (!wait_or_abort(bar_empty + 8 * st, (uint32_t)(((ks / kGStages) & 1) ^ 1), abort_flag)) break;
+      const uint32_t sA = base + st * kStageBytes, sB = sA + kABytes;
+      if (lane == 0) mbar_expect_tx(bar_full + 8 * st, tx);
+      __syncwarp();
+      if (lane == 0 && have_rows) tensor_g2s_2d(sA, &x_map, ks * kGK, m0, bar_full + 8 * st);
+      if (g >= 0) bulk_g2s(sB + slot * kBBlock, b_img + (size_t)ks * b_step, kBBlock, bar_full + 8 * st);
+      __syncwarp();
+    }
+  } else if (warp < kEpiWarps) {
     // ===================== epilogue ============================================
-    if (ok && wait_or_abort(bar_acc, 0, abort_flag)) {
+    // Warp w reads the tensor-memory lanes of quarter w % 4 (the only ones it may) and takes the
+    // tile's heads w / 4, w / 4 + 2, w / 4 + 4: thread = token row = TMEM lane.
+    if (wait_or_abort(bar_acc, 0, abort_flag)) {
       tc_fence_after();
-#pragma unroll 1
-      for (int mh = 0; mh < kGMH; mh++) {
-      const int row = m0 + mh * kGM + warp * 32 + lane;  // token row; TMEM lane = warp * 32 + lane
-      const uint32_t lane_base = ((uint32_t)(warp * 32) << 16) + (uint32_t)(mh * kGN);
+      const int quarter = warp & 3, hb0 = warp >> 2;
+      const int row = m0 + quarter * 32 + lane;  // token row; TMEM lane = quarter * 32 + lane
+      const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+      const bool any_rope = !p.linear && g0 < (p.q_cols + p.kv_cols) / 64;
+      const bool any_cache = !p.linear && g0 + n_heads > p.q_cols / 64;
       // which sequence and position this row is
-      int seq = (which == 3 && row < p.rows) ? 0 : -1, lpos = 0, pos = 0;
-      for (int s = 0; which != 3 && s < p.n_seqs; s++) {
+      int seq = (p.linear && row < p.rows) ? 0 : -1, lpos = 0, pos = 0;
+      for (int s = 0; !p.linear && s < p.n_seqs; s++) {
         const BatchEntry e = p.batch[s];
         if (row >= e.kv_row_off && row < e.kv_row_off + e.n_new) {
           seq = e.seq;
@@ -147,7 +182,7 @@ qkv_gemm_kernel(QkvGemmParams p) {
         }
       }
       int blk = 0;
-      if (seq >= 0 && (which == 1 || which == 2)) {
+      if (seq >= 0 && any_cache) {
         blk = p.tables[(size_t)seq * p.max_blocks_per_seq + lpos / kBlockTok];
         if (blk < 0 || blk >= p.num_blocks) {
           atomicExch(p.status, kStatusBadBlock);
@@ -157,10 +192,10 @@ qkv_gemm_kernel(QkvGemmParams p) {
       const int slot = lpos % kBlockTok;
       // This row's RoPE factors, once per row: 16 vector loads into a private row of the (now
       // idle) stage ring, 65 floats apart so that the 32 lanes of a warp hit 32 banks.  Read per
-      // element from global memory instead (scalar, one 128-byte line per lane and load, 4 heads
+      // element from global memory instead (scalar, one 128-byte line per lane and load, every head
       // over) they made the epilogue longer than the whole MMA loop.
-      float* trow = reinterpret_cast<float*>(sm) + (warp * 32 + lane) * 65;
-      if (which < 2 && seq >= 0) {
+      float* trow = reinterpret_cast<float*>(sm) + (warp * 32 + lane) * 65;  // each warp stages its own copy
+      if (any_rope && seq >= 0) {
         const float4* cs4 = reinterpret_cast<const float4*>(p.cos_table + (size_t)pos * 32);
         const float4* sn4 = reinterpret_cast<const float4*>(p.sin_table + (size_t)pos * 32);
         float4 cv[8], sv[8];
@@ -182,8 +217,11 @@ qkv_gemm_kernel(QkvGemmParams p) {
         }
       }
       __syncwarp();
+      // per row: block id and slot for the cooperative stores below (negative: no token in the row)
+      const int row_info = seq >= 0 ? ((blk << 4) | slot) : -1;
+      unsigned char* stage = sm + kEpiWarps * 32 * 65 * 4 + warp * 4096;  // 32 rows x 128 bytes per warp
 #pragma unroll 1
-      for (int hb = 0; hb < kGN / 64; hb++) {
+      for (int hb = hb0; hb < n_heads; hb += kEpiWarps / 4) {
         uint32_t acc[2][32];
         tmem_ld32(tmem + lane_base + hb * 64, acc[0]);
         tmem_ld32(tmem + lane_base + hb * 64 + 32, acc[1]);
@@ -192,13 +230,14 @@ qkv_gemm_kernel(QkvGemmParams p) {
         // (warp-wide, aligned) tensor-memory load
         __syncwarp();
         if (seq >= 0) {
-        const int head = n0 / 64 + hb;
+        const HeadSrc hs = head_src(p, g0 + hb);
+        const int which = hs.which, head = hs.head;
         // the GEMM's bf16 output, then RoPE on it: element i pairs with i + 32
         uint32_t lo[16], hi[16];  // bf16 pairs of elements 0..31 and 32..63
         if (which == 3) {
           // plain output: bf16 of the accumulator, then (optionally) the residual added in fp32 and
           // rounded once more, as the reference's GEMM and residual_add kernels do in turn
-          const size_t at = (size_t)row * p.q_cols + n0 + hb * 64;
+          const size_t at = (size_t)row * p.q_cols + head * 64;
           uint4 rl[4], rh[4];
           if (p.residual) {
 #pragma unroll
@@ -245,64 +284,89 @@ qkv_gemm_kernel(QkvGemmParams p) {
             hi[i] = pack_bf16(y1a, y1b);
           }
         }
-        if (which == 0 || which == 3) {
-          uint4* dst = reinterpret_cast<uint4*>(p.q_out + ((size_t)row * (p.q_cols / 64) + head) * kHeadDim);
+        // this row's 128 bytes -> the warp's staging tile (chunks XOR-swizzled by row: conflict-free)
 #pragma unroll
-          for (int c = 0; c < 4; c++) {
-            dst[c] = make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
-            dst[c + 4] = make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
-          }
-        } else {
-          char* tile = p.storage + tile_off(blk, p.kv_heads, head, which == 2 ? 1 : 0);
-#pragma unroll
-          for (int c = 0; c < 4; c++) {
-            *reinterpret_cast<uint4*>(tile + tile_chunk_off(slot, c)) =
-                make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
-            *reinterpret_cast<uint4*>(tile + tile_chunk_off(slot, c + 4)) =
-                make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
-          }
+        for (int c = 0; c < 4; c++) {
+          *reinterpret_cast<uint4*>(stage + tile_chunk_off(lane, c)) =
+              make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
+          *reinterpret_cast<uint4*>(stage + tile_chunk_off(lane, c + 4)) =
+              make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
         }
         }
         __syncwarp();
-      }
+        // The warp writes the 32 rows out four at a time, 8 lanes per row: whole 128-byte lines per
+        // store instead of one 16-byte piece of 32 different lines.
+        {
+          const HeadSrc hs = head_src(p, g0 + hb);
+          const int rr0 = lane >> 3, c = lane & 7;
+#pragma unroll
+          for (int it = 0; it < 8; it++) {
+            const int rr = it * 4 + rr0;
+            const int info = __shfl_sync(0xffffffffu, row_info, rr);
+            if (info < 0) continue;  // no token in that row
+            const uint4 v = *reinterpret_cast<const uint4*>(stage + tile_chunk_off(rr, c));
+            if (hs.which == 0 || hs.which == 3) {
+              const size_t r = (size_t)(m0 + quarter * 32 + rr);
+              reinterpret_cast<uint4*>(p.q_out + (r * (p.q_cols / 64) + hs.head) * kHeadDim)[c] = v;
+            } else {
+              char* tile = p.storage + tile_off(info >> 4, p.kv_heads, hs.head, hs.which == 2 ? 1 : 0);
+              *reinterpret_cast<uint4*>(tile + tile_chunk_off(info & 15, c)) = v;
+            }
+          }
+        }
+        __syncwarp();
       }
     }
+  } else if (rank == 0) {
+    // ===================== MMA issue (first CTA of the pair) ====================
+    // First MMA: N = 64 * n1 (the tile's heads 0..3), of which each CTA holds half, two 128-byte
+    // atoms along N, 8 KiB apart (the next head's block): that distance is the descriptor's
+    // leading byte offset.  Second MMA: N = 128 (heads 4, 5), one head per CTA, in slot 2.
+    // (One CTA, N = 64 per MMA: 55.8 us per layer, shared-memory operand bandwidth; N = 128: 46.6.)
+    const uint32_t idesc1 = idesc_bf16(2 * kGM, 64 * n1, true);
+    constexpr uint32_t kIdesc2 = idesc_bf16(2 * kGM, 128, true);
+    constexpr uint64_t kLboNextHead = (uint64_t)(kBBlock >> 4) << 16;
+    for (int ks = 0; ks < k_steps; ks++) {
+      const int st = ks % kGStages;
+      const uint32_t par = (uint32_t)((ks / kGStages) & 1);
+      if (!wait_or_abort(bar_full + 8 * st, par, abort_flag)) break;
+      if (!wait_or_abort_cluster(bar_peer + 8 * st, par, abort_flag)) break;
+      tc_fence_after();
+      if (elect_one()) {
+        const uint32_t sA = base + st * kStageBytes, sB = sA + kABytes;
+#pragma unroll
+        for (int kk = 0; kk < kGK / 16; kk++) {
+          const uint64_t a_desc = smem_desc_sw128(sA + kk * 32);
+          umma_ss_pair(tmem, a_desc,
+                       (smem_desc_sw128(sB + kk * 2048) & ~((uint64_t)0x3FFF << 16)) | kLboNextHead, idesc1,
+                       (ks > 0 || kk > 0) ? 1u : 0u);
+          if (n_heads > 4)
+            umma_ss_pair(tmem + 256, a_desc, smem_desc_sw128(sB + 2 * kBBlock + kk * 2048), kIdesc2,
+                         (ks > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit_pair(bar_empty + 8 * st, 3);
+        if (ks + 1 == k_steps) tc_commit_pair(bar_acc, 3);
+      }
+      __syncwarp();
+    }
   } else {
-    // ===================== MMA issue =========================================
-    // N = 256: the CTA's four heads in one MMA.  The B operand then spans four 128-byte atoms
-    // along N, 8 KiB apart (the next head's block): that distance is the descriptor's leading
-    // byte offset.  (N = 64 per MMA: 55.8 us per layer, shared-memory operand bandwidth; N = 128: 46.6.)
-    constexpr uint32_t kIdesc = idesc_bf16(kGM, kGN, true);
-    constexpr uint64_t kLboNextHead = (uint64_t)((kGK * 128) >> 4) << 16;
-    // the last CTA row may hold one 128-row half only: its second half is never loaded nor multiplied
-    const int n_halves = ((int)blockIdx.y * kGMH + 1 < (p.rows + kGM - 1) / kGM) ? kGMH : 1;
+    // ===================== peer: forward "my stage is full" to the first CTA =====
     for (int ks = 0; ks < k_steps; ks++) {
       const int st = ks % kGStages;
       if (!wait_or_abort(bar_full + 8 * st, (uint32_t)((ks / kGStages) & 1), abort_flag)) break;
-      tc_fence_after();
-      if (elect_one()) {
-        const uint32_t sA = base + st * kStageBytes, sB = sA + kGMH * kABytes;
-#pragma unroll 1
-        for (int mh = 0; mh < n_halves; mh++)
-#pragma unroll
-          for (int kk = 0; kk < kGK / 16; kk++)
-            umma_ss(tmem + mh * kGN, smem_desc_sw128(sA + mh * kABytes + kk * 32),
-                    (smem_desc_sw128(sB + kk * 2048) & ~((uint64_t)0x3FFF << 16)) | kLboNextHead, kIdesc,
-                    (ks > 0 || kk > 0) ? 1u : 0u);
-        tc_commit(bar_empty + 8 * st);
-        if (ks + 1 == k_steps) tc_commit(bar_acc);
-      }
+      if (lane == 0) mbar_arrive_remote(bar_peer + 8 * st, 0);
       __syncwarp();
     }
   }
 
-  // ---- common exit: release tensor memory -----------------------------------
+  // ---- common exit: the pair meets, then tensor memory is released --------------
   tc_fence_before();
   __syncthreads();
   if (tid == 0 && *abort_flag) atomicExch(p.status, kStatusTimeout);
-  if (warp == 4) {
+  cluster_sync_all();  // the peer's shared and tensor memory are no longer in use by this CTA's MMAs
+  if (warp == kMmaWarp) {
     tc_fence_after();
-    tmem_dealloc(tmem, kGTmemCols);
+    tmem_dealloc_pair(tmem, kGTmemCols);
   }
 }
 
@@ -355,6 +419,26 @@ cudaError_t launch_pack_weights(const void* src, void* dst, int hidden, int cols
   return cudaGetLastError();
 }
 
+namespace {
+
+// cuTensorMapEncodeTiled, fetched through the runtime so that the library does not link the driver.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+}  // namespace
+
 cudaError_t launch_qkv_gemm(const QkvGemmParams& p, cudaStream_t stream) {
   if (p.rows <= 0) return cudaSuccess;
   static bool configured[64] = {};
@@ -365,8 +449,25 @@ cudaError_t launch_qkv_gemm(const QkvGemmParams& p, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  const dim3 grid((p.linear ? p.q_cols : p.q_cols + 2 * p.kv_cols) / kGN, (p.rows + kGMH * kGM - 1) / (kGMH * kGM));
-  qkv_gemm_kernel<<<grid, kGemmThreads, kGSmem, stream>>>(p);
+  const int total_heads = (p.linear ? p.q_cols : p.q_cols + 2 * p.kv_cols) / 64;
+  if (total_heads % 2 != 0) return cudaErrorInvalidValue;  // a pair splits every MMA's heads in two
+  // The activations as a 2-D tensor [rows, hidden] of bf16, read in boxes of 128 rows x 64 k with the
+  // 128-byte swizzle.  Base 16-byte aligned, row pitch a multiple of 16 bytes.
+  if ((reinterpret_cast<uintptr_t>(p.x) & 15u) != 0 || p.hidden % 64 != 0) return cudaErrorInvalidValue;
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (!encode) return cudaErrorNotSupported;
+  CUtensorMap x_map;
+  const cuuint64_t dims[2] = {(cuuint64_t)p.hidden, (cuuint64_t)p.rows};
+  const cuuint64_t pitch[1] = {(cuuint64_t)p.hidden * sizeof(__nv_bfloat16)};
+  const cuuint32_t box[2] = {(cuuint32_t)kGK, (cuuint32_t)kGM};
+  const cuuint32_t elem_stride[2] = {1, 1};
+  if (encode(&x_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(p.x), dims, pitch, box, elem_stride,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return cudaErrorInvalidValue;
+  // x: the two CTAs of a pair (the kernel's compile-time cluster) next to each other
+  const dim3 grid(2 * ((total_heads + kTileHeads - 1) / kTileHeads), (p.rows + 2 * kGM - 1) / (2 * kGM));
+  qkv_gemm_kernel<<<grid, kGemmThreads, kGSmem, stream>>>(x_map, p);
   return cudaGetLastError();
 }
 
