@@ -54,12 +54,14 @@ namespace {
 constexpr int kGM = 128;        // tokens per CTA = per packed activation tile; the pair's MMA has M = 256
 constexpr int kTileHeads = 6;   // heads (64 output columns) per pair tile: 4 in the first MMA, 2 in the second
 constexpr int kGK = 64;         // k per stage
-constexpr int kGStages = 5;
+constexpr int kGStages = 4;  // 3 and 5 stages run the MMA loop at the same pace
 constexpr int kABytes = kGM * 128;            // 16 KiB
 constexpr int kBBlock = kGK * 128;            // 8 KiB: 64 weight rows x one head
 constexpr int kBSlots = 3;                    // head blocks a CTA holds per stage: 2 of the first MMA, 1 of the second
 constexpr int kStageBytes = kABytes + kBSlots * kBBlock;  // 40 KiB
-constexpr int kGOffBar = kGStages * kStageBytes;
+constexpr int kGOffRope = kGStages * kStageBytes;  // RoPE factors of the CTA's 128 rows: 65 floats per row
+constexpr int kRopeBytes = kGM * 65 * 4;
+constexpr int kGOffBar = kGOffRope + kRopeBytes;
 constexpr int kGOffMisc = kGOffBar + (3 * kGStages + 1) * 8;
 constexpr int kGSmem = kGOffMisc + 16 + 112;
 constexpr int kEpiWarps = 8;      // two per 32-lane quarter of tensor memory, each takes every other head
@@ -132,6 +134,11 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap x_map, QkvGemmParams p) {
   cluster_sync_all();  // both CTAs' barriers exist before a remote arrive or a multicast commit reaches them
   tc_fence_after();
   const uint32_t tmem = *s_tmem_base;
+  // Launched with programmatic stream serialization: the set-up above may overlap the tail of the
+  // kernel in front (its CTAs leave their SMs one by one); nothing in global memory is touched
+  // before that kernel has completed.  The kernel behind this one may start its own set-up at once.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp == kLoadWarp) {
     // ===================== loads ==============================================
@@ -164,8 +171,9 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap x_map, QkvGemmParams p) {
     // ===================== epilogue ============================================
     // Warp w reads the tensor-memory lanes of quarter w % 4 (the only ones it may) and takes the
     // tile's heads w / 4, w / 4 + 2, w / 4 + 4: thread = token row = TMEM lane.
-    if (wait_or_abort(bar_acc, 0, abort_flag)) {
-      tc_fence_after();
+    // Everything that does not need the accumulators happens while the MMA loop runs: which token a
+    // row is, its cache block, its RoPE factors.
+    {
       const int quarter = warp & 3, hb0 = warp >> 2;
       const int row = m0 + quarter * 32 + lane;  // token row; TMEM lane = quarter * 32 + lane
       const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
@@ -190,11 +198,12 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap x_map, QkvGemmParams p) {
         }
       }
       const int slot = lpos % kBlockTok;
-      // This row's RoPE factors, once per row: 16 vector loads into a private row of the (now
-      // idle) stage ring, 65 floats apart so that the 32 lanes of a warp hit 32 banks.  Read per
+      // This row's RoPE factors, once per row: 16 vector loads into the row's slot of a shared-memory
+      // table, 65 floats apart so that the 32 lanes of a warp hit 32 banks (the two warps of a quarter
+      // write the same values).  Read per
       // element from global memory instead (scalar, one 128-byte line per lane and load, every head
       // over) they made the epilogue longer than the whole MMA loop.
-      float* trow = reinterpret_cast<float*>(sm) + (warp * 32 + lane) * 65;  // each warp stages its own copy
+      float* trow = reinterpret_cast<float*>(sm + kGOffRope) + (quarter * 32 + lane) * 65;
       if (any_rope && seq >= 0) {
         const float4* cs4 = reinterpret_cast<const float4*>(p.cos_table + (size_t)pos * 32);
         const float4* sn4 = reinterpret_cast<const float4*>(p.sin_table + (size_t)pos * 32);
@@ -219,9 +228,11 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap x_map, QkvGemmParams p) {
       __syncwarp();
       // per row: block id and slot for the cooperative stores below (negative: no token in the row)
       const int row_info = seq >= 0 ? ((blk << 4) | slot) : -1;
-      unsigned char* stage = sm + kEpiWarps * 32 * 65 * 4 + warp * 4096;  // 32 rows x 128 bytes per warp
+      unsigned char* stage = sm + warp * 4096;  // 32 rows x 128 bytes per warp, in the (then idle) stage ring
+      const bool acc_ok = wait_or_abort(bar_acc, 0, abort_flag);
+      tc_fence_after();
 #pragma unroll 1
-      for (int hb = hb0; hb < n_heads; hb += kEpiWarps / 4) {
+      for (int hb = hb0; acc_ok && hb < n_heads; hb += kEpiWarps / 4) {
         uint32_t acc[2][32];
         tmem_ld32(tmem + lane_base + hb * 64, acc[0]);
         tmem_ld32(tmem + lane_base + hb * 64 + 32, acc[1]);
@@ -467,8 +478,17 @@ cudaError_t launch_qkv_gemm(const QkvGemmParams& p, cudaStream_t stream) {
     return cudaErrorInvalidValue;
   // x: the two CTAs of a pair (the kernel's compile-time cluster) next to each other
   const dim3 grid(2 * ((total_heads + kTileHeads - 1) / kTileHeads), (p.rows + 2 * kGM - 1) / (2 * kGM));
-  qkv_gemm_kernel<<<grid, kGemmThreads, kGSmem, stream>>>(x_map, p);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = kGSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, qkv_gemm_kernel, x_map, p);
 }
 
 }  // namespace pa
