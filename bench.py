@@ -1098,7 +1098,6 @@ def run_qkv_prefill(env: Env, args, sub: bool = False):
         pool.set_free_order(np.random.default_rng(5).permutation(num_blocks))
         seq = pool.create_seq()
         pool.reserve(seq, S)
-        pool.reserve_rows(S, H)
         pool.batch_set([seq], [S])
         # weights are repacked once, at load time, into the tile image the GEMM bulk-copies
         pq, pk, pv = (paged.pack_projection_weights(w) for w in (wq, wk, wv))

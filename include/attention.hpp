@@ -47,7 +47,6 @@ class Attention {
     const int blocks = (max_seq_len + PA_BLOCK_TOKENS - 1) / PA_BLOCK_TOKENS;
     pa(pa_pool_create(&pool_, dev, 1, blocks, 8, 1, blocks));
     pa(pa_seq_create(pool_, &seq_));
-    pa(pa_pool_reserve_rows(pool_, max_seq_len, kHidden));
     const size_t big = (size_t)kHidden * kHidden * sizeof(__nv_bfloat16), small = (size_t)kHidden * 512 * sizeof(__nv_bfloat16);
     cuda(cudaMalloc(&packed_q_, big));
     cuda(cudaMalloc(&packed_k_, small));

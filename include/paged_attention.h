@@ -9,7 +9,7 @@
  * pa_last_error() gives the message of the calling thread's last failure.
  * Kernel entries are asynchronous on the stream they are given and do no
  * device synchronisation and no allocation: device memory is allocated only by
- * the set-up calls (pa_pool_create, pa_pool_reserve_rows, pa_exchange_create,
+ * the set-up calls (pa_pool_create, pa_exchange_create,
  * pa_gather_create).  A pool's host-side calls are not
  * thread-safe per pool; calls on one pool that overlap on the GPU share its
  * split-KV workspace and therefore must be ordered on one stream.
@@ -70,12 +70,6 @@ const char* pa_last_error(void);
 int pa_pool_create(pa_pool** out, int device, int num_layers, int num_blocks,
                    int kv_heads, int max_seqs, int max_blocks_per_seq);
 int pa_pool_destroy(pa_pool* pool);
-/* Set-up call for the tensor-core projections (pa_qkv_project_append,
- * pa_out_project_rows): sizes the pool's activation staging buffer for chunks of
- * up to max_rows rows of `hidden` columns.  Synchronises the device when it has
- * to replace a smaller buffer; the projection entries themselves never allocate
- * and answer PA_ERR_STATE when the chunk is larger than what was reserved. */
-int pa_pool_reserve_rows(pa_pool* pool, int max_rows, int hidden);
 int pa_pool_free_blocks(const pa_pool* pool, int* n_free);
 /* Order in which free blocks are handed out (order[0] first).  Only valid
  * while no block is in use; lets a seeded permutation reproduce a shuffled or
@@ -347,6 +341,37 @@ int pa_attention_step(pa_pool* pool, pa_exchange* exchange, int layer_begin, int
                       int add_residual, const float* cos_table, const float* sin_table, float scale,
                       void* stream);
 
+/* ---- the component after the attention block: the feed-forward block of a decode step -------
+ * Replaces runtime::FeedForward::forward (src/runtime/ffn.cu:34-145: rmsnorm_launch<2048>,
+ * launch_gemm_2048x8192 twice, launch_silu_mul, launch_gemm_8192x2048, per-call temporaries) and
+ * the residual add that follows it (src/runtime/transformer_block.cu:76-81) for decode shapes
+ * (1 to 8 rows), as two weight-streaming launches:
+ *     xn  = RMSNorm(x, ffn_norm[layer])                      (skipped when ffn_norm is NULL)
+ *     h   = bf16(SiLU(bf16(xn Wgate)) * bf16(xn Wup))        -> h_scratch [rows, inter]
+ *     out = bf16(h Wdown), then bf16(x + out) when add_residual != 0
+ * Weights row-major as the reference holds them: gate, up [hidden, inter], down [inter, hidden];
+ * pointers address layer 0.  Built for hidden 2048 and intermediate 8192.  out may alias x. */
+typedef struct pa_ffn_weights {
+  const void* ffn_norm; /* [layers][hidden] bf16, nullable */
+  const void* gate;     /* [layers][hidden, inter] */
+  const void* up;       /* [layers][hidden, inter] */
+  const void* down;     /* [layers][inter, hidden] */
+  int64_t norm_layer_stride, gate_layer_stride, up_layer_stride, down_layer_stride; /* elements */
+  float rms_eps;        /* the reference passes 1e-5 */
+  int hidden, inter;
+} pa_ffn_weights;
+int pa_ffn(const pa_ffn_weights* weights, int layer, const void* x, void* h_scratch, void* out, int rows,
+           int add_residual, void* stream);
+/* One decode step through whole transformer blocks of layers [layer_begin, layer_end), as
+ * runtime::TransformerBlock::forward chains them (src/runtime/transformer_block.cu:40-90):
+ *     a       = x_l + Attention(x_l)      (pa_attention_step of one layer, add_residual = 1)
+ *     x_{l+1} = a + FeedForward(a)        (pa_ffn, add_residual = 1)
+ * Five launches per layer, every one behind the first chained by programmatic dependent launch;
+ * all intermediate rows live in the pool.  Same batch rules as pa_attention_step. */
+int pa_block_step(pa_pool* pool, pa_exchange* exchange, int layer_begin, int layer_end,
+                  const pa_attention_weights* attention, const pa_ffn_weights* ffn, const void* x_in,
+                  void* x_out, const float* cos_table, const float* sin_table, float scale, void* stream);
+
 /* Host: fp32 cos/sin tables [seq_len][32], Llama-3 frequency scaling. */
 int pa_build_rope_tables(float* cos_table, float* sin_table, int seq_len);
 
@@ -413,8 +438,8 @@ int pa_out_project(const void* attn, const void* wo, const void* residual, void*
                    int64_t out_layer_stride, void* stream);
 /* The same for prompt chunks (any number of rows), on the tensor cores: the projection GEMM of
  * pa_qkv_project_append with a plain epilogue.  wo_packed from pa_pack_projection_weights; cols a
- * multiple of 256; attn [rows, hidden], residual (nullable) and out [rows, cols].  Uses the pool's
- * activation staging buffer (pa_pool_reserve_rows) and status word. */
+ * multiple of 256; attn [rows, hidden] (16-byte aligned, read in place through a tensor map),
+ * residual (nullable) and out [rows, cols].  Uses the pool's status word. */
 int pa_out_project_rows(pa_pool* pool, const void* attn, const void* wo_packed, const void* residual,
                         void* out, int rows, int hidden, int cols, void* stream);
 /* pa_qkv_project on weights repacked by pa_pack_projection_weights (the format
@@ -440,7 +465,7 @@ int pa_pack_projection_weights(const void* w, void* packed, int hidden, int cols
  * in batch order (rows = the batch's new tokens, which must also be its query
  * rows); weights packed by pa_pack_projection_weights; q_out [rows, q_heads*64] receives the rotated queries,
  * K (rotated) and V go straight into the layer's paged cache.  Needs 4 or 8 KV
- * heads in the pool and a staging buffer of at least `rows` rows (pa_pool_reserve_rows). */
+ * heads in the pool; x 16-byte aligned (it is read in place through a tensor map). */
 int pa_qkv_project_append(pa_pool* pool, int layer, const void* x, const void* wq, const void* wk,
                           const void* wv, const float* cos_table, const float* sin_table, void* q_out,
                           int hidden, void* stream);

@@ -1,6 +1,6 @@
 // C-ABI layer (include/paged_attention.h): argument checks, pool ownership and
 // launches.  No torch types, no exceptions across the boundary, no allocation
-// outside the set-up calls pa_pool_create and pa_pool_reserve_rows.
+// outside the set-up call pa_pool_create.
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -35,6 +35,7 @@ int fail(int code, const char* fmt, ...) {
 constexpr int kWsItems = 148 * 64;  // split-KV partials the workspace can hold
 constexpr int kMaxStepRows = 8;     // sequences of a decode step that pa_attention_step chains
 constexpr int kMaxStepHidden = 2048;
+constexpr int kMaxStepInter = 8192;   // feed-forward intermediate width pa_block_step has room for
 
 // Restores the caller's current device on scope exit.
 struct DeviceGuard {
@@ -76,8 +77,6 @@ struct pa_pool {
   bool no_layer_overlap = false;  // pa_pool_set_layer_overlap(pool, 0): a layer starts after the previous one has finished
   int step_combiners_override = 0;  // pa_pool_set_step_combiners
   long long step_launches = 0;  // decode steps that ran as one cooperative launch
-  void* x_pack = nullptr;       // activations in tile-image form for the projection GEMM (pa_pool_reserve_rows)
-  size_t x_pack_bytes = 0;
   // rows of a decode step between the kernels of pa_attention_step: q, k, v, rotated q, attention
   // output and two block inputs in turn, kMaxStepRows rows each
   __nv_bfloat16* step_ws = nullptr;
@@ -104,6 +103,8 @@ int qkv_project_impl(const void* x, const void* norm_weight, int64_t norm_layer_
 int out_project_impl(const void* attn, const void* wo, const void* residual, void* out, int rows, int layers,
                      int hidden, int cols, int64_t attn_layer_stride, int64_t wo_layer_stride,
                      int64_t residual_layer_stride, int64_t out_layer_stride, int pdl, void* stream);
+int ffn_impl(const void* x, const void* norm_w, float eps, const void* wg, const void* wu, const void* wd,
+             const void* residual, void* h, void* out, int rows, int hidden, int inter, int pdl, void* stream);
 }  // namespace pa
 
 struct pa_gather;
@@ -148,7 +149,7 @@ int pa_pool_create(pa_pool** out, int device, int num_layers, int num_blocks, in
     alloc((void**)&p->ws_count, (size_t)max_seqs * kv_heads * pa::kMaxStepLayers * sizeof(unsigned int));
     alloc((void**)&p->prefill_work, 64 * sizeof(int));
     alloc((void**)&p->step_ws, (size_t)kMaxStepRows * (3 * kv_heads * pa::kGroup * pa::kHeadDim +
-                                                        2 * kv_heads * pa::kHeadDim + 2 * kMaxStepHidden) *
+                                                        2 * kv_heads * pa::kHeadDim + 3 * kMaxStepHidden + kMaxStepInter) *
                                    sizeof(__nv_bfloat16));
     alloc((void**)&p->d_status, sizeof(int));
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&p->sm_count, cudaDevAttrMultiProcessorCount, device);
@@ -176,7 +177,6 @@ int pa_pool_destroy(pa_pool* p) {
     cudaFree(p->ws_count);
     cudaFree(p->prefill_work);
     cudaFree(p->step_ws);
-    cudaFree(p->x_pack);
     cudaFree(p->d_status);
   }
   delete p;
@@ -767,9 +767,9 @@ int pa_decode_step_sharded_colocated(pa_pool* const* pools, pa_exchange* const* 
 // programmatic dependent launch: each kernel starts the part of its work that does not depend on
 // the kernel in front (weight loads, cache copies) while that kernel finishes, and waits before it
 // reads its output.  All intermediate rows live in the pool's step workspace.
-int pa_attention_step(pa_pool* p, pa_exchange* x, int layer_begin, int layer_end, const pa_attention_weights* w,
-                      const void* x_in, void* x_out, int add_residual, const float* cos_table,
-                      const float* sin_table, float scale, void* stream) {
+static int step_layers(pa_pool* p, pa_exchange* x, int layer_begin, int layer_end, const pa_attention_weights* w,
+                       const pa_ffn_weights* f, const void* x_in, void* x_out, int add_residual,
+                       const float* cos_table, const float* sin_table, float scale, void* stream) {
   if (!p || !w || !x_in || !x_out || !cos_table || !sin_table)
     return fail(PA_ERR_INVALID_ARG, "pa_attention_step: NULL argument");
   if (!w->wq || !w->wk || !w->wv || !w->wo) return fail(PA_ERR_INVALID_ARG, "pa_attention_step: NULL weight");
@@ -795,6 +795,8 @@ int pa_attention_step(pa_pool* p, pa_exchange* x, int layer_begin, int layer_end
   __nv_bfloat16* attn = q_rot + (size_t)kMaxStepRows * q_cols;
   __nv_bfloat16* xpp[2] = {attn + (size_t)kMaxStepRows * q_cols,
                            attn + (size_t)kMaxStepRows * q_cols + (size_t)kMaxStepRows * kMaxStepHidden};
+  __nv_bfloat16* x_mid = xpp[1] + (size_t)kMaxStepRows * kMaxStepHidden;   // block input of the feed-forward block
+  __nv_bfloat16* h_rows = x_mid + (size_t)kMaxStepRows * kMaxStepHidden;   // its activated rows [rows, inter]
   bool appends = false;
   for (const auto& e : p->batch) appends = appends || e.n_new > 0;
   DeviceGuard g(p->device);
@@ -814,11 +816,37 @@ int pa_attention_step(pa_pool* p, pa_exchange* x, int layer_begin, int layer_end
     r = decode_impl(p, l, q, attn, q_cols, nullptr, nullptr, scale, stream, x, true, &fz);
     if (r != PA_OK) return r;
     __nv_bfloat16* out = l == layer_end - 1 ? (__nv_bfloat16*)x_out : xpp[(l - layer_begin) & 1];
-    r = pa::out_project_impl(attn, wo, add_residual ? cur : nullptr, out, rows, 1, q_cols, hidden, 0, 0, 0, 0, 1, stream);
+    // with a feed-forward block behind it the attention block writes the pool's row buffer
+    __nv_bfloat16* attn_out = f ? x_mid : out;
+    r = pa::out_project_impl(attn, wo, add_residual ? cur : nullptr, attn_out, rows, 1, q_cols, hidden, 0, 0, 0, 0, 1, stream);
     if (r != PA_OK) return r;
+    if (f) {
+      const __nv_bfloat16* fn = f->ffn_norm ? (const __nv_bfloat16*)f->ffn_norm + (size_t)l * f->norm_layer_stride : nullptr;
+      r = pa::ffn_impl(x_mid, fn, f->rms_eps, (const __nv_bfloat16*)f->gate + (size_t)l * f->gate_layer_stride,
+                       (const __nv_bfloat16*)f->up + (size_t)l * f->up_layer_stride,
+                       (const __nv_bfloat16*)f->down + (size_t)l * f->down_layer_stride, x_mid, h_rows, out, rows,
+                       f->hidden, f->inter, 1, stream);
+      if (r != PA_OK) return r;
+    }
     cur = out;
   }
   return PA_OK;
+}
+
+int pa_attention_step(pa_pool* p, pa_exchange* x, int layer_begin, int layer_end, const pa_attention_weights* w,
+                      const void* x_in, void* x_out, int add_residual, const float* cos_table,
+                      const float* sin_table, float scale, void* stream) {
+  return step_layers(p, x, layer_begin, layer_end, w, nullptr, x_in, x_out, add_residual, cos_table, sin_table, scale,
+                     stream);
+}
+
+int pa_block_step(pa_pool* p, pa_exchange* x, int layer_begin, int layer_end, const pa_attention_weights* w,
+                  const pa_ffn_weights* f, const void* x_in, void* x_out, const float* cos_table,
+                  const float* sin_table, float scale, void* stream) {
+  if (!f || !f->gate || !f->up || !f->down) return fail(PA_ERR_INVALID_ARG, "pa_block_step: NULL feed-forward weight");
+  if (w && f->hidden != w->hidden) return fail(PA_ERR_INVALID_ARG, "pa_block_step: the two blocks disagree on hidden");
+  if (f->inter > kMaxStepInter) return fail(PA_ERR_UNSUPPORTED, "pa_block_step: intermediate width above %d", kMaxStepInter);
+  return step_layers(p, x, layer_begin, layer_end, w, f, x_in, x_out, 1, cos_table, sin_table, scale, stream);
 }
 
 int pa_decode_step(pa_pool* p, int layer_begin, int layer_end, const void* q_in, const void* k_in,
@@ -1033,32 +1061,6 @@ int pa_pool_set_step_kernel(pa_pool* p, int enable) {
   return PA_OK;
 }
 
-// The GEMM reads its activations from a tile-image copy (bulk-copyable) in a staging buffer the
-// pool owns.  It is sized by pa_pool_reserve_rows, never by a kernel entry.
-static int check_activation_staging(pa_pool* p, int rows, int hidden, const char* who) {
-  const size_t need = (size_t)((rows + 127) / 128) * 128 * hidden * sizeof(__nv_bfloat16);
-  if (need <= p->x_pack_bytes) return PA_OK;
-  return fail(PA_ERR_STATE, "%s: %d rows x %d need a %zu-byte staging buffer, the pool has %zu "
-                            "(call pa_pool_reserve_rows first)", who, rows, hidden, need, p->x_pack_bytes);
-}
-
-int pa_pool_reserve_rows(pa_pool* p, int max_rows, int hidden) {
-  if (!p || max_rows < 1 || hidden < 64 || hidden % 64 != 0)
-    return fail(PA_ERR_INVALID_ARG, "pa_pool_reserve_rows: bad argument");
-  if (p->device < 0) return fail(PA_ERR_STATE, "pa_pool_reserve_rows: host-only pool");
-  const size_t need = (size_t)((max_rows + 127) / 128) * 128 * hidden * sizeof(__nv_bfloat16);
-  if (need <= p->x_pack_bytes) return PA_OK;
-  DeviceGuard g(p->device);
-  // set-up call: work that still reads the old buffer must have finished
-  PA_CUDA(cudaDeviceSynchronize());
-  if (p->x_pack) cudaFree(p->x_pack);
-  p->x_pack = nullptr;
-  p->x_pack_bytes = 0;
-  PA_CUDA(cudaMalloc(&p->x_pack, need));
-  p->x_pack_bytes = need;
-  return PA_OK;
-}
-
 int pa_pack_projection_weights(const void* w, void* packed, int hidden, int cols, void* stream) {
   if (!w || !packed || w == packed) return fail(PA_ERR_INVALID_ARG, "pa_pack_projection_weights: NULL or aliased argument");
   if (hidden < 64 || hidden % 64 != 0 || cols < 64 || cols % 64 != 0)
@@ -1085,7 +1087,7 @@ int pa_qkv_project_append(pa_pool* p, int layer, const void* x, const void* wq, 
   }
   if (rows == 0) return PA_OK;
   DeviceGuard g(p->device);
-  { const int r = check_activation_staging(p, rows, hidden, "pa_qkv_project_append"); if (r != PA_OK) return r; }
+  if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0) return fail(PA_ERR_INVALID_ARG, "pa_qkv_project_append: x must be 16-byte aligned");
   pa::QkvGemmParams a;
   a.x = (const __nv_bfloat16*)x;
   a.wq = (const __nv_bfloat16*)wq;
@@ -1118,7 +1120,7 @@ int pa_out_project_rows(pa_pool* p, const void* attn, const void* wo_packed, con
   if (hidden < 64 || hidden % 64 != 0 || cols < 256 || cols % 256 != 0)
     return fail(PA_ERR_UNSUPPORTED, "pa_out_project_rows: hidden must be a multiple of 64, cols a multiple of 256");
   DeviceGuard g(p->device);
-  { const int r = check_activation_staging(p, rows, hidden, "pa_out_project_rows"); if (r != PA_OK) return r; }
+  if ((reinterpret_cast<uintptr_t>(attn) & 15u) != 0) return fail(PA_ERR_INVALID_ARG, "pa_out_project_rows: attn must be 16-byte aligned");
   pa::QkvGemmParams a = {};
   a.x = (const __nv_bfloat16*)attn;
   a.wq = a.wk = a.wv = (const __nv_bfloat16*)wo_packed;

@@ -171,7 +171,7 @@ cudaError_t launch_prefill(const PrefillParams& p, int n_seqs, int n_q, cudaStre
 
 // Projection GEMM with RoPE + paged append epilogue (qkv_gemm.cu).
 struct QkvGemmParams {
-  const __nv_bfloat16* x;      // [rows, hidden] packed by launch_pack_x (128-row x 64-k tile images)
+  const __nv_bfloat16* x;      // [rows, hidden] row-major, 16-byte aligned (read through a tensor map)
   const __nv_bfloat16* wq;     // [hidden, q_cols] packed by launch_pack_weights
   const __nv_bfloat16* wk;     // [hidden, kv_cols] packed
   const __nv_bfloat16* wv;     // [hidden, kv_cols] packed
@@ -191,8 +191,6 @@ struct QkvGemmParams {
 cudaError_t launch_qkv_gemm(const QkvGemmParams& p, cudaStream_t stream);
 // row-major [hidden, cols] -> per (64 k-rows, 64 columns) an 8 KiB block in the GEMM's shared-memory layout
 cudaError_t launch_pack_weights(const void* src, void* dst, int hidden, int cols, cudaStream_t stream);
-// row-major [rows, hidden] -> per (128 rows, 64 k) a 16 KiB block; dst holds ceil(rows/128)*128*hidden elements
-cudaError_t launch_pack_x(const void* x, void* dst, int rows, int hidden, cudaStream_t stream);
 
 struct MergeParams {
   const float* o_parts;    // [n_parts][rows][64]

@@ -15,29 +15,36 @@
 // columns (6 heads of the concatenation Wq | Wk | Wv) over K = 2048 in steps of 64 with
 // tcgen05.mma.cta_group::2: M = 256 rows, 128 from each CTA's activation tile, accumulating in
 // each CTA's own tensor memory; of every B operand each CTA loads only half of the N columns.  Per
-// k-step a CTA therefore moves 16 KiB of activations and 24 KiB of weights for 128 x 384 x 64
-// multiply-adds.  Every byte comes through L2, and that traffic is what bounds this kernel: one
-// CTA per 256 x 256 tile (64 KiB per step for 256 x 256 x 64, 96 CTAs, 206.6 MB per layer) ran at
-// 38.8 us per layer; 128 x 256 tiles (295 MB) at 96 us.  2048 tokens x 3072 columns are 8 x 8
-// pair tiles = 128 CTAs.
-//   warp 8      load: per step one 16 KiB bulk (TMA) copy for the A tile (128 token rows x 64 k)
-//               and one 8 KiB bulk copy per head block of B (64 weight rows x 64 columns), issued
-//               by different lanes, 5 stages of 40 KiB.  Both operands are read from tile images
-//               of the shared-memory layout the tensor cores want (rows of 128 bytes, 16-byte
-//               chunks XOR-swizzled; A K-major, B MN-major), the same idea as the KV cache's tile
-//               layout: the weights are packed once, at load time (pack_weights_kernel), the
-//               activations by a small kernel in front of the GEMM (pack_x_kernel, 8 MB in, 8 MB
-//               out per layer).  With 16-byte cp.async from the row-major arrays instead the
-//               kernel ran at 96 us per layer: lg_throttle and long_scoreboard stalls on the load
-//               path, tensor pipe 18 % busy.
-//   warps 0-7   epilogue after the last step: thread = token row = TMEM lane; the two warps of a
-//               32-lane quarter take every other head of the tile.
+// k-step a CTA moves 16 KiB of activations and 24 KiB of weights for 128 x 384 x 64 multiply-adds
+// (one CTA per 256 x 256 tile moved 64 KiB for 256 x 256 x 64 and used 96 SMs).  2048 tokens x 3072
+// columns are 8 x 8 pair tiles = 128 CTAs.
+//   warp 8      load, 4 stages of 40 KiB.  Lane 0: the A tile (128 token rows x 64 k) with one
+//               tiled TMA copy through a tensor map of the row-major activations (128-byte
+//               swizzle: the copy lands as the canonical K-major operand; rows past the end read
+//               as zeros).  Lanes 1..3: one 8 KiB bulk copy per head block of B (64 weight rows x
+//               64 columns) from a tile image of the shared-memory layout the tensor cores want
+//               (rows of 128 bytes, 16-byte chunks XOR-swizzled, MN-major), the same idea as the
+//               KV cache's tile layout; the weights are packed once, at load time
+//               (pack_weights_kernel).  With 16-byte cp.async from row-major weights the kernel
+//               ran at 96 us per layer: lg_throttle and long_scoreboard stalls on the load path.
+//   warps 0-7   while the MMA loop runs: which token each row is, its cache block, its RoPE
+//               factors (into shared memory).  After the last step: thread = token row = TMEM
+//               lane; the two warps of a 32-lane quarter take every other head of the tile; a
+//               head's 32 rows x 128 bytes go through a staging tile so that the stores are whole
+//               128-byte lines.
 //   warp 9      first CTA of the pair: waits for its own stage and for the peer's (the peer's warp
 //               9 forwards its "stage full" barrier with a remote arrive), then one elected lane
 //               issues per 16-wide k-slice one MMA M256 N256 K16 (heads 0..3 of the tile; a CTA
 //               holds two of them, 8 KiB apart: the descriptor's leading byte offset) and one
 //               M256 N128 K16 (heads 4, 5), and frees the stage in BOTH CTAs with a multicast
 //               tcgen05.commit.
+// Measured on B200, 2048 tokens, per layer over 16 layers: 41.9 us with one CTA per 256 x 256
+// tile and a packing kernel for the activations; 37.1 us as pairs with the tensor map and the
+// coalesced epilogue; 34.8 us with the row lookups moved in front of the accumulator wait; 31.6 us
+// with programmatic dependent launch between consecutive calls; 23.2 us (1110 TFLOP/s) once the
+// peer's remote arrive was a CTA-scope release instead of a cluster-scope one, which had cost the
+// forwarding thread 0.6 us per stage and set the pace of the whole loop (3, 4 and 5 stages, with
+// or without the MMAs, with half the bytes: always 1100-1190 cycles per step).
 // Every wait is bounded; on expiry the CTA raises its abort flag, the status word gets
 // PA_ERR_TIMEOUT and all warps leave through the common exit, where the pair meets once more and
 // tensor memory is released.
@@ -399,31 +406,7 @@ pack_weights_kernel(const __nv_bfloat16* src, char* dst, int hidden, int cols) {
   }
 }
 
-// Row-major activations [rows, hidden] -> per (128-row tile, 64-k tile) a 16 KiB block of 128-byte
-// rows, 16-byte chunk c of row r stored at c ^ (r & 7); rows beyond `rows` are zero.
-__global__ void __launch_bounds__(256)
-pack_x_kernel(const __nv_bfloat16* x, char* dst, int rows, int hidden) {
-  const int cpr = hidden / 8;  // chunks per row
-  const size_t total = (size_t)((rows + kGM - 1) / kGM) * kGM * cpr;
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-    const int cg = (int)(i % cpr);
-    const int row = (int)(i / cpr);
-    const int r = row % kGM, mt = row / kGM, kt = cg >> 3, c = cg & 7;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (row < rows) v = *reinterpret_cast<const uint4*>(x + (size_t)row * hidden + cg * 8);
-    *reinterpret_cast<uint4*>(dst + ((size_t)mt * (hidden / kGK) + kt) * kABytes + r * 128 + ((c ^ (r & 7)) << 4)) = v;
-  }
-}
-
 }  // namespace
-
-cudaError_t launch_pack_x(const void* x, void* dst, int rows, int hidden, cudaStream_t stream) {
-  const size_t total = (size_t)((rows + kGM - 1) / kGM) * kGM * (hidden / 8);
-  int blocks = (int)((total + 255) / 256);
-  if (blocks > 148 * 8) blocks = 148 * 8;
-  pack_x_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, (char*)dst, rows, hidden);
-  return cudaGetLastError();
-}
 
 cudaError_t launch_pack_weights(const void* src, void* dst, int hidden, int cols, cudaStream_t stream) {
   pack_weights_kernel<<<148 * 4, 256, 0, stream>>>((const __nv_bfloat16*)src, (char*)dst, hidden, cols);

@@ -10,7 +10,7 @@ import ctypes as C
 
 import numpy as np
 
-from ._lib import AttentionWeights, check, lib
+from ._lib import AttentionWeights, FfnWeights, check, lib
 
 HEAD_DIM = 64
 GROUP = 4
@@ -185,10 +185,6 @@ class KVPool:
 
     def set_decode_shape(self, warps: int, stages: int) -> None:
         check(lib().pa_pool_set_decode_shape(self._h, warps, stages))
-
-    def reserve_rows(self, max_rows: int, hidden: int = 2048) -> None:
-        """Set-up call: size the activation staging buffer of the tensor-core projections."""
-        check(lib().pa_pool_reserve_rows(self._h, max_rows, hidden))
 
 
 class Exchange:
@@ -377,6 +373,35 @@ def attention_step(pool: "KVPool", weights: AttentionWeights, layer_begin: int, 
     check(lib().pa_attention_step(pool._h, xchg._h if xchg is not None else None, layer_begin, layer_end,
                                   C.byref(weights), _ptr(x_in), _ptr(x_out), int(add_residual), _ptr(cos), _ptr(sin),
                                   scale, stream))
+
+
+def ffn_weights(ffn_norm, gate, up, down, eps: float = 1e-5) -> "FfnWeights":
+    """Descriptor of per-layer feed-forward weights stacked along a leading layer dimension (contiguous
+    bf16): ffn_norm [layers, hidden] or None, gate/up [layers, hidden, inter], down [layers, inter, hidden]."""
+    w = FfnWeights()
+    w.ffn_norm = _ptr(ffn_norm)
+    w.gate, w.up, w.down = _ptr(gate), _ptr(up), _ptr(down)
+    hidden, inter = int(gate.shape[-2]), int(gate.shape[-1])
+    w.norm_layer_stride = hidden
+    w.gate_layer_stride = w.up_layer_stride = w.down_layer_stride = hidden * inter
+    w.rms_eps = eps
+    w.hidden, w.inter = hidden, inter
+    return w
+
+
+def ffn(weights: "FfnWeights", layer: int, x, h_scratch, out, rows: int, add_residual: bool = True,
+        stream: int = 0) -> None:
+    """out = (x +) FeedForward(x) of one layer for 1 to 8 rows; h_scratch [rows, inter] bf16."""
+    check(lib().pa_ffn(C.byref(weights), layer, _ptr(x), _ptr(h_scratch), _ptr(out), rows, int(add_residual), stream))
+
+
+def block_step(pool: "KVPool", attention: AttentionWeights, ffn_w: "FfnWeights", layer_begin: int, layer_end: int,
+               x_in, x_out, cos, sin, xchg: "Exchange | None" = None, scale: float = 0.125, stream: int = 0) -> None:
+    """One decode step through the transformer blocks of [layer_begin, layer_end): attention block and
+    feed-forward block with their residuals, layers chained by their data."""
+    check(lib().pa_block_step(pool._h, xchg._h if xchg is not None else None, layer_begin, layer_end,
+                              C.byref(attention), C.byref(ffn_w), _ptr(x_in), _ptr(x_out), _ptr(cos), _ptr(sin), scale,
+                              stream))
 
 
 def pack_projection_weights(w, stream: int = 0):

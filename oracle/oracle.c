@@ -420,3 +420,14 @@ void orc_rmsnorm(const uint16_t* x, const uint16_t* w, uint16_t* y, int rows, in
     }
   }
 }
+
+/* h = bf16((g * (1 / (1 + exp(-g)))) * u) on bf16 gate and up values, as silu_mul of the
+ * reference's activation kernel does in fp32 (src/kernels/silu/silu_8192.cu:55-100; the device
+ * evaluates exp with __expf, here it is expf: results may differ in the last bf16 bit). */
+void orc_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t* out, long long n) {
+  for (long long i = 0; i < n; i++) {
+    const float g = orc_bf16_to_f32(gate[i]), u = orc_bf16_to_f32(up[i]);
+    const float s = g * (1.0f / (1.0f + expf(-g)));
+    out[i] = orc_f32_to_bf16(s * u);
+  }
+}

@@ -115,6 +115,8 @@ void orc_gemm_bf16(const uint16_t* A, const uint16_t* B, uint16_t* C, int M, int
  * Follows rmsnorm_fwd_kernel, src/kernels/rmsnorm/rmsnorm.cu:51-110, including the order in which
  * its 256 threads add up the squares. */
 void orc_rmsnorm(const uint16_t* x, const uint16_t* w, uint16_t* y, int rows, int hidden, float eps);
+/* SiLU(gate) * up on bf16 values, fp32 arithmetic, bf16 result (src/kernels/silu/silu_8192.cu:55-100). */
+void orc_silu_mul(const uint16_t* gate, const uint16_t* up, uint16_t* out, long long n);
 
 int orc_num_threads(void);
 

@@ -206,6 +206,28 @@ def rmsnorm(x: np.ndarray, w: np.ndarray, eps: float = 1e-5) -> np.ndarray:
     return y
 
 
+def silu_mul(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    """bf16 bit patterns: bf16(SiLU(gate) * up), element-wise (src/kernels/silu/silu_8192.cu:55-100)."""
+    gate = np.ascontiguousarray(gate, dtype=np.uint16)
+    up = np.ascontiguousarray(up, dtype=np.uint16)
+    assert gate.shape == up.shape
+    out = np.empty_like(gate)
+    lib().orc_silu_mul(_p(gate), _p(up), _p(out), C.c_longlong(gate.size))
+    return out
+
+
+def ffn(x: np.ndarray, norm_w, wg: np.ndarray, wu: np.ndarray, wd: np.ndarray, eps: float = 1e-5,
+        add_residual: bool = True) -> np.ndarray:
+    """The reference's feed-forward block on bf16 bit patterns (src/runtime/ffn.cu:34-145 and the residual
+    add of src/runtime/transformer_block.cu:76-81): x [rows, hidden] -> [rows, hidden]."""
+    xn = rmsnorm(x, norm_w, eps) if norm_w is not None else np.ascontiguousarray(x, dtype=np.uint16)
+    h = silu_mul(gemm_bf16(xn, wg), gemm_bf16(xn, wu))
+    y = gemm_bf16(h, wd)
+    if not add_residual:
+        return y
+    return f32_to_bf16(bf16_to_f32(x) + bf16_to_f32(y))
+
+
 def num_threads() -> int:
     return int(lib().orc_num_threads())
 
@@ -274,6 +296,8 @@ def ref():
         r.ref_append_strided.restype = i
         r.ref_gemm.argtypes = [vp, vp, vp, i, i, i]
         r.ref_gemm.restype = i
+        r.ref_silu_mul.argtypes = [vp, vp, vp, i]
+        r.ref_silu_mul.restype = None
         r.ref_residual_add.argtypes = [vp, vp, vp, C.c_longlong]
         r.ref_residual_add.restype = i
         r.ref_rmsnorm.argtypes = [vp, vp, vp, i, f]

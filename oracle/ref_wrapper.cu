@@ -12,6 +12,10 @@
 //   ref_flash_output_layout -> launch_flash_output_layout (src/runtime/layout.hpp:5-9)
 //   ref_residual_add        -> transformer::residual_add  (src/kernels/residual_add/residual_add.hpp)
 //   ref_rmsnorm             -> rmsnorm_launch<2048>       (src/kernels/rmsnorm/rmsnorm.hpp:6-14)
+//   ref_gemm                -> launch_gemm_2048x2048 / _2048x512 / _2048x8192 / _8192x2048
+//                              (src/kernels/gemm/*.hpp), chosen by shape as Attention::forward and
+//                              FeedForward::forward choose them
+//   ref_silu_mul            -> launch_silu_mul            (src/kernels/silu/silu_8192.hpp)
 //   ref_append_*            -> the append the reference performs inline in
 //                              Attention::forward (src/runtime/attention.cu:239-262):
 //                              2*8*tokens device-to-device copies of 128 bytes.
@@ -25,10 +29,13 @@
 #include "flashattention.h"
 #include "gemm_2048x2048.hpp"
 #include "gemm_2048x512.hpp"
+#include "gemm_2048x8192.hpp"
+#include "gemm_8192x2048.hpp"
 #include "layout.hpp"
 #include "residual_add.hpp"
 #include "rmsnorm.hpp"
 #include "rope.hpp"
+#include "silu_8192.hpp"
 
 extern "C" {
 
@@ -67,16 +74,29 @@ void ref_flash_attention(const void* Q, const void* K, const void* V, void* O,
   transformer::launch_flash_attention(p);
 }
 
-// The projection GEMMs as Attention::forward calls them (src/runtime/attention.cu:138-191):
-// N = 2048 -> launch_gemm_2048x2048, N = 512 -> launch_gemm_2048x512.
+// The GEMMs as Attention::forward (src/runtime/attention.cu:138-191) and FeedForward::forward
+// (src/runtime/ffn.cu:84-127) call them: K = 2048, N = 2048 -> launch_gemm_2048x2048; N = 512 ->
+// launch_gemm_2048x512; N = 8192 -> launch_gemm_2048x8192; K = 8192, N = 2048 -> launch_gemm_8192x2048.
 int ref_gemm(const void* A, const void* B, void* C, int M, int N, int K) {
-  if (N == 2048)
-    launch_gemm_2048x2048((const __nv_bfloat16*)A, (const __nv_bfloat16*)B, (__nv_bfloat16*)C, M, N, K);
+  const __nv_bfloat16* a = (const __nv_bfloat16*)A;
+  const __nv_bfloat16* b = (const __nv_bfloat16*)B;
+  __nv_bfloat16* c = (__nv_bfloat16*)C;
+  if (K == 8192 && N == 2048)
+    launch_gemm_8192x2048(a, b, c, M, N, K);
+  else if (N == 2048)
+    launch_gemm_2048x2048(a, b, c, M, N, K);
   else if (N == 512)
-    launch_gemm_2048x512((const __nv_bfloat16*)A, (const __nv_bfloat16*)B, (__nv_bfloat16*)C, M, N, K);
+    launch_gemm_2048x512(a, b, c, M, N, K);
+  else if (N == 8192)
+    launch_gemm_2048x8192(a, b, c, M, N, K);
   else
     return 1;
   return (int)cudaGetLastError();
+}
+
+// out = SiLU(gate) * up over rows x 8192 elements (src/runtime/ffn.cu:112-118).
+void ref_silu_mul(const void* gate, const void* up, void* out, int rows) {
+  launch_silu_mul((const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, (__nv_bfloat16*)out, rows, 8192);
 }
 
 // out = a + b as TransformerBlock::forward adds the attention output to the block input

@@ -1,6 +1,6 @@
 """Makes the golden fixtures of this folder by running the REFERENCE's own CUDA
-kernels (oracle/_ref/libref.so: its flashattention.cu, rope.cu and layout.cu
-compiled unmodified for sm_100a) on seeded inputs.  Needs a B200.
+kernels (oracle/_ref/libref.so: its flashattention.cu, rope.cu, layout.cu, rmsnorm.cu and
+silu_8192.cu compiled unmodified for sm_100a) on seeded inputs.  Needs a B200.
 
     python tests/golden/make_golden.py <output folder>
 
@@ -74,6 +74,29 @@ def one_case(name, seed, position, tokens, max_seq, out_dir):
         v_cache_after=host(vc), o_flash=host(of), lse=lse.cpu().numpy(), o_layout=host(ol))
 
 
+def elementwise_cases(out_dir):
+    """The kernels either side of the attention path that have no free parameters: RMSNorm over rows of
+    2048 (rmsnorm_launch<2048>, 256 threads) and SiLU(gate) * up over rows of 8192 (launch_silu_mul)."""
+    rng = np.random.default_rng(105)
+    ref = orc.ref()
+    x = orc.randn_bf16(rng, (3, 2048), 1.5)
+    w = orc.randn_bf16(rng, (2048,), 0.7)
+    y = torch.zeros(3, 2048, dtype=torch.bfloat16, device=DEV)
+    xd, wd = dev(x), dev(w)
+    ref.ref_rmsnorm(xd.data_ptr(), wd.data_ptr(), y.data_ptr(), 3, 1e-5)
+    gate = orc.randn_bf16(rng, (2, 8192), 2.0)
+    up = orc.randn_bf16(rng, (2, 8192), 1.0)
+    gate[0, :8] = orc.f32_to_bf16(np.array([0.0, -0.0, 30.0, -30.0, 88.0, -88.0, 1e-3, -1e-3], np.float32))
+    h = torch.zeros(2, 8192, dtype=torch.bfloat16, device=DEV)
+    gd, ud = dev(gate), dev(up)
+    ref.ref_silu_mul(gd.data_ptr(), ud.data_ptr(), h.data_ptr(), 2)
+    torch.cuda.synchronize()
+    np.savez_compressed(os.path.join(out_dir, "elementwise_rmsnorm_silu.npz"), x=x, norm_w=w, rmsnorm_out=host(y),
+                        gate=gate, up=up, silu_mul_out=host(h))
+    print("elementwise: rmsnorm equal to oracle", np.array_equal(host(y), orc.rmsnorm(x, w, 1e-5)),
+          "; silu_mul bit-equal fraction", float((host(h) == orc.silu_mul(gate, up)).mean()))
+
+
 if __name__ == "__main__":
     out_dir = sys.argv[1]
     os.makedirs(out_dir, exist_ok=True)
@@ -81,3 +104,4 @@ if __name__ == "__main__":
     one_case("decode_1_at_100", 102, 100, 1, 112, out_dir)
     one_case("chunked_prefill_20_at_45", 103, 45, 20, 80, out_dir)
     one_case("prefill_66_at_0", 104, 0, 66, 66, out_dir)
+    elementwise_cases(out_dir)

@@ -178,6 +178,8 @@ def test_golden_vectors_from_reference_kernels():
     (made by tests/golden/make_golden.py on a B200)."""
     for path in sorted(glob.glob(os.path.join(GOLDEN, "*.npz"))):
         g = np.load(path)
+        if "y0_variant" not in g.files:
+            continue  # the element-wise fixture has its own test
         variant = int(g["y0_variant"])
         pos, tokens, max_seq = int(g["position"]), int(g["tokens"]), int(g["max_seq"])
         cos, sin = orc.build_rope_tables(max_seq)
@@ -211,3 +213,38 @@ def test_gemm_restatement_against_numpy():
     want = orc.f32_to_bf16(ref.astype(np.float32))
     # float64 -> float32 -> bf16 can differ from the oracle's path only by double rounding: none here
     assert np.array_equal(got, want)
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(GOLDEN, "elementwise_rmsnorm_silu.npz")), reason="fixture not made yet")
+def test_golden_rmsnorm_and_silu_mul_from_reference_kernels():
+    """RMSNorm: the oracle restates the reference kernel's summation order, so the bits are equal.
+    SiLU(gate) * up: the device evaluates exp with __expf, the oracle with expf; equal to within one
+    bf16 unit everywhere, bit-equal almost everywhere."""
+    g = np.load(os.path.join(GOLDEN, "elementwise_rmsnorm_silu.npz"))
+    assert np.array_equal(orc.rmsnorm(g["x"], g["norm_w"], 1e-5), g["rmsnorm_out"])
+    got = orc.silu_mul(g["gate"], g["up"])
+    a = orc.bf16_to_f32(got).astype(np.float64)
+    b = orc.bf16_to_f32(g["silu_mul_out"]).astype(np.float64)
+    assert np.all(np.abs(a - b) <= np.maximum(np.abs(a), np.abs(b)) * 2.0 ** -7 + 1e-30)
+    assert float((got == g["silu_mul_out"]).mean()) > 0.99
+
+
+def test_silu_mul_and_ffn_restatement_against_numpy():
+    rng = np.random.default_rng(78)
+    gate = orc.randn_bf16(rng, (2, 512), 2.0)
+    up = orc.randn_bf16(rng, (2, 512), 1.0)
+    gf, uf = orc.bf16_to_f32(gate).astype(np.float64), orc.bf16_to_f32(up).astype(np.float64)
+    want = gf / (1.0 + np.exp(-gf)) * uf
+    got = orc.bf16_to_f32(orc.silu_mul(gate, up)).astype(np.float64)
+    assert np.all(np.abs(got - want) <= np.abs(want) * 2.0 ** -7 + 1e-30)
+    # the block: RMSNorm -> gate/up GEMMs -> SiLU * up -> down GEMM -> residual, piece by piece
+    x = orc.randn_bf16(rng, (2, 128), 1.0)
+    nw = orc.randn_bf16(rng, (128,), 0.7)
+    wg = orc.randn_bf16(rng, (128, 256), 0.1)
+    wu = orc.randn_bf16(rng, (128, 256), 0.1)
+    wd = orc.randn_bf16(rng, (256, 128), 0.1)
+    xn = orc.rmsnorm(x, nw, 1e-5)
+    h = orc.silu_mul(orc.gemm_bf16(xn, wg), orc.gemm_bf16(xn, wu))
+    y = orc.gemm_bf16(h, wd)
+    assert np.array_equal(orc.ffn(x, nw, wg, wu, wd, 1e-5, False), y)
+    assert np.array_equal(orc.ffn(x, nw, wg, wu, wd, 1e-5, True), orc.f32_to_bf16(orc.bf16_to_f32(x) + orc.bf16_to_f32(y)))

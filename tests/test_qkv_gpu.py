@@ -128,7 +128,6 @@ def _project_append_case(rng, position, tokens):
     pool.batch_set([s], [tokens])
     q_out = torch.full((tokens, 2048), 3.0, dtype=torch.bfloat16, device=DEV)
     pq, pk, pv = (paged.pack_projection_weights(to_dev(w)) for w in (wq, wk, wv))
-    pool.reserve_rows(tokens)
     pool.qkv_project_append(0, to_dev(x), pq, pk, pv, f32_dev(cos), f32_dev(sin), q_out)
     torch.cuda.synchronize()
     pool.check()
@@ -225,11 +224,11 @@ def test_qkv_project_append_two_sequences(cuda):
     pool.batch_set(seqs, news)
     q_out = torch.zeros(rows, 2048, dtype=torch.bfloat16, device=DEV)
     pq, pk, pv = (paged.pack_projection_weights(to_dev(w)) for w in (wq, wk, wv))
-    # no kernel entry allocates: an unreserved staging buffer is refused, not grown
+    # the activations are read in place through a tensor map: a base that is not 16-byte aligned is refused
+    x_odd = torch.zeros(rows * 2048 + 1, dtype=torch.bfloat16, device=DEV)[1:].view(rows, 2048)
     with pytest.raises(_lib.PagedAttentionError) as ei:
-        pool.qkv_project_append(0, to_dev(x), pq, pk, pv, f32_dev(cos), f32_dev(sin), q_out)
-    assert ei.value.code == 6 and "pa_pool_reserve_rows" in str(ei.value)
-    pool.reserve_rows(rows)
+        pool.qkv_project_append(0, x_odd, pq, pk, pv, f32_dev(cos), f32_dev(sin), q_out)
+    assert ei.value.code == 1 and "16-byte" in str(ei.value)
     pool.qkv_project_append(0, to_dev(x), pq, pk, pv, f32_dev(cos), f32_dev(sin), q_out)
     torch.cuda.synchronize()
     pool.check()
@@ -292,7 +291,6 @@ def test_out_project_rows_on_tensor_cores(cuda, rows, with_residual):
     pool = paged.KVPool(1, 8, 8, 1)
     out = torch.full((rows, 2048), 5.0, dtype=torch.bfloat16, device=DEV)
     ad, wd, rd = to_dev(a), to_dev(wo), to_dev(res)
-    pool.reserve_rows(rows)
     pool.out_project_rows(ad, paged.pack_projection_weights(wd), rd if with_residual else None, out, rows)
     torch.cuda.synchronize()
     pool.check()
