@@ -91,9 +91,11 @@ def measured_tflops():
 
 
 # ncu captures (profiles/): dram read+write bytes per layer of a workload's dominant kernel.
-# decode128k: the 2-layer decode_step_kernel capture read 537.09 MB and wrote 6.00 MB.
-NCU_TRAFFIC_BYTES = {"decode128k": 271544320, "decode4k": None}
-NCU_APPEND_TRAFFIC = None  # dram bytes of one 2048-token append_kernel launch, from the ncu capture
+# decode128k: the 2-layer decode_step_kernel capture read 537.10 MB and wrote 6.58 MB.
+NCU_TRAFFIC_BYTES = {"decode128k": 271840128, "decode4k": None}
+# one 2048-token append_kernel launch: 13.12 MB read from DRAM, 0 written inside the kernel's window (the
+# 12.6 MB it writes are still in L2 when it ends)
+NCU_APPEND_TRAFFIC = 13116416
 
 
 def row_rel_err(got: np.ndarray, want: np.ndarray, row: int = 64) -> float:
@@ -1322,7 +1324,8 @@ def run_prefill(env: Env, args, sub: bool = False, append_only: bool = False):
                             "unit": "GB/s", "frac": round(achieved / peak, 4), "peak_source": f"of {pk}",
                             "us_per_launch": round(ms_k * 1e3, 2), "bytes_per_launch": append_bytes,
                             "traffic": NCU_APPEND_TRAFFIC,
-                            "traffic_note": "ncu capture of one 2048-token append_kernel launch (profiles/)"}
+                            "traffic_note": "ncu capture of one 2048-token append_kernel launch (profiles/): DRAM reads; the rows it "
+                                            "writes are still in L2 when the kernel ends"}
         # check: rotated Q rows of layer 0 against the oracle, bit for bit (first 64 tokens); the CPU
         # baseline is the oracle's RoPE + placement of those tokens
         t0 = time.perf_counter()
@@ -1390,8 +1393,11 @@ def prefill_cpu_baseline(q_rot, out, pool, seq, S, budget_s=10.0):
 # =============================================================================
 # the decode step with its true data flow: projections -> attention -> output projection per layer
 # =============================================================================
-def run_chain(env: Env, args, sub: bool = False):
-    """One token through 16 attention blocks, each layer fed by the one before it (no FFN in between:
+def run_chain(env: Env, args, sub: bool = False, ffn: bool = False):
+    """ffn=True (workload block_chain): whole transformer blocks — the attention block below followed by
+    the feed-forward block (RMSNorm, gate and up projections 2048 -> 8192, SiLU(gate) * up, down
+    projection, residual): two more launches and 100.7 MB more weights per layer.
+    ffn=False (workload decode_chain): one token through 16 attention blocks, each layer fed by the one before it (no FFN in between:
     x_{l+1} = x_l + attention(RMSNorm(x_l)) W_o): per layer RMSNorm + Q/K/V projections (one launch),
     RoPE + append + paged decode attention (one launch), output projection + residual (one launch),
     chained by programmatic dependent launch.  Context 4096 by default (--chain-ctx).  Per layer the
@@ -1416,11 +1422,15 @@ def run_chain(env: Env, args, sub: bool = False):
     mk = lambda *shape, s=0.03: (torch.randn(*shape, generator=gen, device=dev) * s).to(torch.bfloat16)
     Ws = [dict(nw=mk(LAYERS, H, s=0.7), wq=mk(LAYERS, H, NQ), wk=mk(LAYERS, H, NKV), wv=mk(LAYERS, H, NKV),
                wo=mk(LAYERS, NQ, H)) for _ in range(SETS)]
+    INTER = 8192
+    if ffn:
+        for w in Ws:
+            w.update(fn=mk(LAYERS, H, s=0.7), wg=mk(LAYERS, H, INTER), wu=mk(LAYERS, H, INTER), wd=mk(LAYERS, INTER, H, s=0.02))
     x_host = torch.randn(1, H, generator=torch.Generator().manual_seed(6)).to(torch.bfloat16).pin_memory()
     y_host = torch.zeros(1, H, dtype=torch.bfloat16).pin_memory()
     x_dev = x_host.to(dev)
     y_dev = torch.zeros(1, H, dtype=torch.bfloat16, device=dev)
-    weight_bytes = (H * (NQ + 2 * NKV) + NQ * H + H) * 2
+    weight_bytes = (H * (NQ + 2 * NKV) + NQ * H + H) * 2 + ((3 * H * INTER + H) * 2 if ffn else 0)
     total_steps = warmup + 2 * steps + 12
     state = {"len": ctx, "i": 0}
     ref = orc.ref() if orc.ref_available() else None
@@ -1456,6 +1466,13 @@ def run_chain(env: Env, args, sub: bool = False):
         torch.cuda.synchronize()
         del ones, zeros
         descs = [paged.attention_weights(w["nw"], w["wq"], w["wk"], w["wv"], w["wo"]) for w in Ws]
+        fdescs = [paged.ffn_weights(w["fn"], w["wg"], w["wu"], w["wd"]) for w in Ws] if ffn else None
+
+        def run_layers(s, l0, l1, xin, xout):
+            if ffn:
+                paged.block_step(pool, descs[s], fdescs[s], l0, l1, xin, xout, cos, sin, xchg=xchg)
+            else:
+                paged.attention_step(pool, descs[s], l0, l1, xin, xout, cos, sin, add_residual=True, xchg=xchg)
         if world > 1:
             xchg = paged.Exchange(local_rank, rank, world, 1, KV_HEADS)
             handles = [None] * world
@@ -1473,7 +1490,7 @@ def run_chain(env: Env, args, sub: bool = False):
                 pool.batch_set([seq])
             else:
                 pool.batch_set_sharded([seq], [1 if rank == owner else 0], [1], [state["len"] - 1], [lo])
-            paged.attention_step(pool, descs[s], 0, LAYERS, x_dev, y_dev, cos, sin, add_residual=True, xchg=xchg)
+            run_layers(s, 0, LAYERS, x_dev, y_dev)
 
     if ref is not None and (ref_arm or sub) and rank == 0:
         max_seq = ctx + total_steps + 2
@@ -1483,7 +1500,8 @@ def run_chain(env: Env, args, sub: bool = False):
             kc[layer, :, :ctx] = (torch.randn(KV_HEADS, ctx, D, generator=kvgen, device=dev) * 0.5).to(torch.bfloat16)
             vc[layer, :, :ctx] = (torch.randn(KV_HEADS, ctx, D, generator=kvgen, device=dev) * 0.5).to(torch.bfloat16)
         bufs = {n: torch.zeros(1, c, dtype=torch.bfloat16, device=dev) for n, c in
-                (("xn", H), ("q", NQ), ("k", NKV), ("v", NKV), ("arow", NQ), ("lin", H), ("xa", H), ("xb", H))}
+                (("xn", H), ("q", NQ), ("k", NKV), ("v", NKV), ("arow", NQ), ("lin", H), ("xa", H), ("xb", H), ("xm", H),
+                 ("g", INTER), ("u", INTER), ("h", INTER))}
         qf = torch.empty(Q_HEADS, 1, D, dtype=torch.bfloat16, device=dev)
         kf = torch.empty(KV_HEADS, 1, D, dtype=torch.bfloat16, device=dev)
         vf = torch.empty(KV_HEADS, 1, D, dtype=torch.bfloat16, device=dev)
@@ -1513,7 +1531,21 @@ def run_chain(env: Env, args, sub: bool = False):
                 ref.ref_gemm(bufs["arow"].data_ptr(), w["wo"][l].data_ptr(), bufs["lin"].data_ptr(), 1, H, NQ)
                 torch.cuda.synchronize()
                 nxt = bufs["xa"] if l % 2 == 0 else bufs["xb"]
-                ref.ref_residual_add(cur.data_ptr(), bufs["lin"].data_ptr(), nxt.data_ptr(), H)
+                if not ffn:
+                    ref.ref_residual_add(cur.data_ptr(), bufs["lin"].data_ptr(), nxt.data_ptr(), H)
+                    torch.cuda.synchronize()
+                    cur = nxt
+                    continue
+                # FeedForward::forward (one synchronisation, at its end) and the block's second residual add
+                ref.ref_residual_add(cur.data_ptr(), bufs["lin"].data_ptr(), bufs["xm"].data_ptr(), H)
+                torch.cuda.synchronize()
+                ref.ref_rmsnorm(bufs["xm"].data_ptr(), w["fn"][l].data_ptr(), bufs["xn"].data_ptr(), 1, 1e-5)
+                ref.ref_gemm(bufs["xn"].data_ptr(), w["wg"][l].data_ptr(), bufs["g"].data_ptr(), 1, INTER, H)
+                ref.ref_gemm(bufs["xn"].data_ptr(), w["wu"][l].data_ptr(), bufs["u"].data_ptr(), 1, INTER, H)
+                ref.ref_silu_mul(bufs["g"].data_ptr(), bufs["u"].data_ptr(), bufs["h"].data_ptr(), 1)
+                ref.ref_gemm(bufs["h"].data_ptr(), w["wd"][l].data_ptr(), bufs["lin"].data_ptr(), 1, H, INTER)
+                torch.cuda.synchronize()
+                ref.ref_residual_add(bufs["xm"].data_ptr(), bufs["lin"].data_ptr(), nxt.data_ptr(), H)
                 torch.cuda.synchronize()
                 cur = nxt
             y_dev.copy_(cur)
@@ -1543,12 +1575,12 @@ def run_chain(env: Env, args, sub: bool = False):
     line = None
     if rank == 0:
         line = {
-            "metric": "decode_chain_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": 1 if ref_arm else world,
+            "metric": "block_chain_hbm_gbs" if ffn else "decode_chain_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": 1 if ref_arm else world,
             "steps": steps, "warmup": warmup, "ms_per_step": round(ms / steps, 4),
             "us_per_token": round(ms / steps * 1e3, 2), "us_per_layer": round(ms / steps * 1e3 / LAYERS, 2),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"decode_chain_ctx{ctx}_x{LAYERS}layers_batch1", "context": ctx, "layers": LAYERS,
-                       "batch": 1, "hidden": H, "bytes": "per layer: Wq, Wk, Wv, Wo, norm weight + the layer's cache (2048 L + ...)",
+            "config": {"workload": f"{'block' if ffn else 'decode'}_chain_ctx{ctx}_x{LAYERS}layers_batch1", "context": ctx, "layers": LAYERS,
+                       "batch": 1, "hidden": H, "bytes": "per layer: Wq, Wk, Wv, Wo, norm weight" + (", Wgate, Wup, Wdown, FFN norm weight" if ffn else "") + " + the layer's cache (2048 L + ...)",
                        "parallelism": "1 GPU" if world == 1 or ref_arm else
                                       f"cache split by token range over {world} GPUs, weights replicated",
                        "l2": f"{SETS} weight sets in rotation ({SETS * LAYERS * weight_bytes / 1e9:.2f} GB) + "
@@ -1556,7 +1588,8 @@ def run_chain(env: Env, args, sub: bool = False):
             "e2e": {"value": round(nbytes_e2e / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
                     "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2,
                     "ms_per_step": round(ms_e2e / steps, 4)},
-            "gpu_launches": (LAYERS * 11 if ref_arm else LAYERS * 3) * steps, "clocks": env.sampler.summary(m0, m1),
+            "gpu_launches": (LAYERS * (17 if ffn else 11) if ref_arm else LAYERS * (5 if ffn else 3)) * steps,
+            "clocks": env.sampler.summary(m0, m1),
         }
     if ref_arm:
         line["impl"] = "reference"
@@ -1579,8 +1612,8 @@ def run_chain(env: Env, args, sub: bool = False):
         pool.reserve(seq, L0 + 1)
         pool.batch_set([seq])
         y0 = torch.zeros(1, H, dtype=torch.bfloat16, device=dev)
-        paged.attention_step(pool, descs[0], 0, 1, x_dev, y0, cos, sin)
-        paged.attention_step(pool, descs[0], 1, LAYERS, y0, y_dev, cos, sin)
+        run_layers(0, 0, 1, x_dev, y0)
+        run_layers(0, 1, LAYERS, y0, y_dev)
         torch.cuda.synchronize()
         pool.check()
         t0 = time.perf_counter()
@@ -1597,20 +1630,25 @@ def run_chain(env: Env, args, sub: bool = False):
             O, _ = orc.attention(orc.rope(q, cos_h, sin_h, L0, 1), K, V, L0 + 1)
             lin = orc.gemm_bf16(orc.f32_to_bf16(O[:, 0].reshape(1, NQ)), _u16(w["wo"][l]))
             cur = orc.f32_to_bf16(orc.bf16_to_f32(cur) + orc.bf16_to_f32(lin))
+            if ffn:
+                cur = orc.ffn(cur, _u16(w["fn"][l]), _u16(w["wg"][l]), _u16(w["wu"][l]), _u16(w["wd"][l]), 1e-5, True)
             if l == 0:
                 first = cur
         dt = time.perf_counter() - t0
         e0 = row_rel_err(orc.bf16_to_f32(_u16(y0)), orc.bf16_to_f32(first), row=H)
         e15 = row_rel_err(orc.bf16_to_f32(_u16(y_dev)), orc.bf16_to_f32(cur), row=H)
-        line["checks"] = {"oracle_layer0_max_err_over_row_max": e0, "oracle_layer0_ok": bool(e0 <= 2.0 ** -6),
+        line["checks"] = {"oracle_layer0_max_err_over_row_max": e0, "oracle_layer0_ok": bool(e0 <= (2.0 ** -5 if ffn else 2.0 ** -6)),
                           "oracle_16_layer_chain_max_err_over_row_max": e15}
         line["cpu_baseline"] = {"value": round(LAYERS * (decode_bytes(L0 + 1) + weight_bytes) / dt / 1e9, 3), "unit": "GB/s",
                                 "cores": orc.num_threads(), "kind": "port",
                                 "sample": f"one token through all {LAYERS} layers with the CPU oracle chain, {dt:.2f} s"}
-        line["roofline"] = {"bound": "hbm", "kernel": "qkv_project_kernel + decode_kernel + qkv_project_kernel (3 launches per layer)",
+        n_launch = 5 if ffn else 3
+        line["roofline"] = {"bound": "hbm", "kernel": "qkv_project_kernel + decode_kernel + qkv_project_kernel" +
+                                                       (" + ffn_gate_up_kernel + ffn_down_kernel" if ffn else "") +
+                                                       f" ({n_launch} launches per layer)",
                             "achieved": round(value, 1), "peak": peak, "unit": "GB/s", "frac": round(value / peak, 4),
-                            "peak_source": f"of {peak_kind}", "us_per_launch": round(ms / steps * 1e3 / LAYERS / 3, 2),
-                            "bytes_per_launch": (decode_bytes(ctx) + weight_bytes) // 3, "traffic": None}
+                            "peak_source": f"of {peak_kind}", "us_per_launch": round(ms / steps * 1e3 / LAYERS / n_launch, 2),
+                            "bytes_per_launch": (decode_bytes(ctx) + weight_bytes) // n_launch, "traffic": None}
         if sub and ref is not None:
             ref_step()
             rms = local_timed(torch, ref_step, 2) / 2
@@ -1618,7 +1656,9 @@ def run_chain(env: Env, args, sub: bool = False):
             line["reference"] = {"value": round(rb / (rms * 1e-3) / 1e9, 2), "unit": "GB/s",
                                  "us_per_layer": round(rms * 1e3 / LAYERS, 2),
                                  "how": "the reference's RMSNorm, 3 GEMMs, RoPE kernels, append copies, attention kernel, "
-                                        "layout kernel, output GEMM and residual add per layer, with its synchronisations"}
+                                        "layout kernel, output GEMM and residual add" +
+                                        (", then RMSNorm, gate and up GEMMs, SiLU*up kernel, down GEMM and residual add" if ffn else "") +
+                                        " per layer, with its synchronisations"}
     env.barrier()
     if xchg is not None:
         xchg.close()
@@ -1646,6 +1686,7 @@ SUB_BLOCKS = {
     "qkv_decode": lambda env, a: run_qkv(env, a, sub=True, which="qkv"),
     "qkv_prefill": lambda env, a: run_qkv_prefill(env, a, sub=True),
     "decode_chain": lambda env, a: run_chain(env, a, sub=True),
+    "block_chain": lambda env, a: run_chain(env, a, sub=True, ffn=True),
 }
 
 
@@ -1666,7 +1707,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode128k",
                     choices=sorted(WORKLOADS) + ["prefill2k", "append2k", "batch64", "qkv_decode", "out_project", "qkv_prefill",
-                                                  "decode_chain"])
+                                                  "decode_chain", "block_chain"])
     ap.add_argument("--chain-ctx", type=int, default=4096, help="decode_chain: context length")
     ap.add_argument("--no-sub", action="store_true", help="default workload: skip the sub-blocks")
     ap.add_argument("--sub", default="", help="default workload: comma-separated sub-blocks to run (default: all)")
@@ -1690,7 +1731,7 @@ def main():
     rank, _, world = dist_env()
     if args.impl == "reference" and rank != 0:
         return  # the reference is single-GPU: rank 0 alone runs it
-    sharded = args.workload in WORKLOADS or args.workload in ("batch64", "qkv_decode", "out_project", "decode_chain")
+    sharded = args.workload in WORKLOADS or args.workload in ("batch64", "qkv_decode", "out_project", "decode_chain", "block_chain")
     env = Env(want_group=(args.impl == "ours" and sharded))
     line = None
     if args.workload in WORKLOADS:
@@ -1728,6 +1769,8 @@ def main():
         line = run_batch(env, args)
     elif args.workload == "decode_chain":
         line = run_chain(env, args)
+    elif args.workload == "block_chain":
+        line = run_chain(env, args, ffn=True)
     if rank == 0 and line is not None:
         print(json.dumps(line), flush=True)
     env.sampler.stop()
