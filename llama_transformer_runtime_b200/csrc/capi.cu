@@ -1136,6 +1136,57 @@ int pa_out_project_rows(pa_pool* p, const void* attn, const void* wo_packed, con
   return PA_OK;
 }
 
+static int linear_rows(pa_pool* p, const void* x, const void* w_packed, const void* residual, void* out, int rows,
+                       int k, int n, void* stream) {
+  pa::QkvGemmParams a = {};
+  a.x = (const __nv_bfloat16*)x;
+  a.wq = a.wk = a.wv = (const __nv_bfloat16*)w_packed;
+  a.q_out = (__nv_bfloat16*)out;
+  a.status = p->d_status;
+  a.rows = rows;
+  a.hidden = k;
+  a.q_cols = n;
+  a.kv_cols = 256;
+  a.linear = 1;
+  a.residual = (const __nv_bfloat16*)residual;
+  PA_CUDA(pa::launch_qkv_gemm(a, (cudaStream_t)stream));
+  return PA_OK;
+}
+
+int pa_ffn_rows(pa_pool* p, const pa_ffn_weights* w, int layer, const void* x, void* scratch, void* out, int rows,
+                int add_residual, void* stream) {
+  if (!p || !w || !x || !scratch || !out) return fail(PA_ERR_INVALID_ARG, "pa_ffn_rows: NULL argument");
+  if (!w->gate || !w->up || !w->down) return fail(PA_ERR_INVALID_ARG, "pa_ffn_rows: NULL weight");
+  if (p->device < 0) return fail(PA_ERR_STATE, "pa_ffn_rows: host-only pool");
+  if (layer < 0) return fail(PA_ERR_INVALID_ARG, "pa_ffn_rows: negative layer");
+  if (rows < 1) return PA_OK;
+  const int hidden = w->hidden, inter = w->inter;
+  if (hidden < 256 || hidden > 2048 || hidden % 256 != 0 || inter < 128 || inter % 128 != 0)
+    return fail(PA_ERR_UNSUPPORTED, "pa_ffn_rows: hidden a multiple of 256 up to 2048, intermediate a multiple of 128");
+  if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(scratch)) & 15u) != 0)
+    return fail(PA_ERR_INVALID_ARG, "pa_ffn_rows: x and scratch must be 16-byte aligned");
+  DeviceGuard g(p->device);
+  __nv_bfloat16* xn = (__nv_bfloat16*)scratch;
+  __nv_bfloat16* gate = xn + (size_t)rows * hidden;
+  __nv_bfloat16* up = gate + (size_t)rows * inter;
+  const __nv_bfloat16* in = (const __nv_bfloat16*)x;
+  if (w->ffn_norm) {
+    const int r = pa_rmsnorm(x, (const __nv_bfloat16*)w->ffn_norm + (size_t)layer * w->norm_layer_stride, xn, rows, hidden,
+                             w->rms_eps, stream);
+    if (r != PA_OK) return r;
+    in = xn;
+  }
+  int r = linear_rows(p, in, (const __nv_bfloat16*)w->gate + (size_t)layer * w->gate_layer_stride, nullptr, gate, rows,
+                      hidden, inter, stream);
+  if (r != PA_OK) return r;
+  r = linear_rows(p, in, (const __nv_bfloat16*)w->up + (size_t)layer * w->up_layer_stride, nullptr, up, rows, hidden,
+                  inter, stream);
+  if (r != PA_OK) return r;
+  PA_CUDA(pa::launch_silu_mul(gate, up, gate, (size_t)rows * inter, (cudaStream_t)stream));
+  return linear_rows(p, gate, (const __nv_bfloat16*)w->down + (size_t)layer * w->down_layer_stride,
+                     add_residual ? x : nullptr, out, rows, inter, hidden, stream);
+}
+
 int pa_pool_set_layer_overlap(pa_pool* p, int allow) {
   if (!p) return fail(PA_ERR_INVALID_ARG, "pa_pool_set_layer_overlap: NULL pool");
   p->no_layer_overlap = allow == 0;

@@ -189,6 +189,8 @@ struct QkvGemmParams {
   const __nv_bfloat16* residual = nullptr;  // [rows, q_cols], nullable
 };
 cudaError_t launch_qkv_gemm(const QkvGemmParams& p, cudaStream_t stream);
+// out = bf16(SiLU(gate) * up) over `elements` (a multiple of 8) bf16 values; out may alias gate or up
+cudaError_t launch_silu_mul(const void* gate, const void* up, void* out, size_t elements, cudaStream_t stream);
 // row-major [hidden, cols] -> per (64 k-rows, 64 columns) an 8 KiB block in the GEMM's shared-memory layout
 cudaError_t launch_pack_weights(const void* src, void* dst, int hidden, int cols, cudaStream_t stream);
 

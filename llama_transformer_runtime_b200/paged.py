@@ -395,6 +395,14 @@ def ffn(weights: "FfnWeights", layer: int, x, h_scratch, out, rows: int, add_res
     check(lib().pa_ffn(C.byref(weights), layer, _ptr(x), _ptr(h_scratch), _ptr(out), rows, int(add_residual), stream))
 
 
+def ffn_rows(pool: "KVPool", packed_weights: "FfnWeights", layer: int, x, scratch, out, rows: int,
+             add_residual: bool = True, stream: int = 0) -> None:
+    """The feed-forward block for a prompt chunk on the tensor cores; gate/up/down of the descriptor packed by
+    pack_projection_weights; scratch holds rows * (hidden + 2 * inter) bf16."""
+    check(lib().pa_ffn_rows(pool._h, C.byref(packed_weights), layer, _ptr(x), _ptr(scratch), _ptr(out), rows,
+                            int(add_residual), stream))
+
+
 def block_step(pool: "KVPool", attention: AttentionWeights, ffn_w: "FfnWeights", layer_begin: int, layer_end: int,
                x_in, x_out, cos, sin, xchg: "Exchange | None" = None, scale: float = 0.125, stream: int = 0) -> None:
     """One decode step through the transformer blocks of [layer_begin, layer_end): attention block and

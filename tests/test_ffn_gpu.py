@@ -95,6 +95,36 @@ def test_ffn_vs_oracle_and_reference(cuda, rows, residual, norm):
     assert np.array_equal(to_u16(x2), got)
 
 
+@pytest.mark.parametrize("rows,residual", [(5, True), (300, True), (130, False)])
+def test_ffn_rows_on_the_tensor_cores_vs_oracle(cuda, rows, residual):
+    """The prompt-chunk form: RMSNorm kernel, three tcgen05 GEMM launches on packed weights, one SiLU * up
+    kernel.  Against the oracle chain, and (for few rows) against the decode-shape kernels."""
+    rng = np.random.default_rng(930 + rows)
+    fn, wg, wu, wd = _ffn_model(rng, 1)
+    x = orc.randn_bf16(rng, (rows, 2048), 1.2)
+    tens = [to_dev(a) for a in (fn, wg, wu, wd)]
+    packed = [paged.pack_projection_weights(t) for t in tens[1:]]
+    WP = paged.ffn_weights(tens[0], packed[0], packed[1], packed[2], EPS)
+    pool = paged.KVPool(1, 8, 8, 1)
+    xd = to_dev(x)
+    scratch = torch.zeros(rows * (2048 + 2 * 8192), dtype=torch.bfloat16, device=DEV)
+    out = torch.full((rows, 2048), 5.0, dtype=torch.bfloat16, device=DEV)
+    paged.ffn_rows(pool, WP, 0, xd, scratch, out, rows, add_residual=residual)
+    torch.cuda.synchronize()
+    pool.check()
+    got = to_u16(out)
+    want = orc.ffn(x, fn[0], wg[0], wu[0], wd[0], EPS, residual)
+    assert row_rel(got, want) <= ROW_TOL
+    if rows <= 8:
+        W = paged.ffn_weights(*tens, EPS)
+        h = torch.zeros(rows, 8192, dtype=torch.bfloat16, device=DEV)
+        out2 = torch.zeros_like(out)
+        paged.ffn(W, 0, xd, h, out2, rows, add_residual=residual)
+        torch.cuda.synchronize()
+        assert row_rel(got, to_u16(out2)) <= ROW_TOL
+    pool.close()
+
+
 def test_ffn_argument_errors(cuda):
     rng = np.random.default_rng(5)
     fn, wg, wu, wd = _ffn_model(rng, 1)

@@ -89,3 +89,33 @@ def test_drop_in_attention_class_equals_reference_attention(cuda, tmp_path):
     err = np.abs(g - w).max(axis=1)
     scale = np.abs(w).max(axis=1)
     assert np.all(err <= 2.0 ** -5 * scale), (err / scale).max()
+
+
+@pytest.mark.skipif(not _have("ffn_forward_ref"), reason="the reference's callers were not built")
+def test_drop_in_feed_forward_class_equals_reference_feed_forward(cuda, tmp_path):
+    """include/ffn.hpp: the runtime::FeedForward-shaped class over this library (1 and 3 rows through the
+    weight-streaming kernels, 40 rows through the tensor-core GEMMs), driven by the same program as the
+    reference's own FeedForward with its own kernels (src/runtime/ffn.cu)."""
+    root = os.path.dirname(REF_DIR.rstrip("/"))
+    repo = os.path.dirname(root)
+    exe = tmp_path / "ffn_class_shim"
+    r = subprocess.run(["nvcc", "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-w",
+                        "-DPA_SHIM_CLASS", "-I", os.path.join(repo, "include"), "-o", str(exe),
+                        os.path.join(root, "ffn_driver.cu"),
+                        "-L", os.path.join(repo, "llama_transformer_runtime_b200"), "-lpaged_attention",
+                        "-Xlinker", "-rpath", "-Xlinker", os.path.join(repo, "llama_transformer_runtime_b200")],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-3000:]
+    outs = {}
+    for name, cmd in (("shim", str(exe)), ("ref", os.path.join(REF_DIR, "ffn_forward_ref"))):
+        path = tmp_path / (name + ".bin")
+        r = subprocess.run([cmd, str(path)], capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, name + ": " + r.stdout[-2000:] + r.stderr[-2000:]
+        outs[name] = np.fromfile(path, dtype=np.uint16)
+    got, want = outs["shim"], outs["ref"]
+    assert got.size == want.size == (1 + 3 + 40) * 2048
+    g = orc.bf16_to_f32(got).astype(np.float64).reshape(-1, 2048)
+    w = orc.bf16_to_f32(want).astype(np.float64).reshape(-1, 2048)
+    err = np.abs(g - w).max(axis=1)
+    scale = np.abs(w).max(axis=1)
+    assert np.all(scale > 0) and np.all(err <= 2.0 ** -6 * scale), (err / scale).max()
