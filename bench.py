@@ -1452,6 +1452,8 @@ def run_chain(env: Env, args, sub: bool = False, ffn: bool = False):
         num_blocks = need_blocks + need_blocks // 4 + 8
         pool = paged.KVPool(LAYERS, num_blocks, KV_HEADS, 1, need_blocks + 1, device=local_rank)
         pool.set_free_order(np.random.default_rng(1234 + rank).permutation(num_blocks))
+        if getattr(args, "decode_cluster", 0):
+            pool.set_decode_cluster(args.decode_cluster)
         seq = pool.create_seq()
         ones = torch.ones(local_len + 1, 32, dtype=torch.float32, device=dev)
         zeros = torch.zeros(local_len + 1, 32, dtype=torch.float32, device=dev)
@@ -1718,6 +1720,9 @@ def main():
     ap.add_argument("--chunk-blocks", type=int, default=0, help="decode: blocks per split-KV chunk (0 = planner)")
     ap.add_argument("--combiners", type=int, default=0,
                     help="decode: combining CTAs per (sequence, head) in the one-launch step (0 = planner)")
+    ap.add_argument("--decode-cluster", type=int, default=0,
+                    help="decode_chain / block_chain: cluster form of the one-layer decode kernel "
+                         "(0 = planner, -1 = never, 2/4/8/16 = that cluster size)")
     ap.add_argument("--decode-shape", default="", help="decode: WARPSxSTAGES, e.g. 8x4 (empty = planner)")
     ap.add_argument("--qkv-packed", action="store_true",
                     help="qkv_decode: the kernel that reads the packed weight tiles (shared with the prefill GEMM) "

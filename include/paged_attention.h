@@ -389,6 +389,11 @@ int pa_pool_check(pa_pool* pool, void* stream);
 
 /* Tuning knobs (0 keeps the built-in heuristic): blocks per split-KV chunk. */
 int pa_pool_set_decode_chunk_blocks(pa_pool* pool, int chunk_blocks);
+/* The kernel of one layer (pa_decode, pa_attention_step, a one-layer pa_decode_step): the chunks of a
+ * (sequence, head) as one thread-block cluster of 2, 4, 8 or 16 CTAs that combine through distributed
+ * shared memory.  0 (default): the planner uses it for short contexts whose clusters are all
+ * resident at once; -1: never.  No counterpart in the reference. */
+int pa_pool_set_decode_cluster(pa_pool* pool, int mode);
 /* pa_decode_step and pa_decode_step_sharded run the layers of a step as one
  * cooperative launch when the batch allows it (enable != 0, the default);
  * enable == 0 keeps one kernel per layer.  No counterpart in the reference. */

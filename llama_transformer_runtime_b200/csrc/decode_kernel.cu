@@ -680,6 +680,15 @@ __device__ __forceinline__ void stream_cta(const DecodeParams& b, const StreamAr
       }
       if (!STEP && n_chunks == 1) {
         write_row_outputs(b, z, h, r, d, O, M, L);
+      } else if (!STEP && b.cluster > 0) {
+        // the CTA's partial stays in its shared memory (the tile ring is idle: every copy has been
+        // consumed) for the first CTA of the cluster to read
+        float* cpart = reinterpret_cast<float*>(tiles);
+        cpart[idx] = O;
+        if (d == 0) {
+          cpart[kGroup * kHeadDim + r] = M;
+          cpart[kGroup * kHeadDim + kGroup + r] = L;
+        }
       } else {
         ws_acc[idx] = O;
         if (d == 0) {
@@ -704,6 +713,7 @@ __device__ __forceinline__ void stream_cta(const DecodeParams& b, const StreamAr
     exchange_wait_merge(b, z, h, &s_wait_ok, T);
     return;
   }
+  if (b.cluster > 0) return;  // combined by the cluster's first CTA (cluster_finish)
   // combine across chunks: the last CTA to arrive does it
   __threadfence();
   consumer_sync(T);
@@ -712,6 +722,53 @@ __device__ __forceinline__ void stream_cta(const DecodeParams& b, const StreamAr
   if (s_ticket != (unsigned)(n_chunks - 1)) return;
   __threadfence();
   combine_pair<WARPS, STAGES>(b, z, h, n_chunks, smem, &s_wait_ok);
+}
+
+// Cluster form of the one-layer kernel: the consumer threads of the cluster's first CTA read every
+// chunk's partial (O [4][64], m [4], l [4]) from its CTA's shared memory, merge, and finish the
+// (sequence, head) as the last-arriving CTA does in the workspace form.
+__device__ __forceinline__ float ld_cluster_f32(const float* local, uint32_t rank) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(local)), "r"(rank));
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(a) : "memory");
+  return v;
+}
+template <int WARPS, int STAGES>
+__device__ __forceinline__ void cluster_finish(const DecodeParams& p, const int h, const int z, unsigned char* smem) {
+  constexpr int T = WARPS * 32;
+  __shared__ int s_wait_ok;
+  const BatchEntry e = p.batch[z];
+  const int n_blocks = (e.kv_len + kBlockTok - 1) / kBlockTok;
+  const int n_chunks = max(1, (n_blocks + p.chunk_blocks - 1) / p.chunk_blocks);
+  if (n_chunks <= 1) return;  // a single chunk has written its rows itself
+  const float* cpart = reinterpret_cast<const float*>(smem);
+  for (int idx = threadIdx.x; idx < kGroup * kHeadDim; idx += T) {
+    const int r = idx >> 6, d = idx & 63;
+    float m[16], l[16], o[16];
+#pragma unroll
+    for (int c = 0; c < 16; c++) {
+      if (c >= n_chunks) break;
+      m[c] = ld_cluster_f32(cpart + kGroup * kHeadDim + r, (uint32_t)c);
+      l[c] = ld_cluster_f32(cpart + kGroup * kHeadDim + kGroup + r, (uint32_t)c);
+      o[c] = ld_cluster_f32(cpart + idx, (uint32_t)c);
+    }
+    float M = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < 16; c++)
+      if (c < n_chunks) M = fmaxf(M, m[c]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int c = 0; c < 16; c++) {
+      if (c >= n_chunks) break;
+      const float wgt = m[c] == -INFINITY ? 0.f : ex2(m[c] - M);
+      L += wgt * l[c];
+      O += wgt * o[c];
+    }
+    write_row_outputs(p, z, h, r, d, O, M, L);
+  }
+  publish_exchange(p, z, h, T);
+  exchange_wait_merge(p, z, h, &s_wait_ok, T);
 }
 
 template <int WARPS, int STAGES>
@@ -725,6 +782,15 @@ decode_kernel(const __grid_constant__ DecodeParams p) {
   if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const StreamArgs a{1, (int)gridDim.z, 0, 0, 0, 0ull};
   stream_cta<WARPS, STAGES, false>(p, a, blockIdx.x, blockIdx.y, blockIdx.z, smem);
+  if (p.cluster > 0) {
+    // Every thread of every CTA of the cluster comes through here, whatever it did above (CTAs
+    // beyond a sequence's chunks, the producer warp, a thread whose wait ran out), so the two
+    // meetings never wait for a thread that left.
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+    if (blockIdx.x == 0 && (int)threadIdx.x < WARPS * 32) cluster_finish<WARPS, STAGES>(p, blockIdx.y, blockIdx.z, smem);
+    // the peers' shared memory stays until the first CTA has read it
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+  }
 }
 
 template <int WARPS, int STAGES>
@@ -814,10 +880,13 @@ cudaError_t launch_decode_cfg(const DecodeParams& p, int n_seqs, cudaStream_t st
     cudaError_t e = cudaFuncSetAttribute(decode_kernel<WARPS, STAGES>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, S::step_bytes(1));
     if (e != cudaSuccess) return e;
+    // clusters of up to 16 CTAs (8 is the portable limit)
+    e = cudaFuncSetAttribute(decode_kernel<WARPS, STAGES>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
   dim3 grid(p.max_chunks, p.kv_heads, n_seqs);
-  if (!p.pdl) {
+  if (!p.pdl && p.cluster <= 0) {
     decode_kernel<WARPS, STAGES><<<grid, S::kStepThreads, S::step_bytes(1), stream>>>(p);
     return cudaGetLastError();
   }
@@ -826,17 +895,67 @@ cudaError_t launch_decode_cfg(const DecodeParams& p, int n_seqs, cudaStream_t st
   cfg.blockDim = dim3(S::kStepThreads);
   cfg.dynamicSmemBytes = S::step_bytes(1);
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
+  if (p.pdl) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    n_attr++;
+  }
+  if (p.cluster > 0) {
+    if (p.cluster != p.max_chunks) return cudaErrorInvalidValue;  // a cluster is all chunks of a (sequence, head)
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = (unsigned)p.cluster;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    n_attr++;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = n_attr;
   return cudaLaunchKernelEx(&cfg, decode_kernel<WARPS, STAGES>, p);
 }
 
 }  // namespace
 
 size_t decode_ws_acc_floats_per_item() { return kGroup * kHeadDim; }
+
+namespace {
+template <int WARPS, int STAGES>
+int cluster_limit_cfg() {
+  using S = DecodeSmem<WARPS, STAGES>;
+  cudaFuncSetAttribute(decode_kernel<WARPS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::step_bytes(1));
+  cudaFuncSetAttribute(decode_kernel<WARPS, STAGES>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  for (int size = 16; size >= 2; size /= 2) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(size, 1, 1);
+    cfg.blockDim = dim3(S::kStepThreads);
+    cfg.dynamicSmemBytes = S::step_bytes(1);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)size;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, decode_kernel<WARPS, STAGES>, &cfg) == cudaSuccess && n >= 1) return size;
+    cudaGetLastError();  // an unsupported size is an answer, not an error to keep
+  }
+  return 0;
+}
+}  // namespace
+
+// Largest cluster size (16, 8, 4, 2; 0 = none) the one-layer kernel of this shape can be launched
+// with on the current device, asked of the occupancy calculator once per device and shape.
+int decode_cluster_limit(int warps, int stages) {
+  static int cache[64][2] = {};  // [device][shape]: 0 = not asked yet, else limit + 1
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int shape = (warps == 8 && stages == 4) ? 0 : ((warps == 4 && stages == 4) ? 1 : -1);
+  if (shape < 0 || dev < 0 || dev >= 64) return 0;  // the planner's two shapes only
+  if (cache[dev][shape] == 0) cache[dev][shape] = 1 + (shape == 0 ? cluster_limit_cfg<8, 4>() : cluster_limit_cfg<4, 4>());
+  return cache[dev][shape] - 1;
+}
 
 bool decode_shape_supported(int warps, int stages) {
   return (warps == 4 && (stages == 3 || stages == 4 || stages == 6)) ||

@@ -36,6 +36,7 @@ constexpr int kColsPerCta = 32;
 constexpr int kThreads = 256;
 constexpr int kSlice = 2048;   // rows of a weight matrix one CTA walks = elements of x it stages
 constexpr int kDownSplit = 4;  // CTAs of a cluster of the down projection
+constexpr int kRowGroup = 4;   // rows one CTA carries; more rows form a second group of CTAs
 
 struct FfnParams {
   const __nv_bfloat16* x;       // gate/up: [rows, hidden]; down: h [rows, inter]
@@ -143,10 +144,16 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
 }
 
 // h[r][col] = bf16(silu(bf16(x_r . Wg[:, col])) * bf16(x_r . Wu[:, col])), x normalised first.
-template <int ROWS>
-__global__ void __launch_bounds__(kThreads) ffn_gate_up_kernel(FfnParams p) {
+// Rows beyond the first kRowGroup are a second group of CTAs (blockIdx.y = 1): with more than 4 rows per
+// thread the accumulators alone push the kernel to one CTA per SM and 256 CTAs into two waves; the
+// second group's weight reads hit L2 behind the first's.
+template <int ROWS, int WIN>
+__global__ void __launch_bounds__(kThreads, 2) ffn_gate_up_kernel(FfnParams p) {
   __shared__ __align__(16) __nv_bfloat16 sx[ROWS][kSlice];
   __shared__ float red[8][ROWS][2][kColsPerCta];
+  p.x += (size_t)blockIdx.y * kRowGroup * p.k;
+  p.out += (size_t)blockIdx.y * kRowGroup * p.n;
+  p.rows = min(p.rows - (int)blockIdx.y * kRowGroup, kRowGroup);
   const int col0 = blockIdx.x * kColsPerCta;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kr = lane >> 2, c = lane & 3;
@@ -158,7 +165,7 @@ __global__ void __launch_bounds__(kThreads) ffn_gate_up_kernel(FfnParams p) {
   const uint4* up = reinterpret_cast<const uint4*>(p.w1 + first) + c;
   const size_t step = (size_t)64 * n / 8;  // 64 rows further, in 16-byte units
   const int n_steps = p.k / 64;
-  constexpr int kWin = 8;
+  constexpr int kWin = WIN;
   uint4 gv[kWin], uv[kWin];
 #pragma unroll
   for (int u = 0; u < kWin; u++)
@@ -166,7 +173,10 @@ __global__ void __launch_bounds__(kThreads) ffn_gate_up_kernel(FfnParams p) {
       gv[u] = __ldg(gp + (size_t)u * step);
       uv[u] = __ldg(up + (size_t)u * step);
     }
-  // x comes from the kernel in front, the weights do not
+  // x comes from the kernel in front, the weights do not.  (Asking the rest of the weight rows into
+  // L2 here, as the small projection kernels do, made this block slower — 26.7 against 24.8 us per
+  // layer: its 100 MB are bound by DRAM bandwidth, which the prefetches only take from the kernel
+  // in front.)
   if (p.pdl) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -249,10 +259,14 @@ __global__ void __launch_bounds__(kThreads) ffn_gate_up_kernel(FfnParams p) {
 
 // out[r][col] = bf16(residual + bf16(h_r . Wd[:, col])), K split over the four CTAs of a cluster.
 template <int ROWS>
-__global__ void __cluster_dims__(kDownSplit, 1, 1) __launch_bounds__(kThreads) ffn_down_kernel(FfnParams p) {
+__global__ void __cluster_dims__(kDownSplit, 1, 1) __launch_bounds__(kThreads, 2) ffn_down_kernel(FfnParams p) {
   __shared__ __align__(16) __nv_bfloat16 sx[ROWS][kSlice];
   __shared__ float red[8][ROWS][kColsPerCta];
   __shared__ float part[ROWS][kColsPerCta];
+  p.x += (size_t)blockIdx.y * kRowGroup * p.k;
+  p.out += (size_t)blockIdx.y * kRowGroup * p.n;
+  if (p.residual) p.residual += (size_t)blockIdx.y * kRowGroup * p.n;
+  p.rows = min(p.rows - (int)blockIdx.y * kRowGroup, kRowGroup);
   const uint32_t split = cluster_ctarank();
   const int col0 = (int)(blockIdx.x / kDownSplit) * kColsPerCta;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -359,13 +373,13 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const uint4* gate, const 
 }
 
 template <typename K>
-cudaError_t launch(K kern, int ctas, const FfnParams& p, cudaStream_t st) {
+cudaError_t launch(K kern, int ctas, int groups, const FfnParams& p, cudaStream_t st) {
   if (!p.pdl) {
-    kern<<<ctas, kThreads, 0, st>>>(p);
+    kern<<<dim3(ctas, groups), kThreads, 0, st>>>(p);
     return cudaGetLastError();
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(ctas);
+  cfg.gridDim = dim3(ctas, groups);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = st;
@@ -417,18 +431,16 @@ int ffn_impl(const void* x, const void* norm_w, float eps, const void* wg, const
   b.pdl = 1;
   const int ctas_a = inter / kColsPerCta, ctas_b = kDownSplit * (hidden / kColsPerCta);
   cudaError_t e;
+  const int groups = (rows + kRowGroup - 1) / kRowGroup;
   if (rows == 1) {
-    e = launch(ffn_gate_up_kernel<1>, ctas_a, a, st);
-    if (e == cudaSuccess) e = launch(ffn_down_kernel<1>, ctas_b, b, st);
+    e = launch(ffn_gate_up_kernel<1, 8>, ctas_a, 1, a, st);
+    if (e == cudaSuccess) e = launch(ffn_down_kernel<1>, ctas_b, 1, b, st);
   } else if (rows == 2) {
-    e = launch(ffn_gate_up_kernel<2>, ctas_a, a, st);
-    if (e == cudaSuccess) e = launch(ffn_down_kernel<2>, ctas_b, b, st);
-  } else if (rows <= 4) {
-    e = launch(ffn_gate_up_kernel<4>, ctas_a, a, st);
-    if (e == cudaSuccess) e = launch(ffn_down_kernel<4>, ctas_b, b, st);
+    e = launch(ffn_gate_up_kernel<2, 8>, ctas_a, 1, a, st);
+    if (e == cudaSuccess) e = launch(ffn_down_kernel<2>, ctas_b, 1, b, st);
   } else {
-    e = launch(ffn_gate_up_kernel<8>, ctas_a, a, st);
-    if (e == cudaSuccess) e = launch(ffn_down_kernel<8>, ctas_b, b, st);
+    e = launch(ffn_gate_up_kernel<4, 4>, ctas_a, groups, a, st);
+    if (e == cudaSuccess) e = launch(ffn_down_kernel<4>, ctas_b, groups, b, st);
   }
   if (e != cudaSuccess) return ffail(PA_ERR_CUDA, cudaGetErrorString(e));
   return PA_OK;

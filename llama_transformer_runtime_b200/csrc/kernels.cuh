@@ -78,6 +78,10 @@ struct DecodeParams {
   // inputs are ready, it waits before it writes.  2: behind the kernel that produces q, k_new and
   // v_new — it waits before it reads them, after its first cache copies are under way.
   int pdl = 0;
+  // > 0 (the kernel of one layer only): the max_chunks CTAs of a (sequence, head) are one thread-block
+  // cluster of this size; they combine through distributed shared memory instead of the workspace,
+  // the arrival counter and the last-arriver's loads
+  int cluster = 0;
   int fuse = 0;
   const __nv_bfloat16* k_new = nullptr;  // [rows][kv_heads][64], row e.kv_row_off
   const __nv_bfloat16* v_new = nullptr;
@@ -140,6 +144,7 @@ cudaError_t launch_decode(const DecodeParams& p, int n_seqs, int warps, int stag
                           cudaStream_t stream);
 bool decode_shape_supported(int warps, int stages);
 size_t decode_ws_acc_floats_per_item();
+int decode_cluster_limit(int warps, int stages);
 
 // Prefill attention: for every batch sequence z, its n_q query rows (positions
 // q_pos0 ...) against keys [0, kv_len) of its paged cache.  Row `row` of head h

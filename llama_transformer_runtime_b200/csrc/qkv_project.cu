@@ -77,8 +77,13 @@ __global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
     if (u < n_steps) wv[u] = __ldg(wp + (size_t)u * step);
 
   // The weight loads above are all this kernel may do before the kernel in front has finished:
-  // x is its output.  The kernel behind may start its own weight loads from here on.
+  // x is its output.  The kernel behind may start its own weight loads from here on.  The rest of
+  // this thread's weight rows are asked into L2 meanwhile (one lane per 64-byte row piece), so that
+  // after the wait the rolling window is fed from L2 instead of from DRAM.
   if (p.pdl) {
+    if (c == 0)
+      for (int u = 16; u < n_steps; u++)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(wp + (size_t)u * step));
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
   }

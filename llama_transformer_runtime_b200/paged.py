@@ -163,6 +163,10 @@ class KVPool:
     def check(self, stream: int = 0) -> None:
         check(lib().pa_pool_check(self._h, stream))
 
+    def set_decode_cluster(self, mode: int) -> None:
+        """One-layer decode kernel: -1 never clusters, 0 planner, 2/4/8/16 that cluster size."""
+        check(lib().pa_pool_set_decode_cluster(self._h, mode))
+
     def set_decode_chunk_blocks(self, n: int) -> None:
         check(lib().pa_pool_set_decode_chunk_blocks(self._h, n))
 

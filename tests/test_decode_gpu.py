@@ -252,6 +252,7 @@ def test_fused_step_equals_append_then_decode(cuda, chunk_blocks):
         pool = paged.KVPool(layers, 64, 8, n, 20)
         pool.set_free_order(prng.permutation(64))
         pool.set_decode_chunk_blocks(chunk_blocks)
+        pool.set_decode_cluster(-1)  # the step kernel has no cluster form: same chunking on both sides
         seqs = []
         for L in lens:
             s = pool.create_seq()
@@ -310,6 +311,7 @@ def test_step_kernel_equals_one_kernel_per_layer(cuda, chunk_blocks):
         pool = paged.KVPool(layers, 64, 8, n, 20)
         pool.set_free_order(prng.permutation(64))
         pool.set_decode_chunk_blocks(chunk_blocks)
+        pool.set_decode_cluster(-1)  # the step kernel has no cluster form: same chunking in all three modes
         pool.set_step_kernel(mode == "step")
         seqs = []
         for L in lens:
@@ -350,3 +352,77 @@ def test_step_kernel_equals_one_kernel_per_layer(cuda, chunk_blocks):
             assert np.array_equal(o_a[step][1], other[step][1])
     for l in range(layers):
         assert np.array_equal(c_a[l], c_b[l]) and np.array_equal(c_a[l], c_c[l])
+
+
+@pytest.mark.parametrize("mode,lens", [(0, [4097]), (16, [4097]), (8, [513, 2000]), (4, [70, 1000, 64]), (2, [33, 300, 17, 129]),
+                                       (0, [300, 1200]), (16, [16])])
+def test_cluster_form_of_the_one_layer_kernel(cuda, mode, lens):
+    """The chunks of a (sequence, head) as one thread-block cluster that combines through distributed
+    shared memory (mode 0: the planner's choice; 2..16: that cluster size, with CTAs beyond a short
+    sequence's own chunk count idling).  Against the oracle, and against the workspace form of the
+    same pool within one bf16 rounding of the row scale (the chunking differs, so not bit for bit)."""
+    rng = np.random.default_rng(400 + mode + len(lens))
+    n = len(lens)
+    nb = sum((L + 15) // 16 for L in lens) + 5
+    pool = paged.KVPool(1, nb, 8, n, max((L + 15) // 16 for L in lens) + 1)
+    pool.set_free_order(rng.permutation(nb))
+    ks, vs, seqs = [], [], []
+    for L in lens:
+        k = orc.randn_bf16(rng, (8, L, 64), 0.5)
+        v = orc.randn_bf16(rng, (8, L, 64), 0.5)
+        s = pool.create_seq()
+        fill_cache(pool, 0, s, k, v)
+        ks.append(k), vs.append(v), seqs.append(s)
+    q = orc.randn_bf16(rng, (n, 32, 64))
+    pool.set_decode_cluster(mode)
+    got, lse, o32 = gpu_decode(pool, seqs, q, want_f32=True)
+    got2, _, _ = gpu_decode(pool, seqs, q, want_f32=True)  # a second launch: nothing left behind by the first
+    assert np.array_equal(got, got2)
+    pool.set_decode_cluster(-1)
+    ws, ws_lse, _ = gpu_decode(pool, seqs, q, want_f32=True)
+    for i, L in enumerate(lens):
+        want, want_lse = oracle_decode(q[i], ks[i], vs[i], L)
+        check_close(got[i], want, f"len {L}")
+        check_close(o32[i].reshape(-1), want, f"len {L} f32")
+        assert np.max(np.abs(lse[i] - want_lse)) < 1e-2, L
+        check_close(got[i], ws[i], f"len {L} vs the workspace form")
+    pool.close()
+
+
+def test_cluster_form_with_the_fused_append(cuda):
+    """pa_decode_step of one layer (RoPE + append fused in) in the cluster form, against append + decode."""
+    rng = np.random.default_rng(431)
+    lens = [1000, 257]
+    n = len(lens)
+    cos, sin = orc.build_rope_tables(1100)
+    cos_d, sin_d = f32_dev(cos), f32_dev(sin)
+    q = to_dev(orc.randn_bf16(rng, (1, n, 32, 64)))
+    k = to_dev(orc.randn_bf16(rng, (1, n, 8, 64)))
+    v = to_dev(orc.randn_bf16(rng, (1, n, 8, 64)))
+    outs = []
+    for fused in (True, False):
+        prng = np.random.default_rng(432)
+        pool = paged.KVPool(1, 100, 8, n, 70)
+        pool.set_free_order(prng.permutation(100))
+        pool.set_decode_cluster(8)
+        seqs = []
+        for L in lens:
+            s = pool.create_seq()
+            fill_cache(pool, 0, s, orc.randn_bf16(prng, (8, L, 64), 0.5), orc.randn_bf16(prng, (8, L, 64), 0.5))
+            seqs.append(s)
+        for s, L in zip(seqs, lens):
+            pool.reserve(s, L + 1)
+        pool.batch_set(seqs)
+        out = torch.zeros(1, n, 2048, dtype=torch.bfloat16, device=DEV)
+        q_rot = torch.zeros_like(q)
+        if fused:
+            pool.decode_step(0, 1, q, k, v, n * 2048, n * 512, cos_d, sin_d, q_rot, out, 2048, n * 2048)
+        else:
+            pool.append(0, q[0], k[0], v[0], cos_d, sin_d, q_rot[0])
+            pool.decode(0, q_rot[0], out[0], 2048)
+        torch.cuda.synchronize()
+        pool.check()
+        outs.append((to_u16(out), to_u16(q_rot)))
+        pool.close()
+    assert np.array_equal(outs[0][1], outs[1][1])
+    assert np.array_equal(outs[0][0], outs[1][0])  # same cluster size, same chunking: bit for bit
