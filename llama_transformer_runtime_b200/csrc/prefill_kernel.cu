@@ -403,7 +403,7 @@ prefill_kernel(PrefillParams p) {
     // register layout (the mma accumulator layout): thread t holds rows
     // rA = first + t/4 and rB = rA + 8, and of every group of 8 columns the two
     // at 2*(t%4).  A row is spread over the 4 threads of a quad, so row maxima
-    // and sums are quad shuffles, and P goes to shared memory with stmatrix.
+    // and sums are quad shuffles, and P goes back to tensor memory (tcgen05.st) in the same layout.
     const int first_row = (warp & 3) * 32 + (warp >> 2) * 16;
     const uint32_t lane_base = (uint32_t)first_row << 16;
     const int rA = first_row + (lane >> 2), rB = rA + 8;
