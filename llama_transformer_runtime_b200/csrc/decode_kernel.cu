@@ -52,6 +52,11 @@ struct DecodeSmem {
   static constexpr int kStepTbl = kStepEmpty + ((kBars + 8 + 127) & ~127);
   static constexpr int kStepQ = kStepTbl + kStepTblCap * 4;
   static constexpr int step_bytes(int layers) { return 128 + kStepQ + layers * kGroup * kHeadDim * 2; }
+  // the kernel of one layer in its cluster form: behind the one layer's query rows, the partials
+  // (O [4][64], m [4], l [4]) of up to 16 chunks, pushed into the cluster's first CTA by its peers
+  static constexpr int kClusterPartFloats = kGroup * kHeadDim + 2 * kGroup;
+  static constexpr int kClusterParts = ((kStepQ + kGroup * kHeadDim * 2 + 15) & ~15) + 16;  // 16 bytes in front: the chunk count
+  static constexpr int one_layer_bytes() { return 128 + kClusterParts + 16 * kClusterPartFloats * 4; }
   static constexpr int kStepThreads = (WARPS + 2) * 32;  // consumers + producer warp + publisher warp
 };
 
@@ -59,6 +64,13 @@ struct DecodeSmem {
 // publisher warps of a streaming CTA never take part, so __syncthreads is not used past set-up.
 __device__ __forceinline__ void consumer_sync(int threads) {
   asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
+}
+
+// Store into the shared memory of CTA `rank` of the cluster, at the address `local` has in this CTA.
+__device__ __forceinline__ void st_cluster_f32(const float* local, uint32_t rank, float v) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(local)), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory");
 }
 
 // One 8-byte word {value, step number}: value in the low half, step number in the high half,
@@ -386,6 +398,8 @@ __device__ __forceinline__ void stream_cta(const DecodeParams& b, const StreamAr
   const BatchEntry e = b.batch[z];
   const int n_blocks = (e.kv_len + kBlockTok - 1) / kBlockTok;
   const int n_chunks = max(1, (n_blocks + b.chunk_blocks - 1) / b.chunk_blocks);
+  if (!STEP && b.cluster > 0 && x == 0 && threadIdx.x == 0)
+    *reinterpret_cast<int*>(smem + S::kClusterParts - 16) = n_chunks;  // for cluster_finish, behind the cluster meeting
   if (x >= n_chunks) return;  // CTA-uniform
   const int blk_lo = x * b.chunk_blocks;
   const int cnt = max(0, min(n_blocks, blk_lo + b.chunk_blocks) - blk_lo);
@@ -411,7 +425,10 @@ __device__ __forceinline__ void stream_cta(const DecodeParams& b, const StreamAr
     // ================================ producer warp ==============================================
     const int held = min(cnt, S::kStepTblCap);
     for (int j = lane; j < held; j += 32) tbl_s[j] = table[j];
-    if (appends) {
+    if (appends && STEP) {
+      // (The kernel of one layer appends from its consumer side, see the tile loop: the owner of the
+      // last tile patches the new rows into the tile it has just received, so this CTA streams at
+      // once like every other and pays no store -> fence -> copy round trip behind the wait.)
       // Appended rows of ALL layers: same arithmetic and placement as append_kernel; the
       // generic-proxy stores are ordered before this warp's own bulk (async-proxy) reads of that
       // block by the proxy fence below.  pdl == 2: k_new and v_new are the output of the kernel
@@ -517,8 +534,31 @@ __device__ __forceinline__ void stream_cta(const DecodeParams& b, const StreamAr
   const uint32_t bar0 = smem_u32(bars) + warp * STAGES * 8;
   const uint32_t empty0 = smem_u32(empty_bars) + warp * STAGES * 8;
 
-  // pdl == 2: the query rows are the output of the kernel in front
+  // The kernel of one layer appends here: lanes 0..7 of the warp that owns the sequence's last tile
+  // hold the new token's K (lanes 0..3, chunk pairs c and c + 4) and V (lanes 4..7) rows.  What does
+  // not depend on the kernel in front (block id, RoPE factors) is fetched before the wait.
+  const bool patcher = !STEP && appends && warp == (cnt - 1) % WARPS && lane < 8;
+  int new_blk = 0;
+  float4 nc8[2] = {}, ns8[2] = {};
+  if (patcher) {
+    new_blk = table[cnt - 1];
+    if ((lane >> 2) == 0) {
+      const int pos = e.kv_pos_off + e.kv_len - 1;
+      const float4* cs = reinterpret_cast<const float4*>(b.cos_table + (size_t)pos * 32 + (lane & 3) * 8);
+      const float4* sn = reinterpret_cast<const float4*>(b.sin_table + (size_t)pos * 32 + (lane & 3) * 8);
+      nc8[0] = cs[0], nc8[1] = cs[1], ns8[0] = sn[0], ns8[1] = sn[1];
+    }
+  }
+  // pdl == 2: the query rows (and the new K/V rows) are the output of the kernel in front
   if (b.pdl == 2) asm volatile("griddepcontrol.wait;" ::: "memory");
+  uint4 new_lo = make_uint4(0, 0, 0, 0), new_hi = new_lo;
+  if (patcher) {
+    const int c = lane & 3, is_v = lane >> 2;
+    const uint4* src = reinterpret_cast<const uint4*>((is_v ? b.v_new : b.k_new) +
+                                                      ((size_t)e.kv_row_off * b.kv_heads + h) * kHeadDim);
+    new_lo = src[c];
+    new_hi = src[c + 4];
+  }
   // ---- every layer's query rows into shared memory: rotated here (fp32, the rounding of
   // append_kernel) when the append is fused in, copied as they are otherwise
   {
@@ -587,6 +627,36 @@ __device__ __forceinline__ void stream_cta(const DecodeParams& b, const StreamAr
       }
       if (failed) continue;  // keeps joining the layer barriers; its producer lane runs into its own limit
       const uint32_t tile = tile0 + st * kPairBytes;
+      if (!STEP && appends && i == my_n - 1 && warp == (cnt - 1) % WARPS) {
+        // the sequence's last block has arrived with its old contents: put the new token's rows into
+        // the shared-memory tile and into the cache (same arithmetic and placement as append_kernel)
+        if (patcher) {
+          const int c = lane & 3, is_v = lane >> 2;
+          const int slot = (e.kv_len - 1) % kBlockTok;
+          if (new_blk < 0 || new_blk >= b.num_blocks) {
+            atomicExch(b.status, kStatusBadBlock);
+          } else {
+            uint4 lo = new_lo, hi = new_hi;
+            if (!is_v) {
+              uint4 ylo, yhi;
+              rope_chunks<1>(lo, hi, reinterpret_cast<const float*>(nc8), reinterpret_cast<const float*>(ns8), ylo, yhi);
+              lo = ylo;
+              hi = yhi;
+            }
+            const uint32_t base = tile + (is_v ? kTileBytes : 0);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + tile_chunk_off(slot, c)), "r"(lo.x),
+                         "r"(lo.y), "r"(lo.z), "r"(lo.w)
+                         : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + tile_chunk_off(slot, c + 4)), "r"(hi.x),
+                         "r"(hi.y), "r"(hi.z), "r"(hi.w)
+                         : "memory");
+            char* gt = b.storage_w + tile_off(new_blk, b.kv_heads, h, is_v);
+            *reinterpret_cast<uint4*>(gt + tile_chunk_off(slot, c)) = lo;
+            *reinterpret_cast<uint4*>(gt + tile_chunk_off(slot, c + 4)) = hi;
+          }
+        }
+        __syncwarp();
+      }
 
       float s[2][4];
 #pragma unroll
@@ -681,13 +751,13 @@ __device__ __forceinline__ void stream_cta(const DecodeParams& b, const StreamAr
       if (!STEP && n_chunks == 1) {
         write_row_outputs(b, z, h, r, d, O, M, L);
       } else if (!STEP && b.cluster > 0) {
-        // the CTA's partial stays in its shared memory (the tile ring is idle: every copy has been
-        // consumed) for the first CTA of the cluster to read
-        float* cpart = reinterpret_cast<float*>(tiles);
-        cpart[idx] = O;
+        // the CTA's partial goes into slot x of the first CTA's shared memory (remote stores: the
+        // cluster meeting behind them makes them visible), so that CTA merges from local memory
+        const float* slot = reinterpret_cast<const float*>(smem + S::kClusterParts) + x * S::kClusterPartFloats;
+        st_cluster_f32(slot + idx, 0u, O);
         if (d == 0) {
-          cpart[kGroup * kHeadDim + r] = M;
-          cpart[kGroup * kHeadDim + kGroup + r] = L;
+          st_cluster_f32(slot + kGroup * kHeadDim + r, 0u, M);
+          st_cluster_f32(slot + kGroup * kHeadDim + kGroup + r, 0u, L);
         }
       } else {
         ws_acc[idx] = O;
@@ -724,46 +794,30 @@ __device__ __forceinline__ void stream_cta(const DecodeParams& b, const StreamAr
   combine_pair<WARPS, STAGES>(b, z, h, n_chunks, smem, &s_wait_ok);
 }
 
-// Cluster form of the one-layer kernel: the consumer threads of the cluster's first CTA read every
-// chunk's partial (O [4][64], m [4], l [4]) from its CTA's shared memory, merge, and finish the
-// (sequence, head) as the last-arriving CTA does in the workspace form.
-__device__ __forceinline__ float ld_cluster_f32(const float* local, uint32_t rank) {
-  uint32_t a;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(local)), "r"(rank));
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(a) : "memory");
-  return v;
-}
+// Cluster form of the one-layer kernel: the consumer threads of the cluster's first CTA merge the
+// chunks' partials (O [4][64], m [4], l [4]), which the peers have pushed into its shared memory,
+// and finish the (sequence, head) as the last-arriving CTA does in the workspace form.
 template <int WARPS, int STAGES>
 __device__ __forceinline__ void cluster_finish(const DecodeParams& p, const int h, const int z, unsigned char* smem) {
+  using S = DecodeSmem<WARPS, STAGES>;
   constexpr int T = WARPS * 32;
   __shared__ int s_wait_ok;
-  const BatchEntry e = p.batch[z];
-  const int n_blocks = (e.kv_len + kBlockTok - 1) / kBlockTok;
-  const int n_chunks = max(1, (n_blocks + p.chunk_blocks - 1) / p.chunk_blocks);
+  // the chunk count of this (sequence, head): left in shared memory by the streaming part (a load of
+  // the batch entry here would put a round trip to L2 on the critical path)
+  const int n_chunks = *reinterpret_cast<const int*>(smem + S::kClusterParts - 16);
   if (n_chunks <= 1) return;  // a single chunk has written its rows itself
-  const float* cpart = reinterpret_cast<const float*>(smem);
+  const float* parts = reinterpret_cast<const float*>(smem + S::kClusterParts);
   for (int idx = threadIdx.x; idx < kGroup * kHeadDim; idx += T) {
     const int r = idx >> 6, d = idx & 63;
-    float m[16], l[16], o[16];
-#pragma unroll
-    for (int c = 0; c < 16; c++) {
-      if (c >= n_chunks) break;
-      m[c] = ld_cluster_f32(cpart + kGroup * kHeadDim + r, (uint32_t)c);
-      l[c] = ld_cluster_f32(cpart + kGroup * kHeadDim + kGroup + r, (uint32_t)c);
-      o[c] = ld_cluster_f32(cpart + idx, (uint32_t)c);
-    }
     float M = -INFINITY;
-#pragma unroll
-    for (int c = 0; c < 16; c++)
-      if (c < n_chunks) M = fmaxf(M, m[c]);
+    for (int c = 0; c < n_chunks; c++) M = fmaxf(M, parts[c * S::kClusterPartFloats + kGroup * kHeadDim + r]);
     float L = 0.f, O = 0.f;
-#pragma unroll
-    for (int c = 0; c < 16; c++) {
-      if (c >= n_chunks) break;
-      const float wgt = m[c] == -INFINITY ? 0.f : ex2(m[c] - M);
-      L += wgt * l[c];
-      O += wgt * o[c];
+    for (int c = 0; c < n_chunks; c++) {
+      const float* pc = parts + c * S::kClusterPartFloats;
+      const float mc = pc[kGroup * kHeadDim + r];
+      const float wgt = mc == -INFINITY ? 0.f : ex2(mc - M);
+      L += wgt * pc[kGroup * kHeadDim + kGroup + r];
+      O += wgt * pc[idx];
     }
     write_row_outputs(p, z, h, r, d, O, M, L);
   }
@@ -784,12 +838,12 @@ decode_kernel(const __grid_constant__ DecodeParams p) {
   stream_cta<WARPS, STAGES, false>(p, a, blockIdx.x, blockIdx.y, blockIdx.z, smem);
   if (p.cluster > 0) {
     // Every thread of every CTA of the cluster comes through here, whatever it did above (CTAs
-    // beyond a sequence's chunks, the producer warp, a thread whose wait ran out), so the two
-    // meetings never wait for a thread that left.
+    // beyond a sequence's chunks, the producer warp, a thread whose wait ran out), so the meeting
+    // never waits for a thread that left — and the first CTA, whose shared memory the peers store
+    // into, is still there when they do.
     asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+    // every partial is in the first CTA's shared memory; nobody touches a peer's memory from here on
     if (blockIdx.x == 0 && (int)threadIdx.x < WARPS * 32) cluster_finish<WARPS, STAGES>(p, blockIdx.y, blockIdx.z, smem);
-    // the peers' shared memory stays until the first CTA has read it
-    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
   }
 }
 
@@ -878,7 +932,7 @@ cudaError_t launch_decode_cfg(const DecodeParams& p, int n_seqs, cudaStream_t st
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(decode_kernel<WARPS, STAGES>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::step_bytes(1));
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::one_layer_bytes());
     if (e != cudaSuccess) return e;
     // clusters of up to 16 CTAs (8 is the portable limit)
     e = cudaFuncSetAttribute(decode_kernel<WARPS, STAGES>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
@@ -887,13 +941,13 @@ cudaError_t launch_decode_cfg(const DecodeParams& p, int n_seqs, cudaStream_t st
   }
   dim3 grid(p.max_chunks, p.kv_heads, n_seqs);
   if (!p.pdl && p.cluster <= 0) {
-    decode_kernel<WARPS, STAGES><<<grid, S::kStepThreads, S::step_bytes(1), stream>>>(p);
+    decode_kernel<WARPS, STAGES><<<grid, S::kStepThreads, S::one_layer_bytes(), stream>>>(p);
     return cudaGetLastError();
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(S::kStepThreads);
-  cfg.dynamicSmemBytes = S::step_bytes(1);
+  cfg.dynamicSmemBytes = S::one_layer_bytes();
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   int n_attr = 0;
@@ -923,13 +977,13 @@ namespace {
 template <int WARPS, int STAGES>
 int cluster_limit_cfg() {
   using S = DecodeSmem<WARPS, STAGES>;
-  cudaFuncSetAttribute(decode_kernel<WARPS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::step_bytes(1));
+  cudaFuncSetAttribute(decode_kernel<WARPS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::one_layer_bytes());
   cudaFuncSetAttribute(decode_kernel<WARPS, STAGES>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
   for (int size = 16; size >= 2; size /= 2) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(size, 1, 1);
     cfg.blockDim = dim3(S::kStepThreads);
-    cfg.dynamicSmemBytes = S::step_bytes(1);
+    cfg.dynamicSmemBytes = S::one_layer_bytes();
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = (unsigned)size;

@@ -55,8 +55,15 @@ struct QkvParams {
   int pdl = 0;
 };
 
-template <int ROWS>
+// RESIDENT (one layer behind another kernel, launched with programmatic stream serialization): the
+// CTA's whole weight slab (hidden rows x 64 bytes = 128 KiB) is copied into shared memory with
+// cp.async while the kernel in front is still running, so that nothing is left to stream once x
+// is there; the arithmetic and its order are the same as in the streaming form (the results are
+// bit-equal).  The streaming form stays for launches over many layers, where several CTAs per SM
+// keep the stream going.
+template <int ROWS, bool RESIDENT>
 __global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
+  extern __shared__ __align__(16) unsigned char slab[];  // RESIDENT: [hidden][64 bytes]
   __shared__ __align__(16) __nv_bfloat16 sx[ROWS][kMaxHidden];
   __shared__ float red[8][ROWS][kColsPerCta];
   const int t = blockIdx.x, layer = blockIdx.y;
@@ -71,17 +78,37 @@ __global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
   const uint4* wp = reinterpret_cast<const uint4*>(w + (size_t)(warp * 8 + kr) * n + col0) + c;
   const size_t step = (size_t)64 * n / 8;  // 64 rows further, in 16-byte units
   const int n_steps = p.hidden / 64;
-  uint4 wv[16];
+  uint4 wv[RESIDENT ? 1 : 16];
+  if (RESIDENT) {
+    // chunk i of the slab = 16 bytes at row i / 4, chunk i % 4
+    const __nv_bfloat16* wcol = w + col0;
+    const uint32_t slab_u32 = pa::smem_u32(slab);
+    for (int i = threadIdx.x; i < p.hidden * 4; i += kThreads)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(slab_u32 + i * 16),
+                   "l"(wcol + (size_t)(i >> 2) * n + (i & 3) * 8)
+                   : "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  } else {
 #pragma unroll
-  for (int u = 0; u < 16; u++)
-    if (u < n_steps) wv[u] = __ldg(wp + (size_t)u * step);
+    for (int u = 0; u < 16; u++)
+      if (u < n_steps) wv[u] = __ldg(wp + (size_t)u * step);
+  }
 
   // The weight loads above are all this kernel may do before the kernel in front has finished:
   // x is its output.  The kernel behind may start its own weight loads from here on.  The rest of
   // this thread's weight rows are asked into L2 meanwhile (one lane per 64-byte row piece), so that
   // after the wait the rolling window is fed from L2 instead of from DRAM.
+  // The norm weights do not depend on the kernel in front either: this thread's chunks of them are
+  // loaded here (one chunk per thread at hidden = 2048), not after the wait behind x.
+  uint4 nw_pre[kMaxHidden / 8 / kThreads];
+  if (p.norm_w) {
+    const uint4* nwp = reinterpret_cast<const uint4*>(p.norm_w + (size_t)layer * p.norm_layer_stride);
+#pragma unroll
+    for (int i = 0; i < kMaxHidden / 8 / kThreads; i++)
+      if ((int)threadIdx.x + i * kThreads < p.hidden / 8) nw_pre[i] = __ldg(nwp + threadIdx.x + i * kThreads);
+  }
   if (p.pdl) {
-    if (c == 0)
+    if (!RESIDENT && (c & 1) == 0)  // both 32-byte sectors of the row's 64-byte piece
       for (int u = 16; u < n_steps; u++)
         asm volatile("prefetch.global.L2 [%0];" ::"l"(wp + (size_t)u * step));
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -102,7 +129,6 @@ __global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
     // reference's kernel (src/kernels/rmsnorm/rmsnorm.cu:51-110, launched with 256 threads): a
     // thread sums the squares of its 8-element chunks in order, lanes combine by shuffle-down
     // (16, 8, 4, 2, 1), warp sums combine the same way in warp 0; y = bf16((x * r) * w).
-    const uint4* nw = reinterpret_cast<const uint4*>(p.norm_w + (size_t)layer * p.norm_layer_stride);
 #pragma unroll
     for (int r = 0; r < ROWS; r++) {
       if (r >= p.rows) break;  // uniform
@@ -129,9 +155,9 @@ __global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
       }
       __syncthreads();
       const float rms_recip = rsqrtf(red[0][0][8] / static_cast<float>(p.hidden) + p.eps);
-      for (int i = threadIdx.x; i < p.hidden / 8; i += kThreads) {
+      for (int i = threadIdx.x, ii = 0; i < p.hidden / 8; i += kThreads, ii++) {
         const uint4 xd = reinterpret_cast<const uint4*>(&sx[r][0])[i];
-        const uint4 wd = nw[i];
+        const uint4 wd = nw_pre[ii];
         const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&xd);
         const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wd);
         uint4 yd;
@@ -155,13 +181,18 @@ __global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
 #pragma unroll
     for (int i = 0; i < 8; i++) acc[r][i] = 0.f;
 
+  if (RESIDENT) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();  // every thread's copies have landed
+  }
   // rolling window: as soon as a register's row is consumed, the row 16 steps on is requested
   for (int j0 = 0; j0 < n_steps; j0 += 16) {
 #pragma unroll
     for (int u = 0; u < 16; u++) {
       if (j0 + u >= n_steps) break;
       const int k = (j0 + u) * 64 + warp * 8 + kr;
-      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&wv[u]);
+      const uint4 wnow = RESIDENT ? *reinterpret_cast<const uint4*>(slab + (size_t)k * 64 + c * 16) : wv[RESIDENT ? 0 : u];
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&wnow);
       float wf[8];
 #pragma unroll
       for (int i = 0; i < 4; i++) {
@@ -169,7 +200,7 @@ __global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
         wf[2 * i] = f.x;
         wf[2 * i + 1] = f.y;
       }
-      if (j0 + u + 16 < n_steps) wv[u] = __ldg(wp + (size_t)(j0 + u + 16) * step);
+      if (!RESIDENT && j0 + u + 16 < n_steps) wv[RESIDENT ? 0 : u] = __ldg(wp + (size_t)(j0 + u + 16) * step);
 #pragma unroll
       for (int r = 0; r < ROWS; r++) {
         const float xv = __bfloat162float(sx[r][k]);
@@ -367,18 +398,36 @@ int qfail(int code, const char* msg) {
 // Launch of the row-major projection kernel for 1..8 rows, with programmatic stream serialization
 // when p.pdl is set (the kernel then waits for the kernel in front before it reads x).
 cudaError_t launch_rows(const QkvParams& p, dim3 grid, cudaStream_t st) {
-  void (*kern)(QkvParams) = p.rows == 1 ? qkv_project_kernel<1>
-                            : p.rows == 2 ? qkv_project_kernel<2>
-                            : p.rows <= 4 ? qkv_project_kernel<4>
-                                          : qkv_project_kernel<8>;
+  // one layer behind another kernel: the form that holds its weight slab in shared memory
+  const bool resident = p.pdl && grid.y == 1 && p.hidden <= kMaxHidden;
+  void (*kern)(QkvParams) = resident ? (p.rows == 1 ? qkv_project_kernel<1, true>
+                                        : p.rows == 2 ? qkv_project_kernel<2, true>
+                                        : p.rows <= 4 ? qkv_project_kernel<4, true>
+                                                      : qkv_project_kernel<8, true>)
+                                     : (p.rows == 1 ? qkv_project_kernel<1, false>
+                                        : p.rows == 2 ? qkv_project_kernel<2, false>
+                                        : p.rows <= 4 ? qkv_project_kernel<4, false>
+                                                      : qkv_project_kernel<8, false>);
   if (!p.pdl) {
     kern<<<grid, kThreads, 0, st>>>(p);
     return cudaGetLastError();
   }
+  const size_t slab_bytes = resident ? (size_t)p.hidden * 64 : 0;
+  if (resident) {
+    static bool configured[64][4] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int ri = p.rows == 1 ? 0 : (p.rows == 2 ? 1 : (p.rows <= 4 ? 2 : 3));
+    if (dev >= 0 && dev < 64 && !configured[dev][ri]) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxHidden * 64);
+      if (e != cudaSuccess) return e;
+      configured[dev][ri] = true;
+    }
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = 0;
+  cfg.dynamicSmemBytes = slab_bytes;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
