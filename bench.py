@@ -1668,6 +1668,110 @@ def run_chain(env: Env, args, sub: bool = False, ffn: bool = False):
         pool.close()
     return line
 
+def run_lm_head(env: Env, args, sub: bool = False):
+    """The end of a decode step: final RMSNorm + language-model head (hidden 2048 -> 128256 logits, a
+    525 MB weight stream) + greedy sampling, batch 1.  Ours: one weight-streaming launch and one argmax
+    launch.  Reference arm: its RMSNorm, launch_gemm_2048x128256 and launch_argmax with the
+    synchronisations, the per-token cudaMalloc/cudaFree and the blocking copy of its decode loop
+    (src/runtime/llama_runtime.cu:880-930)."""
+    torch = env.torch
+    if env.rank != 0:
+        return None  # independent replicas only
+    from oracle import oracle as orc
+    dev = env.dev
+    H, V = HIDDEN, 128256
+    steps = max(5, args.steps // 2) if sub else args.steps
+    warmup = 3 if sub else args.warmup
+    ref_arm = args.impl == "reference" and not sub
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(321)
+    w = (torch.randn(H, V, generator=gen, device=dev) * 0.03).to(torch.bfloat16)  # 525 MB: larger than L2
+    nw = (torch.randn(H, generator=gen, device=dev) * 0.7).to(torch.bfloat16)
+    x_host = torch.randn(1, H, generator=torch.Generator().manual_seed(8)).to(torch.bfloat16).pin_memory()
+    x = x_host.to(dev)
+    logits = torch.zeros(1, V, dtype=torch.bfloat16, device=dev)
+    token = torch.zeros(1, dtype=torch.int32, device=dev)
+    token_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+    nbytes = (H * V + H + V) * 2
+    ref = orc.ref() if orc.ref_available() else None
+    if ref_arm and ref is None:
+        return {"impl": "reference", "unavailable": "oracle/_ref/libref.so was not built"}
+    xn = torch.zeros(1, H, dtype=torch.bfloat16, device=dev)
+
+    def ref_step():
+        ref.ref_rmsnorm(x.data_ptr(), nw.data_ptr(), xn.data_ptr(), 1, 1e-5)
+        torch.cuda.synchronize()
+        ref.ref_gemm(xn.data_ptr(), w.data_ptr(), logits.data_ptr(), 1, V, H)
+        torch.cuda.synchronize()
+        t = torch.empty(1, dtype=torch.int32, device=dev)  # the loop's per-token cudaMalloc / cudaFree
+        ref.ref_argmax(logits.data_ptr(), t.data_ptr())
+        token_host.copy_(t)  # blocking copy
+        del t
+        torch.cuda.synchronize()
+
+    if not ref_arm:
+        from llama_transformer_runtime_b200 import paged
+
+        def ours_step():
+            paged.lm_head(x, nw, w, logits, 1)
+            paged.argmax(logits, token, 1)
+
+    step = ref_step if ref_arm else ours_step
+
+    def e2e_step():
+        x.copy_(x_host, non_blocking=True)
+        step()
+        if not ref_arm:
+            token_host.copy_(token, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    m0 = env.sampler.mark()
+    for _ in range(warmup):
+        step()
+    ms = local_timed(torch, step, steps)
+    ms_e2e = local_timed(torch, e2e_step, steps)
+    m1 = env.sampler.mark()
+    value = nbytes * steps / (ms * 1e-3) / 1e9
+    peak, pk = measured_peak()
+    line = {
+        "metric": "lm_head_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms / steps, 4), "us_per_token": round(ms / steps * 1e3, 2), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "lm_head_2048x128256_argmax_batch1", "hidden": H, "vocab": V, "batch": 1,
+                   "l2": "the weight (525 MB) is larger than L2"},
+        "e2e": {"value": round(nbytes * steps / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s", "h2d_bytes_per_step": H * 2,
+                "d2h_bytes_per_step": 4, "ms_per_step": round(ms_e2e / steps, 4)},
+        "gpu_launches": (3 if ref_arm else 2) * steps, "clocks": env.sampler.summary(m0, m1),
+    }
+    if ref_arm:
+        line["impl"] = "reference"
+        line["cpu_baseline"] = {"value": line["value"], "unit": "GB/s", "cores": 0, "kind": "reference",
+                                "sample": "whole workload on the GPU: the reference has no CPU implementation of this path"}
+        line["e2e"].update({"h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0, "value": line["value"]})
+        return line
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    want = orc.gemm_bf16(orc.rmsnorm(_u16(x_host), _u16(nw), 1e-5), _u16(w))
+    dt = time.perf_counter() - t0
+    got = _u16(logits)
+    err = row_rel_err(orc.bf16_to_f32(got), orc.bf16_to_f32(want), row=V)
+    tok = int(token.cpu().item())
+    line["checks"] = {"logits_max_err_over_row_max": err, "logits_ok": bool(err <= 2.0 ** -7),
+                      "token": tok, "token_is_the_reference_rule_on_these_logits": bool(tok == int(orc.argmax_reference_rule(got)[0]))}
+    line["cpu_baseline"] = {"value": round(nbytes / dt / 1e9, 3), "unit": "GB/s", "cores": orc.num_threads(), "kind": "port",
+                            "sample": f"one token: RMSNorm + 2048 x 128256 product with the CPU oracle, {dt:.2f} s"}
+    line["roofline"] = {"bound": "hbm", "kernel": "qkv_project_kernel (language-model head)", "achieved": round(value, 1),
+                        "peak": peak, "unit": "GB/s", "frac": round(value / peak, 4), "peak_source": f"of {pk}",
+                        "us_per_launch": round(ms / steps * 1e3, 2), "bytes_per_launch": nbytes, "traffic": None}
+    if sub and ref is not None:
+        ref_step()
+        rms = local_timed(torch, ref_step, 3) / 3
+        line["reference"] = {"value": round(nbytes / (rms * 1e-3) / 1e9, 2), "unit": "GB/s", "us_per_token": round(rms * 1e3, 2),
+                             "how": "the reference's RMSNorm, launch_gemm_2048x128256 and launch_argmax with the "
+                                    "synchronisations, allocation and blocking copy of its decode loop"}
+    return line
+
+
 # =============================================================================
 def decode4k_sub(env: Env, args):
     line = run_decode(env, args, "decode4k", sub=True)
@@ -1689,6 +1793,7 @@ SUB_BLOCKS = {
     "qkv_prefill": lambda env, a: run_qkv_prefill(env, a, sub=True),
     "decode_chain": lambda env, a: run_chain(env, a, sub=True),
     "block_chain": lambda env, a: run_chain(env, a, sub=True, ffn=True),
+    "lm_head": lambda env, a: run_lm_head(env, a, sub=True),
 }
 
 
@@ -1709,7 +1814,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode128k",
                     choices=sorted(WORKLOADS) + ["prefill2k", "append2k", "batch64", "qkv_decode", "out_project", "qkv_prefill",
-                                                  "decode_chain", "block_chain"])
+                                                  "decode_chain", "block_chain", "lm_head"])
     ap.add_argument("--chain-ctx", type=int, default=4096, help="decode_chain: context length")
     ap.add_argument("--no-sub", action="store_true", help="default workload: skip the sub-blocks")
     ap.add_argument("--sub", default="", help="default workload: comma-separated sub-blocks to run (default: all)")
@@ -1776,6 +1881,8 @@ def main():
         line = run_chain(env, args)
     elif args.workload == "block_chain":
         line = run_chain(env, args, ffn=True)
+    elif args.workload == "lm_head":
+        line = run_lm_head(env, args)
     if rank == 0 and line is not None:
         print(json.dumps(line), flush=True)
     env.sampler.stop()

@@ -379,6 +379,19 @@ int pa_block_step(pa_pool* pool, pa_exchange* exchange, int layer_begin, int lay
                   const pa_attention_weights* attention, const pa_ffn_weights* ffn, const void* x_in,
                   void* x_out, const float* cos_table, const float* sin_table, float scale, void* stream);
 
+/* ---- the end of a decode step: language-model head and greedy sampling ----------------------
+ * pa_lm_head replaces rmsnorm_launch<2048> + launch_gemm_2048x128256 of the reference's decode
+ * loop (src/runtime/llama_runtime.cu:880-905): logits [rows, vocab] bf16 = RMSNorm(x, final_norm)
+ * W_lm, W_lm [hidden, vocab] row-major as the reference holds it, final_norm nullable; 1 to 8
+ * rows, vocab a multiple of 32.  pa_argmax replaces launch_argmax
+ * (src/kernels/sampling/argmax_128256.cu) and the cudaMalloc / blocking copy / cudaFree around it
+ * (llama_runtime.cu:907-930): tokens[r] = index of the largest logit of row r; equal largest values
+ * are told apart as the structure of the reference's kernel does (its 256 threads, lanes and warps
+ * in bit-reversed order, then the smallest index).  Top-k sampling (topk_128256.cu) is not built. */
+int pa_lm_head(const void* x, const void* final_norm, float eps, const void* w_lm, void* logits, int rows,
+               int hidden, int vocab, void* stream);
+int pa_argmax(const void* logits, int32_t* tokens, int rows, int vocab, void* stream);
+
 /* Host: fp32 cos/sin tables [seq_len][32], Llama-3 frequency scaling. */
 int pa_build_rope_tables(float* cos_table, float* sin_table, int seq_len);
 

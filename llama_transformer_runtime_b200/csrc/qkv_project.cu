@@ -604,3 +604,40 @@ int pa::out_project_impl(const void* attn, const void* wo, const void* residual,
   }
   return PA_OK;
 }
+
+// The language-model head of a decode step: logits = RMSNorm(x, final_norm) W_lm, bf16, as the
+// reference computes them with rmsnorm_launch<2048> and launch_gemm_2048x128256
+// (src/runtime/llama_runtime.cu:880-905; the weight [hidden, vocab] row-major).  The same
+// weight-streaming kernel as the projections: 525 MB per token for the 128256-entry vocabulary,
+// 4008 column tiles of 32.
+extern "C" int pa_lm_head(const void* x, const void* final_norm, float eps, const void* w_lm, void* logits, int rows,
+                          int hidden, int vocab, void* stream) {
+  if (!x || !w_lm || !logits) return qfail(PA_ERR_INVALID_ARG, "pa_lm_head: NULL argument");
+  if (rows < 1) return qfail(PA_ERR_INVALID_ARG, "pa_lm_head: rows must be >= 1");
+  if (rows > 8) return qfail(PA_ERR_UNSUPPORTED, "pa_lm_head: at most 8 rows per call (decode shapes)");
+  if (hidden < 64 || hidden > kMaxHidden || hidden % 64 != 0)
+    return qfail(PA_ERR_UNSUPPORTED, "pa_lm_head: hidden must be a multiple of 64, at most 2048");
+  if (vocab < kColsPerCta || vocab % kColsPerCta != 0) return qfail(PA_ERR_UNSUPPORTED, "pa_lm_head: vocab must be a multiple of 32");
+  QkvParams p;
+  p.x = (const __nv_bfloat16*)x;
+  p.w[0] = p.w[1] = p.w[2] = (const __nv_bfloat16*)w_lm;
+  p.out[0] = p.out[1] = p.out[2] = (__nv_bfloat16*)logits;
+  p.x_layer_stride = 0;
+  p.w_layer_stride[0] = p.w_layer_stride[1] = p.w_layer_stride[2] = 0;
+  p.out_layer_stride[0] = p.out_layer_stride[1] = p.out_layer_stride[2] = 0;
+  p.n[0] = p.n[1] = p.n[2] = vocab;
+  p.tiles_q = p.tiles_qk = vocab / kColsPerCta;  // every tile belongs to output 0
+  p.rows = rows;
+  p.hidden = hidden;
+  p.norm_w = (const __nv_bfloat16*)final_norm;
+  p.norm_layer_stride = 0;
+  p.eps = eps;
+  const dim3 grid(p.tiles_q, 1);
+  const cudaError_t e = launch_rows(p, grid, (cudaStream_t)stream);
+  if (e != cudaSuccess) {
+    char msg[256];
+    snprintf(msg, sizeof(msg), "pa_lm_head: %s", cudaGetErrorString(e));
+    return qfail(PA_ERR_CUDA, msg);
+  }
+  return PA_OK;
+}

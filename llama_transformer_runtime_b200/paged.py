@@ -416,6 +416,17 @@ def block_step(pool: "KVPool", attention: AttentionWeights, ffn_w: "FfnWeights",
                               stream))
 
 
+def lm_head(x, final_norm, w_lm, logits, rows: int, eps: float = 1e-5, stream: int = 0) -> None:
+    """logits [rows, vocab] bf16 = RMSNorm(x, final_norm) W_lm; w_lm [hidden, vocab] row-major."""
+    check(lib().pa_lm_head(_ptr(x), _ptr(final_norm), eps, _ptr(w_lm), _ptr(logits), rows, int(w_lm.shape[-2]),
+                           int(w_lm.shape[-1]), stream))
+
+
+def argmax(logits, tokens, rows: int, stream: int = 0) -> None:
+    """tokens[r] (int32) = index of the largest logit of row r, ties as the reference's kernel breaks them."""
+    check(lib().pa_argmax(_ptr(logits), _ptr(tokens), rows, int(logits.shape[-1]), stream))
+
+
 def pack_projection_weights(w, stream: int = 0):
     """Row-major [..., hidden, cols] bf16 weights -> the tile image qkv_project_append reads (a new tensor)."""
     import torch

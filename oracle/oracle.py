@@ -228,6 +228,28 @@ def ffn(x: np.ndarray, norm_w, wg: np.ndarray, wu: np.ndarray, wd: np.ndarray, e
     return f32_to_bf16(bf16_to_f32(x) + bf16_to_f32(y))
 
 
+def _bitrev5(x):
+    x = np.asarray(x)
+    return ((x & 1) << 4) | ((x & 2) << 2) | (x & 4) | ((x & 8) >> 2) | ((x & 16) >> 4)
+
+
+def argmax_reference_rule(logits: np.ndarray) -> np.ndarray:
+    """bf16 bit patterns [rows, vocab] -> int32 [rows]: index of the largest logit, ties broken as the
+    structure of the reference's argmax kernel breaks them (src/kernels/sampling/argmax_128256.cu:43-96):
+    256 threads scan t, t + 256, ... with a strict ">" (the smallest index of a thread wins), lanes and
+    then warps are combined by shuffle-down with a strict ">" — a tree whose left operand wins a tie, and
+    whose leaves from left to right are the lanes in bit-reversed order.  So among equal largest values
+    the winner has the smallest (bit-reversed warp number, bit-reversed lane number, index), with
+    thread = index mod 256."""
+    v = bf16_to_f32(np.ascontiguousarray(logits, dtype=np.uint16))
+    out = np.empty(v.shape[0], np.int32)
+    for r in range(v.shape[0]):
+        cand = np.flatnonzero(v[r] == v[r].max())
+        t = cand % 256
+        out[r] = cand[np.lexsort((cand, _bitrev5(t % 32), _bitrev5(t // 32)))[0]]
+    return out
+
+
 def num_threads() -> int:
     return int(lib().orc_num_threads())
 
@@ -296,6 +318,8 @@ def ref():
         r.ref_append_strided.restype = i
         r.ref_gemm.argtypes = [vp, vp, vp, i, i, i]
         r.ref_gemm.restype = i
+        r.ref_argmax.argtypes = [vp, vp]
+        r.ref_argmax.restype = None
         r.ref_silu_mul.argtypes = [vp, vp, vp, i]
         r.ref_silu_mul.restype = None
         r.ref_residual_add.argtypes = [vp, vp, vp, C.c_longlong]

@@ -16,6 +16,7 @@
 //                              (src/kernels/gemm/*.hpp), chosen by shape as Attention::forward and
 //                              FeedForward::forward choose them
 //   ref_silu_mul            -> launch_silu_mul            (src/kernels/silu/silu_8192.hpp)
+//   ref_argmax              -> launch_argmax              (src/kernels/sampling/argmax_128256.hpp)
 //   ref_append_*            -> the append the reference performs inline in
 //                              Attention::forward (src/runtime/attention.cu:239-262):
 //                              2*8*tokens device-to-device copies of 128 bytes.
@@ -28,6 +29,8 @@
 
 #include "flashattention.h"
 #include "gemm_2048x2048.hpp"
+#include "argmax_128256.hpp"
+#include "gemm_2048x128256.hpp"
 #include "gemm_2048x512.hpp"
 #include "gemm_2048x8192.hpp"
 #include "gemm_8192x2048.hpp"
@@ -89,10 +92,15 @@ int ref_gemm(const void* A, const void* B, void* C, int M, int N, int K) {
     launch_gemm_2048x512(a, b, c, M, N, K);
   else if (N == 8192)
     launch_gemm_2048x8192(a, b, c, M, N, K);
+  else if (N == 128256)
+    launch_gemm_2048x128256(a, b, c, M, N, K);  // the language-model head (src/runtime/llama_runtime.cu:895-902)
   else
     return 1;
   return (int)cudaGetLastError();
 }
+
+// token = argmax over the 128256 bf16 logits of one row (src/runtime/llama_runtime.cu:913-917).
+void ref_argmax(const void* logits, int* token) { launch_argmax((const __nv_bfloat16*)logits, token, 0); }
 
 // out = SiLU(gate) * up over rows x 8192 elements (src/runtime/ffn.cu:112-118).
 void ref_silu_mul(const void* gate, const void* up, void* out, int rows) {

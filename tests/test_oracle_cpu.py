@@ -248,3 +248,36 @@ def test_silu_mul_and_ffn_restatement_against_numpy():
     y = orc.gemm_bf16(h, wd)
     assert np.array_equal(orc.ffn(x, nw, wg, wu, wd, 1e-5, False), y)
     assert np.array_equal(orc.ffn(x, nw, wg, wu, wd, 1e-5, True), orc.f32_to_bf16(orc.bf16_to_f32(x) + orc.bf16_to_f32(y)))
+
+
+def test_argmax_rule_of_the_reference_kernel():
+    """A host model of the reference's argmax kernel (256 threads, strided scan with a strict ">",
+    shuffle-down reductions that keep the lower lane on ties) against the closed-form rule."""
+    rng = np.random.default_rng(79)
+
+    def kernel_model(v):
+        best_v = np.full(256, -np.inf, np.float32)
+        best_i = np.full(256, -1, np.int64)
+        for t in range(256):
+            idx = np.arange(t, v.size, 256)
+            j = int(np.argmax(v[idx]))  # first occurrence of the largest: the strict ">" scan
+            best_v[t], best_i[t] = v[idx][j], idx[j]
+        def warp_reduce(vals, idxs):
+            vals, idxs = vals.copy(), idxs.copy()
+            for off in (16, 8, 4, 2, 1):
+                for lane in range(32 - off):  # lanes past the end read themselves: no change
+                    if vals[lane + off] > vals[lane]:
+                        vals[lane], idxs[lane] = vals[lane + off], idxs[lane + off]
+            return vals[0], idxs[0]
+        wv, wi = zip(*(warp_reduce(best_v[32 * w:32 * w + 32], best_i[32 * w:32 * w + 32]) for w in range(8)))
+        pv = np.full(32, -np.inf, np.float32)
+        pi = np.full(32, -1, np.int64)
+        pv[:8], pi[:8] = wv, wi
+        return warp_reduce(pv, pi)[1]
+
+    for trial in range(20):
+        n = 128256 if trial < 2 else 3000
+        lg = orc.randn_bf16(rng, (1, n), 1.0)
+        ties = rng.choice(n, size=rng.integers(1, 5), replace=False)
+        lg[0, ties] = orc.f32_to_bf16(np.array([60.0], np.float32))[0]
+        assert orc.argmax_reference_rule(lg)[0] == kernel_model(orc.bf16_to_f32(lg[0]))
