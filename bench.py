@@ -1393,8 +1393,12 @@ def prefill_cpu_baseline(q_rot, out, pool, seq, S, budget_s=10.0):
 # =============================================================================
 # the decode step with its true data flow: projections -> attention -> output projection per layer
 # =============================================================================
-def run_chain(env: Env, args, sub: bool = False, ffn: bool = False):
-    """ffn=True (workload block_chain): whole transformer blocks — the attention block below followed by
+def run_chain(env: Env, args, sub: bool = False, ffn: bool = False, token: bool = False):
+    """token=True (workload token): a whole decode step of the model, the body of the reference's
+    LlamaRuntime::decode_forward — token id -> embedding row -> 16 blocks -> final RMSNorm + language-model
+    head (vocabulary 128256) -> greedy token, the id staying on the device from one step to the next
+    (pa_decode_token); one GPU.
+    ffn=True (workload block_chain): whole transformer blocks — the attention block below followed by
     the feed-forward block (RMSNorm, gate and up projections 2048 -> 8192, SiLU(gate) * up, down
     projection, residual): two more launches and 100.7 MB more weights per layer.
     ffn=False (workload decode_chain): one token through 16 attention blocks, each layer fed by the one before it (no FFN in between:
@@ -1409,6 +1413,11 @@ def run_chain(env: Env, args, sub: bool = False, ffn: bool = False):
     torch, dist = env.torch, env.dist
     from oracle import oracle as orc
     rank, local_rank, world, dev = env.rank, env.local_rank, env.world, env.dev
+    if token:
+        ffn = True
+        if rank != 0:
+            return None  # independent replicas only
+        world = 1
     ctx = args.chain_ctx
     steps = max(5, args.steps // 2) if sub else args.steps
     warmup = 3 if sub else args.warmup
@@ -1431,6 +1440,17 @@ def run_chain(env: Env, args, sub: bool = False, ffn: bool = False):
     x_dev = x_host.to(dev)
     y_dev = torch.zeros(1, H, dtype=torch.bfloat16, device=dev)
     weight_bytes = (H * (NQ + 2 * NKV) + NQ * H + H) * 2 + ((3 * H * INTER + H) * 2 if ffn else 0)
+    VOC = 128256
+    # per token outside the layers: the embedding row read and written, head weight + norm weight read,
+    # logits written, logits read by the argmax
+    head_bytes = (2 * H * 2 + (H * VOC + H + VOC) * 2 + VOC * 2) if token else 0
+    if token:
+        embed = mk(VOC, H, s=1.0)
+        w_lm = mk(H, VOC)
+        final_norm = mk(H, s=0.7)
+        tok_host = torch.tensor([1234], dtype=torch.int32).pin_memory()
+        tok_dev = tok_host.to(dev)
+        logits_dev = torch.zeros(1, VOC, dtype=torch.bfloat16, device=dev)
     total_steps = warmup + 2 * steps + 12
     state = {"len": ctx, "i": 0}
     ref = orc.ref() if orc.ref_available() else None
@@ -1469,6 +1489,7 @@ def run_chain(env: Env, args, sub: bool = False, ffn: bool = False):
         del ones, zeros
         descs = [paged.attention_weights(w["nw"], w["wq"], w["wk"], w["wv"], w["wo"]) for w in Ws]
         fdescs = [paged.ffn_weights(w["fn"], w["wg"], w["wu"], w["wd"]) for w in Ws] if ffn else None
+        models = [paged.model_weights(embed, descs[i], fdescs[i], final_norm, w_lm) for i in range(SETS)] if token else None
 
         def run_layers(s, l0, l1, xin, xout):
             if ffn:
@@ -1492,7 +1513,10 @@ def run_chain(env: Env, args, sub: bool = False, ffn: bool = False):
                 pool.batch_set([seq])
             else:
                 pool.batch_set_sharded([seq], [1 if rank == owner else 0], [1], [state["len"] - 1], [lo])
-            run_layers(s, 0, LAYERS, x_dev, y_dev)
+            if token:
+                paged.decode_token(pool, models[s], tok_dev, tok_dev, logits_dev, cos, sin, chained=True)
+            else:
+                run_layers(s, 0, LAYERS, x_dev, y_dev)
 
     if ref is not None and (ref_arm or sub) and rank == 0:
         max_seq = ctx + total_steps + 2
@@ -1503,7 +1527,7 @@ def run_chain(env: Env, args, sub: bool = False, ffn: bool = False):
             vc[layer, :, :ctx] = (torch.randn(KV_HEADS, ctx, D, generator=kvgen, device=dev) * 0.5).to(torch.bfloat16)
         bufs = {n: torch.zeros(1, c, dtype=torch.bfloat16, device=dev) for n, c in
                 (("xn", H), ("q", NQ), ("k", NKV), ("v", NKV), ("arow", NQ), ("lin", H), ("xa", H), ("xb", H), ("xm", H),
-                 ("g", INTER), ("u", INTER), ("h", INTER))}
+                 ("g", INTER), ("u", INTER), ("h", INTER), ("emb", H))}
         qf = torch.empty(Q_HEADS, 1, D, dtype=torch.bfloat16, device=dev)
         kf = torch.empty(KV_HEADS, 1, D, dtype=torch.bfloat16, device=dev)
         vf = torch.empty(KV_HEADS, 1, D, dtype=torch.bfloat16, device=dev)
@@ -1516,6 +1540,11 @@ def run_chain(env: Env, args, sub: bool = False, ffn: bool = False):
             w = Ws[rstate["i"] % SETS]
             rstate["i"] += 1
             cur = x_dev
+            if token:  # decode_forward: blocking copy of the id, embedding kernel, synchronisation
+                tok_dev.copy_(tok_host)
+                ref.ref_embedding(tok_dev.data_ptr(), embed.data_ptr(), bufs["emb"].data_ptr(), 1)
+                torch.cuda.synchronize()
+                cur = bufs["emb"]
             for l in range(LAYERS):
                 ref.ref_rmsnorm(cur.data_ptr(), w["nw"][l].data_ptr(), bufs["xn"].data_ptr(), 1, 1e-5)
                 torch.cuda.synchronize()
@@ -1550,11 +1579,31 @@ def run_chain(env: Env, args, sub: bool = False, ffn: bool = False):
                 ref.ref_residual_add(bufs["xm"].data_ptr(), bufs["lin"].data_ptr(), nxt.data_ptr(), H)
                 torch.cuda.synchronize()
                 cur = nxt
-            y_dev.copy_(cur)
+            if not token:
+                y_dev.copy_(cur)
+                return
+            torch.cuda.synchronize()  # after transformer_->forward
+            ref.ref_rmsnorm(cur.data_ptr(), final_norm.data_ptr(), bufs["xn"].data_ptr(), 1, 1e-5)
+            torch.cuda.synchronize()
+            ref.ref_gemm(bufs["xn"].data_ptr(), w_lm.data_ptr(), logits_dev.data_ptr(), 1, VOC, H)
+            torch.cuda.synchronize()
+            t = torch.empty(1, dtype=torch.int32, device=dev)  # the loop's per-token cudaMalloc / cudaFree
+            ref.ref_argmax(logits_dev.data_ptr(), t.data_ptr())
+            tok_host.copy_(t)  # blocking copy
+            del t
+            torch.cuda.synchronize()
 
     step = ref_step if ref_arm else ours_step
 
     def e2e_step():
+        if token:  # a generation loop that reads every token on the host (the reference's own arm does already)
+            if ref_arm:
+                return step()
+            tok_dev.copy_(tok_host, non_blocking=True)
+            step()
+            tok_host.copy_(tok_dev, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            return
         x_dev.copy_(x_host, non_blocking=True)
         step()
         y_host.copy_(y_dev, non_blocking=True)
@@ -1564,7 +1613,7 @@ def run_chain(env: Env, args, sub: bool = False, ffn: bool = False):
         st = rstate if ref_arm else state
         l0 = st["len"]
         ms = local_timed(torch, fn, n) if ref_arm else env.timed(fn, n)
-        return ms, sum(LAYERS * (decode_bytes(L) + weight_bytes) for L in range(l0 + 1, st["len"] + 1))
+        return ms, sum(LAYERS * (decode_bytes(L) + weight_bytes) + head_bytes for L in range(l0 + 1, st["len"] + 1))
 
     m0 = env.sampler.mark()
     for _ in range(warmup):
@@ -1577,22 +1626,29 @@ def run_chain(env: Env, args, sub: bool = False, ffn: bool = False):
     line = None
     if rank == 0:
         line = {
-            "metric": "block_chain_hbm_gbs" if ffn else "decode_chain_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": 1 if ref_arm else world,
+            "metric": "decode_token_hbm_gbs" if token else "block_chain_hbm_gbs" if ffn else "decode_chain_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": 1 if ref_arm else world,
             "steps": steps, "warmup": warmup, "ms_per_step": round(ms / steps, 4),
             "us_per_token": round(ms / steps * 1e3, 2), "us_per_layer": round(ms / steps * 1e3 / LAYERS, 2),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{'block' if ffn else 'decode'}_chain_ctx{ctx}_x{LAYERS}layers_batch1", "context": ctx, "layers": LAYERS,
-                       "batch": 1, "hidden": H, "bytes": "per layer: Wq, Wk, Wv, Wo, norm weight" + (", Wgate, Wup, Wdown, FFN norm weight" if ffn else "") + " + the layer's cache (2048 L + ...)",
+            "config": {"workload": f"token_ctx{ctx}_x{LAYERS}layers_vocab{VOC}_batch1" if token else
+                                   f"{'block' if ffn else 'decode'}_chain_ctx{ctx}_x{LAYERS}layers_batch1", "context": ctx, "layers": LAYERS,
+                       "batch": 1, "hidden": H, "bytes": "per layer: Wq, Wk, Wv, Wo, norm weight" + (", Wgate, Wup, Wdown, FFN norm weight" if ffn else "") + " + the layer's cache (2048 L + ...)" +
+                                (f"; per token: embedding row, final norm + head weight [{H}, {VOC}], logits written and read" if token else ""),
                        "parallelism": "1 GPU" if world == 1 or ref_arm else
                                       f"cache split by token range over {world} GPUs, weights replicated",
                        "l2": f"{SETS} weight sets in rotation ({SETS * LAYERS * weight_bytes / 1e9:.2f} GB) + "
                              f"{LAYERS * decode_bytes(ctx) / 1e9:.2f} GB of cache per step"},
             "e2e": {"value": round(nbytes_e2e / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
-                    "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2,
+                    "h2d_bytes_per_step": 4 if token else x_host.numel() * 2,
+                    "d2h_bytes_per_step": 4 if token else y_host.numel() * 2,
                     "ms_per_step": round(ms_e2e / steps, 4)},
-            "gpu_launches": (LAYERS * (17 if ffn else 11) if ref_arm else LAYERS * (5 if ffn else 3)) * steps,
+            "gpu_launches": ((LAYERS * (17 if ffn else 11) + (4 if token else 0)) if ref_arm else
+                             LAYERS * (5 if ffn else 3) + (3 if token else 0)) * steps,
             "clocks": env.sampler.summary(m0, m1),
         }
+        if token:
+            line["tokens_per_s"] = round(steps / (ms * 1e-3), 1)
+            line["e2e"]["tokens_per_s"] = round(steps / (ms_e2e * 1e-3), 1)
     if ref_arm:
         line["impl"] = "reference"
         line["cpu_baseline"] = {"value": line["value"], "unit": "GB/s", "cores": 0, "kind": "reference",
@@ -1641,26 +1697,45 @@ def run_chain(env: Env, args, sub: bool = False, ffn: bool = False):
         e15 = row_rel_err(orc.bf16_to_f32(_u16(y_dev)), orc.bf16_to_f32(cur), row=H)
         line["checks"] = {"oracle_layer0_max_err_over_row_max": e0, "oracle_layer0_ok": bool(e0 <= (2.0 ** -5 if ffn else 2.0 ** -6)),
                           "oracle_16_layer_chain_max_err_over_row_max": e15}
-        line["cpu_baseline"] = {"value": round(LAYERS * (decode_bytes(L0 + 1) + weight_bytes) / dt / 1e9, 3), "unit": "GB/s",
+        if token:
+            # the head on the GPU's own final row against the oracle on that row; the last timed step's token
+            # against the reference kernel's rule on the logits that step produced
+            last_logits, last_tok = _u16(logits_dev), int(tok_dev.cpu().item())
+            chk = torch.zeros(1, VOC, dtype=torch.bfloat16, device=dev)
+            paged.lm_head(y_dev, final_norm, w_lm, chk, 1)
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            want = orc.gemm_bf16(orc.rmsnorm(_u16(y_dev), _u16(final_norm), 1e-5), _u16(w_lm))
+            dt += time.perf_counter() - t1
+            eh = row_rel_err(orc.bf16_to_f32(_u16(chk)), orc.bf16_to_f32(want), row=VOC)
+            line["checks"].update({"head_logits_max_err_over_row_max": eh, "head_logits_ok": bool(eh <= 2.0 ** -7),
+                                   "token": last_tok, "token_is_the_reference_rule_on_its_logits":
+                                       bool(last_tok == int(orc.argmax_reference_rule(last_logits)[0]))})
+        line["cpu_baseline"] = {"value": round((LAYERS * (decode_bytes(L0 + 1) + weight_bytes) + head_bytes) / dt / 1e9, 3), "unit": "GB/s",
                                 "cores": orc.num_threads(), "kind": "port",
-                                "sample": f"one token through all {LAYERS} layers with the CPU oracle chain, {dt:.2f} s"}
+                                "sample": f"one token through all {LAYERS} layers" + (" and the head" if token else "") +
+                                          f" with the CPU oracle chain, {dt:.2f} s"}
         n_launch = 5 if ffn else 3
-        line["roofline"] = {"bound": "hbm", "kernel": "qkv_project_kernel + decode_kernel + qkv_project_kernel" +
+        line["roofline"] = {"bound": "hbm", "kernel": ("embedding_rows_kernel + " if token else "") +
+                                                       "qkv_project_kernel + decode_kernel + qkv_project_kernel" +
                                                        (" + ffn_gate_up_kernel + ffn_down_kernel" if ffn else "") +
-                                                       f" ({n_launch} launches per layer)",
+                                                       f" ({n_launch} launches per layer)" +
+                                                       (" + qkv_project_kernel (head) + argmax_rows_kernel" if token else ""),
                             "achieved": round(value, 1), "peak": peak, "unit": "GB/s", "frac": round(value / peak, 4),
                             "peak_source": f"of {peak_kind}", "us_per_launch": round(ms / steps * 1e3 / LAYERS / n_launch, 2),
                             "bytes_per_launch": (decode_bytes(ctx) + weight_bytes) // n_launch, "traffic": None}
         if sub and ref is not None:
             ref_step()
             rms = local_timed(torch, ref_step, 2) / 2
-            rb = LAYERS * (decode_bytes(ctx) + weight_bytes)
+            rb = LAYERS * (decode_bytes(ctx) + weight_bytes) + head_bytes
             line["reference"] = {"value": round(rb / (rms * 1e-3) / 1e9, 2), "unit": "GB/s",
-                                 "us_per_layer": round(rms * 1e3 / LAYERS, 2),
+                                 "us_per_layer": round(rms * 1e3 / LAYERS, 2), "us_per_token": round(rms * 1e3, 2),
                                  "how": "the reference's RMSNorm, 3 GEMMs, RoPE kernels, append copies, attention kernel, "
                                         "layout kernel, output GEMM and residual add" +
                                         (", then RMSNorm, gate and up GEMMs, SiLU*up kernel, down GEMM and residual add" if ffn else "") +
-                                        " per layer, with its synchronisations"}
+                                        " per layer, with its synchronisations" +
+                                        ("; around them the blocking id copy, embedding kernel, final RMSNorm, head GEMM, "
+                                         "argmax with its allocation and blocking copy" if token else "")}
     env.barrier()
     if xchg is not None:
         xchg.close()
@@ -1794,6 +1869,7 @@ SUB_BLOCKS = {
     "decode_chain": lambda env, a: run_chain(env, a, sub=True),
     "block_chain": lambda env, a: run_chain(env, a, sub=True, ffn=True),
     "lm_head": lambda env, a: run_lm_head(env, a, sub=True),
+    "token": lambda env, a: run_chain(env, a, sub=True, token=True),
 }
 
 
@@ -1814,7 +1890,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode128k",
                     choices=sorted(WORKLOADS) + ["prefill2k", "append2k", "batch64", "qkv_decode", "out_project", "qkv_prefill",
-                                                  "decode_chain", "block_chain", "lm_head"])
+                                                  "decode_chain", "block_chain", "lm_head", "token"])
     ap.add_argument("--chain-ctx", type=int, default=4096, help="decode_chain: context length")
     ap.add_argument("--no-sub", action="store_true", help="default workload: skip the sub-blocks")
     ap.add_argument("--sub", default="", help="default workload: comma-separated sub-blocks to run (default: all)")
@@ -1883,6 +1959,8 @@ def main():
         line = run_chain(env, args, ffn=True)
     elif args.workload == "lm_head":
         line = run_lm_head(env, args)
+    elif args.workload == "token":
+        line = run_chain(env, args, token=True)
     if rank == 0 and line is not None:
         print(json.dumps(line), flush=True)
     env.sampler.stop()

@@ -392,6 +392,33 @@ int pa_lm_head(const void* x, const void* final_norm, float eps, const void* w_l
                int hidden, int vocab, void* stream);
 int pa_argmax(const void* logits, int32_t* tokens, int rows, int vocab, void* stream);
 
+/* ---- a whole decode step of the model ---------------------------------------------------------
+ * pa_embedding replaces launch_embedding (src/kernels/embedding/embedding.cu:31-95): out[r, :] =
+ * table[tokens[r], :], bf16 rows of `hidden` elements, ids read on the device; an id outside
+ * [0, vocab) gives a row of zeros (the reference reads outside the table).
+ *
+ * pa_decode_token replaces the body of LlamaRuntime::decode_forward
+ * (src/runtime/llama_runtime.cu:822-945) for the sequences of the active batch (pa_batch_set, one new
+ * token each, at most 8): ids -> embedding -> the pool's layers as pa_block_step runs them -> final
+ * RMSNorm + language-model head -> greedy token.  tokens_in, tokens_out: device int32 [sequences]
+ * (they may be the same buffer); logits: device bf16 [sequences, vocab], the caller's.  No host
+ * synchronisation, no allocation; chained != 0 says the ids are the output of the step enqueued
+ * just before on this stream (the embedding kernel is then a dependent launch too).  An id out of
+ * range is recorded in the pool's status word (pa_pool_check). */
+typedef struct pa_model_weights {
+  const void* embed_tokens;              /* [vocab, hidden] bf16 */
+  const pa_attention_weights* attention; /* every layer's attention block */
+  const pa_ffn_weights* ffn;             /* every layer's feed-forward block */
+  const void* final_norm;                /* [hidden] bf16, nullable */
+  const void* lm_head;                   /* [hidden, vocab] bf16 row-major */
+  int vocab;                             /* a multiple of 32 */
+  float rms_eps;                         /* of the final norm */
+} pa_model_weights;
+int pa_embedding(const int32_t* tokens, const void* table, void* out, int rows, int hidden, int vocab, void* stream);
+int pa_decode_token(pa_pool* pool, const pa_model_weights* model, const int32_t* tokens_in, int32_t* tokens_out,
+                    void* logits, const float* cos_table, const float* sin_table, float scale, int chained,
+                    void* stream);
+
 /* Host: fp32 cos/sin tables [seq_len][32], Llama-3 frequency scaling. */
 int pa_build_rope_tables(float* cos_table, float* sin_table, int seq_len);
 

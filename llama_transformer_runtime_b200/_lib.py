@@ -18,7 +18,7 @@ SYMBOLS = [
     "pa_pool_set_free_order", "pa_pool_layer_storage", "pa_seq_create", "pa_seq_free",
     "pa_seq_reserve", "pa_seq_length", "pa_seq_block_table", "pa_batch_set", "pa_batch_set_sharded", "pa_append",
     "pa_decode", "pa_decode_step", "pa_prefill", "pa_merge_partials", "pa_gather_kv", "pa_build_rope_tables",
-    "pa_pool_check", "pa_pool_set_decode_chunk_blocks", "pa_pool_set_decode_cluster", "pa_pool_set_decode_shape", "pa_pool_set_step_kernel", "pa_pool_set_layer_overlap", "pa_pool_set_step_combiners", "pa_pool_step_launches", "pa_qkv_project", "pa_rmsnorm_qkv_project", "pa_rmsnorm", "pa_attention_step", "pa_ffn", "pa_ffn_rows", "pa_block_step", "pa_lm_head", "pa_argmax", "pa_out_project", "pa_out_project_rows", "pa_qkv_project_packed", "pa_qkv_project_append", "pa_pack_projection_weights",
+    "pa_pool_check", "pa_pool_set_decode_chunk_blocks", "pa_pool_set_decode_cluster", "pa_pool_set_decode_shape", "pa_pool_set_step_kernel", "pa_pool_set_layer_overlap", "pa_pool_set_step_combiners", "pa_pool_step_launches", "pa_qkv_project", "pa_rmsnorm_qkv_project", "pa_rmsnorm", "pa_attention_step", "pa_ffn", "pa_ffn_rows", "pa_block_step", "pa_lm_head", "pa_argmax", "pa_embedding", "pa_decode_token", "pa_out_project", "pa_out_project_rows", "pa_qkv_project_packed", "pa_qkv_project_append", "pa_pack_projection_weights",
     "pa_decode_noalloc", "pa_decode_noalloc_check", "pa_decode_step_sharded_colocated", "pa_exchange_create", "pa_exchange_handle", "pa_exchange_connect",
     "pa_exchange_destroy", "pa_decode_step_sharded", "pa_exchange_buffer", "pa_exchange_connect_ptrs",
     "pa_decode_push", "pa_exchange_merge", "pa_gather_create", "pa_gather_handle", "pa_gather_connect",
@@ -52,6 +52,12 @@ class FfnWeights(C.Structure):
     _fields_ = [("ffn_norm", C.c_void_p), ("gate", C.c_void_p), ("up", C.c_void_p), ("down", C.c_void_p),
                 ("norm_layer_stride", C.c_int64), ("gate_layer_stride", C.c_int64), ("up_layer_stride", C.c_int64),
                 ("down_layer_stride", C.c_int64), ("rms_eps", C.c_float), ("hidden", C.c_int), ("inter", C.c_int)]
+
+
+class ModelWeights(C.Structure):
+    """pa_model_weights of include/paged_attention.h."""
+    _fields_ = [("embed_tokens", C.c_void_p), ("attention", C.POINTER(AttentionWeights)), ("ffn", C.POINTER(FfnWeights)),
+                ("final_norm", C.c_void_p), ("lm_head", C.c_void_p), ("vocab", C.c_int), ("rms_eps", C.c_float)]
 
 
 class PagedAttentionError(RuntimeError):
@@ -109,6 +115,8 @@ def lib():
         "pa_ffn_rows": [vp, vp, i, vp, vp, vp, i, i, vp],
         "pa_lm_head": [vp, vp, f, vp, vp, i, i, i, vp],
         "pa_argmax": [vp, vp, i, i, vp],
+        "pa_embedding": [vp, vp, vp, i, i, i, vp],
+        "pa_decode_token": [vp, vp, vp, vp, vp, vp, vp, f, i, vp],
         "pa_block_step": [vp, vp, i, i, vp, vp, vp, vp, vp, vp, f, vp],
         "pa_out_project": [vp, vp, vp, vp, i, i, i, i, i64, i64, i64, vp],
         "pa_out_project_rows": [vp, vp, vp, vp, vp, i, i, i, vp],

@@ -17,7 +17,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libpaged_attention.so")
 
 SOURCES = ["capi.cu", "append_kernel.cu", "decode_kernel.cu", "decode_noalloc.cu", "exchange.cu", "head_gather.cu",
-           "prefill_kernel.cu", "compat.cu", "compat_cxx.cu", "qkv_project.cu", "qkv_gemm.cu", "rmsnorm.cu", "ffn.cu", "sampling.cu", "block_pool.cpp"]
+           "prefill_kernel.cu", "compat.cu", "compat_cxx.cu", "qkv_project.cu", "qkv_gemm.cu", "rmsnorm.cu", "ffn.cu", "sampling.cu", "embedding.cu", "block_pool.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -78,7 +78,8 @@ struct pa_pool {
   int step_combiners_override = 0;  // pa_pool_set_step_combiners
   long long step_launches = 0;  // decode steps that ran as one cooperative launch
   // rows of a decode step between the kernels of pa_attention_step: q, k, v, rotated q, attention
-  // output and two block inputs in turn, kMaxStepRows rows each
+  // output and two block inputs in turn, kMaxStepRows rows each; behind them the feed-forward block's
+  // input and activated rows, and the embedded and final rows of pa_decode_token
   __nv_bfloat16* step_ws = nullptr;
   int cluster_mode = 0;  // one-layer decode kernel: 0 = planner decides, -1 = never clusters, 2/4/8/16 = that cluster size
   int* prefill_work = nullptr;  // 64 item counters, one per prefill launch in rotation, zero when idle
@@ -106,6 +107,11 @@ int out_project_impl(const void* attn, const void* wo, const void* residual, voi
                      int64_t residual_layer_stride, int64_t out_layer_stride, int pdl, void* stream);
 int ffn_impl(const void* x, const void* norm_w, float eps, const void* wg, const void* wu, const void* wd,
              const void* residual, void* h, void* out, int rows, int hidden, int inter, int pdl, void* stream);
+int embedding_impl(const int32_t* tokens, const void* table, void* out, int rows, int hidden, int vocab, int* status,
+                   int pdl, void* stream);
+int lm_head_impl(const void* x, const void* final_norm, float eps, const void* w_lm, void* logits, int rows, int hidden,
+                 int vocab, int pdl, void* stream);
+int argmax_impl(const void* logits, int32_t* tokens, int rows, int vocab, int pdl, void* stream);
 }  // namespace pa
 
 struct pa_gather;
@@ -150,7 +156,7 @@ int pa_pool_create(pa_pool** out, int device, int num_layers, int num_blocks, in
     alloc((void**)&p->ws_count, (size_t)max_seqs * kv_heads * pa::kMaxStepLayers * sizeof(unsigned int));
     alloc((void**)&p->prefill_work, 64 * sizeof(int));
     alloc((void**)&p->step_ws, (size_t)kMaxStepRows * (3 * kv_heads * pa::kGroup * pa::kHeadDim +
-                                                        2 * kv_heads * pa::kHeadDim + 3 * kMaxStepHidden + kMaxStepInter) *
+                                                        2 * kv_heads * pa::kHeadDim + 5 * kMaxStepHidden + kMaxStepInter) *
                                    sizeof(__nv_bfloat16));
     alloc((void**)&p->d_status, sizeof(int));
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&p->sm_count, cudaDevAttrMultiProcessorCount, device);
@@ -799,7 +805,8 @@ int pa_decode_step_sharded_colocated(pa_pool* const* pools, pa_exchange* const* 
 // reads its output.  All intermediate rows live in the pool's step workspace.
 static int step_layers(pa_pool* p, pa_exchange* x, int layer_begin, int layer_end, const pa_attention_weights* w,
                        const pa_ffn_weights* f, const void* x_in, void* x_out, int add_residual,
-                       const float* cos_table, const float* sin_table, float scale, void* stream) {
+                       const float* cos_table, const float* sin_table, float scale, void* stream,
+                       bool follows_own_kernel = false) {
   if (!p || !w || !x_in || !x_out || !cos_table || !sin_table)
     return fail(PA_ERR_INVALID_ARG, "pa_attention_step: NULL argument");
   if (!w->wq || !w->wk || !w->wv || !w->wo) return fail(PA_ERR_INVALID_ARG, "pa_attention_step: NULL weight");
@@ -839,8 +846,9 @@ static int step_layers(pa_pool* p, pa_exchange* x, int layer_begin, int layer_en
     const __nv_bfloat16* wv = (const __nv_bfloat16*)w->wv + (size_t)l * w->wkv_layer_stride;
     const __nv_bfloat16* wo = (const __nv_bfloat16*)w->wo + (size_t)l * w->wo_layer_stride;
     // the first kernel of the call follows work this library knows nothing about: plain launch
+    // (unless the caller is pa_decode_token, whose embedding kernel is in front)
     int r = pa::qkv_project_impl(cur, norm, 0, w->rms_eps, wq, wk, wv, q, k, v, rows, 1, hidden, q_cols, kv_cols, 0, 0, 0,
-                                 0, 0, first ? 0 : 1, stream);
+                                 0, 0, first && !follows_own_kernel ? 0 : 1, stream);
     if (r != PA_OK) return r;
     const FusedAppend fz{appends ? k : nullptr, appends ? v : nullptr, cos_table, sin_table, q_rot, 2};
     r = decode_impl(p, l, q, attn, q_cols, nullptr, nullptr, scale, stream, x, true, &fz);
@@ -877,6 +885,51 @@ int pa_block_step(pa_pool* p, pa_exchange* x, int layer_begin, int layer_end, co
   if (w && f->hidden != w->hidden) return fail(PA_ERR_INVALID_ARG, "pa_block_step: the two blocks disagree on hidden");
   if (f->inter > kMaxStepInter) return fail(PA_ERR_UNSUPPORTED, "pa_block_step: intermediate width above %d", kMaxStepInter);
   return step_layers(p, x, layer_begin, layer_end, w, f, x_in, x_out, 1, cos_table, sin_table, scale, stream);
+}
+
+// One decode step of the whole model for the active batch, the body of the reference's
+// LlamaRuntime::decode_forward (src/runtime/llama_runtime.cu:822-945) without its blocking copies,
+// its per-token cudaMalloc / cudaFree and its seven device synchronisations: token ids (on the
+// device) -> embedding rows -> every layer's block (pa_block_step's chain) -> final RMSNorm +
+// language-model head -> greedy token, all on `stream`, every kernel behind the first a dependent
+// launch.  tokens_out may be tokens_in, so consecutive steps run without the host reading a token.
+int pa_decode_token(pa_pool* p, const pa_model_weights* m, const int32_t* tokens_in, int32_t* tokens_out, void* logits,
+                    const float* cos_table, const float* sin_table, float scale, int chained, void* stream) {
+  if (!p || !m || !tokens_in || !tokens_out || !logits)
+    return fail(PA_ERR_INVALID_ARG, "pa_decode_token: NULL argument");
+  if (!m->embed_tokens || !m->attention || !m->ffn || !m->lm_head)
+    return fail(PA_ERR_INVALID_ARG, "pa_decode_token: NULL weight");
+  if (p->device < 0) return fail(PA_ERR_STATE, "pa_decode_token: host-only pool");
+  if (p->batch.empty()) return fail(PA_ERR_STATE, "pa_decode_token: no active batch (call pa_batch_set)");
+  const int rows = (int)p->batch.size();
+  if (rows > kMaxStepRows) return fail(PA_ERR_UNSUPPORTED, "pa_decode_token: at most %d sequences per step", kMaxStepRows);
+  const int hidden = m->attention->hidden;
+  if (hidden < 64 || hidden > kMaxStepHidden || hidden % 64 != 0)
+    return fail(PA_ERR_UNSUPPORTED, "pa_decode_token: hidden must be a multiple of 64, at most %d", kMaxStepHidden);
+  if (m->vocab < 32 || m->vocab % 32 != 0) return fail(PA_ERR_UNSUPPORTED, "pa_decode_token: vocab must be a multiple of 32");
+  const int q_cols = p->kv_heads * pa::kGroup * pa::kHeadDim, kv_cols = p->kv_heads * pa::kHeadDim;
+  __nv_bfloat16* x_tok = p->step_ws + (size_t)kMaxStepRows * (3 * q_cols + 2 * kv_cols + 3 * kMaxStepHidden + kMaxStepInter);
+  __nv_bfloat16* x_fin = x_tok + (size_t)kMaxStepRows * kMaxStepHidden;
+  {
+    DeviceGuard g(p->device);
+    // chained != 0: the ids are the output of the step enqueued just before on this stream
+    const int r = pa::embedding_impl(tokens_in, m->embed_tokens, x_tok, rows, hidden, m->vocab, p->d_status,
+                                     chained ? 1 : 0, stream);
+    if (r != PA_OK) return r;
+  }
+  const pa_ffn_weights* f = m->ffn;
+  if (!f->gate || !f->up || !f->down) return fail(PA_ERR_INVALID_ARG, "pa_decode_token: NULL feed-forward weight");
+  if (f->hidden != hidden) return fail(PA_ERR_INVALID_ARG, "pa_decode_token: the two blocks disagree on hidden");
+  if (f->inter > kMaxStepInter) return fail(PA_ERR_UNSUPPORTED, "pa_decode_token: intermediate width above %d", kMaxStepInter);
+  int r = step_layers(p, nullptr, 0, p->num_layers, m->attention, f, x_tok, x_fin, 1, cos_table, sin_table, scale, stream,
+                      /*follows_own_kernel=*/true);
+  if (r != PA_OK) return r;
+  DeviceGuard g(p->device);
+  r = pa::lm_head_impl(x_fin, m->final_norm, m->rms_eps, m->lm_head, logits, rows, hidden, m->vocab, 1, stream);
+  if (r != PA_OK) return r;
+  r = pa::argmax_impl(logits, tokens_out, rows, m->vocab, 1, stream);
+  if (r != PA_OK) return r;
+  return PA_OK;
 }
 
 int pa_decode_step(pa_pool* p, int layer_begin, int layer_end, const void* q_in, const void* k_in,

@@ -399,7 +399,8 @@ int qfail(int code, const char* msg) {
 // when p.pdl is set (the kernel then waits for the kernel in front before it reads x).
 cudaError_t launch_rows(const QkvParams& p, dim3 grid, cudaStream_t st) {
   // one layer behind another kernel: the form that holds its weight slab in shared memory
-  const bool resident = p.pdl && grid.y == 1 && p.hidden <= kMaxHidden;
+  // (a grid of many waves, the language-model head, streams: its CTAs overlap one another)
+  const bool resident = p.pdl && grid.y == 1 && p.hidden <= kMaxHidden && grid.x <= 512;
   void (*kern)(QkvParams) = resident ? (p.rows == 1 ? qkv_project_kernel<1, true>
                                         : p.rows == 2 ? qkv_project_kernel<2, true>
                                         : p.rows <= 4 ? qkv_project_kernel<4, true>
@@ -610,8 +611,9 @@ int pa::out_project_impl(const void* attn, const void* wo, const void* residual,
 // (src/runtime/llama_runtime.cu:880-905; the weight [hidden, vocab] row-major).  The same
 // weight-streaming kernel as the projections: 525 MB per token for the 128256-entry vocabulary,
 // 4008 column tiles of 32.
-extern "C" int pa_lm_head(const void* x, const void* final_norm, float eps, const void* w_lm, void* logits, int rows,
-                          int hidden, int vocab, void* stream) {
+namespace pa {
+int lm_head_impl(const void* x, const void* final_norm, float eps, const void* w_lm, void* logits, int rows, int hidden,
+                 int vocab, int pdl, void* stream) {
   if (!x || !w_lm || !logits) return qfail(PA_ERR_INVALID_ARG, "pa_lm_head: NULL argument");
   if (rows < 1) return qfail(PA_ERR_INVALID_ARG, "pa_lm_head: rows must be >= 1");
   if (rows > 8) return qfail(PA_ERR_UNSUPPORTED, "pa_lm_head: at most 8 rows per call (decode shapes)");
@@ -632,6 +634,7 @@ extern "C" int pa_lm_head(const void* x, const void* final_norm, float eps, cons
   p.norm_w = (const __nv_bfloat16*)final_norm;
   p.norm_layer_stride = 0;
   p.eps = eps;
+  p.pdl = pdl;
   const dim3 grid(p.tiles_q, 1);
   const cudaError_t e = launch_rows(p, grid, (cudaStream_t)stream);
   if (e != cudaSuccess) {
@@ -640,4 +643,10 @@ extern "C" int pa_lm_head(const void* x, const void* final_norm, float eps, cons
     return qfail(PA_ERR_CUDA, msg);
   }
   return PA_OK;
+}
+}  // namespace pa
+
+extern "C" int pa_lm_head(const void* x, const void* final_norm, float eps, const void* w_lm, void* logits, int rows,
+                          int hidden, int vocab, void* stream) {
+  return pa::lm_head_impl(x, final_norm, eps, w_lm, logits, rows, hidden, vocab, 0, stream);
 }

@@ -43,8 +43,12 @@ __device__ __forceinline__ bool beats(const Cand& b, const Cand& a) {
   return kb != ka ? kb < ka : b.i < a.i;
 }
 
-__global__ void __launch_bounds__(kArgmaxThreads) argmax_rows_kernel(const __nv_bfloat16* logits, int* tokens, int vocab) {
+__global__ void __launch_bounds__(kArgmaxThreads) argmax_rows_kernel(const __nv_bfloat16* logits, int* tokens, int vocab, int pdl) {
   __shared__ Cand s_best[kArgmaxThreads / 32];
+  if (pdl) {  // behind the language-model head of the same step: the logits are its output
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
   const __nv_bfloat16* row = logits + (size_t)blockIdx.x * vocab;
   Cand best{-FLT_MAX, -1};
   const int chunks = vocab / 8;
@@ -83,21 +87,35 @@ __global__ void __launch_bounds__(kArgmaxThreads) argmax_rows_kernel(const __nv_
 
 }  // namespace
 
-extern "C" int pa_argmax(const void* logits, int32_t* tokens, int rows, int vocab, void* stream) {
+namespace pa {
+int argmax_impl(const void* logits, int32_t* tokens, int rows, int vocab, int pdl, void* stream) {
   if (!logits || !tokens) {
-    pa::set_last_error("pa_argmax: NULL argument");
+    set_last_error("pa_argmax: NULL argument");
     return PA_ERR_INVALID_ARG;
   }
   if (rows < 1) return PA_OK;
   if (vocab < 1 || (vocab % 8 != 0 && rows > 1) || (reinterpret_cast<uintptr_t>(logits) & 15u) != 0) {
-    pa::set_last_error("pa_argmax: logits must be 16-byte aligned and, for several rows, vocab a multiple of 8");
+    set_last_error("pa_argmax: logits must be 16-byte aligned and, for several rows, vocab a multiple of 8");
     return PA_ERR_INVALID_ARG;
   }
-  argmax_rows_kernel<<<rows, kArgmaxThreads, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, tokens, vocab);
-  const cudaError_t e = cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(rows);
+  cfg.blockDim = dim3(kArgmaxThreads);
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, argmax_rows_kernel, (const __nv_bfloat16*)logits, (int*)tokens, vocab, pdl);
   if (e != cudaSuccess) {
-    pa::set_last_error(cudaGetErrorString(e));
+    set_last_error(cudaGetErrorString(e));
     return PA_ERR_CUDA;
   }
   return PA_OK;
+}
+}  // namespace pa
+
+extern "C" int pa_argmax(const void* logits, int32_t* tokens, int rows, int vocab, void* stream) {
+  return pa::argmax_impl(logits, tokens, rows, vocab, 0, stream);
 }

@@ -10,7 +10,7 @@ import ctypes as C
 
 import numpy as np
 
-from ._lib import AttentionWeights, FfnWeights, check, lib
+from ._lib import AttentionWeights, FfnWeights, ModelWeights, check, lib
 
 HEAD_DIM = 64
 GROUP = 4
@@ -425,6 +425,35 @@ def lm_head(x, final_norm, w_lm, logits, rows: int, eps: float = 1e-5, stream: i
 def argmax(logits, tokens, rows: int, stream: int = 0) -> None:
     """tokens[r] (int32) = index of the largest logit of row r, ties as the reference's kernel breaks them."""
     check(lib().pa_argmax(_ptr(logits), _ptr(tokens), rows, int(logits.shape[-1]), stream))
+
+
+def embedding(tokens, table, out, rows: int, stream: int = 0) -> None:
+    """out[r, :] = table[tokens[r], :]; tokens int32 on the device, table [vocab, hidden] bf16."""
+    check(lib().pa_embedding(_ptr(tokens), _ptr(table), _ptr(out), rows, int(table.shape[-1]), int(table.shape[-2]),
+                             stream))
+
+
+def model_weights(embed_tokens, attention: AttentionWeights, ffn_w: "FfnWeights", final_norm, w_lm,
+                  eps: float = 1e-5) -> "ModelWeights":
+    """Descriptor of a whole model for decode_token; keeps the two block descriptors alive."""
+    m = ModelWeights()
+    m.embed_tokens = _ptr(embed_tokens)
+    m.attention = C.pointer(attention)
+    m.ffn = C.pointer(ffn_w)
+    m.final_norm = _ptr(final_norm)
+    m.lm_head = _ptr(w_lm)
+    m.vocab = int(w_lm.shape[-1])
+    m.rms_eps = eps
+    m._keep = (attention, ffn_w)
+    return m
+
+
+def decode_token(pool: "KVPool", model: "ModelWeights", tokens_in, tokens_out, logits, cos, sin, scale: float = 0.125,
+                 chained: bool = False, stream: int = 0) -> None:
+    """One decode step of the whole model for the active batch: token ids (device int32) -> embedding ->
+    every layer's block -> final norm + language-model head -> greedy token ids (device int32)."""
+    check(lib().pa_decode_token(pool._h, C.byref(model), _ptr(tokens_in), _ptr(tokens_out), _ptr(logits), _ptr(cos),
+                                _ptr(sin), scale, int(chained), stream))
 
 
 def pack_projection_weights(w, stream: int = 0):

@@ -320,6 +320,8 @@ def ref():
         r.ref_gemm.restype = i
         r.ref_argmax.argtypes = [vp, vp]
         r.ref_argmax.restype = None
+        r.ref_embedding.argtypes = [vp, vp, vp, i]
+        r.ref_embedding.restype = None
         r.ref_silu_mul.argtypes = [vp, vp, vp, i]
         r.ref_silu_mul.restype = None
         r.ref_residual_add.argtypes = [vp, vp, vp, C.c_longlong]

@@ -17,6 +17,7 @@
 //                              FeedForward::forward choose them
 //   ref_silu_mul            -> launch_silu_mul            (src/kernels/silu/silu_8192.hpp)
 //   ref_argmax              -> launch_argmax              (src/kernels/sampling/argmax_128256.hpp)
+//   ref_embedding           -> launch_embedding           (src/kernels/embedding/embedding.hpp)
 //   ref_append_*            -> the append the reference performs inline in
 //                              Attention::forward (src/runtime/attention.cu:239-262):
 //                              2*8*tokens device-to-device copies of 128 bytes.
@@ -30,6 +31,7 @@
 #include "flashattention.h"
 #include "gemm_2048x2048.hpp"
 #include "argmax_128256.hpp"
+#include "embedding.hpp"
 #include "gemm_2048x128256.hpp"
 #include "gemm_2048x512.hpp"
 #include "gemm_2048x8192.hpp"
@@ -101,6 +103,11 @@ int ref_gemm(const void* A, const void* B, void* C, int M, int N, int K) {
 
 // token = argmax over the 128256 bf16 logits of one row (src/runtime/llama_runtime.cu:913-917).
 void ref_argmax(const void* logits, int* token) { launch_argmax((const __nv_bfloat16*)logits, token, 0); }
+
+// out[r, :] = table[tokens[r], :], rows of 2048 (src/runtime/llama_runtime.cu:846-851).
+void ref_embedding(const int* tokens, const void* table, void* out, int rows) {
+  launch_embedding(tokens, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, rows, 0);
+}
 
 // out = SiLU(gate) * up over rows x 8192 elements (src/runtime/ffn.cu:112-118).
 void ref_silu_mul(const void* gate, const void* up, void* out, int rows) {
