@@ -1,0 +1,203 @@
+// TEST INFRASTRUCTURE — not part of the product.
+//
+// The reference's whole decode step, run both ways on the same seeded model.  oracle/Makefile builds
+// this file into _ref/token_forward_ref with the reference's own runtime::Transformer
+// (src/runtime/transformer.cu, transformer_block.cu, attention.cu, ffn.cu, tensor.cu, compiled
+// unchanged, with all of the reference's kernels) and the calls its LlamaRuntime::decode_forward makes
+// around it (src/runtime/llama_runtime.cu:822-945: launch_embedding, Transformer::forward,
+// rmsnorm_launch<2048>, launch_gemm_2048x128256, launch_argmax — LlamaRuntime itself needs a
+// tokenizer and a weight file, so its body is restated here call for call).  The test builds the same
+// file with -DPA_SHIM against libpaged_attention.so: the same steps through pa_decode_token.
+//
+// Both programs fill the Llama-3.2-1B-shaped weights (3 GB) on the device from the same hash, start
+// with an empty cache and feed the same fixed token ids one per step (not the generated ones, so that
+// the two runs stay on the same inputs), and write per step the logits row (128256 bf16) and the
+// greedy token.
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <vector>
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#ifdef PA_SHIM
+#include "paged_attention.h"
+#else
+#include "argmax_128256.hpp"
+#include "embedding.hpp"
+#include "gemm_2048x128256.hpp"
+#include "rmsnorm.hpp"
+#include "transformer.hpp"
+#endif
+
+namespace {
+
+constexpr int kLayers = 16, kHidden = 2048, kInter = 8192, kVocab = 128256, kQ = 2048, kKv = 512;
+constexpr int kSteps = 6, kMaxSeq = 64;
+
+#define CK(call)                                                                        \
+  do {                                                                                  \
+    cudaError_t e_ = (call);                                                            \
+    if (e_ != cudaSuccess) {                                                            \
+      fprintf(stderr, "%s: %s (line %d)\n", #call, cudaGetErrorString(e_), __LINE__);   \
+      exit(2);                                                                          \
+    }                                                                                   \
+  } while (0)
+
+// element i of stream `seed`: offset + scale * u, u uniform in (-1, 1) from a 64-bit mix of (seed, i)
+__global__ void fill_kernel(__nv_bfloat16* p, size_t n, uint64_t seed, float scale, float offset) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    uint64_t z = seed * 0x9E3779B97F4A7C15ull + i + 1;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    const float u = (float)(z >> 40) / 8388608.0f - 1.0f;
+    p[i] = __float2bfloat16(offset + scale * u);
+  }
+}
+
+__nv_bfloat16* device_fill(size_t n, uint64_t seed, float scale, float offset) {
+  __nv_bfloat16* d = nullptr;
+  CK(cudaMalloc(&d, n * sizeof(__nv_bfloat16)));
+  fill_kernel<<<1184, 256>>>(d, n, seed, scale, offset);
+  CK(cudaGetLastError());
+  return d;
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  if (argc < 2) return 1;
+  CK(cudaSetDevice(0));
+  // per-kind buffers with the layers stacked, so that one layout serves both builds
+  __nv_bfloat16* in_norm = device_fill((size_t)kLayers * kHidden, 1, 0.1f, 1.0f);
+  __nv_bfloat16* wq = device_fill((size_t)kLayers * kHidden * kQ, 2, 0.05f, 0.f);
+  __nv_bfloat16* wk = device_fill((size_t)kLayers * kHidden * kKv, 3, 0.05f, 0.f);
+  __nv_bfloat16* wv = device_fill((size_t)kLayers * kHidden * kKv, 4, 0.05f, 0.f);
+  __nv_bfloat16* wo = device_fill((size_t)kLayers * kQ * kHidden, 5, 0.05f, 0.f);
+  __nv_bfloat16* post_norm = device_fill((size_t)kLayers * kHidden, 6, 0.1f, 1.0f);
+  __nv_bfloat16* wg = device_fill((size_t)kLayers * kHidden * kInter, 7, 0.05f, 0.f);
+  __nv_bfloat16* wu = device_fill((size_t)kLayers * kHidden * kInter, 8, 0.05f, 0.f);
+  __nv_bfloat16* wd = device_fill((size_t)kLayers * kInter * kHidden, 9, 0.025f, 0.f);
+  __nv_bfloat16* embed = device_fill((size_t)kVocab * kHidden, 10, 1.7f, 0.f);
+  __nv_bfloat16* final_norm = device_fill((size_t)kHidden, 11, 0.1f, 1.0f);
+  __nv_bfloat16* lm_head = device_fill((size_t)kHidden * kVocab, 12, 0.05f, 0.f);
+  CK(cudaDeviceSynchronize());
+
+  std::vector<float> hc((size_t)kMaxSeq * 32), hs((size_t)kMaxSeq * 32);
+  for (int p = 0; p < kMaxSeq; p++)
+    for (int i = 0; i < 32; i++) {
+      const float inv = 1.0f / powf(500000.0f, (float)(2 * i) / 64.0f);
+      hc[(size_t)p * 32 + i] = cosf((float)p * inv);
+      hs[(size_t)p * 32 + i] = sinf((float)p * inv);
+    }
+  float *cos_t = nullptr, *sin_t = nullptr;
+  CK(cudaMalloc(&cos_t, hc.size() * 4));
+  CK(cudaMalloc(&sin_t, hs.size() * 4));
+  CK(cudaMemcpy(cos_t, hc.data(), hc.size() * 4, cudaMemcpyHostToDevice));
+  CK(cudaMemcpy(sin_t, hs.data(), hs.size() * 4, cudaMemcpyHostToDevice));
+
+  const int fed[kSteps] = {128000, 9906, 1917, 0, 128255, 31415};  // ids across the table, the first and last rows too
+  int* d_tok = nullptr;
+  int* d_next = nullptr;
+  __nv_bfloat16* logits = nullptr;
+  CK(cudaMalloc(&d_tok, sizeof(int)));
+  CK(cudaMalloc(&d_next, sizeof(int)));
+  CK(cudaMalloc(&logits, (size_t)kVocab * sizeof(__nv_bfloat16)));
+  FILE* f = fopen(argv[1], "wb");
+  if (!f) return 3;
+  std::vector<__nv_bfloat16> h_logits(kVocab);
+
+#ifdef PA_SHIM
+  pa_pool* pool = nullptr;
+  if (pa_pool_create(&pool, 0, kLayers, 16, 8, 1, 8) != PA_OK) {
+    fprintf(stderr, "%s\n", pa_last_error());
+    return 4;
+  }
+  int seq = -1;
+  pa_seq_create(pool, &seq);
+  pa_attention_weights aw = {};
+  aw.input_norm = in_norm;
+  aw.wq = wq;
+  aw.wk = wk;
+  aw.wv = wv;
+  aw.wo = wo;
+  aw.norm_layer_stride = kHidden;
+  aw.wq_layer_stride = (int64_t)kHidden * kQ;
+  aw.wkv_layer_stride = (int64_t)kHidden * kKv;
+  aw.wo_layer_stride = (int64_t)kQ * kHidden;
+  aw.rms_eps = 1e-5f;
+  aw.hidden = kHidden;
+  pa_ffn_weights fw = {};
+  fw.ffn_norm = post_norm;
+  fw.gate = wg;
+  fw.up = wu;
+  fw.down = wd;
+  fw.norm_layer_stride = kHidden;
+  fw.gate_layer_stride = fw.up_layer_stride = fw.down_layer_stride = (int64_t)kHidden * kInter;
+  fw.rms_eps = 1e-5f;
+  fw.hidden = kHidden;
+  fw.inter = kInter;
+  pa_model_weights model = {embed, &aw, &fw, final_norm, lm_head, kVocab, 1e-5f};
+#else
+  llama::LlamaWeights weights;
+  for (int l = 0; l < kLayers; l++) {
+    auto& w = weights.layers[l];
+    w.input_layernorm = in_norm + (size_t)l * kHidden;
+    w.q_proj = wq + (size_t)l * kHidden * kQ;
+    w.k_proj = wk + (size_t)l * kHidden * kKv;
+    w.v_proj = wv + (size_t)l * kHidden * kKv;
+    w.o_proj = wo + (size_t)l * kQ * kHidden;
+    w.post_attention_layernorm = post_norm + (size_t)l * kHidden;
+    w.gate_proj = wg + (size_t)l * kHidden * kInter;
+    w.up_proj = wu + (size_t)l * kHidden * kInter;
+    w.down_proj = wd + (size_t)l * kInter * kHidden;
+  }
+  weights.embed_tokens = embed;
+  weights.final_norm = final_norm;
+  weights.lm_head = lm_head;
+  runtime::Transformer transformer(weights, cos_t, sin_t, kMaxSeq);
+  runtime::Tensor hidden_states({1, kHidden}), transformer_output({1, kHidden}), final_norm_output({1, kHidden});
+#endif
+
+  for (int step = 0; step < kSteps; step++) {
+    const int position = step;
+    CK(cudaMemcpy(d_tok, &fed[step], sizeof(int), cudaMemcpyHostToDevice));
+#ifdef PA_SHIM
+    const int one = 1;
+    int rc = pa_seq_reserve(pool, seq, position + 1);
+    if (rc == PA_OK) rc = pa_batch_set(pool, &seq, &one, 1, nullptr);
+    if (rc == PA_OK)
+      rc = pa_decode_token(pool, &model, d_tok, d_next, logits, cos_t, sin_t, 0.125f, 0, nullptr);
+    if (rc == PA_OK) rc = pa_pool_check(pool, nullptr);
+    if (rc != PA_OK) {
+      fprintf(stderr, "step %d: %s\n", step, pa_last_error());
+      return 5;
+    }
+#else
+    launch_embedding(d_tok, weights.embed_tokens, hidden_states.data_bf16(), 1);
+    cudaDeviceSynchronize();
+    transformer.forward(hidden_states, transformer_output, position, 1);
+    cudaDeviceSynchronize();
+    rmsnorm_launch<llama::HIDDEN_SIZE>(transformer_output.data_bf16(), weights.final_norm,
+                                       final_norm_output.data_bf16(), 1, 1e-5f);
+    cudaDeviceSynchronize();
+    launch_gemm_2048x128256(final_norm_output.data_bf16(), weights.lm_head, logits, 1, llama::VOCAB_SIZE,
+                            llama::HIDDEN_SIZE);
+    cudaDeviceSynchronize();
+    launch_argmax(logits, d_next, 0);
+#endif
+    CK(cudaDeviceSynchronize());
+    int next = -1;
+    CK(cudaMemcpy(&next, d_next, sizeof(int), cudaMemcpyDeviceToHost));
+    CK(cudaMemcpy(h_logits.data(), logits, (size_t)kVocab * sizeof(__nv_bfloat16), cudaMemcpyDeviceToHost));
+    fwrite(h_logits.data(), sizeof(__nv_bfloat16), kVocab, f);
+    fwrite(&next, sizeof(int), 1, f);
+    printf("step %d: fed %d -> %d\n", step, fed[step], next);
+  }
+  fclose(f);
+  CK(cudaGetLastError());
+  return 0;
+}
