@@ -10,7 +10,7 @@
 // file with -DPA_SHIM against libpaged_attention.so: the same steps through pa_decode_token.
 //
 // Both programs fill the Llama-3.2-1B-shaped weights (3 GB) on the device from the same hash, start
-// with an empty cache and feed the same fixed token ids one per step (not the generated ones, so that
+// with an empty cache and feed the same twelve fixed token ids one per step (not the generated ones, so that
 // the two runs stay on the same inputs), and write per step the logits row (128256 bf16) and the
 // greedy token.
 #include <cmath>
@@ -35,7 +35,7 @@
 namespace {
 
 constexpr int kLayers = 16, kHidden = 2048, kInter = 8192, kVocab = 128256, kQ = 2048, kKv = 512;
-constexpr int kSteps = 6, kMaxSeq = 64;
+constexpr int kSteps = 12, kMaxSeq = 64;
 
 #define CK(call)                                                                        \
   do {                                                                                  \
@@ -46,22 +46,25 @@ constexpr int kSteps = 6, kMaxSeq = 64;
     }                                                                                   \
   } while (0)
 
-// element i of stream `seed`: offset + scale * u, u uniform in (-1, 1) from a 64-bit mix of (seed, i)
-__global__ void fill_kernel(__nv_bfloat16* p, size_t n, uint64_t seed, float scale, float offset) {
+// element i of stream `seed`: offset + scale * u, u uniform in (-1, 1) from a 64-bit mix of (seed, i);
+// with hot_cols > 0 the matrix has hot_cols columns and every 64th of them is 16 times larger (a head
+// whose largest logits stand out, so that the greedy token is not decided by the last bit)
+__global__ void fill_kernel(__nv_bfloat16* p, size_t n, uint64_t seed, float scale, float offset, int hot_cols) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     uint64_t z = seed * 0x9E3779B97F4A7C15ull + i + 1;
     z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
     z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
     z ^= z >> 31;
     const float u = (float)(z >> 40) / 8388608.0f - 1.0f;
-    p[i] = __float2bfloat16(offset + scale * u);
+    const float hot = hot_cols > 0 && (i % (size_t)hot_cols) % 64 == 0 ? 16.0f : 1.0f;
+    p[i] = __float2bfloat16(offset + hot * scale * u);
   }
 }
 
-__nv_bfloat16* device_fill(size_t n, uint64_t seed, float scale, float offset) {
+__nv_bfloat16* device_fill(size_t n, uint64_t seed, float scale, float offset, int hot_cols = 0) {
   __nv_bfloat16* d = nullptr;
   CK(cudaMalloc(&d, n * sizeof(__nv_bfloat16)));
-  fill_kernel<<<1184, 256>>>(d, n, seed, scale, offset);
+  fill_kernel<<<1184, 256>>>(d, n, seed, scale, offset, hot_cols);
   CK(cudaGetLastError());
   return d;
 }
@@ -83,7 +86,7 @@ int main(int argc, char** argv) {
   __nv_bfloat16* wd = device_fill((size_t)kLayers * kInter * kHidden, 9, 0.025f, 0.f);
   __nv_bfloat16* embed = device_fill((size_t)kVocab * kHidden, 10, 1.7f, 0.f);
   __nv_bfloat16* final_norm = device_fill((size_t)kHidden, 11, 0.1f, 1.0f);
-  __nv_bfloat16* lm_head = device_fill((size_t)kHidden * kVocab, 12, 0.05f, 0.f);
+  __nv_bfloat16* lm_head = device_fill((size_t)kHidden * kVocab, 12, 0.01f, 0.f, kVocab);
   CK(cudaDeviceSynchronize());
 
   std::vector<float> hc((size_t)kMaxSeq * 32), hs((size_t)kMaxSeq * 32);
@@ -99,7 +102,7 @@ int main(int argc, char** argv) {
   CK(cudaMemcpy(cos_t, hc.data(), hc.size() * 4, cudaMemcpyHostToDevice));
   CK(cudaMemcpy(sin_t, hs.data(), hs.size() * 4, cudaMemcpyHostToDevice));
 
-  const int fed[kSteps] = {128000, 9906, 1917, 0, 128255, 31415};  // ids across the table, the first and last rows too
+  const int fed[kSteps] = {128000, 9906, 1917, 0, 128255, 31415, 27182, 8128, 496, 65536, 100000, 7};  // ids across the table, the first and last rows too
   int* d_tok = nullptr;
   int* d_next = nullptr;
   __nv_bfloat16* logits = nullptr;

@@ -125,7 +125,7 @@ def test_drop_in_feed_forward_class_equals_reference_feed_forward(cuda, tmp_path
 def test_whole_decode_step_equals_the_reference_transformer(cuda, tmp_path):
     """pa_decode_token against the reference's own runtime::Transformer (16 blocks of its Attention and
     FeedForward classes, compiled unchanged, with its kernels) wrapped in the calls of
-    LlamaRuntime::decode_forward: the same seeded Llama-3.2-1B-shaped model, an empty cache, six steps on
+    LlamaRuntime::decode_forward: the same seeded Llama-3.2-1B-shaped model, an empty cache, twelve steps on
     the same fed ids (oracle/token_driver.cu, built here against the product with -DPA_SHIM).  Per step the
     logits rows must agree within 2^-4 of the row's largest magnitude (bf16 roundings in another summation
     order, carried through 16 blocks) and the greedy token must be the same wherever the reference's two
@@ -140,7 +140,7 @@ def test_whole_decode_step_equals_the_reference_transformer(cuda, tmp_path):
                         "-Xlinker", "-rpath", "-Xlinker", os.path.join(repo, "llama_transformer_runtime_b200")],
                        capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stderr[-3000:]
-    vocab, steps = 128256, 6
+    vocab, steps = 128256, 12
     rec = np.dtype([("logits", np.uint16, (vocab,)), ("token", np.int32)])
     outs = {}
     for name, cmd in (("shim", str(exe)), ("ref", os.path.join(REF_DIR, "token_forward_ref"))):
@@ -149,7 +149,7 @@ def test_whole_decode_step_equals_the_reference_transformer(cuda, tmp_path):
         assert r.returncode == 0, name + ": " + r.stdout[-2000:] + r.stderr[-2000:]
         outs[name] = np.fromfile(path, dtype=rec)
         assert outs[name].shape == (steps,)
-    agree = 0
+    agree, report = 0, []
     for s in range(steps):
         g = orc.bf16_to_f32(outs["shim"]["logits"][s]).astype(np.float64)
         w = orc.bf16_to_f32(outs["ref"]["logits"][s]).astype(np.float64)
@@ -161,7 +161,9 @@ def test_whole_decode_step_equals_the_reference_transformer(cuda, tmp_path):
         assert int(outs["shim"]["token"][s]) == int(orc.argmax_reference_rule(outs["shim"]["logits"][s:s + 1])[0])
         assert int(outs["ref"]["token"][s]) == int(orc.argmax_reference_rule(outs["ref"]["logits"][s:s + 1])[0])
         top2 = np.partition(w, -2)[-2:]
+        report.append((s, err / scale, (top2[1] - top2[0]) / scale, int(outs["shim"]["token"][s]), int(outs["ref"]["token"][s])))
         if top2[1] - top2[0] > 2 * err:
             assert int(outs["shim"]["token"][s]) == int(outs["ref"]["token"][s]), f"step {s}"
             agree += 1
-    assert agree >= steps // 2, "too few steps with a clear winner to compare tokens"
+    print("step, max error / row max, (largest - second) / row max, token here, token of the reference:", report)
+    assert agree >= steps // 3, f"too few steps with a clear winner to compare tokens: {report}"
