@@ -167,6 +167,35 @@ int caller(__nv_bfloat16* q, __nv_bfloat16* k, __nv_bfloat16* v, float* c, float
     assert r.returncode == 0, r.stderr
 
 
+def test_drop_in_class_headers_compile(tmp_path):
+    """A translation unit that builds the reference's per-layer objects and its Transformer from a
+    llama::LlamaWeights (src/runtime/transformer.cu:6-40) compiles against include/attention.hpp, ffn.hpp,
+    weights.hpp and transformer.hpp (raw device pointers where the reference passes its Tensor)."""
+    import subprocess
+    src = tmp_path / "model_caller.cu"
+    src.write_text("""
+#include "attention.hpp"
+#include "ffn.hpp"
+#include "transformer.hpp"
+int caller(llama::LlamaWeights& weights, float* cos_table, float* sin_table, __nv_bfloat16* in, __nv_bfloat16* out) {
+  static_assert(llama::NUM_LAYERS == 16 && llama::VOCAB_SIZE == 128256, "model constants");
+  runtime::Attention attention(weights.layers[0].input_layernorm, weights.layers[0].q_proj, weights.layers[0].k_proj,
+                               weights.layers[0].v_proj, weights.layers[0].o_proj, cos_table, sin_table, 128, 0);
+  runtime::FeedForward ffn(weights.layers[0].post_attention_layernorm, weights.layers[0].gate_proj,
+                           weights.layers[0].up_proj, weights.layers[0].down_proj);
+  attention.forward(in, out, 0, 1);
+  ffn.forward(in, out, 1);
+  runtime::Transformer transformer(weights, cos_table, sin_table, 128);
+  transformer.forward(in, out, 0, 1);
+  return transformer.get_key_cache(3) != nullptr && transformer.get_value_cache(15) != nullptr;
+}
+""")
+    r = subprocess.run(["nvcc", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I",
+                        os.path.join(ROOT, "include"), "-c", str(src), "-o", str(tmp_path / "model_caller.o")],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+
+
 def test_projection_entries_validate_before_touching_a_device():
     """Argument checks of the projection entries run on the host, before any CUDA call: they must
     answer with a status and a message, never crash, with no GPU present."""
