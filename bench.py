@@ -1848,6 +1848,188 @@ def run_lm_head(env: Env, args, sub: bool = False):
 
 
 # =============================================================================
+# a whole prompt through the 16 blocks (the prompt path of runtime::Transformer)
+# =============================================================================
+def run_prompt(env: Env, args, sub: bool = False):
+    """A 2048-token prompt through 16 transformer blocks, as Transformer::forward runs it for
+    seq_len > 1 (src/runtime/transformer.cu:47-89, transformer_block.cu:24-123): per layer RMSNorm,
+    Q/K/V projections + RoPE + cache append, causal attention, output projection + residual, RMSNorm,
+    gate/up projections, SiLU(gate) * up, down projection + residual.  Ours: pa_rmsnorm,
+    pa_qkv_project_append, pa_prefill, pa_out_project_rows, pa_ffn_rows (9 launches per layer, the
+    GEMMs on tcgen05).  Reference arm: the reference's kernels in the order of its classes, with their
+    synchronisations.  Metric: TFLOP/s over 2*tokens*(weights of the layer) + the causal attention."""
+    torch = env.torch
+    if env.rank != 0:
+        return None  # independent replicas only
+    from oracle import oracle as orc
+    dev = env.dev
+    S, H, NQ, NKV, INTER = PREFILL_TOKENS, HIDDEN, Q_HEADS * D, KV_HEADS * D, 8192
+    steps = max(3, args.steps // 5) if sub else args.steps
+    warmup = 3 if sub else args.warmup
+    ref_arm = args.impl == "reference" and not sub
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(77)
+    mk = lambda *shape, s=0.03: (torch.randn(*shape, generator=gen, device=dev) * s).to(torch.bfloat16)
+    W = dict(nw=mk(LAYERS, H, s=0.7), wq=mk(LAYERS, H, NQ), wk=mk(LAYERS, H, NKV), wv=mk(LAYERS, H, NKV), wo=mk(LAYERS, NQ, H),
+             fn=mk(LAYERS, H, s=0.7), wg=mk(LAYERS, H, INTER), wu=mk(LAYERS, H, INTER), wd=mk(LAYERS, INTER, H, s=0.02))
+    x_host = torch.randn(S, H, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16).pin_memory()
+    x_dev = x_host.to(dev)
+    y_dev = torch.zeros(S, H, dtype=torch.bfloat16, device=dev)
+    y_host = torch.zeros(1, H, dtype=torch.bfloat16).pin_memory()  # the last row is what the head reads
+    flops_layer = 2.0 * S * (H * (NQ + 2 * NKV) + NQ * H + 3 * H * INTER) + prefill_flops(S)
+    burst, sustained, kind = measured_tflops()
+    ref = orc.ref() if orc.ref_available() else None
+    if ref_arm and ref is None:
+        return {"impl": "reference", "unavailable": "oracle/_ref/libref.so was not built"}
+    cos_h, sin_h = orc.build_rope_tables(S)
+    cos, sin = torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev)
+    rows = lambda c: torch.zeros(S, c, dtype=torch.bfloat16, device=dev)
+
+    if ref is not None and (ref_arm or sub):
+        rb = {n: rows(c) for n, c in (("xn", H), ("q", NQ), ("k", NKV), ("v", NKV), ("arow", NQ), ("lin", H), ("xa", H),
+                                       ("xb", H), ("xm", H), ("g", INTER), ("u", INTER), ("h", INTER))}
+        qf = torch.empty(Q_HEADS, S, D, dtype=torch.bfloat16, device=dev)
+        kf = torch.empty(KV_HEADS, S, D, dtype=torch.bfloat16, device=dev)
+        vf = torch.empty_like(kf)
+        of = torch.empty_like(qf)
+        kc = torch.zeros(LAYERS, KV_HEADS, S, D, dtype=torch.bfloat16, device=dev)
+        vc = torch.zeros_like(kc)
+
+        def ref_step():
+            cur = x_dev
+            for l in range(LAYERS):
+                ref.ref_rmsnorm(cur.data_ptr(), W["nw"][l].data_ptr(), rb["xn"].data_ptr(), S, 1e-5)
+                torch.cuda.synchronize()
+                for wm, o, n in ((W["wq"], rb["q"], NQ), (W["wk"], rb["k"], NKV), (W["wv"], rb["v"], NKV)):
+                    ref.ref_gemm(rb["xn"].data_ptr(), wm[l].data_ptr(), o.data_ptr(), S, n, H)
+                    torch.cuda.synchronize()
+                ref.ref_rope_qkv(rb["q"].data_ptr(), qf.data_ptr(), rb["k"].data_ptr(), kf.data_ptr(), rb["v"].data_ptr(),
+                                 vf.data_ptr(), cos.data_ptr(), sin.data_ptr(), S, 0)
+                ref.ref_append_strided(kc[l].data_ptr(), vc[l].data_ptr(), kf.data_ptr(), vf.data_ptr(), S, 0, S, None)
+                ref.ref_flash_attention(qf.data_ptr(), kc[l].data_ptr(), vc[l].data_ptr(), of.data_ptr(), None, 1,
+                                        Q_HEADS, KV_HEADS, S, S, S, 0.125, 1, None)
+                torch.cuda.synchronize()
+                ref.ref_flash_output_layout(of.data_ptr(), rb["arow"].data_ptr(), S)
+                torch.cuda.synchronize()
+                ref.ref_gemm(rb["arow"].data_ptr(), W["wo"][l].data_ptr(), rb["lin"].data_ptr(), S, H, NQ)
+                torch.cuda.synchronize()
+                ref.ref_residual_add(cur.data_ptr(), rb["lin"].data_ptr(), rb["xm"].data_ptr(), S * H)
+                torch.cuda.synchronize()
+                ref.ref_rmsnorm(rb["xm"].data_ptr(), W["fn"][l].data_ptr(), rb["xn"].data_ptr(), S, 1e-5)
+                ref.ref_gemm(rb["xn"].data_ptr(), W["wg"][l].data_ptr(), rb["g"].data_ptr(), S, INTER, H)
+                ref.ref_gemm(rb["xn"].data_ptr(), W["wu"][l].data_ptr(), rb["u"].data_ptr(), S, INTER, H)
+                ref.ref_silu_mul(rb["g"].data_ptr(), rb["u"].data_ptr(), rb["h"].data_ptr(), S)
+                ref.ref_gemm(rb["h"].data_ptr(), W["wd"][l].data_ptr(), rb["lin"].data_ptr(), S, H, INTER)
+                torch.cuda.synchronize()
+                nxt = rb["xa"] if l % 2 == 0 else rb["xb"]
+                ref.ref_residual_add(rb["xm"].data_ptr(), rb["lin"].data_ptr(), nxt.data_ptr(), S * H)
+                torch.cuda.synchronize()
+                cur = nxt
+            y_dev.copy_(cur)
+
+    pool = None
+    if not ref_arm:
+        from llama_transformer_runtime_b200 import paged
+        nb = (S + BLOCK - 1) // BLOCK
+        num_blocks = nb + nb // 4 + 8
+        pool = paged.KVPool(LAYERS, num_blocks, KV_HEADS, 1, nb + 1, device=env.local_rank)
+        pool.set_free_order(np.random.default_rng(5).permutation(num_blocks))
+        seq = pool.create_seq()
+        pool.reserve(seq, S)
+        pool.batch_set([seq], [S])
+        P = {n: paged.pack_projection_weights(W[n]) for n in ("wq", "wk", "wv", "wo", "wg", "wu", "wd")}
+        F = paged.ffn_weights(W["fn"], P["wg"], P["wu"], P["wd"])
+        xn, q_rot, attn, mid = rows(H), rows(NQ), rows(NQ), rows(H)
+        pp = [rows(H), rows(H)]
+        scratch = torch.zeros(S * (H + 2 * INTER), dtype=torch.bfloat16, device=dev)
+        torch.cuda.synchronize()
+
+        def ours_step(last=None):
+            # the same prompt positions are rewritten every step (the table is fixed)
+            cur = x_dev
+            for l in range(LAYERS if last is None else last):
+                out = y_dev if l == LAYERS - 1 else pp[l & 1]
+                paged.rmsnorm(cur, W["nw"][l], xn, S, H)
+                pool.qkv_project_append(l, xn, P["wq"][l], P["wk"][l], P["wv"][l], cos, sin, q_rot, H)
+                pool.prefill(l, q_rot, attn)
+                pool.out_project_rows(attn, P["wo"][l], cur, mid, S, H)
+                paged.ffn_rows(pool, F, l, mid, scratch, out, S, add_residual=True)
+                cur = out
+            return cur
+
+    step = ref_step if ref_arm else ours_step
+
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        step()
+        y_host.copy_(y_dev[S - 1:S], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    m0 = env.sampler.mark()
+    for _ in range(warmup):
+        step()
+    ms = local_timed(torch, step, steps) / steps
+    ms_e2e = local_timed(torch, e2e_step, steps) / steps
+    m1 = env.sampler.mark()
+    value = flops_layer * LAYERS / (ms * 1e-3) / 1e12
+    line = {
+        "metric": "prompt_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "us_per_layer": round(ms * 1e3 / LAYERS, 2), "tokens_per_s": round(S / (ms * 1e-3), 1),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"prompt_{S}tokens_x{LAYERS}blocks", "tokens": S, "hidden": H, "inter": INTER, "layers": LAYERS,
+                   "flops": "per layer 2*tokens*(Wq+Wk+Wv+Wo+Wgate+Wup+Wdown elements) + 4*32*64*S(S+1)/2",
+                   "l2": "per-layer weights are distinct tensors (122 MB per layer)"},
+        "e2e": {"value": round(flops_layer * LAYERS / (ms_e2e * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2,
+                "ms_per_step": round(ms_e2e, 4)},
+        "gpu_launches": (LAYERS * 19 if ref_arm else LAYERS * 9) * steps, "clocks": env.sampler.summary(m0, m1),
+    }
+    if ref_arm:
+        line["impl"] = "reference"
+        line["cpu_baseline"] = {"value": line["value"], "unit": "TFLOP/s", "cores": 0, "kind": "reference",
+                                "sample": "whole workload on the GPU: the reference has no CPU implementation of this path"}
+        line["e2e"].update({"h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0, "value": line["value"]})
+        return line
+    line["roofline"] = {"bound": "tensor", "kernel": "qkv_gemm_kernel (7 of the 9 launches of a layer) + prefill_kernel",
+                        "achieved": round(value, 2), "peak": burst, "unit": "TFLOP/s", "frac": round(value / burst, 4),
+                        "peak_source": f"of {kind} (cuBLAS bf16 burst)", "us_per_launch": round(ms * 1e3 / LAYERS / 9, 2),
+                        "flops_per_launch": flops_layer / 9, "traffic": None}
+    pool.check()
+    # check and CPU baseline: the first block's output rows 0..31 against the oracle chain on the same input
+    # (causal: these rows attend to themselves only)
+    r = 32
+    first = ours_step(last=1)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    xs = _u16(x_host[:r])
+    xn_o = orc.rmsnorm(xs, _u16(W["nw"][0]), 1e-5)
+    q = orc.gemm_bf16(xn_o, _u16(W["wq"][0])).reshape(r, Q_HEADS, D)
+    k = orc.gemm_bf16(xn_o, _u16(W["wk"][0])).reshape(r, KV_HEADS, D)
+    v = orc.gemm_bf16(xn_o, _u16(W["wv"][0])).reshape(r, KV_HEADS, D)
+    K = orc.rope(k, cos_h, sin_h, 0, 1)  # [heads, rows, 64]
+    V = np.ascontiguousarray(v.transpose(1, 0, 2))
+    O, _ = orc.attention(orc.rope(q, cos_h, sin_h, 0, 1), K, V, r)
+    lin = orc.gemm_bf16(orc.f32_to_bf16(O.transpose(1, 0, 2).reshape(r, NQ)), _u16(W["wo"][0]))
+    a = orc.f32_to_bf16(orc.bf16_to_f32(xs) + orc.bf16_to_f32(lin))
+    want = orc.ffn(a, _u16(W["fn"][0]), _u16(W["wg"][0]), _u16(W["wu"][0]), _u16(W["wd"][0]), 1e-5, True)
+    dt = time.perf_counter() - t0
+    err = row_rel_err(orc.bf16_to_f32(_u16(first[:r])), orc.bf16_to_f32(want), row=H)
+    line["checks"] = {"oracle_block0_rows0_31_max_err_over_row_max": err, "oracle_block0_ok": bool(err <= 2.0 ** -5)}
+    line["cpu_baseline"] = {"value": round(2.0 * r * (H * (NQ + 2 * NKV) + NQ * H + 3 * H * INTER) / dt / 1e12, 5), "unit": "TFLOP/s",
+                            "cores": orc.num_threads(), "kind": "port",
+                            "sample": f"{r} rows through block 0 with the CPU oracle chain, {dt:.2f} s"}
+    if sub and ref is not None:
+        ref_step()
+        rms = local_timed(torch, ref_step, 1)
+        line["reference"] = {"value": round(flops_layer * LAYERS / (rms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+                             "us_per_layer": round(rms * 1e3 / LAYERS, 2), "tokens_per_s": round(S / (rms * 1e-3), 1),
+                             "how": "the reference's RMSNorm, GEMM, RoPE, append, attention, layout, residual and SiLU kernels "
+                                    "in the order of its Attention, FeedForward and TransformerBlock classes, with their synchronisations"}
+    pool.close()
+    return line
+
+
+# =============================================================================
 def decode4k_sub(env: Env, args):
     line = run_decode(env, args, "decode4k", sub=True)
     r = reference_decode(env, "decode4k", 3, 2, with_e2e=False)
@@ -1870,6 +2052,7 @@ SUB_BLOCKS = {
     "block_chain": lambda env, a: run_chain(env, a, sub=True, ffn=True),
     "lm_head": lambda env, a: run_lm_head(env, a, sub=True),
     "token": lambda env, a: run_chain(env, a, sub=True, token=True),
+    "prompt": lambda env, a: run_prompt(env, a, sub=True),
 }
 
 
@@ -1890,7 +2073,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode128k",
                     choices=sorted(WORKLOADS) + ["prefill2k", "append2k", "batch64", "qkv_decode", "out_project", "qkv_prefill",
-                                                  "decode_chain", "block_chain", "lm_head", "token"])
+                                                  "decode_chain", "block_chain", "lm_head", "token", "prompt"])
     ap.add_argument("--chain-ctx", type=int, default=4096, help="decode_chain: context length")
     ap.add_argument("--no-sub", action="store_true", help="default workload: skip the sub-blocks")
     ap.add_argument("--sub", default="", help="default workload: comma-separated sub-blocks to run (default: all)")
@@ -1961,6 +2144,8 @@ def main():
         line = run_lm_head(env, args)
     elif args.workload == "token":
         line = run_chain(env, args, token=True)
+    elif args.workload == "prompt":
+        line = run_prompt(env, args)
     if rank == 0 and line is not None:
         print(json.dumps(line), flush=True)
     env.sampler.stop()

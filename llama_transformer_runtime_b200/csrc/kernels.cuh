@@ -192,6 +192,7 @@ struct QkvGemmParams {
   // [rows, q_cols] rows; no RoPE, no cache, the batch and table fields are unused
   int linear = 0;
   const __nv_bfloat16* residual = nullptr;  // [rows, q_cols], nullable
+  int tile_heads = 0;  // heads per pair tile, 4 or 6; 0: the launcher chooses
 };
 cudaError_t launch_qkv_gemm(const QkvGemmParams& p, cudaStream_t stream);
 // out = bf16(SiLU(gate) * up) over `elements` (a multiple of 8) bf16 values; out may alias gate or up

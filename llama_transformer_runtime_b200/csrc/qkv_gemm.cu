@@ -59,7 +59,7 @@ namespace pa {
 namespace {
 
 constexpr int kGM = 128;        // tokens per CTA = per packed activation tile; the pair's MMA has M = 256
-constexpr int kTileHeads = 6;   // heads (64 output columns) per pair tile: 4 in the first MMA, 2 in the second
+constexpr int kTileHeads = 6;   // most heads (64 output columns) per pair tile: 4 in the first MMA, 2 in the second
 constexpr int kGK = 64;         // k per stage
 constexpr int kGStages = 4;  // 3 and 5 stages run the MMA loop at the same pace
 constexpr int kABytes = kGM * 128;            // 16 KiB
@@ -113,8 +113,8 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap x_map, QkvGemmParams p) {
   const int m0 = tile_m * kGM;
   const bool have_rows = m0 < p.rows;  // the last pair may have one row half only: the peer then loads no A
   const int total_heads = p.linear ? p.q_cols / 64 : (p.q_cols + 2 * p.kv_cols) / 64;
-  const int g0 = (int)(blockIdx.x >> 1) * kTileHeads;
-  const int n_heads = min(kTileHeads, total_heads - g0);  // 2, 4 or 6
+  const int g0 = (int)(blockIdx.x >> 1) * p.tile_heads;
+  const int n_heads = min(p.tile_heads, total_heads - g0);  // 2, 4 or 6
   const int n1 = min(n_heads, 4);                          // heads of the first MMA
   const int k_steps = p.hidden / kGK;
   // head blocks this CTA loads: slots 0 .. n1/2-1 = its half of the first MMA's heads,
@@ -460,7 +460,22 @@ cudaError_t launch_qkv_gemm(const QkvGemmParams& p, cudaStream_t stream) {
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return cudaErrorInvalidValue;
   // x: the two CTAs of a pair (the kernel's compile-time cluster) next to each other
-  const dim3 grid(2 * ((total_heads + kTileHeads - 1) / kTileHeads), (p.rows + 2 * kGM - 1) / (2 * kGM));
+  // Tile width: 6 heads per pair, or 4 where that fills the SMs better (2048 columns are 5 1/3 tiles of
+  // 6 heads = 96 CTAs for 2048 rows, but 8 tiles of 4 = 128 CTAs of two thirds the work).  Cost of a
+  // choice = waves x (heads per tile + 2, the activation tile's share of a step).
+  QkvGemmParams q = p;
+  const int row_pairs = (p.rows + 2 * kGM - 1) / (2 * kGM);
+  if (q.tile_heads != 4 && q.tile_heads != kTileHeads) {
+    int sms = 148;
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    auto cost = [&](int th) {
+      const long long ctas = 2LL * ((total_heads + th - 1) / th) * row_pairs;
+      return ((ctas + sms - 1) / sms) * (th + 2);
+    };
+    q.tile_heads = cost(4) < cost(kTileHeads) ? 4 : kTileHeads;
+  }
+  const dim3 grid(2 * ((total_heads + q.tile_heads - 1) / q.tile_heads), row_pairs);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(kGemmThreads);
@@ -471,7 +486,7 @@ cudaError_t launch_qkv_gemm(const QkvGemmParams& p, cudaStream_t stream) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, qkv_gemm_kernel, x_map, p);
+  return cudaLaunchKernelEx(&cfg, qkv_gemm_kernel, x_map, q);
 }
 
 }  // namespace pa
