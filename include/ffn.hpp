@@ -7,8 +7,8 @@
 // What forward() runs:
 //   seq_len <= 8   pa_ffn: RMSNorm + gate and up projections + SiLU(gate) * up in one weight-streaming
 //                  launch, the down projection in a second one; no per-call allocation.
-//   seq_len  > 8   pa_ffn_rows: RMSNorm kernel, three tensor-core GEMM launches on packed copies of
-//                  the weights, one SiLU * up kernel.  The packed copies (100 MB) and the scratch rows
+//   seq_len  > 8   pa_ffn_rows: RMSNorm kernel, two tensor-core GEMM launches on packed copies of
+//                  the weights (gate and up as one, SiLU * up in its epilogue; down).  The packed copies (100 MB) and the scratch rows
 //                  are made on the first such call and kept; call reserve(max_rows) at set-up to keep
 //                  forward() free of allocations.
 // Like the reference's forward() it writes FeedForward(input) WITHOUT the residual (the block adds
@@ -76,7 +76,7 @@ class FeedForward {
     if (max_rows > scratch_rows_) {
       cuda(cudaDeviceSynchronize());
       cudaFree(scratch_);
-      cuda(cudaMalloc(&scratch_, (size_t)max_rows * (kHidden + 2 * kInter) * sizeof(__nv_bfloat16)));
+      cuda(cudaMalloc(&scratch_, (size_t)max_rows * (kHidden + kInter) * sizeof(__nv_bfloat16)));
       scratch_rows_ = max_rows;
     }
   }

@@ -362,11 +362,12 @@ typedef struct pa_ffn_weights {
 } pa_ffn_weights;
 int pa_ffn(const pa_ffn_weights* weights, int layer, const void* x, void* h_scratch, void* out, int rows,
            int add_residual, void* stream);
-/* The same block for prompt chunks (any number of rows) on the tensor cores: RMSNorm kernel, the
- * projection GEMM of pa_qkv_project_append in its plain form for gate, up and down (+ residual),
- * one element-wise SiLU(gate) * up kernel in between.  gate, up and down of `weights` are PACKED by
+/* The same block for prompt chunks (any number of rows) on the tensor cores: RMSNorm kernel, then
+ * two launches of the projection GEMM of pa_qkv_project_append: gate and up as ONE GEMM whose tiles
+ * hold a gate head and the up head of the same columns, with SiLU(gate) * up as the epilogue, and
+ * the down projection (+ residual).  gate, up and down of `weights` are PACKED by
  * pa_pack_projection_weights (hidden x inter, hidden x inter, inter x hidden); ffn_norm is plain.
- * scratch: rows * (hidden + 2 * inter) bf16, 16-byte aligned; x 16-byte aligned; out must not alias x. */
+ * scratch: rows * (hidden + inter) bf16, 16-byte aligned; x 16-byte aligned; out must not alias x. */
 int pa_ffn_rows(pa_pool* pool, const pa_ffn_weights* weights, int layer, const void* x, void* scratch, void* out,
                 int rows, int add_residual, void* stream);
 /* One decode step through whole transformer blocks of layers [layer_begin, layer_end), as

@@ -118,7 +118,7 @@ class Transformer {
       cuda(cudaDeviceSynchronize());
       cudaFree(rows_);
       // normalised rows, rotated q, attention rows, block middle rows, two block outputs in turn, FFN scratch
-      cuda(cudaMalloc(&rows_, (size_t)max_rows * (6 * kHidden + kHidden + 2 * kInter) * sizeof(__nv_bfloat16)));
+      cuda(cudaMalloc(&rows_, (size_t)max_rows * (6 * kHidden + kHidden + kInter) * sizeof(__nv_bfloat16)));
       rows_cap_ = max_rows;
     }
   }

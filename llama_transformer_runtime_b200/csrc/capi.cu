@@ -1257,8 +1257,7 @@ int pa_ffn_rows(pa_pool* p, const pa_ffn_weights* w, int layer, const void* x, v
     return fail(PA_ERR_INVALID_ARG, "pa_ffn_rows: x and scratch must be 16-byte aligned");
   DeviceGuard g(p->device);
   __nv_bfloat16* xn = (__nv_bfloat16*)scratch;
-  __nv_bfloat16* gate = xn + (size_t)rows * hidden;
-  __nv_bfloat16* up = gate + (size_t)rows * inter;
+  __nv_bfloat16* gate = xn + (size_t)rows * hidden;  // the activated rows [rows, inter]
   const __nv_bfloat16* in = (const __nv_bfloat16*)x;
   if (w->ffn_norm) {
     const int r = pa_rmsnorm(x, (const __nv_bfloat16*)w->ffn_norm + (size_t)layer * w->norm_layer_stride, xn, rows, hidden,
@@ -1266,13 +1265,22 @@ int pa_ffn_rows(pa_pool* p, const pa_ffn_weights* w, int layer, const void* x, v
     if (r != PA_OK) return r;
     in = xn;
   }
-  int r = linear_rows(p, in, (const __nv_bfloat16*)w->gate + (size_t)layer * w->gate_layer_stride, nullptr, gate, rows,
-                      hidden, inter, stream);
-  if (r != PA_OK) return r;
-  r = linear_rows(p, in, (const __nv_bfloat16*)w->up + (size_t)layer * w->up_layer_stride, nullptr, up, rows, hidden,
-                  inter, stream);
-  if (r != PA_OK) return r;
-  PA_CUDA(pa::launch_silu_mul(gate, up, gate, (size_t)rows * inter, (cudaStream_t)stream));
+  // gate and up as one GEMM whose epilogue is SiLU(gate) * up: its tiles hold a gate head and the up
+  // head of the same columns side by side
+  {
+    pa::QkvGemmParams a = {};
+    a.x = in;
+    a.wq = (const __nv_bfloat16*)w->gate + (size_t)layer * w->gate_layer_stride;
+    a.wk = a.wv = (const __nv_bfloat16*)w->up + (size_t)layer * w->up_layer_stride;
+    a.q_out = gate;
+    a.status = p->d_status;
+    a.rows = rows;
+    a.hidden = hidden;
+    a.q_cols = 2 * inter;
+    a.kv_cols = 256;
+    a.linear = 2;
+    PA_CUDA(pa::launch_qkv_gemm(a, (cudaStream_t)stream));
+  }
   return linear_rows(p, gate, (const __nv_bfloat16*)w->down + (size_t)layer * w->down_layer_stride,
                      add_residual ? x : nullptr, out, rows, inter, hidden, stream);
 }

@@ -352,26 +352,6 @@ __global__ void __cluster_dims__(kDownSplit, 1, 1) __launch_bounds__(kThreads, 2
   cluster_sync_all();  // the peers' shared memory stays until the first CTA has read it
 }
 
-// h = bf16(SiLU(gate) * up), element-wise over bf16 rows, 8 elements per thread (the prompt-chunk
-// path, where gate and up come out of two GEMM launches).
-__global__ void __launch_bounds__(256) silu_mul_kernel(const uint4* gate, const uint4* up, uint4* out, size_t chunks) {
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < chunks; i += (size_t)gridDim.x * blockDim.x) {
-    const uint4 g = gate[i], u = up[i];
-    float gf[8], uf[8];
-    unpack8(g, gf);
-    unpack8(u, uf);
-    uint4 o;
-    __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-      const float s0 = __fmul_rn(gf[2 * j], 1.0f / (1.0f + __expf(-gf[2 * j])));
-      const float s1 = __fmul_rn(gf[2 * j + 1], 1.0f / (1.0f + __expf(-gf[2 * j + 1])));
-      ob[j] = __floats2bfloat162_rn(__fmul_rn(s0, uf[2 * j]), __fmul_rn(s1, uf[2 * j + 1]));
-    }
-    out[i] = o;
-  }
-}
-
 template <typename K>
 cudaError_t launch(K kern, int ctas, int groups, const FfnParams& p, cudaStream_t st) {
   if (!p.pdl) {
@@ -444,15 +424,6 @@ int ffn_impl(const void* x, const void* norm_w, float eps, const void* wg, const
   }
   if (e != cudaSuccess) return ffail(PA_ERR_CUDA, cudaGetErrorString(e));
   return PA_OK;
-}
-
-cudaError_t launch_silu_mul(const void* gate, const void* up, void* out, size_t elements, cudaStream_t stream) {
-  const size_t chunks = elements / 8;
-  if (chunks == 0) return cudaSuccess;
-  size_t blocks = (chunks + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  silu_mul_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const uint4*)gate, (const uint4*)up, (uint4*)out, chunks);
-  return cudaGetLastError();
 }
 
 }  // namespace pa

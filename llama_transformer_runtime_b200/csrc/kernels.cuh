@@ -188,15 +188,15 @@ struct QkvGemmParams {
   const float* sin_table;
   int* status;
   int rows, hidden, q_cols, kv_cols, kv_heads, n_seqs, num_blocks, max_blocks_per_seq;
-  // linear != 0: one matrix (wq, q_cols columns), q_out = bf16(residual + bf16(x wq)) with plain
-  // [rows, q_cols] rows; no RoPE, no cache, the batch and table fields are unused
+  // linear == 1: one matrix (wq, q_cols columns), q_out = bf16(residual + bf16(x wq)) with plain
+  // [rows, q_cols] rows; no RoPE, no cache, the batch and table fields are unused.
+  // linear == 2: the gate and up projections of a feed-forward block as one GEMM: wq = gate, wk = up
+  // (each [hidden, q_cols / 2] packed), q_out [rows, q_cols / 2] = bf16(SiLU(bf16(x gate)) * bf16(x up))
   int linear = 0;
   const __nv_bfloat16* residual = nullptr;  // [rows, q_cols], nullable
   int tile_heads = 0;  // heads per pair tile, 4 or 6; 0: the launcher chooses
 };
 cudaError_t launch_qkv_gemm(const QkvGemmParams& p, cudaStream_t stream);
-// out = bf16(SiLU(gate) * up) over `elements` (a multiple of 8) bf16 values; out may alias gate or up
-cudaError_t launch_silu_mul(const void* gate, const void* up, void* out, size_t elements, cudaStream_t stream);
 // row-major [hidden, cols] -> per (64 k-rows, 64 columns) an 8 KiB block in the GEMM's shared-memory layout
 cudaError_t launch_pack_weights(const void* src, void* dst, int hidden, int cols, cudaStream_t stream);
 

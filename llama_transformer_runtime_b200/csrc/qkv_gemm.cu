@@ -82,10 +82,13 @@ struct HeadSrc {
   const __nv_bfloat16* w;  // packed weights of its matrix
   int heads;               // heads (64-column blocks) of that matrix
   int head;                // head index inside the matrix
-  int which;               // 0 Q, 1 K, 2 V (projection with RoPE + append); 3: plain linear layer with residual
+  int which;               // 0 Q, 1 K, 2 V (projection with RoPE + append); 3: plain linear layer with residual;
+                           // 4: gate (even g) or up (odd g) head of the fused feed-forward GEMM
 };
 __device__ __forceinline__ HeadSrc head_src(const QkvGemmParams& p, int g) {
   const int hq = p.q_cols / 64, hk = p.kv_cols / 64;
+  // gate and up heads alternate, so that a tile holds both accumulators of its output columns
+  if (p.linear == 2) return HeadSrc{(g & 1) ? p.wk : p.wq, p.q_cols / 128, g >> 1, 4};
   if (p.linear) return HeadSrc{p.wq, hq, g, 3};
   if (g < hq) return HeadSrc{p.wq, hq, g, 0};
   if (g < hq + hk) return HeadSrc{p.wk, hk, g - hq, 1};
@@ -238,12 +241,37 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap x_map, QkvGemmParams p) {
       unsigned char* stage = sm + warp * 4096;  // 32 rows x 128 bytes per warp, in the (then idle) stage ring
       const bool acc_ok = wait_or_abort(bar_acc, 0, abort_flag);
       tc_fence_after();
+      // gate/up mode: a warp takes every other PAIR of heads (gate at hb, up at hb + 1)
+      const bool gate_up = p.linear == 2;
 #pragma unroll 1
-      for (int hb = hb0; acc_ok && hb < n_heads; hb += kEpiWarps / 4) {
+      for (int hb = gate_up ? 2 * hb0 : hb0; acc_ok && hb < n_heads; hb += gate_up ? kEpiWarps / 2 : kEpiWarps / 4) {
         uint32_t acc[2][32];
-        tmem_ld32(tmem + lane_base + hb * 64, acc[0]);
-        tmem_ld32(tmem + lane_base + hb * 64 + 32, acc[1]);
-        tmem_wait_ld();
+        uint32_t lo[16], hi[16];  // bf16 pairs of elements 0..31 and 32..63
+        if (gate_up) {
+          // h = bf16(SiLU(bf16 gate) * bf16 up), the reference's GEMM outputs and its SiLU kernel's arithmetic
+          // (src/kernels/silu/silu_8192.cu:55-100), as ffn_gate_up_kernel computes them for decode rows
+#pragma unroll
+          for (int half = 0; half < 2; half++) {
+            tmem_ld32(tmem + lane_base + hb * 64 + half * 32, acc[0]);
+            tmem_ld32(tmem + lane_base + (hb + 1) * 64 + half * 32, acc[1]);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+              const float g0f = __bfloat162float(__float2bfloat16_rn(__uint_as_float(acc[0][2 * i])));
+              const float g1f = __bfloat162float(__float2bfloat16_rn(__uint_as_float(acc[0][2 * i + 1])));
+              const float u0f = __bfloat162float(__float2bfloat16_rn(__uint_as_float(acc[1][2 * i])));
+              const float u1f = __bfloat162float(__float2bfloat16_rn(__uint_as_float(acc[1][2 * i + 1])));
+              const float s0 = __fmul_rn(g0f, 1.0f / (1.0f + __expf(-g0f)));
+              const float s1 = __fmul_rn(g1f, 1.0f / (1.0f + __expf(-g1f)));
+              const uint32_t v = pack_bf16(__fmul_rn(s0, u0f), __fmul_rn(s1, u1f));
+              if (half == 0) lo[i] = v; else hi[i] = v;
+            }
+          }
+        } else {
+          tmem_ld32(tmem + lane_base + hb * 64, acc[0]);
+          tmem_ld32(tmem + lane_base + hb * 64 + 32, acc[1]);
+          tmem_wait_ld();
+        }
         // rows without a token skip the stores; the warp meets again before the next
         // (warp-wide, aligned) tensor-memory load
         __syncwarp();
@@ -251,8 +279,9 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap x_map, QkvGemmParams p) {
         const HeadSrc hs = head_src(p, g0 + hb);
         const int which = hs.which, head = hs.head;
         // the GEMM's bf16 output, then RoPE on it: element i pairs with i + 32
-        uint32_t lo[16], hi[16];  // bf16 pairs of elements 0..31 and 32..63
-        if (which == 3) {
+        if (which == 4) {
+          // lo and hi are made above
+        } else if (which == 3) {
           // plain output: bf16 of the accumulator, then (optionally) the residual added in fp32 and
           // rounded once more, as the reference's GEMM and residual_add kernels do in turn
           const size_t at = (size_t)row * p.q_cols + head * 64;
@@ -326,6 +355,9 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap x_map, QkvGemmParams p) {
             if (hs.which == 0 || hs.which == 3) {
               const size_t r = (size_t)(m0 + quarter * 32 + rr);
               reinterpret_cast<uint4*>(p.q_out + (r * (p.q_cols / 64) + hs.head) * kHeadDim)[c] = v;
+            } else if (hs.which == 4) {  // rows of q_cols / 2 columns: one output head per gate/up pair
+              const size_t r = (size_t)(m0 + quarter * 32 + rr);
+              reinterpret_cast<uint4*>(p.q_out + (r * (p.q_cols / 128) + hs.head) * kHeadDim)[c] = v;
             } else {
               char* tile = p.storage + tile_off(info >> 4, p.kv_heads, hs.head, hs.which == 2 ? 1 : 0);
               *reinterpret_cast<uint4*>(tile + tile_chunk_off(info & 15, c)) = v;
@@ -475,6 +507,8 @@ cudaError_t launch_qkv_gemm(const QkvGemmParams& p, cudaStream_t stream) {
     };
     q.tile_heads = cost(4) < cost(kTileHeads) ? 4 : kTileHeads;
   }
+  // (Launch order: pairs of one activation tile next to each other.  Pairs of one weight tile next to
+  // each other made no difference on 2048 x 16384 x 2048: 308 against 310 us per layer of a prompt.)
   const dim3 grid(2 * ((total_heads + q.tile_heads - 1) / q.tile_heads), row_pairs);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;

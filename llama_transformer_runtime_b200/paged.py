@@ -402,7 +402,7 @@ def ffn(weights: "FfnWeights", layer: int, x, h_scratch, out, rows: int, add_res
 def ffn_rows(pool: "KVPool", packed_weights: "FfnWeights", layer: int, x, scratch, out, rows: int,
              add_residual: bool = True, stream: int = 0) -> None:
     """The feed-forward block for a prompt chunk on the tensor cores; gate/up/down of the descriptor packed by
-    pack_projection_weights; scratch holds rows * (hidden + 2 * inter) bf16."""
+    pack_projection_weights; scratch holds rows * (hidden + inter) bf16."""
     check(lib().pa_ffn_rows(pool._h, C.byref(packed_weights), layer, _ptr(x), _ptr(scratch), _ptr(out), rows,
                             int(add_residual), stream))
 
