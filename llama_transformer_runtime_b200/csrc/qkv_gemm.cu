@@ -421,6 +421,276 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap x_map, QkvGemmParams p) {
 }
 
 
+// ---- the plain and the gate/up GEMM over many tiles: persistent pairs -------------------------
+// When a launch has more pair tiles than the GPU has SM pairs (the gate/up GEMM of a prompt: 2048 x
+// 16384 x 2048), CTAs that follow one another on an SM overlap nothing: a tile's set-up and epilogue
+// (about a third of its time) run with the tensor cores idle.  Here a pair stays and takes tiles
+// pair, pair + pairs, ...: tiles of 4 heads (256 columns), so that tensor memory holds TWO accumulator
+// sets (2 x 256 columns); the loader and the MMA warp run on into the next tile while warps 0-7 read
+// the previous tile's accumulators, and hand the set back with an arrival on the first CTA's
+// "accumulators free" barrier (8 warps of each CTA; the peer's arrive remotely, release at cluster
+// scope: the MMAs that follow overwrite the peer's tensor memory).  Same operand layouts, MMA shapes
+// and epilogue arithmetic as qkv_gemm_kernel's linear modes; no RoPE, no cache.
+constexpr int kPHeads = 4;                                  // heads per pair tile
+constexpr int kPStageBytes = kABytes + (kPHeads / 2) * kBBlock;  // 32 KiB
+constexpr int kPOffStaging = kGStages * kPStageBytes;       // 8 warps x 4 KiB, no longer inside the ring
+constexpr int kPOffBar = kPOffStaging + kEpiWarps * 4096;
+constexpr int kPOffMisc = kPOffBar + (3 * kGStages + 4) * 8;
+constexpr int kPSmem = kPOffMisc + 16 + 112;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+linear_gemm_persistent_kernel(const __grid_constant__ CUtensorMap x_map, QkvGemmParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) {
+    if (threadIdx.x == 0) atomicExch(p.status, kStatusBadBlock);
+    return;
+  }
+  unsigned char* sm = smem_raw;
+  const uint32_t bar_full = base + kPOffBar, bar_empty = bar_full + 8 * kGStages;
+  const uint32_t bar_peer = bar_empty + 8 * kGStages;     // first CTA only: the peer's stage is full
+  const uint32_t bar_acc_full = bar_peer + 8 * kGStages;  // [2]: an accumulator set is complete (both CTAs)
+  const uint32_t bar_acc_free = bar_acc_full + 16;        // [2], first CTA only: both CTAs have read the set
+  uint32_t* s_tmem_base = reinterpret_cast<uint32_t*>(sm + kPOffMisc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kPOffMisc + 4);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int total_heads = p.q_cols / 64;
+  const int col_tiles = (total_heads + kPHeads - 1) / kPHeads;
+  const int row_pairs = (p.rows + 2 * kGM - 1) / (2 * kGM);
+  const int n_tiles = col_tiles * row_pairs;
+  const int pair = (int)(blockIdx.x >> 1), n_pairs = (int)(gridDim.x >> 1);
+  const int k_steps = p.hidden / kGK;
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kGStages; s++) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+      mbar_init(bar_peer + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(bar_acc_full + 8 * b, 1);
+      mbar_init(bar_acc_free + 8 * b, 2 * kEpiWarps);
+    }
+    mbar_fence_init();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc_pair(base + kPOffMisc, kGTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem = *s_tmem_base;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  if (warp == kLoadWarp) {
+    // ===================== loads: lane 0 the A tile, lanes 1, 2 this CTA's head blocks ==========
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = pair; ok && t < n_tiles; t += n_pairs) {
+      const int g0 = (t % col_tiles) * kPHeads, m0 = ((t / col_tiles) * 2 + (int)rank) * kGM;
+      const int n_heads = min(kPHeads, total_heads - g0);  // 2 or 4
+      const bool have_rows = m0 < p.rows;
+      const int slot = lane - 1;
+      const char* b_img = nullptr;
+      size_t b_step = 0;
+      if (slot >= 0 && slot < n_heads / 2) {
+        const HeadSrc h = head_src(p, g0 + (int)rank * (n_heads / 2) + slot);
+        b_img = reinterpret_cast<const char*>(h.w) + (size_t)h.head * kBBlock;
+        b_step = (size_t)h.heads * kBBlock;
+      }
+      const uint32_t tx = (have_rows ? kABytes : 0) + (uint32_t)(n_heads / 2) * kBBlock;
+      for (int ks = 0; ks < k_steps; ks++, it++) {
+        const int st = it % kGStages;
+        if (!wait_or_abort(bar_empty + 8 * st, ((it / kGStages) & 1) ^ 1, abort_flag)) {
+          ok = false;
+          break;
+        }
+        const uint32_t sA = base + st * kPStageBytes, sB = sA + kABytes;
+        if (lane == 0) mbar_expect_tx(bar_full + 8 * st, tx);
+        __syncwarp();
+        if (lane == 0 && have_rows) tensor_g2s_2d(sA, &x_map, ks * kGK, m0, bar_full + 8 * st);
+        if (b_img) bulk_g2s(sB + slot * kBBlock, b_img + (size_t)ks * b_step, kBBlock, bar_full + 8 * st);
+        __syncwarp();
+      }
+    }
+  } else if (warp < kEpiWarps) {
+    // ===================== epilogue: warp w reads lane quarter w % 4, heads (pairs) w / 4, ... ====
+    const int quarter = warp & 3, hb0 = warp >> 2;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const bool gate_up = p.linear == 2;
+    unsigned char* stage = sm + kPOffStaging + warp * 4096;
+    uint32_t tile_iter = 0;
+    for (int t = pair; t < n_tiles; t += n_pairs, tile_iter++) {
+      const int g0 = (t % col_tiles) * kPHeads, m0 = ((t / col_tiles) * 2 + (int)rank) * kGM;
+      const int n_heads = min(kPHeads, total_heads - g0);
+      const uint32_t set = tile_iter & 1, acc = tmem + set * 256 + lane_base;
+      const int row = m0 + quarter * 32 + lane;
+      const bool valid = row < p.rows;
+      if (!wait_or_abort(bar_acc_full + 8 * set, (tile_iter >> 1) & 1, abort_flag)) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int hb = gate_up ? 2 * hb0 : hb0; hb < n_heads; hb += 2) {
+        uint32_t a[2][32];
+        uint32_t lo[16], hi[16];
+        int out_head, out_heads;
+        if (gate_up) {
+          out_head = (g0 + hb) >> 1;
+          out_heads = p.q_cols / 128;
+#pragma unroll
+          for (int half = 0; half < 2; half++) {
+            tmem_ld32(acc + hb * 64 + half * 32, a[0]);
+            tmem_ld32(acc + (hb + 1) * 64 + half * 32, a[1]);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+              const float g0f = __bfloat162float(__float2bfloat16_rn(__uint_as_float(a[0][2 * i])));
+              const float g1f = __bfloat162float(__float2bfloat16_rn(__uint_as_float(a[0][2 * i + 1])));
+              const float u0f = __bfloat162float(__float2bfloat16_rn(__uint_as_float(a[1][2 * i])));
+              const float u1f = __bfloat162float(__float2bfloat16_rn(__uint_as_float(a[1][2 * i + 1])));
+              const float s0 = __fmul_rn(g0f, 1.0f / (1.0f + __expf(-g0f)));
+              const float s1 = __fmul_rn(g1f, 1.0f / (1.0f + __expf(-g1f)));
+              const uint32_t v = pack_bf16(__fmul_rn(s0, u0f), __fmul_rn(s1, u1f));
+              if (half == 0) lo[i] = v; else hi[i] = v;
+            }
+          }
+        } else {
+          out_head = g0 + hb;
+          out_heads = p.q_cols / 64;
+          tmem_ld32(acc + hb * 64, a[0]);
+          tmem_ld32(acc + hb * 64 + 32, a[1]);
+          tmem_wait_ld();
+          const size_t at = (size_t)row * p.q_cols + (size_t)out_head * 64;
+          uint4 rl[4], rh[4];
+          const bool res = p.residual && valid;
+          if (res) {
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+              rl[c] = reinterpret_cast<const uint4*>(p.residual + at)[c];
+              rh[c] = reinterpret_cast<const uint4*>(p.residual + at)[c + 4];
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 16; i++) {
+            float a0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(a[0][2 * i])));
+            float a1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(a[0][2 * i + 1])));
+            float b0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(a[1][2 * i])));
+            float b1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(a[1][2 * i + 1])));
+            if (res) {
+              const uint32_t ra = reinterpret_cast<const uint32_t*>(rl)[i], rb = reinterpret_cast<const uint32_t*>(rh)[i];
+              a0 += __uint_as_float(ra << 16);
+              a1 += __uint_as_float(ra & 0xffff0000u);
+              b0 += __uint_as_float(rb << 16);
+              b1 += __uint_as_float(rb & 0xffff0000u);
+            }
+            lo[i] = pack_bf16(a0, a1);
+            hi[i] = pack_bf16(b0, b1);
+          }
+        }
+        __syncwarp();  // the staging tile's previous rows have been written out
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          *reinterpret_cast<uint4*>(stage + tile_chunk_off(lane, c)) =
+              make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
+          *reinterpret_cast<uint4*>(stage + tile_chunk_off(lane, c + 4)) =
+              make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
+        }
+        __syncwarp();
+        // 32 rows out four at a time, 8 lanes per row: whole 128-byte lines per store
+        const int rr0 = lane >> 3, c = lane & 7;
+        const unsigned valid_rows = __ballot_sync(0xffffffffu, valid);
+#pragma unroll
+        for (int it8 = 0; it8 < 8; it8++) {
+          const int rr = it8 * 4 + rr0;
+          if (!((valid_rows >> rr) & 1u)) continue;
+          const uint4 v = *reinterpret_cast<const uint4*>(stage + tile_chunk_off(rr, c));
+          const size_t r = (size_t)(m0 + quarter * 32 + rr);
+          reinterpret_cast<uint4*>(p.q_out + (r * out_heads + out_head) * kHeadDim)[c] = v;
+        }
+      }
+      // this warp has read its share of the set: hand it back to the MMA warp of the first CTA
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0)
+          mbar_arrive(bar_acc_free + 8 * set);
+        else
+          asm volatile(
+              "{\n\t.reg .b32 ra;\n\tmapa.shared::cluster.u32 ra, %0, %1;\n\t"
+              "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}" ::"r"(bar_acc_free + 8 * set),
+              "r"(0)
+              : "memory");
+      }
+      __syncwarp();
+    }
+  } else if (rank == 0) {
+    // ===================== MMA issue (first CTA of the pair) ====================
+    constexpr uint64_t kLboNextHead = (uint64_t)(kBBlock >> 4) << 16;
+    uint32_t it = 0, tile_iter = 0;
+    bool ok = true;
+    for (int t = pair; ok && t < n_tiles; t += n_pairs, tile_iter++) {
+      const int g0 = (t % col_tiles) * kPHeads;
+      const int n_heads = min(kPHeads, total_heads - g0);
+      const uint32_t set = tile_iter & 1, d_tmem = tmem + set * 256;
+      const uint32_t idesc = idesc_bf16(2 * kGM, 64 * n_heads, true);
+      // the set's previous tile (two tiles ago) has been read by all 16 epilogue warps of the pair
+      if (!wait_or_abort_cluster(bar_acc_free + 8 * set, ((tile_iter >> 1) & 1) ^ 1, abort_flag)) break;
+      tc_fence_after();
+      for (int ks = 0; ks < k_steps; ks++, it++) {
+        const int st = it % kGStages;
+        const uint32_t par = (it / kGStages) & 1;
+        if (!wait_or_abort(bar_full + 8 * st, par, abort_flag) ||
+            !wait_or_abort_cluster(bar_peer + 8 * st, par, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (elect_one()) {
+          const uint32_t sA = base + st * kPStageBytes, sB = sA + kABytes;
+#pragma unroll
+          for (int kk = 0; kk < kGK / 16; kk++)
+            umma_ss_pair(d_tmem, smem_desc_sw128(sA + kk * 32),
+                         (smem_desc_sw128(sB + kk * 2048) & ~((uint64_t)0x3FFF << 16)) | kLboNextHead, idesc,
+                         (ks > 0 || kk > 0) ? 1u : 0u);
+          tc_commit_pair(bar_empty + 8 * st, 3);
+          if (ks + 1 == k_steps) tc_commit_pair(bar_acc_full + 8 * set, 3);
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ===================== peer: forward "my stage is full" to the first CTA =====
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = pair; ok && t < n_tiles; t += n_pairs)
+      for (int ks = 0; ks < k_steps; ks++, it++) {
+        const int st = it % kGStages;
+        if (!wait_or_abort(bar_full + 8 * st, (it / kGStages) & 1, abort_flag)) {
+          ok = false;
+          break;
+        }
+        if (lane == 0) mbar_arrive_remote(bar_peer + 8 * st, 0);
+        __syncwarp();
+      }
+  }
+
+  // ---- common exit: the pair meets, then tensor memory is released --------------
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && *abort_flag) atomicExch(p.status, kStatusTimeout);
+  cluster_sync_all();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem, kGTmemCols);
+  }
+}
+
+
 // Row-major [hidden, cols] weights -> the shared-memory image the GEMM copies:
 // block (k-tile of 64 rows, head of 64 columns) = 64 rows of 128 bytes, 16-byte
 // chunk c of row r stored at c ^ (r & 7).  One thread per 16-byte chunk.
@@ -491,6 +761,31 @@ cudaError_t launch_qkv_gemm(const QkvGemmParams& p, cudaStream_t stream) {
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return cudaErrorInvalidValue;
+  // more pair tiles than SM pairs, no RoPE or cache: the persistent form
+  {
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int p_tiles = ((total_heads + kPHeads - 1) / kPHeads) * ((p.rows + 2 * kGM - 1) / (2 * kGM));
+    if (p.linear && p_tiles > sms / 2) {
+      static bool p_configured[64] = {};
+      if (dev >= 0 && dev < 64 && !p_configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(linear_gemm_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPSmem);
+        if (e != cudaSuccess) return e;
+        p_configured[dev] = true;
+      }
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2 * (sms / 2));
+      cfg.blockDim = dim3(kGemmThreads);
+      cfg.dynamicSmemBytes = kPSmem;
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      return cudaLaunchKernelEx(&cfg, linear_gemm_persistent_kernel, x_map, p);
+    }
+  }
   // x: the two CTAs of a pair (the kernel's compile-time cluster) next to each other
   // Tile width: 6 heads per pair, or 4 where that fills the SMs better (2048 columns are 5 1/3 tiles of
   // 6 heads = 96 CTAs for 2048 rows, but 8 tiles of 4 = 128 CTAs of two thirds the work).  Cost of a

@@ -280,10 +280,11 @@ def test_out_project_with_residual(cuda, rows, layers, with_residual):
         bf16_close(got[0], to_u16(want), "out_project against the reference GEMM + residual")
 
 
-@pytest.mark.parametrize("rows,with_residual", [(300, True), (128, False)])
+@pytest.mark.parametrize("rows,with_residual", [(300, True), (128, False), (2400, True)])
 def test_out_project_rows_on_tensor_cores(cuda, rows, with_residual):
     """Output projection of a prompt chunk (the projection GEMM with a plain epilogue) against the
-    oracle and the reference GEMM + residual."""
+    oracle and the reference GEMM + residual.  2400 rows are more pair tiles than SM pairs: the persistent
+    form of the kernel (two accumulator sets in tensor memory), with a last row pair of one CTA's rows."""
     rng = np.random.default_rng(900 + rows)
     a = orc.randn_bf16(rng, (rows, 2048))
     wo = orc.randn_bf16(rng, (2048, 2048), 0.03)
