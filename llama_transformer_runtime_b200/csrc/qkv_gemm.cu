@@ -38,7 +38,7 @@
 //               holds two of them, 8 KiB apart: the descriptor's leading byte offset) and one
 //               M256 N128 K16 (heads 4, 5), and frees the stage in BOTH CTAs with a multicast
 //               tcgen05.commit.
-// Measured on B200, 2048 tokens, per layer over 16 layers: 41.9 us with one CTA per 256 x 256
+// Measured on B200, 2048 tokens, per layer over 16 layers (the Q/K/V launch): 41.9 us with one CTA per 256 x 256
 // tile and a packing kernel for the activations; 37.1 us as pairs with the tensor map and the
 // coalesced epilogue; 34.8 us with the row lookups moved in front of the accumulator wait; 31.6 us
 // with programmatic dependent launch between consecutive calls; 23.2 us (1110 TFLOP/s) once the
