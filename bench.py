@@ -245,6 +245,8 @@ def run_decode(env: Env, args, workload: str, sub: bool = False):
 
     rank, local_rank, world, dev = env.rank, env.local_rank, env.world, env.dev
     wl = WORKLOADS[workload]
+    if getattr(args, "ctx", 0) and not sub:  # another context length on the same workload (planner experiments)
+        wl = dict(ctx=args.ctx, name=f"decode_ctx{args.ctx}_x{LAYERS}layers_batch1")
     ctx = wl["ctx"]
     steps = args.steps
     repeats = 5 if sub else max(1, args.repeats)
@@ -2075,6 +2077,7 @@ def main():
                     choices=sorted(WORKLOADS) + ["prefill2k", "append2k", "batch64", "qkv_decode", "out_project", "qkv_prefill",
                                                   "decode_chain", "block_chain", "lm_head", "token", "prompt"])
     ap.add_argument("--chain-ctx", type=int, default=4096, help="decode_chain: context length")
+    ap.add_argument("--ctx", type=int, default=0, help="decode128k / decode4k: another context length (0 = the workload's own)")
     ap.add_argument("--no-sub", action="store_true", help="default workload: skip the sub-blocks")
     ap.add_argument("--sub", default="", help="default workload: comma-separated sub-blocks to run (default: all)")
     ap.add_argument("--seqs", type=int, default=64, help="batch64: number of sequences")
