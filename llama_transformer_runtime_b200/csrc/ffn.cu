@@ -22,6 +22,7 @@
 // sums are added in rank order by the cluster's first CTA, which reads its peers' shared memory, so
 // the result does not depend on scheduling.
 #include <cstdio>
+#include <cstdlib>
 
 #include "../../include/paged_attention.h"
 #include "kernels.cuh"
@@ -352,6 +353,250 @@ __global__ void __cluster_dims__(kDownSplit, 1, 1) __launch_bounds__(kThreads, 2
   cluster_sync_all();  // the peers' shared memory stays until the first CTA has read it
 }
 
+// ---- the same two kernels on the tensor cores ---------------------------------------------------
+// With fused multiply-adds a thread spends about 50 instructions on every 16 bytes of weights
+// (unpacking, 8 x rows multiply-adds, addresses), and the stream slows down with every row: 25, 27.5,
+// 35 and 60 us per layer for 1, 2, 4 and 8 rows.  Here a warp copies its 16 weight rows of a step
+// (64 bytes each, per matrix) into its own slot of a shared-memory ring with cp.async — no registers
+// held by loads in flight, no CTA-wide barrier in the loop — and multiplies them with
+// mma.sync.m16n8k16: A = the step's x values of up to 8 rows (rows 8..15 of the tile are zero), B =
+// the 16 x 8 weight blocks fetched with ldmatrix.trans (16-byte chunks XOR-swizzled by row pair, so
+// that the 8 rows of a matrix fetch hit 8 different bank groups), fp32 accumulators.  Two ldmatrix.x4
+// and four MMAs per matrix and step replace 2 x 50 instructions per lane.  Sums over the 8 warps in
+// warp order, so results do not depend on scheduling; they differ from the multiply-add form in
+// the order of the fp32 additions inside a warp's 16 rows.
+constexpr int kMmaStepRows = 128;            // weight rows per step: 16 per warp
+constexpr int kMmaWarpTile = 16 * 64;        // a warp's rows of one matrix in one step: 1 KiB
+constexpr int kMmaStepBytes = 8 * kMmaWarpTile;  // one matrix, one step: 8 KiB
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&d)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+               : "r"(addr));
+}
+// c += A B with A's rows 8..15 zero: a0 = (row lane/4, k 2(lane%4), +1), a2 = the same row at k + 8
+__device__ __forceinline__ void mma_rows8(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+
+// The stream of NM matrices (1: down, 2: gate and up) over `n_steps` steps of 128 rows starting at row
+// k_first, columns col0 .. col0 + 31, against the rows staged in sx: acc[m][ng] = this warp's partial
+// sums (its 16 rows of every step) for the 8 columns of group ng, rows lane / 4.
+template <int NM, int STAGES>
+struct MmaStream {
+  const __nv_bfloat16* w[NM];
+  size_t n;        // row pitch of the matrices in elements
+  uint32_t ring;   // shared-memory address of STAGES x NM x 8 KiB
+  int n_steps, warp, lane;
+
+  __device__ __forceinline__ void issue(int j) const {
+    if (j < n_steps) {
+      const int slot = j % STAGES;
+#pragma unroll
+      for (int m = 0; m < NM; m++)
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+          const int q = lane + 32 * h, r = q >> 2, c = q & 3;
+          cp_async16(ring + (slot * NM + m) * kMmaStepBytes + warp * kMmaWarpTile + r * 64 + ((c ^ ((r >> 1) & 3)) << 4),
+                     w[m] + (size_t)(j * kMmaStepRows + warp * 16 + r) * n + c * 8);
+        }
+    }
+    cp_async_commit();  // an empty group past the end keeps the count of groups in flight uniform
+  }
+  __device__ __forceinline__ void prologue() const {
+#pragma unroll
+    for (int j = 0; j < STAGES; j++) issue(j);
+  }
+  template <int ROWS>
+  __device__ __forceinline__ void run(const __nv_bfloat16 (*sx)[kSlice], float (&acc)[NM][4][4]) const {
+#pragma unroll
+    for (int m = 0; m < NM; m++)
+#pragma unroll
+      for (int g = 0; g < 4; g++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[m][g][i] = 0.f;
+    const int row = lane >> 2;
+    const int lr = (lane & 7) + ((lane >> 3) & 1) * 8;  // the row of the 16 x 64-byte tile whose address this lane gives
+    const uint32_t lm_off = lr * 64, lm_sw = (lr >> 1) & 3, lm_chunk = lane >> 4;
+    for (int j = 0; j < n_steps; j++) {
+      cp_async_wait<STAGES - 1>();
+      __syncwarp();
+      const int kbase = j * kMmaStepRows + warp * 16 + 2 * (lane & 3);
+      uint32_t a0 = 0, a2 = 0;
+      if (row < ROWS) {
+        a0 = *reinterpret_cast<const uint32_t*>(&sx[row][kbase]);
+        a2 = *reinterpret_cast<const uint32_t*>(&sx[row][kbase + 8]);
+      }
+      const int slot = j % STAGES;
+#pragma unroll
+      for (int m = 0; m < NM; m++) {
+        const uint32_t tile = ring + (slot * NM + m) * kMmaStepBytes + warp * kMmaWarpTile + lm_off;
+#pragma unroll
+        for (int g0 = 0; g0 < 4; g0 += 2) {
+          uint32_t d[4];
+          ldmatrix_x4_trans(tile + (((g0 + lm_chunk) ^ lm_sw) << 4), d);
+          mma_rows8(acc[m][g0], a0, a2, d[0], d[1]);
+          mma_rows8(acc[m][g0 + 1], a0, a2, d[2], d[3]);
+        }
+      }
+      __syncwarp();  // every lane has read the slot
+      issue(j + STAGES);
+    }
+    cp_async_wait<0>();
+  }
+};
+
+// Partial sums of the 8 warps -> red[warp][row][m][col] (red may lie in the ring: the stream is over).
+template <int NM, int ROWS>
+__device__ __forceinline__ void store_partials(float* red, const float (&acc)[NM][4][4], int warp, int lane) {
+  const int row = lane >> 2, cq = 2 * (lane & 3);
+  if (row < ROWS) {
+#pragma unroll
+    for (int m = 0; m < NM; m++)
+#pragma unroll
+      for (int g = 0; g < 4; g++) {
+        float* at = red + (((size_t)warp * ROWS + row) * NM + m) * kColsPerCta + g * 8 + cq;
+        at[0] = acc[m][g][0];
+        at[1] = acc[m][g][1];
+      }
+  }
+}
+
+constexpr int kGateUpStages = 5, kDownStages = 8;
+template <int ROWS>
+constexpr int gate_up_smem() { return kGateUpStages * 2 * kMmaStepBytes + ROWS * kSlice * 2; }
+template <int ROWS>
+constexpr int down_smem() { return kDownStages * kMmaStepBytes + ROWS * kSlice * 2; }
+
+template <int ROWS>
+__global__ void __launch_bounds__(kThreads, 2) ffn_gate_up_mma_kernel(FfnParams p) {
+  extern __shared__ __align__(128) unsigned char dyn[];
+  __shared__ float nscratch[16];
+  auto sx = reinterpret_cast<__nv_bfloat16(*)[kSlice]>(dyn + kGateUpStages * 2 * kMmaStepBytes);
+  const int col0 = blockIdx.x * kColsPerCta;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  MmaStream<2, kGateUpStages> st;
+  st.w[0] = p.w0 + col0;
+  st.w[1] = p.w1 + col0;
+  st.n = (size_t)p.n;
+  st.ring = pa::smem_u32(dyn);
+  st.n_steps = p.k / kMmaStepRows;
+  st.warp = warp;
+  st.lane = lane;
+  st.prologue();  // the weights do not depend on the kernel in front; x does
+  if (p.pdl) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
+  stage_rows<ROWS>(sx, p.x, (size_t)p.k, p.rows, p.k);
+  __syncthreads();
+  if (p.norm_w) rmsnorm_rows<ROWS>(sx, p.norm_w, p.rows, p.k, p.eps, nscratch);
+  float acc[2][4][4];
+  st.template run<ROWS>(sx, acc);
+  __syncthreads();  // every warp is done with the ring
+  float* red = reinterpret_cast<float*>(dyn);
+  store_partials<2, ROWS>(red, acc, warp, lane);
+  __syncthreads();
+  // over the 8 warps, in warp order; then SiLU(gate) * up on the two bf16 GEMM outputs
+  for (int i = threadIdx.x; i < ROWS * kColsPerCta; i += kThreads) {
+    const int r = i / kColsPerCta, cc = i % kColsPerCta;
+    if (r >= p.rows) continue;
+    float sg = 0.f, su = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < 8; wi++) {
+      sg += red[(((size_t)wi * ROWS + r) * 2 + 0) * kColsPerCta + cc];
+      su += red[(((size_t)wi * ROWS + r) * 2 + 1) * kColsPerCta + cc];
+    }
+    const float g = __bfloat162float(__float2bfloat16_rn(sg));
+    const float u = __bfloat162float(__float2bfloat16_rn(su));
+    const float s = __fmul_rn(g, 1.0f / (1.0f + __expf(-g)));
+    p.out[(size_t)r * p.n + col0 + cc] = __float2bfloat16_rn(__fmul_rn(s, u));
+  }
+}
+
+template <int ROWS>
+__global__ void __cluster_dims__(kDownSplit, 1, 1) __launch_bounds__(kThreads, 2) ffn_down_mma_kernel(FfnParams p) {
+  extern __shared__ __align__(128) unsigned char dyn[];
+  __shared__ float part[ROWS][kColsPerCta];
+  auto sx = reinterpret_cast<__nv_bfloat16(*)[kSlice]>(dyn + kDownStages * kMmaStepBytes);
+  const uint32_t split = cluster_ctarank();
+  const int col0 = (int)(blockIdx.x / kDownSplit) * kColsPerCta;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = p.n;
+  const int k_slice = p.k / kDownSplit;  // rows of Wd this CTA walks
+  const int k0 = (int)split * k_slice;
+  MmaStream<1, kDownStages> st;
+  st.w[0] = p.w0 + (size_t)k0 * n + col0;
+  st.n = (size_t)n;
+  st.ring = pa::smem_u32(dyn);
+  st.n_steps = k_slice / kMmaStepRows;
+  st.warp = warp;
+  st.lane = lane;
+  st.prologue();
+  if (p.pdl) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
+  stage_rows<ROWS>(sx, p.x + k0, (size_t)p.k, p.rows, k_slice);
+  __syncthreads();
+  float acc[1][4][4];
+  st.template run<ROWS>(sx, acc);
+  __syncthreads();
+  float* red = reinterpret_cast<float*>(dyn);
+  store_partials<1, ROWS>(red, acc, warp, lane);
+  __syncthreads();
+  for (int i = threadIdx.x; i < ROWS * kColsPerCta; i += kThreads) {
+    const int r = i / kColsPerCta, cc = i % kColsPerCta;
+    float s = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < 8; wi++) s += red[((size_t)wi * ROWS + r) * kColsPerCta + cc];
+    part[r][cc] = s;
+  }
+  cluster_sync_all();  // every CTA's partial is in its shared memory
+  if (split == 0) {
+    for (int i = threadIdx.x; i < ROWS * kColsPerCta; i += kThreads) {
+      const int r = i / kColsPerCta, cc = i % kColsPerCta;
+      if (r >= p.rows) continue;
+      float s = part[r][cc];
+#pragma unroll
+      for (uint32_t q = 1; q < kDownSplit; q++) s += ld_peer_shared(&part[r][cc], q);
+      __nv_bfloat16 y = __float2bfloat16_rn(s);  // the GEMM's bf16 output
+      if (p.residual)
+        y = __float2bfloat16_rn(__bfloat162float(p.residual[(size_t)r * n + col0 + cc]) + __bfloat162float(y));
+      p.out[(size_t)r * n + col0 + cc] = y;
+    }
+  }
+  cluster_sync_all();  // the peers' shared memory stays until the first CTA has read it
+}
+
+template <typename K>
+cudaError_t launch_dyn(K kern, int ctas, int smem, const FfnParams& p, cudaStream_t st) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ctas);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
 template <typename K>
 cudaError_t launch(K kern, int ctas, int groups, const FfnParams& p, cudaStream_t st) {
   if (!p.pdl) {
@@ -411,7 +656,23 @@ int ffn_impl(const void* x, const void* norm_w, float eps, const void* wg, const
   b.pdl = 1;
   const int ctas_a = inter / kColsPerCta, ctas_b = kDownSplit * (hidden / kColsPerCta);
   cudaError_t e;
+  static const bool fma_form = getenv("PA_FFN_FMA") != nullptr;
   const int groups = (rows + kRowGroup - 1) / kRowGroup;
+  if (!fma_form) {
+    if (rows == 1) {
+      e = launch_dyn(ffn_gate_up_mma_kernel<1>, ctas_a, gate_up_smem<1>(), a, st);
+      if (e == cudaSuccess) e = launch_dyn(ffn_down_mma_kernel<1>, ctas_b, down_smem<1>(), b, st);
+    } else if (rows == 2) {
+      e = launch_dyn(ffn_gate_up_mma_kernel<2>, ctas_a, gate_up_smem<2>(), a, st);
+      if (e == cudaSuccess) e = launch_dyn(ffn_down_mma_kernel<2>, ctas_b, down_smem<2>(), b, st);
+    } else if (rows <= 4) {
+      e = launch_dyn(ffn_gate_up_mma_kernel<4>, ctas_a, gate_up_smem<4>(), a, st);
+      if (e == cudaSuccess) e = launch_dyn(ffn_down_mma_kernel<4>, ctas_b, down_smem<4>(), b, st);
+    } else {
+      e = launch_dyn(ffn_gate_up_mma_kernel<8>, ctas_a, gate_up_smem<8>(), a, st);
+      if (e == cudaSuccess) e = launch_dyn(ffn_down_mma_kernel<8>, ctas_b, down_smem<8>(), b, st);
+    }
+  } else
   if (rows == 1) {
     e = launch(ffn_gate_up_kernel<1, 8>, ctas_a, 1, a, st);
     if (e == cudaSuccess) e = launch(ffn_down_kernel<1>, ctas_b, 1, b, st);
