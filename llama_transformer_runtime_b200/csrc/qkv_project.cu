@@ -12,17 +12,18 @@
 // inside the decode kernel that consumes q, k, v.
 //
 // Grid (column tile, layer): a CTA owns 32 adjacent output columns (64 bytes of
-// every weight row) of the concatenated [q | k | v] output and walks all K rows:
-// warp w, lane (kr, c) reads the 16-byte chunk c of rows 64 j + 8 w + kr, a
-// rolling window of 16 independent loads in flight per thread (64 KiB per CTA),
-// the first of them issued before x is staged.  x sits in shared
-// memory as bf16.  Partial sums are reduced over the 8 row lanes by shuffles
-// and over the 8 warps through shared memory in a fixed order, so the result
-// does not depend on scheduling.
+// every weight row) of the concatenated [q | k | v] output and walks all K rows in
+// steps of 128: warp w copies rows 16 w .. 16 w + 15 of a step into its own slot of
+// a shared-memory ring with cp.async, the first steps before x is staged, and
+// multiplies them on the tensor cores (mma_stream.cuh: mma.sync m16n8k16 on up to
+// 8 rows of x, ldmatrix.trans for the weight blocks).  x sits in shared memory as
+// bf16.  Partial sums are added over the 8 warps through shared memory in a fixed
+// order, so the result does not depend on scheduling.
 #include <cstdio>
 
 #include "../../include/paged_attention.h"
 #include "kernels.cuh"
+#include "mma_stream.cuh"
 
 namespace pa {
 void set_last_error(const char* msg);
@@ -55,49 +56,39 @@ struct QkvParams {
   int pdl = 0;
 };
 
-// RESIDENT (one layer behind another kernel, launched with programmatic stream serialization): the
-// CTA's whole weight slab (hidden rows x 64 bytes = 128 KiB) is copied into shared memory with
-// cp.async while the kernel in front is still running, so that nothing is left to stream once x
-// is there; the arithmetic and its order are the same as in the streaming form (the results are
-// bit-equal).  The streaming form stays for launches over many layers, where several CTAs per SM
-// keep the stream going.
-template <int ROWS, bool RESIDENT>
-__global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
-  extern __shared__ __align__(16) unsigned char slab[];  // RESIDENT: [hidden][64 bytes]
-  __shared__ __align__(16) __nv_bfloat16 sx[ROWS][kMaxHidden];
-  __shared__ float red[8][ROWS][kColsPerCta];
+// STAGES = 16 (one layer behind another kernel, launched with programmatic stream serialization): the
+// ring holds the CTA's whole weight slab (2048 rows x 64 bytes = 128 KiB), copied while the kernel in
+// front is still running, so that nothing is left to stream once x is there.  STAGES = 8: the
+// streaming form for launches over many layers or column tiles, where several CTAs per SM keep the
+// stream going.  The arithmetic and its order are the same in both (the results are bit-equal).
+template <int ROWS, int STAGES>
+constexpr int rows_smem() { return STAGES * pa::kMmaStepBytes + ROWS * kMaxHidden * 2; }
+
+template <int ROWS, int STAGES>
+__global__ void __launch_bounds__(kThreads, STAGES == 16 ? 1 : 2) qkv_project_kernel(QkvParams p) {
+  extern __shared__ __align__(128) unsigned char dyn[];
+  __shared__ float nscratch[16];
+  auto sx = reinterpret_cast<__nv_bfloat16(*)[kMaxHidden]>(dyn + STAGES * pa::kMmaStepBytes);
   const int t = blockIdx.x, layer = blockIdx.y;
   const int which = t < p.tiles_q ? 0 : (t < p.tiles_qk ? 1 : 2);
   const int col0 = (t - (which == 0 ? 0 : (which == 1 ? p.tiles_q : p.tiles_qk))) * kColsPerCta;
   const int n = p.n[which];
   const __nv_bfloat16* w = p.w[which] + (size_t)layer * p.w_layer_stride[which];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kr = lane >> 2, c = lane & 3;
 
-  // the first 16 weight loads go out before anything else: they do not depend on x
-  const uint4* wp = reinterpret_cast<const uint4*>(w + (size_t)(warp * 8 + kr) * n + col0) + c;
-  const size_t step = (size_t)64 * n / 8;  // 64 rows further, in 16-byte units
-  const int n_steps = p.hidden / 64;
-  uint4 wv[RESIDENT ? 1 : 16];
-  if (RESIDENT) {
-    // chunk i of the slab = 16 bytes at row i / 4, chunk i % 4
-    const __nv_bfloat16* wcol = w + col0;
-    const uint32_t slab_u32 = pa::smem_u32(slab);
-    for (int i = threadIdx.x; i < p.hidden * 4; i += kThreads)
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(slab_u32 + i * 16),
-                   "l"(wcol + (size_t)(i >> 2) * n + (i & 3) * 8)
-                   : "memory");
-    asm volatile("cp.async.commit_group;" ::: "memory");
-  } else {
-#pragma unroll
-    for (int u = 0; u < 16; u++)
-      if (u < n_steps) wv[u] = __ldg(wp + (size_t)u * step);
-  }
+  // the first weight copies go out before anything else: they do not depend on x
+  pa::MmaStream<1, STAGES> st;
+  st.w[0] = w + col0;
+  st.n = (size_t)n;
+  st.ring = pa::smem_u32(dyn);
+  st.n_steps = (p.hidden + pa::kMmaStepRows - 1) / pa::kMmaStepRows;
+  st.warp = warp;
+  st.lane = lane;
+  st.k_total = p.hidden;
+  st.prologue();
 
-  // The weight loads above are all this kernel may do before the kernel in front has finished:
-  // x is its output.  The kernel behind may start its own weight loads from here on.  The rest of
-  // this thread's weight rows are asked into L2 meanwhile (one lane per 64-byte row piece), so that
-  // after the wait the rolling window is fed from L2 instead of from DRAM.
+  // The weight copies above are all this kernel may do before the kernel in front has finished:
+  // x is its output.  The kernel behind may start its own weight copies from here on.
   // The norm weights do not depend on the kernel in front either: this thread's chunks of them are
   // loaded here (one chunk per thread at hidden = 2048), not after the wait behind x.
   uint4 nw_pre[kMaxHidden / 8 / kThreads];
@@ -108,19 +99,16 @@ __global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
       if ((int)threadIdx.x + i * kThreads < p.hidden / 8) nw_pre[i] = __ldg(nwp + threadIdx.x + i * kThreads);
   }
   if (p.pdl) {
-    if (!RESIDENT && (c & 1) == 0)  // both 32-byte sectors of the row's 64-byte piece
-      for (int u = 16; u < n_steps; u++)
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(wp + (size_t)u * step));
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
   }
 
-  // x rows of this layer -> shared memory (rows beyond p.rows are zero)
+  // x rows of this layer -> shared memory (rows beyond p.rows and elements beyond hidden are zero)
   const __nv_bfloat16* x = p.x + (size_t)layer * p.x_layer_stride;
-  for (int i = threadIdx.x; i < ROWS * (p.hidden / 8); i += kThreads) {
-    const int r = i / (p.hidden / 8), ch = i % (p.hidden / 8);
+  for (int i = threadIdx.x; i < ROWS * (kMaxHidden / 8); i += kThreads) {
+    const int r = i / (kMaxHidden / 8), ch = i % (kMaxHidden / 8);
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < p.rows) v = reinterpret_cast<const uint4*>(x + (size_t)r * p.hidden)[ch];
+    if (r < p.rows && ch < p.hidden / 8) v = reinterpret_cast<const uint4*>(x + (size_t)r * p.hidden)[ch];
     reinterpret_cast<uint4*>(&sx[r][0])[ch] = v;
   }
   __syncthreads();
@@ -145,16 +133,16 @@ __global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
       }
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) sum_sq += __shfl_down_sync(0xffffffffu, sum_sq, off);
-      if (lane == 0) red[0][0][warp] = sum_sq;
+      if (lane == 0) nscratch[warp] = sum_sq;
       __syncthreads();
-      float tot = lane < kThreads / 32 ? red[0][0][lane] : 0.0f;
+      float tot = lane < kThreads / 32 ? nscratch[lane] : 0.0f;
       if (warp == 0) {
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) tot += __shfl_down_sync(0xffffffffu, tot, off);
-        if (lane == 0) red[0][0][8] = tot;
+        if (lane == 0) nscratch[8] = tot;
       }
       __syncthreads();
-      const float rms_recip = rsqrtf(red[0][0][8] / static_cast<float>(p.hidden) + p.eps);
+      const float rms_recip = rsqrtf(nscratch[8] / static_cast<float>(p.hidden) + p.eps);
       for (int i = threadIdx.x, ii = 0; i < p.hidden / 8; i += kThreads, ii++) {
         const uint4 xd = reinterpret_cast<const uint4*>(&sx[r][0])[i];
         const uint4 wd = nw_pre[ii];
@@ -171,61 +159,15 @@ __global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
         }
         reinterpret_cast<uint4*>(&sx[r][0])[i] = yd;  // a thread rewrites only chunks it alone read
       }
+      __syncthreads();  // the scratch is reused by the next row; the last one publishes the rows
     }
-    __syncthreads();
   }
 
-  float acc[ROWS][8];
-#pragma unroll
-  for (int r = 0; r < ROWS; r++)
-#pragma unroll
-    for (int i = 0; i < 8; i++) acc[r][i] = 0.f;
-
-  if (RESIDENT) {
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();  // every thread's copies have landed
-  }
-  // rolling window: as soon as a register's row is consumed, the row 16 steps on is requested
-  for (int j0 = 0; j0 < n_steps; j0 += 16) {
-#pragma unroll
-    for (int u = 0; u < 16; u++) {
-      if (j0 + u >= n_steps) break;
-      const int k = (j0 + u) * 64 + warp * 8 + kr;
-      const uint4 wnow = RESIDENT ? *reinterpret_cast<const uint4*>(slab + (size_t)k * 64 + c * 16) : wv[RESIDENT ? 0 : u];
-      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&wnow);
-      float wf[8];
-#pragma unroll
-      for (int i = 0; i < 4; i++) {
-        const float2 f = __bfloat1622float2(h2[i]);
-        wf[2 * i] = f.x;
-        wf[2 * i + 1] = f.y;
-      }
-      if (!RESIDENT && j0 + u + 16 < n_steps) wv[RESIDENT ? 0 : u] = __ldg(wp + (size_t)(j0 + u + 16) * step);
-#pragma unroll
-      for (int r = 0; r < ROWS; r++) {
-        const float xv = __bfloat162float(sx[r][k]);
-#pragma unroll
-        for (int i = 0; i < 8; i++) acc[r][i] = fmaf(xv, wf[i], acc[r][i]);
-      }
-    }
-  }
-  // over the 8 row lanes of the warp
-#pragma unroll
-  for (int r = 0; r < ROWS; r++)
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-      float v = acc[r][i];
-      v += __shfl_xor_sync(0xffffffffu, v, 4);
-      v += __shfl_xor_sync(0xffffffffu, v, 8);
-      v += __shfl_xor_sync(0xffffffffu, v, 16);
-      acc[r][i] = v;
-    }
-  if (kr == 0) {
-#pragma unroll
-    for (int r = 0; r < ROWS; r++)
-#pragma unroll
-      for (int i = 0; i < 8; i++) red[warp][r][c * 8 + i] = acc[r][i];
-  }
+  float acc[1][4][4];
+  st.template run<ROWS>(sx, acc);
+  __syncthreads();  // every warp is done with the ring
+  float* red = reinterpret_cast<float*>(dyn);
+  pa::store_partials<1, ROWS>(red, acc, warp, lane);
   __syncthreads();
   // over the 8 warps, in warp order
   __nv_bfloat16* out = p.out[which] + (size_t)layer * p.out_layer_stride[which];
@@ -234,7 +176,7 @@ __global__ void __launch_bounds__(kThreads) qkv_project_kernel(QkvParams p) {
     if (r >= p.rows) continue;
     float s = 0.f;
 #pragma unroll
-    for (int wi = 0; wi < 8; wi++) s += red[wi][r][cc];
+    for (int wi = 0; wi < 8; wi++) s += red[((size_t)wi * ROWS + r) * kColsPerCta + cc];
     __nv_bfloat16 y = __float2bfloat16_rn(s);  // the GEMM's bf16 output
     if (which == 0 && p.residual) {
       // the reference adds the residual in a second kernel on the bf16 GEMM output
@@ -397,45 +339,40 @@ int qfail(int code, const char* msg) {
 
 // Launch of the row-major projection kernel for 1..8 rows, with programmatic stream serialization
 // when p.pdl is set (the kernel then waits for the kernel in front before it reads x).
-cudaError_t launch_rows(const QkvParams& p, dim3 grid, cudaStream_t st) {
-  // one layer behind another kernel: the form that holds its weight slab in shared memory
-  // (a grid of many waves, the language-model head, streams: its CTAs overlap one another)
-  const bool resident = p.pdl && grid.y == 1 && p.hidden <= kMaxHidden && grid.x <= 512;
-  void (*kern)(QkvParams) = resident ? (p.rows == 1 ? qkv_project_kernel<1, true>
-                                        : p.rows == 2 ? qkv_project_kernel<2, true>
-                                        : p.rows <= 4 ? qkv_project_kernel<4, true>
-                                                      : qkv_project_kernel<8, true>)
-                                     : (p.rows == 1 ? qkv_project_kernel<1, false>
-                                        : p.rows == 2 ? qkv_project_kernel<2, false>
-                                        : p.rows <= 4 ? qkv_project_kernel<4, false>
-                                                      : qkv_project_kernel<8, false>);
-  if (!p.pdl) {
-    kern<<<grid, kThreads, 0, st>>>(p);
-    return cudaGetLastError();
-  }
-  const size_t slab_bytes = resident ? (size_t)p.hidden * 64 : 0;
-  if (resident) {
-    static bool configured[64][4] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    const int ri = p.rows == 1 ? 0 : (p.rows == 2 ? 1 : (p.rows <= 4 ? 2 : 3));
-    if (dev >= 0 && dev < 64 && !configured[dev][ri]) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxHidden * 64);
-      if (e != cudaSuccess) return e;
-      configured[dev][ri] = true;
-    }
+template <auto Kern>
+cudaError_t launch_one(int smem, const QkvParams& p, dim3 grid, cudaStream_t st) {
+  static bool configured[64] = {};  // per kernel (the template argument) and device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(Kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = slab_bytes;
+  cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, p);
+  cfg.numAttrs = p.pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, Kern, p);
+}
+template <int STAGES>
+cudaError_t launch_stages(const QkvParams& p, dim3 grid, cudaStream_t st) {
+  if (p.rows == 1) return launch_one<qkv_project_kernel<1, STAGES>>(rows_smem<1, STAGES>(), p, grid, st);
+  if (p.rows == 2) return launch_one<qkv_project_kernel<2, STAGES>>(rows_smem<2, STAGES>(), p, grid, st);
+  if (p.rows <= 4) return launch_one<qkv_project_kernel<4, STAGES>>(rows_smem<4, STAGES>(), p, grid, st);
+  return launch_one<qkv_project_kernel<8, STAGES>>(rows_smem<8, STAGES>(), p, grid, st);
+}
+cudaError_t launch_rows(const QkvParams& p, dim3 grid, cudaStream_t st) {
+  // one layer behind another kernel: the form that holds its weight slab in shared memory
+  // (a grid of many waves, the language-model head, streams: its CTAs overlap one another)
+  const bool resident = p.pdl && grid.y == 1 && p.hidden <= kMaxHidden && grid.x <= 512;
+  return resident ? launch_stages<16>(p, grid, st) : launch_stages<8>(p, grid, st);
 }
 
 }  // namespace
