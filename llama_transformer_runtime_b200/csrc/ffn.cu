@@ -135,11 +135,16 @@ __device__ __forceinline__ void rmsnorm_rows(__nv_bfloat16 (*sx)[kSlice], const 
   }
 }
 
-constexpr int kGateUpStages = 5, kDownStages = 8;
+// Ring depths, measured in the block chain at 1 row (us per layer; gate/up x down): 3 x 8 38.9, 4 x 8 39.0,
+// 5 x 4 38.7, 5 x 8 36.7, 5 x 12 36.3, 5 x 16 40.3, 6 x 12 36.2.  Two CTAs per SM must fit: 12 steps of
+// the down projection only up to 4 rows.
+constexpr int kGateUpStages = 5;
+template <int ROWS>
+constexpr int kDownStages = ROWS <= 4 ? 12 : 8;
 template <int ROWS>
 constexpr int gate_up_smem() { return kGateUpStages * 2 * kMmaStepBytes + ROWS * kSlice * 2; }
 template <int ROWS>
-constexpr int down_smem() { return kDownStages * kMmaStepBytes + ROWS * kSlice * 2; }
+constexpr int down_smem() { return kDownStages<ROWS> * kMmaStepBytes + ROWS * kSlice * 2; }
 
 template <int ROWS>
 __global__ void __launch_bounds__(kThreads, 2) ffn_gate_up_mma_kernel(FfnParams p) {
@@ -192,14 +197,14 @@ template <int ROWS>
 __global__ void __cluster_dims__(kDownSplit, 1, 1) __launch_bounds__(kThreads, 2) ffn_down_mma_kernel(FfnParams p) {
   extern __shared__ __align__(128) unsigned char dyn[];
   __shared__ float part[ROWS][kColsPerCta];
-  auto sx = reinterpret_cast<__nv_bfloat16(*)[kSlice]>(dyn + kDownStages * kMmaStepBytes);
+  auto sx = reinterpret_cast<__nv_bfloat16(*)[kSlice]>(dyn + kDownStages<ROWS> * kMmaStepBytes);
   const uint32_t split = cluster_ctarank();
   const int col0 = (int)(blockIdx.x / kDownSplit) * kColsPerCta;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = p.n;
   const int k_slice = p.k / kDownSplit;  // rows of Wd this CTA walks
   const int k0 = (int)split * k_slice;
-  MmaStream<1, kDownStages> st;
+  MmaStream<1, kDownStages<ROWS>> st;
   st.w[0] = p.w0 + (size_t)k0 * n + col0;
   st.n = (size_t)n;
   st.ring = pa::smem_u32(dyn);
