@@ -42,6 +42,32 @@ def test_qkv_project_vs_oracle(cuda, rows, layers):
         bf16_close(to_u16(v[l]), orc.gemm_bf16(x[l], wv[l]), f"v layer {l}")
 
 
+@pytest.mark.parametrize("hidden,rows", [(64, 1), (192, 3), (1088, 8), (1984, 2)])
+def test_qkv_project_hidden_sizes_that_end_inside_a_step(cuda, hidden, rows):
+    """The kernel walks the weight rows in steps of 128; a hidden size that is a multiple of 64 but not of
+    128 (or shorter than a step) ends inside one: the tile rows past the end must count as zeros, whatever
+    the memory behind the matrix holds (here: NaN patterns)."""
+    rng = np.random.default_rng(520 + hidden + rows)
+    x = orc.randn_bf16(rng, (1, rows, hidden))
+    n_q, n_kv = 256, 64
+    # each matrix sits in front of a guard filled with NaNs: rows past the end would read it
+    def guarded(n):
+        buf = np.full((hidden + 128, n), 0x7FC0, np.uint16)
+        buf[:hidden] = orc.randn_bf16(rng, (hidden, n), 0.05)
+        return buf
+    wq, wk, wv = guarded(n_q), guarded(n_kv), guarded(n_kv)
+    q = torch.full((1, rows, n_q), 7.0, dtype=torch.bfloat16, device=DEV)
+    k = torch.full((1, rows, n_kv), 7.0, dtype=torch.bfloat16, device=DEV)
+    v = torch.full((1, rows, n_kv), 7.0, dtype=torch.bfloat16, device=DEV)
+    wqd, wkd, wvd = to_dev(wq), to_dev(wk), to_dev(wv)
+    paged.qkv_project(to_dev(x), wqd[:hidden].unsqueeze(0), wkd[:hidden].unsqueeze(0), wvd[:hidden].unsqueeze(0), q, k, v,
+                      rows, 1, hidden=hidden)
+    torch.cuda.synchronize()
+    bf16_close(to_u16(q[0]), orc.gemm_bf16(x[0], wq[:hidden]), "q")
+    bf16_close(to_u16(k[0]), orc.gemm_bf16(x[0], wk[:hidden]), "k")
+    bf16_close(to_u16(v[0]), orc.gemm_bf16(x[0], wv[:hidden]), "v")
+
+
 @pytest.mark.parametrize("rows,layers", [(1, 2), (3, 1), (8, 2)])
 def test_qkv_project_packed_equals_row_major(cuda, rows, layers):
     """The packed-weight kernel adds the same products in a different order: compare with the
