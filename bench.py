@@ -2032,6 +2032,121 @@ def run_prompt(env: Env, args, sub: bool = False):
 
 
 # =============================================================================
+# a whole decode step for several sequences at once
+# =============================================================================
+def run_token_batch(env: Env, args):
+    """pa_decode_token for --seqs sequences (1 to 8) of context --chain-ctx in one step: the weights are
+    read once for all of them (the tensor-core weight stream multiplies up to 8 rows per pass), each
+    sequence reads its own cache.  The reference has no batched step: a Transformer object holds one
+    sequence's cache and decode_forward takes one token, so B sequences cost it B steps; its arm here is
+    the single-sequence step of workload `token`."""
+    torch = env.torch
+    if env.rank != 0:
+        return None  # independent replicas only
+    if args.impl == "reference":
+        line = run_chain(env, args, token=True)
+        if line and "config" in line:
+            line["config"]["note"] = ("the reference has no batched decode step: this is its single-sequence step; "
+                                      "B sequences cost it B of them")
+        return line
+    from oracle import oracle as orc
+    from llama_transformer_runtime_b200 import paged
+    dev = env.dev
+    B = max(1, min(8, args.seqs if args.seqs != 64 else 8))
+    ctx, H, NQ, NKV, INTER, VOC = args.chain_ctx, HIDDEN, Q_HEADS * D, KV_HEADS * D, 8192, 128256
+    steps, warmup = args.steps, args.warmup
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(41)
+    mk = lambda *shape, s=0.03: (torch.randn(*shape, generator=gen, device=dev) * s).to(torch.bfloat16)
+    W = dict(nw=mk(LAYERS, H, s=0.7), wq=mk(LAYERS, H, NQ), wk=mk(LAYERS, H, NKV), wv=mk(LAYERS, H, NKV), wo=mk(LAYERS, NQ, H),
+             fn=mk(LAYERS, H, s=0.7), wg=mk(LAYERS, H, INTER), wu=mk(LAYERS, H, INTER), wd=mk(LAYERS, INTER, H, s=0.02))
+    embed, w_lm, final_norm = mk(VOC, H, s=1.0), mk(H, VOC), mk(H, s=0.7)
+    total_steps = warmup + 2 * steps + 8
+    cos_h, sin_h = orc.build_rope_tables(ctx + total_steps + 2)
+    cos, sin = torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev)
+    need = (ctx + total_steps + BLOCK - 1) // BLOCK
+    num_blocks = B * need + B * need // 4 + 8
+    pool = paged.KVPool(LAYERS, num_blocks, KV_HEADS, B, need + 1, device=env.local_rank)
+    pool.set_free_order(np.random.default_rng(77).permutation(num_blocks))
+    seqs = [pool.create_seq() for _ in range(B)]
+    ones = torch.ones(ctx, 32, dtype=torch.float32, device=dev)
+    zeros = torch.zeros(ctx, 32, dtype=torch.float32, device=dev)
+    kvgen = torch.Generator(device=dev)
+    kvgen.manual_seed(99)
+    for sq in seqs:  # every sequence its own cache contents, blocks interleaved in the shared pool
+        pool.reserve(sq, ctx)
+        pool.batch_set([sq], [ctx])
+        for layer in range(LAYERS):
+            k = (torch.randn(ctx, KV_HEADS, D, generator=kvgen, device=dev) * 0.5).to(torch.bfloat16)
+            v = (torch.randn(ctx, KV_HEADS, D, generator=kvgen, device=dev) * 0.5).to(torch.bfloat16)
+            pool.append(layer, None, k, v, ones, zeros, None)
+    torch.cuda.synchronize()
+    del ones, zeros
+    WA = paged.attention_weights(W["nw"], W["wq"], W["wk"], W["wv"], W["wo"])
+    WF = paged.ffn_weights(W["fn"], W["wg"], W["wu"], W["wd"])
+    M = paged.model_weights(embed, WA, WF, final_norm, w_lm)
+    tok_host = torch.arange(1000, 1000 + B, dtype=torch.int32).pin_memory()
+    tok_dev = tok_host.to(dev)
+    logits = torch.zeros(B, VOC, dtype=torch.bfloat16, device=dev)
+    state = {"len": ctx}
+
+    def step():
+        state["len"] += 1
+        for sq in seqs:
+            pool.reserve(sq, state["len"])
+        pool.batch_set(seqs)
+        paged.decode_token(pool, M, tok_dev, tok_dev, logits, cos, sin, chained=True)
+
+    def e2e_step():
+        tok_dev.copy_(tok_host, non_blocking=True)
+        step()
+        tok_host.copy_(tok_dev, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    weight_bytes = LAYERS * ((H * (NQ + 2 * NKV) + NQ * H + H) * 2 + (3 * H * INTER + H) * 2) + (H * VOC + H) * 2
+    def nbytes(l0, l1):
+        return sum(weight_bytes + B * (LAYERS * decode_bytes(L) + 2 * H * 2 + 2 * VOC * 2) for L in range(l0 + 1, l1 + 1))
+
+    m0 = env.sampler.mark()
+    for _ in range(warmup):
+        step()
+    l0 = state["len"]
+    ms = local_timed(torch, step, steps)
+    b1 = nbytes(l0, state["len"])
+    l0 = state["len"]
+    ms_e2e = local_timed(torch, e2e_step, steps)
+    b2 = nbytes(l0, state["len"])
+    m1 = env.sampler.mark()
+    pool.check()
+    value = b1 / (ms * 1e-3) / 1e9
+    peak, pk = measured_peak()
+    got = _u16(logits)
+    toks = tok_dev.cpu().numpy()
+    line = {
+        "metric": "decode_token_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms / steps, 4), "us_per_step": round(ms / steps * 1e3, 2),
+        "tokens_per_s": round(B * steps / (ms * 1e-3), 1), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"token_batch{B}_ctx{ctx}_x{LAYERS}layers_vocab{VOC}", "sequences": B, "context": ctx,
+                   "layers": LAYERS, "bytes": "the model's weights once per step + every sequence's cache, embedding row and logits",
+                   "l2": f"{weight_bytes / 1e9:.2f} GB of weights per step"},
+        "e2e": {"value": round(b2 / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s", "h2d_bytes_per_step": 4 * B,
+                "d2h_bytes_per_step": 4 * B, "ms_per_step": round(ms_e2e / steps, 4),
+                "tokens_per_s": round(B * steps / (ms_e2e * 1e-3), 1)},
+        "gpu_launches": (LAYERS * 5 + 3) * steps, "clocks": env.sampler.summary(m0, m1),
+        "checks": {"logits_finite": bool(np.isfinite(orc.bf16_to_f32(got)).all()),
+                   "tokens_are_the_reference_rule_on_their_logits": bool(np.array_equal(toks, orc.argmax_reference_rule(got)))},
+        "roofline": {"bound": "hbm", "kernel": "the 83 launches of pa_decode_token", "achieved": round(value, 1), "peak": peak,
+                     "unit": "GB/s", "frac": round(value / peak, 4), "peak_source": f"of {pk}",
+                     "us_per_launch": round(ms / steps * 1e3 / (LAYERS * 5 + 3), 2), "bytes_per_launch": b1 // steps // (LAYERS * 5 + 3),
+                     "traffic": None},
+        "cpu_baseline": None,
+    }
+    pool.close()
+    return line
+
+
+# =============================================================================
 def decode4k_sub(env: Env, args):
     line = run_decode(env, args, "decode4k", sub=True)
     r = reference_decode(env, "decode4k", 3, 2, with_e2e=False)
@@ -2075,7 +2190,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode128k",
                     choices=sorted(WORKLOADS) + ["prefill2k", "append2k", "batch64", "qkv_decode", "out_project", "qkv_prefill",
-                                                  "decode_chain", "block_chain", "lm_head", "token", "prompt"])
+                                                  "decode_chain", "block_chain", "lm_head", "token", "token_batch", "prompt"])
     ap.add_argument("--chain-ctx", type=int, default=4096, help="decode_chain: context length")
     ap.add_argument("--ctx", type=int, default=0, help="decode128k / decode4k: another context length (0 = the workload's own)")
     ap.add_argument("--no-sub", action="store_true", help="default workload: skip the sub-blocks")
@@ -2149,6 +2264,8 @@ def main():
         line = run_chain(env, args, token=True)
     elif args.workload == "prompt":
         line = run_prompt(env, args)
+    elif args.workload == "token_batch":
+        line = run_token_batch(env, args)
     if rank == 0 and line is not None:
         print(json.dumps(line), flush=True)
     env.sampler.stop()
