@@ -163,13 +163,29 @@ __global__ void __launch_bounds__(kThreads, 2) ffn_gate_up_mma_kernel(FfnParams 
   st.lane = lane;
   st.k_total = p.k;
   st.prologue();  // the weights do not depend on the kernel in front; x does
+  uint4 nw8[ROWS >= 4 ? 8 : 1];   // nor do this lane's chunks of the norm weight (kernels of 4 and 8 rows)
+  if constexpr (ROWS >= 4) {
+    if (p.norm_w) {
+#pragma unroll
+      for (int g = 0; g < 8; g++) nw8[g] = __ldg(reinterpret_cast<const uint4*>(p.norm_w) + g * 32 + lane);
+    }
+  }
   if (p.pdl) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
   }
   stage_rows<ROWS>(sx, p.x, (size_t)p.k, p.rows, p.k);
   __syncthreads();
-  if (p.norm_w) rmsnorm_rows<ROWS>(sx, p.norm_w, p.rows, p.k, p.eps, nscratch);
+  // the reference kernel's arithmetic and summation order either way: with more than 2 rows one warp
+  // per row side by side, else the whole CTA on a row (a warp alone needs 1 us longer for one row)
+  if constexpr (ROWS >= 4) {
+    if (p.norm_w) {
+      if (warp < ROWS && warp < p.rows) rmsnorm_row_by_warp(&sx[warp][0], nw8, p.k, p.eps, lane);
+      __syncthreads();
+    }
+  } else {
+    if (p.norm_w) rmsnorm_rows<ROWS>(sx, p.norm_w, p.rows, p.k, p.eps, nscratch);
+  }
   float acc[2][4][4];
   st.template run<ROWS>(sx, acc);
   __syncthreads();  // every warp is done with the ring

@@ -134,4 +134,55 @@ __device__ __forceinline__ void store_partials(float* red, const float (&acc)[NM
   }
 }
 
+// RMSNorm of one staged row by ONE warp, in place: y = bf16((x * rsqrt(mean(x^2) + eps)) * w), with the
+// arithmetic AND the summation order of the reference's kernel (src/kernels/rmsnorm/rmsnorm.cu:51-110,
+// 256 threads: thread t sums the squares of chunk t with fused multiply-adds, each warp combines its 32
+// lanes by shuffle-down 16..1, warp 0 the 8 warp totals the same way).  The warp plays the reference's
+// 8 warps in turn (lane l holds chunks l, 32 + l, ...), so the rows of a step are normalised side by
+// side, one per warp, without a CTA-wide barrier.  hidden a multiple of 256, at most 2048; nw8 = this
+// lane's chunks of the norm weight (chunk 32 g + lane in nw8[g]).
+__device__ __forceinline__ void rmsnorm_row_by_warp(__nv_bfloat16* row, const uint4 (&nw8)[8], int hidden, float eps, int lane) {
+  const int groups = hidden / 256;  // the reference's warps that hold data
+  uint4 data[8];
+  float tot = 0.0f;
+#pragma unroll
+  for (int g = 0; g < 8; g++) {
+    if (g >= groups) continue;
+    data[g] = reinterpret_cast<const uint4*>(row)[g * 32 + lane];
+    const __nv_bfloat162* bf = reinterpret_cast<const __nv_bfloat162*>(&data[g]);
+    float s = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const float2 v = __bfloat1622float2(bf[j]);
+      s = __fmaf_rn(v.x, v.x, s);
+      s = __fmaf_rn(v.y, v.y, s);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) s += __shfl_down_sync(0xffffffffu, s, off);
+    s = __shfl_sync(0xffffffffu, s, 0);  // total of group g, on every lane
+    if (lane == g) tot = s;
+  }
+  // second level: lanes 0..groups-1 hold the group totals, the rest zero, shuffle-down again
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) tot += __shfl_down_sync(0xffffffffu, tot, off);
+  tot = __shfl_sync(0xffffffffu, tot, 0);
+  const float rms_recip = rsqrtf(tot / static_cast<float>(hidden) + eps);
+#pragma unroll
+  for (int g = 0; g < 8; g++) {
+    if (g >= groups) continue;
+    const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&data[g]);
+    const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&nw8[g]);
+    uint4 yd;
+    __nv_bfloat162* yb = reinterpret_cast<__nv_bfloat162*>(&yd);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const float2 xf = __bfloat1622float2(xb[j]);
+      const float2 wf = __bfloat1622float2(wb[j]);
+      yb[j] = __floats2bfloat162_rn(__fmul_rn(__fmul_rn(xf.x, rms_recip), wf.x),
+                                    __fmul_rn(__fmul_rn(xf.y, rms_recip), wf.y));
+    }
+    reinterpret_cast<uint4*>(row)[g * 32 + lane] = yd;
+  }
+}
+
 }  // namespace pa

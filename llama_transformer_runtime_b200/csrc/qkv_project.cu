@@ -96,12 +96,27 @@ __global__ void __launch_bounds__(kThreads, STAGES == 16 ? 1 : 2) qkv_project_ke
   // x is its output.  The kernel behind may start its own weight copies from here on.
   // The norm weights do not depend on the kernel in front either: this thread's chunks of them are
   // loaded here (one chunk per thread at hidden = 2048), not after the wait behind x.
+  // More than 2 rows of a hidden size that is a multiple of 256 (the model's): one warp per row side by
+  // side (rmsnorm_row_by_warp), every lane with its 8 chunks of the norm weight; else the CTA-wide form
+  // below, a chunk per thread.  Both give the reference kernel's bits.
+  // (decided per instantiation: the kernels of 1 and 2 rows carry none of the other form's code)
+  const bool norm_by_warp = ROWS >= 4 && p.hidden % 256 == 0;  // a warp alone needs 1 us longer for one row
   uint4 nw_pre[kMaxHidden / 8 / kThreads];
+  uint4 nw8[ROWS >= 4 ? 8 : 1];
   if (p.norm_w) {
     const uint4* nwp = reinterpret_cast<const uint4*>(p.norm_w + (size_t)layer * p.norm_layer_stride);
+    if constexpr (ROWS >= 4) {
+      if (norm_by_warp) {
 #pragma unroll
-    for (int i = 0; i < kMaxHidden / 8 / kThreads; i++)
-      if ((int)threadIdx.x + i * kThreads < p.hidden / 8) nw_pre[i] = __ldg(nwp + threadIdx.x + i * kThreads);
+        for (int g = 0; g < 8; g++)
+          if (g < p.hidden / 256) nw8[g] = __ldg(nwp + g * 32 + lane);
+      }
+    }
+    if (!norm_by_warp) {
+#pragma unroll
+      for (int i = 0; i < kMaxHidden / 8 / kThreads; i++)
+        if ((int)threadIdx.x + i * kThreads < p.hidden / 8) nw_pre[i] = __ldg(nwp + threadIdx.x + i * kThreads);
+    }
   }
   if (p.pdl) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -117,7 +132,12 @@ __global__ void __launch_bounds__(kThreads, STAGES == 16 ? 1 : 2) qkv_project_ke
     reinterpret_cast<uint4*>(&sx[r][0])[ch] = v;
   }
   __syncthreads();
-  if (p.norm_w) {
+  if (p.norm_w && norm_by_warp) {
+    if constexpr (ROWS >= 4) {
+      if (warp < ROWS && warp < p.rows) pa::rmsnorm_row_by_warp(&sx[warp][0], nw8, p.hidden, p.eps, lane);
+      __syncthreads();
+    }
+  } else if (p.norm_w) {
     // RMSNorm of the staged rows, in place, with the arithmetic AND the summation order of the
     // reference's kernel (src/kernels/rmsnorm/rmsnorm.cu:51-110, launched with 256 threads): a
     // thread sums the squares of its 8-element chunks in order, lanes combine by shuffle-down
