@@ -76,6 +76,7 @@ struct pa_pool {
   bool no_step_kernel = false;  // pa_pool_set_step_kernel(pool, 0): one kernel per layer
   bool no_layer_overlap = false;  // pa_pool_set_layer_overlap(pool, 0): a layer starts after the previous one has finished
   int step_combiners_override = 0;  // pa_pool_set_step_combiners
+  bool step_has_exchange = false;   // the step being planned ends every layer with a cross-rank exchange
   long long step_launches = 0;  // decode steps that ran as one cooperative launch
   // rows of a decode step between the kernels of pa_attention_step: q, k, v, rotated q, attention
   // output and two block inputs in turn, kMaxStepRows rows each; behind them the feed-forward block's
@@ -368,7 +369,11 @@ static int step_combiners(const pa_pool* p) {
   long long tokens = 0;
   for (const auto& e : p->batch) tokens += e.kv_len;
   const long long bytes_per_layer = tokens * p->kv_heads * 2 * pa::kHeadDim * 2;
-  if (bytes_per_layer > 48ll * 1000 * 1000) return 1;  // more than about 8 us of streaming
+  // With a cross-rank exchange a combining CTA also pushes the pair's words to the peers and waits for
+  // theirs: one CTA per pair keeps up with about 20 us of streaming per layer (2 GPUs on 131072 tokens:
+  // 12 907 GB/s with one, 12 757 with two), not with 10 us (4 GPUs: 22 494 with one, 23 283 with two).
+  const long long one = p->step_has_exchange ? 100ll * 1000 * 1000 : 48ll * 1000 * 1000;
+  if (bytes_per_layer > one) return 1;  // without exchange: more than about 8 us of streaming
   if (bytes_per_layer > 16ll * 1000 * 1000) return 2;
   return 4;
 }
@@ -572,6 +577,7 @@ static int build_step_params(pa_pool* p, pa_exchange* x, int layer_begin, int la
   const FusedAppend fz{k_in, v_in, cos_table, sin_table, q_rot, 0};
   const int saved_sms = p->sm_count;
   p->sm_count = sms;  // the split plan aims at the SMs this step may use
+  p->step_has_exchange = x != nullptr;
   int r = decode_impl(p, layer_begin, q_in, out, out_stride, nullptr, lse, scale, nullptr, x, true, &fz, nullptr, 0,
                       &sp.base, &plan);
   p->sm_count = saved_sms;
